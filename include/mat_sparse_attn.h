@@ -1,0 +1,157 @@
+/*
+ * C ABI of libmat_sparse_attn: the sparse-attention forward of ma-transformer,
+ * written for NVIDIA B200 (sm_100a).  Plain pointers and sizes only; no torch
+ * or pybind types.  Every tensor is row-major [B, S, H, D] with D contiguous,
+ * the layout of the reference's tensors (src/csrc/tensor.cpp:104-110,
+ * src/cuda/sparse_attention_kernel.cu:28-32).
+ *
+ * All entry points return MAT_OK (0) or a MAT_ERR_* code; mat_last_error()
+ * gives the text of the calling thread's last failure.  Device entry points
+ * enqueue work on the given stream and return without synchronising, as the
+ * reference's extension does (sparse_attention_kernel.cu:450-456).
+ */
+#ifndef MAT_SPARSE_ATTN_H
+#define MAT_SPARSE_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MAT_OK 0
+#define MAT_ERR_INVALID 1      /* malformed argument (shape, pointer, pattern) */
+#define MAT_ERR_UNSUPPORTED 2  /* valid request outside what the kernels cover */
+#define MAT_ERR_CUDA 3         /* a CUDA call failed; text holds its message */
+#define MAT_ERR_WORKSPACE 4    /* workspace missing, misaligned or too small */
+
+/* element types of q, k, v, o (the reference computes in fp32 only,
+ * src/csrc/attention_types.hpp:10; bf16/fp16 accumulate in fp32) */
+#define MAT_F32 0
+#define MAT_BF16 1
+#define MAT_F16 2
+
+/* pattern kinds, after AttentionPattern (src/csrc/attention_types.hpp:26-38) */
+#define MAT_WINDOW 0      /* SLIDING_WINDOW, causal or two-sided, optionally dilated */
+#define MAT_BLOCK 1       /* BLOCK_SPARSE over an explicit block-CSR layout */
+#define MAT_LONGFORMER 2  /* LONGFORMER: window plus global tokens */
+
+/*
+ * Key set of one query row.  With p = i + q_offset the position of query row
+ * i in key coordinates and S_kv the number of key rows:
+ *   MAT_WINDOW      { p + t*dilation : -left <= t <= right } within [0, S_kv)
+ *                   (src/csrc/sparse_attention.cpp:190-197 with left = right =
+ *                   window_size; dilation per doc/sparse_attention_whitepaper.md:102-105)
+ *   MAT_BLOCK       all keys of the key blocks listed in row floor(p/block) of
+ *                   the block-CSR layout, minus keys j > p when causal != 0
+ *                   (src/csrc/sparse_attention.cpp:209-227 is the layout
+ *                   |row - col| <= 1, causal = 0).  Column ids within a row
+ *                   must be distinct.
+ *   MAT_LONGFORMER  [p-left, p+right] united with the global positions; a query
+ *                   at a global position takes every key
+ *                   (src/csrc/sparse_attention.cpp:241-256, de-duplicated).
+ *                   global_idx must be sorted ascending without repeats.
+ * A row whose set is empty produces zeros.
+ * blk_rowptr, blk_colidx and global_idx are DEVICE pointers for
+ * mat_sparse_attn_fwd and HOST pointers for mat_pattern_rowset / mat_pattern_nnz.
+ */
+typedef struct mat_pattern_spec {
+    int32_t kind;
+    int32_t causal;
+    int64_t left;
+    int64_t right;
+    int64_t dilation;
+    int64_t block;
+    int64_t n_qblocks;
+    const int32_t *blk_rowptr; /* [n_qblocks + 1] */
+    const int32_t *blk_colidx;
+    int64_t n_global;
+    const int64_t *global_idx;
+    int64_t q_offset;
+} mat_pattern_spec;
+
+/* Library version, major*10000 + minor*100 + patch. */
+int mat_version(void);
+
+/* Text of the calling thread's most recent error ("" when none). */
+const char *mat_last_error(void);
+
+/*
+ * Forward pass on device buffers.  Replaces sparse_forward_cuda and its kernel
+ * (src/cuda/sparse_attention_kernel.cu:423-458, 211-263) and, for the general
+ * patterns, the intent of SparseAttention::forward
+ * (src/csrc/sparse_attention.cpp:11-41).
+ *   q, o: [B, S_q, H, D]; k, v: [B, S_kv, H, D]; S_kv >= S_q + q_offset lets a
+ *   sequence shard carry halo rows in front of (and behind) its own keys.
+ *   scale <= 0 selects 1/sqrt(D) (sparse_attention_kernel.cu:442).
+ *   workspace: device scratch of at least mat_sparse_attn_workspace_bytes()
+ *   bytes, 256-byte aligned; may be NULL when that size is 0.
+ */
+int mat_sparse_attn_fwd(const void *q, const void *k, const void *v, void *o,
+                        int64_t B, int64_t S_q, int64_t S_kv, int64_t H, int64_t D,
+                        int dtype, const mat_pattern_spec *spec, float scale,
+                        void *workspace, size_t workspace_bytes, void *stream);
+
+/* Scratch bytes mat_sparse_attn_fwd needs for this problem (0 for most). */
+size_t mat_sparse_attn_workspace_bytes(int64_t B, int64_t S_q, int64_t S_kv, int64_t H,
+                                       int64_t D, int dtype, const mat_pattern_spec *spec);
+
+/*
+ * The reference extension's call, unchanged in meaning: keys [i-w, i+w],
+ * w >= 0 (0 = the query itself), w beyond S clamps
+ * (sparse_attention_kernel.cu:423-458: forward(query, key, value, window_size)).
+ */
+int mat_sparse_attn_fwd_window(const void *q, const void *k, const void *v, void *o,
+                               int64_t B, int64_t S, int64_t H, int64_t D, int dtype,
+                               int64_t window_size, void *stream);
+
+/*
+ * Forward pass on HOST buffers: the counterpart of the CPU engine's call
+ * ma_core.compute_sparse_attention and the marshalling around it
+ * (src/csrc/ma_core.cpp:160-246, src/layers/ma_core_bridge.py:102-112,157-181).
+ * Copies q, k, v to the device in sequence chunks, runs the forward and copies
+ * o back, overlapping the three on internal streams; returns after o is
+ * complete in host memory.  staging is caller-owned DEVICE scratch of at least
+ * mat_sparse_attn_host_staging_bytes() bytes (256-byte aligned).  Pinned host
+ * buffers make the copies asynchronous; pageable ones work but serialise.
+ * spec pointers are device pointers, as for mat_sparse_attn_fwd.
+ */
+int mat_sparse_attn_fwd_host(const void *q_host, const void *k_host, const void *v_host,
+                             void *o_host, int64_t B, int64_t S, int64_t H, int64_t D,
+                             int dtype, const mat_pattern_spec *spec, float scale,
+                             void *staging, size_t staging_bytes, int device);
+
+size_t mat_sparse_attn_host_staging_bytes(int64_t B, int64_t S, int64_t H, int64_t D,
+                                          int dtype, const mat_pattern_spec *spec);
+
+/*
+ * Host-side index sets: the sorted, duplicate-free key positions of query row
+ * i, the single source the kernels' masks are checked against.  Counterpart of
+ * the COO generators (src/csrc/ma_core.cpp:34-48,
+ * src/csrc/sparse_attention.cpp:181-259).  Returns the count in *n_out; when
+ * cap is too small nothing is written and MAT_ERR_INVALID is returned with the
+ * needed count in *n_out.
+ */
+int mat_pattern_rowset(const mat_pattern_spec *spec, int64_t S_kv, int64_t i,
+                       int64_t *out, int64_t cap, int64_t *n_out);
+
+/* Number of (query, key) pairs over query rows [0, S_q): the pattern's nnz. */
+int mat_pattern_nnz(const mat_pattern_spec *spec, int64_t S_q, int64_t S_kv, int64_t *nnz_out);
+
+/* Name of the kernel family the last mat_sparse_attn_fwd call on this thread
+ * selected ("rowwarp", "mma_window", ...): lets tests assert which path ran. */
+const char *mat_last_kernel(void);
+
+/*
+ * Reads and clears the device status word of the current device (synchronises
+ * with it).  0 = every kernel ran to completion; 1 = a kernel gave up on a
+ * bounded wait for a staged tile and left its outputs incomplete.  No
+ * counterpart in the reference, whose kernel never waits.
+ */
+int mat_device_status(int *status_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MAT_SPARSE_ATTN_H */

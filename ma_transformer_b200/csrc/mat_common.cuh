@@ -1,0 +1,73 @@
+// Shared declarations of libmat_sparse_attn's translation units: element-type
+// helpers, the device-side copy of the pattern description, error plumbing and
+// the launchers each kernel file exports to the C-ABI layer.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/mat_sparse_attn.h"
+
+namespace mat {
+
+// Pattern description as the kernels see it (pointers are device pointers).
+struct DevPattern {
+    int32_t kind;
+    int32_t causal;
+    int64_t left, right, dilation;
+    int64_t block, n_qblocks;
+    const int32_t *rowptr;
+    const int32_t *colidx;
+    int64_t n_global;
+    const int64_t *gidx;
+    int64_t q_offset;
+};
+
+struct Problem {
+    const void *q, *k, *v;
+    void *o;
+    int64_t B, Sq, Skv, H, D;
+    int dtype;
+    float scale;
+    DevPattern pat;
+    void *workspace;
+    size_t workspace_bytes;
+    cudaStream_t stream;
+};
+
+// error plumbing (api.cu)
+int fail(int code, const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);
+void note_kernel(const char *name);
+// validation + kernel selection shared by the device and host entry points (api.cu)
+int make_problem(Problem &p, const void *q, const void *k, const void *v, void *o, int64_t B,
+                 int64_t S_q, int64_t S_kv, int64_t H, int64_t D, int dtype,
+                 const mat_pattern_spec *spec, float scale, void *ws, size_t ws_bytes, void *stream);
+int run_problem(const Problem &p);
+
+// kernel families; each returns MAT_OK or a MAT_ERR_* after recording the text
+int launch_rowwarp(const Problem &p);        // rowwarp.cu: any pattern, any D <= 512
+bool mma_flash_supports(const Problem &p);   // mma_flash.cu
+int launch_mma_flash(const Problem &p);
+size_t mma_flash_workspace_bytes(const Problem &p);
+int flash_status_read_and_clear(int *out);   // status word left by a kernel whose bounded wait ran out
+
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    static __device__ __forceinline__ float to_f(float x) { return x; }
+    static __device__ __forceinline__ float from_f(float x) { return x; }
+};
+template <> struct Elem<__nv_bfloat16> {
+    static __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+    static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
+};
+template <> struct Elem<__half> {
+    static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+    static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
+};
+
+static inline size_t dtype_size(int dtype) { return dtype == MAT_F32 ? 4 : 2; }
+
+}  // namespace mat

@@ -1,0 +1,430 @@
+// Tiled forward for 16-bit inputs with head width 64: per query tile, fused
+// Q*K^T -> online softmax -> P*V on the warp-level tensor-core path, with Q and
+// the K/V window (halo included) staged in shared memory by TMA.
+//
+// This is the kernel for the narrow-window patterns, which are bound by HBM
+// traffic: every Q/K/V row is one 128-byte line, fetched once per tile by a
+// tiled bulk-tensor copy (128-byte swizzle, so ldmatrix reads are free of bank
+// conflicts), and the output tile leaves through a bulk-tensor store.  Replaces
+// sparse_attention_forward_warp (src/cuda/sparse_attention_kernel.cu:211-263),
+// which re-reads K/V per query row from global memory with 4-byte loads.
+//
+// Work decomposition
+//   - A dilated window over [B,S,H,64] is a plain window over the same memory
+//     viewed as [B, S/dil, dil*H, 64]: query p = m*dil + r attends keys
+//     (m+t)*dil + r, so residue r behaves as dil*H independent heads.  The
+//     kernel only ever sees dil = 1.
+//   - One CTA per (batch, head, tile of TQ queries); TQ/16 consumer warps own
+//     16 query rows each, one extra warp issues the TMA loads through a ring of
+//     64-key K/V stages guarded by full/empty mbarriers.
+//   - A warp skips the 16-key column pairs that lie wholly outside its rows'
+//     key set and masks only the pairs that straddle the edge of it.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <algorithm>
+#include <mutex>
+
+#include "mat_common.cuh"
+#include "ptx.cuh"
+
+namespace mat {
+namespace {
+
+constexpr int TK = 64;               // keys per stage
+constexpr int kStages = 3;
+constexpr int kRowBytes = 128;       // 64 elements of 2 bytes
+constexpr int kStageBytes = 2 * TK * kRowBytes;  // K then V
+
+// status words a kernel can leave in g_flash_status (0 = fine)
+constexpr int kStatusWaitTimeout = 1;
+__device__ int g_flash_status = 0;
+
+struct FlashParams {
+    int32_t Sq1, Skv1, off1;  // query rows, key rows and q_offset of one sub-sequence
+    int32_t left, right;      // window taps (clamped to Skv1)
+    int32_t n_tiles;          // query tiles per (batch, head)
+    int32_t HH;               // heads seen by the kernel (dil * H)
+    float sl2;                // scale * log2(e)
+    DevPattern pat;           // block layout (block, rowptr, colidx, causal)
+};
+
+__device__ __forceinline__ uint32_t swz(uint32_t base, int row, int chunk16) {
+    return base + row * kRowBytes + ((chunk16 ^ (row & 7)) << 4);
+}
+
+// The staged key chunks of one query tile: chunk c starts at key base(c).
+template <int KIND>
+struct Chunks {
+    int n;
+    int start;          // window: first key of chunk 0
+    int e0, per_blk;    // block: first CSR entry, 64-key chunks per block
+    const int32_t *colidx;
+    int block;
+    __device__ __forceinline__ Chunks(const FlashParams &P, int q0, int TQ) {
+        n = 0; start = 0; e0 = 0; per_blk = 1; colidx = nullptr; block = 0;
+        if (KIND == MAT_WINDOW) {
+            int lo = q0 + P.off1 - P.left;
+            if (lo < 0) lo = 0;
+            lo &= ~15;
+            int hi = q0 + TQ - 1 + P.off1 + P.right;
+            if (hi > P.Skv1 - 1) hi = P.Skv1 - 1;
+            start = lo;
+            n = hi >= lo ? (hi - lo) / TK + 1 : 0;
+        } else {
+            block = (int)P.pat.block;
+            per_blk = block / TK;
+            colidx = P.pat.colidx;
+            const int64_t r = (int64_t)(q0 + P.off1) / block;
+            if (r < P.pat.n_qblocks) {
+                e0 = P.pat.rowptr[r];
+                n = (P.pat.rowptr[r + 1] - e0) * per_blk;
+            }
+        }
+    }
+    __device__ __forceinline__ int base(int c) const {
+        if (KIND == MAT_WINDOW) return start + c * TK;
+        return colidx[e0 + c / per_blk] * block + (c % per_blk) * TK;
+    }
+};
+
+template <typename T, int KIND, int TQ>
+__global__ void __launch_bounds__((TQ / 16 + 1) * 32)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                 const FlashParams P) {
+    constexpr int NW = TQ / 16;  // consumer warps
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *sQ = smem;
+    uint8_t *sKV = smem + TQ * kRowBytes;
+    uint64_t *bar_q = (uint64_t *)(sKV + kStages * kStageBytes);
+    uint64_t *bar_full = bar_q + 1;
+    uint64_t *bar_empty = bar_full + kStages;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int64_t w = blockIdx.x;
+    const int hh = (int)(w % P.HH);
+    const int tile = (int)((w / P.HH) % P.n_tiles);
+    const int b = (int)(w / ((int64_t)P.HH * P.n_tiles));
+    const int q0 = tile * TQ;
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(bar_q, 1);
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(bar_full + s, 1);
+            ptx::mbar_init(bar_empty + s, NW);
+        }
+        ptx::fence_barrier_init();
+    }
+    __syncthreads();
+
+    const Chunks<KIND> chunks(P, q0, TQ);
+
+    if (warp == NW) {  // ---- producer warp: one lane feeds the ring ----
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&map_q);
+            ptx::prefetch_tensormap(&map_k);
+            ptx::prefetch_tensormap(&map_v);
+            ptx::mbar_expect_tx(bar_q, TQ * kRowBytes);
+            ptx::tma_load_4d(sQ, &map_q, bar_q, 0, hh, q0, b);
+            for (int c = 0; c < chunks.n; ++c) {
+                const int s = c % kStages, use = c / kStages;
+                if (use > 0 && !ptx::mbar_wait(bar_empty + s, (use - 1) & 1)) {
+                    atomicExch(&g_flash_status, kStatusWaitTimeout);
+                    break;
+                }
+                uint8_t *dst = sKV + s * kStageBytes;
+                const int kb = chunks.base(c);
+                ptx::mbar_expect_tx(bar_full + s, kStageBytes);
+                ptx::tma_load_4d(dst, &map_k, bar_full + s, 0, hh, kb, b);
+                ptx::tma_load_4d(dst + TK * kRowBytes, &map_v, bar_full + s, 0, hh, kb, b);
+            }
+        }
+        return;
+    }
+
+    // ---- consumer warps ----
+    const int g = lane >> 2;   // row within the 8-row group
+    const int tq = lane & 3;   // column pair within an 8-wide tile
+    const int row0 = warp * 16;                 // first row of this warp inside the tile
+    const int p_min = q0 + row0 + P.off1;       // key-coordinate position of that row
+    const int p_max = p_min + 15;
+
+    if (!ptx::mbar_wait(bar_q, 0)) {
+        atomicExch(&g_flash_status, kStatusWaitTimeout);
+        return;
+    }
+    uint32_t qa[4][4];
+    {
+        const uint32_t q_base = ptx::smem_u32(sQ);
+        const int r = row0 + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) ptx::ldmatrix_x4(qa[ks], swz(q_base, r, 2 * ks + (lane >> 4)));
+    }
+
+    float o[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY};
+    float l_run[2] = {0.f, 0.f};
+
+    for (int c = 0; c < chunks.n; ++c) {
+        const int s = c % kStages, use = c / kStages;
+        if (!ptx::mbar_wait(bar_full + s, use & 1)) {
+            atomicExch(&g_flash_status, kStatusWaitTimeout);
+            return;
+        }
+        const int kb = chunks.base(c);
+
+        // which 16-key pairs does this warp need, and which of those need no mask
+        uint32_t need = 0, whole = 0;
+        {
+            int k_lo, k_hi, f_lo, f_hi;  // needed key range; range where no row is masked
+            if (KIND == MAT_WINDOW) {
+                k_lo = max(p_min - P.left, 0);
+                k_hi = min(p_max + P.right, P.Skv1 - 1);
+                f_lo = max(p_max - P.left, 0);
+                f_hi = min(p_min + P.right, P.Skv1 - 1);
+            } else {
+                k_lo = 0;
+                k_hi = P.pat.causal ? min(p_max, P.Skv1 - 1) : P.Skv1 - 1;
+                f_lo = 0;
+                f_hi = P.pat.causal ? min(p_min, P.Skv1 - 1) : P.Skv1 - 1;
+            }
+#pragma unroll
+            for (int pt = 0; pt < 4; ++pt) {
+                const int a = kb + 16 * pt, z = a + 15;
+                if (z >= k_lo && a <= k_hi) need |= 1u << pt;
+                if (a >= f_lo && z <= f_hi) whole |= 1u << pt;
+            }
+        }
+
+        if (need) {
+            const uint32_t k_base = ptx::smem_u32(sKV + s * kStageBytes);
+            const uint32_t v_base = k_base + TK * kRowBytes;
+            float sc[8][4];
+            float mloc[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int pt = 0; pt < 4; ++pt) {
+                if (!((need >> pt) & 1)) continue;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sc[2 * pt][e] = sc[2 * pt + 1][e] = 0.f;
+                const int kr = 16 * pt + (lane & 7) + (lane >> 4) * 8;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    uint32_t kf[4];
+                    ptx::ldmatrix_x4(kf, swz(k_base, kr, 2 * ks + ((lane >> 3) & 1)));
+                    ptx::Mma<T>::run(sc[2 * pt], qa[ks], kf[0], kf[1]);
+                    ptx::Mma<T>::run(sc[2 * pt + 1], qa[ks], kf[2], kf[3]);
+                }
+                if (!((whole >> pt) & 1)) {
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int j = kb + 16 * pt + 8 * half + 2 * tq + (e & 1);
+                            const int p = p_min + g + (e >> 1) * 8;
+                            bool ok = j >= 0 && j < P.Skv1;
+                            if (KIND == MAT_WINDOW) ok = ok && j >= p - P.left && j <= p + P.right;
+                            else ok = ok && (!P.pat.causal || j <= p);
+                            if (!ok) sc[2 * pt + half][e] = -INFINITY;
+                        }
+                }
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    mloc[0] = fmaxf(mloc[0], fmaxf(sc[2 * pt + half][0], sc[2 * pt + half][1]));
+                    mloc[1] = fmaxf(mloc[1], fmaxf(sc[2 * pt + half][2], sc[2 * pt + half][3]));
+                }
+            }
+            float m_use[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                mloc[i] = fmaxf(mloc[i], __shfl_xor_sync(0xffffffffu, mloc[i], 1));
+                mloc[i] = fmaxf(mloc[i], __shfl_xor_sync(0xffffffffu, mloc[i], 2));
+                const float m_new = fmaxf(m_run[i], mloc[i]);
+                m_use[i] = m_new == -INFINITY ? 0.f : m_new;
+                const float alpha = ptx::ex2((m_run[i] - m_use[i]) * P.sl2);
+                m_run[i] = m_new;
+                l_run[i] *= alpha;
+#pragma unroll
+                for (int n = 0; n < 8; ++n) {
+                    o[n][2 * i] *= alpha;
+                    o[n][2 * i + 1] *= alpha;
+                }
+                m_use[i] *= P.sl2;
+            }
+#pragma unroll
+            for (int pt = 0; pt < 4; ++pt) {
+                if (!((need >> pt) & 1)) continue;
+                uint32_t pa[4];
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const float p0 = ptx::ex2(fmaf(sc[2 * pt + half][0], P.sl2, -m_use[0]));
+                    const float p1 = ptx::ex2(fmaf(sc[2 * pt + half][1], P.sl2, -m_use[0]));
+                    const float p2 = ptx::ex2(fmaf(sc[2 * pt + half][2], P.sl2, -m_use[1]));
+                    const float p3 = ptx::ex2(fmaf(sc[2 * pt + half][3], P.sl2, -m_use[1]));
+                    l_run[0] += p0 + p1;
+                    l_run[1] += p2 + p3;
+                    pa[2 * half] = ptx::Mma<T>::pack(p0, p1);
+                    pa[2 * half + 1] = ptx::Mma<T>::pack(p2, p3);
+                }
+                const int vr = 16 * pt + (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+                for (int dp = 0; dp < 4; ++dp) {
+                    uint32_t vf[4];
+                    ptx::ldmatrix_x4_trans(vf, swz(v_base, vr, 2 * dp + (lane >> 4)));
+                    ptx::Mma<T>::run(o[2 * dp], pa, vf[0], vf[1]);
+                    ptx::Mma<T>::run(o[2 * dp + 1], pa, vf[2], vf[3]);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar_empty + s);
+    }
+
+    // ---- epilogue: normalise, stage the warp's 16 rows in its own Q rows, bulk store ----
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+        l_run[i] = l_run[i] > 0.f ? 1.f / l_run[i] : 0.f;
+    }
+    __syncwarp();  // every lane has read its Q fragments before the rows are overwritten
+    {
+        uint8_t *so = sQ + row0 * kRowBytes;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = g + 8 * i;
+                const uint32_t v = ptx::Mma<T>::pack(o[n][2 * i] * l_run[i], o[n][2 * i + 1] * l_run[i]);
+                *reinterpret_cast<uint32_t *>(so + r * kRowBytes + ((n ^ (r & 7)) << 4) + tq * 4) = v;
+            }
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && q0 + row0 < P.Sq1) {
+            ptx::tma_store_4d(&map_o, so, 0, hh, q0 + row0, b);
+            ptx::tma_store_commit();
+            ptx::tma_store_wait_read();
+        }
+    }
+}
+
+// ---- host side ------------------------------------------------------------
+
+PFN_cuTensorMapEncodeTiled encode_fn() {
+    static PFN_cuTensorMapEncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (PFN_cuTensorMapEncodeTiled)p;
+    });
+    return fn;
+}
+
+// [B, S1*HH, 64] 16-bit rows seen as dims {64, HH, S1, B}; box = {64, 1, box_rows, 1}.
+int make_map(CUtensorMap *m, const void *base, int dtype, int64_t HH, int64_t S1, int64_t B,
+             int box_rows) {
+    PFN_cuTensorMapEncodeTiled enc = encode_fn();
+    if (!enc) return fail(MAT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[4] = {64, (cuuint64_t)HH, (cuuint64_t)S1, (cuuint64_t)B};
+    const cuuint64_t strides[3] = {(cuuint64_t)kRowBytes, (cuuint64_t)HH * kRowBytes,
+                                   (cuuint64_t)S1 * HH * kRowBytes};
+    const cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(m, dtype == MAT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                     4, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MAT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return MAT_OK;
+}
+
+template <int TQ> constexpr size_t smem_bytes() {
+    return 1024 + (size_t)TQ * kRowBytes + (size_t)kStages * kStageBytes + 8 * (1 + 2 * kStages);
+}
+
+template <typename T, int KIND, int TQ>
+int launch_kind(const Problem &p, const FlashParams &fp, int64_t dil) {
+    CUtensorMap mq, mk, mv, mo;
+    const int64_t HH = fp.HH;
+    if (int rc = make_map(&mq, p.q, p.dtype, HH, p.Sq / dil, p.B, TQ)) return rc;
+    if (int rc = make_map(&mk, p.k, p.dtype, HH, p.Skv / dil, p.B, TK)) return rc;
+    if (int rc = make_map(&mv, p.v, p.dtype, HH, p.Skv / dil, p.B, TK)) return rc;
+    if (int rc = make_map(&mo, p.o, p.dtype, HH, p.Sq / dil, p.B, 16)) return rc;
+    auto kern = flash_fwd_kernel<T, KIND, TQ>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<TQ>());
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(flash_fwd_kernel)");
+    const int64_t ctas = (int64_t)fp.n_tiles * HH * p.B;
+    if (ctas > 0x7fffffffLL) return fail(MAT_ERR_UNSUPPORTED, "too many query tiles for one launch");
+    kern<<<(unsigned)ctas, (TQ / 16 + 1) * 32, smem_bytes<TQ>(), p.stream>>>(mq, mk, mv, mo, fp);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "flash_fwd_kernel launch");
+    note_kernel(KIND == MAT_WINDOW ? "mma_window" : "mma_block");
+    return MAT_OK;
+}
+
+template <typename T>
+int launch_t(const Problem &p) {
+    constexpr int TQ = 64;
+    const int64_t dil = p.pat.kind == MAT_WINDOW ? p.pat.dilation : 1;
+    FlashParams fp;
+    fp.Sq1 = (int32_t)(p.Sq / dil);
+    fp.Skv1 = (int32_t)(p.Skv / dil);
+    fp.off1 = (int32_t)(p.pat.q_offset / dil);
+    fp.left = (int32_t)std::min<int64_t>(p.pat.left, fp.Skv1);
+    fp.right = (int32_t)std::min<int64_t>(p.pat.right, fp.Skv1);
+    fp.n_tiles = (fp.Sq1 + TQ - 1) / TQ;
+    fp.HH = (int32_t)(p.H * dil);
+    fp.sl2 = p.scale * 1.4426950408889634f;
+    fp.pat = p.pat;
+    if (p.pat.kind == MAT_WINDOW) return launch_kind<T, MAT_WINDOW, TQ>(p, fp, dil);
+    return launch_kind<T, MAT_BLOCK, TQ>(p, fp, dil);
+}
+
+}  // namespace
+
+bool mma_flash_supports(const Problem &p) {
+    if (p.dtype != MAT_BF16 && p.dtype != MAT_F16) return false;
+    if (p.D != 64) return false;
+    const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
+    if (al % 16) return false;
+    if (p.Skv >= (1LL << 31) || p.B > 65535) return false;
+    if (p.pat.kind == MAT_WINDOW) {
+        const int64_t dil = p.pat.dilation;
+        if (p.Sq % dil || p.Skv % dil || p.pat.q_offset % dil) return false;
+        if (p.H * dil >= (1LL << 31)) return false;
+        return true;
+    }
+    if (p.pat.kind == MAT_BLOCK) {
+        // query tiles of 64 rows must not straddle a layout row
+        return p.pat.block % 64 == 0 && p.pat.q_offset % 64 == 0;
+    }
+    return false;
+}
+
+size_t mma_flash_workspace_bytes(const Problem &) { return 0; }
+
+int launch_mma_flash(const Problem &p) {
+    return p.dtype == MAT_BF16 ? launch_t<__nv_bfloat16>(p) : launch_t<__half>(p);
+}
+
+int flash_status_read_and_clear(int *out) {
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_flash_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_flash_status, &zero, sizeof(int));
+    return e == cudaSuccess ? MAT_OK : cuda_fail(e, "reading the kernel status word");
+}
+
+}  // namespace mat

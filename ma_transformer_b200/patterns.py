@@ -1,0 +1,181 @@
+"""Attention-pattern descriptions: which keys each query row attends to.
+
+``PatternSpec`` mirrors the reference's ``AttentionConfig`` / ``AttentionPattern``
+vocabulary (src/csrc/attention_types.hpp:26-56: window_size, block_size,
+num_global_tokens, use_causal_mask) in the closed form the kernels consume; it
+never materialises the COO lists the reference's generators build
+(src/csrc/sparse_attention.cpp:181-259, src/csrc/ma_core.cpp:34-48).  The row
+sets are available on the host through ``rowset`` / ``nnz`` for checking masks.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Dict, Optional, Sequence, Tuple
+
+import numpy as np
+
+from . import _native as nat
+
+WINDOW, BLOCK, LONGFORMER = nat.MAT_WINDOW, nat.MAT_BLOCK, nat.MAT_LONGFORMER
+
+
+@dataclass
+class PatternSpec:
+    kind: int = WINDOW
+    left: int = 0           # taps before the query (dilation steps)
+    right: int = 0          # taps after the query
+    dilation: int = 1
+    causal: bool = False    # block layouts: drop keys behind the query
+    block: int = 0
+    blk_rowptr: Optional[np.ndarray] = None   # int32 [n_qblocks+1]
+    blk_colidx: Optional[np.ndarray] = None   # int32, distinct within a row
+    global_idx: Optional[np.ndarray] = None   # int64, sorted, unique
+    q_offset: int = 0       # key-coordinate position of query row 0 (sequence shards)
+    _dev: Dict[str, tuple] = field(default_factory=dict, repr=False, compare=False)
+
+    def __post_init__(self) -> None:
+        if self.kind not in (WINDOW, BLOCK, LONGFORMER):
+            raise ValueError(f"unknown pattern kind {self.kind}")
+        if self.left < 0 or self.right < 0:
+            raise ValueError("window taps must be >= 0")
+        if self.dilation < 1:
+            raise ValueError("dilation must be >= 1")
+        if self.kind == BLOCK:
+            if self.block < 1:
+                raise ValueError("block size must be >= 1")
+            rp = np.ascontiguousarray(self.blk_rowptr, dtype=np.int32)
+            ci = np.ascontiguousarray(self.blk_colidx, dtype=np.int32)
+            if rp.ndim != 1 or len(rp) < 1 or rp[0] != 0 or rp[-1] != len(ci) or np.any(np.diff(rp) < 0):
+                raise ValueError("malformed block-CSR row pointers")
+            for r in range(len(rp) - 1):
+                row = ci[rp[r]:rp[r + 1]]
+                if len(np.unique(row)) != len(row) or np.any(row < 0):
+                    raise ValueError(f"block row {r}: column ids must be distinct and >= 0")
+            self.blk_rowptr, self.blk_colidx = rp, ci
+        if self.kind == LONGFORMER:
+            g = np.unique(np.asarray(self.global_idx if self.global_idx is not None else [], dtype=np.int64))
+            if np.any(g < 0):
+                raise ValueError("global positions must be >= 0")
+            self.global_idx = g
+
+    # ---- constructors ------------------------------------------------------
+    @staticmethod
+    def sliding_window(window_size: int) -> "PatternSpec":
+        """The reference's key set [i-w, i+w] (src/csrc/ma_core.cpp:197-198)."""
+        return PatternSpec(WINDOW, left=int(window_size), right=int(window_size))
+
+    @staticmethod
+    def causal_window(taps: int, dilation: int = 1) -> "PatternSpec":
+        """``taps`` keys ending at the query: i-(taps-1)*dil, ..., i-dil, i."""
+        if taps < 1:
+            raise ValueError("taps must be >= 1")
+        return PatternSpec(WINDOW, left=int(taps) - 1, right=0, dilation=int(dilation))
+
+    @staticmethod
+    def dilated_window(window_size: int, dilation: int) -> "PatternSpec":
+        """Two-sided dilated set { i - t*d : t in [-w, w] }
+        (doc/sparse_attention_whitepaper.md:102-105)."""
+        return PatternSpec(WINDOW, left=int(window_size), right=int(window_size), dilation=int(dilation))
+
+    @staticmethod
+    def block_sparse(block: int, rowptr: Sequence[int], colidx: Sequence[int],
+                     causal: bool = False) -> "PatternSpec":
+        return PatternSpec(BLOCK, block=int(block), causal=bool(causal),
+                           blk_rowptr=np.asarray(rowptr), blk_colidx=np.asarray(colidx))
+
+    @staticmethod
+    def longformer(left: int, right: int, global_idx: Sequence[int]) -> "PatternSpec":
+        return PatternSpec(LONGFORMER, left=int(left), right=int(right),
+                           global_idx=np.asarray(global_idx, dtype=np.int64))
+
+    def shifted(self, q_offset: int) -> "PatternSpec":
+        """Same pattern for a shard whose first query sits at key row ``q_offset``."""
+        return PatternSpec(self.kind, self.left, self.right, self.dilation, self.causal, self.block,
+                           self.blk_rowptr, self.blk_colidx, self.global_idx, int(q_offset))
+
+    # ---- C structs -----------------------------------------------------------
+    def _fill(self, s: nat.MatPatternSpec) -> None:
+        s.kind, s.causal = int(self.kind), int(bool(self.causal))
+        s.left, s.right, s.dilation = int(self.left), int(self.right), int(self.dilation)
+        s.block, s.q_offset = int(self.block), int(self.q_offset)
+        s.n_qblocks = len(self.blk_rowptr) - 1 if self.blk_rowptr is not None else 0
+        s.n_global = len(self.global_idx) if self.global_idx is not None else 0
+
+    def host_struct(self) -> nat.MatPatternSpec:
+        s = nat.MatPatternSpec()
+        self._fill(s)
+        if self.blk_rowptr is not None:
+            s.blk_rowptr = self.blk_rowptr.ctypes.data
+            s.blk_colidx = self.blk_colidx.ctypes.data
+        if self.global_idx is not None and len(self.global_idx):
+            s.global_idx = self.global_idx.ctypes.data
+        return s
+
+    def device_struct(self, device) -> nat.MatPatternSpec:
+        """Struct whose index arrays live on ``device`` (uploaded once, cached)."""
+        import torch
+        key = str(torch.device(device))
+        if key not in self._dev:
+            rp = ci = g = None
+            if self.blk_rowptr is not None:
+                rp = torch.from_numpy(self.blk_rowptr).to(device)
+                ci = torch.from_numpy(self.blk_colidx).to(device) if len(self.blk_colidx) else \
+                    torch.zeros(1, dtype=torch.int32, device=device)
+            if self.global_idx is not None and len(self.global_idx):
+                g = torch.from_numpy(self.global_idx).to(device)
+            self._dev[key] = (rp, ci, g)
+        rp, ci, g = self._dev[key]
+        s = nat.MatPatternSpec()
+        self._fill(s)
+        if rp is not None:
+            s.blk_rowptr, s.blk_colidx = rp.data_ptr(), ci.data_ptr()
+        if g is not None:
+            s.global_idx = g.data_ptr()
+        return s
+
+    # ---- host index sets -------------------------------------------------------
+    def rowset(self, s_kv: int, i: int) -> np.ndarray:
+        """Sorted unique key positions of query row ``i`` (int64)."""
+        s = self.host_struct()
+        n = C.c_int64(0)
+        cap = int(s_kv)
+        out = np.empty(max(cap, 1), dtype=np.int64)
+        nat.check(nat.lib.mat_pattern_rowset(C.byref(s), s_kv, i, out.ctypes.data, cap, C.byref(n)))
+        return out[:n.value].copy()
+
+    def nnz(self, s_q: int, s_kv: Optional[int] = None) -> int:
+        s = self.host_struct()
+        n = C.c_int64(0)
+        nat.check(nat.lib.mat_pattern_nnz(C.byref(s), s_q, s_kv if s_kv is not None else s_q, C.byref(n)))
+        return int(n.value)
+
+
+# ---- block layouts -------------------------------------------------------------
+
+def tridiagonal_block_layout(seq_len: int, block: int) -> Tuple[np.ndarray, np.ndarray]:
+    """The reference's block-sparse layout: block row r holds columns r-1, r, r+1
+    (src/csrc/sparse_attention.cpp:212-227)."""
+    nb = (seq_len + block - 1) // block
+    rowptr, colidx = [0], []
+    for r in range(nb):
+        colidx += [c for c in (r - 1, r, r + 1) if 0 <= c < nb]
+        rowptr.append(len(colidx))
+    return np.asarray(rowptr, np.int32), np.asarray(colidx, np.int32)
+
+
+def band_random_block_layout(n_blocks: int, band: int = 4, n_random: int = 2,
+                             seed: int = 0) -> Tuple[np.ndarray, np.ndarray]:
+    """Causal local band plus random earlier blocks: block row r holds columns
+    max(0, r-band+1)..r and ``n_random`` columns drawn without replacement from
+    the blocks before the band (fewer when fewer exist), columns sorted."""
+    rng = np.random.default_rng(seed)
+    rowptr, colidx = [0], []
+    for r in range(n_blocks):
+        lo = max(0, r - band + 1)
+        cols = list(range(lo, r + 1))
+        if lo > 0 and n_random > 0:
+            cols += sorted(rng.choice(lo, size=min(n_random, lo), replace=False).tolist())
+        colidx += sorted(cols)
+        rowptr.append(len(colidx))
+    return np.asarray(rowptr, np.int32), np.asarray(colidx, np.int32)

@@ -1,0 +1,191 @@
+"""Sequence-sharded forward: one process per GPU, each owning a contiguous chunk
+of the sequence, with the K/V halo rows its windows reach exchanged between
+neighbours by send/recv (NCCL over NVLink on GPUs, gloo on CPU in the tests).
+
+The reference has no distributed path at all; this is the one parallel strategy
+the long-sequence configuration needs.  Window patterns only need the
+``left*dilation`` key rows before the chunk and the ``right*dilation`` rows after
+it, so the collective is a neighbour exchange and nothing else:
+
+  rank r-1  ... | chunk r-1 ]──last `halo_left` rows──▶[ halo | chunk r | halo ]◀──first `halo_right` rows──[ chunk r+1 | ...
+
+Each rank keeps K and V resident in an *extended* buffer
+``[B, halo_left + chunk + halo_right, H, D]`` (the first rank has no front halo,
+the last no back halo); the exchange receives straight into the halo rows, so the
+kernel sees one dense tensor and ``PatternSpec.q_offset`` tells it where the
+chunk's first query sits.  Queries whose windows stay inside the chunk do not
+wait for the exchange: they are launched first, the edge rows after the receive.
+
+(batch, head) pairs are independent, so block-sparse and Longformer layouts
+shard over those instead (``shard_batch_heads``) and need no exchange.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .patterns import PatternSpec, WINDOW
+
+
+@dataclass
+class ShardLayout:
+    """Where one rank's rows sit in the global sequence and in its extended K/V buffer."""
+    rank: int
+    world: int
+    seq_len: int       # global sequence length
+    start: int         # first global row of the chunk
+    rows: int          # rows in the chunk
+    halo_front: int    # halo rows stored before the chunk (0 on the first rank)
+    halo_back: int     # halo rows stored after the chunk (0 on the last rank)
+
+    @property
+    def kv_rows(self) -> int:
+        return self.halo_front + self.rows + self.halo_back
+
+
+def shard_layout(spec: PatternSpec, seq_len: int, rank: int, world: int) -> ShardLayout:
+    if spec.kind != WINDOW:
+        raise ValueError("sequence sharding applies to window patterns; shard (batch, head) pairs for the others")
+    if seq_len % world:
+        raise ValueError(f"sequence length {seq_len} is not divisible by {world} ranks")
+    rows = seq_len // world
+    reach_l, reach_r = spec.left * spec.dilation, spec.right * spec.dilation
+    if max(reach_l, reach_r) > rows:
+        raise ValueError("window reaches past the neighbouring chunk: use fewer ranks")
+    if rows % spec.dilation:
+        raise ValueError("chunk length must be a multiple of the dilation")
+    return ShardLayout(rank, world, seq_len, rank * rows, rows,
+                       reach_l if rank > 0 else 0, reach_r if rank < world - 1 else 0)
+
+
+def shard_batch_heads(n_units: int, rank: int, world: int) -> Tuple[int, int]:
+    """[lo, hi) of the (batch*head) units rank ``rank`` owns; no communication needed."""
+    base, extra = divmod(n_units, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+class SequenceShardedAttention:
+    """Forward of a window pattern over a sequence cut into ``world`` contiguous chunks.
+
+    ``forward_fn(q, k_ext, v_ext, spec, out=...)`` computes one shard into ``out``;
+    it defaults to the native ``sparse_attention_cuda.forward_pattern``.
+    """
+
+    def __init__(self, spec: PatternSpec, seq_len: int, group: Optional[dist.ProcessGroup] = None,
+                 forward_fn: Optional[Callable] = None, overlap: bool = True):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.spec = spec
+        self.layout = shard_layout(spec, seq_len, self.rank, self.world)
+        self.local_spec = spec.shifted(self.layout.halo_front)
+        if forward_fn is None:
+            from . import sparse_attention_cuda
+            forward_fn = sparse_attention_cuda.forward_pattern
+        self.forward_fn = forward_fn
+        self.overlap = overlap
+
+    # ---- buffers -----------------------------------------------------------
+    def alloc_kv(self, B: int, H: int, D: int, dtype, device) -> torch.Tensor:
+        """Extended K (or V) buffer; write the chunk's rows through ``chunk_view``."""
+        return torch.zeros(B, self.layout.kv_rows, H, D, dtype=dtype, device=device)
+
+    def chunk_view(self, ext: torch.Tensor) -> torch.Tensor:
+        L = self.layout
+        return ext[:, L.halo_front:L.halo_front + L.rows]
+
+    # ---- halo exchange -----------------------------------------------------
+    def _p2p_ops(self, k_ext: torch.Tensor, v_ext: torch.Tensor):
+        """send/recv pairs for both tensors; returns (ops, copies_after_recv)."""
+        L, spec = self.layout, self.spec
+        reach_l, reach_r = spec.left * spec.dilation, spec.right * spec.dilation
+        ops, after = [], []
+        peer = lambda r: r if self.group is None else dist.get_global_rank(self.group, r)
+
+        def send(t: torch.Tensor, dst: int):
+            ops.append(dist.P2POp(dist.isend, t if t.is_contiguous() else t.contiguous(), peer(dst), self.group))
+
+        def recv(view: torch.Tensor, src: int):
+            if view.is_contiguous():
+                ops.append(dist.P2POp(dist.irecv, view, peer(src), self.group))
+            else:  # B > 1: the halo rows of the batch items are not adjacent
+                tmp = torch.empty(view.shape, dtype=view.dtype, device=view.device)
+                ops.append(dist.P2POp(dist.irecv, tmp, peer(src), self.group))
+                after.append((view, tmp))
+
+        for ext in (k_ext, v_ext):
+            c0 = L.halo_front
+            if self.rank < self.world - 1 and reach_l:      # my last rows are the next rank's front halo
+                send(ext[:, c0 + L.rows - reach_l:c0 + L.rows], self.rank + 1)
+            if self.rank > 0 and reach_r:                   # my first rows are the previous rank's back halo
+                send(ext[:, c0:c0 + reach_r], self.rank - 1)
+            if L.halo_front:
+                recv(ext[:, :L.halo_front], self.rank - 1)
+            if L.halo_back:
+                recv(ext[:, c0 + L.rows:], self.rank + 1)
+        return ops, after
+
+    def exchange_halos(self, k_ext: torch.Tensor, v_ext: torch.Tensor):
+        """Starts the neighbour exchange; returns a callable that completes it."""
+        ops, after = self._p2p_ops(k_ext, v_ext)
+        works = dist.batch_isend_irecv(ops) if ops else []
+
+        def finish():
+            for w in works:
+                w.wait()
+            for view, tmp in after:
+                view.copy_(tmp)
+        return finish
+
+    # ---- forward -------------------------------------------------------------
+    def edge_rows(self) -> Tuple[int, int]:
+        """Rows at the front / back of the chunk whose windows reach into a halo,
+        rounded up to whole query tiles."""
+        L, spec = self.layout, self.spec
+        unit = 64 * spec.dilation
+        up = lambda x: min(L.rows, -(-x // unit) * unit) if x else 0
+        return up(L.halo_front), up(L.halo_back)
+
+    def forward(self, q: torch.Tensor, k_ext: torch.Tensor, v_ext: torch.Tensor,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """q: this rank's [B, rows, H, D]; k_ext / v_ext: extended buffers holding
+        the chunk's own rows.  Exchanges halos, then computes the chunk."""
+        L = self.layout
+        if q.shape[1] != L.rows or k_ext.shape[1] != L.kv_rows:
+            raise ValueError("tensor lengths do not match this rank's shard layout")
+        if out is None:
+            out = torch.empty_like(q)
+        finish = self.exchange_halos(k_ext, v_ext)
+        front, back = self.edge_rows()
+        if not self.overlap or q.shape[0] != 1 or front + back >= L.rows:
+            finish()
+            self._run(q, k_ext, v_ext, out, 0, L.rows)
+            return out
+        # interior rows first: their windows never leave the chunk
+        self._run(q, k_ext, v_ext, out, front, L.rows - back)
+        finish()
+        if front:
+            self._run(q, k_ext, v_ext, out, 0, front)
+        if back:
+            self._run(q, k_ext, v_ext, out, L.rows - back, L.rows)
+        return out
+
+    def _run(self, q, k_ext, v_ext, out, a: int, b: int) -> None:
+        if b <= a:
+            return
+        spec = self.spec.shifted(self.layout.halo_front + a)
+        whole = a == 0 and b == q.shape[1]
+        self.forward_fn(q if whole else q[:, a:b], k_ext, v_ext, spec,
+                        out=out if whole else out[:, a:b])
+
+
+def gather_sequence(out_local: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """All-gather of the per-rank outputs along the sequence axis (checking aid)."""
+    world = dist.get_world_size(group)
+    parts: List[torch.Tensor] = [torch.empty_like(out_local) for _ in range(world)]
+    dist.all_gather(parts, out_local.contiguous(), group=group)
+    return torch.cat(parts, dim=1)

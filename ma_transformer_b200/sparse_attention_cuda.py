@@ -1,0 +1,190 @@
+"""Drop-in for the reference's torch extension module ``sparse_attention_cuda``
+(src/cuda/sparse_attention_kernel.cu:501-510): same function names, keyword
+names, argument meaning and error type, served by libmat_sparse_attn through
+its C ABI.  Additions: ``forward_pattern`` (causal / dilated / block-sparse /
+Longformer key sets) and ``forward_host`` (host tensors in, host tensor out).
+
+Differences from the reference extension, all relaxations:
+  * bf16 and fp16 inputs run natively (the reference accepts fp32 only,
+    sparse_attention_kernel.cu:428-429, and its bridge sends 16-bit inputs to a
+    python loop, src/layers/ma_core_bridge.py:77-79);
+There is no CPU fallback: CPU tensors raise RuntimeError here exactly as in the
+reference ("Inputs must be CUDA tensors"); use ``forward_host`` for those.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, List, Optional
+
+import torch
+
+from . import _native as nat
+from .patterns import PatternSpec, WINDOW
+
+_DTYPES = {torch.float32: nat.MAT_F32, torch.bfloat16: nat.MAT_BF16, torch.float16: nat.MAT_F16}
+_workspaces: Dict[str, torch.Tensor] = {}
+
+
+def _check_inputs(*tensors: torch.Tensor) -> None:
+    # the reference's five TORCH_CHECKs (sparse_attention_kernel.cu:427-432)
+    if not all(t.is_cuda for t in tensors):
+        raise RuntimeError("Inputs must be CUDA tensors")
+    dt = tensors[0].dtype
+    if dt not in _DTYPES or any(t.dtype != dt for t in tensors):
+        raise RuntimeError("Only float32, bfloat16 and float16 are supported in CUDA path "
+                           "(all inputs of one dtype)")
+    if not all(t.is_contiguous() for t in tensors):
+        raise RuntimeError("Inputs must be contiguous")
+    if any(t.dim() != 4 for t in tensors):
+        raise RuntimeError("Expected shape [B, S, H, D]")
+    if any(t.device != tensors[0].device for t in tensors):
+        raise RuntimeError("Inputs must be on the same device")
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    key = str(device)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def forward_pattern(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                    spec: PatternSpec, scale: Optional[float] = None,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Sparse-attention forward for any ``PatternSpec``.
+
+    query: [B, S_q, H, D]; key, value: [B, S_kv, H, D] with
+    S_kv >= S_q + spec.q_offset (a sequence shard passes its halo rows in key and
+    value).  Asynchronous on torch's current stream; returns [B, S_q, H, D] in the
+    inputs' dtype.
+    """
+    _check_inputs(query, key, value)
+    if key.shape != value.shape or query.shape[0] != key.shape[0] or query.shape[2:] != key.shape[2:]:
+        raise RuntimeError("Q,K,V must have same shape (key/value may only differ from query in length)")
+    B, Sq, H, D = query.shape
+    Skv = key.shape[1]
+    if out is None:
+        out = torch.empty_like(query)
+    else:
+        _check_inputs(out)
+        if out.shape != query.shape or out.dtype != query.dtype:
+            raise RuntimeError("out must match query in shape and dtype")
+    dt = _DTYPES[query.dtype]
+    with torch.cuda.device(query.device):
+        s = spec.device_struct(query.device)
+        ws_bytes = nat.lib.mat_sparse_attn_workspace_bytes(B, Sq, Skv, H, D, dt, C.byref(s))
+        ws = _workspace(query.device, ws_bytes) if ws_bytes else None
+        stream = torch.cuda.current_stream(query.device).cuda_stream
+        nat.check(nat.lib.mat_sparse_attn_fwd(
+            query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(), B, Sq, Skv, H, D, dt,
+            C.byref(s), float(scale) if scale else 0.0,
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+            C.c_void_p(stream)))
+    return out
+
+
+def forward(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+            window_size: int = 64) -> torch.Tensor:
+    """Sparse attention forward (CUDA): keys [i-window_size, i+window_size].
+
+    Same call as the reference's ``sparse_attention_cuda.forward``
+    (sparse_attention_kernel.cu:423-458); ``window_size`` 0 is legal (a query
+    attends to itself only) and values beyond S clamp.
+    """
+    _check_inputs(query, key, value)
+    if query.shape != key.shape or key.shape != value.shape:
+        raise RuntimeError("Q,K,V must have same shape")
+    B, S, H, D = query.shape
+    out = torch.empty_like(query)
+    with torch.cuda.device(query.device):
+        stream = torch.cuda.current_stream(query.device).cuda_stream
+        nat.check(nat.lib.mat_sparse_attn_fwd_window(
+            query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(), B, S, H, D,
+            _DTYPES[query.dtype], int(window_size), C.c_void_p(stream)))
+    return out
+
+
+def dense_forward(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                  use_causal_mask: bool = False) -> torch.Tensor:
+    """Dense attention forward (CUDA), the call of sparse_attention_kernel.cu:348-382,
+    expressed as the window that covers the whole sequence (left = S, right = S or
+    0 when causal) and run by the same kernels."""
+    _check_inputs(query, key, value)
+    if query.shape != key.shape or key.shape != value.shape:
+        raise RuntimeError("Q,K,V must have same shape")
+    S = query.shape[1]
+    spec = PatternSpec(WINDOW, left=S, right=0 if use_causal_mask else S)
+    return forward_pattern(query, key, value, spec)
+
+
+def forward_host(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, spec: PatternSpec,
+                 scale: Optional[float] = None, device: int = 0,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Forward for HOST tensors: copies in, computes on ``cuda:device``, copies out.
+
+    The counterpart of handing CPU tensors to the reference's CPU engine
+    (src/layers/ma_core_bridge.py:102-112).  Pinned tensors make the copies
+    asynchronous and let them overlap the compute; the call returns when ``out``
+    is complete.
+    """
+    for t in (query, key, value):
+        if t.is_cuda:
+            raise RuntimeError("forward_host expects CPU tensors")
+        if t.dim() != 4:
+            raise RuntimeError("Expected shape [B, S, H, D]")
+        if not t.is_contiguous():
+            raise RuntimeError("Inputs must be contiguous")
+    if query.shape != key.shape or key.shape != value.shape:
+        raise RuntimeError("Q,K,V must have same shape")
+    if query.dtype not in _DTYPES or key.dtype != query.dtype or value.dtype != query.dtype:
+        raise RuntimeError("Only float32, bfloat16 and float16 are supported")
+    B, S, H, D = query.shape
+    dt = _DTYPES[query.dtype]
+    dev = torch.device("cuda", device)
+    if out is None:
+        out = torch.empty_like(query)
+    with torch.cuda.device(dev):
+        s = spec.device_struct(dev)
+        nbytes = nat.lib.mat_sparse_attn_host_staging_bytes(B, S, H, D, dt, C.byref(s))
+        staging = _workspace(dev, nbytes)
+        torch.cuda.current_stream(dev).synchronize()  # staging may still be in use by earlier work
+        nat.check(nat.lib.mat_sparse_attn_fwd_host(
+            query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(), B, S, H, D, dt,
+            C.byref(s), float(scale) if scale else 0.0, staging.data_ptr(), staging.numel(), device))
+    return out
+
+
+def _recompute_and_grad(fn, query, key, value, grad_out) -> List[torch.Tensor]:
+    q = query.detach().requires_grad_(True)
+    k = key.detach().requires_grad_(True)
+    v = value.detach().requires_grad_(True)
+    with torch.enable_grad():
+        y = fn(q, k, v)
+    return list(torch.autograd.grad(y, (q, k, v), grad_out))
+
+
+def backward(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, grad_out: torch.Tensor,
+             window_size: int = 64) -> List[torch.Tensor]:
+    """Sparse attention backward (CUDA) -> [dQ, dK, dV]; the call of
+    sparse_attention_kernel.cu:460-497.  Outside the forward hot path: computed on
+    the device by differentiating a banded torch recomputation."""
+    _check_inputs(query, key, value, grad_out)
+    if not (query.shape == key.shape == value.shape == grad_out.shape):
+        raise RuntimeError("All tensors must have same shape")
+    from .layers.ma_core_bridge import pytorch_sparse_attention
+    return _recompute_and_grad(lambda q, k, v: pytorch_sparse_attention(q, k, v, int(window_size)),
+                               query, key, value, grad_out)
+
+
+def dense_backward(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                   grad_out: torch.Tensor, use_causal_mask: bool = False) -> List[torch.Tensor]:
+    """Dense attention backward (CUDA) -> [dQ, dK, dV]; the call of
+    sparse_attention_kernel.cu:384-421.  Outside the forward hot path."""
+    _check_inputs(query, key, value, grad_out)
+    if not (query.shape == key.shape == value.shape == grad_out.shape):
+        raise RuntimeError("All tensors must have same shape")
+    from .layers.ma_core_bridge import pytorch_dense_attention
+    return _recompute_and_grad(lambda q, k, v: pytorch_dense_attention(q, k, v, bool(use_causal_mask)),
+                               query, key, value, grad_out)

@@ -1,0 +1,331 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle
+and the committed golden vectors of the reference.  Bars: fp32 rel-err <= 1e-5
+(max|gpu-oracle| / max|oracle|), bf16 max-abs <= 2e-2 against the fp32 oracle fed
+the bf16-rounded inputs, index sets bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+import ma_transformer_b200 as mt
+from ma_transformer_b200 import _native as nat
+from ma_transformer_b200 import sparse_attention_cuda as ext
+from ma_transformer_b200.patterns import PatternSpec, band_random_block_layout, tridiagonal_block_layout
+from helpers import check_close, oracle_out, rel_err, seeded_qkv, to_oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def run(spec, q, k, v, scale=None):
+    out = ext.forward_pattern(q.to(DEV), k.to(DEV), v.to(DEV), spec, scale)
+    torch.cuda.synchronize()
+    return out
+
+
+# ---- the reference's own cases (golden vectors) ------------------------------------
+
+def test_golden_vectors_fp32(golden):
+    worst = 0.0
+    for n, (seed, B, S, H, D, W) in enumerate(golden["meta"].tolist()):
+        tag = f"{seed}_{B}_{S}_{H}_{D}"
+        q, k, v = (torch.from_numpy(golden[f"{t}_{tag}"]).to(DEV) for t in "qkv")
+        got = ext.forward(q, k, v, W).cpu().numpy()
+        want = golden[f"ref_cpp{n}"]
+        worst = max(worst, rel_err(got, want))
+        # the reference's own CUDA tolerance (tests/integration/test_cuda_parity.py:42-57)
+        assert np.abs(got - golden[f"ref_torch{n}"]).max() < 1e-4
+    assert worst <= 1e-5, worst
+    assert nat.last_kernel() == "rowwarp"
+
+
+def test_cfg1_causal_window_fp32():
+    # B=1, H=4, N=1024, d=64, 32 causal taps, scale 1/8
+    spec = PatternSpec.causal_window(32)
+    q, k, v = seeded_qkv(1, 1, 1024, 4, 64)
+    check_close(run(spec, q, k, v), oracle_out(q, k, v, spec), torch.float32)
+    check_close(run(spec, q, k, v, scale=0.125), oracle_out(q, k, v, spec, 0.125), torch.float32)
+
+
+@pytest.mark.parametrize("B,S,H,D", [(1, 1, 1, 1), (1, 7, 2, 5), (2, 33, 1, 13), (1, 100, 3, 40), (1, 65, 2, 96),
+                                     (1, 40, 1, 200), (1, 18, 1, 512)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_rowwarp_odd_shapes(B, S, H, D, dtype):
+    for spec in (PatternSpec.sliding_window(4), PatternSpec.causal_window(9, dilation=3),
+                 PatternSpec(left=2, right=5, dilation=2)):
+        q, k, v = seeded_qkv(7, B, S, H, D, dtype)
+        check_close(run(spec, q, k, v), oracle_out(q, k, v, spec), dtype)
+        assert nat.last_kernel() == "rowwarp"
+
+
+def test_head_width_beyond_maximum_is_refused_loudly():
+    q = torch.zeros(1, 2, 1, 520, device=DEV)
+    with pytest.raises(RuntimeError, match="512"):
+        ext.forward(q, q, q, 1)
+
+
+# ---- tensor-core window kernel --------------------------------------------------------
+
+WINDOW_SPECS = [
+    PatternSpec.causal_window(64),
+    PatternSpec.causal_window(32),
+    PatternSpec.causal_window(1),
+    PatternSpec.sliding_window(17),
+    PatternSpec.sliding_window(64),
+    PatternSpec(left=5, right=90),
+    PatternSpec.causal_window(200),
+    PatternSpec.sliding_window(1000),
+]
+
+
+@pytest.mark.parametrize("spec", WINDOW_SPECS, ids=lambda s: f"l{s.left}r{s.right}")
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,S,H", [(1, 256, 2), (2, 333, 3), (1, 64, 1), (1, 17, 2), (1, 1, 1)])
+def test_mma_window_vs_oracle(spec, dtype, B, S, H):
+    q, k, v = seeded_qkv(11, B, S, H, 64, dtype)
+    got = run(spec, q, k, v)
+    assert nat.last_kernel() == "mma_window"
+    check_close(got, oracle_out(q, k, v, spec), dtype)
+
+
+@pytest.mark.parametrize("dil", [2, 3, 4])
+@pytest.mark.parametrize("spec0", [PatternSpec.causal_window(64), PatternSpec.sliding_window(9)], ids=["causal64", "pm9"])
+def test_mma_window_dilated(spec0, dil):
+    spec = PatternSpec(left=spec0.left, right=spec0.right, dilation=dil)
+    S = 96 * dil
+    q, k, v = seeded_qkv(12, 2, S, 2, 64, torch.bfloat16)
+    got = run(spec, q, k, v)
+    assert nat.last_kernel() == "mma_window"
+    check_close(got, oracle_out(q, k, v, spec), torch.bfloat16)
+    # ragged against the dilation: the general kernel takes over, same answer
+    q, k, v = seeded_qkv(13, 1, S + 1, 2, 64, torch.bfloat16)
+    got = run(spec, q, k, v)
+    assert nat.last_kernel() == "rowwarp"
+    check_close(got, oracle_out(q, k, v, spec), torch.bfloat16)
+
+
+def test_cfg2_shape_reduced_length_bf16():
+    # cfg-2's heads, width, taps and value distribution at a length the oracle finishes quickly
+    spec = PatternSpec.causal_window(64)
+    q, k, v = seeded_qkv(2, 1, 4096, 8, 64, torch.bfloat16, scale=0.5)
+    check_close(run(spec, q, k, v), oracle_out(q, k, v, spec), torch.bfloat16)
+    assert nat.last_kernel() == "mma_window"
+
+
+def test_large_magnitudes_stay_finite():
+    # tests/integration/test_cuda_extensive.py:77-92 scales the inputs by 100
+    spec = PatternSpec.sliding_window(8)
+    for dtype in (torch.float32, torch.bfloat16):
+        q, k, v = seeded_qkv(3, 1, 130, 2, 64, dtype, scale=100.0)
+        got = run(spec, q, k, v).float().cpu().numpy()
+        want = oracle_out(q, k, v, spec)
+        assert np.isfinite(got).all()
+        assert np.abs(got - want).max() <= (5e-3 if dtype == torch.float32 else 2.0) * 100
+
+
+# ---- sequence shards: halo rows in front of / behind the shard's keys -------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("spec", [PatternSpec.causal_window(64), PatternSpec.sliding_window(20),
+                                  PatternSpec.causal_window(16, dilation=2)], ids=["causal64", "pm20", "dil2"])
+def test_shard_with_halo_equals_full_run(spec, dtype):
+    S, P = 512, 4
+    q, k, v = seeded_qkv(21, 1, S, 2, 64, dtype)
+    full = run(spec, q, k, v)
+    chunk = S // P
+    for r in range(P):
+        lo = max(0, r * chunk - spec.left * spec.dilation)
+        hi = min(S, (r + 1) * chunk + spec.right * spec.dilation)
+        part = run(spec.shifted(r * chunk - lo), q[:, r * chunk:(r + 1) * chunk].contiguous(),
+                   k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous())
+        assert torch.equal(part, full[:, r * chunk:(r + 1) * chunk]), f"shard {r}"
+    check_close(full, oracle_out(q, k, v, spec), dtype)
+
+
+# ---- block-sparse -----------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_block_sparse_band_random(dtype):
+    # cfg-3's layout (band of 4 + 2 random earlier blocks, causal diagonal) at reduced length
+    S, block = 1024, 64
+    rp, ci = band_random_block_layout(S // block, 4, 2, seed=5)
+    spec = PatternSpec.block_sparse(block, rp, ci, causal=True)
+    q, k, v = seeded_qkv(31, 2, S, 2, 64, dtype)
+    got = run(spec, q, k, v)
+    assert nat.last_kernel() == ("rowwarp" if dtype == torch.float32 else "mma_block")
+    check_close(got, oracle_out(q, k, v, spec), dtype)
+
+
+def test_block_sparse_reference_tridiagonal_ragged():
+    # the reference's own layout |bi-bj| <= 1 (sparse_attention.cpp:212-227), ragged last block
+    for S, block, dtype in [(200, 64, torch.bfloat16), (300, 128, torch.bfloat16), (50, 4, torch.float32),
+                            (37, 8, torch.bfloat16)]:
+        rp, ci = tridiagonal_block_layout(S, block)
+        spec = PatternSpec.block_sparse(block, rp, ci)
+        q, k, v = seeded_qkv(32, 1, S, 2, 64, dtype)
+        check_close(run(spec, q, k, v), oracle_out(q, k, v, spec), dtype)
+
+
+def test_block_sparse_empty_rows_give_zeros():
+    spec = PatternSpec.block_sparse(64, [0, 1, 1, 3], [0, 0, 2])
+    for dtype in (torch.float32, torch.bfloat16):
+        q, k, v = seeded_qkv(33, 1, 192, 1, 64, dtype)
+        got = run(spec, q, k, v)
+        assert torch.count_nonzero(got[:, 64:128]) == 0
+        check_close(got, oracle_out(q, k, v, spec), dtype)
+
+
+# ---- Longformer -----------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_longformer_vs_oracle(dtype):
+    g = torch.Generator().manual_seed(41)
+    S = 512
+    glob = torch.randperm(S, generator=g)[:8].sort().values.numpy()
+    for spec in (PatternSpec.longformer(16, 16, glob), PatternSpec.longformer(64, 64, glob[:3]),
+                 PatternSpec.longformer(2, 2, [0, 1]), PatternSpec.longformer(4, 0, [])):
+        q, k, v = seeded_qkv(42, 2, S, 3, 64, dtype)
+        check_close(run(spec, q, k, v), oracle_out(q, k, v, spec), dtype)
+
+
+# ---- index sets, recovered from the kernels themselves -----------------------------------------
+
+def _attended_sets(spec, S, dtype, D):
+    """q = 0 gives uniform weights; V = identity rows make output[i, j] > 0 exactly
+    for the keys row i attended."""
+    q = torch.zeros(1, S, 1, D, dtype=dtype)
+    k = torch.zeros(1, S, 1, D, dtype=dtype)
+    v = torch.zeros(1, S, 1, D, dtype=dtype)
+    v[0, torch.arange(S), 0, torch.arange(S)] = 1.0
+    out = run(spec, q, k, v)[0, :, 0, :S].float().cpu().numpy()
+    return [np.nonzero(out[i] > 0)[0].astype(np.int64) for i in range(S)], out
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 48), (torch.bfloat16, 64)])
+def test_index_sets_bit_exact(dtype, D, oracle):
+    S = 48
+    rp, ci = band_random_block_layout(S // 8, 2, 1, seed=1)
+    rp64, ci64 = tridiagonal_block_layout(64, 64)
+    specs = [PatternSpec.sliding_window(3), PatternSpec.causal_window(5), PatternSpec.causal_window(4, dilation=3),
+             PatternSpec(left=0, right=7), PatternSpec.block_sparse(8, rp, ci, causal=True),
+             PatternSpec.block_sparse(64, rp64, ci64, causal=True),
+             PatternSpec.longformer(2, 3, [5, 40, 17]), PatternSpec.sliding_window(500)]
+    for spec in specs:
+        sets, out = _attended_sets(spec, S, dtype, D)
+        for i in range(S):
+            want = oracle.rowset(to_oracle(spec), S, i)
+            assert np.array_equal(sets[i], want), (spec, i)
+            assert np.array_equal(spec.rowset(S, i), want)
+            if len(want):  # uniform weights: every attended key carries 1/n
+                assert abs(out[i, want[0]] - 1.0 / len(want)) < (1e-6 if dtype == torch.float32 else 4e-3)
+
+
+# ---- reference extension behaviour ---------------------------------------------------------------
+
+def test_extension_call_contract():
+    q, k, v = (t.to(DEV) for t in seeded_qkv(51, 2, 33, 2, 16))
+    # window 0 = self only: output equals V (tests/python/test_cuda_sparse_kernel_launch.py W=0)
+    assert torch.allclose(ext.forward(q, k, v, 0), v, atol=1e-6)
+    # window beyond S clamps to dense
+    dense = ext.dense_forward(q, k, v, False)
+    assert torch.allclose(ext.forward(q, k, v, 10_000), dense, atol=1e-6)
+    np.testing.assert_allclose(dense.cpu().numpy(), mt.pytorch_dense_attention(q.cpu(), k.cpu(), v.cpu()).numpy(),
+                               rtol=1e-4, atol=1e-5)
+    causal = ext.dense_forward(q, k, v, True)
+    np.testing.assert_allclose(causal.cpu().numpy(),
+                               mt.pytorch_dense_attention(q.cpu(), k.cpu(), v.cpu(), True).numpy(), rtol=1e-4, atol=1e-5)
+    # non-contiguous input raises RuntimeError (tests/integration/test_cuda_extensive.py:196-204)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        ext.forward(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), 4)
+    with pytest.raises(RuntimeError, match="same shape"):
+        ext.forward(q, k[:, :5].contiguous(), v, 4)
+    with pytest.raises(RuntimeError):
+        ext.forward(q, k.double(), v, 4)
+    # inputs are never written
+    q0 = q.clone()
+    ext.forward(q, k, v, 4)
+    assert torch.equal(q, q0)
+
+
+def test_module_surface_on_gpu():
+    q, k, v = (t.to(DEV) for t in seeded_qkv(52, 2, 40, 4, 32))
+    attn = mt.MACoreAttention(sparse=True, window_size=8, fallback_training=False).eval()
+    want = oracle_out(q.cpu(), k.cpu(), v.cpu(), PatternSpec.sliding_window(8))
+    check_close(attn(q, k, v), want, torch.float32)
+    # non-contiguous inputs are made contiguous by the bridge (test_cuda_extensive.py:95-115)
+    qt = q.transpose(1, 2).contiguous().transpose(1, 2)
+    check_close(attn(qt, k, v), want, torch.float32)
+    # 16-bit inputs keep their dtype and now run natively (test_cuda_extensive.py:118-136)
+    for dt in (torch.bfloat16, torch.float16):
+        y = attn(q.to(dt), k.to(dt), v.to(dt))
+        assert y.dtype == dt
+        assert (y.float().cpu() - torch.from_numpy(want)).abs().max() < 3e-2
+    # [B,S,D] layer, eval mode
+    layer = mt.SparseAttention(window_size=3).eval()
+    x = torch.randn(2, 50, 24, device=DEV)
+    y = layer(x, x, x)
+    want3 = oracle_out(x.cpu().unsqueeze(2), x.cpu().unsqueeze(2), x.cpu().unsqueeze(2), PatternSpec.sliding_window(3))
+    check_close(y.unsqueeze(2), want3, torch.float32)
+    # backward through the native forward (tests/python/test_cuda_backward.py)
+    qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+    attn(qg, kg, vg).square().sum().backward()
+    qr, kr, vr = (t.clone().requires_grad_(True) for t in (q, k, v))
+    mt.pytorch_sparse_attention(qr, kr, vr, 8).square().sum().backward()
+    for a, b in ((qg, qr), (kg, kr), (vg, vr)):
+        assert torch.allclose(a.grad, b.grad, atol=2e-3)
+
+
+# ---- host-buffer entry point ------------------------------------------------------------------------
+
+@pytest.mark.parametrize("spec", [PatternSpec.causal_window(64), PatternSpec.sliding_window(30),
+                                  PatternSpec.causal_window(8, dilation=2)], ids=["causal64", "pm30", "dil2"])
+def test_host_entry_point_equals_device_entry_point(spec):
+    # long enough for several pipeline chunks (about 4 MiB each)
+    q, k, v = seeded_qkv(61, 2, 20000, 8, 64, torch.bfloat16)
+    qp, kp, vp = (t.pin_memory() for t in (q, k, v))
+    got = ext.forward_host(qp, kp, vp, spec)
+    want = run(spec, q, k, v).cpu()
+    assert torch.equal(got, want)
+
+
+def test_host_entry_point_general_patterns_and_module():
+    S = 1024
+    rp, ci = band_random_block_layout(S // 64, 4, 2, seed=2)
+    for spec, dtype in [(PatternSpec.block_sparse(64, rp, ci, causal=True), torch.bfloat16),
+                        (PatternSpec.longformer(8, 8, [3, 500]), torch.float32)]:
+        q, k, v = seeded_qkv(62, 1, S, 2, 64, dtype)
+        check_close(ext.forward_host(q, k, v, spec), oracle_out(q, k, v, spec), dtype)
+    # CPU tensors through the module: computed on the GPU, returned on the CPU
+    q, k, v = seeded_qkv(63, 1, 64, 2, 16)
+    attn = mt.MACoreAttention(sparse=True, window_size=4).eval()
+    y = attn(q, k, v)
+    assert y.device.type == "cpu"
+    check_close(y, oracle_out(q, k, v, PatternSpec.sliding_window(4)), torch.float32)
+
+
+# ---- full BASELINE sizes: size-independent properties ---------------------------------------------------
+
+def test_cfg2_full_size_properties():
+    B, S, H, D = 1, 65536, 8, 64
+    spec = PatternSpec.causal_window(64)
+    q, k, v = (t.to(DEV) for t in seeded_qkv(2, B, S, H, D, torch.bfloat16, scale=0.5))
+    out = ext.forward_pattern(q, k, v, spec)
+    assert nat.last_kernel() == "mma_window"
+    assert torch.isfinite(out.float()).all()
+    # (a) linear in V: doubling V doubles the output exactly (power of two)
+    assert torch.equal(ext.forward_pattern(q, k, v * 2, spec), out * 2)
+    # (b) constant V rows come back unchanged (weights sum to one)
+    vc = torch.full_like(v, 0.75)
+    assert (ext.forward_pattern(q, k, vc, spec).float() - 0.75).abs().max() <= 0.75 * 2 ** -7
+    # (c) deterministic
+    assert torch.equal(ext.forward_pattern(q, k, v, spec), out)
+    # (d) sampled row blocks against the oracle, each with its 63-row halo
+    for a in (0, 64, 4096 - 32, 32768, S - 128):
+        lo = max(0, a - 63)
+        sl = spec.shifted(a - lo)
+        want = oracle_out(q[:, a:a + 128].cpu(), k[:, lo:a + 128].cpu(), v[:, lo:a + 128].cpu(), sl)
+        check_close(out[:, a:a + 128], want, torch.bfloat16)
+
+
+def test_device_status_word_is_clear():
+    torch.cuda.synchronize()
+    assert nat.device_status() == 0
