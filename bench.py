@@ -54,7 +54,7 @@ def measured_peak_gbs():
 class ClockSampler:
     """Polls SM clock and throttle reasons of one GPU through NVML from a thread."""
 
-    def __init__(self, index: int, period_s: float = 0.002):
+    def __init__(self, index: int, period_s: float = 0.0002):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._thread = None
@@ -284,6 +284,13 @@ def gpu_arm(args):
     status = nat.device_status()
 
     # ---- end to end: pinned host tensors in, host tensor out, per rank its chunk plus halo ----
+    if args.no_e2e:   # profiling runs: the device-resident leg only
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "ms_per_step": ms_per_step, "n_gpus": world,
+                              "clocks": clocks, "note": "device leg only (--no-e2e)"}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     lo = max(0, a - (TAPS - 1))
     hq, hk, hv = (t[:, lo:b].contiguous().pin_memory() for t in (q_cpu, k_cpu, v_cpu))
     ho = torch.empty_like(hq).pin_memory()
@@ -334,6 +341,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="device-resident leg only (for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 

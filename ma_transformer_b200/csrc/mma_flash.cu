@@ -1,6 +1,6 @@
 // Tiled forward for 16-bit inputs with head width 64: per query tile, fused
-// Q*K^T -> online softmax -> P*V on the warp-level tensor-core path, with Q and
-// the K/V window (halo included) staged in shared memory by TMA.
+// Q*K^T -> softmax -> P*V on the warp-level tensor-core path, with Q and the
+// K/V window (halo included) staged in shared memory by TMA.
 //
 // This is the kernel for the narrow-window patterns, which are bound by HBM
 // traffic: every Q/K/V row is one 128-byte line, fetched once per tile by a
@@ -16,9 +16,13 @@
 //     kernel only ever sees dil = 1.
 //   - One CTA per (batch, head, tile of TQ queries); TQ/16 consumer warps own
 //     16 query rows each, one extra warp issues the TMA loads through a ring of
-//     64-key K/V stages guarded by full/empty mbarriers.
-//   - A warp skips the 16-key column pairs that lie wholly outside its rows'
-//     key set and masks only the pairs that straddle the edge of it.
+//     TK-key K/V stages guarded by full/empty mbarriers.
+//   - A warp walks only the 16-key column pairs that intersect its rows' key
+//     set, NP pairs per softmax step, and masks only the pairs that straddle the
+//     edge of the set.  When the whole window of a tile fits one stage and NP
+//     pairs per warp (SINGLE, the case of 64 causal taps), there is exactly one
+//     step: no running max / rescale, and the output accumulators are not live
+//     while the scores are computed.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -31,22 +35,25 @@
 namespace mat {
 namespace {
 
-constexpr int TK = 64;               // keys per stage
-constexpr int kStages = 3;
-constexpr int kRowBytes = 128;       // 64 elements of 2 bytes
-constexpr int kStageBytes = 2 * TK * kRowBytes;  // K then V
+constexpr int kRowBytes = 128;  // 64 elements of 2 bytes
+constexpr int kBig = 1 << 29;   // "no limit" for a mask edge
 
 // status words a kernel can leave in g_flash_status (0 = fine)
 constexpr int kStatusWaitTimeout = 1;
 __device__ int g_flash_status = 0;
 
 struct FlashParams {
-    int32_t Sq1, Skv1, off1;  // query rows, key rows and q_offset of one sub-sequence
-    int32_t left, right;      // window taps (clamped to Skv1)
-    int32_t n_tiles;          // query tiles per (batch, head)
-    int32_t HH;               // heads seen by the kernel (dil * H)
-    float sl2;                // scale * log2(e)
-    DevPattern pat;           // block layout (block, rowptr, colidx, causal)
+    int32_t Sq1, Skv1, off1;      // query rows, key rows and q_offset of one sub-sequence
+    int32_t left, right;          // window taps (clamped to Skv1); chunk enumeration
+    int32_t mask_left, mask_right;  // a key j is attended by row p iff -mask_left <= j-p <= mask_right
+    int32_t n_tiles;              // query tiles per (batch, head)
+    int32_t HH;                   // heads seen by the kernel (dil * H)
+    float sl2;                    // scale * log2(e)
+    // block layout
+    int32_t block, per_blk;
+    int64_t n_qblocks;
+    const int32_t *rowptr;
+    const int32_t *colidx;
 };
 
 __device__ __forceinline__ uint32_t swz(uint32_t base, int row, int chunk16) {
@@ -54,15 +61,13 @@ __device__ __forceinline__ uint32_t swz(uint32_t base, int row, int chunk16) {
 }
 
 // The staged key chunks of one query tile: chunk c starts at key base(c).
-template <int KIND>
+template <int KIND, int TQ, int TK>
 struct Chunks {
     int n;
-    int start;          // window: first key of chunk 0
-    int e0, per_blk;    // block: first CSR entry, 64-key chunks per block
-    const int32_t *colidx;
-    int block;
-    __device__ __forceinline__ Chunks(const FlashParams &P, int q0, int TQ) {
-        n = 0; start = 0; e0 = 0; per_blk = 1; colidx = nullptr; block = 0;
+    int start;  // window: first key of chunk 0
+    int e0;     // block: first CSR entry of the tile's layout row
+    __device__ __forceinline__ Chunks(const FlashParams &P, int q0) {
+        n = 0; start = 0; e0 = 0;
         if (KIND == MAT_WINDOW) {
             int lo = q0 + P.off1 - P.left;
             if (lo < 0) lo = 0;
@@ -72,35 +77,38 @@ struct Chunks {
             start = lo;
             n = hi >= lo ? (hi - lo) / TK + 1 : 0;
         } else {
-            block = (int)P.pat.block;
-            per_blk = block / TK;
-            colidx = P.pat.colidx;
-            const int64_t r = (int64_t)(q0 + P.off1) / block;
-            if (r < P.pat.n_qblocks) {
-                e0 = P.pat.rowptr[r];
-                n = (P.pat.rowptr[r + 1] - e0) * per_blk;
+            const int64_t r = (int64_t)(q0 + P.off1) / P.block;
+            if (r < P.n_qblocks) {
+                e0 = P.rowptr[r];
+                n = (P.rowptr[r + 1] - e0) * P.per_blk;
             }
         }
     }
-    __device__ __forceinline__ int base(int c) const {
+    __device__ __forceinline__ int base(const FlashParams &P, int c) const {
         if (KIND == MAT_WINDOW) return start + c * TK;
-        return colidx[e0 + c / per_blk] * block + (c % per_blk) * TK;
+        return P.colidx[e0 + c / P.per_blk] * P.block + (c % P.per_blk) * TK;
     }
 };
 
-template <typename T, int KIND, int TQ>
-__global__ void __launch_bounds__((TQ / 16 + 1) * 32)
+template <int TQ, int TK, int STAGES>
+constexpr size_t flash_smem_bytes() {
+    return 1024 + (size_t)TQ * kRowBytes + (size_t)STAGES * 2 * TK * kRowBytes + 8 * (1 + 2 * STAGES);
+}
+
+template <typename T, int KIND, int TQ, int TK, int NP, int STAGES, bool SINGLE, int MINB>
+__global__ void __launch_bounds__((TQ / 16 + 1) * 32, MINB)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                  const FlashParams P) {
     constexpr int NW = TQ / 16;  // consumer warps
+    constexpr int kStageBytes = 2 * TK * kRowBytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *sQ = smem;
     uint8_t *sKV = smem + TQ * kRowBytes;
-    uint64_t *bar_q = (uint64_t *)(sKV + kStages * kStageBytes);
+    uint64_t *bar_q = (uint64_t *)(sKV + STAGES * kStageBytes);
     uint64_t *bar_full = bar_q + 1;
-    uint64_t *bar_empty = bar_full + kStages;
+    uint64_t *bar_empty = bar_full + STAGES;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -113,7 +121,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(bar_q, 1);
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(bar_full + s, 1);
             ptx::mbar_init(bar_empty + s, NW);
         }
@@ -121,23 +129,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     __syncthreads();
 
-    const Chunks<KIND> chunks(P, q0, TQ);
+    const Chunks<KIND, TQ, TK> chunks(P, q0);
 
     if (warp == NW) {  // ---- producer warp: one lane feeds the ring ----
         if (lane == 0) {
-            ptx::prefetch_tensormap(&map_q);
-            ptx::prefetch_tensormap(&map_k);
-            ptx::prefetch_tensormap(&map_v);
             ptx::mbar_expect_tx(bar_q, TQ * kRowBytes);
             ptx::tma_load_4d(sQ, &map_q, bar_q, 0, hh, q0, b);
             for (int c = 0; c < chunks.n; ++c) {
-                const int s = c % kStages, use = c / kStages;
+                const int s = c % STAGES, use = c / STAGES;
                 if (use > 0 && !ptx::mbar_wait(bar_empty + s, (use - 1) & 1)) {
                     atomicExch(&g_flash_status, kStatusWaitTimeout);
                     break;
                 }
                 uint8_t *dst = sKV + s * kStageBytes;
-                const int kb = chunks.base(c);
+                const int kb = chunks.base(P, c);
                 ptx::mbar_expect_tx(bar_full + s, kStageBytes);
                 ptx::tma_load_4d(dst, &map_k, bar_full + s, 0, hh, kb, b);
                 ptx::tma_load_4d(dst + TK * kRowBytes, &map_v, bar_full + s, 0, hh, kb, b);
@@ -152,18 +157,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int row0 = warp * 16;                 // first row of this warp inside the tile
     const int p_min = q0 + row0 + P.off1;       // key-coordinate position of that row
     const int p_max = p_min + 15;
+    const uint32_t mask_span = (uint32_t)(P.mask_left + P.mask_right);
+
+    // key range this warp's rows can attend
+    const int k_lo = max(p_min - P.mask_left, 0);
+    const int k_hi = min(p_max + P.mask_right, P.Skv1 - 1);
 
     if (!ptx::mbar_wait(bar_q, 0)) {
         atomicExch(&g_flash_status, kStatusWaitTimeout);
         return;
     }
-    uint32_t qa[4][4];
-    {
-        const uint32_t q_base = ptx::smem_u32(sQ);
-        const int r = row0 + (lane & 7) + ((lane >> 3) & 1) * 8;
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) ptx::ldmatrix_x4(qa[ks], swz(q_base, r, 2 * ks + (lane >> 4)));
-    }
+    const uint32_t q_base = ptx::smem_u32(sQ);
+    const int q_row = row0 + (lane & 7) + ((lane >> 3) & 1) * 8;
 
     float o[8][4];
 #pragma unroll
@@ -172,71 +177,72 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     float l_run[2] = {0.f, 0.f};
 
     for (int c = 0; c < chunks.n; ++c) {
-        const int s = c % kStages, use = c / kStages;
+        const int s = c % STAGES, use = c / STAGES;
         if (!ptx::mbar_wait(bar_full + s, use & 1)) {
             atomicExch(&g_flash_status, kStatusWaitTimeout);
             return;
         }
-        const int kb = chunks.base(c);
+        const int kb = chunks.base(P, c);
+        const uint32_t k_base = ptx::smem_u32(sKV + s * kStageBytes);
+        const uint32_t v_base = k_base + TK * kRowBytes;
+        // pairs of this chunk that intersect [k_lo, k_hi]
+        const int first = max(0, (k_lo - kb) >> 4);
+        const int last = k_hi >= kb ? min(TK / 16 - 1, (k_hi - kb) >> 4) : -1;
+        const bool edge = kb < 0 || kb + TK > P.Skv1;  // chunk reaches outside the key tensor
 
-        // which 16-key pairs does this warp need, and which of those need no mask
-        uint32_t need = 0, whole = 0;
-        {
-            int k_lo, k_hi, f_lo, f_hi;  // needed key range; range where no row is masked
-            if (KIND == MAT_WINDOW) {
-                k_lo = max(p_min - P.left, 0);
-                k_hi = min(p_max + P.right, P.Skv1 - 1);
-                f_lo = max(p_max - P.left, 0);
-                f_hi = min(p_min + P.right, P.Skv1 - 1);
-            } else {
-                k_lo = 0;
-                k_hi = P.pat.causal ? min(p_max, P.Skv1 - 1) : P.Skv1 - 1;
-                f_lo = 0;
-                f_hi = P.pat.causal ? min(p_min, P.Skv1 - 1) : P.Skv1 - 1;
-            }
+        for (int pp = first; pp <= last; pp += NP) {
+            const int npairs = min(NP, last - pp + 1);
+            float sc[2 * NP][4];
 #pragma unroll
-            for (int pt = 0; pt < 4; ++pt) {
-                const int a = kb + 16 * pt, z = a + 15;
-                if (z >= k_lo && a <= k_hi) need |= 1u << pt;
-                if (a >= f_lo && z <= f_hi) whole |= 1u << pt;
-            }
-        }
+            for (int n = 0; n < 2 * NP; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
 
-        if (need) {
-            const uint32_t k_base = ptx::smem_u32(sKV + s * kStageBytes);
-            const uint32_t v_base = k_base + TK * kRowBytes;
-            float sc[8][4];
+            // ---- S = Q K^T over the step's pairs ----
+            const int kr = 16 * pp + (lane & 7) + (lane >> 4) * 8;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                uint32_t qa[4];
+                ptx::ldmatrix_x4(qa, swz(q_base, q_row, 2 * ks + (lane >> 4)));
+                const uint32_t k_addr = swz(k_base, kr, 2 * ks + ((lane >> 3) & 1));
+#pragma unroll
+                for (int j = 0; j < NP; ++j) {
+                    if (j < npairs) {
+                        uint32_t kf[4];
+                        ptx::ldmatrix_x4(kf, k_addr + j * 16 * kRowBytes);
+                        ptx::Mma<T>::run(sc[2 * j], qa, kf[0], kf[1]);
+                        ptx::Mma<T>::run(sc[2 * j + 1], qa, kf[2], kf[3]);
+                    }
+                }
+            }
+
+            // ---- mask the pairs that straddle the edge of the key set; row max ----
             float mloc[2] = {-INFINITY, -INFINITY};
+            // d = j - p for element (pair 0, half 0, e = 0) of this lane, shifted so that 0 <= d + mask_left
+            const int u0 = kb + 16 * pp + 2 * tq - (p_min + g) + P.mask_left;
 #pragma unroll
-            for (int pt = 0; pt < 4; ++pt) {
-                if (!((need >> pt) & 1)) continue;
+            for (int j = 0; j < NP; ++j) {
+                if (j < npairs) {
+                    const int a = kb + 16 * (pp + j);
+                    const bool whole = a - p_max >= -P.mask_left && a + 15 - p_min <= P.mask_right &&
+                                       a >= 0 && a + 15 < P.Skv1;
+                    if (!whole) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) sc[2 * pt][e] = sc[2 * pt + 1][e] = 0.f;
-                const int kr = 16 * pt + (lane & 7) + (lane >> 4) * 8;
+                        for (int half = 0; half < 2; ++half)
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    uint32_t kf[4];
-                    ptx::ldmatrix_x4(kf, swz(k_base, kr, 2 * ks + ((lane >> 3) & 1)));
-                    ptx::Mma<T>::run(sc[2 * pt], qa[ks], kf[0], kf[1]);
-                    ptx::Mma<T>::run(sc[2 * pt + 1], qa[ks], kf[2], kf[3]);
-                }
-                if (!((whole >> pt) & 1)) {
+                            for (int e = 0; e < 4; ++e) {
+                                const int du = u0 + 16 * j + 8 * half + (e & 1) - 8 * (e >> 1);
+                                bool ok = (uint32_t)du <= mask_span;
+                                if (edge) {
+                                    const int key = a + 8 * half + 2 * tq + (e & 1);
+                                    ok = ok && key >= 0 && key < P.Skv1;
+                                }
+                                if (!ok) sc[2 * j + half][e] = -INFINITY;
+                            }
+                    }
 #pragma unroll
-                    for (int half = 0; half < 2; ++half)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int j = kb + 16 * pt + 8 * half + 2 * tq + (e & 1);
-                            const int p = p_min + g + (e >> 1) * 8;
-                            bool ok = j >= 0 && j < P.Skv1;
-                            if (KIND == MAT_WINDOW) ok = ok && j >= p - P.left && j <= p + P.right;
-                            else ok = ok && (!P.pat.causal || j <= p);
-                            if (!ok) sc[2 * pt + half][e] = -INFINITY;
-                        }
-                }
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    mloc[0] = fmaxf(mloc[0], fmaxf(sc[2 * pt + half][0], sc[2 * pt + half][1]));
-                    mloc[1] = fmaxf(mloc[1], fmaxf(sc[2 * pt + half][2], sc[2 * pt + half][3]));
+                    for (int half = 0; half < 2; ++half) {
+                        mloc[0] = fmaxf(mloc[0], fmaxf(sc[2 * j + half][0], sc[2 * j + half][1]));
+                        mloc[1] = fmaxf(mloc[1], fmaxf(sc[2 * j + half][2], sc[2 * j + half][3]));
+                    }
                 }
             }
             float m_use[2];
@@ -244,40 +250,49 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             for (int i = 0; i < 2; ++i) {
                 mloc[i] = fmaxf(mloc[i], __shfl_xor_sync(0xffffffffu, mloc[i], 1));
                 mloc[i] = fmaxf(mloc[i], __shfl_xor_sync(0xffffffffu, mloc[i], 2));
-                const float m_new = fmaxf(m_run[i], mloc[i]);
-                m_use[i] = m_new == -INFINITY ? 0.f : m_new;
-                const float alpha = ptx::ex2((m_run[i] - m_use[i]) * P.sl2);
-                m_run[i] = m_new;
-                l_run[i] *= alpha;
+                if (SINGLE) {
+                    m_use[i] = mloc[i] == -INFINITY ? 0.f : mloc[i] * P.sl2;
+                } else {
+                    const float m_new = fmaxf(m_run[i], mloc[i]);
+                    const float mu = m_new == -INFINITY ? 0.f : m_new;
+                    const float alpha = ptx::ex2((m_run[i] - mu) * P.sl2);
+                    m_run[i] = m_new;
+                    l_run[i] *= alpha;
 #pragma unroll
-                for (int n = 0; n < 8; ++n) {
-                    o[n][2 * i] *= alpha;
-                    o[n][2 * i + 1] *= alpha;
+                    for (int n = 0; n < 8; ++n) {
+                        o[n][2 * i] *= alpha;
+                        o[n][2 * i + 1] *= alpha;
+                    }
+                    m_use[i] = mu * P.sl2;
                 }
-                m_use[i] *= P.sl2;
             }
+
+            // ---- P = exp2(S*sl2 - m), O += P V ----
+            const int vr = 16 * pp + (lane & 7) + ((lane >> 3) & 1) * 8;
+            const uint32_t v_addr0 = swz(v_base, vr, lane >> 4);
 #pragma unroll
-            for (int pt = 0; pt < 4; ++pt) {
-                if (!((need >> pt) & 1)) continue;
-                uint32_t pa[4];
+            for (int j = 0; j < NP; ++j) {
+                if (j < npairs) {
+                    uint32_t pa[4];
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const float p0 = ptx::ex2(fmaf(sc[2 * pt + half][0], P.sl2, -m_use[0]));
-                    const float p1 = ptx::ex2(fmaf(sc[2 * pt + half][1], P.sl2, -m_use[0]));
-                    const float p2 = ptx::ex2(fmaf(sc[2 * pt + half][2], P.sl2, -m_use[1]));
-                    const float p3 = ptx::ex2(fmaf(sc[2 * pt + half][3], P.sl2, -m_use[1]));
-                    l_run[0] += p0 + p1;
-                    l_run[1] += p2 + p3;
-                    pa[2 * half] = ptx::Mma<T>::pack(p0, p1);
-                    pa[2 * half + 1] = ptx::Mma<T>::pack(p2, p3);
-                }
-                const int vr = 16 * pt + (lane & 7) + ((lane >> 3) & 1) * 8;
+                    for (int half = 0; half < 2; ++half) {
+                        const float p0 = ptx::ex2(fmaf(sc[2 * j + half][0], P.sl2, -m_use[0]));
+                        const float p1 = ptx::ex2(fmaf(sc[2 * j + half][1], P.sl2, -m_use[0]));
+                        const float p2 = ptx::ex2(fmaf(sc[2 * j + half][2], P.sl2, -m_use[1]));
+                        const float p3 = ptx::ex2(fmaf(sc[2 * j + half][3], P.sl2, -m_use[1]));
+                        l_run[0] += p0 + p1;
+                        l_run[1] += p2 + p3;
+                        pa[2 * half] = ptx::Mma<T>::pack(p0, p1);
+                        pa[2 * half + 1] = ptx::Mma<T>::pack(p2, p3);
+                    }
 #pragma unroll
-                for (int dp = 0; dp < 4; ++dp) {
-                    uint32_t vf[4];
-                    ptx::ldmatrix_x4_trans(vf, swz(v_base, vr, 2 * dp + (lane >> 4)));
-                    ptx::Mma<T>::run(o[2 * dp], pa, vf[0], vf[1]);
-                    ptx::Mma<T>::run(o[2 * dp + 1], pa, vf[2], vf[3]);
+                    for (int dp = 0; dp < 4; ++dp) {
+                        uint32_t vf[4];
+                        // the 16-byte column index 2*dp + (lane>>4) xor (row&7): xor distributes over the even part
+                        ptx::ldmatrix_x4_trans(vf, (v_addr0 ^ (uint32_t)(dp << 5)) + j * 16 * kRowBytes);
+                        ptx::Mma<T>::run(o[2 * dp], pa, vf[0], vf[1]);
+                        ptx::Mma<T>::run(o[2 * dp + 1], pa, vf[2], vf[3]);
+                    }
                 }
             }
         }
@@ -292,7 +307,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
         l_run[i] = l_run[i] > 0.f ? 1.f / l_run[i] : 0.f;
     }
-    __syncwarp();  // every lane has read its Q fragments before the rows are overwritten
+    __syncwarp();  // every lane has finished reading Q before the rows are overwritten
     {
         uint8_t *so = sQ + row0 * kRowBytes;
 #pragma unroll
@@ -347,31 +362,28 @@ int make_map(CUtensorMap *m, const void *base, int dtype, int64_t HH, int64_t S1
     return MAT_OK;
 }
 
-template <int TQ> constexpr size_t smem_bytes() {
-    return 1024 + (size_t)TQ * kRowBytes + (size_t)kStages * kStageBytes + 8 * (1 + 2 * kStages);
-}
-
-template <typename T, int KIND, int TQ>
-int launch_kind(const Problem &p, const FlashParams &fp, int64_t dil) {
+template <typename T, int KIND, int TQ, int TK, int NP, int STAGES, bool SINGLE, int MINB>
+int launch_kind(const Problem &p, const FlashParams &fp, int64_t dil, const char *name) {
     CUtensorMap mq, mk, mv, mo;
     const int64_t HH = fp.HH;
     if (int rc = make_map(&mq, p.q, p.dtype, HH, p.Sq / dil, p.B, TQ)) return rc;
     if (int rc = make_map(&mk, p.k, p.dtype, HH, p.Skv / dil, p.B, TK)) return rc;
     if (int rc = make_map(&mv, p.v, p.dtype, HH, p.Skv / dil, p.B, TK)) return rc;
     if (int rc = make_map(&mo, p.o, p.dtype, HH, p.Sq / dil, p.B, 16)) return rc;
-    auto kern = flash_fwd_kernel<T, KIND, TQ>;
+    auto kern = flash_fwd_kernel<T, KIND, TQ, TK, NP, STAGES, SINGLE, MINB>;
+    constexpr size_t smem = flash_smem_bytes<TQ, TK, STAGES>();
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<TQ>());
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(flash_fwd_kernel)");
     const int64_t ctas = (int64_t)fp.n_tiles * HH * p.B;
     if (ctas > 0x7fffffffLL) return fail(MAT_ERR_UNSUPPORTED, "too many query tiles for one launch");
-    kern<<<(unsigned)ctas, (TQ / 16 + 1) * 32, smem_bytes<TQ>(), p.stream>>>(mq, mk, mv, mo, fp);
+    kern<<<(unsigned)ctas, (TQ / 16 + 1) * 32, smem, p.stream>>>(mq, mk, mv, mo, fp);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "flash_fwd_kernel launch");
-    note_kernel(KIND == MAT_WINDOW ? "mma_window" : "mma_block");
+    note_kernel(name);
     return MAT_OK;
 }
 
@@ -383,14 +395,31 @@ int launch_t(const Problem &p) {
     fp.Sq1 = (int32_t)(p.Sq / dil);
     fp.Skv1 = (int32_t)(p.Skv / dil);
     fp.off1 = (int32_t)(p.pat.q_offset / dil);
-    fp.left = (int32_t)std::min<int64_t>(p.pat.left, fp.Skv1);
-    fp.right = (int32_t)std::min<int64_t>(p.pat.right, fp.Skv1);
     fp.n_tiles = (fp.Sq1 + TQ - 1) / TQ;
     fp.HH = (int32_t)(p.H * dil);
     fp.sl2 = p.scale * 1.4426950408889634f;
-    fp.pat = p.pat;
-    if (p.pat.kind == MAT_WINDOW) return launch_kind<T, MAT_WINDOW, TQ>(p, fp, dil);
-    return launch_kind<T, MAT_BLOCK, TQ>(p, fp, dil);
+    fp.block = (int32_t)p.pat.block;
+    fp.per_blk = fp.block / 64;
+    fp.n_qblocks = p.pat.n_qblocks;
+    fp.rowptr = p.pat.rowptr;
+    fp.colidx = p.pat.colidx;
+    if (p.pat.kind == MAT_WINDOW) {
+        fp.left = fp.mask_left = (int32_t)std::min<int64_t>(p.pat.left, fp.Skv1);
+        fp.right = fp.mask_right = (int32_t)std::min<int64_t>(p.pat.right, fp.Skv1);
+        // one stage holds the tile's whole window when TQ + left (rounded up to 16, plus the
+        // misalignment of the shard offset) + right fits TQ + 64 keys
+        const int mis = fp.off1 & 15;
+        // chunk 0 starts at the tile's first key rounded down to 16: that slack adds to the span
+        const int slack = (((mis - fp.left) % 16) + 16) % 16;
+        const int pairs = (fp.left + 15) / 16 + (15 + fp.right) / 16 + 1 + (mis ? 1 : 0);
+        if (fp.left + slack + fp.right <= 64 && pairs <= 5)
+            return launch_kind<T, MAT_WINDOW, TQ, TQ + 64, 5, 1, true, 4>(p, fp, dil, "mma_window");
+        return launch_kind<T, MAT_WINDOW, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_window");
+    }
+    fp.left = fp.right = 0;
+    fp.mask_left = kBig;
+    fp.mask_right = p.pat.causal ? 0 : kBig;
+    return launch_kind<T, MAT_BLOCK, TQ, 64, 4, 3, false, 3>(p, fp, dil, "mma_block");
 }
 
 }  // namespace
@@ -400,7 +429,7 @@ bool mma_flash_supports(const Problem &p) {
     if (p.D != 64) return false;
     const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
     if (al % 16) return false;
-    if (p.Skv >= (1LL << 31) || p.B > 65535) return false;
+    if (p.Skv >= (1LL << 28) || p.B > 65535) return false;
     if (p.pat.kind == MAT_WINDOW) {
         const int64_t dil = p.pat.dilation;
         if (p.Sq % dil || p.Skv % dil || p.pat.q_offset % dil) return false;
@@ -409,7 +438,7 @@ bool mma_flash_supports(const Problem &p) {
     }
     if (p.pat.kind == MAT_BLOCK) {
         // query tiles of 64 rows must not straddle a layout row
-        return p.pat.block % 64 == 0 && p.pat.q_offset % 64 == 0;
+        return p.pat.block % 64 == 0 && p.pat.q_offset % 64 == 0 && p.pat.block < (1 << 24);
     }
     return false;
 }

@@ -137,7 +137,11 @@ def test_shard_with_halo_equals_full_run(spec, dtype):
         hi = min(S, (r + 1) * chunk + spec.right * spec.dilation)
         part = run(spec.shifted(r * chunk - lo), q[:, r * chunk:(r + 1) * chunk].contiguous(),
                    k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous())
-        assert torch.equal(part, full[:, r * chunk:(r + 1) * chunk]), f"shard {r}"
+        ref = full[:, r * chunk:(r + 1) * chunk]
+        if dtype == torch.float32:   # row-warp kernel: same key order per row, bit-identical
+            assert torch.equal(part, ref), f"shard {r}"
+        else:  # tiled kernel: key chunks align to the shard's own origin, so sums regroup (a few bf16 ulps)
+            assert (part.float() - ref.float()).abs().max() <= 2 ** -6, f"shard {r}"
     check_close(full, oracle_out(q, k, v, spec), dtype)
 
 
