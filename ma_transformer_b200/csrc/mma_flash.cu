@@ -77,8 +77,8 @@ struct Chunks {
             start = lo;
             n = hi >= lo ? (hi - lo) / TK + 1 : 0;
         } else {
-            const int64_t r = (int64_t)(q0 + P.off1) / P.block;
-            if (r < P.n_qblocks) {
+            const uint32_t r = (uint32_t)(q0 + P.off1) / (uint32_t)P.block;
+            if ((int64_t)r < P.n_qblocks) {
                 e0 = P.rowptr[r];
                 n = (P.rowptr[r + 1] - e0) * P.per_blk;
             }
@@ -113,11 +113,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    const int64_t w = blockIdx.x;
-    const int hh = (int)(w % P.HH);
-    const int tile = (int)((w / P.HH) % P.n_tiles);
-    const int b = (int)(w / ((int64_t)P.HH * P.n_tiles));
-    const int q0 = tile * TQ;
+    // grid = (heads, query tiles, batch): the heads of one tile are scheduled together, so the
+    // 128-byte rows they fetch from the same token range share DRAM pages
+    const int hh = blockIdx.x;
+    const int b = blockIdx.z;
+    const int q0 = blockIdx.y * TQ;
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(bar_q, 1);
@@ -162,6 +162,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     // key range this warp's rows can attend
     const int k_lo = max(p_min - P.mask_left, 0);
     const int k_hi = min(p_max + P.mask_right, P.Skv1 - 1);
+    // a 16-key pair starting at key a needs no mask iff w_lo <= a <= w_hi
+    const int w_lo = max(p_max - P.mask_left, 0);
+    const int w_hi = min(p_min + P.mask_right, P.Skv1 - 1) - 15;
 
     if (!ptx::mbar_wait(bar_q, 0)) {
         atomicExch(&g_flash_status, kStatusWaitTimeout);
@@ -190,8 +193,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const int last = k_hi >= kb ? min(TK / 16 - 1, (k_hi - kb) >> 4) : -1;
         const bool edge = kb < 0 || kb + TK > P.Skv1;  // chunk reaches outside the key tensor
 
-        for (int pp = first; pp <= last; pp += NP) {
-            const int npairs = min(NP, last - pp + 1);
+        // SINGLE: one step of exactly NP pairs (pairs past the key set are masked away, which
+        // only costs work on the sequence's first and last tiles), so the step is straight-line code
+        for (int pp = SINGLE ? min(first, TK / 16 - NP) : first; pp <= last; pp += SINGLE ? TK : NP) {
+            const int npairs = SINGLE ? NP : min(NP, last - pp + 1);
             float sc[2 * NP][4];
 #pragma unroll
             for (int n = 0; n < 2 * NP; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
@@ -222,9 +227,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             for (int j = 0; j < NP; ++j) {
                 if (j < npairs) {
                     const int a = kb + 16 * (pp + j);
-                    const bool whole = a - p_max >= -P.mask_left && a + 15 - p_min <= P.mask_right &&
-                                       a >= 0 && a + 15 < P.Skv1;
-                    if (!whole) {
+                    if (a < w_lo || a > w_hi) {
 #pragma unroll
                         for (int half = 0; half < 2; ++half)
 #pragma unroll
@@ -305,18 +308,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     for (int i = 0; i < 2; ++i) {
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
-        l_run[i] = l_run[i] > 0.f ? 1.f / l_run[i] : 0.f;
+        l_run[i] = l_run[i] > 0.f ? __frcp_rn(l_run[i]) : 0.f;
     }
     __syncwarp();  // every lane has finished reading Q before the rows are overwritten
     {
         uint8_t *so = sQ + row0 * kRowBytes;
+        // element (row g + 8i, columns 8n + 2tq..) sits in 16-byte column n ^ g of its row
+        const uint32_t so_lane = ptx::smem_u32(so) + g * kRowBytes + (g << 4) + tq * 4;
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                const int r = g + 8 * i;
                 const uint32_t v = ptx::Mma<T>::pack(o[n][2 * i] * l_run[i], o[n][2 * i + 1] * l_run[i]);
-                *reinterpret_cast<uint32_t *>(so + r * kRowBytes + ((n ^ (r & 7)) << 4) + tq * 4) = v;
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"((so_lane ^ (uint32_t)(n << 4)) + i * 8 * kRowBytes), "r"(v)
+                             : "memory");
             }
         }
         ptx::fence_proxy_async_smem();
@@ -378,9 +383,8 @@ int launch_kind(const Problem &p, const FlashParams &fp, int64_t dil, const char
         attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(flash_fwd_kernel)");
-    const int64_t ctas = (int64_t)fp.n_tiles * HH * p.B;
-    if (ctas > 0x7fffffffLL) return fail(MAT_ERR_UNSUPPORTED, "too many query tiles for one launch");
-    kern<<<(unsigned)ctas, (TQ / 16 + 1) * 32, smem, p.stream>>>(mq, mk, mv, mo, fp);
+    const dim3 grid((unsigned)HH, (unsigned)fp.n_tiles, (unsigned)p.B);
+    kern<<<grid, (TQ / 16 + 1) * 32, smem, p.stream>>>(mq, mk, mv, mo, fp);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "flash_fwd_kernel launch");
     note_kernel(name);
@@ -412,6 +416,8 @@ int launch_t(const Problem &p) {
         // chunk 0 starts at the tile's first key rounded down to 16: that slack adds to the span
         const int slack = (((mis - fp.left) % 16) + 16) % 16;
         const int pairs = (fp.left + 15) / 16 + (15 + fp.right) / 16 + 1 + (mis ? 1 : 0);
+        if (fp.left + slack + fp.right <= 64 && pairs <= 3)
+            return launch_kind<T, MAT_WINDOW, TQ, TQ + 64, 3, 1, true, 4>(p, fp, dil, "mma_window");
         if (fp.left + slack + fp.right <= 64 && pairs <= 5)
             return launch_kind<T, MAT_WINDOW, TQ, TQ + 64, 5, 1, true, 4>(p, fp, dil, "mma_window");
         return launch_kind<T, MAT_WINDOW, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_window");
@@ -430,6 +436,10 @@ bool mma_flash_supports(const Problem &p) {
     const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
     if (al % 16) return false;
     if (p.Skv >= (1LL << 28) || p.B > 65535) return false;
+    {   // grid.y carries the query tiles
+        const int64_t dil = p.pat.kind == MAT_WINDOW ? p.pat.dilation : 1;
+        if ((p.Sq / dil + 63) / 64 > 65535) return false;
+    }
     if (p.pat.kind == MAT_WINDOW) {
         const int64_t dil = p.pat.dilation;
         if (p.Sq % dil || p.Skv % dil || p.pat.q_offset % dil) return false;
