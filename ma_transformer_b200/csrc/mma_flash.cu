@@ -177,7 +177,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
     for (int n = 0; n < 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY};
-    float l_run[2] = {0.f, 0.f};
+    float lsum[4] = {0.f, 0.f, 0.f, 0.f};  // P * ones: [0] = row g, [2] = row g + 8 (every column alike)
 
     for (int c = 0; c < chunks.n; ++c) {
         const int s = c % STAGES, use = c / STAGES;
@@ -260,7 +260,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     const float mu = m_new == -INFINITY ? 0.f : m_new;
                     const float alpha = ptx::ex2((m_run[i] - mu) * P.sl2);
                     m_run[i] = m_new;
-                    l_run[i] *= alpha;
+                    lsum[2 * i] *= alpha;
 #pragma unroll
                     for (int n = 0; n < 8; ++n) {
                         o[n][2 * i] *= alpha;
@@ -276,18 +276,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
             for (int j = 0; j < NP; ++j) {
                 if (j < npairs) {
+                    // exp2 on packed 16-bit pairs: the argument is rounded to the operand type first
+                    // (error in a weight <= |x| * 2^x * 2^-9, i.e. < 1e-3 of the row maximum), and the
+                    // row sums come out of the tensor core as P times a column of ones, so the
+                    // normaliser is the sum of exactly the weights that multiply V.
                     uint32_t pa[4];
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
-                        const float p0 = ptx::ex2(fmaf(sc[2 * j + half][0], P.sl2, -m_use[0]));
-                        const float p1 = ptx::ex2(fmaf(sc[2 * j + half][1], P.sl2, -m_use[0]));
-                        const float p2 = ptx::ex2(fmaf(sc[2 * j + half][2], P.sl2, -m_use[1]));
-                        const float p3 = ptx::ex2(fmaf(sc[2 * j + half][3], P.sl2, -m_use[1]));
-                        l_run[0] += p0 + p1;
-                        l_run[1] += p2 + p3;
-                        pa[2 * half] = ptx::Mma<T>::pack(p0, p1);
-                        pa[2 * half + 1] = ptx::Mma<T>::pack(p2, p3);
+                        const float x0 = fmaf(sc[2 * j + half][0], P.sl2, -m_use[0]);
+                        const float x1 = fmaf(sc[2 * j + half][1], P.sl2, -m_use[0]);
+                        const float x2 = fmaf(sc[2 * j + half][2], P.sl2, -m_use[1]);
+                        const float x3 = fmaf(sc[2 * j + half][3], P.sl2, -m_use[1]);
+                        pa[2 * half] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
+                        pa[2 * half + 1] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x2, x3));
                     }
+                    ptx::Mma<T>::run(lsum, pa, ptx::Mma<T>::kOnes, ptx::Mma<T>::kOnes);
 #pragma unroll
                     for (int dp = 0; dp < 4; ++dp) {
                         uint32_t vf[4];
@@ -304,12 +307,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
 
     // ---- epilogue: normalise, stage the warp's 16 rows in its own Q rows, bulk store ----
+    float l_run[2];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
-        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
-        l_run[i] = l_run[i] > 0.f ? __frcp_rn(l_run[i]) : 0.f;
-    }
+    for (int i = 0; i < 2; ++i) l_run[i] = lsum[2 * i] > 0.f ? __frcp_rn(lsum[2 * i]) : 0.f;
     __syncwarp();  // every lane has finished reading Q before the rows are overwritten
     {
         uint8_t *so = sQ + row0 * kRowBytes;

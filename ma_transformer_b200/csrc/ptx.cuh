@@ -30,16 +30,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+// One try_wait with a suspend-time hint: the thread sleeps in hardware until the
+// phase completes or about `hint_ns` have passed, instead of spinning.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity, uint32_t hint_ns = 200000u) {
     uint32_t ok;
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok != 0;
 }
@@ -48,16 +50,13 @@ __device__ __forceinline__ uint64_t global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait: polls for at most about two seconds of wall time, then gives up.
+// Bounded wait: gives up after about two seconds of wall time.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    uint64_t t0 = 0;
-    for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+    for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 1023u) == 1023u) {
-            const uint64_t now = global_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > 2000000000ull) return false;
-        }
+        if (global_ns() - t0 > 2000000000ull) return false;
     }
 }
 
@@ -109,6 +108,19 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// exp2 of two packed 16-bit values in one instruction; the result is already the
+// packed operand the P*V mma consumes.
+__device__ __forceinline__ uint32_t ex2_bf16x2(uint32_t x) {
+    uint32_t y;
+    asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
+    uint32_t y;
+    asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+
 template <typename T> struct Mma;
 template <> struct Mma<__nv_bfloat16> {
     static __device__ __forceinline__ void run(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
@@ -123,6 +135,8 @@ template <> struct Mma<__nv_bfloat16> {
         __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
         return *reinterpret_cast<uint32_t *>(&v);
     }
+    static __device__ __forceinline__ uint32_t ex2_packed(uint32_t x) { return ex2_bf16x2(x); }
+    static constexpr uint32_t kOnes = 0x3F803F80u;  // (1.0, 1.0)
 };
 template <> struct Mma<__half> {
     static __device__ __forceinline__ void run(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
@@ -137,6 +151,8 @@ template <> struct Mma<__half> {
         __half2 v = __floats2half2_rn(lo, hi);
         return *reinterpret_cast<uint32_t *>(&v);
     }
+    static __device__ __forceinline__ uint32_t ex2_packed(uint32_t x) { return ex2_f16x2(x); }
+    static constexpr uint32_t kOnes = 0x3C003C00u;  // (1.0, 1.0)
 };
 
 }  // namespace ptx
