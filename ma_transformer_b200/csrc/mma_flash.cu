@@ -95,8 +95,12 @@ constexpr size_t flash_smem_bytes() {
     return 1024 + (size_t)TQ * kRowBytes + (size_t)STAGES * 2 * TK * kRowBytes + 8 * (1 + 2 * STAGES);
 }
 
+// SINGLE kernels issue all their loads up front, so they carry no producer warp: lane 0 of
+// warp 0 issues the copies and then computes like every other lane.
+template <int TQ, bool SINGLE> constexpr int flash_threads() { return (TQ / 16 + (SINGLE ? 0 : 1)) * 32; }
+
 template <typename T, int KIND, int TQ, int TK, int NP, int STAGES, bool SINGLE, int MINB>
-__global__ void __launch_bounds__((TQ / 16 + 1) * 32, MINB)
+__global__ void __launch_bounds__(flash_threads<TQ, SINGLE>(), MINB)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                  const FlashParams P) {
@@ -131,7 +135,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     const Chunks<KIND, TQ, TK> chunks(P, q0);
 
-    if (warp == NW) {  // ---- producer warp: one lane feeds the ring ----
+    if (SINGLE ? warp == 0 : warp == NW) {  // ---- producer: one lane feeds the ring ----
         if (lane == 0) {
             ptx::mbar_expect_tx(bar_q, TQ * kRowBytes);
             ptx::tma_load_4d(sQ, &map_q, bar_q, 0, hh, q0, b);
@@ -148,7 +152,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 ptx::tma_load_4d(dst + TK * kRowBytes, &map_v, bar_full + s, 0, hh, kb, b);
             }
         }
-        return;
+        if (!SINGLE) return;
+        __syncwarp();
     }
 
     // ---- consumer warps ----
@@ -384,7 +389,7 @@ int launch_kind(const Problem &p, const FlashParams &fp, int64_t dil, const char
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(flash_fwd_kernel)");
     const dim3 grid((unsigned)HH, (unsigned)fp.n_tiles, (unsigned)p.B);
-    kern<<<grid, (TQ / 16 + 1) * 32, smem, p.stream>>>(mq, mk, mv, mo, fp);
+    kern<<<grid, flash_threads<TQ, SINGLE>(), smem, p.stream>>>(mq, mk, mv, mo, fp);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "flash_fwd_kernel launch");
     note_kernel(name);
@@ -417,9 +422,9 @@ int launch_t(const Problem &p) {
         const int slack = (((mis - fp.left) % 16) + 16) % 16;
         const int pairs = (fp.left + 15) / 16 + (15 + fp.right) / 16 + 1 + (mis ? 1 : 0);
         if (fp.left + slack + fp.right <= 64 && pairs <= 3)
-            return launch_kind<T, MAT_WINDOW, TQ, TQ + 64, 3, 1, true, 4>(p, fp, dil, "mma_window");
+            return launch_kind<T, MAT_WINDOW, TQ, TQ + 64, 3, 1, true, 5>(p, fp, dil, "mma_window");
         if (fp.left + slack + fp.right <= 64 && pairs <= 5)
-            return launch_kind<T, MAT_WINDOW, TQ, TQ + 64, 5, 1, true, 4>(p, fp, dil, "mma_window");
+            return launch_kind<T, MAT_WINDOW, TQ, TQ + 64, 5, 1, true, 5>(p, fp, dil, "mma_window");
         return launch_kind<T, MAT_WINDOW, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_window");
     }
     fp.left = fp.right = 0;
