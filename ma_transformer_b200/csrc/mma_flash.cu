@@ -203,8 +203,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         for (int pp = SINGLE ? min(first, TK / 16 - NP) : first; pp <= last; pp += SINGLE ? TK : NP) {
             const int npairs = SINGLE ? NP : min(NP, last - pp + 1);
             float sc[2 * NP][4];
-#pragma unroll
-            for (int n = 0; n < 2 * NP; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
 
             // ---- S = Q K^T over the step's pairs ----
             const int kr = 16 * pp + (lane & 7) + (lane >> 4) * 8;
@@ -218,8 +216,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     if (j < npairs) {
                         uint32_t kf[4];
                         ptx::ldmatrix_x4(kf, k_addr + j * 16 * kRowBytes);
-                        ptx::Mma<T>::run(sc[2 * j], qa, kf[0], kf[1]);
-                        ptx::Mma<T>::run(sc[2 * j + 1], qa, kf[2], kf[3]);
+                        if (ks == 0) {
+                            ptx::Mma<T>::run0(sc[2 * j], qa, kf[0], kf[1]);
+                            ptx::Mma<T>::run0(sc[2 * j + 1], qa, kf[2], kf[3]);
+                        } else {
+                            ptx::Mma<T>::run(sc[2 * j], qa, kf[0], kf[1]);
+                            ptx::Mma<T>::run(sc[2 * j + 1], qa, kf[2], kf[3]);
+                        }
                     }
                 }
             }
@@ -295,14 +298,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         pa[2 * half] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
                         pa[2 * half + 1] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x2, x3));
                     }
-                    ptx::Mma<T>::run(lsum, pa, ptx::Mma<T>::kOnes, ptx::Mma<T>::kOnes);
+                    if (SINGLE && j == 0) ptx::Mma<T>::run0(lsum, pa, ptx::Mma<T>::kOnes, ptx::Mma<T>::kOnes);
+                    else ptx::Mma<T>::run(lsum, pa, ptx::Mma<T>::kOnes, ptx::Mma<T>::kOnes);
 #pragma unroll
                     for (int dp = 0; dp < 4; ++dp) {
                         uint32_t vf[4];
                         // the 16-byte column index 2*dp + (lane>>4) xor (row&7): xor distributes over the even part
                         ptx::ldmatrix_x4_trans(vf, (v_addr0 ^ (uint32_t)(dp << 5)) + j * 16 * kRowBytes);
-                        ptx::Mma<T>::run(o[2 * dp], pa, vf[0], vf[1]);
-                        ptx::Mma<T>::run(o[2 * dp + 1], pa, vf[2], vf[3]);
+                        if (SINGLE && j == 0) {
+                            ptx::Mma<T>::run0(o[2 * dp], pa, vf[0], vf[1]);
+                            ptx::Mma<T>::run0(o[2 * dp + 1], pa, vf[2], vf[3]);
+                        } else {
+                            ptx::Mma<T>::run(o[2 * dp], pa, vf[0], vf[1]);
+                            ptx::Mma<T>::run(o[2 * dp + 1], pa, vf[2], vf[3]);
+                        }
                     }
                 }
             }

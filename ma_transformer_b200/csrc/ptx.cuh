@@ -131,6 +131,15 @@ template <> struct Mma<__nv_bfloat16> {
             : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
     }
+    // D = A*B with a zero accumulator: no registers have to be cleared first
+    static __device__ __forceinline__ void run0(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                                uint32_t b1) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+            "{%8,%9}, {%10,%10,%10,%10};"
+            : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+    }
     static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
         __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
         return *reinterpret_cast<uint32_t *>(&v);
@@ -146,6 +155,14 @@ template <> struct Mma<__half> {
             "{%8,%9}, {%0,%1,%2,%3};"
             : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    static __device__ __forceinline__ void run0(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                                uint32_t b1) {
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+            "{%8,%9}, {%10,%10,%10,%10};"
+            : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
     }
     static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
         __half2 v = __floats2half2_rn(lo, hi);
