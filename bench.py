@@ -37,6 +37,9 @@ SEED = 2
 WORKLOAD = f"causal sliding-window fwd B={B} N={SEQ} H={H} d={D} taps={TAPS} bf16"
 BYTES_PER_TOKEN = 4 * H * D * 2          # read Q,K,V + write O, bf16
 METRIC = "sparse-attn fwd tokens/s @N=64K,w=64,bf16"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the window kernel on this
+# workload, from the ncu capture summarised in profiles/mma_window_cfg2_n64k.md, per token
+NCU_TRAFFIC_PER_TOKEN = (201.354e6 + 49.839e6) / 65536
 
 
 def measured_peak_gbs():
@@ -316,14 +319,14 @@ def gpu_arm(args):
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "sharding": f"sequence x{world}, {TAPS - 1}-row K/V halo" if world > 1 else "none",
+            "config": {"workload": WORKLOAD, "sharding": f"sequence x{world}, {TAPS - 1}-row K/V halo (64 rows exchanged)" if world > 1 else "none",
                        "l2": f"{n_sets} rotating input sets of {per_rank_bytes >> 20} MiB per GPU (> 126 MB L2 between reuses)"},
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "api": "sparse_attention_cuda.forward_host (mat_sparse_attn_fwd_host)"},
             "gpu_launches": int(n_launch.item()),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": f"{peak_kind} HBM copy bandwidth",
+                         "traffic": NCU_TRAFFIC_PER_TOKEN * rows, "peak_source": f"{peak_kind} HBM copy bandwidth",
                          "kernel": nat.last_kernel(), "bytes_per_launch_algorithmic": per_rank_bytes},
             "device_status": status,
         }

@@ -46,13 +46,21 @@ class ShardLayout:
         return self.halo_front + self.rows + self.halo_back
 
 
+def front_halo_rows(spec: PatternSpec) -> int:
+    """Key rows a shard keeps in front of its chunk: the window's reach
+    ``left*dilation`` rounded up to a multiple of ``16*dilation``, so the chunk's
+    first query stays aligned to the kernels' 16-key column pairs (63 -> 64)."""
+    unit = 16 * spec.dilation
+    return -(-(spec.left * spec.dilation) // unit) * unit
+
+
 def shard_layout(spec: PatternSpec, seq_len: int, rank: int, world: int) -> ShardLayout:
     if spec.kind != WINDOW:
         raise ValueError("sequence sharding applies to window patterns; shard (batch, head) pairs for the others")
     if seq_len % world:
         raise ValueError(f"sequence length {seq_len} is not divisible by {world} ranks")
     rows = seq_len // world
-    reach_l, reach_r = spec.left * spec.dilation, spec.right * spec.dilation
+    reach_l, reach_r = front_halo_rows(spec), spec.right * spec.dilation
     if max(reach_l, reach_r) > rows:
         raise ValueError("window reaches past the neighbouring chunk: use fewer ranks")
     if rows % spec.dilation:
@@ -102,7 +110,7 @@ class SequenceShardedAttention:
     def _p2p_ops(self, k_ext: torch.Tensor, v_ext: torch.Tensor):
         """send/recv pairs for both tensors; returns (ops, copies_after_recv)."""
         L, spec = self.layout, self.spec
-        reach_l, reach_r = spec.left * spec.dilation, spec.right * spec.dilation
+        reach_l, reach_r = front_halo_rows(spec), spec.right * spec.dilation
         ops, after = [], []
         peer = lambda r: r if self.group is None else dist.get_global_rank(self.group, r)
 

