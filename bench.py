@@ -203,7 +203,7 @@ def gpu_arm(args):
     from ma_transformer_b200 import _native as nat
     from ma_transformer_b200 import sparse_attention_cuda as ext
     from ma_transformer_b200.patterns import PatternSpec
-    from ma_transformer_b200.sharded import SequenceShardedAttention
+    from ma_transformer_b200.sharded import PeerHaloAttention, SequenceShardedAttention
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -228,13 +228,13 @@ def gpu_arm(args):
     per_rank_bytes = rows * BYTES_PER_TOKEN
     n_sets = max(2, -(-(2 * 126 * 2 ** 20) // per_rank_bytes) + 1)
     sets = []
+    sharded = peer = None
     if world == 1:
         for s in range(n_sets):
             sets.append(tuple(t.to(dev).roll(s, dims=1).contiguous() for t in (q_cpu, k_cpu, v_cpu)))
-        sharded = None
-    else:
+    elif args.halo == "nccl":
+        # halo rows exchanged by send/recv into an extended K/V buffer before the edge tiles run
         sharded = SequenceShardedAttention(spec, SEQ)
-        L = sharded.layout
         for s in range(n_sets):
             q = q_cpu[:, a:b].to(dev).roll(s, dims=1).contiguous()
             k_ext = sharded.alloc_kv(B, H, D, torch.bfloat16, dev)
@@ -242,18 +242,28 @@ def gpu_arm(args):
             sharded.chunk_view(k_ext).copy_(k_cpu[:, a:b].to(dev).roll(s, dims=1))
             sharded.chunk_view(v_ext).copy_(v_cpu[:, a:b].to(dev).roll(s, dims=1))
             sets.append((q, k_ext, v_ext))
+    else:
+        # each rank holds only its chunk; edge tiles read the neighbour's rows in place over NVLink
+        peer = PeerHaloAttention(spec, SEQ)
+        for s in range(n_sets):
+            q, k, v = (t[:, a:b].to(dev).roll(s, dims=1).contiguous() for t in (q_cpu, k_cpu, v_cpu))
+            sets.append((q, peer.register(k, v)))
     out = torch.empty(B, rows, H, D, dtype=torch.bfloat16, device=dev)
     launches = [0]
 
     def step(i):
-        q, k, v = sets[i % n_sets]
-        if sharded is None:
-            ext.forward_pattern(q, k, v, spec, out=out)
-            launches[0] += 1
-        else:
+        if sharded is not None:
+            q, k, v = sets[i % n_sets]
             sharded.forward(q, k, v, out=out)
             front, back = sharded.edge_rows()
-            launches[0] += 1 + (1 if front else 0) + (1 if back else 0)
+            return 1 + (1 if front else 0) + (1 if back else 0)
+        if peer is not None:
+            q, shard = sets[i % n_sets]
+            peer.forward(q, shard, out=out)
+        else:
+            q, k, v = sets[i % n_sets]
+            ext.forward_pattern(q, k, v, spec, out=out)
+        return 1
 
     def barrier():
         if world > 1:
@@ -263,15 +273,45 @@ def gpu_arm(args):
     for i in range(args.warmup):
         step(i)
     barrier()
+
+    # Launch-bound at 8 GPUs (a shard's forward is a few microseconds): the steps are captured in
+    # CUDA graphs, one graph that runs one step per input set plus one single-step graph per set
+    # for the remainder, so exactly K steps run and the host issues K / n_sets launches.
+    use_graph = args.graph and sharded is None
+    if use_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            round_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(round_graph, stream=side):
+                for s in range(n_sets):
+                    step(s)
+            single_graphs = []
+            for s in range(n_sets):
+                g1 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g1, stream=side):
+                    step(s)
+                single_graphs.append(g1)
+        torch.cuda.current_stream().wait_stream(side)
+        round_graph.replay()      # one untimed round warms the instantiated graphs
+        barrier()
+
     sampler = ClockSampler(local)
     sampler.start()
-    launches[0] = 0
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t_host0 = time.perf_counter()
     ev0.record()
-    for i in range(args.steps):
-        step(args.warmup + i)
+    if use_graph:
+        rounds, rest = divmod(args.steps, n_sets)
+        for _ in range(rounds):
+            round_graph.replay()
+        for s in range(rest):
+            single_graphs[s].replay()
+        launches[0] = args.steps
+    else:
+        for i in range(args.steps):
+            launches[0] += step(args.warmup + i)
     ev1.record()
     barrier()
     t_host1 = time.perf_counter()
@@ -319,7 +359,8 @@ def gpu_arm(args):
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "sharding": f"sequence x{world}, {TAPS - 1}-row K/V halo (64 rows exchanged)" if world > 1 else "none",
+            "config": {"workload": WORKLOAD, "sharding": (f"sequence x{world}, {TAPS - 1}-row K/V halo, " + ("read in place from the neighbour GPU by the kernel" if peer is not None else "64 rows exchanged by NCCL send/recv")) if world > 1 else "none",
+                       "launch": "CUDA graphs" if use_graph else "one host launch per kernel",
                        "l2": f"{n_sets} rotating input sets of {per_rank_bytes >> 20} MiB per GPU (> 126 MB L2 between reuses)"},
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -345,6 +386,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="device-resident leg only (for profiler captures)")
+    ap.add_argument("--halo", default="peer", choices=["peer", "nccl"],
+                    help="N>1: edge tiles read the neighbour's rows in place (peer), or send/recv exchange (nccl)")
+    ap.add_argument("--no-graph", dest="graph", action="store_false", help="launch every step from the host")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 

@@ -107,6 +107,51 @@ int mat_sparse_attn_fwd_window(const void *q, const void *k, const void *v, void
                                int64_t window_size, void *stream);
 
 /*
+ * Forward pass of one SEQUENCE SHARD whose window reaches into its neighbours:
+ * one process per GPU owns a contiguous chunk [B, S, H, D] of a longer sequence,
+ * and the query tiles at the chunk's edges read the halo rows they need straight
+ * from the neighbouring GPUs' K/V tensors (peer-mapped device pointers, fetched
+ * by ordinary tiled TMA loads inside the same kernel): no separate exchange step,
+ * no halo copy.  k_prev/v_prev: the previous shard's [B, S_prev, H, D] tensors or
+ * NULL on the first shard; k_next/v_next likewise for two-sided windows.
+ * MAT_WINDOW patterns with 16-bit inputs and D = 64; S_prev (and S when a next
+ * shard is given) must be multiples of 16*dilation and cover the window's reach.
+ * The caller guarantees that the neighbours' tensors are complete before the
+ * launch and stay unchanged until it finishes.  The reference has no distributed
+ * path (no counterpart); the single-GPU call it extends is sparse_forward_cuda
+ * (src/cuda/sparse_attention_kernel.cu:423-458).
+ */
+int mat_sparse_attn_fwd_sharded(const void *q, const void *k, const void *v, void *o,
+                                const void *k_prev, const void *v_prev, int64_t S_prev,
+                                const void *k_next, const void *v_next, int64_t S_next,
+                                int64_t B, int64_t S, int64_t H, int64_t D, int dtype,
+                                const mat_pattern_spec *spec, float scale, void *stream);
+
+/*
+ * Lets kernels running on `device` read memory that lives on `peer_device`
+ * (cudaDeviceEnablePeerAccess; already-enabled is not an error).  Call once per
+ * neighbour before mat_sparse_attn_fwd_sharded.  No counterpart in the reference.
+ */
+int mat_enable_peer_access(int device, int peer_device);
+
+/*
+ * Sharing a shard's K/V with the process that drives the neighbouring GPU (one
+ * process per GPU).  No counterpart in the reference (it is single-process).
+ *   mat_ipc_export  fills a MAT_IPC_HANDLE_BYTES handle naming the device
+ *                   allocation that contains dev_ptr, and dev_ptr's byte offset
+ *                   inside it; send both to the neighbour by any host channel.
+ *   mat_ipc_open    in the neighbour's process: maps that allocation for kernels
+ *                   running on `device` (peer access over NVLink) and returns its
+ *                   base; the tensor is at base + offset.  Open each handle once
+ *                   per process and reuse the base.
+ *   mat_ipc_close   unmaps it.
+ */
+#define MAT_IPC_HANDLE_BYTES 64
+int mat_ipc_export(const void *dev_ptr, void *handle_out, int64_t *offset_out);
+int mat_ipc_open(const void *handle, int device, void **base_out);
+int mat_ipc_close(void *base, int device);
+
+/*
  * Forward pass on HOST buffers: the counterpart of the CPU engine's call
  * ma_core.compute_sparse_attention and the marshalling around it
  * (src/csrc/ma_core.cpp:160-246, src/layers/ma_core_bridge.py:102-112,157-181).

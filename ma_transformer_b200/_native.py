@@ -18,8 +18,9 @@ MAT_WINDOW, MAT_BLOCK, MAT_LONGFORMER = 0, 1, 2
 EXPORTS = (
     "mat_version", "mat_last_error", "mat_last_kernel", "mat_device_status",
     "mat_sparse_attn_fwd", "mat_sparse_attn_workspace_bytes", "mat_sparse_attn_fwd_window",
-    "mat_sparse_attn_fwd_host", "mat_sparse_attn_host_staging_bytes",
-    "mat_pattern_rowset", "mat_pattern_nnz",
+    "mat_sparse_attn_fwd_host", "mat_sparse_attn_host_staging_bytes", "mat_sparse_attn_fwd_sharded",
+    "mat_pattern_rowset", "mat_pattern_nnz", "mat_enable_peer_access",
+    "mat_ipc_export", "mat_ipc_open", "mat_ipc_close",
 )
 
 
@@ -43,7 +44,7 @@ class NativeError(RuntimeError):
 def _load() -> C.CDLL:
     if not LIB_PATH.exists():
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m ma_transformer_b200.build_native` "
+            f"{LIB_PATH} is missing: build it with `python ma_transformer_b200/build_native.py` "
             "(there is no CPU fallback)")
     lib = C.CDLL(str(LIB_PATH))
     i64, vp, sz = C.c_int64, C.c_void_p, C.c_size_t
@@ -60,6 +61,17 @@ def _load() -> C.CDLL:
     lib.mat_sparse_attn_workspace_bytes.argtypes = [i64, i64, i64, i64, i64, C.c_int, spec_p]
     lib.mat_sparse_attn_fwd_window.restype = C.c_int
     lib.mat_sparse_attn_fwd_window.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, C.c_int, i64, vp]
+    lib.mat_sparse_attn_fwd_sharded.restype = C.c_int
+    lib.mat_sparse_attn_fwd_sharded.argtypes = [vp, vp, vp, vp, vp, vp, i64, vp, vp, i64, i64, i64, i64, i64,
+                                                C.c_int, spec_p, C.c_float, vp]
+    lib.mat_enable_peer_access.restype = C.c_int
+    lib.mat_enable_peer_access.argtypes = [C.c_int, C.c_int]
+    lib.mat_ipc_export.restype = C.c_int
+    lib.mat_ipc_export.argtypes = [vp, vp, C.POINTER(i64)]
+    lib.mat_ipc_open.restype = C.c_int
+    lib.mat_ipc_open.argtypes = [vp, C.c_int, C.POINTER(vp)]
+    lib.mat_ipc_close.restype = C.c_int
+    lib.mat_ipc_close.argtypes = [vp, C.c_int]
     lib.mat_sparse_attn_fwd_host.restype = C.c_int
     lib.mat_sparse_attn_fwd_host.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, C.c_int, spec_p,
                                              C.c_float, vp, sz, C.c_int]

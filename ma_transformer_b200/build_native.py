@@ -1,6 +1,6 @@
 """Compiles libmat_sparse_attn.so for sm_100a with nvcc, in-tree.
 
-    python -m ma_transformer_b200.build_native [--force] [--verbose]
+    python ma_transformer_b200/build_native.py [--force] [--verbose]
 
 Every .cu under csrc/ becomes one object; the objects link into
 csrc/libmat_sparse_attn.so.  nvcc cross-compiles, so no GPU is needed here.

@@ -199,6 +199,61 @@ int mat_sparse_attn_fwd_window(const void *q, const void *k, const void *v, void
     return mat_sparse_attn_fwd(q, k, v, o, B, S, S, H, D, dtype, &s, 0.f, nullptr, 0, stream);
 }
 
+int mat_sparse_attn_fwd_sharded(const void *q, const void *k, const void *v, void *o,
+                                const void *k_prev, const void *v_prev, int64_t S_prev,
+                                const void *k_next, const void *v_next, int64_t S_next, int64_t B,
+                                int64_t S, int64_t H, int64_t D, int dtype,
+                                const mat_pattern_spec *spec, float scale, void *stream) {
+    Problem p;
+    if (int rc = make_problem(p, q, k, v, o, B, S, S, H, D, dtype, spec, scale, nullptr, 0, stream))
+        return rc;
+    if (spec->kind != MAT_WINDOW)
+        return fail(MAT_ERR_UNSUPPORTED, "sequence shards apply to window patterns only");
+    if (spec->q_offset != 0) return fail(MAT_ERR_INVALID, "q_offset must be 0: the shard holds no halo rows");
+    if ((k_prev == nullptr) != (v_prev == nullptr) || (k_next == nullptr) != (v_next == nullptr))
+        return fail(MAT_ERR_INVALID, "a neighbour needs both its K and its V");
+    const int64_t dil = spec->dilation, unit = 16 * dil;
+    if (!mma_flash_supports(p))
+        return fail(MAT_ERR_UNSUPPORTED,
+                    "in-place neighbour reads need 16-bit inputs, head width 64 and S divisible by the dilation");
+    if (k_prev) {
+        if (S_prev <= 0 || S_prev % unit) return fail(MAT_ERR_INVALID, "S_prev must be a positive multiple of 16*dilation");
+        if (spec->left * dil > S_prev) return fail(MAT_ERR_UNSUPPORTED, "window reaches past the previous shard");
+        if (((uintptr_t)k_prev | (uintptr_t)v_prev) % 16) return fail(MAT_ERR_INVALID, "neighbour tensors must be 16-byte aligned");
+    } else {
+        S_prev = 0;
+    }
+    if (k_next) {
+        if (S_next <= 0 || S_next % dil || S % unit)
+            return fail(MAT_ERR_INVALID, "with a next shard, S must be a multiple of 16*dilation and S_next of the dilation");
+        if (spec->right * dil > S_next) return fail(MAT_ERR_UNSUPPORTED, "window reaches past the next shard");
+        if (((uintptr_t)k_next | (uintptr_t)v_next) % 16) return fail(MAT_ERR_INVALID, "neighbour tensors must be 16-byte aligned");
+    } else {
+        S_next = 0;
+    }
+    p.k_prev = k_prev; p.v_prev = v_prev; p.S_prev = S_prev;
+    p.k_next = k_next; p.v_next = v_next; p.S_next = S_next;
+    return launch_mma_flash(p);
+}
+
+int mat_enable_peer_access(int device, int peer_device) {
+    if (device == peer_device) return MAT_OK;
+    int can = 0;
+    cudaError_t e = cudaDeviceCanAccessPeer(&can, device, peer_device);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceCanAccessPeer");
+    if (!can) return fail(MAT_ERR_UNSUPPORTED, "device %d cannot map memory of device %d", device, peer_device);
+    int prev = 0;
+    if ((e = cudaGetDevice(&prev)) != cudaSuccess || (e = cudaSetDevice(device)) != cudaSuccess)
+        return cuda_fail(e, "selecting the device");
+    e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        (void)cudaGetLastError();  // clear the sticky-free error state
+        e = cudaSuccess;
+    }
+    cudaSetDevice(prev);
+    return e == cudaSuccess ? MAT_OK : cuda_fail(e, "cudaDeviceEnablePeerAccess");
+}
+
 int mat_pattern_rowset(const mat_pattern_spec *spec, int64_t S_kv, int64_t i, int64_t *out,
                        int64_t cap, int64_t *n_out) {
     if (int rc = check_spec(spec)) return rc;

@@ -35,6 +35,9 @@ struct Problem {
     void *workspace;
     size_t workspace_bytes;
     cudaStream_t stream;
+    // neighbouring sequence shards read in place (peer memory); NULL when absent
+    const void *k_prev = nullptr, *v_prev = nullptr, *k_next = nullptr, *v_next = nullptr;
+    int64_t S_prev = 0, S_next = 0;
 };
 
 // error plumbing (api.cu)

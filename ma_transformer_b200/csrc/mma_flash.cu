@@ -44,6 +44,11 @@ __device__ int g_flash_status = 0;
 
 struct FlashParams {
     int32_t Sq1, Skv1, off1;      // query rows, key rows and q_offset of one sub-sequence
+    // Keys live in a virtual coordinate line: [0, Skv1) is this GPU's own K/V, [key_lo, 0) the tail
+    // of the previous sequence shard and [Skv1, key_hi) the head of the next one, both read in
+    // place from the neighbour GPU's memory.  Without neighbours key_lo = 0 and key_hi = Skv1.
+    int32_t key_lo, key_hi;
+    int32_t prev_rows, next_rows;  // rows per sub-sequence of the neighbours' K/V tensors
     int32_t left, right;          // window taps (clamped to Skv1); chunk enumeration
     int32_t mask_left, mask_right;  // a key j is attended by row p iff -mask_left <= j-p <= mask_right
     int32_t n_tiles;              // query tiles per (batch, head)
@@ -70,10 +75,10 @@ struct Chunks {
         n = 0; start = 0; e0 = 0;
         if (KIND == MAT_WINDOW) {
             int lo = q0 + P.off1 - P.left;
-            if (lo < 0) lo = 0;
+            if (lo < P.key_lo) lo = P.key_lo;
             lo &= ~15;
             int hi = q0 + TQ - 1 + P.off1 + P.right;
-            if (hi > P.Skv1 - 1) hi = P.Skv1 - 1;
+            if (hi > P.key_hi - 1) hi = P.key_hi - 1;
             start = lo;
             n = hi >= lo ? (hi - lo) / TK + 1 : 0;
         } else {
@@ -90,6 +95,13 @@ struct Chunks {
     }
 };
 
+// 16-row views of K and V used where a stage straddles the edge of this GPU's shard: own rows,
+// the previous shard's rows and the next shard's rows (the neighbours' live in peer memory and
+// are read by ordinary tiled TMA loads).
+struct PeerMaps {
+    CUtensorMap k_own, v_own, k_prev, v_prev, k_next, v_next;
+};
+
 template <int TQ, int TK, int STAGES>
 constexpr size_t flash_smem_bytes() {
     return 1024 + (size_t)TQ * kRowBytes + (size_t)STAGES * 2 * TK * kRowBytes + 8 * (1 + 2 * STAGES);
@@ -103,7 +115,7 @@ template <typename T, int KIND, int TQ, int TK, int NP, int STAGES, bool SINGLE,
 __global__ void __launch_bounds__(flash_threads<TQ, SINGLE>(), MINB)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
-                 const FlashParams P) {
+                 const __grid_constant__ PeerMaps peer, const FlashParams P) {
     constexpr int NW = TQ / 16;  // consumer warps
     constexpr int kStageBytes = 2 * TK * kRowBytes;
     extern __shared__ uint8_t smem_raw[];
@@ -148,8 +160,25 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 uint8_t *dst = sKV + s * kStageBytes;
                 const int kb = chunks.base(P, c);
                 ptx::mbar_expect_tx(bar_full + s, kStageBytes);
-                ptx::tma_load_4d(dst, &map_k, bar_full + s, 0, hh, kb, b);
-                ptx::tma_load_4d(dst + TK * kRowBytes, &map_v, bar_full + s, 0, hh, kb, b);
+                if (kb >= 0 && kb + TK <= P.Skv1 || P.key_lo == 0 && P.key_hi == P.Skv1) {
+                    ptx::tma_load_4d(dst, &map_k, bar_full + s, 0, hh, kb, b);
+                    ptx::tma_load_4d(dst + TK * kRowBytes, &map_v, bar_full + s, 0, hh, kb, b);
+                } else {
+                    // the stage crosses into a neighbour's rows: fetch it 16 rows at a time, each
+                    // piece from the tensor that owns it
+                    for (int i = 0; i < TK / 16; ++i) {
+                        const int a = kb + 16 * i;
+                        const CUtensorMap *mk = &peer.k_own, *mv = &peer.v_own;
+                        int row = a;
+                        if (a < 0 && P.key_lo < 0) {
+                            mk = &peer.k_prev; mv = &peer.v_prev; row = P.prev_rows + a;
+                        } else if (a >= P.Skv1 && P.key_hi > P.Skv1) {
+                            mk = &peer.k_next; mv = &peer.v_next; row = a - P.Skv1;
+                        }
+                        ptx::tma_load_4d(dst + i * 16 * kRowBytes, mk, bar_full + s, 0, hh, row, b);
+                        ptx::tma_load_4d(dst + (TK + i * 16) * kRowBytes, mv, bar_full + s, 0, hh, row, b);
+                    }
+                }
             }
         }
         if (!SINGLE) return;
@@ -165,11 +194,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const uint32_t mask_span = (uint32_t)(P.mask_left + P.mask_right);
 
     // key range this warp's rows can attend
-    const int k_lo = max(p_min - P.mask_left, 0);
-    const int k_hi = min(p_max + P.mask_right, P.Skv1 - 1);
+    const int k_lo = max(p_min - P.mask_left, P.key_lo);
+    const int k_hi = min(p_max + P.mask_right, P.key_hi - 1);
     // a 16-key pair starting at key a needs no mask iff w_lo <= a <= w_hi
-    const int w_lo = max(p_max - P.mask_left, 0);
-    const int w_hi = min(p_min + P.mask_right, P.Skv1 - 1) - 15;
+    const int w_lo = max(p_max - P.mask_left, P.key_lo);
+    const int w_hi = min(p_min + P.mask_right, P.key_hi - 1) - 15;
 
     if (!ptx::mbar_wait(bar_q, 0)) {
         atomicExch(&g_flash_status, kStatusWaitTimeout);
@@ -194,9 +223,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const uint32_t k_base = ptx::smem_u32(sKV + s * kStageBytes);
         const uint32_t v_base = k_base + TK * kRowBytes;
         // pairs of this chunk that intersect [k_lo, k_hi]
-        const int first = max(0, (k_lo - kb) >> 4);
+        const int first = max(0, (k_lo - kb) >> 4);  // k_lo - kb may be negative: >> floors
         const int last = k_hi >= kb ? min(TK / 16 - 1, (k_hi - kb) >> 4) : -1;
-        const bool edge = kb < 0 || kb + TK > P.Skv1;  // chunk reaches outside the key tensor
+        const bool edge = kb < P.key_lo || kb + TK > P.key_hi;  // chunk reaches outside the key line
 
         // SINGLE: one step of exactly NP pairs (pairs past the key set are masked away, which
         // only costs work on the sequence's first and last tiles), so the step is straight-line code
@@ -244,7 +273,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                 bool ok = (uint32_t)du <= mask_span;
                                 if (edge) {
                                     const int key = a + 8 * half + 2 * tq + (e & 1);
-                                    ok = ok && key >= 0 && key < P.Skv1;
+                                    ok = ok && key >= P.key_lo && key < P.key_hi;
                                 }
                                 if (!ok) sc[2 * j + half][e] = -INFINITY;
                             }
@@ -389,6 +418,19 @@ int launch_kind(const Problem &p, const FlashParams &fp, int64_t dil, const char
     if (int rc = make_map(&mk, p.k, p.dtype, HH, p.Skv / dil, p.B, TK)) return rc;
     if (int rc = make_map(&mv, p.v, p.dtype, HH, p.Skv / dil, p.B, TK)) return rc;
     if (int rc = make_map(&mo, p.o, p.dtype, HH, p.Sq / dil, p.B, 16)) return rc;
+    PeerMaps pm;
+    if (int rc = make_map(&pm.k_own, p.k, p.dtype, HH, p.Skv / dil, p.B, 16)) return rc;
+    if (int rc = make_map(&pm.v_own, p.v, p.dtype, HH, p.Skv / dil, p.B, 16)) return rc;
+    pm.k_prev = pm.k_next = pm.k_own;
+    pm.v_prev = pm.v_next = pm.v_own;
+    if (p.k_prev) {
+        if (int rc = make_map(&pm.k_prev, p.k_prev, p.dtype, HH, p.S_prev / dil, p.B, 16)) return rc;
+        if (int rc = make_map(&pm.v_prev, p.v_prev, p.dtype, HH, p.S_prev / dil, p.B, 16)) return rc;
+    }
+    if (p.k_next) {
+        if (int rc = make_map(&pm.k_next, p.k_next, p.dtype, HH, p.S_next / dil, p.B, 16)) return rc;
+        if (int rc = make_map(&pm.v_next, p.v_next, p.dtype, HH, p.S_next / dil, p.B, 16)) return rc;
+    }
     auto kern = flash_fwd_kernel<T, KIND, TQ, TK, NP, STAGES, SINGLE, MINB>;
     constexpr size_t smem = flash_smem_bytes<TQ, TK, STAGES>();
     static std::once_flag once;
@@ -398,7 +440,7 @@ int launch_kind(const Problem &p, const FlashParams &fp, int64_t dil, const char
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(flash_fwd_kernel)");
     const dim3 grid((unsigned)HH, (unsigned)fp.n_tiles, (unsigned)p.B);
-    kern<<<grid, flash_threads<TQ, SINGLE>(), smem, p.stream>>>(mq, mk, mv, mo, fp);
+    kern<<<grid, flash_threads<TQ, SINGLE>(), smem, p.stream>>>(mq, mk, mv, mo, pm, fp);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "flash_fwd_kernel launch");
     note_kernel(name);
@@ -414,6 +456,10 @@ int launch_t(const Problem &p) {
     fp.Skv1 = (int32_t)(p.Skv / dil);
     fp.off1 = (int32_t)(p.pat.q_offset / dil);
     fp.n_tiles = (fp.Sq1 + TQ - 1) / TQ;
+    fp.prev_rows = p.k_prev ? (int32_t)(p.S_prev / dil) : 0;
+    fp.next_rows = p.k_next ? (int32_t)(p.S_next / dil) : 0;
+    fp.key_lo = -fp.prev_rows;
+    fp.key_hi = fp.Skv1 + fp.next_rows;
     fp.HH = (int32_t)(p.H * dil);
     fp.sl2 = p.scale * 1.4426950408889634f;
     fp.block = (int32_t)p.pat.block;
@@ -422,8 +468,8 @@ int launch_t(const Problem &p) {
     fp.rowptr = p.pat.rowptr;
     fp.colidx = p.pat.colidx;
     if (p.pat.kind == MAT_WINDOW) {
-        fp.left = fp.mask_left = (int32_t)std::min<int64_t>(p.pat.left, fp.Skv1);
-        fp.right = fp.mask_right = (int32_t)std::min<int64_t>(p.pat.right, fp.Skv1);
+        fp.left = fp.mask_left = (int32_t)std::min<int64_t>(p.pat.left, fp.Skv1 + fp.prev_rows);
+        fp.right = fp.mask_right = (int32_t)std::min<int64_t>(p.pat.right, fp.Skv1 + fp.next_rows);
         // one stage holds the tile's whole window when TQ + left (rounded up to 16, plus the
         // misalignment of the shard offset) + right fits TQ + 64 keys
         const int mis = fp.off1 & 15;

@@ -191,6 +191,112 @@ class SequenceShardedAttention:
                         out=out if whole else out[:, a:b])
 
 
+class PeerTensor:
+    """A contiguous [B, S, H, D] tensor that lives on a neighbouring GPU, mapped into
+    this process for kernels on this rank's device: just an address and a shape."""
+
+    def __init__(self, ptr: int, shape: Tuple[int, ...], dtype: torch.dtype):
+        self._ptr, self.shape, self.dtype = int(ptr), tuple(shape), dtype
+
+    def data_ptr(self) -> int:
+        return self._ptr
+
+    def dim(self) -> int:
+        return len(self.shape)
+
+    def is_contiguous(self) -> bool:
+        return True
+
+
+@dataclass
+class PeerShard:
+    """One rank's K/V chunk plus its neighbours' chunks mapped into this process."""
+    k: torch.Tensor
+    v: torch.Tensor
+    prev_kv: Optional[Tuple[PeerTensor, PeerTensor]]
+    next_kv: Optional[Tuple[PeerTensor, PeerTensor]]
+
+
+class PeerHaloAttention:
+    """Sequence-sharded forward WITHOUT an exchange step: each rank keeps only its own
+    chunk of K and V, and the kernel's edge tiles read the halo rows they need straight
+    out of the neighbouring GPUs' memory over NVLink (peer-mapped pointers, plain tiled
+    TMA loads issued by the same kernel that does the attention).  One launch per step,
+    no send/recv, no halo copy, nothing for the host to wait on.
+
+    ``register`` is collective: every rank passes its own contiguous [B, rows, H, 64]
+    K and V once; CUDA IPC handles go to the neighbours, which map them.  The tensors
+    must then be updated in place.  Ordering is the caller's: a rank may launch
+    ``forward`` only when its neighbours' K/V for that step are complete (a
+    ``dist.barrier()`` or a stream-ordered flag in a pipeline; static K/V need nothing).
+    """
+
+    def __init__(self, spec: PatternSpec, seq_len: int, group: Optional[dist.ProcessGroup] = None):
+        if spec.kind != WINDOW:
+            raise ValueError("sequence sharding applies to window patterns")
+        self.group, self.spec = group, spec
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if seq_len % self.world:
+            raise ValueError(f"sequence length {seq_len} is not divisible by {self.world} ranks")
+        self.rows = seq_len // self.world
+        unit = 16 * spec.dilation
+        if self.rows % unit:
+            raise ValueError(f"chunk length {self.rows} must be a multiple of 16*dilation = {unit}")
+        if max(spec.left, spec.right) * spec.dilation > self.rows:
+            raise ValueError("window reaches past the neighbouring chunk: use fewer ranks")
+        self.start = self.rank * self.rows
+        self._opened = {}   # IPC handle bytes -> mapped base address
+
+    def register(self, k_local: torch.Tensor, v_local: torch.Tensor) -> PeerShard:
+        import ctypes as C
+        from . import _native as nat
+        for t in (k_local, v_local):
+            if not (t.is_cuda and t.is_contiguous() and t.dim() == 4 and t.shape[1] == self.rows):
+                raise ValueError("expected contiguous CUDA tensors [B, rows, H, D] holding this rank's chunk")
+        my_dev = k_local.device.index
+
+        def export(t):
+            handle = C.create_string_buffer(64)
+            off = C.c_int64(0)
+            with torch.cuda.device(my_dev):
+                nat.check(nat.lib.mat_ipc_export(t.data_ptr(), handle, C.byref(off)))
+            return bytes(handle.raw), int(off.value), tuple(t.shape), t.dtype
+
+        torch.cuda.synchronize(my_dev)   # the chunk's contents are in place before anyone maps it
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, (export(k_local), export(v_local)), group=self.group)
+
+        def open_one(desc):
+            handle, off, shape, dtype = desc
+            base = self._opened.get(handle)
+            if base is None:   # one mapping per exported allocation and process
+                out = C.c_void_p()
+                nat.check(nat.lib.mat_ipc_open(handle, my_dev, C.byref(out)))
+                base = self._opened[handle] = int(out.value)
+            return PeerTensor(base + off, shape, dtype)
+
+        def open_neighbour(r):
+            return tuple(open_one(d) for d in everyone[r])
+
+        prev_kv = open_neighbour(self.rank - 1) if self.rank > 0 and self.spec.left else None
+        next_kv = open_neighbour(self.rank + 1) if self.rank < self.world - 1 and self.spec.right else None
+        dist.barrier(group=self.group)   # every mapping exists before anyone may free or reuse memory
+        return PeerShard(k_local, v_local, prev_kv, next_kv)
+
+    def close(self) -> None:
+        """Unmaps every neighbour allocation this object opened (collective use not required)."""
+        from . import _native as nat
+        dev = torch.cuda.current_device()
+        for base in self._opened.values():
+            nat.check(nat.lib.mat_ipc_close(base, dev))
+        self._opened.clear()
+
+    def forward(self, q: torch.Tensor, shard: PeerShard, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        from . import sparse_attention_cuda
+        return sparse_attention_cuda.forward_sharded(q, shard.k, shard.v, self.spec, shard.prev_kv,
+                                                     shard.next_kv, out=out)
+
+
 def gather_sequence(out_local: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """All-gather of the per-rank outputs along the sequence axis (checking aid)."""
     world = dist.get_world_size(group)

@@ -85,6 +85,41 @@ def forward_pattern(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
     return out
 
 
+def forward_sharded(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, spec: PatternSpec,
+                    prev_kv=None, next_kv=None, scale: Optional[float] = None,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Forward of one sequence shard [B, S, H, 64]; ``prev_kv`` / ``next_kv`` are
+    ``(key, value)`` pairs of the neighbouring shards, usually tensors that live on
+    another GPU and are mapped into this process (see ``sharded.PeerHaloAttention``).
+    The edge tiles read the halo rows from them inside the kernel."""
+    _check_inputs(query, key, value)
+    if not (query.shape == key.shape == value.shape):
+        raise RuntimeError("Q,K,V must have same shape")
+    B, S, H, D = query.shape
+    if out is None:
+        out = torch.empty_like(query)
+
+    def side(kv):
+        if kv is None:
+            return None, None, 0
+        k, v = kv
+        if k.dtype != query.dtype or v.dtype != query.dtype or not (k.is_contiguous() and v.is_contiguous()):
+            raise RuntimeError("neighbour tensors must be contiguous and of the query's dtype")
+        if k.shape != v.shape or k.dim() != 4 or k.shape[0] != B or tuple(k.shape[2:]) != (H, D):
+            raise RuntimeError("neighbour tensors must be [B, S_neighbour, H, D]")
+        return k.data_ptr(), v.data_ptr(), k.shape[1]
+
+    kp, vp, sp = side(prev_kv)
+    kn, vn, sn = side(next_kv)
+    with torch.cuda.device(query.device):
+        s = spec.device_struct(query.device)
+        stream = torch.cuda.current_stream(query.device).cuda_stream
+        nat.check(nat.lib.mat_sparse_attn_fwd_sharded(
+            query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(), kp, vp, sp, kn, vn, sn,
+            B, S, H, D, _DTYPES[query.dtype], C.byref(s), float(scale) if scale else 0.0, C.c_void_p(stream)))
+    return out
+
+
 def forward(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
             window_size: int = 64) -> torch.Tensor:
     """Sparse attention forward (CUDA): keys [i-window_size, i+window_size].

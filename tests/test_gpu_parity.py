@@ -145,6 +145,41 @@ def test_shard_with_halo_equals_full_run(spec, dtype):
     check_close(full, oracle_out(q, k, v, spec), dtype)
 
 
+@pytest.mark.parametrize("spec", [PatternSpec.causal_window(64), PatternSpec.causal_window(33), PatternSpec.sliding_window(20),
+                                  PatternSpec(left=10, right=40), PatternSpec.causal_window(16, dilation=2),
+                                  PatternSpec.causal_window(200), PatternSpec.sliding_window(100)],
+                         ids=["causal64", "causal33", "pm20", "l10r40", "dil2", "causal200", "pm100"])
+@pytest.mark.parametrize("B", [1, 2])
+def test_neighbour_shards_read_in_place(spec, B):
+    """The sharded entry point: every chunk is its own tensor and the edge tiles read
+    their halo rows from the neighbouring chunks' tensors (here on the same GPU; across
+    GPUs the pointers are peer-mapped).  Must equal the unsharded run."""
+    S, P = 1024, 4
+    q, k, v = seeded_qkv(22, B, S, 2, 64, torch.bfloat16)
+    want = oracle_out(q, k, v, spec)
+    chunk = S // P
+    parts = [tuple(t[:, r * chunk:(r + 1) * chunk].contiguous().to(DEV) for t in (q, k, v)) for r in range(P)]
+    for r in range(P):
+        qr, kr, vr = parts[r]
+        prev_kv = parts[r - 1][1:] if r > 0 else None
+        next_kv = parts[r + 1][1:] if r < P - 1 and spec.right else None
+        out = ext.forward_sharded(qr, kr, vr, spec, prev_kv, next_kv)
+        torch.cuda.synchronize()
+        assert nat.last_kernel() == "mma_window"
+        check_close(out, want[:, r * chunk:(r + 1) * chunk], torch.bfloat16)
+
+
+def test_neighbour_shards_argument_checks():
+    q = torch.zeros(1, 128, 2, 64, dtype=torch.bfloat16, device=DEV)
+    short = torch.zeros(1, 32, 2, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError, match="previous shard"):
+        ext.forward_sharded(q, q, q, PatternSpec.causal_window(64), (short, short))
+    with pytest.raises(RuntimeError, match="window patterns"):
+        ext.forward_sharded(q, q, q, PatternSpec.longformer(4, 4, [0]), (q, q))
+    with pytest.raises(RuntimeError):
+        ext.forward_sharded(q.float(), q.float(), q.float(), PatternSpec.causal_window(64), (q.float(), q.float()))
+
+
 # ---- block-sparse -----------------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
