@@ -59,7 +59,18 @@ struct FlashParams {
     int64_t n_qblocks;
     const int32_t *rowptr;
     const int32_t *colidx;
+    // Longformer: sorted global positions.  Every row attends them besides its window
+    // (MAT_LONGFORMER); the rows AT those positions attend every key (kGlobalRows pass).
+    int32_t n_global;
+    const int64_t *gidx;
+    // kGlobalRows: the key axis is cut into n_splits ranges of split_len keys; each CTA leaves
+    // (max, sum, unnormalised output) per row in `partial`, merged by merge_global_rows_kernel
+    int32_t split_len, n_splits, ng_pad;
+    float *partial;  // [B, HH, n_splits, ng_pad, kPartialStride]
 };
+
+constexpr int kGlobalRows = 3;       // kernel kind beside the MAT_* pattern kinds
+constexpr int kPartialStride = 66;   // floats per row: max, sum, 64 outputs
 
 __device__ __forceinline__ uint32_t swz(uint32_t base, int row, int chunk16) {
     return base + row * kRowBytes + ((chunk16 ^ (row & 7)) << 4);
@@ -69,28 +80,34 @@ __device__ __forceinline__ uint32_t swz(uint32_t base, int row, int chunk16) {
 template <int KIND, int TQ, int TK>
 struct Chunks {
     int n;
-    int start;  // window: first key of chunk 0
+    int n_seq;  // chunks that are contiguous key ranges (the rest gather global keys)
+    int start;  // first key of chunk 0 (window kinds, global-row pass)
     int e0;     // block: first CSR entry of the tile's layout row
-    __device__ __forceinline__ Chunks(const FlashParams &P, int q0) {
-        n = 0; start = 0; e0 = 0;
-        if (KIND == MAT_WINDOW) {
+    // key_lo / key_hi: the keys this CTA may touch
+    __device__ __forceinline__ Chunks(const FlashParams &P, int q0, int key_lo, int key_hi) {
+        n = 0; n_seq = 0; start = 0; e0 = 0;
+        if (KIND == MAT_WINDOW || KIND == MAT_LONGFORMER) {
             int lo = q0 + P.off1 - P.left;
-            if (lo < P.key_lo) lo = P.key_lo;
+            if (lo < key_lo) lo = key_lo;
             lo &= ~15;
             int hi = q0 + TQ - 1 + P.off1 + P.right;
-            if (hi > P.key_hi - 1) hi = P.key_hi - 1;
+            if (hi > key_hi - 1) hi = key_hi - 1;
             start = lo;
-            n = hi >= lo ? (hi - lo) / TK + 1 : 0;
+            n_seq = hi >= lo ? (hi - lo) / TK + 1 : 0;
+            n = n_seq + (KIND == MAT_LONGFORMER ? (P.n_global + TK - 1) / TK : 0);
+        } else if (KIND == kGlobalRows) {
+            start = key_lo;
+            n = n_seq = key_hi > key_lo ? (key_hi - key_lo + TK - 1) / TK : 0;
         } else {
             const uint32_t r = (uint32_t)(q0 + P.off1) / (uint32_t)P.block;
             if ((int64_t)r < P.n_qblocks) {
                 e0 = P.rowptr[r];
-                n = (P.rowptr[r + 1] - e0) * P.per_blk;
+                n = n_seq = (P.rowptr[r + 1] - e0) * P.per_blk;
             }
         }
     }
     __device__ __forceinline__ int base(const FlashParams &P, int c) const {
-        if (KIND == MAT_WINDOW) return start + c * TK;
+        if (KIND != MAT_BLOCK) return start + c * TK;
         return P.colidx[e0 + c / P.per_blk] * P.block + (c % P.per_blk) * TK;
     }
 };
@@ -98,14 +115,19 @@ struct Chunks {
 // 16-row views of K and V used where a stage straddles the edge of this GPU's shard: own rows,
 // the previous shard's rows and the next shard's rows (the neighbours' live in peer memory and
 // are read by ordinary tiled TMA loads).
+// q_row / k_row / v_row are one-row views used to gather the rows at the global positions.
 struct PeerMaps {
-    CUtensorMap k_own, v_own, k_prev, v_prev, k_next, v_next;
+    CUtensorMap k_own, v_own, k_prev, v_prev, k_next, v_next, q_row, k_row, v_row;
 };
 
 template <int TQ, int TK, int STAGES>
 constexpr size_t flash_smem_bytes() {
-    return 1024 + (size_t)TQ * kRowBytes + (size_t)STAGES * 2 * TK * kRowBytes + 8 * (1 + 2 * STAGES);
+    // Q tile, K/V stages, barriers, then per stage the global positions of a gathered chunk
+    return 1024 + (size_t)TQ * kRowBytes + (size_t)STAGES * 2 * TK * kRowBytes + 8 * (1 + 2 * STAGES) +
+           8 + (size_t)STAGES * TK * 4;
 }
+
+constexpr int kNoKey = INT32_MIN;  // marks an unused slot of a gathered chunk
 
 // SINGLE kernels issue all their loads up front, so they carry no producer warp: lane 0 of
 // warp 0 issues the copies and then computes like every other lane.
@@ -125,6 +147,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     uint64_t *bar_q = (uint64_t *)(sKV + STAGES * kStageBytes);
     uint64_t *bar_full = bar_q + 1;
     uint64_t *bar_empty = bar_full + STAGES;
+    int32_t *sG = (int32_t *)(bar_empty + STAGES + 1);  // [STAGES][TK] positions of gathered keys
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -133,7 +156,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     // 128-byte rows they fetch from the same token range share DRAM pages
     const int hh = blockIdx.x;
     const int b = blockIdx.z;
-    const int q0 = blockIdx.y * TQ;
+    // kGlobalRows: blockIdx.y = (tile of the global-position list) * n_splits + key split
+    const int split = KIND == kGlobalRows ? blockIdx.y % P.n_splits : 0;
+    const int q0 = (KIND == kGlobalRows ? blockIdx.y / P.n_splits : blockIdx.y) * TQ;
+    const int key_lo = KIND == kGlobalRows ? split * P.split_len : P.key_lo;
+    const int key_hi = KIND == kGlobalRows ? min(key_lo + P.split_len, P.Skv1) : P.key_hi;
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(bar_q, 1);
@@ -145,12 +172,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     __syncthreads();
 
-    const Chunks<KIND, TQ, TK> chunks(P, q0);
+    const Chunks<KIND, TQ, TK> chunks(P, q0, key_lo, key_hi);
 
     if (SINGLE ? warp == 0 : warp == NW) {  // ---- producer: one lane feeds the ring ----
         if (lane == 0) {
             ptx::mbar_expect_tx(bar_q, TQ * kRowBytes);
-            ptx::tma_load_4d(sQ, &map_q, bar_q, 0, hh, q0, b);
+            if (KIND == kGlobalRows) {
+                // the query tile is gathered: row r of the tile is the query at global position
+                // gidx[q0 + r]; slots past the list read out of bounds, i.e. zeros
+                for (int r = 0; r < TQ; ++r) {
+                    const int e = q0 + r;
+                    const int row = e < P.n_global ? (int)P.gidx[e] : P.Sq1;
+                    ptx::tma_load_4d(sQ + r * kRowBytes, &peer.q_row, bar_q, 0, hh, row, b);
+                }
+            } else {
+                ptx::tma_load_4d(sQ, &map_q, bar_q, 0, hh, q0, b);
+            }
             for (int c = 0; c < chunks.n; ++c) {
                 const int s = c % STAGES, use = c / STAGES;
                 if (use > 0 && !ptx::mbar_wait(bar_empty + s, (use - 1) & 1)) {
@@ -158,6 +195,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     break;
                 }
                 uint8_t *dst = sKV + s * kStageBytes;
+                if (KIND == MAT_LONGFORMER && c >= chunks.n_seq) {
+                    // gathered chunk: the K/V rows at the next TK global positions, whole 16-key
+                    // pairs only (slots past the list read out of bounds: zeros, so that a zero
+                    // weight never meets a non-finite value)
+                    const int e0 = (c - chunks.n_seq) * TK;
+                    const int n_in = min(TK, P.n_global - e0);
+                    const int rows = (n_in + 15) & ~15;
+                    for (int i = 0; i < rows; ++i) sG[s * TK + i] = i < n_in ? (int)P.gidx[e0 + i] : kNoKey;
+                    ptx::mbar_expect_tx(bar_full + s, rows * 2 * kRowBytes);
+                    for (int i = 0; i < rows; ++i) {
+                        const int row = i < n_in ? sG[s * TK + i] : P.Skv1;
+                        ptx::tma_load_4d(dst + i * kRowBytes, &peer.k_row, bar_full + s, 0, hh, row, b);
+                        ptx::tma_load_4d(dst + (TK + i) * kRowBytes, &peer.v_row, bar_full + s, 0, hh, row, b);
+                    }
+                    continue;
+                }
                 const int kb = chunks.base(P, c);
                 ptx::mbar_expect_tx(bar_full + s, kStageBytes);
                 if (kb >= 0 && kb + TK <= P.Skv1 || P.key_lo == 0 && P.key_hi == P.Skv1) {
@@ -189,16 +242,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int g = lane >> 2;   // row within the 8-row group
     const int tq = lane & 3;   // column pair within an 8-wide tile
     const int row0 = warp * 16;                 // first row of this warp inside the tile
-    const int p_min = q0 + row0 + P.off1;       // key-coordinate position of that row
+    // key-coordinate position of that row (the global-row pass has no band: every key counts)
+    const int p_min = KIND == kGlobalRows ? 0 : q0 + row0 + P.off1;
     const int p_max = p_min + 15;
     const uint32_t mask_span = (uint32_t)(P.mask_left + P.mask_right);
 
     // key range this warp's rows can attend
-    const int k_lo = max(p_min - P.mask_left, P.key_lo);
-    const int k_hi = min(p_max + P.mask_right, P.key_hi - 1);
+    const int k_lo = max(p_min - P.mask_left, key_lo);
+    const int k_hi = min(p_max + P.mask_right, key_hi - 1);
     // a 16-key pair starting at key a needs no mask iff w_lo <= a <= w_hi
-    const int w_lo = max(p_max - P.mask_left, P.key_lo);
-    const int w_hi = min(p_min + P.mask_right, P.key_hi - 1) - 15;
+    const int w_lo = max(p_max - P.mask_left, key_lo);
+    const int w_hi = min(p_min + P.mask_right, key_hi - 1) - 15;
 
     if (!ptx::mbar_wait(bar_q, 0)) {
         atomicExch(&g_flash_status, kStatusWaitTimeout);
@@ -219,13 +273,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             atomicExch(&g_flash_status, kStatusWaitTimeout);
             return;
         }
+        const bool gathered = KIND == MAT_LONGFORMER && c >= chunks.n_seq;  // keys at global positions
         const int kb = chunks.base(P, c);
         const uint32_t k_base = ptx::smem_u32(sKV + s * kStageBytes);
         const uint32_t v_base = k_base + TK * kRowBytes;
         // pairs of this chunk that intersect [k_lo, k_hi]
-        const int first = max(0, (k_lo - kb) >> 4);  // k_lo - kb may be negative: >> floors
-        const int last = k_hi >= kb ? min(TK / 16 - 1, (k_hi - kb) >> 4) : -1;
-        const bool edge = kb < P.key_lo || kb + TK > P.key_hi;  // chunk reaches outside the key line
+        int first = max(0, (k_lo - kb) >> 4);  // k_lo - kb may be negative: >> floors
+        int last = k_hi >= kb ? min(TK / 16 - 1, (k_hi - kb) >> 4) : -1;
+        if (gathered) {
+            first = 0;
+            last = (min(TK, P.n_global - (c - chunks.n_seq) * TK) - 1) >> 4;
+        }
+        const bool edge = kb < key_lo || kb + TK > key_hi;  // chunk reaches outside the key line
 
         // SINGLE: one step of exactly NP pairs (pairs past the key set are masked away, which
         // only costs work on the sequence's first and last tiles), so the step is straight-line code
@@ -264,7 +323,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             for (int j = 0; j < NP; ++j) {
                 if (j < npairs) {
                     const int a = kb + 16 * (pp + j);
-                    if (a < w_lo || a > w_hi) {
+                    if (KIND == MAT_LONGFORMER && gathered) {
+                        // a gathered key counts unless the slot is unused or the row's window
+                        // already holds that position
+#pragma unroll
+                        for (int half = 0; half < 2; ++half) {
+                            const int2 gp = *reinterpret_cast<const int2 *>(
+                                sG + s * TK + 16 * (pp + j) + 8 * half + 2 * tq);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int gk = (e & 1) ? gp.y : gp.x;
+                                const int p = p_min + g + 8 * (e >> 1);
+                                const bool in_window =
+                                    (uint32_t)gk - (uint32_t)p + (uint32_t)P.mask_left <= mask_span;
+                                if (gk == kNoKey || in_window) sc[2 * j + half][e] = -INFINITY;
+                            }
+                        }
+                    } else if (a < w_lo || a > w_hi) {
 #pragma unroll
                         for (int half = 0; half < 2; ++half)
 #pragma unroll
@@ -273,7 +348,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                 bool ok = (uint32_t)du <= mask_span;
                                 if (edge) {
                                     const int key = a + 8 * half + 2 * tq + (e & 1);
-                                    ok = ok && key >= P.key_lo && key < P.key_hi;
+                                    ok = ok && key >= key_lo && key < key_hi;
                                 }
                                 if (!ok) sc[2 * j + half][e] = -INFINITY;
                             }
@@ -349,6 +424,26 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         if (lane == 0) ptx::mbar_arrive(bar_empty + s);
     }
 
+    if (KIND == kGlobalRows) {
+        // ---- epilogue of the global-row pass: leave (max, sum, unnormalised output) per row ----
+        float *part = P.partial +
+                      ((((int64_t)b * P.HH + hh) * P.n_splits + split) * P.ng_pad + q0 + row0) * kPartialStride;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = g + 8 * i;
+            if (q0 + row0 + r >= P.n_global) continue;
+            float *pr = part + r * kPartialStride;
+            if (tq == 0) {
+                pr[0] = m_run[i];
+                pr[1] = lsum[2 * i];
+            }
+#pragma unroll
+            for (int n = 0; n < 8; ++n)
+                *reinterpret_cast<float2 *>(pr + 2 + 8 * n + 2 * tq) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+        }
+        return;
+    }
+
     // ---- epilogue: normalise, stage the warp's 16 rows in its own Q rows, bulk store ----
     float l_run[2];
 #pragma unroll
@@ -375,6 +470,30 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             ptx::tma_store_wait_read();
         }
     }
+}
+
+// Combines the per-split partials of the global-row pass and writes the rows at the global
+// positions: out = sum_s w_s * acc_s / sum_s w_s * l_s with w_s = exp2((m_s - max_s m_s) * sl2).
+// grid = (global position, head, batch), 64 threads = one per output column.
+template <typename T>
+__global__ void __launch_bounds__(64)
+merge_global_rows_kernel(const float *__restrict__ partial, T *__restrict__ out, const int64_t *__restrict__ gidx,
+                         int n_splits, int ng_pad, int HH, int64_t Sq1, float sl2) {
+    const int e = blockIdx.x, hh = blockIdx.y, b = blockIdx.z, d = threadIdx.x;
+    const float *base = partial + (((int64_t)b * HH + hh) * n_splits * ng_pad + e) * kPartialStride;
+    const int64_t split_stride = (int64_t)ng_pad * kPartialStride;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, base[s * split_stride]);
+    float l = 0.f, acc = 0.f;
+    if (m != -INFINITY)
+        for (int s = 0; s < n_splits; ++s) {
+            const float *pr = base + s * split_stride;
+            const float w = ptx::ex2((pr[0] - m) * sl2);
+            l = fmaf(w, pr[1], l);
+            acc = fmaf(w, pr[2 + d], acc);
+        }
+    const int64_t row = gidx[e];
+    out[((b * Sq1 + row) * HH + hh) * 64 + d] = Elem<T>::from_f(l > 0.f ? acc / l : 0.f);
 }
 
 // ---- host side ------------------------------------------------------------
@@ -411,7 +530,7 @@ int make_map(CUtensorMap *m, const void *base, int dtype, int64_t HH, int64_t S1
 }
 
 template <typename T, int KIND, int TQ, int TK, int NP, int STAGES, bool SINGLE, int MINB>
-int launch_kind(const Problem &p, const FlashParams &fp, int64_t dil, const char *name) {
+int launch_kind(const Problem &p, const FlashParams &fp, int64_t dil, const char *name, int64_t grid_y = -1) {
     CUtensorMap mq, mk, mv, mo;
     const int64_t HH = fp.HH;
     if (int rc = make_map(&mq, p.q, p.dtype, HH, p.Sq / dil, p.B, TQ)) return rc;
@@ -431,6 +550,13 @@ int launch_kind(const Problem &p, const FlashParams &fp, int64_t dil, const char
         if (int rc = make_map(&pm.k_next, p.k_next, p.dtype, HH, p.S_next / dil, p.B, 16)) return rc;
         if (int rc = make_map(&pm.v_next, p.v_next, p.dtype, HH, p.S_next / dil, p.B, 16)) return rc;
     }
+    pm.q_row = pm.k_row = pm.k_own;
+    pm.v_row = pm.v_own;
+    if (KIND == MAT_LONGFORMER || KIND == kGlobalRows) {
+        if (int rc = make_map(&pm.q_row, p.q, p.dtype, HH, p.Sq / dil, p.B, 1)) return rc;
+        if (int rc = make_map(&pm.k_row, p.k, p.dtype, HH, p.Skv / dil, p.B, 1)) return rc;
+        if (int rc = make_map(&pm.v_row, p.v, p.dtype, HH, p.Skv / dil, p.B, 1)) return rc;
+    }
     auto kern = flash_fwd_kernel<T, KIND, TQ, TK, NP, STAGES, SINGLE, MINB>;
     constexpr size_t smem = flash_smem_bytes<TQ, TK, STAGES>();
     static std::once_flag once;
@@ -439,12 +565,33 @@ int launch_kind(const Problem &p, const FlashParams &fp, int64_t dil, const char
         attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(flash_fwd_kernel)");
-    const dim3 grid((unsigned)HH, (unsigned)fp.n_tiles, (unsigned)p.B);
+    const dim3 grid((unsigned)HH, (unsigned)(grid_y >= 0 ? grid_y : fp.n_tiles), (unsigned)p.B);
     kern<<<grid, flash_threads<TQ, SINGLE>(), smem, p.stream>>>(mq, mk, mv, mo, pm, fp);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "flash_fwd_kernel launch");
     note_kernel(name);
     return MAT_OK;
+}
+
+// How the global-row pass cuts the key axis: enough CTAs to fill the GPU a few times over,
+// splits a multiple of the 128-key stage, at least 512 keys each.
+struct GlobalRowPlan {
+    int tiles;      // 64-row tiles of the global-position list
+    int n_splits, split_len;
+    size_t bytes;   // partial buffer
+};
+
+GlobalRowPlan plan_global_rows(const Problem &p) {
+    GlobalRowPlan g;
+    g.tiles = (int)((p.pat.n_global + 63) / 64);
+    const int64_t units = std::max<int64_t>(1, p.B * p.H * g.tiles);
+    int64_t want = std::max<int64_t>(1, 2048 / units);
+    int64_t len = (p.Skv + want - 1) / want;
+    len = std::max<int64_t>(512, (len + 127) / 128 * 128);
+    g.split_len = (int)len;
+    g.n_splits = (int)((p.Skv + len - 1) / len);
+    g.bytes = (size_t)p.B * p.H * g.n_splits * g.tiles * 64 * kPartialStride * sizeof(float);
+    return g;
 }
 
 template <typename T>
@@ -467,6 +614,10 @@ int launch_t(const Problem &p) {
     fp.n_qblocks = p.pat.n_qblocks;
     fp.rowptr = p.pat.rowptr;
     fp.colidx = p.pat.colidx;
+    fp.n_global = 0;
+    fp.gidx = nullptr;
+    fp.split_len = fp.n_splits = fp.ng_pad = 0;
+    fp.partial = nullptr;
     if (p.pat.kind == MAT_WINDOW) {
         fp.left = fp.mask_left = (int32_t)std::min<int64_t>(p.pat.left, fp.Skv1 + fp.prev_rows);
         fp.right = fp.mask_right = (int32_t)std::min<int64_t>(p.pat.right, fp.Skv1 + fp.next_rows);
@@ -481,6 +632,32 @@ int launch_t(const Problem &p) {
         if (fp.left + slack + fp.right <= 64 && pairs <= 5)
             return launch_kind<T, MAT_WINDOW, TQ, TQ + 64, 5, 1, true, 5>(p, fp, dil, "mma_window");
         return launch_kind<T, MAT_WINDOW, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_window");
+    }
+    if (p.pat.kind == MAT_LONGFORMER) {
+        fp.left = fp.mask_left = (int32_t)std::min<int64_t>(p.pat.left, fp.Skv1);
+        fp.right = fp.mask_right = (int32_t)std::min<int64_t>(p.pat.right, fp.Skv1);
+        fp.n_global = (int32_t)p.pat.n_global;
+        fp.gidx = p.pat.gidx;
+        // pass 1: every row over its window plus the keys at the global positions
+        if (int rc = launch_kind<T, MAT_LONGFORMER, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_longformer")) return rc;
+        if (fp.n_global == 0) return MAT_OK;
+        // pass 2: the rows AT the global positions over every key, split along the key axis
+        const GlobalRowPlan g = plan_global_rows(p);
+        fp.left = fp.right = 0;
+        fp.mask_left = fp.mask_right = kBig;
+        fp.n_splits = g.n_splits;
+        fp.split_len = g.split_len;
+        fp.ng_pad = g.tiles * 64;
+        fp.partial = (float *)p.workspace;
+        if (int rc = launch_kind<T, kGlobalRows, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_longformer",
+                                                                         (int64_t)g.tiles * g.n_splits))
+            return rc;
+        // pass 3: merge the splits and overwrite those rows of the output
+        const dim3 grid((unsigned)fp.n_global, (unsigned)fp.HH, (unsigned)p.B);
+        merge_global_rows_kernel<T><<<grid, 64, 0, p.stream>>>(fp.partial, (T *)p.o, fp.gidx, fp.n_splits,
+                                                              fp.ng_pad, fp.HH, fp.Sq1, fp.sl2);
+        cudaError_t e = cudaGetLastError();
+        return e == cudaSuccess ? MAT_OK : cuda_fail(e, "merge_global_rows_kernel launch");
     }
     fp.left = fp.right = 0;
     fp.mask_left = kBig;
@@ -510,10 +687,18 @@ bool mma_flash_supports(const Problem &p) {
         // query tiles of 64 rows must not straddle a layout row
         return p.pat.block % 64 == 0 && p.pat.q_offset % 64 == 0 && p.pat.block < (1 << 24);
     }
+    if (p.pat.kind == MAT_LONGFORMER) {
+        // whole sequences only (the global rows need every key); the list of global positions
+        // must fit the grid of the merge kernel
+        return p.pat.q_offset == 0 && p.Sq == p.Skv && p.pat.n_global <= 65535 * 64 && p.H <= 65535;
+    }
     return false;
 }
 
-size_t mma_flash_workspace_bytes(const Problem &) { return 0; }
+size_t mma_flash_workspace_bytes(const Problem &p) {
+    if (p.pat.kind != MAT_LONGFORMER || p.pat.n_global == 0) return 0;
+    return plan_global_rows(p).bytes;
+}
 
 int launch_mma_flash(const Problem &p) {
     return p.dtype == MAT_BF16 ? launch_t<__nv_bfloat16>(p) : launch_t<__half>(p);

@@ -226,6 +226,24 @@ def test_longformer_vs_oracle(dtype):
         check_close(run(spec, q, k, v), oracle_out(q, k, v, spec), dtype)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_longformer_cfg4_shape_reduced_length(dtype):
+    # cfg-4's window (+-64), 32 seeded global positions, 12 heads, at a length the oracle finishes quickly
+    g = torch.Generator().manual_seed(4)
+    S = 4096
+    glob = torch.randperm(S, generator=g)[:32].sort().values.numpy()
+    spec = PatternSpec.longformer(64, 64, glob)
+    q, k, v = seeded_qkv(43, 2, S, 12, 64, dtype)
+    got = run(spec, q, k, v)
+    assert nat.last_kernel() == "mma_longformer"
+    check_close(got, oracle_out(q, k, v, spec), dtype)
+    # many global positions: several gathered chunks and several tiles of global rows
+    glob = torch.randperm(1500, generator=g)[:200].sort().values.numpy()
+    spec = PatternSpec.longformer(10, 3, glob)
+    q, k, v = seeded_qkv(44, 1, 1500, 2, 64, dtype)
+    check_close(run(spec, q, k, v), oracle_out(q, k, v, spec), dtype)
+
+
 # ---- index sets, recovered from the kernels themselves -----------------------------------------
 
 def _attended_sets(spec, S, dtype, D):
