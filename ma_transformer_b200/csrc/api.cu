@@ -180,8 +180,8 @@ int mat_sparse_attn_fwd(const void *q, const void *k, const void *v, void *o, in
 size_t mat_sparse_attn_workspace_bytes(int64_t B, int64_t S_q, int64_t S_kv, int64_t H, int64_t D,
                                        int dtype, const mat_pattern_spec *spec) {
     Problem p;
-    static const char dummy = 0;
-    if (make_problem(p, &dummy, &dummy, &dummy, (void *)&dummy, B, S_q, S_kv, H, D, dtype, spec,
+    alignas(256) static char dummy[256];  // stands in for the tensors: kernel selection looks at alignment
+    if (make_problem(p, dummy, dummy, dummy, dummy, B, S_q, S_kv, H, D, dtype, spec,
                      0.f, nullptr, 0, nullptr))
         return 0;
     return mma_flash_supports(p) ? mma_flash_workspace_bytes(p) : 0;
