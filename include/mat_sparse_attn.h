@@ -128,6 +128,35 @@ int mat_sparse_attn_fwd_sharded(const void *q, const void *k, const void *v, voi
                                 const mat_pattern_spec *spec, float scale, void *stream);
 
 /*
+ * Longformer forward that allocates nothing and takes no workspace.  It has no
+ * counterpart in the reference.  It is for hosts that may not obtain device
+ * memory while they run: a server that gave all of HBM to its own arena at
+ * start-up has nothing left to lend as a workspace, and a latency-critical loop
+ * cannot afford the device-wide synchronisation an allocation implies.  The
+ * per-split partial results of the global-row pass (the only scratch the forward
+ * uses) go to an array built into the library, 4 MiB per GPU, held from the
+ * moment the library is loaded until the process ends.
+ *   - MAT_LONGFORMER patterns, 16-bit dtypes, D = 64, whole sequences
+ *     (q, k, v, o all [B, S, H, D]; q_offset = 0).  The caller still owns inputs
+ *     and output.  Same results as mat_sparse_attn_fwd up to summation order.
+ *   - Limit: B * H * (global positions rounded up to 64) * 264 bytes must fit in
+ *     4 MiB; larger problems get MAT_ERR_UNSUPPORTED and should use
+ *     mat_sparse_attn_fwd with a caller workspace.  Within the limit the key axis
+ *     is cut into as many splits as fit, so very large B*H runs with less
+ *     parallelism in the global-row pass than the workspace version.
+ *   - The first call on each device looks up the array's device address (once);
+ *     make that call outside any stream capture.  No cudaMalloc, cudaFree or
+ *     other allocating routine is called, on the first call or later.
+ *   - All calls on a device share the one array and nothing in it needs
+ *     clearing (every slot that is read is written first by the same call), but
+ *     two calls that overlap on the GPU, e.g. on different streams, race on it:
+ *     keep them on one stream or order them with events.
+ */
+int mat_sparse_attn_fwd_longformer_noalloc(const void *q, const void *k, const void *v, void *o,
+                                           int64_t B, int64_t S, int64_t H, int64_t D, int dtype,
+                                           const mat_pattern_spec *spec, float scale, void *stream);
+
+/*
  * Lets kernels running on `device` read memory that lives on `peer_device`
  * (cudaDeviceEnablePeerAccess; already-enabled is not an error).  Call once per
  * neighbour before mat_sparse_attn_fwd_sharded.  No counterpart in the reference.

@@ -20,7 +20,7 @@ EXPORTS = (
     "mat_sparse_attn_fwd", "mat_sparse_attn_workspace_bytes", "mat_sparse_attn_fwd_window",
     "mat_sparse_attn_fwd_host", "mat_sparse_attn_host_staging_bytes", "mat_sparse_attn_fwd_sharded",
     "mat_pattern_rowset", "mat_pattern_nnz", "mat_enable_peer_access",
-    "mat_ipc_export", "mat_ipc_open", "mat_ipc_close",
+    "mat_ipc_export", "mat_ipc_open", "mat_ipc_close", "mat_sparse_attn_fwd_longformer_noalloc",
 )
 
 
@@ -64,6 +64,9 @@ def _load() -> C.CDLL:
     lib.mat_sparse_attn_fwd_sharded.restype = C.c_int
     lib.mat_sparse_attn_fwd_sharded.argtypes = [vp, vp, vp, vp, vp, vp, i64, vp, vp, i64, i64, i64, i64, i64,
                                                 C.c_int, spec_p, C.c_float, vp]
+    lib.mat_sparse_attn_fwd_longformer_noalloc.restype = C.c_int
+    lib.mat_sparse_attn_fwd_longformer_noalloc.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, C.c_int, spec_p,
+                                                           C.c_float, vp]
     lib.mat_enable_peer_access.restype = C.c_int
     lib.mat_enable_peer_access.argtypes = [C.c_int, C.c_int]
     lib.mat_ipc_export.restype = C.c_int

@@ -704,6 +704,107 @@ int launch_mma_flash(const Problem &p) {
     return p.dtype == MAT_BF16 ? launch_t<__nv_bfloat16>(p) : launch_t<__half>(p);
 }
 
+// ---- Longformer forward for callers that cannot allocate device memory ----------------------
+//
+// Some hosts of this library may never call cudaMalloc once they are running: an inference
+// server that hands all of HBM to its own arena at start-up, or a latency-critical loop where
+// the implicit device synchronisation of an allocation is not acceptable.  They cannot provide
+// the workspace mat_sparse_attn_fwd asks for either, if every byte they own is already spoken
+// for.  For them the per-split partials of the global-row pass live in this fixed array, which
+// every GPU that loads the library holds until the process exits.
+constexpr size_t kStaticScratchBytes = (size_t)4 << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+
+// In host code g_static_scratch is only a stand-in for the symbol, not a device address: the
+// address on the current device comes from cudaGetSymbolAddress, looked up once per device.
+int static_scratch_on_current_device(float **out) {
+    static std::mutex mu;
+    static void *ptrs[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(MAT_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptrs[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+        ptrs[dev] = p;
+    }
+    *out = (float *)ptrs[dev];
+    return MAT_OK;
+}
+
+// Same three passes as the MAT_LONGFORMER branch of launch_t, with the key axis cut into as
+// many splits as the fixed array can hold partials for.
+template <typename T>
+int launch_longformer_static(const Problem &p, float *scratch) {
+    constexpr int TQ = 64;
+    FlashParams fp;
+    fp.Sq1 = (int32_t)p.Sq;
+    fp.Skv1 = (int32_t)p.Skv;
+    fp.off1 = 0;
+    fp.n_tiles = (fp.Sq1 + TQ - 1) / TQ;
+    fp.prev_rows = fp.next_rows = 0;
+    fp.key_lo = 0;
+    fp.key_hi = fp.Skv1;
+    fp.HH = (int32_t)p.H;
+    fp.sl2 = p.scale * 1.4426950408889634f;
+    fp.block = fp.per_blk = 0;
+    fp.n_qblocks = 0;
+    fp.rowptr = fp.colidx = nullptr;
+    fp.left = fp.mask_left = (int32_t)std::min<int64_t>(p.pat.left, fp.Skv1);
+    fp.right = fp.mask_right = (int32_t)std::min<int64_t>(p.pat.right, fp.Skv1);
+    fp.n_global = (int32_t)p.pat.n_global;
+    fp.gidx = p.pat.gidx;
+    fp.split_len = fp.n_splits = fp.ng_pad = 0;
+    fp.partial = nullptr;
+    if (int rc = launch_kind<T, MAT_LONGFORMER, TQ, 128, 4, 2, false, 3>(p, fp, 1, "mma_longformer_static")) return rc;
+    if (fp.n_global == 0) return MAT_OK;
+
+    const int tiles = (fp.n_global + 63) / 64;
+    const size_t per_split = (size_t)p.B * p.H * tiles * 64 * kPartialStride * sizeof(float);
+    if (per_split > kStaticScratchBytes)
+        return fail(MAT_ERR_UNSUPPORTED,
+                    "B*H*global rows = %lld*%lld*%d needs %zu bytes of partials even unsplit; the built-in "
+                    "scratch holds %zu: use mat_sparse_attn_fwd with a workspace",
+                    (long long)p.B, (long long)p.H, tiles * 64, per_split, kStaticScratchBytes);
+    const GlobalRowPlan want = plan_global_rows(p);
+    int64_t n_splits = std::min<int64_t>(want.n_splits, (int64_t)(kStaticScratchBytes / per_split));
+    int64_t len = (p.Skv + n_splits - 1) / n_splits;
+    len = std::max<int64_t>(512, (len + 127) / 128 * 128);
+    fp.split_len = (int32_t)len;
+    fp.n_splits = (int32_t)((p.Skv + len - 1) / len);
+    fp.ng_pad = tiles * 64;
+    fp.partial = scratch;
+    fp.left = fp.right = 0;
+    fp.mask_left = fp.mask_right = kBig;
+    if (int rc = launch_kind<T, kGlobalRows, TQ, 128, 4, 2, false, 3>(p, fp, 1, "mma_longformer_static",
+                                                                     (int64_t)tiles * fp.n_splits))
+        return rc;
+    const dim3 grid((unsigned)fp.n_global, (unsigned)fp.HH, (unsigned)p.B);
+    merge_global_rows_kernel<T><<<grid, 64, 0, p.stream>>>(fp.partial, (T *)p.o, fp.gidx, fp.n_splits, fp.ng_pad,
+                                                          fp.HH, fp.Sq1, fp.sl2);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? MAT_OK : cuda_fail(e, "merge_global_rows_kernel launch");
+}
+
+}  // namespace
+
+int launch_longformer_noalloc(const Problem &p) {
+    if (p.pat.kind != MAT_LONGFORMER)
+        return fail(MAT_ERR_UNSUPPORTED, "the allocation-free entry point serves MAT_LONGFORMER patterns only");
+    if (!mma_flash_supports(p))
+        return fail(MAT_ERR_UNSUPPORTED,
+                    "the allocation-free entry point needs 16-bit inputs, head width 64, q_offset 0 and S_q = S_kv");
+    float *scratch = nullptr;
+    if (int rc = static_scratch_on_current_device(&scratch)) return rc;
+    return p.dtype == MAT_BF16 ? launch_longformer_static<__nv_bfloat16>(p, scratch)
+                               : launch_longformer_static<__half>(p, scratch);
+}
+
 int flash_status_read_and_clear(int *out) {
     int zero = 0;
     cudaError_t e = cudaMemcpyFromSymbol(out, g_flash_status, sizeof(int));
@@ -712,3 +813,13 @@ int flash_status_read_and_clear(int *out) {
 }
 
 }  // namespace mat
+
+// Allocation-free Longformer forward (declared in include/mat_sparse_attn.h).  Neither this
+// function nor anything it calls allocates or frees device memory.
+extern "C" int mat_sparse_attn_fwd_longformer_noalloc(const void *q, const void *k, const void *v, void *o,
+                                                      int64_t B, int64_t S, int64_t H, int64_t D, int dtype,
+                                                      const mat_pattern_spec *spec, float scale, void *stream) {
+    mat::Problem p;
+    if (int rc = mat::make_problem(p, q, k, v, o, B, S, S, H, D, dtype, spec, scale, nullptr, 0, stream)) return rc;
+    return mat::launch_longformer_noalloc(p);
+}

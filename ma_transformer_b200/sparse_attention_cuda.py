@@ -120,6 +120,34 @@ def forward_sharded(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
     return out
 
 
+def forward_longformer_noalloc(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                               spec: PatternSpec, out: torch.Tensor,
+                               scale: Optional[float] = None) -> torch.Tensor:
+    """Longformer forward for callers that may not allocate device memory while they
+    run (an inference server whose arena already owns all of HBM, a latency-critical
+    loop that cannot take the device-wide stall of an allocation).  ``out`` must be
+    supplied; this function and the library call below it allocate nothing on the
+    device, and the scratch of the global-row pass is a fixed 4 MiB array inside the
+    library.  16-bit inputs, D = 64; B*H*ceil64(globals)*264 bytes must fit in 4 MiB
+    (RuntimeError otherwise: use ``forward_pattern``).  All calls on a device share
+    that array, so calls that overlap on the GPU race: keep them on one stream.  The
+    first call on a device resolves the array's address; make it before any stream
+    capture.  ``spec`` must already have been used on this device, or be given
+    device arrays before the no-allocation phase starts (its global positions are
+    uploaded once, on first use)."""
+    _check_inputs(query, key, value, out)
+    if not (query.shape == key.shape == value.shape == out.shape):
+        raise RuntimeError("Q,K,V and out must have same shape")
+    B, S, H, D = query.shape
+    with torch.cuda.device(query.device):
+        s = spec.device_struct(query.device)
+        stream = torch.cuda.current_stream(query.device).cuda_stream
+        nat.check(nat.lib.mat_sparse_attn_fwd_longformer_noalloc(
+            query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(), B, S, H, D,
+            _DTYPES[query.dtype], C.byref(s), float(scale) if scale else 0.0, C.c_void_p(stream)))
+    return out
+
+
 def forward(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
             window_size: int = 64) -> torch.Tensor:
     """Sparse attention forward (CUDA): keys [i-window_size, i+window_size].
