@@ -248,10 +248,14 @@ def gpu_arm(args):
         for s in range(n_sets):
             q, k, v = (t[:, a:b].to(dev).roll(s, dims=1).contiguous() for t in (q_cpu, k_cpu, v_cpu))
             sets.append((q, peer.register(k, v)))
-    out = torch.empty(B, rows, H, D, dtype=torch.bfloat16, device=dev)
+    # one output buffer per lane: steps are independent forwards, and two lanes (streams) let
+    # the tail of one step overlap the head of the next, as concurrent requests would
+    n_lanes = max(1, args.lanes)
+    outs = [torch.empty(B, rows, H, D, dtype=torch.bfloat16, device=dev) for _ in range(n_lanes)]
+    out = outs[0]
     launches = [0]
 
-    def step(i):
+    def step(i, out=out):
         if sharded is not None:
             q, k, v = sets[i % n_sets]
             sharded.forward(q, k, v, out=out)
@@ -279,15 +283,22 @@ def gpu_arm(args):
     # for the remainder, so exactly K steps run and the host issues K / n_sets launches.
     use_graph = args.graph and sharded is None
     if use_graph:
+        round_len = n_sets * -(-24 // n_sets)   # steps per captured round: whole passes over the sets
         side = torch.cuda.Stream()
+        lanes = [side] + [torch.cuda.Stream() for _ in range(n_lanes - 1)]
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             round_graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(round_graph, stream=side):
-                for s in range(n_sets):
-                    step(s)
+                for ln in lanes[1:]:
+                    ln.wait_stream(side)            # fork
+                for s in range(round_len):
+                    with torch.cuda.stream(lanes[s % n_lanes]):
+                        step(s, outs[s % n_lanes])
+                for ln in lanes[1:]:
+                    side.wait_stream(ln)            # join
             single_graphs = []
-            for s in range(n_sets):
+            for s in range(min(round_len, args.steps)):
                 g1 = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g1, stream=side):
                     step(s)
@@ -303,7 +314,7 @@ def gpu_arm(args):
     t_host0 = time.perf_counter()
     ev0.record()
     if use_graph:
-        rounds, rest = divmod(args.steps, n_sets)
+        rounds, rest = divmod(args.steps, round_len)
         for _ in range(rounds):
             round_graph.replay()
         for s in range(rest):
@@ -360,7 +371,7 @@ def gpu_arm(args):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "sharding": (f"sequence x{world}, {TAPS - 1}-row K/V halo, " + ("read in place from the neighbour GPU by the kernel" if peer is not None else "64 rows exchanged by NCCL send/recv")) if world > 1 else "none",
-                       "launch": "CUDA graphs" if use_graph else "one host launch per kernel",
+                       "launch": f"CUDA graphs, steps alternate over {n_lanes} streams" if use_graph else "one host launch per kernel",
                        "l2": f"{n_sets} rotating input sets of {per_rank_bytes >> 20} MiB per GPU (> 126 MB L2 between reuses)"},
             "clocks": clocks,
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -378,8 +389,66 @@ def gpu_arm(args):
         dist.destroy_process_group()
 
 
+def other_workload_arm(args):
+    """Device-resident timing of the block-sparse (cfg-3) and Longformer (cfg-4) configurations on
+    one GPU: same timing rules as the headline arm (events, warm-up, rotating input sets), one JSON
+    line with the HBM roofline of the algorithmic bytes and the executed tensor-core FLOP rate."""
+    import numpy as np
+    import torch
+    from ma_transformer_b200 import _native as nat
+    from ma_transformer_b200 import sparse_attention_cuda as ext
+    from ma_transformer_b200.patterns import PatternSpec, band_random_block_layout
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator().manual_seed(SEED)
+    if args.workload == "block":
+        Bw, S, Hw = 4, 16384, 8
+        rp, ci = band_random_block_layout(S // 64, 4, 2, seed=SEED)
+        spec = PatternSpec.block_sparse(64, rp, ci, causal=True)
+        flops = Bw * Hw * int(rp[-1]) * 4 * 64 ** 3
+        name = f"block-sparse fwd B={Bw} N={S} H={Hw} d=64 block=64 band4+2 random causal bf16"
+    else:
+        Bw, S, Hw = 2, 32768, 12
+        glob = torch.randperm(S, generator=g)[:32].sort().values.numpy()
+        spec = PatternSpec.longformer(64, 64, glob)
+        flops = Bw * Hw * (S * 129 + 2 * 32 * S) * 4 * 64
+        name = f"Longformer fwd B={Bw} N={S} H={Hw} d=64 window +-64, 32 global tokens bf16"
+    nbytes = 4 * Bw * S * Hw * 64 * 2
+    sets = [tuple(torch.randn(Bw, S, Hw, 64, generator=g).to(torch.bfloat16).to(dev) for _ in range(3))
+            for _ in range(2)]
+    out = torch.empty_like(sets[0][0])
+    for i in range(args.warmup):
+        ext.forward_pattern(*sets[i % 2], spec, out=out)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    ev0.record()
+    for i in range(args.steps):
+        ext.forward_pattern(*sets[i % 2], spec, out=out)
+    ev1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop(t0, time.perf_counter())
+    ms = ev0.elapsed_time(ev1) / args.steps
+    peak, peak_kind = measured_peak_gbs()
+    achieved = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": f"sparse-attn fwd tokens/s ({args.workload})", "value": Bw * S / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "dtype": "bf16", "data": "synthetic", "config": {"workload": name, "l2": "2 rotating input sets"},
+        "clocks": clocks, "kernel": nat.last_kernel(),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": f"{peak_kind} HBM copy bandwidth", "bytes_per_launch_algorithmic": nbytes},
+        "tensor": {"useful_flop_per_step": flops, "tflops": flops / (ms * 1e-3) / 1e12},
+        "device_status": nat.device_status()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="window", choices=["window", "block", "longformer"],
+                    help="window = the headline configuration; block / longformer = one-GPU timing of cfg-3 / cfg-4")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
@@ -389,6 +458,8 @@ def main():
     ap.add_argument("--halo", default="peer", choices=["peer", "nccl"],
                     help="N>1: edge tiles read the neighbour's rows in place (peer), or send/recv exchange (nccl)")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="launch every step from the host")
+    ap.add_argument("--lanes", type=int, default=2,
+                    help="streams the captured steps alternate over (each with its own output buffer)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -404,6 +475,9 @@ def main():
             "cpu_baseline": info,
             "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }), flush=True)
+        return
+    if args.workload != "window":
+        other_workload_arm(args)
         return
     gpu_arm(args)
 

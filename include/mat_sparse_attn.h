@@ -47,7 +47,7 @@ extern "C" {
  *                   the block-CSR layout, minus keys j > p when causal != 0
  *                   (src/csrc/sparse_attention.cpp:209-227 is the layout
  *                   |row - col| <= 1, causal = 0).  Column ids within a row
- *                   must be distinct.
+ *                   must be distinct and ascending.
  *   MAT_LONGFORMER  [p-left, p+right] united with the global positions; a query
  *                   at a global position takes every key
  *                   (src/csrc/sparse_attention.cpp:241-256, de-duplicated).

@@ -100,6 +100,7 @@ int make_problem(Problem &p, const void *q, const void *k, const void *v, void *
 }
 
 int run_problem(const Problem &p) {
+    if (umma_block_supports(p)) return launch_umma_block(p);
     if (mma_flash_supports(p)) {
         const size_t need = mma_flash_workspace_bytes(p);
         if (need > 0) {
@@ -163,7 +164,11 @@ const char *mat_last_kernel(void) { return g_last_kernel; }
 
 int mat_device_status(int *status_out) {
     if (!status_out) return fail(MAT_ERR_INVALID, "status_out is NULL");
-    return flash_status_read_and_clear(status_out);
+    int a = 0, b = 0;
+    if (int rc = flash_status_read_and_clear(&a)) return rc;
+    if (int rc = umma_status_read_and_clear(&b)) return rc;
+    *status_out = a | b;
+    return MAT_OK;
 }
 
 int mat_sparse_attn_fwd(const void *q, const void *k, const void *v, void *o, int64_t B,

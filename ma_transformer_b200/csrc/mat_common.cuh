@@ -56,6 +56,9 @@ bool mma_flash_supports(const Problem &p);   // mma_flash.cu
 int launch_mma_flash(const Problem &p);
 size_t mma_flash_workspace_bytes(const Problem &p);
 int flash_status_read_and_clear(int *out);   // status word left by a kernel whose bounded wait ran out
+bool umma_block_supports(const Problem &p);  // umma_block.cu: block layouts on tcgen05 / TMEM
+int launch_umma_block(const Problem &p);
+int umma_status_read_and_clear(int *out);
 
 template <typename T> struct Elem;
 template <> struct Elem<float> {

@@ -1,0 +1,468 @@
+// Block-sparse forward on the 5th-generation tensor cores: tcgen05.mma with the
+// accumulators in tensor memory (TMEM), operands staged by TMA.
+//
+// Block layouts with 64-wide (or wider) blocks make both contractions dense
+// 128 x 64 x 64 tiles, which is what tcgen05 is built for; the narrow-window
+// kernel stays on the warp-level mma path because its tiles are mostly mask.
+// Replaces, for MAT_BLOCK patterns, the intent of the reference's
+// BlockSparseAttention (src/csrc/sparse_attention.cpp:203-231 builds the layout,
+// :43-152 would walk it entry by entry in COO form).
+//
+// One CTA = 128 query rows of one (batch, head) = two 64-row halves that may
+// belong to different rows of the block layout.  The CTA walks the union of the
+// two rows' key blocks in ascending order (column ids are ascending within a
+// layout row, so the union is a two-pointer merge, done identically by every
+// thread that needs it), 64 keys per step:
+//
+//   control warp (warp 4, one lane):  TMA K/V chunk -> smem (2 stages)
+//                                     S = Q K^T      tcgen05.mma 128x64x16 x4 -> TMEM cols [0,64)
+//                                     O_part = P V   tcgen05.mma 128x64x16 x4 -> TMEM cols [64,128)
+//   softmax warps (warps 0-3):        thread r owns query row r: tcgen05.ld its 64 scores, mask,
+//                                     running max / sum, P as bf16 into smem (K-major, 128B swizzle),
+//                                     then tcgen05.ld its O_part row and fold it into registers.
+//
+// A half whose layout row does not hold the step's key block skips the softmax
+// work of that step (its rows of P and O_part are never read).  Everything that
+// waits does so on an mbarrier with a bounded wait; a wait that runs out sets the
+// library's status word and the CTA drains, frees its TMEM and leaves.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <cstdlib>
+#include <type_traits>
+#include <mutex>
+
+#include "mat_common.cuh"
+#include "ptx.cuh"
+
+namespace mat {
+namespace {
+
+constexpr int kRowBytes = 128;
+constexpr int kTileQ = 128;     // query rows per CTA (UMMA M)
+constexpr int kTileK = 64;      // keys per step (UMMA N for S, K extent for P V)
+constexpr int kTmemCols = 128;  // S in [0,64), O_part in [64,128)
+
+__device__ int g_umma_status = 0;
+
+struct UmmaParams {
+    int32_t Sq, Skv, off;  // query rows, key rows, q_offset
+    int32_t H;
+    int32_t block, per_blk;  // layout block edge, 64-key chunks per block
+    int32_t causal;
+    int64_t n_qblocks;
+    const int32_t *rowptr;
+    const int32_t *colidx;
+    float sl2;
+};
+
+// ---- tcgen05 wrappers -------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_u32(dst_smem)),
+                 "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// D[tmem] (+)= A[smem] * B[smem], M = 128, one K step of 16 elements
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrive on an mbarrier when every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     ptx::smem_u32(bar))
+                 : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a tile whose rows are 128 bytes, 128-byte swizzled, 8-row
+// groups 1024 bytes apart (the layout a {64, rows} TMA box with SWIZZLE_128B produces, and the one
+// the softmax warps write P in).  K-major operands step 32 bytes per K slice of 16 elements;
+// the MN-major operand (V as the B matrix of P V) steps 16 rows = 2048 bytes.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);   // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                        // leading byte offset (unused with one swizzle atom)
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset: next 8-row group
+    d |= (uint64_t)1 << 46;                        // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+    return d;
+}
+// kind::f16 instruction descriptor: fp32 accumulate, A/B type, M = 128, N = 64
+template <typename T>
+__device__ __forceinline__ uint32_t instr_desc(bool b_mn_major) {
+    const uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+    uint32_t d = 0;
+    d |= 1u << 4;                       // accumulator format f32
+    d |= fmt << 7;                      // A format
+    d |= fmt << 10;                     // B format
+    d |= (b_mn_major ? 1u : 0u) << 16;  // B major-ness
+    d |= (uint32_t)(kTileK >> 3) << 17; // N
+    d |= (uint32_t)(kTileQ >> 4) << 24; // M
+    return d;
+}
+
+// Ascending merge of the key blocks of the two layout rows a CTA covers, 64 keys per step.
+struct ChunkWalk {
+    const int32_t *colidx;
+    int ia, ea, ib, eb;  // cursors / ends of half A's and half B's row
+    int sub, per_blk, block;
+    int cur;             // current key block, -1 when exhausted
+    int flags;           // bit 0: half A holds it, bit 1: half B
+    __device__ __forceinline__ void init(const UmmaParams &P, int q0) {
+        colidx = P.colidx;
+        per_blk = P.per_blk;
+        block = P.block;
+        const int64_t ra = (int64_t)((uint32_t)(q0 + P.off) / (uint32_t)P.block);
+        const int64_t rb = (int64_t)((uint32_t)(q0 + 64 + P.off) / (uint32_t)P.block);
+        ia = ea = ib = eb = 0;
+        if (ra < P.n_qblocks) { ia = P.rowptr[ra]; ea = P.rowptr[ra + 1]; }
+        if (q0 + 64 < P.Sq && rb < P.n_qblocks) { ib = P.rowptr[rb]; eb = P.rowptr[rb + 1]; }
+        same = ra == rb;
+        if (same) { ib = eb = 0; }
+        sub = 0;
+        load();
+    }
+    bool same;  // both halves lie in one layout row
+    __device__ __forceinline__ void load() {
+        const int ca = ia < ea ? __ldg(colidx + ia) : INT32_MAX;
+        const int cb = ib < eb ? __ldg(colidx + ib) : INT32_MAX;
+        const int c = min(ca, cb);
+        if (c == INT32_MAX) { cur = -1; flags = 0; return; }
+        cur = c;
+        flags = (ca == c ? 1 : 0) | (cb == c ? 2 : 0);
+        if (same) flags = 3;
+    }
+    __device__ __forceinline__ bool done() const { return cur < 0; }
+    __device__ __forceinline__ int key_base() const { return cur * block + sub * kTileK; }
+    __device__ __forceinline__ void next() {
+        if (++sub < per_blk) return;
+        sub = 0;
+        if (flags & 1 && !same) ++ia;
+        if (same) ++ia;
+        if (flags & 2 && !same) ++ib;
+        load();
+    }
+};
+
+constexpr int kThreads = 160;  // 4 softmax warps + 1 control warp
+constexpr size_t kSmemBytes = 1024 + kTileQ * kRowBytes /*Q*/ + 2 * 2 * kTileK * kRowBytes /*K,V x2*/ +
+                              kTileQ * kRowBytes /*P*/ + 128 /*barriers, tmem address*/;
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, T *__restrict__ out, const UmmaParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *sQ = smem;
+    uint8_t *sKV = sQ + kTileQ * kRowBytes;            // stage s: K at +0, V at +8 KB
+    uint8_t *sP = sKV + 2 * 2 * kTileK * kRowBytes;
+    uint64_t *bars = (uint64_t *)(sP + kTileQ * kRowBytes);
+    uint64_t *bar_q = bars, *bar_kv = bars + 1 /*[2]*/, *bar_s = bars + 3, *bar_p = bars + 4, *bar_o = bars + 5,
+             *bar_done = bars + 6;
+    uint32_t *tmem_slot = (uint32_t *)(bars + 8);
+    constexpr int kStage = 2 * kTileK * kRowBytes;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.x, b = blockIdx.z;
+    const int q0 = blockIdx.y * kTileQ;
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(bar_q, 1);
+        ptx::mbar_init(bar_kv, 1);
+        ptx::mbar_init(bar_kv + 1, 1);
+        ptx::mbar_init(bar_s, 1);
+        ptx::mbar_init(bar_p, 4);
+        ptx::mbar_init(bar_o, 1);
+        ptx::mbar_init(bar_done, 4);
+        ptx::fence_barrier_init();
+    }
+    if (warp == 4) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 4) {
+        // ================= control warp =================
+        bool ok = true;
+        if (lane == 0) {
+            ChunkWalk w;
+            w.init(P, q0);
+            ptx::mbar_expect_tx(bar_q, kTileQ * kRowBytes);
+            ptx::tma_load_4d(sQ, &map_q, bar_q, 0, h, q0, b);
+            auto issue_load = [&](int t, int kb) {
+                uint8_t *dst = sKV + (t & 1) * kStage;
+                ptx::mbar_expect_tx(bar_kv + (t & 1), kStage);
+                ptx::tma_load_4d(dst, &map_k, bar_kv + (t & 1), 0, h, kb, b);
+                ptx::tma_load_4d(dst + kTileK * kRowBytes, &map_v, bar_kv + (t & 1), 0, h, kb, b);
+            };
+            const uint32_t idesc_s = instr_desc<T>(false), idesc_pv = instr_desc<T>(true);
+            const uint32_t q_addr = ptx::smem_u32(sQ), p_addr = ptx::smem_u32(sP);
+            if (!w.done()) issue_load(0, w.key_base());
+            ok = ptx::mbar_wait(bar_q, 0);
+            ChunkWalk ahead = w;  // cursor of the chunk being prefetched
+            if (!ahead.done()) ahead.next();
+            for (int t = 0; ok && !w.done(); ++t, w.next()) {
+                // stage (t+1)&1 was last read by P V of step t-1: wait for that before refilling it
+                if (!ahead.done()) {
+                    if (t >= 1) ok = ptx::mbar_wait(bar_o, (t - 1) & 1);
+                    if (!ok) break;
+                    issue_load(t + 1, ahead.key_base());
+                    ahead.next();
+                }
+                if (!(ok = ptx::mbar_wait(bar_kv + (t & 1), (t >> 1) & 1))) break;
+                tc_fence_after();
+                const uint32_t k_addr = ptx::smem_u32(sKV + (t & 1) * kStage);
+                const uint32_t v_addr = k_addr + kTileK * kRowBytes;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)   // S = Q K^T, 16 of the 64 head columns per instruction
+                    umma_f16(tmem, smem_desc(q_addr + ks * 32), smem_desc(k_addr + ks * 32), idesc_s, ks > 0);
+                umma_commit(bar_s);
+                if (!(ok = ptx::mbar_wait(bar_p, t & 1))) break;   // P of this step is in shared memory
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)   // O_part = P V, 16 of the 64 keys per instruction
+                    umma_f16(tmem + kTileK, smem_desc(p_addr + ks * 32), smem_desc(v_addr + ks * 16 * kRowBytes),
+                             idesc_pv, ks > 0);
+                umma_commit(bar_o);
+            }
+            if (!ok) atomicExch(&g_umma_status, 1);
+            // every softmax warp has read its last TMEM values before the columns are freed
+            if (!ptx::mbar_wait(bar_done, 0)) atomicExch(&g_umma_status, 1);
+        }
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+        return;
+    }
+
+    // ================= softmax warps: thread r owns query row r of the tile =================
+    const int r = threadIdx.x;             // 0..127 == TMEM lane
+    const int half = r >> 6;
+    const int p = q0 + r + P.off;          // key-coordinate position of this row
+    const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);
+    float o[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+
+    ChunkWalk w;
+    w.init(P, q0);
+    uint8_t *p_row = sP + r * kRowBytes;
+    for (int t = 0; !w.done(); ++t, w.next()) {
+        const int kb = w.key_base();
+        const bool mine = (w.flags >> half) & 1;   // uniform within a warp
+        if (!(ok = ptx::mbar_wait(bar_s, t & 1))) break;
+        tc_fence_after();
+        float alpha = 1.f;
+        if (mine) {
+            // keys this row may use in the chunk: j < j_end
+            int j_end = min(kTileK, P.Skv - kb);
+            if (P.causal) j_end = min(j_end, p - kb + 1);
+            // pass 1: row maximum
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 32) {
+                float s[32];
+                tmem_ld32(t_lane + c0, s);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, c0 + i < j_end ? s[i] : -INFINITY);
+            }
+            const float m_new = fmaxf(m_run, mx);
+            const float mu = m_new == -INFINITY ? 0.f : m_new;
+            alpha = ptx::ex2((m_run - mu) * P.sl2);
+            m_run = m_new;
+            const float mus = mu * P.sl2;
+            // pass 2: weights, packed to the operand type two at a time, into the swizzled P row
+            float sum = 0.f;
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 32) {
+                float s[32];
+                tmem_ld32(t_lane + c0, s);
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float x0 = c0 + 2 * i < j_end ? fmaf(s[2 * i], P.sl2, -mus) : -INFINITY;
+                    const float x1 = c0 + 2 * i + 1 < j_end ? fmaf(s[2 * i + 1], P.sl2, -mus) : -INFINITY;
+                    pk[i] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
+                    if (sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value) {
+                        sum += __uint_as_float(pk[i] << 16) + __uint_as_float(pk[i] & 0xffff0000u);
+                    } else {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&pk[i]));
+                        sum += f.x + f.y;
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {   // four 16-byte pieces = columns c0 + 8q .. c0 + 8q + 7
+                    const int chunk16 = (c0 >> 3) + q;
+                    *reinterpret_cast<uint4 *>(p_row + ((chunk16 ^ (r & 7)) << 4)) =
+                        make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+                }
+            }
+            l_run = l_run * alpha + sum;
+        }
+        ptx::fence_proxy_async_smem();   // the tensor core reads P through the async proxy
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar_p);
+        if (!(ok = ptx::mbar_wait(bar_o, t & 1))) break;
+        tc_fence_after();
+        if (mine) {
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 32) {
+                float part[32];
+                tmem_ld32(t_lane + kTileK + c0, part);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, part[i]);
+            }
+        }
+    }
+    if (!ok) atomicExch(&g_umma_status, 1);
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(bar_done);
+
+    if (ok && q0 + r < P.Sq) {
+        const float inv = l_run > 0.f ? __frcp_rn(l_run) : 0.f;
+        T *dst = out + (((int64_t)b * P.Sq + q0 + r) * P.H + h) * 64;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            uint4 v;
+            v.x = ptx::Mma<T>::pack(o[8 * q] * inv, o[8 * q + 1] * inv);
+            v.y = ptx::Mma<T>::pack(o[8 * q + 2] * inv, o[8 * q + 3] * inv);
+            v.z = ptx::Mma<T>::pack(o[8 * q + 4] * inv, o[8 * q + 5] * inv);
+            v.w = ptx::Mma<T>::pack(o[8 * q + 6] * inv, o[8 * q + 7] * inv);
+            *reinterpret_cast<uint4 *>(dst + 8 * q) = v;
+        }
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+
+PFN_cuTensorMapEncodeTiled encode_fn() {
+    static PFN_cuTensorMapEncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (PFN_cuTensorMapEncodeTiled)p;
+    });
+    return fn;
+}
+
+// [B, S, H, 64] 16-bit rows as dims {64, H, S, B}, box {64, 1, rows, 1}, 128-byte swizzle
+int make_map(CUtensorMap *m, const void *base, int dtype, int64_t H, int64_t S, int64_t B, int rows) {
+    PFN_cuTensorMapEncodeTiled enc = encode_fn();
+    if (!enc) return fail(MAT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[4] = {64, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
+    const cuuint64_t strides[3] = {128, (cuuint64_t)H * 128, (cuuint64_t)S * H * 128};
+    const cuuint32_t box[4] = {64, 1, (cuuint32_t)rows, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(m, dtype == MAT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                     const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MAT_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return MAT_OK;
+}
+
+template <typename T>
+int launch_t(const Problem &p) {
+    CUtensorMap mq, mk, mv;
+    if (int rc = make_map(&mq, p.q, p.dtype, p.H, p.Sq, p.B, kTileQ)) return rc;
+    if (int rc = make_map(&mk, p.k, p.dtype, p.H, p.Skv, p.B, kTileK)) return rc;
+    if (int rc = make_map(&mv, p.v, p.dtype, p.H, p.Skv, p.B, kTileK)) return rc;
+    UmmaParams up;
+    up.Sq = (int32_t)p.Sq;
+    up.Skv = (int32_t)p.Skv;
+    up.off = (int32_t)p.pat.q_offset;
+    up.H = (int32_t)p.H;
+    up.block = (int32_t)p.pat.block;
+    up.per_blk = up.block / kTileK;
+    up.causal = p.pat.causal;
+    up.n_qblocks = p.pat.n_qblocks;
+    up.rowptr = p.pat.rowptr;
+    up.colidx = p.pat.colidx;
+    up.sl2 = p.scale * 1.4426950408889634f;
+    auto kern = umma_block_fwd_kernel<T>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(umma_block_fwd_kernel)");
+    const dim3 grid((unsigned)p.H, (unsigned)((p.Sq + kTileQ - 1) / kTileQ), (unsigned)p.B);
+    kern<<<grid, kThreads, kSmemBytes, p.stream>>>(mq, mk, mv, (T *)p.o, up);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "umma_block_fwd_kernel launch");
+    note_kernel("umma_block");
+    return MAT_OK;
+}
+
+}  // namespace
+
+// Column ids must ascend within each layout row (the merge of the two rows a CTA covers relies
+// on it); the python front end sorts them, C callers are told so in the header.
+bool umma_block_supports(const Problem &p) {
+    if (p.pat.kind != MAT_BLOCK) return false;
+    if (p.dtype != MAT_BF16 && p.dtype != MAT_F16) return false;
+    if (p.D != 64 || p.pat.block % 64 != 0 || p.pat.q_offset % 64 != 0) return false;
+    const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
+    if (al % 16) return false;
+    if (p.Skv >= (1LL << 28) || p.B > 65535 || p.H > 0x7fffffffLL || (p.Sq + kTileQ - 1) / kTileQ > 65535) return false;
+    if (p.pat.block >= (1 << 24)) return false;
+    const char *force = std::getenv("MAT_BLOCK_KERNEL");  // debugging aid: "mma" keeps the warp-level kernel
+    return !(force && force[0] == 'm');
+}
+
+int launch_umma_block(const Problem &p) {
+    return p.dtype == MAT_BF16 ? launch_t<__nv_bfloat16>(p) : launch_t<__half>(p);
+}
+
+int umma_status_read_and_clear(int *out) {
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_umma_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_umma_status, &zero, sizeof(int));
+    return e == cudaSuccess ? MAT_OK : cuda_fail(e, "reading the kernel status word");
+}
+
+}  // namespace mat

@@ -52,6 +52,7 @@ class PatternSpec:
                 row = ci[rp[r]:rp[r + 1]]
                 if len(np.unique(row)) != len(row) or np.any(row < 0):
                     raise ValueError(f"block row {r}: column ids must be distinct and >= 0")
+                ci[rp[r]:rp[r + 1]] = np.sort(row)   # the library wants them ascending within a row
             self.blk_rowptr, self.blk_colidx = rp, ci
         if self.kind == LONGFORMER:
             g = np.unique(np.asarray(self.global_idx if self.global_idx is not None else [], dtype=np.int64))

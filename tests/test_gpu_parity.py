@@ -190,7 +190,7 @@ def test_block_sparse_band_random(dtype):
     spec = PatternSpec.block_sparse(block, rp, ci, causal=True)
     q, k, v = seeded_qkv(31, 2, S, 2, 64, dtype)
     got = run(spec, q, k, v)
-    assert nat.last_kernel() == ("rowwarp" if dtype == torch.float32 else "mma_block")
+    assert nat.last_kernel() == ("rowwarp" if dtype == torch.float32 else "umma_block")   # tcgen05 / TMEM path
     check_close(got, oracle_out(q, k, v, spec), dtype)
 
 
