@@ -41,7 +41,7 @@ namespace {
 constexpr int kRowBytes = 128;
 constexpr int kTileQ = 128;     // query rows per CTA (UMMA M)
 constexpr int kTileK = 64;      // keys per step (UMMA N for S, K extent for P V)
-constexpr int kTmemCols = 128;  // S in [0,64), O_part in [64,128)
+constexpr int kTmemCols = 256;  // S buffers in [0,128), O_part buffers in [128,256)
 
 __device__ int g_umma_status = 0;
 
@@ -177,9 +177,17 @@ struct ChunkWalk {
 };
 
 constexpr int kThreads = 160;  // 4 softmax warps + 1 control warp
-constexpr size_t kSmemBytes = 1024 + kTileQ * kRowBytes /*Q*/ + 2 * 2 * kTileK * kRowBytes /*K,V x2*/ +
-                              kTileQ * kRowBytes /*P*/ + 128 /*barriers, tmem address*/;
+constexpr int kKvStages = 3;
+constexpr int kStage = 2 * kTileK * kRowBytes;  // one K/V stage: K then V
+constexpr size_t kSmemBytes = 1024 + kTileQ * kRowBytes /*Q*/ + kKvStages * kStage + 2 * kTileQ * kRowBytes /*P x2*/ +
+                              256 /*barriers, tmem address*/;
 
+// The step pipeline (t = index of the 64-key chunk):
+//   control:  S(t+1) is issued before P V(t), so the tensor core computes the next scores while
+//             the softmax warps work on the current ones; S and O_part are double-buffered in
+//             TMEM (columns S0 S1 O0 O1), P is double-buffered in shared memory, K/V has 3 stages.
+//   softmax:  softmax(t) -> publish P(t) -> fold O_part(t-1) into the registers.  The fold of a
+//             chunk uses the rescale factor of that chunk's own softmax step (kept one step).
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -188,12 +196,11 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *sQ = smem;
     uint8_t *sKV = sQ + kTileQ * kRowBytes;            // stage s: K at +0, V at +8 KB
-    uint8_t *sP = sKV + 2 * 2 * kTileK * kRowBytes;
-    uint64_t *bars = (uint64_t *)(sP + kTileQ * kRowBytes);
-    uint64_t *bar_q = bars, *bar_kv = bars + 1 /*[2]*/, *bar_s = bars + 3, *bar_p = bars + 4, *bar_o = bars + 5,
-             *bar_done = bars + 6;
-    uint32_t *tmem_slot = (uint32_t *)(bars + 8);
-    constexpr int kStage = 2 * kTileK * kRowBytes;
+    uint8_t *sP = sKV + kKvStages * kStage;            // two P tiles
+    uint64_t *bars = (uint64_t *)(sP + 2 * kTileQ * kRowBytes);
+    uint64_t *bar_q = bars, *bar_kv = bars + 1 /*[3]*/, *bar_s = bars + 4 /*[2]*/, *bar_p = bars + 6 /*[2]*/,
+             *bar_o = bars + 8 /*[2]*/, *bar_done = bars + 10;
+    uint32_t *tmem_slot = (uint32_t *)(bars + 12);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x, b = blockIdx.z;
@@ -201,11 +208,12 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(bar_q, 1);
-        ptx::mbar_init(bar_kv, 1);
-        ptx::mbar_init(bar_kv + 1, 1);
-        ptx::mbar_init(bar_s, 1);
-        ptx::mbar_init(bar_p, 4);
-        ptx::mbar_init(bar_o, 1);
+        for (int i = 0; i < kKvStages; ++i) ptx::mbar_init(bar_kv + i, 1);
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(bar_s + i, 1);
+            ptx::mbar_init(bar_p + i, 4);
+            ptx::mbar_init(bar_o + i, 1);
+        }
         ptx::mbar_init(bar_done, 4);
         ptx::fence_barrier_init();
     }
@@ -217,50 +225,64 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    // TMEM columns: S buffer i at 64*i, O_part buffer i at 128 + 64*i
 
     if (warp == 4) {
         // ================= control warp =================
-        bool ok = true;
         if (lane == 0) {
-            ChunkWalk w;
-            w.init(P, q0);
+            bool ok = true;
+            ChunkWalk w_load, w_s, w_pv;     // cursors of the next chunk to load / to score / to multiply by V
+            w_load.init(P, q0);
+            w_s = w_pv = w_load;
             ptx::mbar_expect_tx(bar_q, kTileQ * kRowBytes);
             ptx::tma_load_4d(sQ, &map_q, bar_q, 0, h, q0, b);
-            auto issue_load = [&](int t, int kb) {
-                uint8_t *dst = sKV + (t & 1) * kStage;
-                ptx::mbar_expect_tx(bar_kv + (t & 1), kStage);
-                ptx::tma_load_4d(dst, &map_k, bar_kv + (t & 1), 0, h, kb, b);
-                ptx::tma_load_4d(dst + kTileK * kRowBytes, &map_v, bar_kv + (t & 1), 0, h, kb, b);
+            int t_load = 0;
+            auto issue_load = [&]() {
+                const int s = t_load % kKvStages, kb = w_load.key_base();
+                uint8_t *dst = sKV + s * kStage;
+                ptx::mbar_expect_tx(bar_kv + s, kStage);
+                ptx::tma_load_4d(dst, &map_k, bar_kv + s, 0, h, kb, b);
+                ptx::tma_load_4d(dst + kTileK * kRowBytes, &map_v, bar_kv + s, 0, h, kb, b);
+                ++t_load;
+                w_load.next();
             };
+            for (int i = 0; i < kKvStages && !w_load.done(); ++i) issue_load();
             const uint32_t idesc_s = instr_desc<T>(false), idesc_pv = instr_desc<T>(true);
             const uint32_t q_addr = ptx::smem_u32(sQ), p_addr = ptx::smem_u32(sP);
-            if (!w.done()) issue_load(0, w.key_base());
-            ok = ptx::mbar_wait(bar_q, 0);
-            ChunkWalk ahead = w;  // cursor of the chunk being prefetched
-            if (!ahead.done()) ahead.next();
-            for (int t = 0; ok && !w.done(); ++t, w.next()) {
-                // stage (t+1)&1 was last read by P V of step t-1: wait for that before refilling it
-                if (!ahead.done()) {
-                    if (t >= 1) ok = ptx::mbar_wait(bar_o, (t - 1) & 1);
-                    if (!ok) break;
-                    issue_load(t + 1, ahead.key_base());
-                    ahead.next();
-                }
-                if (!(ok = ptx::mbar_wait(bar_kv + (t & 1), (t >> 1) & 1))) break;
+            int t_s = 0;
+            auto issue_s = [&]() -> bool {   // S(t_s) = Q K^T into S buffer t_s & 1
+                const int s = t_s % kKvStages;
+                if (!ptx::mbar_wait(bar_kv + s, (t_s / kKvStages) & 1)) return false;
                 tc_fence_after();
-                const uint32_t k_addr = ptx::smem_u32(sKV + (t & 1) * kStage);
-                const uint32_t v_addr = k_addr + kTileK * kRowBytes;
+                const uint32_t k_addr = ptx::smem_u32(sKV + s * kStage);
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)   // S = Q K^T, 16 of the 64 head columns per instruction
-                    umma_f16(tmem, smem_desc(q_addr + ks * 32), smem_desc(k_addr + ks * 32), idesc_s, ks > 0);
-                umma_commit(bar_s);
-                if (!(ok = ptx::mbar_wait(bar_p, t & 1))) break;   // P of this step is in shared memory
+                for (int ks = 0; ks < 4; ++ks)   // 16 of the 64 head columns per instruction
+                    umma_f16(tmem + (t_s & 1) * kTileK, smem_desc(q_addr + ks * 32), smem_desc(k_addr + ks * 32),
+                             idesc_s, ks > 0);
+                umma_commit(bar_s + (t_s & 1));
+                ++t_s;
+                w_s.next();
+                return true;
+            };
+            ok = ptx::mbar_wait(bar_q, 0);
+            if (ok && !w_s.done()) ok = issue_s();
+            for (int t = 0; ok && !w_pv.done(); ++t, w_pv.next()) {
+                // the next scores first: their S buffer was released by p(t-1), waited for last round
+                if (!w_s.done() && !(ok = issue_s())) break;
+                if (!(ok = ptx::mbar_wait(bar_p + (t & 1), (t >> 1) & 1))) break;   // P(t) is in shared memory
                 tc_fence_after();
+                const uint32_t v_addr = ptx::smem_u32(sKV + (t % kKvStages) * kStage) + kTileK * kRowBytes;
+                const uint32_t pa = p_addr + (t & 1) * kTileQ * kRowBytes;
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)   // O_part = P V, 16 of the 64 keys per instruction
-                    umma_f16(tmem + kTileK, smem_desc(p_addr + ks * 32), smem_desc(v_addr + ks * 16 * kRowBytes),
-                             idesc_pv, ks > 0);
-                umma_commit(bar_o);
+                    umma_f16(tmem + 2 * kTileK + (t & 1) * kTileK, smem_desc(pa + ks * 32),
+                             smem_desc(v_addr + ks * 16 * kRowBytes), idesc_pv, ks > 0);
+                umma_commit(bar_o + (t & 1));
+                // stage t % 3 is free once P V(t) has read V: refill it with chunk t + 3
+                if (!w_load.done()) {
+                    if (!(ok = ptx::mbar_wait(bar_o + (t & 1), (t >> 1) & 1))) break;
+                    issue_load();
+                }
             }
             if (!ok) atomicExch(&g_umma_status, 1);
             // every softmax warp has read its last TMEM values before the columns are freed
@@ -283,16 +305,34 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
 
+    // fold O_part of chunk c (buffer c & 1) into the registers: o = o * alpha_c + O_part(c)
+    auto fold = [&](int c, float alpha_c) -> bool {
+        if (!ptx::mbar_wait(bar_o + (c & 1), (c >> 1) & 1)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+            float part[32];
+            tmem_ld32(t_lane + 2 * kTileK + (c & 1) * kTileK + c0, part);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha_c, part[i]);
+        }
+        return true;
+    };
+
     ChunkWalk w;
     w.init(P, q0);
-    uint8_t *p_row = sP + r * kRowBytes;
-    for (int t = 0; !w.done(); ++t, w.next()) {
+    bool prev_mine = false;
+    float prev_alpha = 1.f;
+    int t = 0;
+    for (; !w.done(); ++t, w.next()) {
         const int kb = w.key_base();
         const bool mine = (w.flags >> half) & 1;   // uniform within a warp
-        if (!(ok = ptx::mbar_wait(bar_s, t & 1))) break;
+        if (!(ok = ptx::mbar_wait(bar_s + (t & 1), (t >> 1) & 1))) break;
         tc_fence_after();
         float alpha = 1.f;
         if (mine) {
+            const uint32_t s_addr = t_lane + (t & 1) * kTileK;
+            uint8_t *p_row = sP + (t & 1) * kTileQ * kRowBytes + r * kRowBytes;
             // keys this row may use in the chunk: j < j_end
             int j_end = min(kTileK, P.Skv - kb);
             if (P.causal) j_end = min(j_end, p - kb + 1);
@@ -301,7 +341,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
             for (int c0 = 0; c0 < 64; c0 += 32) {
                 float s[32];
-                tmem_ld32(t_lane + c0, s);
+                tmem_ld32(s_addr + c0, s);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) mx = fmaxf(mx, c0 + i < j_end ? s[i] : -INFINITY);
             }
@@ -315,7 +355,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
             for (int c0 = 0; c0 < 64; c0 += 32) {
                 float s[32];
-                tmem_ld32(t_lane + c0, s);
+                tmem_ld32(s_addr + c0, s);
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -341,19 +381,13 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         ptx::fence_proxy_async_smem();   // the tensor core reads P through the async proxy
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar_p);
-        if (!(ok = ptx::mbar_wait(bar_o, t & 1))) break;
-        tc_fence_after();
-        if (mine) {
-#pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 32) {
-                float part[32];
-                tmem_ld32(t_lane + kTileK + c0, part);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, part[i]);
-            }
-        }
+        if (lane == 0) ptx::mbar_arrive(bar_p + (t & 1));
+        // while the tensor core multiplies P(t) by V, take in the result of the previous chunk
+        if (t >= 1 && prev_mine && !(ok = fold(t - 1, prev_alpha))) break;
+        prev_mine = mine;
+        prev_alpha = alpha;
     }
+    if (ok && t >= 1 && prev_mine) ok = fold(t - 1, prev_alpha);
     if (!ok) atomicExch(&g_umma_status, 1);
     tc_fence_before();
     __syncwarp();
