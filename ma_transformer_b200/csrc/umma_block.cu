@@ -342,8 +342,12 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             for (int c0 = 0; c0 < 64; c0 += 32) {
                 float s[32];
                 tmem_ld32(s_addr + c0, s);
+                if (j_end < c0 + 32) {   // only the chunks on the causal diagonal or at the sequence end
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, c0 + i < j_end ? s[i] : -INFINITY);
+                    for (int i = 0; i < 32; ++i) if (c0 + i >= j_end) s[i] = -INFINITY;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, s[i]);
             }
             const float m_new = fmaxf(m_run, mx);
             const float mu = m_new == -INFINITY ? 0.f : m_new;
@@ -356,11 +360,15 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             for (int c0 = 0; c0 < 64; c0 += 32) {
                 float s[32];
                 tmem_ld32(s_addr + c0, s);
+                if (j_end < c0 + 32) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) if (c0 + i >= j_end) s[i] = -INFINITY;
+                }
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float x0 = c0 + 2 * i < j_end ? fmaf(s[2 * i], P.sl2, -mus) : -INFINITY;
-                    const float x1 = c0 + 2 * i + 1 < j_end ? fmaf(s[2 * i + 1], P.sl2, -mus) : -INFINITY;
+                    const float x0 = fmaf(s[2 * i], P.sl2, -mus);
+                    const float x1 = fmaf(s[2 * i + 1], P.sl2, -mus);
                     pk[i] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
                     if (sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value) {
                         sum += __uint_as_float(pk[i] << 16) + __uint_as_float(pk[i] & 0xffff0000u);
