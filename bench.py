@@ -283,7 +283,8 @@ def gpu_arm(args):
     # for the remainder, so exactly K steps run and the host issues K / n_sets launches.
     use_graph = args.graph and sharded is None
     if use_graph:
-        round_len = n_sets * -(-24 // n_sets)   # steps per captured round: whole passes over the sets
+        # steps per captured round: whole passes over the input sets, about 24 steps, never more than K
+        round_len = n_sets * max(1, min(-(-24 // n_sets), args.steps // n_sets))
         side = torch.cuda.Stream()
         lanes = [side] + [torch.cuda.Stream() for _ in range(n_lanes - 1)]
         side.wait_stream(torch.cuda.current_stream())

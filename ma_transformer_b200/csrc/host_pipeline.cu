@@ -58,7 +58,11 @@ int64_t chunk_rows(int64_t S, int64_t H, int64_t D, int dtype, const mat_pattern
         while (b) { int64_t t = a % b; a = b; b = t; }
         unit = unit / a * spec->block;
     }
-    const int64_t target = (4 << 20) / row_bytes;  // about 4 MiB per tensor and chunk
+    // about 4 MiB per tensor and chunk, but at least 8 chunks per sequence (down to 512 KiB), so
+    // that short sequences still overlap their copies with the forward
+    int64_t chunk_bytes = S * row_bytes / 8;
+    chunk_bytes = chunk_bytes > (4 << 20) ? (4 << 20) : (chunk_bytes < (512 << 10) ? (512 << 10) : chunk_bytes);
+    const int64_t target = chunk_bytes / row_bytes;
     int64_t c = target / unit * unit;
     if (c < unit) c = unit;
     return c >= S ? S : c;
