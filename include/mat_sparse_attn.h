@@ -128,6 +128,21 @@ int mat_sparse_attn_fwd_sharded(const void *q, const void *k, const void *v, voi
                                 const mat_pattern_spec *spec, float scale, void *stream);
 
 /*
+ * Backward of window attention: dQ, dK, dV from Q, K, V and the output gradient,
+ * all [B, S, H, D].  Replaces sparse_backward_cuda / dense_backward_cuda and their
+ * kernels (src/cuda/sparse_attention_kernel.cu:460-497, 384-421, 265-346, 104-208):
+ * the reference's window is left = right = window_size, its dense call is the
+ * window that covers S (right = 0 when causal).  MAT_WINDOW patterns, q_offset = 0.
+ * Deterministic (no atomics).  workspace: mat_sparse_attn_bwd_workspace_bytes()
+ * bytes of device scratch, 256-byte aligned (per-row log-sum-exp and delta).
+ */
+int mat_sparse_attn_bwd(const void *q, const void *k, const void *v, const void *dout,
+                        void *dq, void *dk, void *dv, int64_t B, int64_t S, int64_t H, int64_t D,
+                        int dtype, const mat_pattern_spec *spec, float scale,
+                        void *workspace, size_t workspace_bytes, void *stream);
+size_t mat_sparse_attn_bwd_workspace_bytes(int64_t B, int64_t S, int64_t H);
+
+/*
  * Longformer forward that allocates nothing and takes no workspace.  It has no
  * counterpart in the reference.  It is for hosts that may not obtain device
  * memory while they run: a server that gave all of HBM to its own arena at

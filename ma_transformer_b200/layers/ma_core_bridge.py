@@ -141,11 +141,13 @@ class MACoreAttentionFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output: torch.Tensor):
         query, key, value = ctx.saved_tensors
-        if ctx.pattern is not None:
-            raise NotImplementedError("backward is defined for the reference's window and dense patterns only")
+        if ctx.pattern is not None and not (query.is_cuda and ctx.pattern.kind == 0):
+            raise NotImplementedError("backward is defined for window patterns (and on CUDA tensors for custom ones)")
         if query.is_cuda:
             args = (query.contiguous(), key.contiguous(), value.contiguous(), grad_output.contiguous())
-            if ctx.sparse:
+            if ctx.pattern is not None:
+                dq, dk, dv = sparse_attention_cuda.backward_pattern(*args, ctx.pattern)
+            elif ctx.sparse:
                 dq, dk, dv = sparse_attention_cuda.backward(*args, int(ctx.window_size))
             else:
                 dq, dk, dv = sparse_attention_cuda.dense_backward(*args, bool(ctx.use_causal_mask))

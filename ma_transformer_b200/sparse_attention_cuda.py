@@ -219,35 +219,37 @@ def forward_host(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, sp
     return out
 
 
-def _recompute_and_grad(fn, query, key, value, grad_out) -> List[torch.Tensor]:
-    q = query.detach().requires_grad_(True)
-    k = key.detach().requires_grad_(True)
-    v = value.detach().requires_grad_(True)
-    with torch.enable_grad():
-        y = fn(q, k, v)
-    return list(torch.autograd.grad(y, (q, k, v), grad_out))
+def backward_pattern(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, grad_out: torch.Tensor,
+                     spec: PatternSpec, scale: Optional[float] = None) -> List[torch.Tensor]:
+    """[dQ, dK, dV] of a window pattern (sliding, causal, dilated, dense-as-window) by the
+    library's backward kernels: deterministic, no atomics, fp32 math for every dtype."""
+    _check_inputs(query, key, value, grad_out)
+    if not (query.shape == key.shape == value.shape == grad_out.shape):
+        raise RuntimeError("All tensors must have same shape")
+    B, S, H, D = query.shape
+    dq, dk, dv = torch.empty_like(query), torch.empty_like(key), torch.empty_like(value)
+    with torch.cuda.device(query.device):
+        s = spec.device_struct(query.device)
+        ws = _workspace(query.device, nat.lib.mat_sparse_attn_bwd_workspace_bytes(B, S, H))
+        stream = torch.cuda.current_stream(query.device).cuda_stream
+        nat.check(nat.lib.mat_sparse_attn_bwd(
+            query.data_ptr(), key.data_ptr(), value.data_ptr(), grad_out.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+            dv.data_ptr(), B, S, H, D, _DTYPES[query.dtype], C.byref(s), float(scale) if scale else 0.0,
+            ws.data_ptr(), ws.numel(), C.c_void_p(stream)))
+    return [dq, dk, dv]
 
 
 def backward(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, grad_out: torch.Tensor,
              window_size: int = 64) -> List[torch.Tensor]:
     """Sparse attention backward (CUDA) -> [dQ, dK, dV]; the call of
-    sparse_attention_kernel.cu:460-497.  Outside the forward hot path: computed on
-    the device by differentiating a banded torch recomputation."""
-    _check_inputs(query, key, value, grad_out)
-    if not (query.shape == key.shape == value.shape == grad_out.shape):
-        raise RuntimeError("All tensors must have same shape")
-    from .layers.ma_core_bridge import pytorch_sparse_attention
-    return _recompute_and_grad(lambda q, k, v: pytorch_sparse_attention(q, k, v, int(window_size)),
-                               query, key, value, grad_out)
+    sparse_attention_kernel.cu:460-497 (keys [i-window_size, i+window_size])."""
+    return backward_pattern(query, key, value, grad_out, PatternSpec.sliding_window(int(window_size)))
 
 
 def dense_backward(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                    grad_out: torch.Tensor, use_causal_mask: bool = False) -> List[torch.Tensor]:
     """Dense attention backward (CUDA) -> [dQ, dK, dV]; the call of
-    sparse_attention_kernel.cu:384-421.  Outside the forward hot path."""
-    _check_inputs(query, key, value, grad_out)
-    if not (query.shape == key.shape == value.shape == grad_out.shape):
-        raise RuntimeError("All tensors must have same shape")
-    from .layers.ma_core_bridge import pytorch_dense_attention
-    return _recompute_and_grad(lambda q, k, v: pytorch_dense_attention(q, k, v, bool(use_causal_mask)),
-                               query, key, value, grad_out)
+    sparse_attention_kernel.cu:384-421, as the window that covers the sequence."""
+    S = query.shape[1] if query.dim() == 4 else 0
+    return backward_pattern(query, key, value, grad_out,
+                            PatternSpec(WINDOW, left=S, right=0 if use_causal_mask else S))

@@ -386,3 +386,42 @@ def test_cfg2_full_size_properties():
 def test_device_status_word_is_clear():
     torch.cuda.synchronize()
     assert nat.device_status() == 0
+
+
+# ---- backward kernels (next row after the forward) -----------------------------------------------------
+
+@pytest.mark.parametrize("B,S,H,D", [(2, 33, 2, 16), (1, 7, 1, 5), (2, 65, 3, 32), (1, 128, 2, 64)])
+@pytest.mark.parametrize("W", [0, 1, 4, 8, 200])
+def test_backward_matches_autograd_of_reference_oracle(B, S, H, D, W):
+    """tests/python/test_cuda_backward.py:75-101 and test_cuda_extensive.py:168-193 compare the extension's
+    backward with autograd through the python oracle at 2e-3."""
+    q, k, v = (t.to(DEV) for t in seeded_qkv(81, B, S, H, D))
+    go = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(82)).to(DEV)
+    dq, dk, dv = ext.backward(q, k, v, go, W)
+    assert nat.last_kernel() == "bwd_window"
+    qr, kr, vr = (t.detach().cpu().double().requires_grad_(True) for t in (q, k, v))
+    mt.pytorch_sparse_attention(qr, kr, vr, W).backward(go.cpu().double())
+    for got, ref in ((dq, qr), (dk, kr), (dv, vr)):
+        assert (got.cpu().double() - ref.grad).abs().max() < 2e-5 * max(1.0, float(ref.grad.abs().max()))
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_dense_backward_and_custom_windows(causal):
+    q, k, v = (t.to(DEV) for t in seeded_qkv(83, 2, 40, 2, 24))
+    go = torch.randn(2, 40, 2, 24, generator=torch.Generator().manual_seed(84)).to(DEV)
+    dq, dk, dv = ext.dense_backward(q, k, v, go, causal)
+    qr, kr, vr = (t.detach().cpu().double().requires_grad_(True) for t in (q, k, v))
+    mt.pytorch_dense_attention(qr, kr, vr, causal).backward(go.cpu().double())
+    for got, ref in ((dq, qr), (dk, kr), (dv, vr)):
+        assert (got.cpu().double() - ref.grad).abs().max() < 2e-5 * max(1.0, float(ref.grad.abs().max()))
+    # a dilated causal window through the module (bf16): gradients flow and match the fp32 kernels loosely
+    spec = PatternSpec.causal_window(8, dilation=2)
+    attn = mt.MACoreAttention(sparse=True, window_size=8, pattern=spec, fallback_training=False)
+    qb, kb, vb = (t.to(torch.bfloat16).requires_grad_(True) for t in seeded_qkv(85, 1, 64, 2, 64))
+    qb, kb, vb = (t.detach().to(DEV).requires_grad_(True) for t in (qb, kb, vb))
+    attn(qb, kb, vb).float().square().sum().backward()
+    q32, k32, v32 = (t.detach().float().requires_grad_(True) for t in (qb, kb, vb))
+    attn(q32, k32, v32).square().sum().backward()
+    for a16, a32 in ((qb, q32), (kb, k32), (vb, v32)):
+        assert torch.isfinite(a16.grad.float()).all()
+        assert (a16.grad.float() - a32.grad).abs().max() < 0.06 * max(1.0, float(a32.grad.abs().max()))
