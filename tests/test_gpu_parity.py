@@ -425,3 +425,39 @@ def test_dense_backward_and_custom_windows(causal):
     for a16, a32 in ((qb, q32), (kb, k32), (vb, v32)):
         assert torch.isfinite(a16.grad.float()).all()
         assert (a16.grad.float() - a32.grad).abs().max() < 0.06 * max(1.0, float(a32.grad.abs().max()))
+
+
+def test_block_layout_on_warp_level_kernel_too(monkeypatch):
+    """MAT_BLOCK_KERNEL=mma keeps block layouts on the warp-level ring kernel (debugging aid);
+    both kernels must agree with the oracle."""
+    S, block = 512, 64
+    rp, ci = band_random_block_layout(S // block, 4, 2, seed=9)
+    spec = PatternSpec.block_sparse(block, rp, ci, causal=True)
+    q, k, v = seeded_qkv(34, 1, S, 2, 64, torch.bfloat16)
+    want = oracle_out(q, k, v, spec)
+    monkeypatch.setenv("MAT_BLOCK_KERNEL", "mma")
+    got = run(spec, q, k, v)
+    assert nat.last_kernel() == "mma_block"
+    check_close(got, want, torch.bfloat16)
+    monkeypatch.delenv("MAT_BLOCK_KERNEL")
+    got = run(spec, q, k, v)
+    assert nat.last_kernel() == "umma_block"
+    check_close(got, want, torch.bfloat16)
+
+
+def test_random_windows_and_offsets_fuzz():
+    """Seeded sweep over window shapes, dilations, lengths and shard offsets on the tiled kernel."""
+    rng = np.random.default_rng(77)
+    for _ in range(40):
+        dil = int(rng.choice([1, 1, 2, 3]))
+        left, right = int(rng.integers(0, 90)), int(rng.integers(0, 90))
+        if rng.random() < 0.4:
+            right = 0
+        Sq = int(rng.integers(1, 12)) * 16 * dil
+        off = int(rng.integers(0, 6)) * dil * int(rng.choice([1, 16]))
+        tail = int(rng.integers(0, 5)) * dil
+        spec = PatternSpec(left=left, right=right, dilation=dil).shifted(off)
+        q, k, v = seeded_qkv(int(rng.integers(1 << 30)), 1, Sq, 2, 64, torch.bfloat16, Skv=Sq + off + tail)
+        got = run(spec, q, k, v)
+        assert nat.last_kernel() == "mma_window", (left, right, dil, Sq, off, tail)
+        check_close(got, oracle_out(q, k, v, spec), torch.bfloat16)
