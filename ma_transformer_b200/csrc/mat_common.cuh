@@ -59,6 +59,16 @@ int flash_status_read_and_clear(int *out);   // status word left by a kernel who
 bool umma_block_supports(const Problem &p);  // umma_block.cu: block layouts on tcgen05 / TMEM
 int launch_umma_block(const Problem &p);
 int umma_status_read_and_clear(int *out);
+// Longformer global-row pass on tcgen05 (umma_block.cu): how the key axis is split, and the launch
+constexpr int kPartialStride = 66;   // floats per row of a partial: max, sum, 64 outputs
+struct GlobalRowSplit {
+    int tiles, tile_rows;   // tiles of the global-position list, rows per tile
+    int n_splits, split_len;
+    int ng_pad;             // rows per split in the partial buffer
+    size_t bytes;           // partial buffer size
+};
+GlobalRowSplit plan_umma_global_rows(const Problem &p);
+int launch_umma_global_rows(const Problem &p, const GlobalRowSplit &g, float *partial);
 
 template <typename T> struct Elem;
 template <> struct Elem<float> {

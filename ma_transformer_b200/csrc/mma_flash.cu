@@ -27,6 +27,7 @@
 #include <cudaTypedefs.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "mat_common.cuh"
@@ -70,7 +71,6 @@ struct FlashParams {
 };
 
 constexpr int kGlobalRows = 3;       // kernel kind beside the MAT_* pattern kinds
-constexpr int kPartialStride = 66;   // floats per row: max, sum, 64 outputs
 
 __device__ __forceinline__ uint32_t swz(uint32_t base, int row, int chunk16) {
     return base + row * kRowBytes + ((chunk16 ^ (row & 7)) << 4);
@@ -594,6 +594,11 @@ GlobalRowPlan plan_global_rows(const Problem &p) {
     return g;
 }
 
+bool use_mma_global_rows() {
+    const char *force = std::getenv("MAT_GLOBAL_ROWS_KERNEL");
+    return force && force[0] == 'm';
+}
+
 template <typename T>
 int launch_t(const Problem &p) {
     constexpr int TQ = 64;
@@ -641,7 +646,18 @@ int launch_t(const Problem &p) {
         // pass 1: every row over its window plus the keys at the global positions
         if (int rc = launch_kind<T, MAT_LONGFORMER, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_longformer")) return rc;
         if (fp.n_global == 0) return MAT_OK;
-        // pass 2: the rows AT the global positions over every key, split along the key axis
+        // pass 2: the rows AT the global positions over every key, split along the key axis:
+        // on tcgen05 (128 gathered rows per CTA) unless MAT_GLOBAL_ROWS_KERNEL=mma asks for the
+        // warp-level kernel (debugging aid)
+        if (!use_mma_global_rows()) {
+            const GlobalRowSplit u = plan_umma_global_rows(p);
+            if (int rc = launch_umma_global_rows(p, u, (float *)p.workspace)) return rc;
+            const dim3 grid_m((unsigned)fp.n_global, (unsigned)fp.HH, (unsigned)p.B);
+            merge_global_rows_kernel<T><<<grid_m, 64, 0, p.stream>>>((const float *)p.workspace, (T *)p.o, fp.gidx,
+                                                                    u.n_splits, u.ng_pad, fp.HH, fp.Sq1, fp.sl2);
+            cudaError_t e2 = cudaGetLastError();
+            return e2 == cudaSuccess ? MAT_OK : cuda_fail(e2, "merge_global_rows_kernel launch");
+        }
         const GlobalRowPlan g = plan_global_rows(p);
         fp.left = fp.right = 0;
         fp.mask_left = fp.mask_right = kBig;
@@ -697,7 +713,7 @@ bool mma_flash_supports(const Problem &p) {
 
 size_t mma_flash_workspace_bytes(const Problem &p) {
     if (p.pat.kind != MAT_LONGFORMER || p.pat.n_global == 0) return 0;
-    return plan_global_rows(p).bytes;
+    return std::max(plan_global_rows(p).bytes, plan_umma_global_rows(p).bytes);   // either pass-2 kernel fits
 }
 
 int launch_mma_flash(const Problem &p) {

@@ -28,6 +28,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <type_traits>
 #include <mutex>
@@ -54,7 +55,15 @@ struct UmmaParams {
     const int32_t *rowptr;
     const int32_t *colidx;
     float sl2;
+    // global-row pass (kModeGlobalRows): the query tile is the rows at the Longformer global
+    // positions, the keys are one split of the whole sequence, the result is a partial
+    int32_t n_global;
+    const int64_t *gidx;
+    int32_t split_len, n_splits, ng_pad;
+    float *partial;   // [B, H, n_splits, ng_pad, kPartialStride]: max, sum, unnormalised output
 };
+
+constexpr int kModeBlock = 0, kModeGlobalRows = 1;
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols) {
@@ -164,9 +173,20 @@ struct ChunkWalk {
         flags = (ca == c ? 1 : 0) | (cb == c ? 2 : 0);
         if (same) flags = 3;
     }
+    // a plain key range [lo, hi) instead of a layout: 64-key steps, both halves take part
+    __device__ __forceinline__ void init_range(int lo, int hi) {
+        colidx = nullptr;
+        block = kTileK; per_blk = 1; sub = 0; same = true;
+        ia = lo / kTileK;                    // lo is a multiple of 64
+        ea = (hi + kTileK - 1) / kTileK;
+        ib = eb = 0;
+        cur = ia < ea ? ia : -1;
+        flags = 3;
+    }
     __device__ __forceinline__ bool done() const { return cur < 0; }
     __device__ __forceinline__ int key_base() const { return cur * block + sub * kTileK; }
     __device__ __forceinline__ void next() {
+        if (colidx == nullptr) { cur = ++ia < ea ? ia : -1; return; }
         if (++sub < per_blk) return;
         sub = 0;
         if (flags & 1 && !same) ++ia;
@@ -188,7 +208,7 @@ constexpr size_t kSmemBytes = 1024 + kTileQ * kRowBytes /*Q*/ + kKvStages * kSta
 //             TMEM (columns S0 S1 O0 O1), P is double-buffered in shared memory, K/V has 3 stages.
 //   softmax:  softmax(t) -> publish P(t) -> fold O_part(t-1) into the registers.  The fold of a
 //             chunk uses the rescale factor of that chunk's own softmax step (kept one step).
-template <typename T>
+template <typename T, int MODE>
 __global__ void __launch_bounds__(kThreads)
 umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, T *__restrict__ out, const UmmaParams P) {
@@ -204,7 +224,11 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x, b = blockIdx.z;
-    const int q0 = blockIdx.y * kTileQ;
+    // global-row pass: blockIdx.y = (128-row tile of the global-position list) * n_splits + key split
+    const int split = MODE == kModeGlobalRows ? blockIdx.y % P.n_splits : 0;
+    const int q0 = (MODE == kModeGlobalRows ? blockIdx.y / P.n_splits : blockIdx.y) * kTileQ;
+    const int range_lo = split * P.split_len;
+    const int range_hi = min(range_lo + P.split_len, P.Skv);
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(bar_q, 1);
@@ -232,10 +256,21 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (lane == 0) {
             bool ok = true;
             ChunkWalk w_load, w_s, w_pv;     // cursors of the next chunk to load / to score / to multiply by V
-            w_load.init(P, q0);
+            if (MODE == kModeGlobalRows) w_load.init_range(range_lo, range_hi);
+            else w_load.init(P, q0);
             w_s = w_pv = w_load;
             ptx::mbar_expect_tx(bar_q, kTileQ * kRowBytes);
-            ptx::tma_load_4d(sQ, &map_q, bar_q, 0, h, q0, b);
+            if (MODE == kModeGlobalRows) {
+                // map_q is a one-row view here: row r of the tile is the query at global position
+                // gidx[q0 + r]; slots past the list read out of bounds, i.e. zeros
+                for (int r = 0; r < kTileQ; ++r) {
+                    const int e = q0 + r;
+                    const int row = e < P.n_global ? (int)P.gidx[e] : P.Sq;
+                    ptx::tma_load_4d(sQ + r * kRowBytes, &map_q, bar_q, 0, h, row, b);
+                }
+            } else {
+                ptx::tma_load_4d(sQ, &map_q, bar_q, 0, h, q0, b);
+            }
             int t_load = 0;
             auto issue_load = [&]() {
                 const int s = t_load % kKvStages, kb = w_load.key_base();
@@ -320,13 +355,16 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     };
 
     ChunkWalk w;
-    w.init(P, q0);
+    if (MODE == kModeGlobalRows) w.init_range(range_lo, range_hi);
+    else w.init(P, q0);
+    // global-row pass: a warp takes part iff any of its 32 rows is a real global position
+    const bool warp_has_rows = MODE != kModeGlobalRows || q0 + warp * 32 < P.n_global;
     bool prev_mine = false;
     float prev_alpha = 1.f;
     int t = 0;
     for (; !w.done(); ++t, w.next()) {
         const int kb = w.key_base();
-        const bool mine = (w.flags >> half) & 1;   // uniform within a warp
+        const bool mine = MODE == kModeGlobalRows ? warp_has_rows : (w.flags >> half) & 1;   // uniform within a warp
         if (!(ok = ptx::mbar_wait(bar_s + (t & 1), (t >> 1) & 1))) break;
         tc_fence_after();
         float alpha = 1.f;
@@ -334,8 +372,8 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const uint32_t s_addr = t_lane + (t & 1) * kTileK;
             uint8_t *p_row = sP + (t & 1) * kTileQ * kRowBytes + r * kRowBytes;
             // keys this row may use in the chunk: j < j_end
-            int j_end = min(kTileK, P.Skv - kb);
-            if (P.causal) j_end = min(j_end, p - kb + 1);
+            int j_end = min(kTileK, (MODE == kModeGlobalRows ? range_hi : P.Skv) - kb);
+            if (MODE == kModeBlock && P.causal) j_end = min(j_end, p - kb + 1);
             // pass 1: row maximum
             float mx = -INFINITY;
 #pragma unroll
@@ -401,6 +439,17 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(bar_done);
 
+    if (MODE == kModeGlobalRows) {
+        if (ok && q0 + r < P.n_global) {
+            float *pr = P.partial +
+                        ((((int64_t)b * P.H + h) * P.n_splits + split) * P.ng_pad + q0 + r) * kPartialStride;
+            pr[0] = m_run;
+            pr[1] = l_run;
+#pragma unroll
+            for (int i = 0; i < 64; i += 2) *reinterpret_cast<float2 *>(pr + 2 + i) = make_float2(o[i], o[i + 1]);
+        }
+        return;
+    }
     if (ok && q0 + r < P.Sq) {
         const float inv = l_run > 0.f ? __frcp_rn(l_run) : 0.f;
         T *dst = out + (((int64_t)b * P.Sq + q0 + r) * P.H + h) * 64;
@@ -465,7 +514,8 @@ int launch_t(const Problem &p) {
     up.rowptr = p.pat.rowptr;
     up.colidx = p.pat.colidx;
     up.sl2 = p.scale * 1.4426950408889634f;
-    auto kern = umma_block_fwd_kernel<T>;
+    up.n_global = 0; up.gidx = nullptr; up.split_len = up.n_splits = up.ng_pad = 0; up.partial = nullptr;
+    auto kern = umma_block_fwd_kernel<T, kModeBlock>;
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [&] {
@@ -480,7 +530,56 @@ int launch_t(const Problem &p) {
     return MAT_OK;
 }
 
+template <typename T>
+int launch_global_rows_t(const Problem &p, const GlobalRowSplit &g, float *partial) {
+    CUtensorMap mq, mk, mv;
+    if (int rc = make_map(&mq, p.q, p.dtype, p.H, p.Sq, p.B, 1)) return rc;   // one-row view: gathered tile
+    if (int rc = make_map(&mk, p.k, p.dtype, p.H, p.Skv, p.B, kTileK)) return rc;
+    if (int rc = make_map(&mv, p.v, p.dtype, p.H, p.Skv, p.B, kTileK)) return rc;
+    UmmaParams up;
+    up.Sq = (int32_t)p.Sq; up.Skv = (int32_t)p.Skv; up.off = 0; up.H = (int32_t)p.H;
+    up.block = kTileK; up.per_blk = 1; up.causal = 0; up.n_qblocks = 0; up.rowptr = up.colidx = nullptr;
+    up.sl2 = p.scale * 1.4426950408889634f;
+    up.n_global = (int32_t)p.pat.n_global;
+    up.gidx = p.pat.gidx;
+    up.split_len = g.split_len; up.n_splits = g.n_splits; up.ng_pad = g.ng_pad;
+    up.partial = partial;
+    auto kern = umma_block_fwd_kernel<T, kModeGlobalRows>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(umma global rows)");
+    const dim3 grid((unsigned)p.H, (unsigned)(g.tiles * g.n_splits), (unsigned)p.B);
+    kern<<<grid, kThreads, kSmemBytes, p.stream>>>(mq, mk, mv, (T *)nullptr, up);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? MAT_OK : cuda_fail(e, "umma global-row kernel launch");
+}
+
 }  // namespace
+
+// The rows at the Longformer global positions over every key, on tcgen05: 128 gathered query rows
+// per CTA, the key axis cut into splits (64 a multiple), partials left for the merge kernel.
+GlobalRowSplit plan_umma_global_rows(const Problem &p) {
+    GlobalRowSplit g;
+    g.tile_rows = kTileQ;
+    g.tiles = (int)((p.pat.n_global + kTileQ - 1) / kTileQ);
+    g.ng_pad = (int)((p.pat.n_global + 31) / 32 * 32);
+    const int64_t units = std::max<int64_t>(1, p.B * p.H * g.tiles);
+    const int64_t want = std::max<int64_t>(1, 600 / units);
+    int64_t len = (p.Skv + want - 1) / want;
+    len = std::max<int64_t>(512, (len + kTileK - 1) / kTileK * kTileK);
+    g.split_len = (int)len;
+    g.n_splits = (int)((p.Skv + len - 1) / len);
+    g.bytes = (size_t)p.B * p.H * g.n_splits * g.ng_pad * kPartialStride * sizeof(float);
+    return g;
+}
+
+int launch_umma_global_rows(const Problem &p, const GlobalRowSplit &g, float *partial) {
+    return p.dtype == MAT_BF16 ? launch_global_rows_t<__nv_bfloat16>(p, g, partial)
+                               : launch_global_rows_t<__half>(p, g, partial);
+}
 
 // Column ids must ascend within each layout row (the merge of the two rows a CTA covers relies
 // on it); the python front end sorts them, C callers are told so in the header.
