@@ -68,6 +68,9 @@ struct FlashParams {
     // (max, sum, unnormalised output) per row in `partial`, merged by merge_global_rows_kernel
     int32_t split_len, n_splits, ng_pad;
     float *partial;  // [B, HH, n_splits, ng_pad, kPartialStride]
+    // MAT_LONGFORMER: the K/V rows at the global positions, gathered once into [B, n_global, HH, 64]
+    // buffers by gather_global_rows_kernel (NULL: every tile gathers them itself, row by row)
+    const void *kg, *vg;
 };
 
 constexpr int kGlobalRows = 3;       // kernel kind beside the MAT_* pattern kinds
@@ -203,6 +206,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     const int n_in = min(TK, P.n_global - e0);
                     const int rows = (n_in + 15) & ~15;
                     for (int i = 0; i < rows; ++i) sG[s * TK + i] = i < n_in ? (int)P.gidx[e0 + i] : kNoKey;
+                    if (P.kg) {   // pre-gathered: one box per tensor; rows past the list are out of bounds = zeros
+                        ptx::mbar_expect_tx(bar_full + s, kStageBytes);
+                        ptx::tma_load_4d(dst, &peer.k_row, bar_full + s, 0, hh, e0, b);
+                        ptx::tma_load_4d(dst + TK * kRowBytes, &peer.v_row, bar_full + s, 0, hh, e0, b);
+                        continue;
+                    }
                     ptx::mbar_expect_tx(bar_full + s, rows * 2 * kRowBytes);
                     for (int i = 0; i < rows; ++i) {
                         const int row = i < n_in ? sG[s * TK + i] : P.Skv1;
@@ -472,6 +481,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
 }
 
+// Copies the K and V rows at the global positions into dense [B, n_global, HH, 64] buffers, once per
+// forward, so that the tiles of the first pass fetch them with one bulk copy each.
+// grid = (global position, batch), threads stride over the HH * 8 16-byte pieces of a row set.
+__global__ void gather_global_rows_kernel(const uint4 *__restrict__ k, const uint4 *__restrict__ v,
+                                          uint4 *__restrict__ kg, uint4 *__restrict__ vg,
+                                          const int64_t *__restrict__ gidx, int n_global, int64_t S, int HH) {
+    const int e = blockIdx.x, b = blockIdx.y;
+    const int64_t src = ((int64_t)b * S + gidx[e]) * HH * 8, dst = ((int64_t)b * n_global + e) * HH * 8;
+    for (int i = threadIdx.x; i < HH * 8; i += blockDim.x) {
+        kg[dst + i] = k[src + i];
+        vg[dst + i] = v[src + i];
+    }
+}
+
 // Combines the per-split partials of the global-row pass and writes the rows at the global
 // positions: out = sum_s w_s * acc_s / sum_s w_s * l_s with w_s = exp2((m_s - max_s m_s) * sl2).
 // grid = (global position, head, batch), 64 threads = one per output column.
@@ -552,7 +575,10 @@ int launch_kind(const Problem &p, const FlashParams &fp, int64_t dil, const char
     }
     pm.q_row = pm.k_row = pm.k_own;
     pm.v_row = pm.v_own;
-    if (KIND == MAT_LONGFORMER || KIND == kGlobalRows) {
+    if (KIND == MAT_LONGFORMER && fp.kg) {
+        if (int rc = make_map(&pm.k_row, fp.kg, p.dtype, HH, fp.n_global, p.B, TK)) return rc;
+        if (int rc = make_map(&pm.v_row, fp.vg, p.dtype, HH, fp.n_global, p.B, TK)) return rc;
+    } else if (KIND == MAT_LONGFORMER || KIND == kGlobalRows) {
         if (int rc = make_map(&pm.q_row, p.q, p.dtype, HH, p.Sq / dil, p.B, 1)) return rc;
         if (int rc = make_map(&pm.k_row, p.k, p.dtype, HH, p.Skv / dil, p.B, 1)) return rc;
         if (int rc = make_map(&pm.v_row, p.v, p.dtype, HH, p.Skv / dil, p.B, 1)) return rc;
@@ -594,6 +620,13 @@ GlobalRowPlan plan_global_rows(const Problem &p) {
     return g;
 }
 
+size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+// workspace layout of a Longformer forward: [partials of the global-row pass][K at globals][V at globals]
+size_t partial_region_bytes(const Problem &p) {
+    return align256(std::max(plan_global_rows(p).bytes, plan_umma_global_rows(p).bytes));
+}
+size_t gathered_region_bytes(const Problem &p) { return align256((size_t)p.B * p.pat.n_global * p.H * kRowBytes); }
+
 bool use_mma_global_rows() {
     const char *force = std::getenv("MAT_GLOBAL_ROWS_KERNEL");
     return force && force[0] == 'm';
@@ -623,6 +656,7 @@ int launch_t(const Problem &p) {
     fp.gidx = nullptr;
     fp.split_len = fp.n_splits = fp.ng_pad = 0;
     fp.partial = nullptr;
+    fp.kg = fp.vg = nullptr;
     if (p.pat.kind == MAT_WINDOW) {
         fp.left = fp.mask_left = (int32_t)std::min<int64_t>(p.pat.left, fp.Skv1 + fp.prev_rows);
         fp.right = fp.mask_right = (int32_t)std::min<int64_t>(p.pat.right, fp.Skv1 + fp.next_rows);
@@ -643,6 +677,19 @@ int launch_t(const Problem &p) {
         fp.right = fp.mask_right = (int32_t)std::min<int64_t>(p.pat.right, fp.Skv1);
         fp.n_global = (int32_t)p.pat.n_global;
         fp.gidx = p.pat.gidx;
+        if (fp.n_global > 0) {
+            // pass 0: the K/V rows at the global positions, gathered once behind the partials
+            const size_t part = partial_region_bytes(p);
+            const size_t gbytes = gathered_region_bytes(p);
+            uint8_t *kg = (uint8_t *)p.workspace + part, *vg = kg + gbytes;
+            gather_global_rows_kernel<<<dim3((unsigned)fp.n_global, (unsigned)p.B), 128, 0, p.stream>>>(
+                (const uint4 *)p.k, (const uint4 *)p.v, (uint4 *)kg, (uint4 *)vg, fp.gidx, fp.n_global, p.Skv,
+                fp.HH);
+            cudaError_t e0 = cudaGetLastError();
+            if (e0 != cudaSuccess) return cuda_fail(e0, "gather_global_rows_kernel launch");
+            fp.kg = kg;
+            fp.vg = vg;
+        }
         // pass 1: every row over its window plus the keys at the global positions
         if (int rc = launch_kind<T, MAT_LONGFORMER, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_longformer")) return rc;
         if (fp.n_global == 0) return MAT_OK;
@@ -713,7 +760,7 @@ bool mma_flash_supports(const Problem &p) {
 
 size_t mma_flash_workspace_bytes(const Problem &p) {
     if (p.pat.kind != MAT_LONGFORMER || p.pat.n_global == 0) return 0;
-    return std::max(plan_global_rows(p).bytes, plan_umma_global_rows(p).bytes);   // either pass-2 kernel fits
+    return partial_region_bytes(p) + 2 * gathered_region_bytes(p);
 }
 
 int launch_mma_flash(const Problem &p) {
@@ -777,6 +824,7 @@ int launch_longformer_static(const Problem &p, float *scratch) {
     fp.gidx = p.pat.gidx;
     fp.split_len = fp.n_splits = fp.ng_pad = 0;
     fp.partial = nullptr;
+    fp.kg = fp.vg = nullptr;   // no workspace here: every tile gathers the global rows itself
     if (int rc = launch_kind<T, MAT_LONGFORMER, TQ, 128, 4, 2, false, 3>(p, fp, 1, "mma_longformer_static")) return rc;
     if (fp.n_global == 0) return MAT_OK;
 
