@@ -403,6 +403,46 @@ def other_workload_arm(args):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     g = torch.Generator().manual_seed(SEED)
+    if args.workload == "orderbook":
+        # cfg-5: the whole order-book transformer forward (library GEMMs around the native attention)
+        from ma_transformer_b200.layers.orderbook_model import OrderBookTransformer, synthetic_ticks
+        Bw, S = 16, 8192
+        torch.manual_seed(SEED)
+        model = OrderBookTransformer().eval().to(dev).to(torch.bfloat16)
+        ticks = synthetic_ticks(Bw, S, seed=SEED)
+        ticks = ((ticks - ticks.mean(dim=(0, 1))) / (ticks.std(dim=(0, 1)) + 1e-6)).to(dev).to(torch.bfloat16)
+        qkv = [torch.randn(Bw, S, 4, 64, generator=g).to(torch.bfloat16).to(dev) for _ in range(3)]
+        out = torch.empty_like(qkv[0])
+
+        def timed(fn, n):
+            for _ in range(args.warmup):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / n
+
+        with torch.no_grad():
+            ms_model = timed(lambda: model(ticks), args.steps)
+            ms_attn = timed(lambda: ext.forward_pattern(*qkv, model.pattern, out=out), args.steps)
+        peak, peak_kind = measured_peak_gbs()
+        attn_bytes = 4 * Bw * S * 4 * 64 * 2
+        print(json.dumps({
+            "metric": "order-book transformer fwd tokens/s (orderbook)", "value": Bw * S / (ms_model * 1e-3),
+            "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_model,
+            "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"ticks [{Bw},{S},40] -> Linear(40,256) -> 4 pre-LN blocks (4 heads x 64, "
+                                   "64 causal taps dilation 2, GELU FFN 1024) -> Linear(256,3), random-init weights"},
+            "attention": {"ms_per_layer": ms_attn, "share_of_forward": 4 * ms_attn / ms_model, "kernel": nat.last_kernel(),
+                          "roofline": {"bound": "hbm", "achieved": attn_bytes / (ms_attn * 1e-3) / 1e9, "peak": peak,
+                                       "unit": "GB/s", "frac": attn_bytes / (ms_attn * 1e-3) / 1e9 / peak,
+                                       "peak_source": f"{peak_kind} HBM copy bandwidth"}},
+            "device_status": nat.device_status()}), flush=True)
+        return
     if args.workload == "block":
         Bw, S, Hw = 4, 16384, 8
         rp, ci = band_random_block_layout(S // 64, 4, 2, seed=SEED)
@@ -448,8 +488,9 @@ def other_workload_arm(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="window", choices=["window", "block", "longformer"],
-                    help="window = the headline configuration; block / longformer = one-GPU timing of cfg-3 / cfg-4")
+    ap.add_argument("--workload", default="window", choices=["window", "block", "longformer", "orderbook"],
+                    help="window = the headline configuration; block / longformer / orderbook = one-GPU timing of "
+                         "the block-sparse, Longformer and order-book-transformer configurations")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)

@@ -1,9 +1,9 @@
 """Regenerates tests/golden/reference_window.npz from the reference itself.
 
-Run in a container that holds the reference tree (default /root/reference) and
+Run in a container that holds the reference tree (``--ref``, or $MAT_REFERENCE_DIR) and
 the compiled reference engine (``make -C oracle`` builds oracle/_ref):
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py --ref <path to the ma-transformer checkout>
 
 For every case the file stores the seeded inputs (once per seed and shape,
 under ``q_<seed>_<B>_<S>_<H>_<D>``) and two outputs of the
@@ -33,7 +33,8 @@ ROOT = HERE.parent.parent
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    import os
+    ap.add_argument("--ref", default=os.environ.get("MAT_REFERENCE_DIR", str(ROOT.parent / "reference")))
     args = ap.parse_args()
     sys.path.insert(0, str(ROOT / "oracle" / "_ref"))
     sys.path.insert(0, args.ref)
