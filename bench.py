@@ -7,8 +7,12 @@ Workload (``config.workload``): the long-sequence causal sliding-window case,
 B=1, N=65536, H=8, d_head=64, 64 taps, bf16, Q/K/V ~ N(0,1)*0.5 from a seed
 (synthetic: the reference benchmarks on torch.randn as well).  One step is one
 forward over the whole sequence.  With N GPUs the sequence is cut into N
-contiguous chunks (strong scaling); each step then includes the 63-row K/V halo
-exchange between neighbours.
+contiguous chunks (strong scaling); the edge tiles of every chunk read the 63
+K/V rows they need from the neighbouring GPU inside the kernel (``--halo nccl``
+exchanges them by send/recv instead).  Steps are independent forwards over
+rotating input sets; they are captured in CUDA graphs and alternate over two
+streams (``--lanes``), each with its own output buffer.
+``--workload block|longformer|orderbook`` time the other configurations on one GPU.
 
 Prints ONE JSON line.  ``value`` is tokens/s with inputs resident in HBM, timed
 with CUDA events over exactly K steps (max over ranks); ``e2e`` is the same

@@ -1,6 +1,12 @@
 """Sequence-sharded forward: one process per GPU, each owning a contiguous chunk
-of the sequence, with the K/V halo rows its windows reach exchanged between
-neighbours by send/recv (NCCL over NVLink on GPUs, gloo on CPU in the tests).
+of the sequence.  Two ways to get the K/V halo rows a chunk's windows reach:
+
+``PeerHaloAttention``         no exchange step: every rank keeps only its own chunk
+                              and the attention kernel's edge tiles read the
+                              neighbour's rows in place over NVLink (the default on GPUs).
+``SequenceShardedAttention``  the halo rows are exchanged between neighbours by
+                              send/recv (NCCL on GPUs, gloo on CPU in the tests)
+                              into an extended K/V buffer.  Described first, below.
 
 The reference has no distributed path at all; this is the one parallel strategy
 the long-sequence configuration needs.  Window patterns only need the
