@@ -283,8 +283,8 @@ def gpu_arm(args):
     barrier()
 
     # Launch-bound at 8 GPUs (a shard's forward is a few microseconds): the steps are captured in
-    # CUDA graphs, one graph that runs one step per input set plus one single-step graph per set
-    # for the remainder, so exactly K steps run and the host issues K / n_sets launches.
+    # CUDA graphs: one graph of about 24 steps (whole passes over the input sets), replayed, plus
+    # one graph with the K mod 24 steps left over, so exactly K steps run.
     use_graph = args.graph and sharded is None
     if use_graph:
         # steps per captured round: whole passes over the input sets, about 24 steps, never more than K
@@ -292,22 +292,23 @@ def gpu_arm(args):
         side = torch.cuda.Stream()
         lanes = [side] + [torch.cuda.Stream() for _ in range(n_lanes - 1)]
         side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            round_graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(round_graph, stream=side):
+        rounds, rest = divmod(args.steps, round_len)
+
+        def capture(n_steps):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
                 for ln in lanes[1:]:
                     ln.wait_stream(side)            # fork
-                for s in range(round_len):
+                for s in range(n_steps):
                     with torch.cuda.stream(lanes[s % n_lanes]):
                         step(s, outs[s % n_lanes])
                 for ln in lanes[1:]:
                     side.wait_stream(ln)            # join
-            single_graphs = []
-            for s in range(min(round_len, args.steps)):
-                g1 = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g1, stream=side):
-                    step(s)
-                single_graphs.append(g1)
+            return graph
+
+        with torch.cuda.stream(side):
+            round_graph = capture(round_len)
+            rest_graph = capture(rest) if rest else None   # the K mod round_len steps left over
         torch.cuda.current_stream().wait_stream(side)
         round_graph.replay()      # one untimed round warms the instantiated graphs
         barrier()
@@ -322,8 +323,8 @@ def gpu_arm(args):
         rounds, rest = divmod(args.steps, round_len)
         for _ in range(rounds):
             round_graph.replay()
-        for s in range(rest):
-            single_graphs[s].replay()
+        if rest_graph is not None:
+            rest_graph.replay()
         launches[0] = args.steps
     else:
         for i in range(args.steps):
