@@ -133,16 +133,18 @@ constexpr size_t flash_smem_bytes() {
 
 constexpr int kNoKey = INT32_MIN;  // marks an unused slot of a gathered chunk
 
-// SINGLE kernels issue all their loads up front, so they carry no producer warp: lane 0 of
-// warp 0 issues the copies and then computes like every other lane.
-template <int TQ, bool SINGLE> constexpr int flash_threads() { return (TQ / 16 + (SINGLE ? 0 : 1)) * 32; }
+// Kernels whose tile needs at most one K/V stage (STAGES == 1, which includes every SINGLE
+// kernel) issue all their loads up front, so they carry no producer warp: lane 0 of warp 0 issues
+// the copies and then computes like every other lane.
+template <int TQ, bool UPFRONT> constexpr int flash_threads() { return (TQ / 16 + (UPFRONT ? 0 : 1)) * 32; }
 
 template <typename T, int KIND, int TQ, int TK, int NP, int STAGES, bool SINGLE, int MINB>
-__global__ void __launch_bounds__(flash_threads<TQ, SINGLE>(), MINB)
+__global__ void __launch_bounds__(flash_threads<TQ, SINGLE || STAGES == 1>(), MINB)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                  const __grid_constant__ PeerMaps peer, const FlashParams P) {
     constexpr int NW = TQ / 16;  // consumer warps
+    constexpr bool UPFRONT = SINGLE || STAGES == 1;  // no producer warp
     constexpr int kStageBytes = 2 * TK * kRowBytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -178,7 +180,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
     const Chunks<KIND, TQ, TK> chunks(P, q0, key_lo, key_hi);
 
-    if (SINGLE ? warp == 0 : warp == NW) {  // ---- producer: one lane feeds the ring ----
+    if (UPFRONT ? warp == 0 : warp == NW) {  // ---- producer: one lane feeds the ring ----
         if (lane == 0) {
             ptx::mbar_expect_tx(bar_q, TQ * kRowBytes);
             if (KIND == kGlobalRows) {
@@ -261,7 +263,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
             }
         }
-        if (!SINGLE) return;
+        if (!UPFRONT) return;
         __syncwarp();
     }
 
@@ -571,7 +573,9 @@ int make_map(CUtensorMap *m, const void *base, int dtype, int64_t HH, int64_t S1
 }
 
 template <typename T, int KIND, int TQ, int TK, int NP, int STAGES, bool SINGLE, int MINB>
-int launch_kind(const Problem &p, const FlashParams &fp, int64_t dil, const char *name, int64_t grid_y = -1) {
+int launch_kind(const Problem &p, const FlashParams &fp_in, int64_t dil, const char *name, int64_t grid_y = -1) {
+    FlashParams fp = fp_in;
+    fp.n_tiles = (fp.Sq1 + TQ - 1) / TQ;   // query tiles of this instantiation's height
     CUtensorMap mq, mk, mv, mo;
     const int64_t HH = fp.HH;
     if (int rc = make_map(&mq, p.q, p.dtype, HH, p.Sq / dil, p.B, TQ)) return rc;
@@ -610,7 +614,7 @@ int launch_kind(const Problem &p, const FlashParams &fp, int64_t dil, const char
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(flash_fwd_kernel)");
     const dim3 grid((unsigned)HH, (unsigned)(grid_y >= 0 ? grid_y : fp.n_tiles), (unsigned)p.B);
-    kern<<<grid, flash_threads<TQ, SINGLE>(), smem, p.stream>>>(mq, mk, mv, mo, pm, fp);
+    kern<<<grid, flash_threads<TQ, SINGLE || STAGES == 1>(), smem, p.stream>>>(mq, mk, mv, mo, pm, fp);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "flash_fwd_kernel launch");
     note_kernel(name);
@@ -706,6 +710,11 @@ int launch_t(const Problem &p) {
             return launch_kind<T, MAT_WINDOW, TQ, TQ + 64, 3, 1, true, 5>(p, fp, dil, "mma_window");
         if (fp.left + slack + fp.right <= 64 && pairs <= 5)
             return launch_kind<T, MAT_WINDOW, TQ, TQ + 64, 5, 1, true, 5>(p, fp, dil, "mma_window");
+        // up to 128 keys of reach (the reference's default window of +-64): 128-row tiles whose
+        // 256-key window is still one stage, two softmax steps per warp, no producer warp
+        // (102 us against 125 us on the ring path at the 64K-token shape)
+        if (fp.left + slack + fp.right <= 128 && (p.Sq / dil + 127) / 128 <= 65535)
+            return launch_kind<T, MAT_WINDOW, 128, 256, 5, 1, false, 2>(p, fp, dil, "mma_window");
         return launch_kind<T, MAT_WINDOW, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_window");
     }
     if (p.pat.kind == MAT_LONGFORMER) {
