@@ -124,11 +124,14 @@ struct PeerMaps {
     CUtensorMap k_own, v_own, k_prev, v_prev, k_next, v_next, q_row, k_row, v_row;
 };
 
-template <int TQ, int TK, int STAGES>
+constexpr int kSideRows = 64;  // one-stage Longformer kernel: rows of the side region for the gathered keys
+
+template <int TQ, int TK, int STAGES, bool SIDE = false>
 constexpr size_t flash_smem_bytes() {
-    // Q tile, K/V stages, barriers, then per stage the global positions of a gathered chunk
-    return 1024 + (size_t)TQ * kRowBytes + (size_t)STAGES * 2 * TK * kRowBytes + 8 * (1 + 2 * STAGES) +
-           8 + (size_t)STAGES * TK * 4;
+    // Q tile, K/V stages, [side region for gathered keys], barriers, then per stage the global
+    // positions of a gathered chunk
+    return 1024 + (size_t)TQ * kRowBytes + (size_t)STAGES * 2 * TK * kRowBytes +
+           (SIDE ? 2 * kSideRows * kRowBytes : 0) + 8 * (1 + 2 * STAGES) + 8 + (size_t)STAGES * TK * 4;
 }
 
 constexpr int kNoKey = INT32_MIN;  // marks an unused slot of a gathered chunk
@@ -145,14 +148,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                  const __grid_constant__ PeerMaps peer, const FlashParams P) {
     constexpr int NW = TQ / 16;  // consumer warps
     constexpr bool UPFRONT = SINGLE || STAGES == 1;  // no producer warp
+    // Longformer with one stage: the window is the stage, the gathered keys (at most kSideRows of
+    // them, pre-gathered by the host side) sit in a side region with a barrier of their own
+    constexpr bool SIDE = KIND == MAT_LONGFORMER && STAGES == 1;
     constexpr int kStageBytes = 2 * TK * kRowBytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *sQ = smem;
     uint8_t *sKV = smem + TQ * kRowBytes;
-    uint64_t *bar_q = (uint64_t *)(sKV + STAGES * kStageBytes);
+    uint8_t *sSide = sKV + STAGES * kStageBytes;
+    uint64_t *bar_q = (uint64_t *)(sSide + (SIDE ? 2 * kSideRows * kRowBytes : 0));
     uint64_t *bar_full = bar_q + 1;
     uint64_t *bar_empty = bar_full + STAGES;
+    uint64_t *bar_side = bar_empty + STAGES;            // completion of the side region's copies
     int32_t *sG = (int32_t *)(bar_empty + STAGES + 1);  // [STAGES][TK] positions of gathered keys
 
     const int warp = threadIdx.x >> 5;
@@ -174,6 +182,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             ptx::mbar_init(bar_full + s, 1);
             ptx::mbar_init(bar_empty + s, NW);
         }
+        ptx::mbar_init(bar_side, 1);
         ptx::fence_barrier_init();
     }
     __syncthreads();
@@ -196,6 +205,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
             for (int c = 0; c < chunks.n; ++c) {
                 const int s = c % STAGES, use = c / STAGES;
+                if (SIDE && c >= chunks.n_seq) {
+                    // the (single) gathered chunk goes to the side region
+                    const int n_in = min(kSideRows, P.n_global);
+                    for (int i = 0; i < kSideRows; ++i) sG[i] = i < n_in ? (int)P.gidx[i] : kNoKey;
+                    ptx::mbar_expect_tx(bar_side, 2 * kSideRows * kRowBytes);
+                    ptx::tma_load_4d(sSide, &peer.k_row, bar_side, 0, hh, 0, b);
+                    ptx::tma_load_4d(sSide + kSideRows * kRowBytes, &peer.v_row, bar_side, 0, hh, 0, b);
+                    continue;
+                }
                 if (use > 0 && !ptx::mbar_wait(bar_empty + s, (use - 1) & 1)) {
                     atomicExch(&g_flash_status, kStatusWaitTimeout);
                     break;
@@ -297,15 +315,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     float lsum[4] = {0.f, 0.f, 0.f, 0.f};  // P * ones: [0] = row g, [2] = row g + 8 (every column alike)
 
     for (int c = 0; c < chunks.n; ++c) {
-        const int s = c % STAGES, use = c / STAGES;
-        if (!ptx::mbar_wait(bar_full + s, use & 1)) {
+        const bool gathered = KIND == MAT_LONGFORMER && c >= chunks.n_seq;  // keys at global positions
+        const bool side = SIDE && gathered;
+        const int s = side ? 0 : c % STAGES, use = side ? 0 : c / STAGES;
+        if (!ptx::mbar_wait(side ? bar_side : bar_full + s, use & 1)) {
             atomicExch(&g_flash_status, kStatusWaitTimeout);
             return;
         }
-        const bool gathered = KIND == MAT_LONGFORMER && c >= chunks.n_seq;  // keys at global positions
         const int kb = chunks.base(P, c);
-        const uint32_t k_base = ptx::smem_u32(sKV + s * kStageBytes);
-        const uint32_t v_base = k_base + TK * kRowBytes;
+        const uint32_t k_base = ptx::smem_u32(side ? sSide : sKV + s * kStageBytes);
+        const uint32_t v_base = k_base + (side ? kSideRows : TK) * kRowBytes;
         // pairs of this chunk that intersect [k_lo, k_hi]
         int first = max(0, (k_lo - kb) >> 4);  // k_lo - kb may be negative: >> floors
         int last = k_hi >= kb ? min(TK / 16 - 1, (k_hi - kb) >> 4) : -1;
@@ -450,7 +469,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
         }
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar_empty + s);
+        if (lane == 0 && !side) ptx::mbar_arrive(bar_empty + s);
     }
 
     if (KIND == kGlobalRows) {
@@ -597,16 +616,17 @@ int launch_kind(const Problem &p, const FlashParams &fp_in, int64_t dil, const c
     }
     pm.q_row = pm.k_row = pm.k_own;
     pm.v_row = pm.v_own;
+    constexpr bool SIDE = KIND == MAT_LONGFORMER && STAGES == 1;
     if (KIND == MAT_LONGFORMER && fp.kg) {
-        if (int rc = make_map(&pm.k_row, fp.kg, p.dtype, HH, fp.n_global, p.B, TK)) return rc;
-        if (int rc = make_map(&pm.v_row, fp.vg, p.dtype, HH, fp.n_global, p.B, TK)) return rc;
+        if (int rc = make_map(&pm.k_row, fp.kg, p.dtype, HH, fp.n_global, p.B, SIDE ? kSideRows : TK)) return rc;
+        if (int rc = make_map(&pm.v_row, fp.vg, p.dtype, HH, fp.n_global, p.B, SIDE ? kSideRows : TK)) return rc;
     } else if (KIND == MAT_LONGFORMER || KIND == kGlobalRows) {
         if (int rc = make_map(&pm.q_row, p.q, p.dtype, HH, p.Sq / dil, p.B, 1)) return rc;
         if (int rc = make_map(&pm.k_row, p.k, p.dtype, HH, p.Skv / dil, p.B, 1)) return rc;
         if (int rc = make_map(&pm.v_row, p.v, p.dtype, HH, p.Skv / dil, p.B, 1)) return rc;
     }
     auto kern = flash_fwd_kernel<T, KIND, TQ, TK, NP, STAGES, SINGLE, MINB>;
-    constexpr size_t smem = flash_smem_bytes<TQ, TK, STAGES>();
+    constexpr size_t smem = flash_smem_bytes<TQ, TK, STAGES, KIND == MAT_LONGFORMER && STAGES == 1>();
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [&] {
@@ -735,8 +755,15 @@ int launch_t(const Problem &p) {
             fp.kg = kg;
             fp.vg = vg;
         }
-        // pass 1: every row over its window plus the keys at the global positions
-        if (int rc = launch_kind<T, MAT_LONGFORMER, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_longformer")) return rc;
+        // pass 1: every row over its window plus the keys at the global positions.  Windows that
+        // reach at most 128 keys with at most 64 global positions (the +-64 / 32-token configuration):
+        // 128-row tiles, the whole window in one stage, the gathered keys in a side region, no
+        // producer warp; otherwise the ring of stages
+        const bool one_stage = fp.left + ((16 - fp.left % 16) % 16) + fp.right <= 128 && fp.n_global <= kSideRows &&
+                               (fp.n_global == 0 || fp.kg) && (fp.Sq1 + 127) / 128 <= 65535;
+        if (one_stage) {
+            if (int rc = launch_kind<T, MAT_LONGFORMER, 128, 256, 5, 1, false, 2>(p, fp, dil, "mma_longformer")) return rc;
+        } else if (int rc = launch_kind<T, MAT_LONGFORMER, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_longformer")) return rc;
         if (fp.n_global == 0) return MAT_OK;
         // pass 2: the rows AT the global positions over every key, split along the key axis:
         // on tcgen05 (128 gathered rows per CTA) unless MAT_GLOBAL_ROWS_KERNEL=mma asks for the
