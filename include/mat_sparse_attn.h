@@ -172,6 +172,42 @@ int mat_sparse_attn_fwd_longformer_noalloc(const void *q, const void *k, const v
                                            const mat_pattern_spec *spec, float scale, void *stream);
 
 /*
+ * Longformer over a sequence spread across GPUs (one shard [B, S, H, 64] per process): three
+ * building blocks around two small collectives the caller runs (all-gather of the Q/K/V rows at
+ * the global positions, all-gather of the partials).  No counterpart in the reference, whose
+ * LongformerAttention (src/csrc/sparse_attention.cpp:234-259) is single-process.
+ *   mat_longformer_shard_fwd       pass 1 of a shard: every local row over its window (halo rows
+ *                                  read in place from the neighbour shards, as in
+ *                                  mat_sparse_attn_fwd_sharded) plus the keys at ALL global
+ *                                  positions (kg, vg: [B, n_global, H, 64]).  g_pos[e] = position of
+ *                                  global token e relative to this shard's first row (device
+ *                                  array, ascending; negative or >= S for other shards' tokens).
+ *   mat_global_rows_partial        (max, sum, unnormalised output) of the global queries
+ *                                  qg [B, n_global, H, 64] against this shard's keys, per key
+ *                                  split; layout and size from mat_global_rows_partial_layout.
+ *   mat_global_rows_merge          merges n_parts such buffers (one per shard,
+ *                                  part_stride_floats apart) for the global tokens
+ *                                  [e_first, e_first + n_rows) this shard owns and writes their
+ *                                  rows of o.
+ * 16-bit dtypes, D = 64.
+ */
+int mat_longformer_shard_fwd(const void *q, const void *k, const void *v, void *o,
+                             const void *k_prev, const void *v_prev, int64_t S_prev,
+                             const void *k_next, const void *v_next, int64_t S_next,
+                             const void *kg, const void *vg, const int64_t *g_pos, int64_t n_global,
+                             int64_t B, int64_t S, int64_t H, int64_t D, int dtype,
+                             int64_t left, int64_t right, float scale, void *stream);
+size_t mat_global_rows_partial_layout(int64_t B, int64_t n_global, int64_t S_kv, int64_t H,
+                                      int32_t *n_splits_out, int32_t *ng_pad_out);
+int mat_global_rows_partial(const void *qg, const void *k, const void *v, void *partial,
+                            int64_t B, int64_t n_global, int64_t S_kv, int64_t H, int64_t D,
+                            int dtype, float scale, void *stream);
+int mat_global_rows_merge(const void *partials, int64_t n_parts, int64_t part_stride_floats, void *o,
+                          const int64_t *g_pos, int64_t e_first, int64_t n_rows, int64_t B, int64_t S,
+                          int64_t H, int32_t n_splits, int32_t ng_pad, int dtype, float scale,
+                          void *stream);
+
+/*
  * Lets kernels running on `device` read memory that lives on `peer_device`
  * (cudaDeviceEnablePeerAccess; already-enabled is not an error).  Call once per
  * neighbour before mat_sparse_attn_fwd_sharded.  No counterpart in the reference.

@@ -22,6 +22,7 @@ EXPORTS = (
     "mat_pattern_rowset", "mat_pattern_nnz", "mat_enable_peer_access",
     "mat_ipc_export", "mat_ipc_open", "mat_ipc_close", "mat_sparse_attn_fwd_longformer_noalloc",
     "mat_sparse_attn_bwd", "mat_sparse_attn_bwd_workspace_bytes",
+    "mat_longformer_shard_fwd", "mat_global_rows_partial_layout", "mat_global_rows_partial", "mat_global_rows_merge",
 )
 
 
@@ -72,6 +73,16 @@ def _load() -> C.CDLL:
     lib.mat_sparse_attn_bwd.argtypes = [vp] * 7 + [i64, i64, i64, i64, C.c_int, spec_p, C.c_float, vp, sz, vp]
     lib.mat_sparse_attn_bwd_workspace_bytes.restype = sz
     lib.mat_sparse_attn_bwd_workspace_bytes.argtypes = [i64, i64, i64]
+    lib.mat_longformer_shard_fwd.restype = C.c_int
+    lib.mat_longformer_shard_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i64, vp, vp, i64, vp, vp, vp, i64,
+                                             i64, i64, i64, i64, C.c_int, i64, i64, C.c_float, vp]
+    lib.mat_global_rows_partial_layout.restype = sz
+    lib.mat_global_rows_partial_layout.argtypes = [i64, i64, i64, i64, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
+    lib.mat_global_rows_partial.restype = C.c_int
+    lib.mat_global_rows_partial.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, C.c_int, C.c_float, vp]
+    lib.mat_global_rows_merge.restype = C.c_int
+    lib.mat_global_rows_merge.argtypes = [vp, i64, i64, vp, vp, i64, i64, i64, i64, i64, C.c_int32, C.c_int32,
+                                          C.c_int, C.c_float, vp]
     lib.mat_enable_peer_access.restype = C.c_int
     lib.mat_enable_peer_access.argtypes = [C.c_int, C.c_int]
     lib.mat_ipc_export.restype = C.c_int

@@ -38,6 +38,8 @@ struct Problem {
     // neighbouring sequence shards read in place (peer memory); NULL when absent
     const void *k_prev = nullptr, *v_prev = nullptr, *k_next = nullptr, *v_next = nullptr;
     int64_t S_prev = 0, S_next = 0;
+    // Longformer shard of a sequence spread over GPUs: K/V rows at all global positions, gathered by the caller
+    const void *shard_kg = nullptr, *shard_vg = nullptr;
 };
 
 // error plumbing (api.cu)

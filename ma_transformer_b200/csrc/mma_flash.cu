@@ -534,26 +534,31 @@ __global__ void gather_global_rows_kernel(const uint4 *__restrict__ k, const uin
     }
 }
 
-// Combines the per-split partials of the global-row pass and writes the rows at the global
-// positions: out = sum_s w_s * acc_s / sum_s w_s * l_s with w_s = exp2((m_s - max_s m_s) * sl2).
-// grid = (global position, head, batch), 64 threads = one per output column.
+// Combines the partials of the global-row pass and writes the rows at the global positions:
+// out = sum w * acc / sum w * l with w = exp2((m - max m) * sl2), over n_outer groups (one per
+// sequence shard when the key axis is spread over GPUs, else 1) of n_splits partials each.
+// grid = (global position index - e_first, head, batch), 64 threads = one per output column;
+// gidx[e] is the output row of global position e.
 template <typename T>
 __global__ void __launch_bounds__(64)
 merge_global_rows_kernel(const float *__restrict__ partial, T *__restrict__ out, const int64_t *__restrict__ gidx,
-                         int n_splits, int ng_pad, int HH, int64_t Sq1, float sl2) {
-    const int e = blockIdx.x, hh = blockIdx.y, b = blockIdx.z, d = threadIdx.x;
+                         int n_splits, int ng_pad, int HH, int64_t Sq1, float sl2, int n_outer,
+                         int64_t outer_stride, int e_first) {
+    const int e = e_first + blockIdx.x, hh = blockIdx.y, b = blockIdx.z, d = threadIdx.x;
     const float *base = partial + (((int64_t)b * HH + hh) * n_splits * ng_pad + e) * kPartialStride;
     const int64_t split_stride = (int64_t)ng_pad * kPartialStride;
     float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, base[s * split_stride]);
+    for (int g = 0; g < n_outer; ++g)
+        for (int s = 0; s < n_splits; ++s) m = fmaxf(m, base[g * outer_stride + s * split_stride]);
     float l = 0.f, acc = 0.f;
     if (m != -INFINITY)
-        for (int s = 0; s < n_splits; ++s) {
-            const float *pr = base + s * split_stride;
-            const float w = ptx::ex2((pr[0] - m) * sl2);
-            l = fmaf(w, pr[1], l);
-            acc = fmaf(w, pr[2 + d], acc);
-        }
+        for (int g = 0; g < n_outer; ++g)
+            for (int s = 0; s < n_splits; ++s) {
+                const float *pr = base + g * outer_stride + s * split_stride;
+                const float w = ptx::ex2((pr[0] - m) * sl2);
+                l = fmaf(w, pr[1], l);
+                acc = fmaf(w, pr[2 + d], acc);
+            }
     const int64_t row = gidx[e];
     out[((b * Sq1 + row) * HH + hh) * 64 + d] = Elem<T>::from_f(l > 0.f ? acc / l : 0.f);
 }
@@ -738,11 +743,17 @@ int launch_t(const Problem &p) {
         return launch_kind<T, MAT_WINDOW, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_window");
     }
     if (p.pat.kind == MAT_LONGFORMER) {
-        fp.left = fp.mask_left = (int32_t)std::min<int64_t>(p.pat.left, fp.Skv1);
-        fp.right = fp.mask_right = (int32_t)std::min<int64_t>(p.pat.right, fp.Skv1);
+        fp.left = fp.mask_left = (int32_t)std::min<int64_t>(p.pat.left, fp.Skv1 + fp.prev_rows);
+        fp.right = fp.mask_right = (int32_t)std::min<int64_t>(p.pat.right, fp.Skv1 + fp.next_rows);
         fp.n_global = (int32_t)p.pat.n_global;
         fp.gidx = p.pat.gidx;
-        if (fp.n_global > 0) {
+        if (p.shard_kg) {
+            // one shard of a sequence spread over GPUs: the caller gathered the K/V rows at ALL global
+            // positions (gidx holds their positions relative to this shard's first row); only the first
+            // pass runs here, the rows at global positions are finished by the partial / merge calls
+            fp.kg = p.shard_kg;
+            fp.vg = p.shard_vg;
+        } else if (fp.n_global > 0) {
             // pass 0: the K/V rows at the global positions, gathered once behind the partials
             const size_t part = partial_region_bytes(p);
             const size_t gbytes = gathered_region_bytes(p);
@@ -764,7 +775,7 @@ int launch_t(const Problem &p) {
         if (one_stage) {
             if (int rc = launch_kind<T, MAT_LONGFORMER, 128, 256, 5, 1, false, 2>(p, fp, dil, "mma_longformer")) return rc;
         } else if (int rc = launch_kind<T, MAT_LONGFORMER, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_longformer")) return rc;
-        if (fp.n_global == 0) return MAT_OK;
+        if (fp.n_global == 0 || p.shard_kg) return MAT_OK;
         // pass 2: the rows AT the global positions over every key, split along the key axis:
         // on tcgen05 (128 gathered rows per CTA) unless MAT_GLOBAL_ROWS_KERNEL=mma asks for the
         // warp-level kernel (debugging aid)
@@ -773,7 +784,7 @@ int launch_t(const Problem &p) {
             if (int rc = launch_umma_global_rows(p, u, (float *)p.workspace)) return rc;
             const dim3 grid_m((unsigned)fp.n_global, (unsigned)fp.HH, (unsigned)p.B);
             merge_global_rows_kernel<T><<<grid_m, 64, 0, p.stream>>>((const float *)p.workspace, (T *)p.o, fp.gidx,
-                                                                    u.n_splits, u.ng_pad, fp.HH, fp.Sq1, fp.sl2);
+                                                                    u.n_splits, u.ng_pad, fp.HH, fp.Sq1, fp.sl2, 1, 0, 0);
             cudaError_t e2 = cudaGetLastError();
             return e2 == cudaSuccess ? MAT_OK : cuda_fail(e2, "merge_global_rows_kernel launch");
         }
@@ -790,7 +801,7 @@ int launch_t(const Problem &p) {
         // pass 3: merge the splits and overwrite those rows of the output
         const dim3 grid((unsigned)fp.n_global, (unsigned)fp.HH, (unsigned)p.B);
         merge_global_rows_kernel<T><<<grid, 64, 0, p.stream>>>(fp.partial, (T *)p.o, fp.gidx, fp.n_splits,
-                                                              fp.ng_pad, fp.HH, fp.Sq1, fp.sl2);
+                                                              fp.ng_pad, fp.HH, fp.Sq1, fp.sl2, 1, 0, 0);
         cudaError_t e = cudaGetLastError();
         return e == cudaSuccess ? MAT_OK : cuda_fail(e, "merge_global_rows_kernel launch");
     }
@@ -923,7 +934,7 @@ int launch_longformer_static(const Problem &p, float *scratch) {
         return rc;
     const dim3 grid((unsigned)fp.n_global, (unsigned)fp.HH, (unsigned)p.B);
     merge_global_rows_kernel<T><<<grid, 64, 0, p.stream>>>(fp.partial, (T *)p.o, fp.gidx, fp.n_splits, fp.ng_pad,
-                                                          fp.HH, fp.Sq1, fp.sl2);
+                                                          fp.HH, fp.Sq1, fp.sl2, 1, 0, 0);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? MAT_OK : cuda_fail(e, "merge_global_rows_kernel launch");
 }
@@ -959,4 +970,106 @@ extern "C" int mat_sparse_attn_fwd_longformer_noalloc(const void *q, const void 
     mat::Problem p;
     if (int rc = mat::make_problem(p, q, k, v, o, B, S, S, H, D, dtype, spec, scale, nullptr, 0, stream)) return rc;
     return mat::launch_longformer_noalloc(p);
+}
+
+// ---- Longformer over a sequence spread across GPUs: the three building blocks ----------------------
+
+// Pass 1 of one shard: every local row over its window (halo rows read in place from the neighbour
+// shards) plus the keys at all global positions (kg / vg: [B, n_global, H, 64], gathered by the
+// caller across the shards).  g_pos: device array, position of each global token relative to this
+// shard's first row (negative / beyond S for tokens owned by other shards).
+extern "C" int mat_longformer_shard_fwd(const void *q, const void *k, const void *v, void *o, const void *k_prev,
+                                        const void *v_prev, int64_t S_prev, const void *k_next,
+                                        const void *v_next, int64_t S_next, const void *kg, const void *vg,
+                                        const int64_t *g_pos, int64_t n_global, int64_t B, int64_t S, int64_t H,
+                                        int64_t D, int dtype, int64_t left, int64_t right, float scale,
+                                        void *stream) {
+    using namespace mat;
+    mat_pattern_spec spec = {};
+    spec.kind = MAT_LONGFORMER;
+    spec.left = left;
+    spec.right = right;
+    spec.dilation = 1;
+    spec.n_global = n_global;
+    spec.global_idx = g_pos;
+    Problem p;
+    if (int rc = make_problem(p, q, k, v, o, B, S, S, H, D, dtype, &spec, scale, nullptr, 0, stream)) return rc;
+    if (n_global > 0 && (!kg || !vg || !g_pos)) return fail(MAT_ERR_INVALID, "gathered global rows missing");
+    if (!mma_flash_supports(p))
+        return fail(MAT_ERR_UNSUPPORTED, "the sharded Longformer pass needs 16-bit inputs and head width 64");
+    if ((k_prev == nullptr) != (v_prev == nullptr) || (k_next == nullptr) != (v_next == nullptr))
+        return fail(MAT_ERR_INVALID, "a neighbour needs both its K and its V");
+    if (k_prev && (S_prev % 16 || left > S_prev)) return fail(MAT_ERR_INVALID, "S_prev must be a multiple of 16 covering the window");
+    if (k_next && (S % 16 || right > S_next)) return fail(MAT_ERR_INVALID, "S must be a multiple of 16 and S_next cover the window");
+    p.k_prev = k_prev; p.v_prev = v_prev; p.S_prev = k_prev ? S_prev : 0;
+    p.k_next = k_next; p.v_next = v_next; p.S_next = k_next ? S_next : 0;
+    p.shard_kg = n_global > 0 ? kg : nullptr;   // without global tokens only the window pass exists anyway
+    p.shard_vg = n_global > 0 ? vg : nullptr;
+    return launch_mma_flash(p);
+}
+
+// Partials of the global queries qg [B, n_global, H, 64] against one shard's keys k, v [B, S_kv, H, 64]:
+// per key split and row (max, sum, unnormalised output).  The layout is reported by
+// mat_global_rows_partial_layout; partial must hold that many bytes.
+extern "C" size_t mat_global_rows_partial_layout(int64_t B, int64_t n_global, int64_t S_kv, int64_t H,
+                                                 int32_t *n_splits_out, int32_t *ng_pad_out) {
+    using namespace mat;
+    Problem p;
+    p.B = B; p.Sq = n_global; p.Skv = S_kv; p.H = H; p.D = 64;
+    p.pat = DevPattern{};
+    p.pat.n_global = n_global;
+    const GlobalRowSplit g = plan_umma_global_rows(p);
+    if (n_splits_out) *n_splits_out = g.n_splits;
+    if (ng_pad_out) *ng_pad_out = g.ng_pad;
+    return g.bytes;
+}
+
+extern "C" int mat_global_rows_partial(const void *qg, const void *k, const void *v, void *partial, int64_t B,
+                                       int64_t n_global, int64_t S_kv, int64_t H, int64_t D, int dtype,
+                                       float scale, void *stream) {
+    using namespace mat;
+    if (D != 64 || (dtype != MAT_BF16 && dtype != MAT_F16))
+        return fail(MAT_ERR_UNSUPPORTED, "the global-row pass needs 16-bit inputs and head width 64");
+    if (!qg || !k || !v || !partial || B <= 0 || n_global <= 0 || S_kv <= 0 || H <= 0)
+        return fail(MAT_ERR_INVALID, "bad argument");
+    Problem p;
+    p.q = qg; p.k = k; p.v = v; p.o = nullptr;
+    p.B = B; p.Sq = n_global; p.Skv = S_kv; p.H = H; p.D = D;
+    p.dtype = dtype;
+    p.scale = scale > 0.f ? scale : 0.125f;
+    p.pat = DevPattern{};
+    p.pat.kind = MAT_LONGFORMER;
+    p.pat.n_global = n_global;
+    p.pat.gidx = nullptr;   // the queries are already gathered: row e of qg is global token e
+    p.workspace = nullptr; p.workspace_bytes = 0;
+    p.stream = (cudaStream_t)stream;
+    return launch_umma_global_rows(p, plan_umma_global_rows(p), (float *)partial);
+}
+
+// Merges n_parts partial buffers (one per shard, part_stride_floats apart) for the global tokens
+// [e_first, e_first + n_rows) and writes their rows of o [B, S, H, 64] at g_pos[e] (positions
+// relative to this shard: the caller passes the range of tokens the shard owns).
+extern "C" int mat_global_rows_merge(const void *partials, int64_t n_parts, int64_t part_stride_floats, void *o,
+                                     const int64_t *g_pos, int64_t e_first, int64_t n_rows, int64_t B, int64_t S,
+                                     int64_t H, int32_t n_splits, int32_t ng_pad, int dtype, float scale,
+                                     void *stream) {
+    using namespace mat;
+    if (n_rows <= 0) return MAT_OK;
+    if (!partials || !o || !g_pos || n_parts <= 0 || B <= 0 || H <= 0 || H > 65535 || B > 65535)
+        return fail(MAT_ERR_INVALID, "bad argument");
+    const float sl2 = (scale > 0.f ? scale : 0.125f) * 1.4426950408889634f;
+    const dim3 grid((unsigned)n_rows, (unsigned)H, (unsigned)B);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == MAT_BF16)
+        merge_global_rows_kernel<__nv_bfloat16><<<grid, 64, 0, st>>>((const float *)partials, (__nv_bfloat16 *)o, g_pos,
+                                                                   n_splits, ng_pad, (int)H, S, sl2, (int)n_parts,
+                                                                   part_stride_floats, (int)e_first);
+    else if (dtype == MAT_F16)
+        merge_global_rows_kernel<__half><<<grid, 64, 0, st>>>((const float *)partials, (__half *)o, g_pos, n_splits,
+                                                            ng_pad, (int)H, S, sl2, (int)n_parts, part_stride_floats,
+                                                            (int)e_first);
+    else
+        return fail(MAT_ERR_UNSUPPORTED, "16-bit outputs only");
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? MAT_OK : cuda_fail(e, "merge_global_rows_kernel launch");
 }

@@ -265,7 +265,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 // gidx[q0 + r]; slots past the list read out of bounds, i.e. zeros
                 for (int r = 0; r < kTileQ; ++r) {
                     const int e = q0 + r;
-                    const int row = e < P.n_global ? (int)P.gidx[e] : P.Sq;
+                    const int row = e < P.n_global ? (P.gidx ? (int)P.gidx[e] : e) : P.Sq;   // no list: already gathered
                     ptx::tma_load_4d(sQ + r * kRowBytes, &map_q, bar_q, 0, h, row, b);
                 }
             } else {

@@ -461,3 +461,34 @@ def test_random_windows_and_offsets_fuzz():
         got = run(spec, q, k, v)
         assert nat.last_kernel() == "mma_window", (left, right, dil, Sq, off, tail)
         check_close(got, oracle_out(q, k, v, spec), torch.bfloat16)
+
+
+def test_longformer_over_sequence_shards_building_blocks():
+    """Longformer with the sequence cut into 4 shards, emulated on one GPU: the per-shard window +
+    global-key pass (halo rows read from the neighbour shards' tensors), the partials of all global
+    queries over each shard's keys, and the merge by the shard that owns a token; the two
+    all-gathers are a torch.cat here.  Must equal the unsharded oracle."""
+    from ma_transformer_b200 import longformer_sharded as ls
+    g = torch.Generator().manual_seed(5)
+    S, P, H = 2048, 4, 3
+    glob = torch.randperm(S, generator=g)[:20].sort().values
+    spec = PatternSpec.longformer(40, 24, glob.numpy())
+    q, k, v = seeded_qkv(91, 2, S, H, 64, torch.bfloat16)
+    want = oracle_out(q, k, v, spec)
+    rows = S // P
+    qd, kd, vd = (t.to(DEV) for t in (q, k, v))
+    chunks = [tuple(t[:, r * rows:(r + 1) * rows].contiguous() for t in (qd, kd, vd)) for r in range(P)]
+    gd = glob.to(DEV)
+    qg, kg, vg = (t[:, gd].contiguous() for t in (qd, kd, vd))                      # collective 1
+    partials = torch.stack([ls.global_rows_partial(qg, c[1], c[2]) for c in chunks])    # collective 2
+    for r in range(P):
+        cq, ck, cv = chunks[r]
+        g_pos = (gd - r * rows).contiguous()
+        out = ls.shard_pass1(cq, ck, cv, 40, 24, kg, vg, g_pos,
+                             chunks[r - 1][1:] if r > 0 else None, chunks[r + 1][1:] if r < P - 1 else None)
+        own = ((glob >= r * rows) & (glob < (r + 1) * rows)).nonzero().flatten()
+        if len(own):
+            ls.global_rows_merge(partials, out, g_pos, int(own[0]), len(own))
+        torch.cuda.synchronize()
+        check_close(out, want[:, r * rows:(r + 1) * rows], torch.bfloat16)
+    assert nat.device_status() == 0
