@@ -101,6 +101,7 @@ int make_problem(Problem &p, const void *q, const void *k, const void *v, void *
 
 int run_problem(const Problem &p) {
     if (umma_block_supports(p)) return launch_umma_block(p);
+    if (umma_dense_supports(p)) return launch_umma_dense(p);
     if (mma_flash_supports(p)) {
         const size_t need = mma_flash_workspace_bytes(p);
         if (need > 0) {

@@ -60,6 +60,8 @@ size_t mma_flash_workspace_bytes(const Problem &p);
 int flash_status_read_and_clear(int *out);   // status word left by a kernel whose bounded wait ran out
 bool umma_block_supports(const Problem &p);  // umma_block.cu: block layouts on tcgen05 / TMEM
 int launch_umma_block(const Problem &p);
+bool umma_dense_supports(const Problem &p);  // dense / causal dense on the same tcgen05 pipeline
+int launch_umma_dense(const Problem &p);
 int umma_status_read_and_clear(int *out);
 // Longformer global-row pass on tcgen05 (umma_block.cu): how the key axis is split, and the launch
 constexpr int kPartialStride = 66;   // floats per row of a partial: max, sum, 64 outputs

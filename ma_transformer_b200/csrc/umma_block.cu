@@ -63,7 +63,7 @@ struct UmmaParams {
     float *partial;   // [B, H, n_splits, ng_pad, kPartialStride]: max, sum, unnormalised output
 };
 
-constexpr int kModeBlock = 0, kModeGlobalRows = 1;
+constexpr int kModeBlock = 0, kModeGlobalRows = 1, kModeDense = 2;   // kModeDense: every key (up to the query when causal)
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols) {
@@ -227,8 +227,11 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     // global-row pass: blockIdx.y = (128-row tile of the global-position list) * n_splits + key split
     const int split = MODE == kModeGlobalRows ? blockIdx.y % P.n_splits : 0;
     const int q0 = (MODE == kModeGlobalRows ? blockIdx.y / P.n_splits : blockIdx.y) * kTileQ;
-    const int range_lo = split * P.split_len;
-    const int range_hi = min(range_lo + P.split_len, P.Skv);
+    // key range of the tile: a split of the sequence (global rows), or everything / everything up to
+    // the tile's last row (dense and causal dense)
+    const int range_lo = MODE == kModeGlobalRows ? split * P.split_len : 0;
+    const int range_hi = MODE == kModeGlobalRows ? min(range_lo + P.split_len, P.Skv)
+                       : (P.causal ? min(P.Skv, q0 + P.off + kTileQ) : P.Skv);
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(bar_q, 1);
@@ -256,7 +259,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (lane == 0) {
             bool ok = true;
             ChunkWalk w_load, w_s, w_pv;     // cursors of the next chunk to load / to score / to multiply by V
-            if (MODE == kModeGlobalRows) w_load.init_range(range_lo, range_hi);
+            if (MODE != kModeBlock) w_load.init_range(range_lo, range_hi);
             else w_load.init(P, q0);
             w_s = w_pv = w_load;
             ptx::mbar_expect_tx(bar_q, kTileQ * kRowBytes);
@@ -355,7 +358,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     };
 
     ChunkWalk w;
-    if (MODE == kModeGlobalRows) w.init_range(range_lo, range_hi);
+    if (MODE != kModeBlock) w.init_range(range_lo, range_hi);
     else w.init(P, q0);
     // global-row pass: a warp takes part iff any of its 32 rows is a real global position
     const bool warp_has_rows = MODE != kModeGlobalRows || q0 + warp * 32 < P.n_global;
@@ -364,7 +367,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     int t = 0;
     for (; !w.done(); ++t, w.next()) {
         const int kb = w.key_base();
-        const bool mine = MODE == kModeGlobalRows ? warp_has_rows : (w.flags >> half) & 1;   // uniform within a warp
+        const bool mine = MODE == kModeGlobalRows ? warp_has_rows : (w.flags >> half) & 1;   // uniform within a warp (dense: always)
         if (!(ok = ptx::mbar_wait(bar_s + (t & 1), (t >> 1) & 1))) break;
         tc_fence_after();
         float alpha = 1.f;
@@ -373,7 +376,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             uint8_t *p_row = sP + (t & 1) * kTileQ * kRowBytes + r * kRowBytes;
             // keys this row may use in the chunk: j < j_end
             int j_end = min(kTileK, (MODE == kModeGlobalRows ? range_hi : P.Skv) - kb);
-            if (MODE == kModeBlock && P.causal) j_end = min(j_end, p - kb + 1);
+            if (MODE != kModeGlobalRows && P.causal) j_end = min(j_end, p - kb + 1);
             // pass 1: row maximum
             float mx = -INFINITY;
 #pragma unroll
@@ -531,6 +534,32 @@ int launch_t(const Problem &p) {
 }
 
 template <typename T>
+int launch_dense_t(const Problem &p, bool causal) {
+    CUtensorMap mq, mk, mv;
+    if (int rc = make_map(&mq, p.q, p.dtype, p.H, p.Sq, p.B, kTileQ)) return rc;
+    if (int rc = make_map(&mk, p.k, p.dtype, p.H, p.Skv, p.B, kTileK)) return rc;
+    if (int rc = make_map(&mv, p.v, p.dtype, p.H, p.Skv, p.B, kTileK)) return rc;
+    UmmaParams up;
+    up.Sq = (int32_t)p.Sq; up.Skv = (int32_t)p.Skv; up.off = (int32_t)p.pat.q_offset; up.H = (int32_t)p.H;
+    up.block = kTileK; up.per_blk = 1; up.causal = causal; up.n_qblocks = 0; up.rowptr = up.colidx = nullptr;
+    up.sl2 = p.scale * 1.4426950408889634f;
+    up.n_global = 0; up.gidx = nullptr; up.split_len = up.n_splits = up.ng_pad = 0; up.partial = nullptr;
+    auto kern = umma_block_fwd_kernel<T, kModeDense>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(umma dense)");
+    const dim3 grid((unsigned)p.H, (unsigned)((p.Sq + kTileQ - 1) / kTileQ), (unsigned)p.B);
+    kern<<<grid, kThreads, kSmemBytes, p.stream>>>(mq, mk, mv, (T *)p.o, up);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "umma dense kernel launch");
+    note_kernel("umma_dense");
+    return MAT_OK;
+}
+
+template <typename T>
 int launch_global_rows_t(const Problem &p, const GlobalRowSplit &g, float *partial) {
     CUtensorMap mq, mk, mv;
     if (int rc = make_map(&mq, p.q, p.dtype, p.H, p.Sq, p.B, 1)) return rc;   // one-row view: gathered tile
@@ -593,6 +622,27 @@ bool umma_block_supports(const Problem &p) {
     if (p.pat.block >= (1 << 24)) return false;
     const char *force = std::getenv("MAT_BLOCK_KERNEL");  // debugging aid: "mma" keeps the warp-level kernel
     return !(force && force[0] == 'm');
+}
+
+// Dense and causal-dense attention (the window that covers the whole sequence, the reference's
+// dense_forward, src/cuda/sparse_attention_kernel.cu:348-382) on the same tcgen05 pipeline: every
+// 128-row tile walks all keys (up to its last row when causal) 64 at a time.
+bool umma_dense_supports(const Problem &p) {
+    if (p.pat.kind != MAT_WINDOW || p.pat.dilation != 1) return false;
+    if (p.dtype != MAT_BF16 && p.dtype != MAT_F16) return false;
+    if (p.D != 64 || p.pat.q_offset % 64 != 0) return false;
+    const bool left_all = p.pat.left >= p.Skv - 1;
+    const bool right_all = p.pat.right >= p.Skv - 1, right_none = p.pat.right == 0;
+    if (!left_all || !(right_all || right_none)) return false;
+    if (p.Skv < 256) return false;   // short sequences: the window kernels are as good and need no TMEM
+    const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
+    if (al % 16) return false;
+    return p.Skv < (1LL << 28) && p.B <= 65535 && (p.Sq + kTileQ - 1) / kTileQ <= 65535;
+}
+
+int launch_umma_dense(const Problem &p) {
+    const bool causal = p.pat.right == 0;
+    return p.dtype == MAT_BF16 ? launch_dense_t<__nv_bfloat16>(p, causal) : launch_dense_t<__half>(p, causal);
 }
 
 int launch_umma_block(const Problem &p) {

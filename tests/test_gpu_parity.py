@@ -83,8 +83,24 @@ WINDOW_SPECS = [
 def test_mma_window_vs_oracle(spec, dtype, B, S, H):
     q, k, v = seeded_qkv(11, B, S, H, 64, dtype)
     got = run(spec, q, k, v)
-    assert nat.last_kernel() == "mma_window"
+    # a window that covers a long enough sequence is dense attention: that runs on the tcgen05 pipeline
+    covers = spec.left >= S - 1 and spec.right >= S - 1 and S >= 256
+    assert nat.last_kernel() == ("umma_dense" if covers else "mma_window")
     check_close(got, oracle_out(q, k, v, spec), dtype)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("B,S,H", [(1, 1024, 2), (2, 1000, 3), (1, 256, 1), (1, 4160, 2)])
+def test_dense_forward_on_tcgen05(causal, B, S, H):
+    """dense_forward (src/cuda/sparse_attention_kernel.cu:348-382) for 16-bit inputs: the window that
+    covers the sequence, run by the tcgen05 pipeline."""
+    for dtype in (torch.bfloat16, torch.float16):
+        q, k, v = seeded_qkv(14, B, S, H, 64, dtype)
+        got = ext.dense_forward(q.to(DEV), k.to(DEV), v.to(DEV), causal)
+        torch.cuda.synchronize()
+        assert nat.last_kernel() == "umma_dense"
+        spec = PatternSpec(left=S, right=0 if causal else S)
+        check_close(got, oracle_out(q, k, v, spec), dtype)
 
 
 @pytest.mark.parametrize("dil", [2, 3, 4])
