@@ -6,7 +6,10 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "mat_common.cuh"
@@ -31,6 +34,21 @@ int cuda_fail(cudaError_t e, const char *what) {
 }
 
 void note_kernel(const char *name) { g_last_kernel = name; }
+
+int ensure_dynamic_smem(const void *kernel, size_t bytes, const char *what) {
+    static std::mutex mu;
+    static std::map<std::pair<const void *, int>, size_t> done;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    std::lock_guard<std::mutex> lock(mu);
+    size_t &have = done[{kernel, dev}];
+    if (have >= bytes) return MAT_OK;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return cuda_fail(e, what);
+    have = bytes;
+    return MAT_OK;
+}
 
 static int check_spec(const mat_pattern_spec *s) {
     if (!s) return fail(MAT_ERR_INVALID, "pattern description is NULL");

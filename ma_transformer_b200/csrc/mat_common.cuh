@@ -46,6 +46,9 @@ struct Problem {
 int fail(int code, const char *fmt, ...);
 int cuda_fail(cudaError_t e, const char *what);
 void note_kernel(const char *name);
+// Raises a kernel's dynamic shared-memory limit, once per (kernel, device): the attribute belongs
+// to the function on one device, so a process that drives several GPUs needs it on each.
+int ensure_dynamic_smem(const void *kernel, size_t bytes, const char *what);
 // validation + kernel selection shared by the device and host entry points (api.cu)
 int make_problem(Problem &p, const void *q, const void *k, const void *v, void *o, int64_t B,
                  int64_t S_q, int64_t S_kv, int64_t H, int64_t D, int dtype,

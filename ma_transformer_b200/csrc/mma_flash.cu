@@ -632,12 +632,7 @@ int launch_kind(const Problem &p, const FlashParams &fp_in, int64_t dil, const c
     }
     auto kern = flash_fwd_kernel<T, KIND, TQ, TK, NP, STAGES, SINGLE, MINB>;
     constexpr size_t smem = flash_smem_bytes<TQ, TK, STAGES, KIND == MAT_LONGFORMER && STAGES == 1>();
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    });
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(flash_fwd_kernel)");
+    if (int rc = ensure_dynamic_smem((const void *)kern, smem, "cudaFuncSetAttribute(flash_fwd_kernel)")) return rc;
     const dim3 grid((unsigned)HH, (unsigned)(grid_y >= 0 ? grid_y : fp.n_tiles), (unsigned)p.B);
     kern<<<grid, flash_threads<TQ, SINGLE || STAGES == 1>(), smem, p.stream>>>(mq, mk, mv, mo, pm, fp);
     cudaError_t e = cudaGetLastError();

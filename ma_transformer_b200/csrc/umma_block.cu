@@ -519,12 +519,7 @@ int launch_t(const Problem &p) {
     up.sl2 = p.scale * 1.4426950408889634f;
     up.n_global = 0; up.gidx = nullptr; up.split_len = up.n_splits = up.ng_pad = 0; up.partial = nullptr;
     auto kern = umma_block_fwd_kernel<T, kModeBlock>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    });
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(umma_block_fwd_kernel)");
+    if (int rc = ensure_dynamic_smem((const void *)kern, kSmemBytes, "cudaFuncSetAttribute(umma_block_fwd_kernel)")) return rc;
     const dim3 grid((unsigned)p.H, (unsigned)((p.Sq + kTileQ - 1) / kTileQ), (unsigned)p.B);
     kern<<<grid, kThreads, kSmemBytes, p.stream>>>(mq, mk, mv, (T *)p.o, up);
     cudaError_t e = cudaGetLastError();
@@ -545,12 +540,7 @@ int launch_dense_t(const Problem &p, bool causal) {
     up.sl2 = p.scale * 1.4426950408889634f;
     up.n_global = 0; up.gidx = nullptr; up.split_len = up.n_splits = up.ng_pad = 0; up.partial = nullptr;
     auto kern = umma_block_fwd_kernel<T, kModeDense>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    });
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(umma dense)");
+    if (int rc = ensure_dynamic_smem((const void *)kern, kSmemBytes, "cudaFuncSetAttribute(umma dense)")) return rc;
     const dim3 grid((unsigned)p.H, (unsigned)((p.Sq + kTileQ - 1) / kTileQ), (unsigned)p.B);
     kern<<<grid, kThreads, kSmemBytes, p.stream>>>(mq, mk, mv, (T *)p.o, up);
     cudaError_t e = cudaGetLastError();
@@ -574,12 +564,7 @@ int launch_global_rows_t(const Problem &p, const GlobalRowSplit &g, float *parti
     up.split_len = g.split_len; up.n_splits = g.n_splits; up.ng_pad = g.ng_pad;
     up.partial = partial;
     auto kern = umma_block_fwd_kernel<T, kModeGlobalRows>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    });
-    if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(umma global rows)");
+    if (int rc = ensure_dynamic_smem((const void *)kern, kSmemBytes, "cudaFuncSetAttribute(umma global rows)")) return rc;
     const dim3 grid((unsigned)p.H, (unsigned)(g.tiles * g.n_splits), (unsigned)p.B);
     kern<<<grid, kThreads, kSmemBytes, p.stream>>>(mq, mk, mv, (T *)nullptr, up);
     cudaError_t e = cudaGetLastError();
