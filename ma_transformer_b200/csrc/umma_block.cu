@@ -14,17 +14,23 @@
 // layout row, so the union is a two-pointer merge, done identically by every
 // thread that needs it), 64 keys per step:
 //
-//   control warp (warp 4, one lane):  TMA K/V chunk -> smem (2 stages)
-//                                     S = Q K^T      tcgen05.mma 128x64x16 x4 -> TMEM cols [0,64)
-//                                     O_part = P V   tcgen05.mma 128x64x16 x4 -> TMEM cols [64,128)
+//   control warp (warp 4, one lane):  TMA K/V chunk -> smem (3 stages)
+//                                     S = Q K^T      tcgen05.mma 128x64x16 x4 -> TMEM S buffer (two of them)
+//                                     O += P V       tcgen05.mma 128x64x16 x4 -> TMEM O (accumulates in place)
+//                                     l += P 1       tcgen05.mma 128x16x16 x4 -> TMEM row sums
 //   softmax warps (warps 0-3):        thread r owns query row r: tcgen05.ld its 64 scores, mask,
-//                                     running max / sum, P as bf16 into smem (K-major, 128B swizzle),
-//                                     then tcgen05.ld its O_part row and fold it into registers.
+//                                     row maximum, P = 2^(s - m) as bf16 into smem (K-major, 128B swizzle).
 //
-// A half whose layout row does not hold the step's key block skips the softmax
-// work of that step (its rows of P and O_part are never read).  Everything that
-// waits does so on an mbarrier with a bounded wait; a wait that runs out sets the
-// library's status word and the CTA drains, frees its TMEM and leaves.
+// The output and the row sums stay in TMEM for the whole walk.  The reference maximum m of a row
+// moves only when the chunk's maximum exceeds it by more than a factor 2 (weights then stay <= 2:
+// the exponent, rounded to the 16-bit operand type before ex2, keeps an absolute error <= 2^-9
+// for the large weights, as with an exact running maximum); only then are the row's O and l read
+// back, scaled and stored again (tcgen05.ld / tcgen05.st), which after the first chunks of a
+// long row is rare.
+//
+// A half whose layout row does not hold the step's key block writes a zero row of P for that
+// step.  Everything that waits does so on an mbarrier with a bounded wait; a wait that runs out
+// sets the library's status word and the CTA drains, frees its TMEM and leaves.
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -42,7 +48,10 @@ namespace {
 constexpr int kRowBytes = 128;
 constexpr int kTileQ = 128;     // query rows per CTA (UMMA M)
 constexpr int kTileK = 64;      // keys per step (UMMA N for S, K extent for P V)
-constexpr int kTmemCols = 256;  // S buffers in [0,128), O_part buffers in [128,256)
+constexpr int kTmemCols = 256;  // S buffers in [0,128), O in [128,192), row sums in [192,208)
+constexpr int kColO = 128, kColSum = 192;
+constexpr int kSumN = 16;       // narrowest N of an M = 128 instruction; column 0 is read
+constexpr float kLazyLog2 = 1.f;  // a row's reference maximum moves when the scores outgrow it by 2^1
 
 __device__ int g_umma_status = 0;
 
@@ -97,22 +106,56 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
                      ptx::smem_u32(bar))
                  : "memory");
 }
-// 32 consecutive fp32 columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
+// 64 consecutive fp32 columns of this thread's TMEM lane, one instruction and one wait
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
+    uint32_t r[64];
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
         : "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+// the same plus one more column elsewhere in the lane (the row sum), both in flight before the wait
+__device__ __forceinline__ void tmem_ld64_and_1(uint32_t taddr, float (&v)[64], uint32_t taddr1, float &x) {
+    uint32_t r[64], r1;
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%65];\n"
+        "tcgen05.ld.sync.aligned.32x32b.x1.b32 {%64}, [%66];\n"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63]), "=r"(r1)
+        : "r"(taddr), "r"(taddr1)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+    x = __uint_as_float(r1);
+}
+__device__ __forceinline__ void tmem_st64(uint32_t taddr, const float (&v)[64]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x64.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63, %64};" ::"r"(taddr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]), "f"(v[8]), "f"(v[9]), "f"(v[10]), "f"(v[11]), "f"(v[12]), "f"(v[13]), "f"(v[14]), "f"(v[15]), "f"(v[16]), "f"(v[17]), "f"(v[18]), "f"(v[19]), "f"(v[20]), "f"(v[21]), "f"(v[22]), "f"(v[23]), "f"(v[24]), "f"(v[25]), "f"(v[26]), "f"(v[27]), "f"(v[28]), "f"(v[29]), "f"(v[30]), "f"(v[31]), "f"(v[32]), "f"(v[33]), "f"(v[34]), "f"(v[35]), "f"(v[36]), "f"(v[37]), "f"(v[38]), "f"(v[39]), "f"(v[40]), "f"(v[41]), "f"(v[42]), "f"(v[43]), "f"(v[44]), "f"(v[45]), "f"(v[46]), "f"(v[47]), "f"(v[48]), "f"(v[49]), "f"(v[50]), "f"(v[51]), "f"(v[52]), "f"(v[53]), "f"(v[54]), "f"(v[55]), "f"(v[56]), "f"(v[57]), "f"(v[58]), "f"(v[59]), "f"(v[60]), "f"(v[61]), "f"(v[62]), "f"(v[63]) : "memory");
+}
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, float v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// two fp32 lanes per instruction: (d0, d1) = (a0, a1) * b + c
+__device__ __forceinline__ void ffma2(float &d0, float &d1, float a0, float a1, float b, float c) {
+    asm("{\n.reg .b64 ra, rb, rc, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %4};\nmov.b64 rc, {%5, %5};\n"
+        "fma.rn.f32x2 rd, ra, rb, rc;\nmov.b64 {%0, %1}, rd;\n}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void fmul2(float &d0, float &d1, float a0, float a1, float b) {
+    asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %4};\n"
+        "mul.rn.f32x2 rd, ra, rb;\nmov.b64 {%0, %1}, rd;\n}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 // Shared-memory matrix descriptor of a tile whose rows are 128 bytes, 128-byte swizzled, 8-row
@@ -128,16 +171,16 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
     return d;
 }
-// kind::f16 instruction descriptor: fp32 accumulate, A/B type, M = 128, N = 64
+// kind::f16 instruction descriptor: fp32 accumulate, A/B type, M = 128, N = n
 template <typename T>
-__device__ __forceinline__ uint32_t instr_desc(bool b_mn_major) {
+__device__ __forceinline__ uint32_t instr_desc(bool b_mn_major, int n = kTileK) {
     const uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
     uint32_t d = 0;
     d |= 1u << 4;                       // accumulator format f32
     d |= fmt << 7;                      // A format
     d |= fmt << 10;                     // B format
     d |= (b_mn_major ? 1u : 0u) << 16;  // B major-ness
-    d |= (uint32_t)(kTileK >> 3) << 17; // N
+    d |= (uint32_t)(n >> 3) << 17;      // N
     d |= (uint32_t)(kTileQ >> 4) << 24; // M
     return d;
 }
@@ -199,15 +242,16 @@ struct ChunkWalk {
 constexpr int kThreads = 160;  // 4 softmax warps + 1 control warp
 constexpr int kKvStages = 3;
 constexpr int kStage = 2 * kTileK * kRowBytes;  // one K/V stage: K then V
+constexpr int kOnesBytes = kSumN * kRowBytes;   // B operand of the row-sum product: 16 rows of ones
 constexpr size_t kSmemBytes = 1024 + kTileQ * kRowBytes /*Q*/ + kKvStages * kStage + 2 * kTileQ * kRowBytes /*P x2*/ +
-                              256 /*barriers, tmem address*/;
+                              kOnesBytes + 256 /*barriers, tmem address*/;
 
 // The step pipeline (t = index of the 64-key chunk):
 //   control:  S(t+1) is issued before P V(t), so the tensor core computes the next scores while
-//             the softmax warps work on the current ones; S and O_part are double-buffered in
-//             TMEM (columns S0 S1 O0 O1), P is double-buffered in shared memory, K/V has 3 stages.
-//   softmax:  softmax(t) -> publish P(t) -> fold O_part(t-1) into the registers.  The fold of a
-//             chunk uses the rescale factor of that chunk's own softmax step (kept one step).
+//             the softmax warps work on the current ones; S is double-buffered in TMEM, P is
+//             double-buffered in shared memory, K/V has 3 stages.  P V(t) and the row-sum product
+//             accumulate into O and l in TMEM (the first chunk overwrites).
+//   softmax:  softmax(t) -> (rarely: wait for P V(t-1), rescale O and l in TMEM) -> publish P(t).
 template <typename T, int MODE>
 __global__ void __launch_bounds__(kThreads)
 umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -217,9 +261,10 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     uint8_t *sQ = smem;
     uint8_t *sKV = sQ + kTileQ * kRowBytes;            // stage s: K at +0, V at +8 KB
     uint8_t *sP = sKV + kKvStages * kStage;            // two P tiles
-    uint64_t *bars = (uint64_t *)(sP + 2 * kTileQ * kRowBytes);
+    uint8_t *sOnes = sP + 2 * kTileQ * kRowBytes;      // 16 rows of ones
+    uint64_t *bars = (uint64_t *)(sOnes + kOnesBytes);
     uint64_t *bar_q = bars, *bar_kv = bars + 1 /*[3]*/, *bar_s = bars + 4 /*[2]*/, *bar_p = bars + 6 /*[2]*/,
-             *bar_o = bars + 8 /*[2]*/, *bar_done = bars + 10;
+             *bar_o = bars + 8, *bar_fin = bars + 9, *bar_done = bars + 10;
     uint32_t *tmem_slot = (uint32_t *)(bars + 12);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -239,10 +284,16 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(bar_s + i, 1);
             ptx::mbar_init(bar_p + i, 4);
-            ptx::mbar_init(bar_o + i, 1);
         }
+        ptx::mbar_init(bar_o, 1);
+        ptx::mbar_init(bar_fin, 1);
         ptx::mbar_init(bar_done, 4);
         ptx::fence_barrier_init();
+    }
+    if (threadIdx.x < kOnesBytes / 16) {
+        const uint32_t one2 = ptx::Mma<T>::kOnes;
+        reinterpret_cast<uint4 *>(sOnes)[threadIdx.x] = make_uint4(one2, one2, one2, one2);
+        ptx::fence_proxy_async_smem();
     }
     if (warp == 4) {
         tmem_alloc(tmem_slot, kTmemCols);
@@ -252,7 +303,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    // TMEM columns: S buffer i at 64*i, O_part buffer i at 128 + 64*i
+    // TMEM columns: S buffer i at 64*i, O at kColO, row sums at kColSum
 
     if (warp == 4) {
         // ================= control warp =================
@@ -285,8 +336,9 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 w_load.next();
             };
             for (int i = 0; i < kKvStages && !w_load.done(); ++i) issue_load();
-            const uint32_t idesc_s = instr_desc<T>(false), idesc_pv = instr_desc<T>(true);
-            const uint32_t q_addr = ptx::smem_u32(sQ), p_addr = ptx::smem_u32(sP);
+            const uint32_t idesc_s = instr_desc<T>(false), idesc_pv = instr_desc<T>(true),
+                           idesc_sum = instr_desc<T>(false, kSumN);
+            const uint32_t q_addr = ptx::smem_u32(sQ), p_addr = ptx::smem_u32(sP), ones_addr = ptx::smem_u32(sOnes);
             int t_s = 0;
             auto issue_s = [&]() -> bool {   // S(t_s) = Q K^T into S buffer t_s & 1
                 const int s = t_s % kKvStages;
@@ -312,16 +364,23 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 const uint32_t v_addr = ptx::smem_u32(sKV + (t % kKvStages) * kStage) + kTileK * kRowBytes;
                 const uint32_t pa = p_addr + (t & 1) * kTileQ * kRowBytes;
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)   // O_part = P V, 16 of the 64 keys per instruction
-                    umma_f16(tmem + 2 * kTileK + (t & 1) * kTileK, smem_desc(pa + ks * 32),
-                             smem_desc(v_addr + ks * 16 * kRowBytes), idesc_pv, ks > 0);
-                umma_commit(bar_o + (t & 1));
+                for (int ks = 0; ks < 4; ++ks)   // O += P V, 16 of the 64 keys per instruction
+                    umma_f16(tmem + kColO, smem_desc(pa + ks * 32), smem_desc(v_addr + ks * 16 * kRowBytes),
+                             idesc_pv, t > 0 || ks > 0);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)   // l += P 1
+                    umma_f16(tmem + kColSum, smem_desc(pa + ks * 32), smem_desc(ones_addr + ks * 32), idesc_sum,
+                             t > 0 || ks > 0);
+                umma_commit(bar_o);
                 // stage t % 3 is free once P V(t) has read V: refill it with chunk t + 3
                 if (!w_load.done()) {
-                    if (!(ok = ptx::mbar_wait(bar_o + (t & 1), (t >> 1) & 1))) break;
+                    if (!(ok = ptx::mbar_wait(bar_o, t & 1))) break;
                     issue_load();
                 }
             }
+            // bar_o's parity tells two states apart, enough inside the walk (a softmax warp is at most one
+            // product behind); the end of the walk gets a barrier of its own
+            if (ok) umma_commit(bar_fin);
             if (!ok) atomicExch(&g_umma_status, 1);
             // every softmax warp has read its last TMEM values before the columns are freed
             if (!ptx::mbar_wait(bar_done, 0)) atomicExch(&g_umma_status, 1);
@@ -337,106 +396,100 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int half = r >> 6;
     const int p = q0 + r + P.off;          // key-coordinate position of this row
     const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);
-    float o[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_run = -INFINITY;   // reference maximum of the row's weights (raw score units); -inf: no key yet
     bool ok = true;
-
-    // fold O_part of chunk c (buffer c & 1) into the registers: o = o * alpha_c + O_part(c)
-    auto fold = [&](int c, float alpha_c) -> bool {
-        if (!ptx::mbar_wait(bar_o + (c & 1), (c >> 1) & 1)) return false;
-        tc_fence_after();
-#pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 32) {
-            float part[32];
-            tmem_ld32(t_lane + 2 * kTileK + (c & 1) * kTileK + c0, part);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha_c, part[i]);
-        }
-        return true;
-    };
 
     ChunkWalk w;
     if (MODE != kModeBlock) w.init_range(range_lo, range_hi);
     else w.init(P, q0);
     // global-row pass: a warp takes part iff any of its 32 rows is a real global position
     const bool warp_has_rows = MODE != kModeGlobalRows || q0 + warp * 32 < P.n_global;
-    bool prev_mine = false;
-    float prev_alpha = 1.f;
+    int zeroed = 0;            // bit i: this row of P buffer i holds zeros
     int t = 0;
     for (; !w.done(); ++t, w.next()) {
         const int kb = w.key_base();
         const bool mine = MODE == kModeGlobalRows ? warp_has_rows : (w.flags >> half) & 1;   // uniform within a warp (dense: always)
         if (!(ok = ptx::mbar_wait(bar_s + (t & 1), (t >> 1) & 1))) break;
         tc_fence_after();
-        float alpha = 1.f;
+        uint8_t *p_row = sP + (t & 1) * kTileQ * kRowBytes + r * kRowBytes;
         if (mine) {
             const uint32_t s_addr = t_lane + (t & 1) * kTileK;
-            uint8_t *p_row = sP + (t & 1) * kTileQ * kRowBytes + r * kRowBytes;
             // keys this row may use in the chunk: j < j_end
             int j_end = min(kTileK, (MODE == kModeGlobalRows ? range_hi : P.Skv) - kb);
             if (MODE != kModeGlobalRows && P.causal) j_end = min(j_end, p - kb + 1);
-            // pass 1: row maximum
-            float mx = -INFINITY;
+            float s[64];
+            tmem_ld64(s_addr, s);
+            if (j_end < kTileK) {   // only the chunks on the causal diagonal or at the sequence end
 #pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 32) {
-                float s[32];
-                tmem_ld32(s_addr + c0, s);
-                if (j_end < c0 + 32) {   // only the chunks on the causal diagonal or at the sequence end
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) if (c0 + i >= j_end) s[i] = -INFINITY;
-                }
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, s[i]);
+                for (int i = 0; i < 64; ++i) if (i >= j_end) s[i] = -INFINITY;
             }
-            const float m_new = fmaxf(m_run, mx);
-            const float mu = m_new == -INFINITY ? 0.f : m_new;
-            alpha = ptx::ex2((m_run - mu) * P.sl2);
-            m_run = m_new;
-            const float mus = mu * P.sl2;
-            // pass 2: weights, packed to the operand type two at a time, into the swizzled P row
-            float sum = 0.f;
+            float mq[4];   // four independent chains of three-input maxima
 #pragma unroll
-            for (int c0 = 0; c0 < 64; c0 += 32) {
-                float s[32];
-                tmem_ld32(s_addr + c0, s);
-                if (j_end < c0 + 32) {
+            for (int q = 0; q < 4; ++q) {
+                mq[q] = max3(s[16 * q], s[16 * q + 1], s[16 * q + 2]);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) if (c0 + i >= j_end) s[i] = -INFINITY;
-                }
-                uint32_t pk[16];
+                for (int i = 3; i < 15; i += 2) mq[q] = max3(mq[q], s[16 * q + i], s[16 * q + i + 1]);
+                mq[q] = fmaxf(mq[q], s[16 * q + 15]);
+            }
+            const float mx = fmaxf(max3(mq[0], mq[1], mq[2]), mq[3]);
+            // move the reference maximum only when the scores outgrow it by 2^kLazyLog2
+            const bool seen = m_run != -INFINITY;
+            const bool grow = seen ? (mx - m_run) * P.sl2 > kLazyLog2 : mx != -INFINITY;
+            const bool rescale = seen && grow;
+            const float alpha = rescale ? ptx::ex2((m_run - mx) * P.sl2) : 1.f;
+            if (grow) m_run = mx;
+            const float mus = (m_run == -INFINITY ? 0.f : m_run) * P.sl2;
+            // weights, packed to the operand type two at a time, into the swizzled P row
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float x0 = fmaf(s[2 * i], P.sl2, -mus);
-                    const float x1 = fmaf(s[2 * i + 1], P.sl2, -mus);
+            for (int q = 0; q < 8; ++q) {   // eight 16-byte pieces = columns 8q .. 8q + 7
+                uint32_t pk[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float x0, x1;
+                    ffma2(x0, x1, s[8 * q + 2 * i], s[8 * q + 2 * i + 1], P.sl2, -mus);
                     pk[i] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
-                    if (sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value) {
-                        sum += __uint_as_float(pk[i] << 16) + __uint_as_float(pk[i] & 0xffff0000u);
-                    } else {
-                        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&pk[i]));
-                        sum += f.x + f.y;
-                    }
                 }
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {   // four 16-byte pieces = columns c0 + 8q .. c0 + 8q + 7
-                    const int chunk16 = (c0 >> 3) + q;
-                    *reinterpret_cast<uint4 *>(p_row + ((chunk16 ^ (r & 7)) << 4)) =
-                        make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-                }
+                *reinterpret_cast<uint4 *>(p_row + ((q ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
-            l_run = l_run * alpha + sum;
+            if (__any_sync(0xffffffffu, rescale)) {
+                // O and l hold the chunks up to t-1: wait for P V(t-1), then scale this row in place
+                if (!(ok = ptx::mbar_wait(bar_o, (t - 1) & 1))) break;
+                tc_fence_after();
+                float part[64], l_part;
+                tmem_ld64_and_1(t_lane + kColO, part, t_lane + kColSum, l_part);
+#pragma unroll
+                for (int i = 0; i < 64; i += 2) fmul2(part[i], part[i + 1], part[i], part[i + 1], alpha);
+                tmem_st64(t_lane + kColO, part);
+                tmem_st1(t_lane + kColSum, l_part * alpha);
+                tmem_wait_st();
+            }
+            zeroed &= ~(1 << (t & 1));
+        } else if (!((zeroed >> (t & 1)) & 1)) {
+            // this half sits the chunk out: its rows of P must add nothing to O and l
+#pragma unroll
+            for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4 *>(p_row + (q << 4)) = make_uint4(0, 0, 0, 0);
+            zeroed |= 1 << (t & 1);
         }
         ptx::fence_proxy_async_smem();   // the tensor core reads P through the async proxy
         tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(bar_p + (t & 1));
-        // while the tensor core multiplies P(t) by V, take in the result of the previous chunk
-        if (t >= 1 && prev_mine && !(ok = fold(t - 1, prev_alpha))) break;
-        prev_mine = mine;
-        prev_alpha = alpha;
     }
-    if (ok && t >= 1 && prev_mine) ok = fold(t - 1, prev_alpha);
+    // the accumulated row and its sum, once the last P V has completed
+    float o[64];
+    float l_run = 0.f;
+    if (ok && t >= 1) {
+        ok = ptx::mbar_wait(bar_fin, 0);
+        tc_fence_after();
+        if (ok) {
+            tmem_ld64_and_1(t_lane + kColO, o, t_lane + kColSum, l_run);
+        }
+    }
+    if (!ok || t == 0) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) o[i] = 0.f;
+        l_run = 0.f;
+    }
     if (!ok) atomicExch(&g_umma_status, 1);
     tc_fence_before();
     __syncwarp();
