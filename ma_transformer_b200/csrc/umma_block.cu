@@ -14,12 +14,14 @@
 // layout row, so the union is a two-pointer merge, done identically by every
 // thread that needs it), 64 keys per step:
 //
-//   control warp (warp 4, one lane):  TMA K/V chunk -> smem (3 stages)
-//                                     S = Q K^T      tcgen05.mma 128x64x16 x4 -> TMEM S buffer (two of them)
+//   load warp (warp 9, one lane):     TMA K/V chunk -> smem (3 stages each)
+//   MMA warp (warp 8, one lane):      S = Q K^T      tcgen05.mma 128x64x16 x4 -> TMEM S buffer (two of them)
 //                                     O += P V       tcgen05.mma 128x64x16 x4 -> TMEM O (accumulates in place)
 //                                     l += P 1       tcgen05.mma 128x16x16 x4 -> TMEM row sums
-//   softmax warps (warps 0-3):        thread r owns query row r: tcgen05.ld its 64 scores, mask,
-//                                     row maximum, P = 2^(s - m) as bf16 into smem (K-major, 128B swizzle).
+//   softmax warps (warps 0-7):        two threads per query row (warps w and w+4 reach the same 32 TMEM
+//                                     lanes): each loads the row's 64 scores, masks, takes the row
+//                                     maximum, and writes its half (32 keys) of P = 2^(s - m) as bf16
+//                                     into smem (K-major, 128B swizzle).
 //
 // The output and the row sums stay in TMEM for the whole walk.  The reference maximum m of a row
 // moves only when the chunk's maximum exceeds it by more than a factor 2 (weights then stay <= 2:
@@ -48,8 +50,8 @@ namespace {
 constexpr int kRowBytes = 128;
 constexpr int kTileQ = 128;     // query rows per CTA (UMMA M)
 constexpr int kTileK = 64;      // keys per step (UMMA N for S, K extent for P V)
-constexpr int kTmemCols = 256;  // S buffers in [0,128), O in [128,192), row sums in [192,208)
-constexpr int kColO = 128, kColSum = 192;
+constexpr int kTmemCols = 256;  // S buffers in [0,128), O in [128,192), row sums in [192,208), Q in [208,240)
+constexpr int kColO = 128, kColSum = 192, kColQ = 208;   // Q: 64 values of a row in 32 columns
 constexpr int kSumN = 16;       // narrowest N of an M = 128 instruction; column 0 is read
 constexpr float kLazyLog2 = 1.f;  // a row's reference maximum moves when the scores outgrow it by 2^1
 
@@ -69,6 +71,7 @@ struct UmmaParams {
     int32_t n_global;
     const int64_t *gidx;
     int32_t split_len, n_splits, ng_pad;
+    int32_t dbg = 0;
     float *partial;   // [B, H, n_splits, ng_pad, kPartialStride]: max, sum, unnormalised output
 };
 
@@ -88,16 +91,17 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-// D[tmem] (+)= A[smem] * B[smem], M = 128, one K step of 16 elements
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                         uint32_t accumulate) {
+// D[tmem] (+)= A * B[smem], M = 128, one K step of 16 elements,
+// the A operand in TMEM (lane = row, 32-bit column = two consecutive K elements)
+__device__ __forceinline__ void umma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
         "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
         "}\n" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // arrive on an mbarrier when every tcgen05.mma issued so far by this thread has completed
@@ -118,7 +122,7 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64]) {
 #pragma unroll
     for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
-// the same plus one more column elsewhere in the lane (the row sum), both in flight before the wait
+// 64 columns plus one more column elsewhere in the lane (the row sum), both in flight before the wait
 __device__ __forceinline__ void tmem_ld64_and_1(uint32_t taddr, float (&v)[64], uint32_t taddr1, float &x) {
     uint32_t r[64], r1;
     asm volatile(
@@ -134,6 +138,9 @@ __device__ __forceinline__ void tmem_ld64_and_1(uint32_t taddr, float (&v)[64], 
 }
 __device__ __forceinline__ void tmem_st64(uint32_t taddr, const float (&v)[64]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x64.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63, %64};" ::"r"(taddr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]), "f"(v[8]), "f"(v[9]), "f"(v[10]), "f"(v[11]), "f"(v[12]), "f"(v[13]), "f"(v[14]), "f"(v[15]), "f"(v[16]), "f"(v[17]), "f"(v[18]), "f"(v[19]), "f"(v[20]), "f"(v[21]), "f"(v[22]), "f"(v[23]), "f"(v[24]), "f"(v[25]), "f"(v[26]), "f"(v[27]), "f"(v[28]), "f"(v[29]), "f"(v[30]), "f"(v[31]), "f"(v[32]), "f"(v[33]), "f"(v[34]), "f"(v[35]), "f"(v[36]), "f"(v[37]), "f"(v[38]), "f"(v[39]), "f"(v[40]), "f"(v[41]), "f"(v[42]), "f"(v[43]), "f"(v[44]), "f"(v[45]), "f"(v[46]), "f"(v[47]), "f"(v[48]), "f"(v[49]), "f"(v[50]), "f"(v[51]), "f"(v[52]), "f"(v[53]), "f"(v[54]), "f"(v[55]), "f"(v[56]), "f"(v[57]), "f"(v[58]), "f"(v[59]), "f"(v[60]), "f"(v[61]), "f"(v[62]), "f"(v[63]) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
 }
 __device__ __forceinline__ void tmem_st1(uint32_t taddr, float v) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "f"(v) : "memory");
@@ -239,19 +246,25 @@ struct ChunkWalk {
     }
 };
 
-constexpr int kThreads = 160;  // 4 softmax warps + 1 control warp
-constexpr int kKvStages = 3;
+constexpr int kSoftmaxWarps = 4;
+constexpr int kThreads = (kSoftmaxWarps + 2) * 32;  // 4 softmax warps + MMA warp + load warp
+constexpr int kKvStages = 5;
 constexpr int kStage = 2 * kTileK * kRowBytes;  // one K/V stage: K then V
 constexpr int kOnesBytes = kSumN * kRowBytes;   // B operand of the row-sum product: 16 rows of ones
-constexpr size_t kSmemBytes = 1024 + kTileQ * kRowBytes /*Q*/ + kKvStages * kStage + 2 * kTileQ * kRowBytes /*P x2*/ +
-                              kOnesBytes + 256 /*barriers, tmem address*/;
+constexpr size_t kSmemBytes = 1024 + kTileQ * kRowBytes /*Q*/ + kKvStages * kStage + kOnesBytes +
+                              512 /*barriers, tmem address*/;
 
 // The step pipeline (t = index of the 64-key chunk):
-//   control:  S(t+1) is issued before P V(t), so the tensor core computes the next scores while
-//             the softmax warps work on the current ones; S is double-buffered in TMEM, P is
-//             double-buffered in shared memory, K/V has 3 stages.  P V(t) and the row-sum product
-//             accumulate into O and l in TMEM (the first chunk overwrites).
-//   softmax:  softmax(t) -> (rarely: wait for P V(t-1), rescale O and l in TMEM) -> publish P(t).
+//   load warp: K(t) as soon as S(t - kKvStages) has left its stage, V(t) once P V(t - kKvStages) has.
+//   MMA warp:  S(t+1) is issued before P V(t), so the tensor core computes the next scores while
+//              the softmax warps work on the current ones; S is double-buffered in TMEM.  Q and P
+//              are A operands read from TMEM: Q is copied there once per tile, P(t) is stored by
+//              the softmax warps over the first 32 columns of the S buffer it was computed from
+//              (S(t+2), which overwrites them, is issued after P V(t) and so runs after it).
+//              Shared memory then carries only K and V (its bandwidth, not the tensor pipe, bounded
+//              the variant that kept Q and P there).  P V(t) and the row-sum product accumulate
+//              into O and l in TMEM (the first chunk overwrites).
+//   softmax:   softmax(t) -> store P(t) -> (rarely: wait for P V(t-1), rescale O and l) -> publish.
 template <typename T, int MODE>
 __global__ void __launch_bounds__(kThreads)
 umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -260,12 +273,12 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *sQ = smem;
     uint8_t *sKV = sQ + kTileQ * kRowBytes;            // stage s: K at +0, V at +8 KB
-    uint8_t *sP = sKV + kKvStages * kStage;            // two P tiles
-    uint8_t *sOnes = sP + 2 * kTileQ * kRowBytes;      // 16 rows of ones
+    uint8_t *sOnes = sKV + kKvStages * kStage;         // 16 rows of ones
     uint64_t *bars = (uint64_t *)(sOnes + kOnesBytes);
-    uint64_t *bar_q = bars, *bar_kv = bars + 1 /*[3]*/, *bar_s = bars + 4 /*[2]*/, *bar_p = bars + 6 /*[2]*/,
-             *bar_o = bars + 8, *bar_fin = bars + 9, *bar_done = bars + 10;
-    uint32_t *tmem_slot = (uint32_t *)(bars + 12);
+    uint64_t *bar_q = bars, *bar_qt = bars + 1, *bar_fin = bars + 2, *bar_done = bars + 3, *bar_s = bars + 4 /*[2]*/,
+             *bar_p = bars + 6 /*[2]*/, *bar_o = bars + 8 /*[2]*/, *bar_k = bars + 10 /*[kKvStages]*/,
+             *bar_v = bar_k + kKvStages, *bar_kfree = bar_v + kKvStages, *bar_vfree = bar_kfree + kKvStages;
+    uint32_t *tmem_slot = (uint32_t *)(bar_vfree + kKvStages);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x, b = blockIdx.z;
@@ -280,14 +293,20 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(bar_q, 1);
-        for (int i = 0; i < kKvStages; ++i) ptx::mbar_init(bar_kv + i, 1);
+        ptx::mbar_init(bar_qt, kSoftmaxWarps);
+        for (int i = 0; i < kKvStages; ++i) {
+            ptx::mbar_init(bar_k + i, 1);
+            ptx::mbar_init(bar_v + i, 1);
+            ptx::mbar_init(bar_kfree + i, 1);
+            ptx::mbar_init(bar_vfree + i, 1);
+        }
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(bar_s + i, 1);
-            ptx::mbar_init(bar_p + i, 4);
+            ptx::mbar_init(bar_p + i, kSoftmaxWarps);
+            ptx::mbar_init(bar_o + i, 1);
         }
-        ptx::mbar_init(bar_o, 1);
         ptx::mbar_init(bar_fin, 1);
-        ptx::mbar_init(bar_done, 4);
+        ptx::mbar_init(bar_done, kSoftmaxWarps);
         ptx::fence_barrier_init();
     }
     if (threadIdx.x < kOnesBytes / 16) {
@@ -295,7 +314,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         reinterpret_cast<uint4 *>(sOnes)[threadIdx.x] = make_uint4(one2, one2, one2, one2);
         ptx::fence_proxy_async_smem();
     }
-    if (warp == 4) {
+    if (warp == kSoftmaxWarps) {
         tmem_alloc(tmem_slot, kTmemCols);
         tmem_relinquish();
     }
@@ -303,16 +322,16 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    // TMEM columns: S buffer i at 64*i, O at kColO, row sums at kColSum
+    // TMEM columns: S buffer i at 64*i (P(t) over its first 32), O at kColO, row sums at kColSum, Q at kColQ
 
-    if (warp == 4) {
-        // ================= control warp =================
+    if (warp == kSoftmaxWarps + 1) {
+        // ================= load warp: Q once, then K and V chunk by chunk =================
         if (lane == 0) {
             bool ok = true;
-            ChunkWalk w_load, w_s, w_pv;     // cursors of the next chunk to load / to score / to multiply by V
-            if (MODE != kModeBlock) w_load.init_range(range_lo, range_hi);
-            else w_load.init(P, q0);
-            w_s = w_pv = w_load;
+            ChunkWalk w_k, w_v;   // K runs one chunk ahead of V: its stage is free earlier (after S, not after P V)
+            if (MODE != kModeBlock) w_k.init_range(range_lo, range_hi);
+            else w_k.init(P, q0);
+            w_v = w_k;
             ptx::mbar_expect_tx(bar_q, kTileQ * kRowBytes);
             if (MODE == kModeGlobalRows) {
                 // map_q is a one-row view here: row r of the tile is the query at global position
@@ -325,61 +344,77 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             } else {
                 ptx::tma_load_4d(sQ, &map_q, bar_q, 0, h, q0, b);
             }
-            int t_load = 0;
-            auto issue_load = [&]() {
-                const int s = t_load % kKvStages, kb = w_load.key_base();
-                uint8_t *dst = sKV + s * kStage;
-                ptx::mbar_expect_tx(bar_kv + s, kStage);
-                ptx::tma_load_4d(dst, &map_k, bar_kv + s, 0, h, kb, b);
-                ptx::tma_load_4d(dst + kTileK * kRowBytes, &map_v, bar_kv + s, 0, h, kb, b);
-                ++t_load;
-                w_load.next();
+            int c_k = 0;
+            auto load_k = [&]() -> bool {   // K(c_k) once S(c_k - kKvStages) has left the stage
+                const int s = c_k % kKvStages;
+                if (c_k >= kKvStages && !ptx::mbar_wait(bar_kfree + s, (c_k / kKvStages - 1) & 1)) return false;
+                ptx::mbar_expect_tx(bar_k + s, kTileK * kRowBytes);
+                ptx::tma_load_4d(sKV + s * kStage, &map_k, bar_k + s, 0, h, w_k.key_base(), b);
+                ++c_k;
+                w_k.next();
+                return true;
             };
-            for (int i = 0; i < kKvStages && !w_load.done(); ++i) issue_load();
+            if (!w_k.done()) ok = load_k();
+            for (int c = 0; ok && !w_v.done(); ++c, w_v.next()) {
+                if (!w_k.done() && !(ok = load_k())) break;
+                const int s = c % kKvStages;   // V(c) once P V(c - kKvStages) has left the stage
+                if (c >= kKvStages && !(ok = ptx::mbar_wait(bar_vfree + s, (c / kKvStages - 1) & 1))) break;
+                ptx::mbar_expect_tx(bar_v + s, kTileK * kRowBytes);
+                ptx::tma_load_4d(sKV + s * kStage + kTileK * kRowBytes, &map_v, bar_v + s, 0, h, w_v.key_base(), b);
+            }
+            if (!ok) atomicExch(&g_umma_status, 1);
+        }
+        return;
+    }
+    if (warp == kSoftmaxWarps) {
+        // ================= MMA warp: one lane issues every tcgen05.mma of the tile =================
+        if (lane == 0) {
+            bool ok = true;
+            ChunkWalk w_s;     // only counts the chunks here
+            if (MODE != kModeBlock) w_s.init_range(range_lo, range_hi);
+            else w_s.init(P, q0);
             const uint32_t idesc_s = instr_desc<T>(false), idesc_pv = instr_desc<T>(true),
                            idesc_sum = instr_desc<T>(false, kSumN);
-            const uint32_t q_addr = ptx::smem_u32(sQ), p_addr = ptx::smem_u32(sP), ones_addr = ptx::smem_u32(sOnes);
+            // descriptors differ from step to step only in the start address field (16-byte units)
+            const uint64_t dkv = smem_desc(ptx::smem_u32(sKV)), dones = smem_desc(ptx::smem_u32(sOnes));
             int t_s = 0;
             auto issue_s = [&]() -> bool {   // S(t_s) = Q K^T into S buffer t_s & 1
                 const int s = t_s % kKvStages;
-                if (!ptx::mbar_wait(bar_kv + s, (t_s / kKvStages) & 1)) return false;
+                if (!ptx::mbar_wait(bar_k + s, (t_s / kKvStages) & 1)) return false;
                 tc_fence_after();
-                const uint32_t k_addr = ptx::smem_u32(sKV + s * kStage);
+                const uint64_t dk = dkv + (uint64_t)(s * (kStage >> 4));
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)   // 16 of the 64 head columns per instruction
-                    umma_f16(tmem + (t_s & 1) * kTileK, smem_desc(q_addr + ks * 32), smem_desc(k_addr + ks * 32),
-                             idesc_s, ks > 0);
+                for (int ks = 0; ks < 4; ++ks)   // 16 of the 64 head columns (8 TMEM columns of Q) per instruction
+                    umma_f16_ta(tmem + (t_s & 1) * kTileK, tmem + kColQ + ks * 8, dk + ks * 2, idesc_s, ks > 0);
                 umma_commit(bar_s + (t_s & 1));
+                umma_commit(bar_kfree + s);
                 ++t_s;
                 w_s.next();
                 return true;
             };
-            ok = ptx::mbar_wait(bar_q, 0);
+            ok = ptx::mbar_wait(bar_qt, 0);   // Q is in TMEM
+            tc_fence_after();
             if (ok && !w_s.done()) ok = issue_s();
-            for (int t = 0; ok && !w_pv.done(); ++t, w_pv.next()) {
+            for (int t = 0; ok && t < t_s; ++t) {
                 // the next scores first: their S buffer was released by p(t-1), waited for last round
                 if (!w_s.done() && !(ok = issue_s())) break;
-                if (!(ok = ptx::mbar_wait(bar_p + (t & 1), (t >> 1) & 1))) break;   // P(t) is in shared memory
+                const int s = t % kKvStages;
+                if (!(ok = ptx::mbar_wait(bar_v + s, (t / kKvStages) & 1))) break;
+                if (!(ok = ptx::mbar_wait(bar_p + (t & 1), (t >> 1) & 1))) break;   // P(t) is in TMEM
                 tc_fence_after();
-                const uint32_t v_addr = ptx::smem_u32(sKV + (t % kKvStages) * kStage) + kTileK * kRowBytes;
-                const uint32_t pa = p_addr + (t & 1) * kTileQ * kRowBytes;
+                const uint64_t dv = dkv + (uint64_t)((s * kStage + kTileK * kRowBytes) >> 4);
+                const uint32_t tp = tmem + (t & 1) * kTileK;   // P(t): 64 weights of a row in 32 columns
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)   // O += P V, 16 of the 64 keys per instruction
-                    umma_f16(tmem + kColO, smem_desc(pa + ks * 32), smem_desc(v_addr + ks * 16 * kRowBytes),
-                             idesc_pv, t > 0 || ks > 0);
+                    umma_f16_ta(tmem + kColO, tp + ks * 8, dv + ks * ((16 * kRowBytes) >> 4), idesc_pv, t > 0 || ks > 0);
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)   // l += P 1
-                    umma_f16(tmem + kColSum, smem_desc(pa + ks * 32), smem_desc(ones_addr + ks * 32), idesc_sum,
-                             t > 0 || ks > 0);
-                umma_commit(bar_o);
-                // stage t % 3 is free once P V(t) has read V: refill it with chunk t + 3
-                if (!w_load.done()) {
-                    if (!(ok = ptx::mbar_wait(bar_o, t & 1))) break;
-                    issue_load();
-                }
+                    umma_f16_ta(tmem + kColSum, tp + ks * 8, dones + ks * 2, idesc_sum, t > 0 || ks > 0);
+                umma_commit(bar_o + (t & 1));
+                umma_commit(bar_vfree + s);
             }
-            // bar_o's parity tells two states apart, enough inside the walk (a softmax warp is at most one
-            // product behind); the end of the walk gets a barrier of its own
+            // each bar_o barrier sees every other product, so its parity names one product for a
+            // waiter that is at most one product behind; the end of the walk gets a barrier of its own
             if (ok) umma_commit(bar_fin);
             if (!ok) atomicExch(&g_umma_status, 1);
             // every softmax warp has read its last TMEM values before the columns are freed
@@ -399,21 +434,36 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     float m_run = -INFINITY;   // reference maximum of the row's weights (raw score units); -inf: no key yet
     bool ok = true;
 
+    // the query row, from the swizzled tile the TMA wrote, into TMEM: the A operand of every S product
+    ok = ptx::mbar_wait(bar_q, 0);
+    {
+        uint32_t qv[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(sQ + r * kRowBytes + ((c ^ (r & 7)) << 4));
+            qv[4 * c] = v.x; qv[4 * c + 1] = v.y; qv[4 * c + 2] = v.z; qv[4 * c + 3] = v.w;
+        }
+        tmem_st32(t_lane + kColQ, qv);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0 && ok) ptx::mbar_arrive(bar_qt);
+    }
+
     ChunkWalk w;
     if (MODE != kModeBlock) w.init_range(range_lo, range_hi);
     else w.init(P, q0);
     // global-row pass: a warp takes part iff any of its 32 rows is a real global position
     const bool warp_has_rows = MODE != kModeGlobalRows || q0 + warp * 32 < P.n_global;
-    int zeroed = 0;            // bit i: this row of P buffer i holds zeros
     int t = 0;
-    for (; !w.done(); ++t, w.next()) {
+    for (; ok && !w.done(); ++t) {
         const int kb = w.key_base();
         const bool mine = MODE == kModeGlobalRows ? warp_has_rows : (w.flags >> half) & 1;   // uniform within a warp (dense: always)
+        w.next();   // the layout reads for the next step are in flight during this one
         if (!(ok = ptx::mbar_wait(bar_s + (t & 1), (t >> 1) & 1))) break;
         tc_fence_after();
-        uint8_t *p_row = sP + (t & 1) * kTileQ * kRowBytes + r * kRowBytes;
+        const uint32_t s_addr = t_lane + (t & 1) * kTileK;   // S(t), and P(t) over its first 32 columns
         if (mine) {
-            const uint32_t s_addr = t_lane + (t & 1) * kTileK;
             // keys this row may use in the chunk: j < j_end
             int j_end = min(kTileK, (MODE == kModeGlobalRows ? range_hi : P.Skv) - kb);
             if (MODE != kModeGlobalRows && P.causal) j_end = min(j_end, p - kb + 1);
@@ -439,21 +489,19 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const float alpha = rescale ? ptx::ex2((m_run - mx) * P.sl2) : 1.f;
             if (grow) m_run = mx;
             const float mus = (m_run == -INFINITY ? 0.f : m_run) * P.sl2;
-            // weights, packed to the operand type two at a time, into the swizzled P row
+            // weights, packed to the operand type two at a time: column i of P holds keys 2i and 2i+1
+            uint32_t pk[32];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {   // eight 16-byte pieces = columns 8q .. 8q + 7
-                uint32_t pk[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    float x0, x1;
-                    ffma2(x0, x1, s[8 * q + 2 * i], s[8 * q + 2 * i + 1], P.sl2, -mus);
-                    pk[i] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
-                }
-                *reinterpret_cast<uint4 *>(p_row + ((q ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            for (int i = 0; i < 32; ++i) {
+                float x0, x1;
+                ffma2(x0, x1, s[2 * i], s[2 * i + 1], P.sl2, -mus);
+                if (P.dbg & 2) pk[i] = __float_as_uint(x0) ^ __float_as_uint(x1);
+                else pk[i] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
             }
+            tmem_st32(s_addr, pk);
             if (__any_sync(0xffffffffu, rescale)) {
                 // O and l hold the chunks up to t-1: wait for P V(t-1), then scale this row in place
-                if (!(ok = ptx::mbar_wait(bar_o, (t - 1) & 1))) break;
+                if (!(ok = ptx::mbar_wait(bar_o + ((t - 1) & 1), ((t - 1) >> 1) & 1))) break;
                 tc_fence_after();
                 float part[64], l_part;
                 tmem_ld64_and_1(t_lane + kColO, part, t_lane + kColSum, l_part);
@@ -461,16 +509,16 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 for (int i = 0; i < 64; i += 2) fmul2(part[i], part[i + 1], part[i], part[i + 1], alpha);
                 tmem_st64(t_lane + kColO, part);
                 tmem_st1(t_lane + kColSum, l_part * alpha);
-                tmem_wait_st();
             }
-            zeroed &= ~(1 << (t & 1));
-        } else if (!((zeroed >> (t & 1)) & 1)) {
-            // this half sits the chunk out: its rows of P must add nothing to O and l
+            tmem_wait_st();
+        } else {
+            // this half sits the chunk out: its rows of P (scores at this point) must add nothing to O and l
+            uint32_t z[32];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4 *>(p_row + (q << 4)) = make_uint4(0, 0, 0, 0);
-            zeroed |= 1 << (t & 1);
+            for (int i = 0; i < 32; ++i) z[i] = 0u;
+            tmem_st32(s_addr, z);
+            tmem_wait_st();
         }
-        ptx::fence_proxy_async_smem();   // the tensor core reads P through the async proxy
         tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(bar_p + (t & 1));
@@ -481,9 +529,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (ok && t >= 1) {
         ok = ptx::mbar_wait(bar_fin, 0);
         tc_fence_after();
-        if (ok) {
-            tmem_ld64_and_1(t_lane + kColO, o, t_lane + kColSum, l_run);
-        }
+        if (ok) tmem_ld64_and_1(t_lane + kColO, o, t_lane + kColSum, l_run);
     }
     if (!ok || t == 0) {
 #pragma unroll
@@ -592,6 +638,7 @@ int launch_dense_t(const Problem &p, bool causal) {
     up.block = kTileK; up.per_blk = 1; up.causal = causal; up.n_qblocks = 0; up.rowptr = up.colidx = nullptr;
     up.sl2 = p.scale * 1.4426950408889634f;
     up.n_global = 0; up.gidx = nullptr; up.split_len = up.n_splits = up.ng_pad = 0; up.partial = nullptr;
+    { const char *e = std::getenv("MAT_UMMA_DEBUG"); up.dbg = e ? std::atoi(e) : 0; }
     auto kern = umma_block_fwd_kernel<T, kModeDense>;
     if (int rc = ensure_dynamic_smem((const void *)kern, kSmemBytes, "cudaFuncSetAttribute(umma dense)")) return rc;
     const dim3 grid((unsigned)p.H, (unsigned)((p.Sq + kTileQ - 1) / kTileQ), (unsigned)p.B);
