@@ -17,7 +17,9 @@
 //   load warp (warp 9, one lane):     TMA K/V chunk -> smem (3 stages each)
 //   MMA warp (warp 8, one lane):      S = Q K^T      tcgen05.mma 128x64x16 x4 -> TMEM S buffer (two of them)
 //                                     O += P V       tcgen05.mma 128x64x16 x4 -> TMEM O (accumulates in place)
-//                                     l += P 1       tcgen05.mma 128x16x16 x4 -> TMEM row sums
+//                                     (the same products also give l += P 1: B is widened to 80
+//                                     columns whose last 16 read a block of ones, so the row sums
+//                                     land in the 16 TMEM columns after O)
 //   softmax warps (warps 0-7):        two threads per query row (warps w and w+4 reach the same 32 TMEM
 //                                     lanes): each loads the row's 64 scores, masks, takes the row
 //                                     maximum, and writes its half (32 keys) of P = 2^(s - m) as bf16
@@ -52,7 +54,7 @@ constexpr int kTileQ = 128;     // query rows per CTA (UMMA M)
 constexpr int kTileK = 64;      // keys per step (UMMA N for S, K extent for P V)
 constexpr int kTmemCols = 256;  // S buffers in [0,128), O in [128,192), row sums in [192,208), Q in [208,240)
 constexpr int kColO = 128, kColSum = 192, kColQ = 208;   // Q: 64 values of a row in 32 columns
-constexpr int kSumN = 16;       // narrowest N of an M = 128 instruction; column 0 is read
+constexpr int kSumN = 16;       // N grows in steps of 16 for M = 128; column 0 of the extra 16 is read
 constexpr float kLazyLog2 = 1.f;  // a row's reference maximum moves when the scores outgrow it by 2^1
 
 __device__ int g_umma_status = 0;
@@ -169,10 +171,11 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // groups 1024 bytes apart (the layout a {64, rows} TMA box with SWIZZLE_128B produces, and the one
 // the softmax warps write P in).  K-major operands step 32 bytes per K slice of 16 elements;
 // the MN-major operand (V as the B matrix of P V) steps 16 rows = 2048 bytes.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr) {
+__device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr, uint32_t lead16 = 1) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);   // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                        // leading byte offset (unused with one swizzle atom)
+    d |= (uint64_t)(lead16 & 0x3FFF) << 16;        // leading byte offset, 16-byte units: the next 64-wide block
+                                                   // of an MN-major operand (unused with one swizzle atom)
     d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset: next 8-row group
     d |= (uint64_t)1 << 46;                        // descriptor version of this architecture
     d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
@@ -373,10 +376,10 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             ChunkWalk w_s;     // only counts the chunks here
             if (MODE != kModeBlock) w_s.init_range(range_lo, range_hi);
             else w_s.init(P, q0);
-            const uint32_t idesc_s = instr_desc<T>(false), idesc_pv = instr_desc<T>(true),
-                           idesc_sum = instr_desc<T>(false, kSumN);
+            const uint32_t idesc_s = instr_desc<T>(false), idesc_pv = instr_desc<T>(true, kTileK + kSumN);
             // descriptors differ from step to step only in the start address field (16-byte units)
-            const uint64_t dkv = smem_desc(ptx::smem_u32(sKV)), dones = smem_desc(ptx::smem_u32(sOnes));
+            const uint32_t kv_addr = ptx::smem_u32(sKV), ones_addr = ptx::smem_u32(sOnes);
+            const uint64_t dkv = smem_desc(kv_addr);
             int t_s = 0;
             auto issue_s = [&]() -> bool {   // S(t_s) = Q K^T into S buffer t_s & 1
                 const int s = t_s % kKvStages;
@@ -402,14 +405,15 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 if (!(ok = ptx::mbar_wait(bar_v + s, (t / kKvStages) & 1))) break;
                 if (!(ok = ptx::mbar_wait(bar_p + (t & 1), (t >> 1) & 1))) break;   // P(t) is in TMEM
                 tc_fence_after();
-                const uint64_t dv = dkv + (uint64_t)((s * kStage + kTileK * kRowBytes) >> 4);
+                const uint32_t v_addr = kv_addr + s * kStage + kTileK * kRowBytes;
                 const uint32_t tp = tmem + (t & 1) * kTileK;   // P(t): 64 weights of a row in 32 columns
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)   // O += P V, 16 of the 64 keys per instruction
-                    umma_f16_ta(tmem + kColO, tp + ks * 8, dv + ks * ((16 * kRowBytes) >> 4), idesc_pv, t > 0 || ks > 0);
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks)   // l += P 1
-                    umma_f16_ta(tmem + kColSum, tp + ks * 8, dones + ks * 2, idesc_sum, t > 0 || ks > 0);
+                for (int ks = 0; ks < 4; ++ks) {   // [O | l] += P [V | 1], 16 of the 64 keys per instruction
+                    // B is 16 keys x 80 columns: the 64 head columns from the V stage, then a second
+                    // 64-wide block (16 of it used) that the leading-dimension offset points at the ones
+                    const uint32_t vk = v_addr + ks * 16 * kRowBytes;
+                    umma_f16_ta(tmem + kColO, tp + ks * 8, smem_desc(vk, (ones_addr - vk) >> 4), idesc_pv, t > 0 || ks > 0);
+                }
                 umma_commit(bar_o + (t & 1));
                 umma_commit(bar_vfree + s);
             }
