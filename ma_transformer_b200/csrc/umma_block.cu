@@ -52,7 +52,7 @@ namespace {
 constexpr int kRowBytes = 128;
 constexpr int kTileQ = 128;     // query rows per CTA (UMMA M)
 constexpr int kTileK = 64;      // keys per step (UMMA N for S, K extent for P V)
-constexpr int kTmemCols = 256;  // S buffers in [0,128), O in [128,192), row sums in [192,208), Q in [208,240)
+// TMEM columns of one tile (256 allocated): S buffers in [0,128), O in [128,192), row sums in [192,208), Q in [208,240)
 constexpr int kColO = 128, kColSum = 192, kColQ = 208;   // Q: 64 values of a row in 32 columns
 constexpr int kSumN = 16;       // N grows in steps of 16 for M = 128; column 0 of the extra 16 is read
 constexpr float kLazyLog2 = 1.f;  // a row's reference maximum moves when the scores outgrow it by 2^1
@@ -73,7 +73,6 @@ struct UmmaParams {
     int32_t n_global;
     const int64_t *gidx;
     int32_t split_len, n_splits, ng_pad;
-    int32_t dbg = 0;
     float *partial;   // [B, H, n_splits, ng_pad, kPartialStride]: max, sum, unnormalised output
 };
 
@@ -195,121 +194,152 @@ __device__ __forceinline__ uint32_t instr_desc(bool b_mn_major, int n = kTileK) 
     return d;
 }
 
-// Ascending merge of the key blocks of the two layout rows a CTA covers, 64 keys per step.
+// Ascending merge of the key blocks of the layout rows a CTA covers (one per 64-row half of each
+// 128-row tile), 64 keys per step.  Column ids ascend within a layout row, so the union is a merge
+// that every thread needing it performs identically.
+template <int NH>
 struct ChunkWalk {
     const int32_t *colidx;
-    int ia, ea, ib, eb;  // cursors / ends of half A's and half B's row
+    int it[NH], en[NH];  // cursor / end of each half's layout row (empty for a half that shares the row of an earlier half)
+    int rep[NH];         // the first half that lies in the same layout row
     int sub, per_blk, block;
     int cur;             // current key block, -1 when exhausted
-    int flags;           // bit 0: half A holds it, bit 1: half B
+    int hit;             // bit i: half i's own cursor stands on the current block
+    int flags;           // bit i: half i holds the current block
     __device__ __forceinline__ void init(const UmmaParams &P, int q0) {
         colidx = P.colidx;
         per_blk = P.per_blk;
         block = P.block;
-        const int64_t ra = (int64_t)((uint32_t)(q0 + P.off) / (uint32_t)P.block);
-        const int64_t rb = (int64_t)((uint32_t)(q0 + 64 + P.off) / (uint32_t)P.block);
-        ia = ea = ib = eb = 0;
-        if (ra < P.n_qblocks) { ia = P.rowptr[ra]; ea = P.rowptr[ra + 1]; }
-        if (q0 + 64 < P.Sq && rb < P.n_qblocks) { ib = P.rowptr[rb]; eb = P.rowptr[rb + 1]; }
-        same = ra == rb;
-        if (same) { ib = eb = 0; }
+        int64_t prev_row = -1;
+        int prev_i = 0;
+#pragma unroll
+        for (int i = 0; i < NH; ++i) {
+            it[i] = en[i] = 0;
+            rep[i] = i;
+            const int64_t row = (int64_t)((uint32_t)(q0 + 64 * i + P.off) / (uint32_t)P.block);
+            if (i > 0 && row == prev_row) { rep[i] = prev_i; continue; }
+            if (q0 + 64 * i < P.Sq && row < P.n_qblocks) { it[i] = P.rowptr[row]; en[i] = P.rowptr[row + 1]; }
+            prev_row = row;
+            prev_i = i;
+        }
         sub = 0;
         load();
     }
-    bool same;  // both halves lie in one layout row
     __device__ __forceinline__ void load() {
-        const int ca = ia < ea ? __ldg(colidx + ia) : INT32_MAX;
-        const int cb = ib < eb ? __ldg(colidx + ib) : INT32_MAX;
-        const int c = min(ca, cb);
-        if (c == INT32_MAX) { cur = -1; flags = 0; return; }
+        int col[NH];
+        int c = INT32_MAX;
+#pragma unroll
+        for (int i = 0; i < NH; ++i) {
+            col[i] = it[i] < en[i] ? __ldg(colidx + it[i]) : INT32_MAX;
+            c = min(c, col[i]);
+        }
+        if (c == INT32_MAX) { cur = -1; hit = flags = 0; return; }
         cur = c;
-        flags = (ca == c ? 1 : 0) | (cb == c ? 2 : 0);
-        if (same) flags = 3;
+        hit = flags = 0;
+#pragma unroll
+        for (int i = 0; i < NH; ++i) hit |= (col[i] == c ? 1 : 0) << i;
+#pragma unroll
+        for (int i = 0; i < NH; ++i) flags |= ((hit >> rep[i]) & 1) << i;
     }
-    // a plain key range [lo, hi) instead of a layout: 64-key steps, both halves take part
+    // a plain key range [lo, hi) instead of a layout: 64-key steps, every half takes part
     __device__ __forceinline__ void init_range(int lo, int hi) {
         colidx = nullptr;
-        block = kTileK; per_blk = 1; sub = 0; same = true;
-        ia = lo / kTileK;                    // lo is a multiple of 64
-        ea = (hi + kTileK - 1) / kTileK;
-        ib = eb = 0;
-        cur = ia < ea ? ia : -1;
-        flags = 3;
+        block = kTileK; per_blk = 1; sub = 0;
+#pragma unroll
+        for (int i = 0; i < NH; ++i) { it[i] = en[i] = 0; rep[i] = 0; }
+        it[0] = lo / kTileK;                    // lo is a multiple of 64
+        en[0] = (hi + kTileK - 1) / kTileK;
+        cur = it[0] < en[0] ? it[0] : -1;
+        hit = 1;
+        flags = (1 << NH) - 1;
     }
     __device__ __forceinline__ bool done() const { return cur < 0; }
     __device__ __forceinline__ int key_base() const { return cur * block + sub * kTileK; }
     __device__ __forceinline__ void next() {
-        if (colidx == nullptr) { cur = ++ia < ea ? ia : -1; return; }
+        if (colidx == nullptr) { cur = ++it[0] < en[0] ? it[0] : -1; return; }
         if (++sub < per_blk) return;
         sub = 0;
-        if (flags & 1 && !same) ++ia;
-        if (same) ++ia;
-        if (flags & 2 && !same) ++ib;
+#pragma unroll
+        for (int i = 0; i < NH; ++i) it[i] += (hit >> i) & 1;
         load();
     }
 };
 
-constexpr int kSoftmaxWarps = 4;
-constexpr int kThreads = (kSoftmaxWarps + 2) * 32;  // 4 softmax warps + MMA warp + load warp
-constexpr int kKvStages = 5;
+// NT = 128-row query tiles per CTA.  One tile: 256 TMEM columns, two CTAs per SM.  Two tiles: all 512
+// columns, one CTA per SM, and every K/V chunk fetched from L2 serves 256 query rows instead of 128.
+constexpr int kSoftmaxWarpsPerTile = 4;
+template <int NT> struct Cfg {
+    static constexpr int kSoftmaxWarps = kSoftmaxWarpsPerTile * NT;
+    static constexpr int kThreads = (kSoftmaxWarps + NT + 1) * 32;   // softmax warps, one MMA warp per tile, load warp
+    static constexpr int kKvStages = NT == 1 ? 5 : 8;
+    static constexpr int kTmemCols = 256 * NT;
+    static constexpr int kBars = 2 + NT * 9 + 4 * kKvStages;
+    static constexpr size_t kSmemBytes = 1024 + (size_t)NT * kTileQ * kRowBytes /*Q*/ +
+                                         (size_t)kKvStages * 2 * kTileK * kRowBytes + kSumN * kRowBytes +
+                                         kBars * 8 + 16 /*tmem address*/;
+};
 constexpr int kStage = 2 * kTileK * kRowBytes;  // one K/V stage: K then V
-constexpr int kOnesBytes = kSumN * kRowBytes;   // B operand of the row-sum product: 16 rows of ones
-constexpr size_t kSmemBytes = 1024 + kTileQ * kRowBytes /*Q*/ + kKvStages * kStage + kOnesBytes +
-                              512 /*barriers, tmem address*/;
+constexpr int kOnesBytes = kSumN * kRowBytes;   // the second 64-wide block of the P V product's B operand: ones
 
-// The step pipeline (t = index of the 64-key chunk):
-//   load warp: K(t) as soon as S(t - kKvStages) has left its stage, V(t) once P V(t - kKvStages) has.
+// The step pipeline (t = index of the 64-key chunk), per tile:
+//   load warp: K(t) as soon as S(t - kKvStages) has left its stage (in every tile), V(t) once P V(t - kKvStages) has.
 //   MMA warp:  S(t+1) is issued before P V(t), so the tensor core computes the next scores while
 //              the softmax warps work on the current ones; S is double-buffered in TMEM.  Q and P
 //              are A operands read from TMEM: Q is copied there once per tile, P(t) is stored by
 //              the softmax warps over the first 32 columns of the S buffer it was computed from
 //              (S(t+2), which overwrites them, is issued after P V(t) and so runs after it).
 //              Shared memory then carries only K and V (its bandwidth, not the tensor pipe, bounded
-//              the variant that kept Q and P there).  P V(t) and the row-sum product accumulate
-//              into O and l in TMEM (the first chunk overwrites).
+//              the variant that kept Q and P there).  P V(t) accumulates into O and l in TMEM (the
+//              first chunk overwrites).
 //   softmax:   softmax(t) -> store P(t) -> (rarely: wait for P V(t-1), rescale O and l) -> publish.
-template <typename T, int MODE>
-__global__ void __launch_bounds__(kThreads)
+template <typename T, int MODE, int NT>
+__global__ void __launch_bounds__(Cfg<NT>::kThreads)
 umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, T *__restrict__ out, const UmmaParams P) {
+    constexpr int kSoftmaxWarps = Cfg<NT>::kSoftmaxWarps, kKvStages = Cfg<NT>::kKvStages, NH = 2 * NT;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t *sQ = smem;
-    uint8_t *sKV = sQ + kTileQ * kRowBytes;            // stage s: K at +0, V at +8 KB
+    uint8_t *sQ = smem;                                // NT tiles of 128 rows
+    uint8_t *sKV = sQ + NT * kTileQ * kRowBytes;       // stage s: K at +0, V at +8 KB
     uint8_t *sOnes = sKV + kKvStages * kStage;         // 16 rows of ones
     uint64_t *bars = (uint64_t *)(sOnes + kOnesBytes);
-    uint64_t *bar_q = bars, *bar_qt = bars + 1, *bar_fin = bars + 2, *bar_done = bars + 3, *bar_s = bars + 4 /*[2]*/,
-             *bar_p = bars + 6 /*[2]*/, *bar_o = bars + 8 /*[2]*/, *bar_k = bars + 10 /*[kKvStages]*/,
-             *bar_v = bar_k + kKvStages, *bar_kfree = bar_v + kKvStages, *bar_vfree = bar_kfree + kKvStages;
-    uint32_t *tmem_slot = (uint32_t *)(bar_vfree + kKvStages);
+    // shared by the tiles: Q arrival, K/V arrival and release per stage
+    uint64_t *bar_q = bars, *bar_k = bars + 2, *bar_v = bar_k + kKvStages, *bar_kfree = bar_v + kKvStages,
+             *bar_vfree = bar_kfree + kKvStages;
+    // per tile (9 each): Q in TMEM, end of walk, TMEM reads done, S ready [2], P ready [2], P V done [2]
+    uint64_t *tile_bars = bar_vfree + kKvStages;
+    uint32_t *tmem_slot = (uint32_t *)(tile_bars + 9 * NT);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x, b = blockIdx.z;
     // global-row pass: blockIdx.y = (128-row tile of the global-position list) * n_splits + key split
     const int split = MODE == kModeGlobalRows ? blockIdx.y % P.n_splits : 0;
-    const int q0 = (MODE == kModeGlobalRows ? blockIdx.y / P.n_splits : blockIdx.y) * kTileQ;
-    // key range of the tile: a split of the sequence (global rows), or everything / everything up to
-    // the tile's last row (dense and causal dense)
+    const int q0 = (MODE == kModeGlobalRows ? blockIdx.y / P.n_splits : blockIdx.y) * (NT * kTileQ);
+    // key range of the CTA: a split of the sequence (global rows), or everything / everything up to
+    // the CTA's last row (dense and causal dense)
     const int range_lo = MODE == kModeGlobalRows ? split * P.split_len : 0;
     const int range_hi = MODE == kModeGlobalRows ? min(range_lo + P.split_len, P.Skv)
-                       : (P.causal ? min(P.Skv, q0 + P.off + kTileQ) : P.Skv);
+                       : (P.causal ? min(P.Skv, q0 + P.off + NT * kTileQ) : P.Skv);
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(bar_q, 1);
-        ptx::mbar_init(bar_qt, kSoftmaxWarps);
         for (int i = 0; i < kKvStages; ++i) {
             ptx::mbar_init(bar_k + i, 1);
             ptx::mbar_init(bar_v + i, 1);
-            ptx::mbar_init(bar_kfree + i, 1);
-            ptx::mbar_init(bar_vfree + i, 1);
+            ptx::mbar_init(bar_kfree + i, NT);
+            ptx::mbar_init(bar_vfree + i, NT);
         }
-        for (int i = 0; i < 2; ++i) {
-            ptx::mbar_init(bar_s + i, 1);
-            ptx::mbar_init(bar_p + i, kSoftmaxWarps);
-            ptx::mbar_init(bar_o + i, 1);
+        for (int tl = 0; tl < NT; ++tl) {
+            uint64_t *tb = tile_bars + 9 * tl;
+            ptx::mbar_init(tb + 0, kSoftmaxWarpsPerTile);   // Q in TMEM
+            ptx::mbar_init(tb + 1, 1);                      // end of walk
+            ptx::mbar_init(tb + 2, kSoftmaxWarpsPerTile);   // TMEM reads done
+            for (int i = 0; i < 2; ++i) {
+                ptx::mbar_init(tb + 3 + i, 1);                      // S ready
+                ptx::mbar_init(tb + 5 + i, kSoftmaxWarpsPerTile);   // P ready
+                ptx::mbar_init(tb + 7 + i, 1);                      // P V done
+            }
         }
-        ptx::mbar_init(bar_fin, 1);
-        ptx::mbar_init(bar_done, kSoftmaxWarps);
         ptx::fence_barrier_init();
     }
     if (threadIdx.x < kOnesBytes / 16) {
@@ -318,34 +348,36 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         ptx::fence_proxy_async_smem();
     }
     if (warp == kSoftmaxWarps) {
-        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_alloc(tmem_slot, Cfg<NT>::kTmemCols);
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
-    // TMEM columns: S buffer i at 64*i (P(t) over its first 32), O at kColO, row sums at kColSum, Q at kColQ
+    const uint32_t tmem_base = *tmem_slot;
+    // TMEM columns of tile i start at 256 i: S buffer j at 64 j (P(t) over its first 32), O at kColO,
+    // row sums at kColSum, Q at kColQ
 
-    if (warp == kSoftmaxWarps + 1) {
+    if (warp == kSoftmaxWarps + NT) {
         // ================= load warp: Q once, then K and V chunk by chunk =================
         if (lane == 0) {
             bool ok = true;
-            ChunkWalk w_k, w_v;   // K runs one chunk ahead of V: its stage is free earlier (after S, not after P V)
+            ChunkWalk<NH> w_k, w_v;   // K runs one chunk ahead of V: its stage is free earlier (after S, not after P V)
             if (MODE != kModeBlock) w_k.init_range(range_lo, range_hi);
             else w_k.init(P, q0);
             w_v = w_k;
-            ptx::mbar_expect_tx(bar_q, kTileQ * kRowBytes);
+            ptx::mbar_expect_tx(bar_q, NT * kTileQ * kRowBytes);
             if (MODE == kModeGlobalRows) {
                 // map_q is a one-row view here: row r of the tile is the query at global position
                 // gidx[q0 + r]; slots past the list read out of bounds, i.e. zeros
-                for (int r = 0; r < kTileQ; ++r) {
+                for (int r = 0; r < NT * kTileQ; ++r) {
                     const int e = q0 + r;
                     const int row = e < P.n_global ? (P.gidx ? (int)P.gidx[e] : e) : P.Sq;   // no list: already gathered
                     ptx::tma_load_4d(sQ + r * kRowBytes, &map_q, bar_q, 0, h, row, b);
                 }
             } else {
-                ptx::tma_load_4d(sQ, &map_q, bar_q, 0, h, q0, b);
+                for (int tl = 0; tl < NT; ++tl)
+                    ptx::tma_load_4d(sQ + tl * kTileQ * kRowBytes, &map_q, bar_q, 0, h, q0 + tl * kTileQ, b);
             }
             int c_k = 0;
             auto load_k = [&]() -> bool {   // K(c_k) once S(c_k - kKvStages) has left the stage
@@ -369,11 +401,17 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         return;
     }
-    if (warp == kSoftmaxWarps) {
-        // ================= MMA warp: one lane issues every tcgen05.mma of the tile =================
+    // everything below belongs to one tile
+    const int tile = warp >= kSoftmaxWarps ? warp - kSoftmaxWarps : warp / kSoftmaxWarpsPerTile;
+    const uint32_t tmem = tmem_base + 256 * tile;
+    uint64_t *tb = tile_bars + 9 * tile;
+    uint64_t *bar_qt = tb, *bar_fin = tb + 1, *bar_done = tb + 2, *bar_s = tb + 3, *bar_p = tb + 5, *bar_o = tb + 7;
+
+    if (warp >= kSoftmaxWarps) {
+        // ================= MMA warp of the tile: one lane issues every tcgen05.mma =================
         if (lane == 0) {
             bool ok = true;
-            ChunkWalk w_s;     // only counts the chunks here
+            ChunkWalk<NH> w_s;     // only counts the chunks here
             if (MODE != kModeBlock) w_s.init_range(range_lo, range_hi);
             else w_s.init(P, q0);
             const uint32_t idesc_s = instr_desc<T>(false), idesc_pv = instr_desc<T>(true, kTileK + kSumN);
@@ -421,30 +459,36 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             // waiter that is at most one product behind; the end of the walk gets a barrier of its own
             if (ok) umma_commit(bar_fin);
             if (!ok) atomicExch(&g_umma_status, 1);
-            // every softmax warp has read its last TMEM values before the columns are freed
-            if (!ptx::mbar_wait(bar_done, 0)) atomicExch(&g_umma_status, 1);
+            // every softmax warp of every tile has read its last TMEM values before the columns are freed
+            for (int tl = 0; tl < NT; ++tl)
+                if (warp == kSoftmaxWarps && !ptx::mbar_wait(tile_bars + 9 * tl + 2, 0)) atomicExch(&g_umma_status, 1);
         }
         __syncwarp();
-        tc_fence_after();
-        tmem_dealloc(tmem, kTmemCols);
+        if (warp == kSoftmaxWarps) {   // the allocating warp frees
+            tc_fence_after();
+            tmem_dealloc(tmem_base, Cfg<NT>::kTmemCols);
+        }
         return;
     }
 
-    // ================= softmax warps: thread r owns query row r of the tile =================
-    const int r = threadIdx.x;             // 0..127 == TMEM lane
-    const int half = r >> 6;
-    const int p = q0 + r + P.off;          // key-coordinate position of this row
-    const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);
+    // ================= softmax warps: thread r owns query row r of its tile =================
+    const int quad = warp % kSoftmaxWarpsPerTile;   // == warp % 4: the TMEM lanes this warp may access
+    const int r = quad * 32 + lane;        // row of the tile == TMEM lane
+    const int tq0 = q0 + tile * kTileQ;    // first row of the tile
+    const int half = tile * 2 + (r >> 6);
+    const int p = tq0 + r + P.off;         // key-coordinate position of this row
+    const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
     float m_run = -INFINITY;   // reference maximum of the row's weights (raw score units); -inf: no key yet
     bool ok = true;
 
     // the query row, from the swizzled tile the TMA wrote, into TMEM: the A operand of every S product
     ok = ptx::mbar_wait(bar_q, 0);
     {
+        const uint8_t *q_row = sQ + (tile * kTileQ + r) * kRowBytes;
         uint32_t qv[32];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-            const uint4 v = *reinterpret_cast<const uint4 *>(sQ + r * kRowBytes + ((c ^ (r & 7)) << 4));
+            const uint4 v = *reinterpret_cast<const uint4 *>(q_row + ((c ^ (r & 7)) << 4));
             qv[4 * c] = v.x; qv[4 * c + 1] = v.y; qv[4 * c + 2] = v.z; qv[4 * c + 3] = v.w;
         }
         tmem_st32(t_lane + kColQ, qv);
@@ -454,11 +498,11 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (lane == 0 && ok) ptx::mbar_arrive(bar_qt);
     }
 
-    ChunkWalk w;
+    ChunkWalk<NH> w;
     if (MODE != kModeBlock) w.init_range(range_lo, range_hi);
     else w.init(P, q0);
     // global-row pass: a warp takes part iff any of its 32 rows is a real global position
-    const bool warp_has_rows = MODE != kModeGlobalRows || q0 + warp * 32 < P.n_global;
+    const bool warp_has_rows = MODE != kModeGlobalRows || tq0 + quad * 32 < P.n_global;
     int t = 0;
     for (; ok && !w.done(); ++t) {
         const int kb = w.key_base();
@@ -499,8 +543,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             for (int i = 0; i < 32; ++i) {
                 float x0, x1;
                 ffma2(x0, x1, s[2 * i], s[2 * i + 1], P.sl2, -mus);
-                if (P.dbg & 2) pk[i] = __float_as_uint(x0) ^ __float_as_uint(x1);
-                else pk[i] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
+                pk[i] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
             }
             tmem_st32(s_addr, pk);
             if (__any_sync(0xffffffffu, rescale)) {
@@ -546,9 +589,9 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (lane == 0) ptx::mbar_arrive(bar_done);
 
     if (MODE == kModeGlobalRows) {
-        if (ok && q0 + r < P.n_global) {
+        if (ok && tq0 + r < P.n_global) {
             float *pr = P.partial +
-                        ((((int64_t)b * P.H + h) * P.n_splits + split) * P.ng_pad + q0 + r) * kPartialStride;
+                        ((((int64_t)b * P.H + h) * P.n_splits + split) * P.ng_pad + tq0 + r) * kPartialStride;
             pr[0] = m_run;
             pr[1] = l_run;
 #pragma unroll
@@ -556,9 +599,9 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         return;
     }
-    if (ok && q0 + r < P.Sq) {
+    if (ok && tq0 + r < P.Sq) {
         const float inv = l_run > 0.f ? __frcp_rn(l_run) : 0.f;
-        T *dst = out + (((int64_t)b * P.Sq + q0 + r) * P.H + h) * 64;
+        T *dst = out + (((int64_t)b * P.Sq + tq0 + r) * P.H + h) * 64;
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
             uint4 v;
@@ -602,6 +645,25 @@ int make_map(CUtensorMap *m, const void *base, int dtype, int64_t H, int64_t S, 
     return MAT_OK;
 }
 
+// One 128-row tile per CTA (two CTAs per SM) is the measured optimum: two tiles per CTA sharing the
+// K/V stages fetch every chunk from L2 half as often but came out slower (dense 16K tokens x 8 heads:
+// 0.91 ms against 0.83 ms; the 16K block-sparse workload 267 us against 193 us), so the L2 -> shared
+// memory traffic is not what bounds the walk.  MAT_UMMA_TILES=2 selects the two-tile variant.
+int tiles_per_cta() {
+    const char *e = std::getenv("MAT_UMMA_TILES");
+    return e && e[0] == '2' ? 2 : 1;
+}
+
+template <typename T, int MODE, int NT>
+int launch_mode(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, T *out, const UmmaParams &up,
+                dim3 grid, cudaStream_t stream, const char *what) {
+    auto kern = umma_block_fwd_kernel<T, MODE, NT>;
+    if (int rc = ensure_dynamic_smem((const void *)kern, Cfg<NT>::kSmemBytes, what)) return rc;
+    kern<<<grid, Cfg<NT>::kThreads, Cfg<NT>::kSmemBytes, stream>>>(mq, mk, mv, out, up);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? MAT_OK : cuda_fail(e, what);
+}
+
 template <typename T>
 int launch_t(const Problem &p) {
     CUtensorMap mq, mk, mv;
@@ -621,14 +683,12 @@ int launch_t(const Problem &p) {
     up.colidx = p.pat.colidx;
     up.sl2 = p.scale * 1.4426950408889634f;
     up.n_global = 0; up.gidx = nullptr; up.split_len = up.n_splits = up.ng_pad = 0; up.partial = nullptr;
-    auto kern = umma_block_fwd_kernel<T, kModeBlock>;
-    if (int rc = ensure_dynamic_smem((const void *)kern, kSmemBytes, "cudaFuncSetAttribute(umma_block_fwd_kernel)")) return rc;
-    const dim3 grid((unsigned)p.H, (unsigned)((p.Sq + kTileQ - 1) / kTileQ), (unsigned)p.B);
-    kern<<<grid, kThreads, kSmemBytes, p.stream>>>(mq, mk, mv, (T *)p.o, up);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e, "umma_block_fwd_kernel launch");
-    note_kernel("umma_block");
-    return MAT_OK;
+    const int nt = tiles_per_cta();
+    const dim3 grid((unsigned)p.H, (unsigned)((p.Sq + nt * kTileQ - 1) / (nt * kTileQ)), (unsigned)p.B);
+    const int rc = nt == 2 ? launch_mode<T, kModeBlock, 2>(mq, mk, mv, (T *)p.o, up, grid, p.stream, "umma block kernel")
+                           : launch_mode<T, kModeBlock, 1>(mq, mk, mv, (T *)p.o, up, grid, p.stream, "umma block kernel");
+    if (rc == MAT_OK) note_kernel("umma_block");
+    return rc;
 }
 
 template <typename T>
@@ -642,15 +702,12 @@ int launch_dense_t(const Problem &p, bool causal) {
     up.block = kTileK; up.per_blk = 1; up.causal = causal; up.n_qblocks = 0; up.rowptr = up.colidx = nullptr;
     up.sl2 = p.scale * 1.4426950408889634f;
     up.n_global = 0; up.gidx = nullptr; up.split_len = up.n_splits = up.ng_pad = 0; up.partial = nullptr;
-    { const char *e = std::getenv("MAT_UMMA_DEBUG"); up.dbg = e ? std::atoi(e) : 0; }
-    auto kern = umma_block_fwd_kernel<T, kModeDense>;
-    if (int rc = ensure_dynamic_smem((const void *)kern, kSmemBytes, "cudaFuncSetAttribute(umma dense)")) return rc;
-    const dim3 grid((unsigned)p.H, (unsigned)((p.Sq + kTileQ - 1) / kTileQ), (unsigned)p.B);
-    kern<<<grid, kThreads, kSmemBytes, p.stream>>>(mq, mk, mv, (T *)p.o, up);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e, "umma dense kernel launch");
-    note_kernel("umma_dense");
-    return MAT_OK;
+    const int nt = tiles_per_cta();
+    const dim3 grid((unsigned)p.H, (unsigned)((p.Sq + nt * kTileQ - 1) / (nt * kTileQ)), (unsigned)p.B);
+    const int rc = nt == 2 ? launch_mode<T, kModeDense, 2>(mq, mk, mv, (T *)p.o, up, grid, p.stream, "umma dense kernel")
+                           : launch_mode<T, kModeDense, 1>(mq, mk, mv, (T *)p.o, up, grid, p.stream, "umma dense kernel");
+    if (rc == MAT_OK) note_kernel("umma_dense");
+    return rc;
 }
 
 template <typename T>
@@ -667,12 +724,8 @@ int launch_global_rows_t(const Problem &p, const GlobalRowSplit &g, float *parti
     up.gidx = p.pat.gidx;
     up.split_len = g.split_len; up.n_splits = g.n_splits; up.ng_pad = g.ng_pad;
     up.partial = partial;
-    auto kern = umma_block_fwd_kernel<T, kModeGlobalRows>;
-    if (int rc = ensure_dynamic_smem((const void *)kern, kSmemBytes, "cudaFuncSetAttribute(umma global rows)")) return rc;
     const dim3 grid((unsigned)p.H, (unsigned)(g.tiles * g.n_splits), (unsigned)p.B);
-    kern<<<grid, kThreads, kSmemBytes, p.stream>>>(mq, mk, mv, (T *)nullptr, up);
-    cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? MAT_OK : cuda_fail(e, "umma global-row kernel launch");
+    return launch_mode<T, kModeGlobalRows, 1>(mq, mk, mv, (T *)nullptr, up, grid, p.stream, "umma global-row kernel");
 }
 
 }  // namespace

@@ -461,6 +461,32 @@ def test_block_layout_on_warp_level_kernel_too(monkeypatch):
     check_close(got, want, torch.bfloat16)
 
 
+@pytest.mark.parametrize("tiles", ["1", "2"])
+def test_tcgen05_tiles_per_cta(monkeypatch, tiles):
+    """The tcgen05 pipeline with one 128-row tile per CTA and with two tiles sharing the K/V stages
+    (MAT_UMMA_TILES overrides the size-based choice): block layouts whose four 64-row halves hold
+    different blocks, ragged ends, block edges of 64, 128 and 256, dense and causal dense."""
+    monkeypatch.setenv("MAT_UMMA_TILES", tiles)
+    for S, block, seed in [(1024, 64, 5), (832, 64, 6), (1280, 128, 7), (1536, 256, 8)]:
+        rp, ci = band_random_block_layout((S + block - 1) // block, 3, 2, seed=seed)
+        spec = PatternSpec.block_sparse(block, rp, ci, causal=True)
+        for dtype in (torch.bfloat16, torch.float16):
+            q, k, v = seeded_qkv(40 + seed, 1, S, 2, 64, dtype)
+            got = run(spec, q, k, v)
+            assert nat.last_kernel() == "umma_block"
+            check_close(got, oracle_out(q, k, v, spec), dtype)
+    spec = PatternSpec.block_sparse(64, [0, 1, 1, 3, 4, 4, 6], [0, 0, 2, 1, 0, 5])   # empty rows among the four halves
+    q, k, v = seeded_qkv(49, 1, 384, 1, 64, torch.bfloat16)
+    got = run(spec, q, k, v)
+    assert torch.count_nonzero(got[:, 64:128]) == 0 and torch.count_nonzero(got[:, 256:320]) == 0
+    check_close(got, oracle_out(q, k, v, spec), torch.bfloat16)
+    for S, causal in [(1024, False), (896, True), (1000, True), (384, False)]:
+        q, k, v = seeded_qkv(50, 1, S, 2, 64, torch.bfloat16)
+        got = ext.dense_forward(q.to(DEV), k.to(DEV), v.to(DEV), causal)
+        assert nat.last_kernel() == "umma_dense"
+        check_close(got, oracle_out(q, k, v, PatternSpec(left=S, right=0 if causal else S)), torch.bfloat16)
+
+
 def test_random_windows_and_offsets_fuzz():
     """Seeded sweep over window shapes, dilations, lengths and shard offsets on the tiled kernel."""
     rng = np.random.default_rng(77)
