@@ -12,7 +12,7 @@ K/V rows they need from the neighbouring GPU inside the kernel (``--halo nccl``
 exchanges them by send/recv instead).  Steps are independent forwards over
 rotating input sets; they are captured in CUDA graphs and alternate over two
 streams (``--lanes``), each with its own output buffer.
-``--workload block|longformer|orderbook`` time the other configurations on one GPU.
+``--workload block|longformer|orderbook|dense`` time the other configurations on one GPU.
 
 Prints ONE JSON line.  ``value`` is tokens/s with inputs resident in HBM, timed
 with CUDA events over exactly K steps (max over ranks); ``e2e`` is the same
@@ -54,6 +54,17 @@ def measured_peak_gbs():
         except Exception:
             pass
     return 6650.0, "fallback"
+
+
+def measured_peak_tflops():
+    """Dense bf16 GEMM throughput of this pool's GPUs (the burst figure: the kernel is timed alone)."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return 1590.0, "fallback"
 
 
 # ---- clocks during the timed region ------------------------------------------------
@@ -454,6 +465,12 @@ def other_workload_arm(args):
         spec = PatternSpec.block_sparse(64, rp, ci, causal=True)
         flops = Bw * Hw * int(rp[-1]) * 4 * 64 ** 3
         name = f"block-sparse fwd B={Bw} N={S} H={Hw} d=64 block=64 band4+2 random causal bf16"
+    elif args.workload == "dense":
+        # the reference's dense_forward (every query over every key), the tensor-bound end of the path
+        Bw, S, Hw = 2, 8192, 8
+        spec = PatternSpec(left=S, right=S)
+        flops = Bw * Hw * 4 * S * S * 64
+        name = f"dense fwd B={Bw} N={S} H={Hw} d=64 bf16"
     else:
         Bw, S, Hw = 2, 32768, 12
         glob = torch.randperm(S, generator=g)[:32].sort().values.numpy()
@@ -480,6 +497,18 @@ def other_workload_arm(args):
     ms = ev0.elapsed_time(ev1) / args.steps
     peak, peak_kind = measured_peak_gbs()
     achieved = nbytes / (ms * 1e-3) / 1e9
+    if args.workload == "dense":
+        tpeak, tkind = measured_peak_tflops()
+        tf = flops / (ms * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "dense attention fwd tokens/s (dense)", "value": Bw * S / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "dtype": "bf16", "data": "synthetic", "config": {"workload": name, "l2": "2 rotating input sets"},
+            "clocks": clocks, "kernel": nat.last_kernel(),
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s", "frac": tf / tpeak,
+                         "peak_source": f"{tkind} dense bf16 GEMM throughput", "flop_per_launch_algorithmic": flops},
+            "device_status": nat.device_status()}), flush=True)
+        return
     print(json.dumps({
         "metric": f"sparse-attn fwd tokens/s ({args.workload})", "value": Bw * S / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
@@ -493,9 +522,9 @@ def other_workload_arm(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="window", choices=["window", "block", "longformer", "orderbook"],
-                    help="window = the headline configuration; block / longformer / orderbook = one-GPU timing of "
-                         "the block-sparse, Longformer and order-book-transformer configurations")
+    ap.add_argument("--workload", default="window", choices=["window", "block", "longformer", "orderbook", "dense"],
+                    help="window = the headline configuration; block / longformer / orderbook / dense = one-GPU timing "
+                         "of the block-sparse, Longformer, order-book-transformer and dense configurations")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
