@@ -110,6 +110,9 @@ class ClockSampler:
             self._thread = threading.Thread(target=self._loop, daemon=True)
             self._thread.start()
 
+    def count_between(self, t0, t1):
+        return sum(1 for (t, _) in list(self.samples) if t0 <= t <= t1)
+
     def stop(self, t0=None, t1=None):
         if self._thread is not None:
             self._stop.set()
@@ -343,7 +346,26 @@ def gpu_arm(args):
     ev1.record()
     barrier()
     t_host1 = time.perf_counter()
+    # A timed region of a few milliseconds is shorter than one NVML poll: keep the identical load
+    # running (untimed) until the sampler has seen it, so that clocks and throttle reasons are read
+    # under the load that was timed.
+    extended = False
+    # (only where a step holds no collective: every rank decides this for itself)
+    if (use_graph or world == 1) and sampler.count_between(t_host0, t_host1) < 3:
+        extended = True
+        t_end = time.perf_counter() + 0.3
+        i = 0
+        while time.perf_counter() < t_end:
+            if use_graph:
+                round_graph.replay()
+            else:
+                step(args.warmup + args.steps + i)
+                i += 1
+        torch.cuda.synchronize()
+        t_host1 = time.perf_counter()
     clocks = sampler.stop(t_host0, t_host1)
+    if extended:
+        clocks["sampled"] = "timed steps plus 0.3 s of the same steps continued untimed (the timed region is shorter than an NVML poll)"
     ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
     n_launch = torch.tensor([launches[0]], device=dev)
     if world > 1:
