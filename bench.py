@@ -329,6 +329,10 @@ def gpu_arm(args):
 
     sampler = ClockSampler(local)
     sampler.start()
+    # the timed region can be a few milliseconds: let the sampling thread in more often than the
+    # interpreter's default 5 ms switch interval
+    switch_interval = sys.getswitchinterval()
+    sys.setswitchinterval(1e-4)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t_host0 = time.perf_counter()
@@ -346,16 +350,16 @@ def gpu_arm(args):
     ev1.record()
     barrier()
     t_host1 = time.perf_counter()
-    # A timed region of a few milliseconds is shorter than one NVML poll: keep the identical load
-    # running (untimed) until the sampler has seen it, so that clocks and throttle reasons are read
-    # under the load that was timed.
+    # If the timed region was still too short for the sampler, keep the identical load running
+    # (untimed) until it has three samples, at most 50 ms, so that clocks and throttle reasons are
+    # read under the load that was timed.
     extended = False
     # (only where a step holds no collective: every rank decides this for itself)
     if (use_graph or world == 1) and sampler.count_between(t_host0, t_host1) < 3:
         extended = True
-        t_end = time.perf_counter() + 0.3
+        t_end = time.perf_counter() + 0.05
         i = 0
-        while time.perf_counter() < t_end:
+        while time.perf_counter() < t_end and sampler.count_between(t_host0, time.perf_counter()) < 3:
             if use_graph:
                 round_graph.replay()
             else:
@@ -364,8 +368,9 @@ def gpu_arm(args):
         torch.cuda.synchronize()
         t_host1 = time.perf_counter()
     clocks = sampler.stop(t_host0, t_host1)
+    sys.setswitchinterval(switch_interval)
     if extended:
-        clocks["sampled"] = "timed steps plus 0.3 s of the same steps continued untimed (the timed region is shorter than an NVML poll)"
+        clocks["sampled"] = "timed steps plus up to 50 ms of the same steps continued untimed (the timed region was shorter than the sampler's reach)"
     ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
     n_launch = torch.tensor([launches[0]], device=dev)
     if world > 1:

@@ -737,10 +737,24 @@ GlobalRowSplit plan_umma_global_rows(const Problem &p) {
     g.tile_rows = kTileQ;
     g.tiles = (int)((p.pat.n_global + kTileQ - 1) / kTileQ);
     g.ng_pad = (int)((p.pat.n_global + 31) / 32 * 32);
+    // Splits of the key axis: as many CTAs as fill whole waves of the resident slots (2 per SM); a
+    // wave that is nearly empty costs as much as a full one.  Cost model: waves x (steps + 4), the
+    // 4 standing for a CTA's start and read-out; at least 8 steps per split.
     const int64_t units = std::max<int64_t>(1, p.B * p.H * g.tiles);
-    const int64_t want = std::max<int64_t>(1, 600 / units);
-    int64_t len = (p.Skv + want - 1) / want;
-    len = std::max<int64_t>(512, (len + kTileK - 1) / kTileK * kTileK);
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t slots = 2 * (int64_t)sms, n_chunks = (p.Skv + kTileK - 1) / kTileK;
+    int64_t best_steps = n_chunks, best_cost = INT64_MAX;
+    for (int64_t w = 1; w <= 4; ++w) {
+        int64_t splits = std::max<int64_t>(1, slots * w / units);
+        splits = std::min(splits, std::max<int64_t>(1, n_chunks / 8));
+        const int64_t steps = (n_chunks + splits - 1) / splits;
+        const int64_t real_splits = (n_chunks + steps - 1) / steps;
+        const int64_t waves = (units * real_splits + slots - 1) / slots;
+        const int64_t cost = waves * (steps + 4);
+        if (cost < best_cost) { best_cost = cost; best_steps = steps; }
+    }
+    const int64_t len = best_steps * kTileK;
     g.split_len = (int)len;
     g.n_splits = (int)((p.Skv + len - 1) / len);
     g.bytes = (size_t)p.B * p.H * g.n_splits * g.ng_pad * kPartialStride * sizeof(float);
