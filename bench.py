@@ -292,6 +292,10 @@ def gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # the clock sampler runs from before the warm-up (its first NVML calls take milliseconds);
+    # only the samples that fall inside the timed region are used
+    sampler = ClockSampler(local)
+    sampler.start()
     for i in range(args.warmup):
         step(i)
     barrier()
@@ -327,8 +331,6 @@ def gpu_arm(args):
         round_graph.replay()      # one untimed round warms the instantiated graphs
         barrier()
 
-    sampler = ClockSampler(local)
-    sampler.start()
     # the timed region can be a few milliseconds: let the sampling thread in more often than the
     # interpreter's default 5 ms switch interval
     switch_interval = sys.getswitchinterval()
@@ -348,8 +350,10 @@ def gpu_arm(args):
         for i in range(args.steps):
             launches[0] += step(args.warmup + i)
     ev1.record()
-    barrier()
+    while not ev1.query():      # wait in the interpreter, not inside a blocking call, so that the
+        time.sleep(0)           # clock-sampling thread runs while the timed steps execute
     t_host1 = time.perf_counter()
+    barrier()
     # If the timed region was still too short for the sampler, keep the identical load running
     # (untimed) until it has three samples, at most 50 ms, so that clocks and throttle reasons are
     # read under the load that was timed.
@@ -365,6 +369,7 @@ def gpu_arm(args):
             else:
                 step(args.warmup + args.steps + i)
                 i += 1
+            torch.cuda.synchronize()     # one round at a time: nothing queues up behind the check
         torch.cuda.synchronize()
         t_host1 = time.perf_counter()
     clocks = sampler.stop(t_host0, t_host1)
