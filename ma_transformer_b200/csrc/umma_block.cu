@@ -14,17 +14,18 @@
 // layout row, so the union is a two-pointer merge, done identically by every
 // thread that needs it), 64 keys per step:
 //
-//   load warp (warp 9, one lane):     TMA K/V chunk -> smem (3 stages each)
-//   MMA warp (warp 8, one lane):      S = Q K^T      tcgen05.mma 128x64x16 x4 -> TMEM S buffer (two of them)
-//                                     O += P V       tcgen05.mma 128x64x16 x4 -> TMEM O (accumulates in place)
-//                                     (the same products also give l += P 1: B is widened to 80
-//                                     columns whose last 16 read a block of ones, so the row sums
-//                                     land in the 16 TMEM columns after O)
-//   softmax warps (warps 0-7):        two threads per query row (warps w and w+4 reach the same 32 TMEM
-//                                     lanes): each loads the row's 64 scores, masks, takes the row
-//                                     maximum, and writes its half (32 keys) of P = 2^(s - m) as bf16
-//                                     into smem (K-major, 128B swizzle).
+//   softmax warps (0-3 of a tile):    thread r owns query row r: copies it once from the TMA tile
+//                                     into TMEM, then per step tcgen05.ld its 64 scores, masks, takes
+//                                     the row maximum and stores P = 2^(s - m) as 16-bit pairs over
+//                                     the first 32 columns of the score buffer (tcgen05.st).
+//   MMA warp (one lane per tile):     S = Q K^T      tcgen05.mma 128x64x16 x4, A = Q from TMEM, B = K
+//                                     from smem, into one of two TMEM S buffers
+//                                     [O | l] += P [V | 1]   tcgen05.mma 128x80x16 x4, A = P from TMEM,
+//                                     B = V from smem widened to 80 columns whose last 16 read a block
+//                                     of ones, so the row sums land in the 16 TMEM columns after O
+//   load warp (one lane):             TMA K and V chunks -> smem stages, each released by a commit
 //
+// A CTA holds one such tile (two CTAs per SM) or, as an option, two tiles sharing the K/V stages.
 // The output and the row sums stay in TMEM for the whole walk.  The reference maximum m of a row
 // moves only when the chunk's maximum exceeds it by more than a factor 2 (weights then stay <= 2:
 // the exponent, rounded to the 16-bit operand type before ex2, keeps an absolute error <= 2^-9
