@@ -180,3 +180,101 @@ def band_random_block_layout(n_blocks: int, band: int = 4, n_random: int = 2,
         colidx += sorted(cols)
         rowptr.append(len(colidx))
     return np.asarray(rowptr, np.int32), np.asarray(colidx, np.int32)
+
+
+def bigbird_block_layout(n_blocks: int, window_blocks: int = 3, n_global_blocks: int = 1,
+                         n_random_blocks: int = 3, seed: int = 0) -> Tuple[np.ndarray, np.ndarray]:
+    """BIG_BIRD of the reference's vocabulary (``AttentionPattern::BIG_BIRD`` with
+    ``num_global_tokens`` / ``num_random_blocks``, src/csrc/attention_types.hpp:26-56; the
+    reference's factory throws on it, src/csrc/attention_factory.cpp:25-28) as a block layout:
+    block row r holds a centred band of ``window_blocks`` columns, the first
+    ``n_global_blocks`` columns, ``n_random_blocks`` further columns drawn without replacement
+    by a seeded generator; the first ``n_global_blocks`` rows hold every column."""
+    rng = np.random.default_rng(seed)
+    half = window_blocks // 2
+    rowptr, colidx = [0], []
+    for r in range(n_blocks):
+        if r < n_global_blocks:
+            cols = set(range(n_blocks))
+        else:
+            cols = {c for c in range(r - half, r + half + 1) if 0 <= c < n_blocks}
+            cols |= set(range(min(n_global_blocks, n_blocks)))
+            rest = np.asarray([c for c in range(n_blocks) if c not in cols], dtype=np.int64)
+            if n_random_blocks > 0 and rest.size:
+                cols |= set(rng.choice(rest, size=min(n_random_blocks, rest.size), replace=False).tolist())
+        colidx += sorted(cols)
+        rowptr.append(len(colidx))
+    return np.asarray(rowptr, np.int32), np.asarray(colidx, np.int32)
+
+
+def random_block_layout(n_blocks: int, density: float, seed: int = 0,
+                        keep_diagonal: bool = True) -> Tuple[np.ndarray, np.ndarray]:
+    """RANDOM_SPARSE at block granularity: about ``density`` of the block columns of every row,
+    drawn by a seeded generator (the reference draws single (i, j) pairs from an unseeded
+    ``std::random_device``, src/csrc/sparse_attention.cpp:286-308, which no test can pin and no
+    tiled kernel can use); the diagonal block is kept so that no row is empty."""
+    if not 0.0 <= density <= 1.0:
+        raise ValueError(f"density must be in [0, 1], got {density}")
+    rng = np.random.default_rng(seed)
+    per_row = min(n_blocks, max(1 if keep_diagonal else 0, int(round(density * n_blocks))))
+    rowptr, colidx = [0], []
+    for r in range(n_blocks):
+        cols = set(rng.choice(n_blocks, size=per_row, replace=False).tolist())
+        if keep_diagonal and r not in cols:
+            if len(cols) >= per_row and cols:
+                cols.pop()
+            cols.add(r)
+        colidx += sorted(cols)
+        rowptr.append(len(colidx))
+    return np.asarray(rowptr, np.int32), np.asarray(colidx, np.int32)
+
+
+# ---- statistics and estimates ------------------------------------------------------
+
+def pattern_statistics(spec: PatternSpec, seq_len: int) -> str:
+    """The text of the reference's ``get_pattern_statistics`` (src/csrc/ma_core.cpp:50-63) for any
+    pattern, from the closed form (no COO list is built)."""
+    total = int(seq_len) * int(seq_len)
+    nnz = spec.nnz(seq_len)
+    sparsity = np.float32(1.0) - np.float32(nnz) / np.float32(total) if total else np.float32(0.0)
+    return ("Pattern Statistics:\n"
+            f"  Total elements: {total}\n"
+            f"  Non-zero elements: {nnz}\n"
+            f"  Sparsity ratio: {float(sparsity * np.float32(100.0)):.6f}%\n")
+
+
+def estimate_flops(pattern: str, batch: int, seq_len: int, heads: int, head_dim: int,
+                   window_size: int = 64, block_size: int = 64) -> int:
+    """``attention_utils::estimate_flops`` (src/csrc/sparse_attention.cpp:312-334), same
+    conventions: one matmul counted, ``window_size`` keys per row for a sliding window, three
+    blocks per block row for a block-sparse layout, the conservative S*S*D elsewhere."""
+    p = pattern.upper()
+    if p in ("FULL", "CAUSAL"):
+        return batch * heads * seq_len * seq_len * head_dim * 2
+    if p == "SLIDING_WINDOW":
+        return batch * heads * seq_len * window_size * head_dim * 2
+    if p == "BLOCK_SPARSE":
+        nb = (seq_len + block_size - 1) // block_size
+        return batch * heads * nb * 3 * block_size * block_size * head_dim
+    return batch * heads * seq_len * seq_len * head_dim
+
+
+def estimate_memory_usage(pattern: str, batch: int, seq_len: int, heads: int,
+                          window_size: int = 64, block_size: int = 64) -> int:
+    """``attention_utils::estimate_memory_usage`` (src/csrc/sparse_attention.cpp:336-357): elements
+    of the score and weight arrays the reference's class path would hold (this library holds none
+    of them: scores live in registers or TMEM)."""
+    p = pattern.upper()
+    if p in ("FULL", "CAUSAL"):
+        return batch * heads * seq_len * seq_len * 2
+    if p == "SLIDING_WINDOW":
+        return batch * heads * seq_len * window_size * 2
+    if p == "BLOCK_SPARSE":
+        nb = (seq_len + block_size - 1) // block_size
+        return batch * heads * nb * 3 * block_size * block_size
+    return batch * heads * seq_len * seq_len
+
+
+def pattern_flops(spec: PatternSpec, batch: int, seq_len: int, heads: int, head_dim: int) -> int:
+    """FLOPs the forward actually needs for a pattern: two products of 2*D per (query, key) pair."""
+    return 4 * batch * heads * head_dim * spec.nnz(seq_len)

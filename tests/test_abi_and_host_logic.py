@@ -88,6 +88,60 @@ def test_band_random_layout_shape():
         assert set(range(max(0, r - 3), r + 1)) <= set(row.tolist())
 
 
+def test_pattern_statistics_and_estimates():
+    """Pattern tooling of the reference (get_pattern_statistics, tests/python/test_tensor_functionality.py:181-202;
+    attention_utils::estimate_flops / estimate_memory_usage, src/csrc/sparse_attention.cpp:312-357) from the
+    closed-form patterns."""
+    from ma_transformer_b200.patterns import (estimate_flops, estimate_memory_usage, pattern_flops,
+                                               pattern_statistics)
+    stats = pattern_statistics(PatternSpec.sliding_window(3), 16)
+    assert isinstance(stats, str)
+    for key in ("Pattern Statistics", "Total elements", "Non-zero elements", "Sparsity ratio"):
+        assert key in stats
+    lines = stats.split("\n")
+    total = int([l for l in lines if "Total elements" in l][0].split(": ")[1])
+    nonzero = int([l for l in lines if "Non-zero elements" in l][0].split(": ")[1])
+    assert total == 256 and nonzero == 16 * 7 - 2 * (1 + 2 + 3)       # +-3 window clipped at both ends
+    assert "60.937500%" in stats                                       # std::to_string of the float ratio
+    # the reference's conventions on the long-sequence shape: w keys per row, one matmul
+    assert estimate_flops("sliding_window", 1, 65536, 8, 64, window_size=64) == 4294967296
+    assert estimate_memory_usage("sliding_window", 1, 65536, 8, window_size=64) == 67108864
+    assert estimate_flops("full", 2, 128, 4, 64) == 2 * 4 * 128 * 128 * 64 * 2
+    assert estimate_flops("block_sparse", 1, 200, 2, 64, block_size=64) == 2 * 4 * 3 * 64 * 64 * 64
+    assert estimate_flops("big_bird", 1, 100, 1, 8) == 100 * 100 * 8
+    assert estimate_memory_usage("causal", 1, 100, 2) == 2 * 100 * 100 * 2
+    # what a pattern really costs: both products over its (query, key) pairs
+    assert pattern_flops(PatternSpec.causal_window(64), 1, 65536, 8, 64) == 4 * 8 * 64 * (65536 * 64 - 63 * 64 // 2)
+
+
+def test_bigbird_and_random_block_layouts():
+    """BIG_BIRD and RANDOM_SPARSE of the reference's pattern vocabulary (src/csrc/attention_types.hpp:26-56),
+    as seeded block layouts."""
+    from ma_transformer_b200.patterns import bigbird_block_layout, random_block_layout
+    nb = 12
+    rp, ci = bigbird_block_layout(nb, window_blocks=3, n_global_blocks=2, n_random_blocks=2, seed=3)
+    assert rp[0] == 0 and len(rp) == nb + 1 and rp[-1] == len(ci)
+    for r in range(nb):
+        cols = ci[rp[r]:rp[r + 1]].tolist()
+        assert cols == sorted(set(cols)) and all(0 <= c < nb for c in cols)
+        if r < 2:
+            assert cols == list(range(nb))                      # global rows see everything
+        else:
+            assert {0, 1} <= set(cols)                          # global columns
+            assert {c for c in (r - 1, r, r + 1) if c < nb} <= set(cols)
+            assert len(cols) == len({0, 1} | {c for c in (r - 1, r, r + 1) if c < nb}) + 2
+    again = bigbird_block_layout(nb, 3, 2, 2, seed=3)
+    assert np.array_equal(again[0], rp) and np.array_equal(again[1], ci)          # seeded: reproducible
+    rp, ci = random_block_layout(16, 0.25, seed=4)
+    for r in range(16):
+        cols = ci[rp[r]:rp[r + 1]].tolist()
+        assert len(cols) == 4 and r in cols and cols == sorted(set(cols))
+    spec = PatternSpec.block_sparse(8, rp, ci)
+    assert spec.nnz(16 * 8) == 16 * 4 * 64
+    with pytest.raises(ValueError):
+        random_block_layout(4, 1.5)
+
+
 def test_malformed_patterns_are_rejected():
     with pytest.raises(ValueError):
         PatternSpec(left=-1)

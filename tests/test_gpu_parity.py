@@ -229,6 +229,20 @@ def test_block_sparse_empty_rows_give_zeros():
         check_close(got, oracle_out(q, k, v, spec), dtype)
 
 
+def test_bigbird_and_random_block_layouts_vs_oracle():
+    """BIG_BIRD (band + global blocks + seeded random blocks, global rows over everything) and
+    block-granular RANDOM_SPARSE layouts, two-sided, on the tcgen05 kernel and on the fp32 kernel."""
+    from ma_transformer_b200.patterns import bigbird_block_layout, random_block_layout
+    S, block = 768, 64
+    for rp, ci in (bigbird_block_layout(S // block, 3, 1, 2, seed=11), random_block_layout(S // block, 0.3, seed=12)):
+        spec = PatternSpec.block_sparse(block, rp, ci)
+        for dtype in (torch.bfloat16, torch.float32):
+            q, k, v = seeded_qkv(36, 1, S, 2, 64, dtype)
+            got = run(spec, q, k, v)
+            assert nat.last_kernel() == ("rowwarp" if dtype == torch.float32 else "umma_block")
+            check_close(got, oracle_out(q, k, v, spec), dtype)
+
+
 # ---- Longformer -----------------------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
