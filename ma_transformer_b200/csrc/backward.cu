@@ -15,8 +15,9 @@
 //                    dK_j = scale * sum_i p_ij (dO_i . v_j - delta_i) q_i,
 //                    dV_j = sum_i p_ij dO_i.
 //
-// Outside the forward hot path; written for clarity and exactness (fp32 math for
-// every dtype), any head width up to 512.
+// Written for clarity and exactness (fp32 math for every dtype), any head width up
+// to 512.  16-bit inputs with head width 64 and at most 64 taps between the two
+// sides of the window go to the tensor-core kernels of bwd_mma.cu instead.
 #include "mat_common.cuh"
 
 namespace mat {
@@ -263,6 +264,8 @@ int mat_sparse_attn_bwd(const void *q, const void *k, const void *v, const void 
     a.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
     float2 *stats = (float2 *)workspace;
     cudaStream_t st = (cudaStream_t)stream;
+    if (bwd_mma_supports(B, S, H, D, dtype, a.left, a.right, a.dil))
+        return launch_bwd_mma(q, k, v, dout, dq, dk, dv, stats, B, S, H, dtype, a.left, a.right, a.dil, a.scale, st);
     switch (dtype) {
         case MAT_F32: return launch_t<float>(q, k, v, dout, dq, dk, dv, stats, a, st);
         case MAT_BF16: return launch_t<__nv_bfloat16>(q, k, v, dout, dq, dk, dv, stats, a, st);

@@ -1,0 +1,368 @@
+// Tensor-core backward of narrow window attention: bf16 / fp16, head width 64, windows
+// with left + right <= 64 taps (causal, two-sided, and dilated through a view), the
+// shapes the tiled forward window kernel serves.
+//
+// Replaces sparse_attention_backward_kernel (src/cuda/sparse_attention_kernel.cu:265-346),
+// which runs one thread per query row and scatters dK / dV with fp32 atomicAdd (:322, :343).
+// Nothing here is atomic; the result is deterministic.  Two launches of one kernel template:
+//
+//   rows pass (COLS = false)  one CTA per (batch, head, 64 queries): S = Q K^T on the band of
+//       keys the tile can see, softmax statistics, dP = dO V^T, delta_i = sum_j P_ij dP_ij,
+//       dS = P (dP - delta) scale, dQ = dS K.  Leaves (log2-sum-exp, delta) per row in the
+//       workspace.
+//   cols pass (COLS = true)   one CTA per (batch, head, 64 keys): the same band walk with the
+//       roles mirrored (rows are keys, the band holds the queries that attend to them):
+//       P^T from the stored statistics, dV = P^T dO, dK = dS^T Q.
+//
+// Both passes share the structure "16 rows per warp against a band of at most 80 columns":
+// the row operands are A fragments held in registers, the band operands sit in shared
+// memory (128-byte rows, 16-byte chunks XOR-swizzled by the row so every ldmatrix is
+// conflict-free) and feed mma.sync.m16n8k16 as B fragments, plain for the score-shaped
+// products and transposed for the output-shaped ones.  A dilated window over [B,S,H,64] is a
+// plain window over the same bytes viewed as [B, S/dil, dil*H, 64], so the kernel never sees
+// a dilation.
+#include "mat_common.cuh"
+#include "ptx.cuh"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+namespace mat {
+namespace {
+
+constexpr int kTile = 64;       // rows per CTA (4 warps x 16)
+constexpr int kPairs = 5;       // 16-column groups one warp's rows can reach: 16 + 64 = 80 columns
+constexpr int kThreads = 128;
+constexpr int kSmemBytes = 2 * 8192 + 2 * 16384 + 128 * (int)sizeof(float2);
+
+struct BwdArgs {
+    const void *q, *k, *v, *go;
+    void *dq, *dk, *dv;
+    float2 *stats;            // per (batch, head, row), row fastest: (log2-sum-exp of the scaled scores, delta)
+    int64_t B, S, HH;         // sequence length and head count of the (possibly dilated) view
+    int left, right;
+    float scale;
+};
+
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+    return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid) {
+    const int n = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// rows [row0, row0 + nrows) of one head into swizzled shared memory; rows outside [0, S) become zeros
+template <typename T>
+__device__ __forceinline__ void stage_rows(uint32_t dst, const T *head, int64_t row0, int nrows, int64_t S,
+                                           int64_t stride) {
+    for (int idx = threadIdx.x; idx < nrows * 8; idx += kThreads) {
+        const int row = idx >> 3, chunk = idx & 7;
+        const int64_t gr = row0 + row;
+        const bool ok = gr >= 0 && gr < S;
+        cp_async16(dst + swz(row, chunk), head + (ok ? gr : 0) * stride + chunk * 8, ok);
+    }
+}
+
+__device__ __forceinline__ float quad_max(float x) {
+    x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 1));
+    return fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 2));
+}
+__device__ __forceinline__ float quad_sum(float x) {
+    x += __shfl_xor_sync(0xffffffffu, x, 1);
+    return x + __shfl_xor_sync(0xffffffffu, x, 2);
+}
+
+// a warp's 16 x 64 fp32 accumulator tile -> its own 16 rows of a swizzled shared tile -> global, 16 bytes per lane
+template <typename T>
+__device__ __forceinline__ void store_tile(uint8_t *smem, uint32_t tile_off, const float (&o)[8][4], T *head,
+                                           int64_t row0, int64_t S, int64_t stride, int warp, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    __syncwarp();
+#pragma unroll
+    for (int dt = 0; dt < 8; ++dt) {
+        *(uint32_t *)(smem + tile_off + swz(16 * warp + g, dt) + 4 * t) = ptx::Mma<T>::pack(o[dt][0], o[dt][1]);
+        *(uint32_t *)(smem + tile_off + swz(16 * warp + g + 8, dt) + 4 * t) = ptx::Mma<T>::pack(o[dt][2], o[dt][3]);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int idx = lane + 32 * i, row = idx >> 3, chunk = idx & 7;
+        const int64_t gr = row0 + 16 * warp + row;
+        if (gr < S) {
+            const uint4 val = *(const uint4 *)(smem + tile_off + swz(16 * warp + row, chunk));
+            *(uint4 *)(head + gr * stride + chunk * 8) = val;
+        }
+    }
+}
+
+template <typename T, bool COLS>
+__global__ void __launch_bounds__(kThreads)
+bwd_window_mma_kernel(BwdArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    using M = ptx::Mma<T>;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int64_t r0 = (int64_t)blockIdx.x * kTile;
+    const int64_t h = blockIdx.y, b = blockIdx.z;
+    const int W = a.left + a.right;
+    const int back = COLS ? a.right : a.left;       // how far the band starts before the tile's first row
+    const int64_t c0 = r0 - back;                   // global index of band row 0
+    const int np = min(kPairs, (15 + W) / 16 + 1);  // 16-column groups a warp walks
+    const int64_t stride = a.HH * 64;
+    const int64_t head_off = (b * a.S * a.HH + h) * 64;
+    const T *x1 = (const T *)(COLS ? a.k : a.q) + head_off;    // row operands: one A fragment set each
+    const T *x2 = (const T *)(COLS ? a.v : a.go) + head_off;
+    const T *y1 = (const T *)(COLS ? a.q : a.k) + head_off;    // band operands
+    const T *y2 = (const T *)(COLS ? a.go : a.v) + head_off;
+    constexpr uint32_t oX1 = 0, oX2 = 8192, oY1 = 16384, oY2 = 32768, oSt = 49152;
+    const uint32_t sbase = ptx::smem_u32(smem);
+    float2 *sst = (float2 *)(smem + oSt);
+
+    const int band_rows = 48 + 16 * np;
+    stage_rows(sbase + oX1, x1, r0, kTile, a.S, stride);
+    stage_rows(sbase + oX2, x2, r0, kTile, a.S, stride);
+    stage_rows(sbase + oY1, y1, c0, band_rows, a.S, stride);
+    stage_rows(sbase + oY2, y2, c0, band_rows, a.S, stride);
+    if (COLS) {
+        const float2 *st = a.stats + (b * a.HH + h) * a.S;
+        for (int i = tid; i < band_rows; i += kThreads) {
+            const int64_t gi = c0 + i;
+            sst[i] = (gi >= 0 && gi < a.S) ? st[gi] : make_float2(0.f, 0.f);
+        }
+    }
+    cp_async_wait_all();
+    __syncthreads();
+
+    // A fragments of the warp's 16 rows, four k-steps over the head width
+    uint32_t a1[4][4], a2[4][4];
+    {
+        const int row = 16 * warp + (lane & 15), cadd = lane >> 4;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            ptx::ldmatrix_x4(a1[ks], sbase + oX1 + swz(row, 2 * ks + cadd));
+            ptx::ldmatrix_x4(a2[ks], sbase + oX2 + swz(row, 2 * ks + cadd));
+        }
+    }
+    const int mi = lane >> 3, rr = lane & 7;
+    const int brow_n = 16 * warp + (mi >> 1) * 8 + rr;   // + 16p: band row a lane addresses, plain B fragments
+    const int bchk_n = mi & 1;                           // + 2ks
+    const int brow_t = 16 * warp + (mi & 1) * 8 + rr;    // transposed B fragments
+    const int bchk_t = mi >> 1;                          // + 2dn
+    const float sl = a.scale * 1.4426950408889634f;
+    const int64_t colbase = c0 + 16 * warp;              // global index of the warp's column 0
+    // column c (0..79, relative to the warp) is seen by row r (0..15) iff 0 <= c - r <= W and it exists
+    auto seen = [&](int c, int r) -> bool {
+        const int64_t gc = colbase + c;
+        return (unsigned)(c - r) <= (unsigned)W && gc >= 0 && gc < a.S;
+    };
+
+    if constexpr (!COLS) {
+        float s[kPairs][2][4], dp[kPairs][2][4];
+#pragma unroll
+        for (int p = 0; p < kPairs; ++p)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[p][nt][e] = dp[p][nt][e] = 0.f;
+#pragma unroll
+        for (int p = 0; p < kPairs; ++p) {
+            if (p < np) {
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    uint32_t bf[4];
+                    ptx::ldmatrix_x4(bf, sbase + oY1 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
+                    M::run(s[p][0], a1[ks], bf[0], bf[1]);
+                    M::run(s[p][1], a1[ks], bf[2], bf[3]);
+                    ptx::ldmatrix_x4(bf, sbase + oY2 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
+                    M::run(dp[p][0], a2[ks], bf[0], bf[1]);
+                    M::run(dp[p][1], a2[ks], bf[2], bf[3]);
+                }
+            }
+        }
+        // softmax statistics of rows g and g + 8
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int p = 0; p < kPairs; ++p)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const bool ok = p < np && seen(16 * p + 8 * nt + 2 * t + (e & 1), g + (e >> 1) * 8);
+                    s[p][nt][e] = ok ? s[p][nt][e] * sl : -INFINITY;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], s[p][nt][e]);
+                }
+        float sum[2] = {0.f, 0.f}, delta[2] = {0.f, 0.f};
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            mx[hh] = quad_max(mx[hh]);
+            if (mx[hh] == -INFINITY) mx[hh] = 0.f;   // a row past the end of the sequence
+        }
+#pragma unroll
+        for (int p = 0; p < kPairs; ++p)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    s[p][nt][e] = ptx::ex2(s[p][nt][e] - mx[e >> 1]);
+                    sum[e >> 1] += s[p][nt][e];
+                }
+        float inv[2];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            sum[hh] = quad_sum(sum[hh]);
+            inv[hh] = sum[hh] > 0.f ? 1.f / sum[hh] : 0.f;
+        }
+#pragma unroll
+        for (int p = 0; p < kPairs; ++p)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    s[p][nt][e] *= inv[e >> 1];
+                    delta[e >> 1] = fmaf(s[p][nt][e], dp[p][nt][e], delta[e >> 1]);
+                }
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) delta[hh] = quad_sum(delta[hh]);
+        if (t == 0) {
+            float2 *st = a.stats + (b * a.HH + h) * a.S;
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int64_t gr = r0 + 16 * warp + g + 8 * hh;
+                if (gr < a.S) st[gr] = make_float2(mx[hh] + log2f(sum[hh]), delta[hh]);
+            }
+        }
+        // dQ = dS K over the band, dS = P (dP - delta) scale
+        float o[8][4];
+#pragma unroll
+        for (int dt = 0; dt < 8; ++dt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[dt][e] = 0.f;
+#pragma unroll
+        for (int p = 0; p < kPairs; ++p) {
+            if (p < np) {
+                uint32_t af[4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    float ds[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) ds[e] = s[p][nt][e] * (dp[p][nt][e] - delta[e >> 1]) * a.scale;
+                    af[2 * nt] = M::pack(ds[0], ds[1]);
+                    af[2 * nt + 1] = M::pack(ds[2], ds[3]);
+                }
+#pragma unroll
+                for (int dn = 0; dn < 4; ++dn) {
+                    uint32_t bf[4];
+                    ptx::ldmatrix_x4_trans(bf, sbase + oY1 + swz(brow_t + 16 * p, 2 * dn + bchk_t));
+                    M::run(o[2 * dn], af, bf[0], bf[1]);
+                    M::run(o[2 * dn + 1], af, bf[2], bf[3]);
+                }
+            }
+        }
+        store_tile<T>(smem, oX1, o, (T *)a.dq + head_off, r0, a.S, stride, warp, lane);
+    } else {
+        float ok_[8][4], ov[8][4];   // dK and dV of the warp's 16 keys
+#pragma unroll
+        for (int dt = 0; dt < 8; ++dt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ok_[dt][e] = ov[dt][e] = 0.f;
+#pragma unroll
+        for (int p = 0; p < kPairs; ++p) {
+            if (p < np) {
+                float st[2][4], dpt[2][4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) st[nt][e] = dpt[nt][e] = 0.f;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    uint32_t bf[4];
+                    ptx::ldmatrix_x4(bf, sbase + oY1 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
+                    M::run(st[0], a1[ks], bf[0], bf[1]);
+                    M::run(st[1], a1[ks], bf[2], bf[3]);
+                    ptx::ldmatrix_x4(bf, sbase + oY2 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
+                    M::run(dpt[0], a2[ks], bf[0], bf[1]);
+                    M::run(dpt[1], a2[ks], bf[2], bf[3]);
+                }
+                uint32_t ap[4], as[4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int cb = 16 * p + 8 * nt + 2 * t;
+                    const float4 sd = *(const float4 *)&sst[16 * warp + cb];   // (lse, delta) of two queries
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const bool ok = seen(cb + (e & 1), g + (e >> 1) * 8);
+                        const float lse = (e & 1) ? sd.z : sd.x, dl = (e & 1) ? sd.w : sd.y;
+                        const float pp = ok ? ptx::ex2(fmaf(st[nt][e], sl, -lse)) : 0.f;
+                        st[nt][e] = pp;
+                        dpt[nt][e] = pp * (dpt[nt][e] - dl) * a.scale;
+                    }
+                    ap[2 * nt] = M::pack(st[nt][0], st[nt][1]);
+                    ap[2 * nt + 1] = M::pack(st[nt][2], st[nt][3]);
+                    as[2 * nt] = M::pack(dpt[nt][0], dpt[nt][1]);
+                    as[2 * nt + 1] = M::pack(dpt[nt][2], dpt[nt][3]);
+                }
+#pragma unroll
+                for (int dn = 0; dn < 4; ++dn) {
+                    uint32_t bf[4];
+                    ptx::ldmatrix_x4_trans(bf, sbase + oY2 + swz(brow_t + 16 * p, 2 * dn + bchk_t));
+                    M::run(ov[2 * dn], ap, bf[0], bf[1]);
+                    M::run(ov[2 * dn + 1], ap, bf[2], bf[3]);
+                    ptx::ldmatrix_x4_trans(bf, sbase + oY1 + swz(brow_t + 16 * p, 2 * dn + bchk_t));
+                    M::run(ok_[2 * dn], as, bf[0], bf[1]);
+                    M::run(ok_[2 * dn + 1], as, bf[2], bf[3]);
+                }
+            }
+        }
+        store_tile<T>(smem, oX1, ok_, (T *)a.dk + head_off, r0, a.S, stride, warp, lane);
+        store_tile<T>(smem, oX2, ov, (T *)a.dv + head_off, r0, a.S, stride, warp, lane);
+    }
+}
+
+template <typename T>
+int launch_bwd(const BwdArgs &a, cudaStream_t stream) {
+    int rc = ensure_dynamic_smem((const void *)bwd_window_mma_kernel<T, false>, kSmemBytes, "bwd_window_mma rows");
+    if (rc != MAT_OK) return rc;
+    rc = ensure_dynamic_smem((const void *)bwd_window_mma_kernel<T, true>, kSmemBytes, "bwd_window_mma cols");
+    if (rc != MAT_OK) return rc;
+    const dim3 grid((unsigned)((a.S + kTile - 1) / kTile), (unsigned)a.HH, (unsigned)a.B);
+    bwd_window_mma_kernel<T, false><<<grid, kThreads, kSmemBytes, stream>>>(a);
+    bwd_window_mma_kernel<T, true><<<grid, kThreads, kSmemBytes, stream>>>(a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "tensor-core backward launch");
+    note_kernel("bwd_window_mma");
+    return MAT_OK;
+}
+
+}  // namespace
+
+bool bwd_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t left, int64_t right,
+                      int64_t dil) {
+    if (dtype != MAT_BF16 && dtype != MAT_F16) return false;
+    if (D != 64 || dil < 1 || S % dil != 0) return false;
+    const char *env = getenv("MAT_BWD_KERNEL");
+    if (env && strcmp(env, "warp") == 0) return false;
+    const int64_t Sv = S / dil;
+    const int64_t l = left < Sv - 1 ? left : Sv - 1, r = right < Sv - 1 ? right : Sv - 1;
+    if (l + r > 64) return false;
+    return H * dil <= 65535 && B <= 65535;
+}
+
+int launch_bwd_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk, void *dv,
+                   float2 *stats, int64_t B, int64_t S, int64_t H, int dtype, int64_t left, int64_t right,
+                   int64_t dil, float scale, cudaStream_t stream) {
+    BwdArgs a;
+    a.q = q; a.k = k; a.v = v; a.go = dout;
+    a.dq = dq; a.dk = dk; a.dv = dv;
+    a.stats = stats;
+    a.B = B; a.S = S / dil; a.HH = H * dil;
+    a.left = (int)(left < a.S - 1 ? left : a.S - 1);
+    a.right = (int)(right < a.S - 1 ? right : a.S - 1);
+    if (a.left < 0) a.left = 0;     // a one-row sequence
+    if (a.right < 0) a.right = 0;
+    a.scale = scale;
+    return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16>(a, stream) : launch_bwd<__half>(a, stream);
+}
+
+}  // namespace mat

@@ -77,6 +77,13 @@ struct GlobalRowSplit {
 GlobalRowSplit plan_umma_global_rows(const Problem &p);
 int launch_umma_global_rows(const Problem &p, const GlobalRowSplit &g, float *partial);
 
+// tensor-core backward of narrow windows (bwd_mma.cu): 16-bit types, D = 64, left + right <= 64 taps
+bool bwd_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t left, int64_t right,
+                      int64_t dil);
+int launch_bwd_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk, void *dv,
+                   float2 *stats, int64_t B, int64_t S, int64_t H, int dtype, int64_t left, int64_t right,
+                   int64_t dil, float scale, cudaStream_t stream);
+
 template <typename T> struct Elem;
 template <> struct Elem<float> {
     static __device__ __forceinline__ float to_f(float x) { return x; }

@@ -457,6 +457,58 @@ def test_dense_backward_and_custom_windows(causal):
         assert (a16.grad.float() - a32.grad).abs().max() < 0.06 * max(1.0, float(a32.grad.abs().max()))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,S,H,left,right,dil", [
+    (1, 512, 2, 63, 0, 1),      # 64 causal taps: the headline window
+    (2, 200, 3, 32, 32, 1),     # two-sided, ragged last tile
+    (1, 33, 1, 8, 8, 1),        # shorter than one tile
+    (1, 130, 2, 10, 3, 1),      # lopsided
+    (1, 257, 1, 0, 0, 1),       # self only
+    (1, 64, 2, 0, 64, 1),       # looking ahead only
+    (1, 384, 2, 63, 0, 2),      # dilated causal taps i - 2k (the order-book model's window)
+    (1, 96, 1, 5, 5, 3),        # dilated, two-sided
+    (1, 30, 2, 200, 200, 1),    # reaches past both ends: clamps to the sequence
+])
+def test_tensor_core_backward_matches_fp32_math_kernels(monkeypatch, dtype, B, S, H, left, right, dil):
+    """The mma backward (16-bit, D = 64, at most 64 taps between the two sides) against the warp-level
+    kernels, which compute in fp32 from the same 16-bit inputs and are themselves held to autograd through
+    the reference's python oracle (tests/python/test_cuda_backward.py:75-101)."""
+    spec = PatternSpec(left=left, right=right, dilation=dil)
+    q, k, v = (t.to(DEV) for t in seeded_qkv(91, B, S, H, 64, dtype))
+    go = torch.randn(B, S, H, 64, generator=torch.Generator().manual_seed(92)).to(dtype).to(DEV)
+    got = ext.backward_pattern(q, k, v, go, spec)
+    torch.cuda.synchronize()
+    assert nat.last_kernel() == "bwd_window_mma"
+    monkeypatch.setenv("MAT_BWD_KERNEL", "warp")
+    want = ext.backward_pattern(q, k, v, go, spec)
+    torch.cuda.synchronize()
+    assert nat.last_kernel() == "bwd_window"
+    tol = 2e-2 if dtype == torch.bfloat16 else 5e-3
+    for name, a, b in zip(("dQ", "dK", "dV"), got, want):
+        a, b = a.float(), b.float()
+        assert torch.isfinite(a).all(), name
+        err = float((a - b).abs().max())
+        assert err <= tol * max(1.0, float(b.abs().max())), f"{name}: {err}"
+    # deterministic: a second run gives the same bits
+    monkeypatch.delenv("MAT_BWD_KERNEL")
+    again = ext.backward_pattern(q, k, v, go, spec)
+    for a, b in zip(got, again):
+        assert torch.equal(a, b)
+
+
+def test_tensor_core_backward_against_fp64_autograd():
+    """Same bar as the fp32 kernels' test, at the 16-bit tolerance: autograd in fp64 through the reference's
+    python oracle (src/layers/ma_core_bridge.py:224-247) on the bf16-rounded inputs."""
+    q, k, v = seeded_qkv(93, 2, 192, 2, 64, torch.bfloat16)
+    go = torch.randn(2, 192, 2, 64, generator=torch.Generator().manual_seed(94)).to(torch.bfloat16)
+    dq, dk, dv = ext.backward(q.to(DEV), k.to(DEV), v.to(DEV), go.to(DEV), 16)
+    assert nat.last_kernel() == "bwd_window_mma"
+    qr, kr, vr = (t.double().requires_grad_(True) for t in (q, k, v))
+    mt.pytorch_sparse_attention(qr, kr, vr, 16).backward(go.double())
+    for got, ref in ((dq, qr), (dk, kr), (dv, vr)):
+        assert (got.cpu().double() - ref.grad).abs().max() < 2e-2 * max(1.0, float(ref.grad.abs().max()))
+
+
 def test_block_layout_on_warp_level_kernel_too(monkeypatch):
     """MAT_BLOCK_KERNEL=mma keeps block layouts on the warp-level ring kernel (debugging aid);
     both kernels must agree with the oracle."""
