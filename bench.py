@@ -12,7 +12,7 @@ K/V rows they need from the neighbouring GPU inside the kernel (``--halo nccl``
 exchanges them by send/recv instead).  Steps are independent forwards over
 rotating input sets; they are captured in CUDA graphs and alternate over two
 streams (``--lanes``), each with its own output buffer.
-``--workload block|longformer|orderbook|dense`` time the other configurations on one GPU.
+``--workload block|longformer|orderbook|dense|backward`` time the other configurations on one GPU.
 
 Prints ONE JSON line.  ``value`` is tokens/s with inputs resident in HBM, timed
 with CUDA events over exactly K steps (max over ranks); ``e2e`` is the same
@@ -491,6 +491,41 @@ def other_workload_arm(args):
                                        "peak_source": f"{peak_kind} HBM copy bandwidth"}},
             "device_status": nat.device_status()}), flush=True)
         return
+    if args.workload == "backward":
+        # backward of the headline window (64 causal taps at the cfg-2 shape): dQ, dK, dV from Q, K, V, dO
+        Bw, S, Hw = B, SEQ, H
+        spec = PatternSpec.causal_window(TAPS)
+        nbytes = 7 * Bw * S * Hw * 64 * 2      # four tensors read once, three written once
+        sets = [tuple((torch.randn(Bw, S, Hw, 64, generator=g) * 0.5).to(torch.bfloat16).to(dev) for _ in range(4))
+                for _ in range(3)]
+        for i in range(args.warmup):
+            ext.backward_pattern(*sets[i % 3], spec)
+        torch.cuda.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        ev0.record()
+        for i in range(args.steps):
+            ext.backward_pattern(*sets[i % 3], spec)
+        ev1.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop(t0, time.perf_counter())
+        ms = ev0.elapsed_time(ev1) / args.steps
+        peak, peak_kind = measured_peak_gbs()
+        achieved = nbytes / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "sparse-attn bwd tokens/s (backward)", "value": Bw * S / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"causal sliding-window bwd B={Bw} N={S} H={Hw} d=64 taps={TAPS} bf16",
+                       "l2": "3 rotating input sets"},
+            "clocks": clocks, "kernel": nat.last_kernel(), "gpu_launches": 2 * args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": f"{peak_kind} HBM copy bandwidth", "bytes_per_launch_algorithmic": nbytes,
+                         "note": "per backward (two launches: rows pass and cols pass)"},
+            "device_status": nat.device_status()}), flush=True)
+        return
     if args.workload == "block":
         Bw, S, Hw = 4, 16384, 8
         rp, ci = band_random_block_layout(S // 64, 4, 2, seed=SEED)
@@ -554,7 +589,7 @@ def other_workload_arm(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="window", choices=["window", "block", "longformer", "orderbook", "dense"],
+    ap.add_argument("--workload", default="window", choices=["window", "block", "longformer", "orderbook", "dense", "backward"],
                     help="window = the headline configuration; block / longformer / orderbook / dense = one-GPU timing "
                          "of the block-sparse, Longformer, order-book-transformer and dense configurations")
     ap.add_argument("--gpus", type=int, default=1)
