@@ -1,6 +1,6 @@
 // Tensor-core backward of narrow window attention: bf16 / fp16, head width 64, windows
-// with left + right <= 64 taps (causal, two-sided, and dilated through a view), the
-// shapes the tiled forward window kernel serves.
+// with left + right <= 128 taps (causal, two-sided, and dilated through a view), the
+// shapes the tiled forward window kernels serve.
 //
 // Replaces sparse_attention_backward_kernel (src/cuda/sparse_attention_kernel.cu:265-346),
 // which runs one thread per query row and scatters dK / dV with fp32 atomicAdd (:322, :343).
@@ -8,13 +8,15 @@
 //
 //   rows pass (COLS = false)  one CTA per (batch, head, 64 queries): S = Q K^T on the band of
 //       keys the tile can see, softmax statistics, dP = dO V^T, delta_i = sum_j P_ij dP_ij,
-//       dS = P (dP - delta) scale, dQ = dS K.  Leaves (log2-sum-exp, delta) per row in the
+//       dS = P (dP - delta) scale, dQ = dS K.  Leaves (log2-sum-exp, delta scale) per row in the
 //       workspace.
 //   cols pass (COLS = true)   one CTA per (batch, head, 64 keys): the same band walk with the
 //       roles mirrored (rows are keys, the band holds the queries that attend to them):
 //       P^T from the stored statistics, dV = P^T dO, dK = dS^T Q.
 //
-// Both passes share the structure "16 rows per warp against a band of at most 80 columns":
+// Both passes share the structure "16 rows per warp against a band of at most 80 columns"
+// (144 for windows of more than 64 taps, where the rows pass sweeps the band twice instead of
+// holding it in registers):
 // the row operands are A fragments held in registers, the band operands sit in shared
 // memory (128-byte rows, 16-byte chunks XOR-swizzled by the row so every ldmatrix is
 // conflict-free) and feed mma.sync.m16n8k16 as B fragments, plain for the score-shaped
@@ -32,14 +34,16 @@ namespace mat {
 namespace {
 
 constexpr int kTile = 64;       // rows per CTA (4 warps x 16)
-constexpr int kPairs = 5;       // 16-column groups one warp's rows can reach: 16 + 64 = 80 columns
 constexpr int kThreads = 128;
-constexpr int kSmemBytes = 2 * 8192 + 2 * 16384 + 128 * (int)sizeof(float2);
+// NP = 16-column groups one warp's rows can reach: 5 (16 + 64 = 80 columns) for windows of at most 64 taps
+// between the two sides, 9 (16 + 128 = 144 columns) for up to 128 (the reference's default +-64)
+constexpr int band_rows_max(int NP) { return 48 + 16 * NP; }
+constexpr int smem_bytes(int NP) { return 2 * 8192 + band_rows_max(NP) * (2 * 128 + (int)sizeof(float2)); }
 
 struct BwdArgs {
     const void *q, *k, *v, *go;
     void *dq, *dk, *dv;
-    float2 *stats;            // per (batch, head, row), row fastest: (log2-sum-exp of the scaled scores, delta)
+    float2 *stats;            // per (batch, head, row), row fastest: (log2-sum-exp of the scaled scores, delta * scale)
     int64_t B, S, HH;         // sequence length and head count of the (possibly dilated) view
     int left, right;
     float scale;
@@ -98,9 +102,10 @@ __device__ __forceinline__ void store_tile(uint8_t *smem, uint32_t tile_off, con
     }
 }
 
-template <typename T, bool COLS>
-__global__ void __launch_bounds__(kThreads)
+template <typename T, bool COLS, int NP>
+__global__ void __launch_bounds__(kThreads, NP == 5 ? 4 : 3)
 bwd_window_mma_kernel(BwdArgs a) {
+    constexpr int kPairs = NP;
     extern __shared__ __align__(1024) uint8_t smem[];
     using M = ptx::Mma<T>;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
@@ -116,7 +121,8 @@ bwd_window_mma_kernel(BwdArgs a) {
     const T *x2 = (const T *)(COLS ? a.v : a.go) + head_off;
     const T *y1 = (const T *)(COLS ? a.q : a.k) + head_off;    // band operands
     const T *y2 = (const T *)(COLS ? a.go : a.v) + head_off;
-    constexpr uint32_t oX1 = 0, oX2 = 8192, oY1 = 16384, oY2 = 32768, oSt = 49152;
+    constexpr uint32_t oX1 = 0, oX2 = 8192, oY1 = 16384, oY2 = oY1 + band_rows_max(NP) * 128,
+                       oSt = oY2 + band_rows_max(NP) * 128;
     const uint32_t sbase = ptx::smem_u32(smem);
     float2 *sst = (float2 *)(smem + oSt);
 
@@ -152,13 +158,18 @@ bwd_window_mma_kernel(BwdArgs a) {
     const int bchk_t = mi >> 1;                          // + 2dn
     const float sl = a.scale * 1.4426950408889634f;
     const int64_t colbase = c0 + 16 * warp;              // global index of the warp's column 0
-    // column c (0..79, relative to the warp) is seen by row r (0..15) iff 0 <= c - r <= W and it exists
+    // Column c (0..16 NP - 1, relative to the warp) is seen by row r (0..15) iff 0 <= c - r <= W and the column
+    // exists.  Existence only matters in CTAs whose band crosses an end of the sequence (clo, chi clip it);
+    // the diagonal test only in the first group and in groups that reach past W - 15.
+    const int clo = colbase < 0 ? (int)-colbase : 0;
+    const int chi = a.S - colbase < 16 * NP ? (int)(a.S - colbase) - 1 : 16 * NP - 1;
+    const bool clipped = clo > 0 || chi < 16 * NP - 1;
     auto seen = [&](int c, int r) -> bool {
-        const int64_t gc = colbase + c;
-        return (unsigned)(c - r) <= (unsigned)W && gc >= 0 && gc < a.S;
+        return (unsigned)(c - r) <= (unsigned)W && c >= clo && c <= chi;
     };
+    auto group_masked = [&](int p) -> bool { return clipped || p == 0 || 16 * p + 15 > W; };
 
-    if constexpr (!COLS) {
+    if constexpr (!COLS && NP <= 5) {
         float s[kPairs][2][4], dp[kPairs][2][4];
 #pragma unroll
         for (int p = 0; p < kPairs; ++p)
@@ -181,56 +192,61 @@ bwd_window_mma_kernel(BwdArgs a) {
                 }
             }
         }
-        // softmax statistics of rows g and g + 8
+        // softmax statistics of rows g and g + 8 (maximum of the raw scores: the scale is positive)
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int p = 0; p < kPairs; ++p)
+        for (int p = 0; p < kPairs; ++p) {
+            if (p < np) {
+                if (group_masked(p)) {
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
+                    for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const bool ok = p < np && seen(16 * p + 8 * nt + 2 * t + (e & 1), g + (e >> 1) * 8);
-                    s[p][nt][e] = ok ? s[p][nt][e] * sl : -INFINITY;
-                    mx[e >> 1] = fmaxf(mx[e >> 1], s[p][nt][e]);
+                        for (int e = 0; e < 4; ++e)
+                            if (!seen(16 * p + 8 * nt + 2 * t + (e & 1), g + (e >> 1) * 8)) s[p][nt][e] = -INFINITY;
                 }
-        float sum[2] = {0.f, 0.f}, delta[2] = {0.f, 0.f};
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[p][nt][e]);
+            }
+        }
+        float sum[2] = {0.f, 0.f}, delta[2] = {0.f, 0.f}, msl[2];
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
             mx[hh] = quad_max(mx[hh]);
             if (mx[hh] == -INFINITY) mx[hh] = 0.f;   // a row past the end of the sequence
+            msl[hh] = mx[hh] * sl;
         }
+        // e = exp2(s sl - max sl); row sums of e and of e dP
 #pragma unroll
-        for (int p = 0; p < kPairs; ++p)
+        for (int p = 0; p < kPairs; ++p) {
+            if (p < np) {
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
+                for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    s[p][nt][e] = ptx::ex2(s[p][nt][e] - mx[e >> 1]);
-                    sum[e >> 1] += s[p][nt][e];
-                }
-        float inv[2];
+                    for (int e = 0; e < 4; ++e) {
+                        const float ex = ptx::ex2(fmaf(s[p][nt][e], sl, -msl[e >> 1]));
+                        s[p][nt][e] = ex;
+                        sum[e >> 1] += ex;
+                        delta[e >> 1] = fmaf(ex, dp[p][nt][e], delta[e >> 1]);
+                    }
+            }
+        }
+        float cs[2], dcs[2];   // scale / sum and delta scale / sum: dS = e (dP cs - dcs)
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
             sum[hh] = quad_sum(sum[hh]);
-            inv[hh] = sum[hh] > 0.f ? 1.f / sum[hh] : 0.f;
+            const float inv = sum[hh] > 0.f ? 1.f / sum[hh] : 0.f;
+            delta[hh] = quad_sum(delta[hh]) * inv;
+            cs[hh] = inv * a.scale;
+            dcs[hh] = delta[hh] * cs[hh];
         }
-#pragma unroll
-        for (int p = 0; p < kPairs; ++p)
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    s[p][nt][e] *= inv[e >> 1];
-                    delta[e >> 1] = fmaf(s[p][nt][e], dp[p][nt][e], delta[e >> 1]);
-                }
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) delta[hh] = quad_sum(delta[hh]);
         if (t == 0) {
             float2 *st = a.stats + (b * a.HH + h) * a.S;
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 const int64_t gr = r0 + 16 * warp + g + 8 * hh;
-                if (gr < a.S) st[gr] = make_float2(mx[hh] + log2f(sum[hh]), delta[hh]);
+                if (gr < a.S) st[gr] = make_float2(msl[hh] + log2f(sum[hh]), delta[hh] * a.scale);
             }
         }
         // dQ = dS K over the band, dS = P (dP - delta) scale
@@ -247,7 +263,7 @@ bwd_window_mma_kernel(BwdArgs a) {
                 for (int nt = 0; nt < 2; ++nt) {
                     float ds[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) ds[e] = s[p][nt][e] * (dp[p][nt][e] - delta[e >> 1]) * a.scale;
+                    for (int e = 0; e < 4; ++e) ds[e] = s[p][nt][e] * fmaf(dp[p][nt][e], cs[e >> 1], -dcs[e >> 1]);
                     af[2 * nt] = M::pack(ds[0], ds[1]);
                     af[2 * nt + 1] = M::pack(ds[2], ds[3]);
                 }
@@ -258,6 +274,106 @@ bwd_window_mma_kernel(BwdArgs a) {
                     M::run(o[2 * dn], af, bf[0], bf[1]);
                     M::run(o[2 * dn + 1], af, bf[2], bf[3]);
                 }
+            }
+        }
+        store_tile<T>(smem, oX1, o, (T *)a.dq + head_off, r0, a.S, stride, warp, lane);
+    } else if constexpr (!COLS) {
+        // Wide bands do not fit in registers: one sweep for the row statistics with a running maximum
+        // (sum of e and of e dP rescaled together), a second sweep that recomputes S and dP group by
+        // group and feeds dS straight into the dQ products.
+        auto group_products = [&](int p, float (&s)[2][4], float (&dp)[2][4]) {
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[nt][e] = dp[nt][e] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                uint32_t bf[4];
+                ptx::ldmatrix_x4(bf, sbase + oY1 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
+                M::run(s[0], a1[ks], bf[0], bf[1]);
+                M::run(s[1], a1[ks], bf[2], bf[3]);
+                ptx::ldmatrix_x4(bf, sbase + oY2 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
+                M::run(dp[0], a2[ks], bf[0], bf[1]);
+                M::run(dp[1], a2[ks], bf[2], bf[3]);
+            }
+            if (group_masked(p)) {
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (!seen(16 * p + 8 * nt + 2 * t + (e & 1), g + (e >> 1) * 8)) s[nt][e] = -INFINITY;
+            }
+        };
+        float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f}, dr[2] = {0.f, 0.f};
+#pragma unroll 1
+        for (int p = 0; p < np; ++p) {
+            float s[2][4], dp[2][4];
+            group_products(p, s, dp);
+            float gm[2] = {-INFINITY, -INFINITY}, msl[2];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) gm[e >> 1] = fmaxf(gm[e >> 1], s[nt][e]);
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const float m_new = fmaxf(mx[hh], quad_max(gm[hh]));
+                const float alpha = mx[hh] == -INFINITY ? 0.f : ptx::ex2((mx[hh] - m_new) * sl);
+                sum[hh] *= alpha;
+                dr[hh] *= alpha;
+                mx[hh] = m_new;
+                msl[hh] = m_new == -INFINITY ? 0.f : m_new * sl;
+            }
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float ex = ptx::ex2(fmaf(s[nt][e], sl, -msl[e >> 1]));
+                    sum[e >> 1] += ex;
+                    dr[e >> 1] = fmaf(ex, dp[nt][e], dr[e >> 1]);
+                }
+        }
+        float lse[2], dsc[2];   // log2-sum-exp of the scaled scores, delta scale
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            sum[hh] = quad_sum(sum[hh]);
+            dr[hh] = quad_sum(dr[hh]);            // every lane takes part in the shuffles, live row or not
+            const bool live = sum[hh] > 0.f;      // false only for rows past the end of the sequence
+            lse[hh] = live ? mx[hh] * sl + log2f(sum[hh]) : 0.f;
+            dsc[hh] = live ? dr[hh] / sum[hh] * a.scale : 0.f;
+        }
+        if (t == 0) {
+            float2 *st = a.stats + (b * a.HH + h) * a.S;
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int64_t gr = r0 + 16 * warp + g + 8 * hh;
+                if (gr < a.S) st[gr] = make_float2(lse[hh], dsc[hh]);
+            }
+        }
+        float o[8][4];
+#pragma unroll
+        for (int dt = 0; dt < 8; ++dt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[dt][e] = 0.f;
+#pragma unroll 1
+        for (int p = 0; p < np; ++p) {
+            float s[2][4], dp[2][4];
+            group_products(p, s, dp);
+            uint32_t af[4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                float ds[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    ds[e] = ptx::ex2(fmaf(s[nt][e], sl, -lse[e >> 1])) * fmaf(dp[nt][e], a.scale, -dsc[e >> 1]);
+                af[2 * nt] = M::pack(ds[0], ds[1]);
+                af[2 * nt + 1] = M::pack(ds[2], ds[3]);
+            }
+#pragma unroll
+            for (int dn = 0; dn < 4; ++dn) {
+                uint32_t bf[4];
+                ptx::ldmatrix_x4_trans(bf, sbase + oY1 + swz(brow_t + 16 * p, 2 * dn + bchk_t));
+                M::run(o[2 * dn], af, bf[0], bf[1]);
+                M::run(o[2 * dn + 1], af, bf[2], bf[3]);
             }
         }
         store_tile<T>(smem, oX1, o, (T *)a.dq + head_off, r0, a.S, stride, warp, lane);
@@ -286,17 +402,18 @@ bwd_window_mma_kernel(BwdArgs a) {
                     M::run(dpt[1], a2[ks], bf[2], bf[3]);
                 }
                 uint32_t ap[4], as[4];
+                const bool masked = group_masked(p);
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
                     const int cb = 16 * p + 8 * nt + 2 * t;
-                    const float4 sd = *(const float4 *)&sst[16 * warp + cb];   // (lse, delta) of two queries
+                    const float4 sd = *(const float4 *)&sst[16 * warp + cb];   // (lse, delta scale) of two queries
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const bool ok = seen(cb + (e & 1), g + (e >> 1) * 8);
                         const float lse = (e & 1) ? sd.z : sd.x, dl = (e & 1) ? sd.w : sd.y;
-                        const float pp = ok ? ptx::ex2(fmaf(st[nt][e], sl, -lse)) : 0.f;
+                        float pp = ptx::ex2(fmaf(st[nt][e], sl, -lse));
+                        if (masked && !seen(cb + (e & 1), g + (e >> 1) * 8)) pp = 0.f;
                         st[nt][e] = pp;
-                        dpt[nt][e] = pp * (dpt[nt][e] - dl) * a.scale;
+                        dpt[nt][e] = pp * fmaf(dpt[nt][e], a.scale, -dl);
                     }
                     ap[2 * nt] = M::pack(st[nt][0], st[nt][1]);
                     ap[2 * nt + 1] = M::pack(st[nt][2], st[nt][3]);
@@ -320,15 +437,15 @@ bwd_window_mma_kernel(BwdArgs a) {
     }
 }
 
-template <typename T>
+template <typename T, int NP>
 int launch_bwd(const BwdArgs &a, cudaStream_t stream) {
-    int rc = ensure_dynamic_smem((const void *)bwd_window_mma_kernel<T, false>, kSmemBytes, "bwd_window_mma rows");
+    int rc = ensure_dynamic_smem((const void *)bwd_window_mma_kernel<T, false, NP>, smem_bytes(NP), "bwd_window_mma rows");
     if (rc != MAT_OK) return rc;
-    rc = ensure_dynamic_smem((const void *)bwd_window_mma_kernel<T, true>, kSmemBytes, "bwd_window_mma cols");
+    rc = ensure_dynamic_smem((const void *)bwd_window_mma_kernel<T, true, NP>, smem_bytes(NP), "bwd_window_mma cols");
     if (rc != MAT_OK) return rc;
     const dim3 grid((unsigned)((a.S + kTile - 1) / kTile), (unsigned)a.HH, (unsigned)a.B);
-    bwd_window_mma_kernel<T, false><<<grid, kThreads, kSmemBytes, stream>>>(a);
-    bwd_window_mma_kernel<T, true><<<grid, kThreads, kSmemBytes, stream>>>(a);
+    bwd_window_mma_kernel<T, false, NP><<<grid, kThreads, smem_bytes(NP), stream>>>(a);
+    bwd_window_mma_kernel<T, true, NP><<<grid, kThreads, smem_bytes(NP), stream>>>(a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "tensor-core backward launch");
     note_kernel("bwd_window_mma");
@@ -345,7 +462,7 @@ bool bwd_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int
     if (env && strcmp(env, "warp") == 0) return false;
     const int64_t Sv = S / dil;
     const int64_t l = left < Sv - 1 ? left : Sv - 1, r = right < Sv - 1 ? right : Sv - 1;
-    if (l + r > 64) return false;
+    if (l + r > 128) return false;
     return H * dil <= 65535 && B <= 65535;
 }
 
@@ -362,7 +479,9 @@ int launch_bwd_mma(const void *q, const void *k, const void *v, const void *dout
     if (a.left < 0) a.left = 0;     // a one-row sequence
     if (a.right < 0) a.right = 0;
     a.scale = scale;
-    return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16>(a, stream) : launch_bwd<__half>(a, stream);
+    if (a.left + a.right <= 64)
+        return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16, 5>(a, stream) : launch_bwd<__half, 5>(a, stream);
+    return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16, 9>(a, stream) : launch_bwd<__half, 9>(a, stream);
 }
 
 }  // namespace mat

@@ -77,7 +77,7 @@ struct GlobalRowSplit {
 GlobalRowSplit plan_umma_global_rows(const Problem &p);
 int launch_umma_global_rows(const Problem &p, const GlobalRowSplit &g, float *partial);
 
-// tensor-core backward of narrow windows (bwd_mma.cu): 16-bit types, D = 64, left + right <= 64 taps
+// tensor-core backward of narrow windows (bwd_mma.cu): 16-bit types, D = 64, left + right <= 128 taps
 bool bwd_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t left, int64_t right,
                       int64_t dil);
 int launch_bwd_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk, void *dv,

@@ -468,9 +468,14 @@ def test_dense_backward_and_custom_windows(causal):
     (1, 384, 2, 63, 0, 2),      # dilated causal taps i - 2k (the order-book model's window)
     (1, 96, 1, 5, 5, 3),        # dilated, two-sided
     (1, 30, 2, 200, 200, 1),    # reaches past both ends: clamps to the sequence
+    (1, 512, 2, 64, 64, 1),     # the reference's default window_size=64 (+-64): the two-sweep rows pass
+    (1, 300, 2, 127, 0, 1),     # 128 causal taps, ragged last tile
+    (2, 200, 1, 100, 20, 1),    # lopsided, wide
+    (1, 256, 2, 64, 64, 2),     # wide and dilated
+    (1, 70, 1, 40, 41, 1),      # just past 64 taps on a sequence barely longer than a tile
 ])
 def test_tensor_core_backward_matches_fp32_math_kernels(monkeypatch, dtype, B, S, H, left, right, dil):
-    """The mma backward (16-bit, D = 64, at most 64 taps between the two sides) against the warp-level
+    """The mma backward (16-bit, D = 64, at most 128 taps between the two sides) against the warp-level
     kernels, which compute in fp32 from the same 16-bit inputs and are themselves held to autograd through
     the reference's python oracle (tests/python/test_cuda_backward.py:75-101)."""
     spec = PatternSpec(left=left, right=right, dilation=dil)
