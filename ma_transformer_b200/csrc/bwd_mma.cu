@@ -58,15 +58,24 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool v
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-// rows [row0, row0 + nrows) of one head into swizzled shared memory; rows outside [0, S) become zeros
+// rows [row0, row0 + nrows) of one head into swizzled shared memory (nrows a multiple of 16); rows outside
+// [0, S) become zeros.  A thread keeps its 16-byte chunk and moves 16 rows per step, so the swizzle term
+// (row & 7) is fixed and source and destination advance by constants.
 template <typename T>
 __device__ __forceinline__ void stage_rows(uint32_t dst, const T *head, int64_t row0, int nrows, int64_t S,
                                            int64_t stride) {
-    for (int idx = threadIdx.x; idx < nrows * 8; idx += kThreads) {
-        const int row = idx >> 3, chunk = idx & 7;
-        const int64_t gr = row0 + row;
-        const bool ok = gr >= 0 && gr < S;
-        cp_async16(dst + swz(row, chunk), head + (ok ? gr : 0) * stride + chunk * 8, ok);
+    const int chunk = threadIdx.x & 7, rsub = threadIdx.x >> 3;
+    uint32_t d = dst + swz(rsub, chunk);
+    int64_t gr = row0 + rsub;
+    const T *src = head + gr * stride + chunk * 8;
+    const int64_t step = 16 * stride;
+    if (row0 >= 0 && row0 + nrows <= S) {
+        for (int i = 0; i < nrows; i += 16, d += 16 * 128, src += step) cp_async16(d, src, true);
+    } else {
+        for (int i = 0; i < nrows; i += 16, d += 16 * 128, src += step, gr += 16) {
+            const bool ok = gr >= 0 && gr < S;
+            cp_async16(d, ok ? src : head, ok);
+        }
     }
 }
 
