@@ -183,10 +183,11 @@ const char *mat_last_kernel(void) { return g_last_kernel; }
 
 int mat_device_status(int *status_out) {
     if (!status_out) return fail(MAT_ERR_INVALID, "status_out is NULL");
-    int a = 0, b = 0;
+    int a = 0, b = 0, c = 0;
     if (int rc = flash_status_read_and_clear(&a)) return rc;
     if (int rc = umma_status_read_and_clear(&b)) return rc;
-    *status_out = a | b;
+    if (int rc = bwd_status_read_and_clear(&c)) return rc;
+    *status_out = a | b | c;
     return MAT_OK;
 }
 

@@ -17,9 +17,9 @@
 // Both passes share the structure "16 rows per warp against a band of at most 80 columns"
 // (144 for windows of more than 64 taps, where the rows pass sweeps the band twice instead of
 // holding it in registers):
-// the row operands are A fragments held in registers, the band operands sit in shared
-// memory (128-byte rows, 16-byte chunks XOR-swizzled by the row so every ldmatrix is
-// conflict-free) and feed mma.sync.m16n8k16 as B fragments, plain for the score-shaped
+// one thread stages the tile's rows and the band by TMA (64-row boxes, 128-byte swizzle, zeros
+// outside the sequence; the wait for them is bounded), the row operands are A fragments held in
+// registers, the band operands stay in shared memory (every ldmatrix conflict-free) and feed mma.sync.m16n8k16 as B fragments, plain for the score-shaped
 // products and transposed for the output-shaped ones.  A dilated window over [B,S,H,64] is a
 // plain window over the same bytes viewed as [B, S/dil, dil*H, 64], so the kernel never sees
 // a dilation.
@@ -38,7 +38,7 @@ constexpr int kThreads = 128;
 // NP = 16-column groups one warp's rows can reach: 5 (16 + 64 = 80 columns) for windows of at most 64 taps
 // between the two sides, 9 (16 + 128 = 144 columns) for up to 128 (the reference's default +-64)
 constexpr int band_rows_max(int NP) { return 48 + 16 * NP; }
-constexpr int smem_bytes(int NP) { return 2 * 8192 + band_rows_max(NP) * (2 * 128 + (int)sizeof(float2)); }
+constexpr int smem_bytes(int NP) { return 2 * 8192 + band_rows_max(NP) * (2 * 128 + (int)sizeof(float2)) + 16; }
 
 struct BwdArgs {
     const void *q, *k, *v, *go;
@@ -52,32 +52,8 @@ struct BwdArgs {
 __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4));
 }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid) {
-    const int n = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
-// rows [row0, row0 + nrows) of one head into swizzled shared memory (nrows a multiple of 16); rows outside
-// [0, S) become zeros.  A thread keeps its 16-byte chunk and moves 16 rows per step, so the swizzle term
-// (row & 7) is fixed and source and destination advance by constants.
-template <typename T>
-__device__ __forceinline__ void stage_rows(uint32_t dst, const T *head, int64_t row0, int nrows, int64_t S,
-                                           int64_t stride) {
-    const int chunk = threadIdx.x & 7, rsub = threadIdx.x >> 3;
-    uint32_t d = dst + swz(rsub, chunk);
-    int64_t gr = row0 + rsub;
-    const T *src = head + gr * stride + chunk * 8;
-    const int64_t step = 16 * stride;
-    if (row0 >= 0 && row0 + nrows <= S) {
-        for (int i = 0; i < nrows; i += 16, d += 16 * 128, src += step) cp_async16(d, src, true);
-    } else {
-        for (int i = 0; i < nrows; i += 16, d += 16 * 128, src += step, gr += 16) {
-            const bool ok = gr >= 0 && gr < S;
-            cp_async16(d, ok ? src : head, ok);
-        }
-    }
-}
+// a kernel whose bounded wait for its tile copies ran out leaves 1 here and returns (read by mat_device_status)
+__device__ int g_bwd_status = 0;
 
 __device__ __forceinline__ float quad_max(float x) {
     x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 1));
@@ -113,7 +89,8 @@ __device__ __forceinline__ void store_tile(uint8_t *smem, uint32_t tile_off, con
 
 template <typename T, bool COLS, int NP>
 __global__ void __launch_bounds__(kThreads, NP == 5 ? 4 : 3)
-bwd_window_mma_kernel(BwdArgs a) {
+bwd_window_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                      const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mgo, BwdArgs a) {
     constexpr int kPairs = NP;
     extern __shared__ __align__(1024) uint8_t smem[];
     using M = ptx::Mma<T>;
@@ -126,20 +103,32 @@ bwd_window_mma_kernel(BwdArgs a) {
     const int np = min(kPairs, (15 + W) / 16 + 1);  // 16-column groups a warp walks
     const int64_t stride = a.HH * 64;
     const int64_t head_off = (b * a.S * a.HH + h) * 64;
-    const T *x1 = (const T *)(COLS ? a.k : a.q) + head_off;    // row operands: one A fragment set each
-    const T *x2 = (const T *)(COLS ? a.v : a.go) + head_off;
-    const T *y1 = (const T *)(COLS ? a.q : a.k) + head_off;    // band operands
-    const T *y2 = (const T *)(COLS ? a.go : a.v) + head_off;
+    const CUtensorMap *x1 = COLS ? &mk : &mq, *x2 = COLS ? &mv : &mgo;   // row operands: one A fragment set each
+    const CUtensorMap *y1 = COLS ? &mq : &mk, *y2 = COLS ? &mgo : &mv;   // band operands
     constexpr uint32_t oX1 = 0, oX2 = 8192, oY1 = 16384, oY2 = oY1 + band_rows_max(NP) * 128,
-                       oSt = oY2 + band_rows_max(NP) * 128;
+                       oSt = oY2 + band_rows_max(NP) * 128, oBar = oSt + band_rows_max(NP) * 8;
     const uint32_t sbase = ptx::smem_u32(smem);
     float2 *sst = (float2 *)(smem + oSt);
+    uint64_t *bar = (uint64_t *)(smem + oBar);
 
+    // One thread stages everything by TMA: 64-row boxes, 128-byte swizzle (chunk ^ (row & 7), the pattern swz()
+    // addresses), rows outside [0, S) arrive as zeros.  Band boxes beyond the groups the warps walk are skipped.
     const int band_rows = 48 + 16 * np;
-    stage_rows(sbase + oX1, x1, r0, kTile, a.S, stride);
-    stage_rows(sbase + oX2, x2, r0, kTile, a.S, stride);
-    stage_rows(sbase + oY1, y1, c0, band_rows, a.S, stride);
-    stage_rows(sbase + oY2, y2, c0, band_rows, a.S, stride);
+    const int boxes = (band_rows + 63) / 64;
+    if (tid == 0) {
+        ptx::mbar_init(bar, 1);
+        ptx::fence_barrier_init();
+    }
+    __syncthreads();
+    if (tid == 0) {
+        ptx::mbar_expect_tx(bar, (uint32_t)((2 + 2 * boxes) * 8192));
+        ptx::tma_load_4d(smem + oX1, x1, bar, 0, (int)h, (int)r0, (int)b);
+        ptx::tma_load_4d(smem + oX2, x2, bar, 0, (int)h, (int)r0, (int)b);
+        for (int i = 0; i < boxes; ++i) {
+            ptx::tma_load_4d(smem + oY1 + i * 8192, y1, bar, 0, (int)h, (int)c0 + 64 * i, (int)b);
+            ptx::tma_load_4d(smem + oY2 + i * 8192, y2, bar, 0, (int)h, (int)c0 + 64 * i, (int)b);
+        }
+    }
     if (COLS) {
         const float2 *st = a.stats + (b * a.HH + h) * a.S;
         for (int i = tid; i < band_rows; i += kThreads) {
@@ -147,7 +136,10 @@ bwd_window_mma_kernel(BwdArgs a) {
             sst[i] = (gi >= 0 && gi < a.S) ? st[gi] : make_float2(0.f, 0.f);
         }
     }
-    cp_async_wait_all();
+    if (!ptx::mbar_wait(bar, 0)) {
+        atomicExch(&g_bwd_status, 1);
+        return;
+    }
     __syncthreads();
 
     // A fragments of the warp's 16 rows, four k-steps over the head width
@@ -447,14 +439,19 @@ bwd_window_mma_kernel(BwdArgs a) {
 }
 
 template <typename T, int NP>
-int launch_bwd(const BwdArgs &a, cudaStream_t stream) {
+int launch_bwd(const BwdArgs &a, int dtype, cudaStream_t stream) {
     int rc = ensure_dynamic_smem((const void *)bwd_window_mma_kernel<T, false, NP>, smem_bytes(NP), "bwd_window_mma rows");
     if (rc != MAT_OK) return rc;
     rc = ensure_dynamic_smem((const void *)bwd_window_mma_kernel<T, true, NP>, smem_bytes(NP), "bwd_window_mma cols");
     if (rc != MAT_OK) return rc;
+    CUtensorMap mq, mk, mv, mgo;
+    if ((rc = make_row_tensor_map(&mq, a.q, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
+    if ((rc = make_row_tensor_map(&mk, a.k, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
+    if ((rc = make_row_tensor_map(&mv, a.v, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
+    if ((rc = make_row_tensor_map(&mgo, a.go, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
     const dim3 grid((unsigned)((a.S + kTile - 1) / kTile), (unsigned)a.HH, (unsigned)a.B);
-    bwd_window_mma_kernel<T, false, NP><<<grid, kThreads, smem_bytes(NP), stream>>>(a);
-    bwd_window_mma_kernel<T, true, NP><<<grid, kThreads, smem_bytes(NP), stream>>>(a);
+    bwd_window_mma_kernel<T, false, NP><<<grid, kThreads, smem_bytes(NP), stream>>>(mq, mk, mv, mgo, a);
+    bwd_window_mma_kernel<T, true, NP><<<grid, kThreads, smem_bytes(NP), stream>>>(mq, mk, mv, mgo, a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "tensor-core backward launch");
     note_kernel("bwd_window_mma");
@@ -462,6 +459,13 @@ int launch_bwd(const BwdArgs &a, cudaStream_t stream) {
 }
 
 }  // namespace
+
+int bwd_status_read_and_clear(int *out) {
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_bwd_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_bwd_status, &zero, sizeof(int));
+    return e == cudaSuccess ? MAT_OK : cuda_fail(e, "reading the backward kernels' status word");
+}
 
 bool bwd_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t left, int64_t right,
                       int64_t dil) {
@@ -489,8 +493,8 @@ int launch_bwd_mma(const void *q, const void *k, const void *v, const void *dout
     if (a.right < 0) a.right = 0;
     a.scale = scale;
     if (a.left + a.right <= 64)
-        return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16, 5>(a, stream) : launch_bwd<__half, 5>(a, stream);
-    return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16, 9>(a, stream) : launch_bwd<__half, 9>(a, stream);
+        return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16, 5>(a, dtype, stream) : launch_bwd<__half, 5>(a, dtype, stream);
+    return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16, 9>(a, dtype, stream) : launch_bwd<__half, 9>(a, dtype, stream);
 }
 
 }  // namespace mat

@@ -3,6 +3,7 @@
 // the launchers each kernel file exports to the C-ABI layer.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -77,6 +78,11 @@ struct GlobalRowSplit {
 GlobalRowSplit plan_umma_global_rows(const Problem &p);
 int launch_umma_global_rows(const Problem &p, const GlobalRowSplit &g, float *partial);
 
+// Tiled tensor map over 16-bit [B, S1, HH, 64] rows (mma_flash.cu): dims {64, HH, S1, B}, box {64, 1, box_rows, 1},
+// 128-byte swizzle, zeros for rows outside the tensor.
+int make_row_tensor_map(CUtensorMap *m, const void *base, int dtype, int64_t HH, int64_t S1, int64_t B,
+                        int box_rows);
+int bwd_status_read_and_clear(int *out);     // bwd_mma.cu
 // tensor-core backward of narrow windows (bwd_mma.cu): 16-bit types, D = 64, left + right <= 128 taps
 bool bwd_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t left, int64_t right,
                       int64_t dil);

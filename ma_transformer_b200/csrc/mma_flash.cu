@@ -948,6 +948,11 @@ int launch_longformer_noalloc(const Problem &p) {
                                : launch_longformer_static<__half>(p, scratch);
 }
 
+int make_row_tensor_map(CUtensorMap *m, const void *base, int dtype, int64_t HH, int64_t S1, int64_t B,
+                        int box_rows) {
+    return make_map(m, base, dtype, HH, S1, B, box_rows);
+}
+
 int flash_status_read_and_clear(int *out) {
     int zero = 0;
     cudaError_t e = cudaMemcpyFromSymbol(out, g_flash_status, sizeof(int));
