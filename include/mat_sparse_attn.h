@@ -135,10 +135,11 @@ int mat_sparse_attn_fwd_sharded(const void *q, const void *k, const void *v, voi
  * window that covers S (right = 0 when causal).  MAT_WINDOW patterns, q_offset = 0.
  * Deterministic (no atomics).  workspace: mat_sparse_attn_bwd_workspace_bytes()
  * bytes of device scratch, 256-byte aligned (per-row log-sum-exp and delta).
- * 16-bit inputs with D = 64, S a multiple of the dilation and at most 128 taps
- * between the two sides of the window run on tensor-core kernels (probabilities
- * rounded to the input type for the second products); everything else, fp32
- * included, on warp-level kernels with fp32 math throughout.
+ * 16-bit inputs with D = 64 and S a multiple of the dilation run on tensor-core
+ * kernels (probabilities rounded to the input type for the second products; the
+ * band of a window with at most 128 taps between its two sides stays in shared
+ * memory, wider windows and dense stream it); everything else, fp32 included, on
+ * warp-level kernels with fp32 math throughout.
  */
 int mat_sparse_attn_bwd(const void *q, const void *k, const void *v, const void *dout,
                         void *dq, void *dk, void *dv, int64_t B, int64_t S, int64_t H, int64_t D,

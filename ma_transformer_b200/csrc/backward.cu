@@ -16,8 +16,7 @@
 //                    dV_j = sum_i p_ij dO_i.
 //
 // Written for clarity and exactness (fp32 math for every dtype), any head width up
-// to 512.  16-bit inputs with head width 64 and at most 128 taps between the two
-// sides of the window go to the tensor-core kernels of bwd_mma.cu instead.
+// to 512.  16-bit inputs with head width 64 go to the tensor-core kernels of bwd_mma.cu instead.
 #include "mat_common.cuh"
 
 namespace mat {

@@ -1,6 +1,8 @@
-// Tensor-core backward of narrow window attention: bf16 / fp16, head width 64, windows
-// with left + right <= 128 taps (causal, two-sided, and dilated through a view), the
-// shapes the tiled forward window kernels serve.
+// Tensor-core backward of window attention for bf16 / fp16 with head width 64: causal,
+// two-sided, dilated (through a view) and dense (the window that covers the sequence).
+// Windows with left + right <= 128 taps keep their whole band in shared memory
+// (bwd_window_mma_kernel); wider ones stream it in 64-column chunks (bwd_stream_mma_kernel,
+// described above that kernel).
 //
 // Replaces sparse_attention_backward_kernel (src/cuda/sparse_attention_kernel.cu:265-346),
 // which runs one thread per query row and scatters dK / dV with fp32 atomicAdd (:322, :343).
@@ -458,6 +460,281 @@ int launch_bwd(const BwdArgs &a, int dtype, cudaStream_t stream) {
     return MAT_OK;
 }
 
+// ---- any window wider than 128 taps, dense included: the band streamed through shared memory ----------------
+//
+// Same two passes, same roles, but the band no longer fits in shared memory: it is walked in 64-column chunks
+// aligned to the sequence (one TMA box of each band operand per chunk, single-buffered; the other resident CTAs
+// cover the wait).  The rows pass walks it twice, once for the row statistics with a running maximum and once for
+// dQ; the cols pass walks it once.  A warp skips the 16-column groups none of its rows can see and masks only
+// the groups that straddle an edge of the window or the end of the sequence.
+constexpr int kStreamSmemBytes = 4 * 8192 + 64 * (int)sizeof(float2) + 16;
+
+template <typename T, bool COLS>
+__global__ void __launch_bounds__(kThreads, COLS ? 3 : 4)
+bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                      const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mgo, BwdArgs a) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    using M = ptx::Mma<T>;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int64_t r0 = (int64_t)blockIdx.x * kTile;
+    const int64_t h = blockIdx.y, b = blockIdx.z;
+    const int64_t back = COLS ? a.right : a.left, fwd = COLS ? a.left : a.right;   // row r sees columns r - back .. r + fwd
+    const unsigned W = (unsigned)(back + fwd);
+    const int64_t stride = a.HH * 64;
+    const int64_t head_off = (b * a.S * a.HH + h) * 64;
+    const CUtensorMap *x1 = COLS ? &mk : &mq, *x2 = COLS ? &mv : &mgo;
+    const CUtensorMap *y1 = COLS ? &mq : &mk, *y2 = COLS ? &mgo : &mv;
+    constexpr uint32_t oX1 = 0, oX2 = 8192, oY1 = 16384, oY2 = 24576, oSt = 32768, oBar = oSt + 512;
+    const uint32_t sbase = ptx::smem_u32(smem);
+    float2 *sst = (float2 *)(smem + oSt);
+    uint64_t *bar = (uint64_t *)(smem + oBar);
+    const int64_t lo = r0 - back > 0 ? r0 - back : 0;
+    const int64_t hi = r0 + 63 + fwd < a.S - 1 ? r0 + 63 + fwd : a.S - 1;
+    const int64_t k_first = lo / 64, k_last = hi / 64;
+    const int64_t wrow = r0 + 16 * warp;     // the warp's first row
+    uint32_t phase = 0;
+
+    if (tid == 0) {
+        ptx::mbar_init(bar, 1);
+        ptx::fence_barrier_init();
+    }
+    // chunk k of the band operands (and the tile's own rows with the first one) into shared memory
+    auto load_chunk = [&](int64_t k, bool with_tile) -> bool {
+        __syncthreads();   // the previous chunk's readers are done (and the barrier is initialised)
+        if (tid == 0) {
+            ptx::mbar_expect_tx(bar, with_tile ? 32768u : 16384u);
+            if (with_tile) {
+                ptx::tma_load_4d(smem + oX1, x1, bar, 0, (int)h, (int)r0, (int)b);
+                ptx::tma_load_4d(smem + oX2, x2, bar, 0, (int)h, (int)r0, (int)b);
+            }
+            ptx::tma_load_4d(smem + oY1, y1, bar, 0, (int)h, (int)(64 * k), (int)b);
+            ptx::tma_load_4d(smem + oY2, y2, bar, 0, (int)h, (int)(64 * k), (int)b);
+        }
+        if (COLS && tid < 64) {
+            const int64_t gi = 64 * k + tid;
+            sst[tid] = gi < a.S ? a.stats[(b * a.HH + h) * a.S + gi] : make_float2(0.f, 0.f);
+        }
+        const bool ok = ptx::mbar_wait(bar, phase);
+        phase ^= 1;
+        if (COLS) __syncthreads();   // the statistics of this chunk are visible
+        return ok;
+    };
+    const int mi = lane >> 3, rr = lane & 7;
+    const int brow_n = (mi >> 1) * 8 + rr, bchk_n = mi & 1;   // + 16p / + 2ks: plain B fragments
+    const int brow_t = (mi & 1) * 8 + rr, bchk_t = mi >> 1;   // + 16p / + 2dn: transposed B fragments
+    const float sl = a.scale * 1.4426950408889634f;
+    uint32_t a1[4][4], a2[4][4];
+    auto load_a = [&]() {
+        const int row = 16 * warp + (lane & 15), cadd = lane >> 4;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            ptx::ldmatrix_x4(a1[ks], sbase + oX1 + swz(row, 2 * ks + cadd));
+            ptx::ldmatrix_x4(a2[ks], sbase + oX2 + swz(row, 2 * ks + cadd));
+        }
+    };
+    // group p of chunk k: 0 = none of the warp's rows sees it, 1 = every (row, column) pair is seen, 2 = mask it
+    auto group_kind = [&](int64_t k, int p) -> int {
+        const int64_t c = 64 * k + 16 * p;      // the group's first column
+        if (c + 15 < wrow - back || c > wrow + 15 + fwd || c >= a.S) return 0;
+        return (c - (wrow + 15) >= -back && c + 15 - wrow <= fwd && c + 15 < a.S) ? 1 : 2;
+    };
+    // column 64k + 16p + cc of row wrow + r is seen iff -back <= column - row <= fwd and the column exists
+    auto seen = [&](int64_t k, int p, int cc, int r) -> bool {
+        const int64_t c = 64 * k + 16 * p;
+        const int d = (int)(c - wrow) + cc - r;
+        return (unsigned)(d + (int)back) <= W && c + cc < a.S;
+    };
+    auto group_products = [&](int p, float (&s)[2][4], float (&dp)[2][4]) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[nt][e] = dp[nt][e] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            uint32_t bf[4];
+            ptx::ldmatrix_x4(bf, sbase + oY1 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
+            M::run(s[0], a1[ks], bf[0], bf[1]);
+            M::run(s[1], a1[ks], bf[2], bf[3]);
+            ptx::ldmatrix_x4(bf, sbase + oY2 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
+            M::run(dp[0], a2[ks], bf[0], bf[1]);
+            M::run(dp[1], a2[ks], bf[2], bf[3]);
+        }
+    };
+
+    if constexpr (!COLS) {
+        float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f}, dr[2] = {0.f, 0.f};
+        for (int64_t k = k_first; k <= k_last; ++k) {
+            if (!load_chunk(k, k == k_first)) {
+                atomicExch(&g_bwd_status, 1);
+                return;
+            }
+            if (k == k_first) load_a();
+#pragma unroll 1
+            for (int p = 0; p < 4; ++p) {
+                const int kind = group_kind(k, p);
+                if (kind == 0) continue;
+                float s[2][4], dp[2][4];
+                group_products(p, s, dp);
+                if (kind == 2) {
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (!seen(k, p, 8 * nt + 2 * t + (e & 1), g + (e >> 1) * 8)) s[nt][e] = -INFINITY;
+                }
+                float gm[2] = {-INFINITY, -INFINITY}, msl[2];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) gm[e >> 1] = fmaxf(gm[e >> 1], s[nt][e]);
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const float m_new = fmaxf(mx[hh], quad_max(gm[hh]));
+                    const float alpha = mx[hh] == -INFINITY ? 0.f : ptx::ex2((mx[hh] - m_new) * sl);
+                    sum[hh] *= alpha;
+                    dr[hh] *= alpha;
+                    mx[hh] = m_new;
+                    msl[hh] = m_new == -INFINITY ? 0.f : m_new * sl;
+                }
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float ex = ptx::ex2(fmaf(s[nt][e], sl, -msl[e >> 1]));
+                        sum[e >> 1] += ex;
+                        dr[e >> 1] = fmaf(ex, dp[nt][e], dr[e >> 1]);
+                    }
+            }
+        }
+        float lse[2], dsc[2];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            sum[hh] = quad_sum(sum[hh]);
+            dr[hh] = quad_sum(dr[hh]);            // every lane takes part in the shuffles, live row or not
+            const bool live = sum[hh] > 0.f;
+            lse[hh] = live ? mx[hh] * sl + log2f(sum[hh]) : 0.f;
+            dsc[hh] = live ? dr[hh] / sum[hh] * a.scale : 0.f;
+        }
+        if (t == 0) {
+            float2 *st = a.stats + (b * a.HH + h) * a.S;
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int64_t gr = wrow + g + 8 * hh;
+                if (gr < a.S) st[gr] = make_float2(lse[hh], dsc[hh]);
+            }
+        }
+        float o[8][4];
+#pragma unroll
+        for (int dt = 0; dt < 8; ++dt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[dt][e] = 0.f;
+        for (int64_t k = k_first; k <= k_last; ++k) {
+            if (!load_chunk(k, false)) {
+                atomicExch(&g_bwd_status, 1);
+                return;
+            }
+#pragma unroll 1
+            for (int p = 0; p < 4; ++p) {
+                const int kind = group_kind(k, p);
+                if (kind == 0) continue;
+                float s[2][4], dp[2][4];
+                group_products(p, s, dp);
+                uint32_t af[4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    float ds[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float pp = ptx::ex2(fmaf(s[nt][e], sl, -lse[e >> 1]));
+                        if (kind == 2 && !seen(k, p, 8 * nt + 2 * t + (e & 1), g + (e >> 1) * 8)) pp = 0.f;
+                        ds[e] = pp * fmaf(dp[nt][e], a.scale, -dsc[e >> 1]);
+                    }
+                    af[2 * nt] = M::pack(ds[0], ds[1]);
+                    af[2 * nt + 1] = M::pack(ds[2], ds[3]);
+                }
+#pragma unroll
+                for (int dn = 0; dn < 4; ++dn) {
+                    uint32_t bf[4];
+                    ptx::ldmatrix_x4_trans(bf, sbase + oY1 + swz(brow_t + 16 * p, 2 * dn + bchk_t));
+                    M::run(o[2 * dn], af, bf[0], bf[1]);
+                    M::run(o[2 * dn + 1], af, bf[2], bf[3]);
+                }
+            }
+        }
+        store_tile<T>(smem, oX1, o, (T *)a.dq + head_off, r0, a.S, stride, warp, lane);
+    } else {
+        float ok_[8][4], ov[8][4];
+#pragma unroll
+        for (int dt = 0; dt < 8; ++dt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ok_[dt][e] = ov[dt][e] = 0.f;
+        for (int64_t k = k_first; k <= k_last; ++k) {
+            if (!load_chunk(k, k == k_first)) {
+                atomicExch(&g_bwd_status, 1);
+                return;
+            }
+            if (k == k_first) load_a();
+#pragma unroll 1
+            for (int p = 0; p < 4; ++p) {
+                const int kind = group_kind(k, p);
+                if (kind == 0) continue;
+                float st[2][4], dpt[2][4];
+                group_products(p, st, dpt);
+                uint32_t ap[4], as[4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int cb = 8 * nt + 2 * t;
+                    const float4 sd = *(const float4 *)&sst[16 * p + cb];   // (lse, delta scale) of two queries
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float lse = (e & 1) ? sd.z : sd.x, dl = (e & 1) ? sd.w : sd.y;
+                        float pp = ptx::ex2(fmaf(st[nt][e], sl, -lse));
+                        if (kind == 2 && !seen(k, p, cb + (e & 1), g + (e >> 1) * 8)) pp = 0.f;
+                        st[nt][e] = pp;
+                        dpt[nt][e] = pp * fmaf(dpt[nt][e], a.scale, -dl);
+                    }
+                    ap[2 * nt] = M::pack(st[nt][0], st[nt][1]);
+                    ap[2 * nt + 1] = M::pack(st[nt][2], st[nt][3]);
+                    as[2 * nt] = M::pack(dpt[nt][0], dpt[nt][1]);
+                    as[2 * nt + 1] = M::pack(dpt[nt][2], dpt[nt][3]);
+                }
+#pragma unroll
+                for (int dn = 0; dn < 4; ++dn) {
+                    uint32_t bf[4];
+                    ptx::ldmatrix_x4_trans(bf, sbase + oY2 + swz(brow_t + 16 * p, 2 * dn + bchk_t));
+                    M::run(ov[2 * dn], ap, bf[0], bf[1]);
+                    M::run(ov[2 * dn + 1], ap, bf[2], bf[3]);
+                    ptx::ldmatrix_x4_trans(bf, sbase + oY1 + swz(brow_t + 16 * p, 2 * dn + bchk_t));
+                    M::run(ok_[2 * dn], as, bf[0], bf[1]);
+                    M::run(ok_[2 * dn + 1], as, bf[2], bf[3]);
+                }
+            }
+        }
+        store_tile<T>(smem, oX1, ok_, (T *)a.dk + head_off, r0, a.S, stride, warp, lane);
+        store_tile<T>(smem, oX2, ov, (T *)a.dv + head_off, r0, a.S, stride, warp, lane);
+    }
+}
+
+template <typename T>
+int launch_bwd_stream(const BwdArgs &a, int dtype, cudaStream_t stream) {
+    int rc = ensure_dynamic_smem((const void *)bwd_stream_mma_kernel<T, false>, kStreamSmemBytes, "bwd_stream_mma rows");
+    if (rc != MAT_OK) return rc;
+    rc = ensure_dynamic_smem((const void *)bwd_stream_mma_kernel<T, true>, kStreamSmemBytes, "bwd_stream_mma cols");
+    if (rc != MAT_OK) return rc;
+    CUtensorMap mq, mk, mv, mgo;
+    if ((rc = make_row_tensor_map(&mq, a.q, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
+    if ((rc = make_row_tensor_map(&mk, a.k, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
+    if ((rc = make_row_tensor_map(&mv, a.v, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
+    if ((rc = make_row_tensor_map(&mgo, a.go, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
+    const dim3 grid((unsigned)((a.S + kTile - 1) / kTile), (unsigned)a.HH, (unsigned)a.B);
+    bwd_stream_mma_kernel<T, false><<<grid, kThreads, kStreamSmemBytes, stream>>>(mq, mk, mv, mgo, a);
+    bwd_stream_mma_kernel<T, true><<<grid, kThreads, kStreamSmemBytes, stream>>>(mq, mk, mv, mgo, a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "tensor-core backward launch");
+    note_kernel("bwd_stream_mma");
+    return MAT_OK;
+}
+
 }  // namespace
 
 int bwd_status_read_and_clear(int *out) {
@@ -475,7 +752,6 @@ bool bwd_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int
     if (env && strcmp(env, "warp") == 0) return false;
     const int64_t Sv = S / dil;
     const int64_t l = left < Sv - 1 ? left : Sv - 1, r = right < Sv - 1 ? right : Sv - 1;
-    if (l + r > 128) return false;
     return H * dil <= 65535 && B <= 65535;
 }
 
@@ -494,7 +770,9 @@ int launch_bwd_mma(const void *q, const void *k, const void *v, const void *dout
     a.scale = scale;
     if (a.left + a.right <= 64)
         return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16, 5>(a, dtype, stream) : launch_bwd<__half, 5>(a, dtype, stream);
-    return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16, 9>(a, dtype, stream) : launch_bwd<__half, 9>(a, dtype, stream);
+    if (a.left + a.right <= 128)
+        return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16, 9>(a, dtype, stream) : launch_bwd<__half, 9>(a, dtype, stream);
+    return dtype == MAT_BF16 ? launch_bwd_stream<__nv_bfloat16>(a, dtype, stream) : launch_bwd_stream<__half>(a, dtype, stream);
 }
 
 }  // namespace mat

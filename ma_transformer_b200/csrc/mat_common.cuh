@@ -83,7 +83,7 @@ int launch_umma_global_rows(const Problem &p, const GlobalRowSplit &g, float *pa
 int make_row_tensor_map(CUtensorMap *m, const void *base, int dtype, int64_t HH, int64_t S1, int64_t B,
                         int box_rows);
 int bwd_status_read_and_clear(int *out);     // bwd_mma.cu
-// tensor-core backward of narrow windows (bwd_mma.cu): 16-bit types, D = 64, left + right <= 128 taps
+// tensor-core backward of window patterns, dense included (bwd_mma.cu): 16-bit types, D = 64, S a multiple of the dilation
 bool bwd_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t left, int64_t right,
                       int64_t dil);
 int launch_bwd_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk, void *dv,

@@ -473,9 +473,16 @@ def test_dense_backward_and_custom_windows(causal):
     (2, 200, 1, 100, 20, 1),    # lopsided, wide
     (1, 256, 2, 64, 64, 2),     # wide and dilated
     (1, 70, 1, 40, 41, 1),      # just past 64 taps on a sequence barely longer than a tile
+    (1, 512, 2, 512, 512, 1),   # dense (the reference's dense_backward): the band streamed in 64-column chunks
+    (1, 300, 2, 300, 0, 1),     # causal dense, ragged last tile
+    (2, 200, 1, 150, 20, 1),    # wide and lopsided
+    (1, 1024, 1, 200, 0, 1),    # 201 causal taps: chunks skipped on both sides of the band
+    (1, 512, 2, 100, 100, 2),   # wide, two-sided and dilated
+    (1, 129, 1, 65, 64, 1),     # one tap past the resident-band kernels
 ])
 def test_tensor_core_backward_matches_fp32_math_kernels(monkeypatch, dtype, B, S, H, left, right, dil):
-    """The mma backward (16-bit, D = 64, at most 128 taps between the two sides) against the warp-level
+    """The mma backward (16-bit, D = 64; band resident in shared memory up to 128 taps between the two sides,
+    streamed beyond) against the warp-level
     kernels, which compute in fp32 from the same 16-bit inputs and are themselves held to autograd through
     the reference's python oracle (tests/python/test_cuda_backward.py:75-101)."""
     spec = PatternSpec(left=left, right=right, dilation=dil)
@@ -483,7 +490,8 @@ def test_tensor_core_backward_matches_fp32_math_kernels(monkeypatch, dtype, B, S
     go = torch.randn(B, S, H, 64, generator=torch.Generator().manual_seed(92)).to(dtype).to(DEV)
     got = ext.backward_pattern(q, k, v, go, spec)
     torch.cuda.synchronize()
-    assert nat.last_kernel() == "bwd_window_mma"
+    taps = min(left, S // dil - 1) + min(right, S // dil - 1)
+    assert nat.last_kernel() == ("bwd_window_mma" if taps <= 128 else "bwd_stream_mma")
     monkeypatch.setenv("MAT_BWD_KERNEL", "warp")
     want = ext.backward_pattern(q, k, v, go, spec)
     torch.cuda.synchronize()
