@@ -41,6 +41,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <cstring>
 #include <type_traits>
 #include <mutex>
 
@@ -65,6 +66,7 @@ struct UmmaParams {
     int32_t H;
     int32_t block, per_blk;  // layout block edge, 64-key chunks per block
     int32_t causal;
+    int32_t win_left, win_right;   // kModeDense: row p uses keys p - win_left .. p + win_right (clamped to the sequence by the host)
     int64_t n_qblocks;
     const int32_t *rowptr;
     const int32_t *colidx;
@@ -318,9 +320,12 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int q0 = (MODE == kModeGlobalRows ? blockIdx.y / P.n_splits : blockIdx.y) * (NT * kTileQ);
     // key range of the CTA: a split of the sequence (global rows), or everything / everything up to
     // the CTA's last row (dense and causal dense)
-    const int range_lo = MODE == kModeGlobalRows ? split * P.split_len : 0;
+    // (a window: from the 64-key chunk that holds the first row's first key to the last row's last key)
+    const int range_lo = MODE == kModeGlobalRows ? split * P.split_len
+                       : MODE == kModeDense ? (max(0, q0 + P.off - P.win_left) & ~(kTileK - 1)) : 0;
     const int range_hi = MODE == kModeGlobalRows ? min(range_lo + P.split_len, P.Skv)
-                       : (P.causal ? min(P.Skv, q0 + P.off + NT * kTileQ) : P.Skv);
+                       : MODE == kModeDense ? min(P.Skv, q0 + P.off + NT * kTileQ + P.win_right)
+                       : P.Skv;
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(bar_q, 1);
@@ -515,12 +520,17 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (mine) {
             // keys this row may use in the chunk: j < j_end
             int j_end = min(kTileK, (MODE == kModeGlobalRows ? range_hi : P.Skv) - kb);
-            if (MODE != kModeGlobalRows && P.causal) j_end = min(j_end, p - kb + 1);
+            if (MODE == kModeBlock && P.causal) j_end = min(j_end, p - kb + 1);
+            int j_begin = 0;   // and j >= j_begin (a window's left edge)
+            if (MODE == kModeDense) {
+                j_end = min(j_end, p + P.win_right - kb + 1);
+                j_begin = p - P.win_left - kb;
+            }
             float s[64];
             tmem_ld64(s_addr, s);
-            if (j_end < kTileK) {   // only the chunks on the causal diagonal or at the sequence end
+            if (j_end < kTileK || j_begin > 0) {   // only the chunks on an edge of the window or at the sequence end
 #pragma unroll
-                for (int i = 0; i < 64; ++i) if (i >= j_end) s[i] = -INFINITY;
+                for (int i = 0; i < 64; ++i) if (i >= j_end || i < j_begin) s[i] = -INFINITY;
             }
             float mq[4];   // four independent chains of three-input maxima
 #pragma unroll
@@ -679,6 +689,7 @@ int launch_t(const Problem &p) {
     up.block = (int32_t)p.pat.block;
     up.per_blk = up.block / kTileK;
     up.causal = p.pat.causal;
+    up.win_left = up.win_right = 0;
     up.n_qblocks = p.pat.n_qblocks;
     up.rowptr = p.pat.rowptr;
     up.colidx = p.pat.colidx;
@@ -693,21 +704,22 @@ int launch_t(const Problem &p) {
 }
 
 template <typename T>
-int launch_dense_t(const Problem &p, bool causal) {
+int launch_dense_t(const Problem &p) {
     CUtensorMap mq, mk, mv;
     if (int rc = make_map(&mq, p.q, p.dtype, p.H, p.Sq, p.B, kTileQ)) return rc;
     if (int rc = make_map(&mk, p.k, p.dtype, p.H, p.Skv, p.B, kTileK)) return rc;
     if (int rc = make_map(&mv, p.v, p.dtype, p.H, p.Skv, p.B, kTileK)) return rc;
     UmmaParams up;
     up.Sq = (int32_t)p.Sq; up.Skv = (int32_t)p.Skv; up.off = (int32_t)p.pat.q_offset; up.H = (int32_t)p.H;
-    up.block = kTileK; up.per_blk = 1; up.causal = causal; up.n_qblocks = 0; up.rowptr = up.colidx = nullptr;
+    up.block = kTileK; up.per_blk = 1; up.causal = 0; up.n_qblocks = 0; up.rowptr = up.colidx = nullptr;
+    up.win_left = (int32_t)std::min<int64_t>(p.pat.left, p.Skv); up.win_right = (int32_t)std::min<int64_t>(p.pat.right, p.Skv);
     up.sl2 = p.scale * 1.4426950408889634f;
     up.n_global = 0; up.gidx = nullptr; up.split_len = up.n_splits = up.ng_pad = 0; up.partial = nullptr;
     const int nt = tiles_per_cta();
     const dim3 grid((unsigned)p.H, (unsigned)((p.Sq + nt * kTileQ - 1) / (nt * kTileQ)), (unsigned)p.B);
     const int rc = nt == 2 ? launch_mode<T, kModeDense, 2>(mq, mk, mv, (T *)p.o, up, grid, p.stream, "umma dense kernel")
                            : launch_mode<T, kModeDense, 1>(mq, mk, mv, (T *)p.o, up, grid, p.stream, "umma dense kernel");
-    if (rc == MAT_OK) note_kernel("umma_dense");
+    if (rc == MAT_OK) note_kernel(up.win_left >= p.Skv - 1 && (up.win_right >= p.Skv - 1 || up.win_right == 0) ? "umma_dense" : "umma_window");
     return rc;
 }
 
@@ -720,6 +732,7 @@ int launch_global_rows_t(const Problem &p, const GlobalRowSplit &g, float *parti
     UmmaParams up;
     up.Sq = (int32_t)p.Sq; up.Skv = (int32_t)p.Skv; up.off = 0; up.H = (int32_t)p.H;
     up.block = kTileK; up.per_blk = 1; up.causal = 0; up.n_qblocks = 0; up.rowptr = up.colidx = nullptr;
+    up.win_left = up.win_right = 0;
     up.sl2 = p.scale * 1.4426950408889634f;
     up.n_global = (int32_t)p.pat.n_global;
     up.gidx = p.pat.gidx;
@@ -782,15 +795,23 @@ bool umma_block_supports(const Problem &p) {
 }
 
 // Dense and causal-dense attention (the window that covers the whole sequence, the reference's
-// dense_forward, src/cuda/sparse_attention_kernel.cu:348-382) on the same tcgen05 pipeline: every
-// 128-row tile walks all keys (up to its last row when causal) 64 at a time.
+// dense_forward, src/cuda/sparse_attention_kernel.cu:348-382) and windows of more than 128 taps between
+// their two sides on the same tcgen05 pipeline: every 128-row tile walks the keys its rows can see 64 at
+// a time; the chunks on an edge of the window are masked.  Narrower windows stay on the warp-level
+// kernels: a walk of four steps does not amortise the pipeline's start and read-out.  MAT_WINDOW_KERNEL=mma keeps
+// every window that is not dense on the warp-level kernels (debugging and measurement aid).
 bool umma_dense_supports(const Problem &p) {
     if (p.pat.kind != MAT_WINDOW || p.pat.dilation != 1) return false;
     if (p.dtype != MAT_BF16 && p.dtype != MAT_F16) return false;
     if (p.D != 64 || p.pat.q_offset % 64 != 0) return false;
-    const bool left_all = p.pat.left >= p.Skv - 1;
-    const bool right_all = p.pat.right >= p.Skv - 1, right_none = p.pat.right == 0;
-    if (!left_all || !(right_all || right_none)) return false;
+    if (p.k_prev || p.k_next) return false;   // neighbour shards are read by the warp-level kernel only
+    const int64_t left = std::min<int64_t>(p.pat.left, p.Skv - 1), right = std::min<int64_t>(p.pat.right, p.Skv - 1);
+    const bool dense = left >= p.Skv - 1 && (right >= p.Skv - 1 || right == 0);
+    if (!dense) {
+        if (left + right <= 128) return false;   // measured: the warp-level tiles win up to 128 taps (102 against 117 us at 64K x 8)
+        const char *force = std::getenv("MAT_WINDOW_KERNEL");
+        if (force && std::strcmp(force, "mma") == 0) return false;
+    }
     if (p.Skv < 256) return false;   // short sequences: the window kernels are as good and need no TMEM
     const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
     if (al % 16) return false;
@@ -798,8 +819,7 @@ bool umma_dense_supports(const Problem &p) {
 }
 
 int launch_umma_dense(const Problem &p) {
-    const bool causal = p.pat.right == 0;
-    return p.dtype == MAT_BF16 ? launch_dense_t<__nv_bfloat16>(p, causal) : launch_dense_t<__half>(p, causal);
+    return p.dtype == MAT_BF16 ? launch_dense_t<__nv_bfloat16>(p) : launch_dense_t<__half>(p);
 }
 
 int launch_umma_block(const Problem &p) {

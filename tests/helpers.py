@@ -47,3 +47,15 @@ def check_close(got: torch.Tensor, want: np.ndarray, dtype):
         tol = BF16_ABS if dtype == torch.bfloat16 else F16_ABS
         e = float(np.abs(got - want).max())
         assert e <= tol, f"max-abs {e:.3e} > {tol}"
+
+
+def expected_window_kernel(spec: PatternSpec, Skv: int) -> str:
+    """Which kernel family the library picks for a 16-bit, D = 64 window call it can tile (the routing
+    of run_problem): dense and windows of more than 128 taps on tcgen05 when the sequence is long
+    enough and the shard offset is a multiple of 64, the warp-level tiled kernel otherwise."""
+    left, right = min(spec.left, Skv - 1), min(spec.right, Skv - 1)
+    if spec.dilation != 1 or spec.q_offset % 64 or Skv < 256:
+        return "mma_window"
+    if left >= Skv - 1 and (right >= Skv - 1 or right == 0):
+        return "umma_dense"
+    return "umma_window" if left + right > 128 else "mma_window"

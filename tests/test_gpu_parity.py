@@ -10,7 +10,7 @@ import ma_transformer_b200 as mt
 from ma_transformer_b200 import _native as nat
 from ma_transformer_b200 import sparse_attention_cuda as ext
 from ma_transformer_b200.patterns import PatternSpec, band_random_block_layout, tridiagonal_block_layout
-from helpers import check_close, oracle_out, rel_err, seeded_qkv, to_oracle
+from helpers import check_close, expected_window_kernel, oracle_out, rel_err, seeded_qkv, to_oracle
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -83,10 +83,39 @@ WINDOW_SPECS = [
 def test_mma_window_vs_oracle(spec, dtype, B, S, H):
     q, k, v = seeded_qkv(11, B, S, H, 64, dtype)
     got = run(spec, q, k, v)
-    # a window that covers a long enough sequence is dense attention: that runs on the tcgen05 pipeline
-    covers = spec.left >= S - 1 and spec.right >= S - 1 and S >= 256
-    assert nat.last_kernel() == ("umma_dense" if covers else "mma_window")
+    # dense attention and windows of more than 64 taps run on the tcgen05 pipeline when the sequence is long enough
+    assert nat.last_kernel() == expected_window_kernel(spec, S)
     check_close(got, oracle_out(q, k, v, spec), dtype)
+
+
+@pytest.mark.parametrize("spec", [PatternSpec.sliding_window(65), PatternSpec.causal_window(130),
+                                  PatternSpec.causal_window(200), PatternSpec(left=40, right=90),
+                                  PatternSpec(left=300, right=17), PatternSpec.sliding_window(1000),
+                                  PatternSpec(left=0, right=129)], ids=lambda s: f"l{s.left}r{s.right}")
+@pytest.mark.parametrize("B,S,H", [(1, 1024, 2), (2, 1000, 3), (1, 4160, 2), (1, 257, 1)])
+def test_wide_windows_on_tcgen05(spec, B, S, H):
+    """Windows of more than 128 taps as a key range and an edge mask on the tcgen05 pipeline;
+    MAT_WINDOW_KERNEL=mma keeps them on the warp-level kernel."""
+    for dtype in (torch.bfloat16, torch.float16):
+        q, k, v = seeded_qkv(15, B, S, H, 64, dtype)
+        got = run(spec, q, k, v)
+        assert nat.last_kernel() == expected_window_kernel(spec, S) != "mma_window"
+        check_close(got, oracle_out(q, k, v, spec), dtype)
+
+
+def test_wide_window_with_halo_prefix_and_kernel_switch(monkeypatch):
+    """A sequence shard whose K/V carry 128 halo rows in front (q_offset = 128) on the tcgen05 window path,
+    and the same call forced onto the warp-level kernel."""
+    spec = PatternSpec(left=100, right=40).shifted(128)
+    q, k, v = seeded_qkv(16, 1, 512, 2, 64, torch.bfloat16, Skv=640)
+    want = oracle_out(q, k, v, spec)
+    got = run(spec, q, k, v)
+    assert nat.last_kernel() == "umma_window"
+    check_close(got, want, torch.bfloat16)
+    monkeypatch.setenv("MAT_WINDOW_KERNEL", "mma")
+    got = run(spec, q, k, v)
+    assert nat.last_kernel() == "mma_window"
+    check_close(got, want, torch.bfloat16)
 
 
 @pytest.mark.parametrize("causal", [False, True])
@@ -580,7 +609,7 @@ def test_random_windows_and_offsets_fuzz():
         spec = PatternSpec(left=left, right=right, dilation=dil).shifted(off)
         q, k, v = seeded_qkv(int(rng.integers(1 << 30)), 1, Sq, 2, 64, torch.bfloat16, Skv=Sq + off + tail)
         got = run(spec, q, k, v)
-        assert nat.last_kernel() == "mma_window", (left, right, dil, Sq, off, tail)
+        assert nat.last_kernel() == expected_window_kernel(spec, Sq + off + tail), (left, right, dil, Sq, off, tail)
         check_close(got, oracle_out(q, k, v, spec), torch.bfloat16)
 
 
