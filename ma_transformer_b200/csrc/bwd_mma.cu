@@ -29,6 +29,7 @@
 #include "ptx.cuh"
 
 #include <math.h>
+#include <mutex>
 #include <stdlib.h>
 #include <string.h>
 
@@ -49,6 +50,7 @@ struct BwdArgs {
     int64_t B, S, HH;         // sequence length and head count of the (possibly dilated) view
     int left, right;
     float scale;
+    int prefetch_ahead;       // resident-band kernels: L2-prefetch the tile this many CTAs ahead (0 = off)
 };
 
 __device__ __forceinline__ uint32_t swz(int row, int chunk) {
@@ -97,8 +99,8 @@ bwd_window_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     extern __shared__ __align__(1024) uint8_t smem[];
     using M = ptx::Mma<T>;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-    const int64_t r0 = (int64_t)blockIdx.x * kTile;
-    const int64_t h = blockIdx.y, b = blockIdx.z;
+    const int64_t r0 = (int64_t)blockIdx.y * kTile;   // heads vary fastest over the grid: neighbouring CTAs read neighbouring bytes
+    const int64_t h = blockIdx.x, b = blockIdx.z;
     const int W = a.left + a.right;
     const int back = COLS ? a.right : a.left;       // how far the band starts before the tile's first row
     const int64_t c0 = r0 - back;                   // global index of band row 0
@@ -129,6 +131,27 @@ bwd_window_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
         for (int i = 0; i < boxes; ++i) {
             ptx::tma_load_4d(smem + oY1 + i * 8192, y1, bar, 0, (int)h, (int)c0 + 64 * i, (int)b);
             ptx::tma_load_4d(smem + oY2 + i * 8192, y2, bar, 0, (int)h, (int)c0 + 64 * i, (int)b);
+        }
+    }
+    if (tid == 32 && a.prefetch_ahead > 0) {
+        // Pull the tile that will run in this CTA's slot a generation from now into L2 (same boxes as the real
+        // copies, nothing lands in shared memory), so that its own copies find their rows there.
+        const uint32_t gx = gridDim.x, gy = gridDim.y;
+        const uint32_t lin = (blockIdx.z * gy + blockIdx.y) * gx + blockIdx.x + (uint32_t)a.prefetch_ahead;
+        const int h2 = (int)(lin % gx), t2 = (int)((lin / gx) % gy), b2 = (int)(lin / (gx * gy));
+        if (b2 < (int)gridDim.z) {
+            const int64_t r2 = (int64_t)t2 * kTile, c2 = r2 - back;
+            if (r2 + kTile <= a.S) {
+                ptx::tma_prefetch_4d(x1, 0, h2, (int)r2, b2);
+                ptx::tma_prefetch_4d(x2, 0, h2, (int)r2, b2);
+            }
+            for (int i = 0; i < boxes; ++i) {
+                const int64_t cr = c2 + 64 * i;
+                if (cr >= 0 && cr + 64 <= a.S && (cr < r2 || cr >= r2 + kTile)) {   // the tile's own rows are on their way already
+                    ptx::tma_prefetch_4d(y1, 0, h2, (int)cr, b2);
+                    ptx::tma_prefetch_4d(y2, 0, h2, (int)cr, b2);
+                }
+            }
         }
     }
     if (COLS) {
@@ -451,7 +474,7 @@ int launch_bwd(const BwdArgs &a, int dtype, cudaStream_t stream) {
     if ((rc = make_row_tensor_map(&mk, a.k, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
     if ((rc = make_row_tensor_map(&mv, a.v, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
     if ((rc = make_row_tensor_map(&mgo, a.go, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
-    const dim3 grid((unsigned)((a.S + kTile - 1) / kTile), (unsigned)a.HH, (unsigned)a.B);
+    const dim3 grid((unsigned)a.HH, (unsigned)((a.S + kTile - 1) / kTile), (unsigned)a.B);
     bwd_window_mma_kernel<T, false, NP><<<grid, kThreads, smem_bytes(NP), stream>>>(mq, mk, mv, mgo, a);
     bwd_window_mma_kernel<T, true, NP><<<grid, kThreads, smem_bytes(NP), stream>>>(mq, mk, mv, mgo, a);
     cudaError_t e = cudaGetLastError();
@@ -476,8 +499,8 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     extern __shared__ __align__(1024) uint8_t smem[];
     using M = ptx::Mma<T>;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-    const int64_t r0 = (int64_t)blockIdx.x * kTile;
-    const int64_t h = blockIdx.y, b = blockIdx.z;
+    const int64_t r0 = (int64_t)blockIdx.y * kTile;   // heads vary fastest over the grid: neighbouring CTAs read neighbouring bytes
+    const int64_t h = blockIdx.x, b = blockIdx.z;
     const int64_t back = COLS ? a.right : a.left, fwd = COLS ? a.left : a.right;   // row r sees columns r - back .. r + fwd
     const unsigned W = (unsigned)(back + fwd);
     const int64_t stride = a.HH * 64;
@@ -726,7 +749,7 @@ int launch_bwd_stream(const BwdArgs &a, int dtype, cudaStream_t stream) {
     if ((rc = make_row_tensor_map(&mk, a.k, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
     if ((rc = make_row_tensor_map(&mv, a.v, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
     if ((rc = make_row_tensor_map(&mgo, a.go, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
-    const dim3 grid((unsigned)((a.S + kTile - 1) / kTile), (unsigned)a.HH, (unsigned)a.B);
+    const dim3 grid((unsigned)a.HH, (unsigned)((a.S + kTile - 1) / kTile), (unsigned)a.B);
     bwd_stream_mma_kernel<T, false><<<grid, kThreads, kStreamSmemBytes, stream>>>(mq, mk, mv, mgo, a);
     bwd_stream_mma_kernel<T, true><<<grid, kThreads, kStreamSmemBytes, stream>>>(mq, mk, mv, mgo, a);
     cudaError_t e = cudaGetLastError();
@@ -752,7 +775,7 @@ bool bwd_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int
     if (env && strcmp(env, "warp") == 0) return false;
     const int64_t Sv = S / dil;
     const int64_t l = left < Sv - 1 ? left : Sv - 1, r = right < Sv - 1 ? right : Sv - 1;
-    return H * dil <= 65535 && B <= 65535;
+    return H * dil < (1LL << 31) && (Sv + kTile - 1) / kTile <= 65535 && B <= 65535;
 }
 
 int launch_bwd_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk, void *dv,
@@ -768,6 +791,18 @@ int launch_bwd_mma(const void *q, const void *k, const void *v, const void *dout
     if (a.left < 0) a.left = 0;     // a one-row sequence
     if (a.right < 0) a.right = 0;
     a.scale = scale;
+    {   // prefetch distance: half of the CTAs resident on the GPU (4 per SM); MAT_BWD_PREFETCH_AHEAD overrides, 0 = off
+        static int dist = -1;
+        static std::once_flag once;
+        std::call_once(once, [] {
+            const char *env = getenv("MAT_BWD_PREFETCH_AHEAD");
+            if (env) { dist = atoi(env); return; }
+            int dev = 0, sms = 148;
+            if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            dist = 2 * sms;
+        });
+        a.prefetch_ahead = dist;
+    }
     if (a.left + a.right <= 64)
         return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16, 5>(a, dtype, stream) : launch_bwd<__half, 5>(a, dtype, stream);
     if (a.left + a.right <= 128)
