@@ -263,7 +263,10 @@ int mat_sparse_attn_bwd(const void *q, const void *k, const void *v, const void 
     a.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
     float2 *stats = (float2 *)workspace;
     cudaStream_t st = (cudaStream_t)stream;
-    if (bwd_mma_supports(B, S, H, D, dtype, a.left, a.right, a.dil))
+    // the tensor-core kernels move 16-byte vectors and TMA boxes: unaligned tensors stay on the warp-level kernels
+    const uintptr_t al = (uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)dout | (uintptr_t)dq | (uintptr_t)dk |
+                         (uintptr_t)dv;
+    if (al % 16 == 0 && bwd_mma_supports(B, S, H, D, dtype, a.left, a.right, a.dil))
         return launch_bwd_mma(q, k, v, dout, dq, dk, dv, stats, B, S, H, dtype, a.left, a.right, a.dil, a.scale, st);
     switch (dtype) {
         case MAT_F32: return launch_t<float>(q, k, v, dout, dq, dk, dv, stats, a, st);

@@ -538,6 +538,19 @@ def test_tensor_core_backward_matches_fp32_math_kernels(monkeypatch, dtype, B, S
         assert torch.equal(a, b)
 
 
+def test_backward_of_unaligned_tensors_stays_on_warp_kernels():
+    """Tensors that do not start on a 16-byte boundary cannot be moved by TMA: the call still works."""
+    flat = [torch.randn(1 * 128 * 2 * 64 + 4, generator=torch.Generator().manual_seed(95 + i)).to(torch.bfloat16).to(DEV)
+            for i in range(4)]
+    q, k, v, go = (f[4:].view(1, 128, 2, 64) for f in flat)          # 8 bytes past an aligned address
+    got = ext.backward_pattern(q, k, v, go, PatternSpec.causal_window(16))
+    assert nat.last_kernel() == "bwd_window"
+    want = ext.backward_pattern(q.clone(), k.clone(), v.clone(), go.clone(), PatternSpec.causal_window(16))
+    assert nat.last_kernel() == "bwd_window_mma"
+    for a, b in zip(got, want):
+        assert (a.float() - b.float()).abs().max() <= 2e-2 * max(1.0, float(b.float().abs().max()))
+
+
 def test_tensor_core_backward_against_fp64_autograd():
     """Same bar as the fp32 kernels' test, at the 16-bit tolerance: autograd in fp64 through the reference's
     python oracle (src/layers/ma_core_bridge.py:224-247) on the bf16-rounded inputs."""
