@@ -523,6 +523,8 @@ def other_workload_arm(args):
             "clocks": clocks, "kernel": nat.last_kernel(), "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": f"{peak_kind} HBM copy bandwidth", "bytes_per_launch_algorithmic": nbytes,
+                         # dram bytes of the two passes from the ncu capture in profiles/bwd_window_mma_cfg2_n64k.md
+                         "traffic": 322e6 + 375e6,
                          "note": "per backward (two launches: rows pass and cols pass)"},
             "device_status": nat.device_status()}), flush=True)
         return
