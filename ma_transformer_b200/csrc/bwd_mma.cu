@@ -486,11 +486,11 @@ int launch_bwd(const BwdArgs &a, int dtype, cudaStream_t stream) {
 // ---- any window wider than 128 taps, dense included: the band streamed through shared memory ----------------
 //
 // Same two passes, same roles, but the band no longer fits in shared memory: it is walked in 64-column chunks
-// aligned to the sequence (one TMA box of each band operand per chunk, single-buffered; the other resident CTAs
-// cover the wait).  The rows pass walks it twice, once for the row statistics with a running maximum and once for
+// aligned to the sequence (one TMA box of each band operand per chunk, two stages: a chunk's copies are issued
+// while the previous chunk is being computed).  The rows pass walks it twice, once for the row statistics with a running maximum and once for
 // dQ; the cols pass walks it once.  A warp skips the 16-column groups none of its rows can see and masks only
 // the groups that straddle an edge of the window or the end of the sequence.
-constexpr int kStreamSmemBytes = 4 * 8192 + 64 * (int)sizeof(float2) + 16;
+constexpr int kStreamSmemBytes = 2 * 8192 + 2 * 16384 + 2 * 64 * (int)sizeof(float2) + 16;
 
 template <typename T, bool COLS>
 __global__ void __launch_bounds__(kThreads, COLS ? 3 : 4)
@@ -499,7 +499,7 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     extern __shared__ __align__(1024) uint8_t smem[];
     using M = ptx::Mma<T>;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-    const int64_t r0 = (int64_t)blockIdx.y * kTile;   // heads vary fastest over the grid: neighbouring CTAs read neighbouring bytes
+    const int64_t r0 = (int64_t)blockIdx.y * kTile;   // heads vary fastest over the grid
     const int64_t h = blockIdx.x, b = blockIdx.z;
     const int64_t back = COLS ? a.right : a.left, fwd = COLS ? a.left : a.right;   // row r sees columns r - back .. r + fwd
     const unsigned W = (unsigned)(back + fwd);
@@ -507,54 +507,50 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     const int64_t head_off = (b * a.S * a.HH + h) * 64;
     const CUtensorMap *x1 = COLS ? &mk : &mq, *x2 = COLS ? &mv : &mgo;
     const CUtensorMap *y1 = COLS ? &mq : &mk, *y2 = COLS ? &mgo : &mv;
-    constexpr uint32_t oX1 = 0, oX2 = 8192, oY1 = 16384, oY2 = 24576, oSt = 32768, oBar = oSt + 512;
+    // tile rows | two stages of (band operand 1, band operand 2) | two stages of statistics | two barriers
+    constexpr uint32_t oX1 = 0, oX2 = 8192, oY = 16384, oSt = oY + 2 * 16384, oBar = oSt + 2 * 512;
     const uint32_t sbase = ptx::smem_u32(smem);
-    float2 *sst = (float2 *)(smem + oSt);
     uint64_t *bar = (uint64_t *)(smem + oBar);
     const int64_t lo = r0 - back > 0 ? r0 - back : 0;
     const int64_t hi = r0 + 63 + fwd < a.S - 1 ? r0 + 63 + fwd : a.S - 1;
-    const int64_t k_first = lo / 64, k_last = hi / 64;
-    const int64_t wrow = r0 + 16 * warp;     // the warp's first row
-    uint32_t phase = 0;
+    const int64_t k_first = lo / 64;
+    const int nch = (int)(hi / 64 - k_first) + 1;        // chunks per walk of the band
+    const int total = COLS ? nch : 2 * nch;              // the rows pass walks it twice
+    const int64_t wrow = r0 + 16 * warp;                 // the warp's first row
 
     if (tid == 0) {
         ptx::mbar_init(bar, 1);
+        ptx::mbar_init(bar + 1, 1);
         ptx::fence_barrier_init();
     }
-    // chunk k of the band operands (and the tile's own rows with the first one) into shared memory
-    auto load_chunk = [&](int64_t k, bool with_tile) -> bool {
-        __syncthreads();   // the previous chunk's readers are done (and the barrier is initialised)
+    __syncthreads();
+    // Step n of the flat walk (chunk k_first + n % nch) goes to stage n & 1.  It is issued while step n - 1 is
+    // being computed, after the barrier that says every warp has left step n - 2, the stage's previous tenant.
+    auto issue = [&](int n) {
+        const int64_t k = k_first + n % nch;
+        const int st = n & 1;
         if (tid == 0) {
-            ptx::mbar_expect_tx(bar, with_tile ? 32768u : 16384u);
-            if (with_tile) {
+            ptx::mbar_expect_tx(bar + st, n == 0 ? 32768u : 16384u);
+            if (n == 0) {
                 ptx::tma_load_4d(smem + oX1, x1, bar, 0, (int)h, (int)r0, (int)b);
                 ptx::tma_load_4d(smem + oX2, x2, bar, 0, (int)h, (int)r0, (int)b);
             }
-            ptx::tma_load_4d(smem + oY1, y1, bar, 0, (int)h, (int)(64 * k), (int)b);
-            ptx::tma_load_4d(smem + oY2, y2, bar, 0, (int)h, (int)(64 * k), (int)b);
+            ptx::tma_load_4d(smem + oY + st * 16384, y1, bar + st, 0, (int)h, (int)(64 * k), (int)b);
+            ptx::tma_load_4d(smem + oY + st * 16384 + 8192, y2, bar + st, 0, (int)h, (int)(64 * k), (int)b);
         }
         if (COLS && tid < 64) {
             const int64_t gi = 64 * k + tid;
-            sst[tid] = gi < a.S ? a.stats[(b * a.HH + h) * a.S + gi] : make_float2(0.f, 0.f);
+            ((float2 *)(smem + oSt + st * 512))[tid] =
+                gi < a.S ? a.stats[(b * a.HH + h) * a.S + gi] : make_float2(0.f, 0.f);
         }
-        const bool ok = ptx::mbar_wait(bar, phase);
-        phase ^= 1;
-        if (COLS) __syncthreads();   // the statistics of this chunk are visible
-        return ok;
     };
+    issue(0);
+
     const int mi = lane >> 3, rr = lane & 7;
     const int brow_n = (mi >> 1) * 8 + rr, bchk_n = mi & 1;   // + 16p / + 2ks: plain B fragments
     const int brow_t = (mi & 1) * 8 + rr, bchk_t = mi >> 1;   // + 16p / + 2dn: transposed B fragments
     const float sl = a.scale * 1.4426950408889634f;
     uint32_t a1[4][4], a2[4][4];
-    auto load_a = [&]() {
-        const int row = 16 * warp + (lane & 15), cadd = lane >> 4;
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            ptx::ldmatrix_x4(a1[ks], sbase + oX1 + swz(row, 2 * ks + cadd));
-            ptx::ldmatrix_x4(a2[ks], sbase + oX2 + swz(row, 2 * ks + cadd));
-        }
-    };
     // group p of chunk k: 0 = none of the warp's rows sees it, 1 = every (row, column) pair is seen, 2 = mask it
     auto group_kind = [&](int64_t k, int p) -> int {
         const int64_t c = 64 * k + 16 * p;      // the group's first column
@@ -567,7 +563,7 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
         const int d = (int)(c - wrow) + cc - r;
         return (unsigned)(d + (int)back) <= W && c + cc < a.S;
     };
-    auto group_products = [&](int p, float (&s)[2][4], float (&dp)[2][4]) {
+    auto group_products = [&](uint32_t y, int p, float (&s)[2][4], float (&dp)[2][4]) {
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -575,134 +571,129 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
             uint32_t bf[4];
-            ptx::ldmatrix_x4(bf, sbase + oY1 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
+            ptx::ldmatrix_x4(bf, y + swz(brow_n + 16 * p, 2 * ks + bchk_n));
             M::run(s[0], a1[ks], bf[0], bf[1]);
             M::run(s[1], a1[ks], bf[2], bf[3]);
-            ptx::ldmatrix_x4(bf, sbase + oY2 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
+            ptx::ldmatrix_x4(bf, y + 8192 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
             M::run(dp[0], a2[ks], bf[0], bf[1]);
             M::run(dp[1], a2[ks], bf[2], bf[3]);
         }
     };
 
-    if constexpr (!COLS) {
-        float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f}, dr[2] = {0.f, 0.f};
-        for (int64_t k = k_first; k <= k_last; ++k) {
-            if (!load_chunk(k, k == k_first)) {
-                atomicExch(&g_bwd_status, 1);
-                return;
+    // rows pass: running statistics of sweep one, then what sweep two needs; cols pass: the two outputs
+    float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f}, dr[2] = {0.f, 0.f}, lse[2] = {0.f, 0.f}, dsc[2] = {0.f, 0.f};
+    float o[8][4], ov[COLS ? 8 : 1][4];   // rows: dQ; cols: dK in o, dV in ov
+#pragma unroll
+    for (int dt = 0; dt < 8; ++dt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            o[dt][e] = 0.f;
+            if (COLS) ov[dt][e] = 0.f;
+        }
+
+    for (int n = 0; n < total; ++n) {
+        __syncthreads();   // every warp has left step n - 1; the statistics written for step n are visible
+        if (n + 1 < total) issue(n + 1);
+        if (!ptx::mbar_wait(bar + (n & 1), (n >> 1) & 1)) {
+            atomicExch(&g_bwd_status, 1);
+            return;
+        }
+        if (n == 0) {
+            const int row = 16 * warp + (lane & 15), cadd = lane >> 4;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                ptx::ldmatrix_x4(a1[ks], sbase + oX1 + swz(row, 2 * ks + cadd));
+                ptx::ldmatrix_x4(a2[ks], sbase + oX2 + swz(row, 2 * ks + cadd));
             }
-            if (k == k_first) load_a();
+        }
+        const int64_t k = k_first + n % nch;
+        const uint32_t y = sbase + oY + (n & 1) * 16384;
+        if constexpr (!COLS) {
+            if (n == nch) {   // between the sweeps: the statistics are complete
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    sum[hh] = quad_sum(sum[hh]);
+                    dr[hh] = quad_sum(dr[hh]);            // every lane takes part in the shuffles, live row or not
+                    const bool live = sum[hh] > 0.f;
+                    lse[hh] = live ? mx[hh] * sl + log2f(sum[hh]) : 0.f;
+                    dsc[hh] = live ? dr[hh] / sum[hh] * a.scale : 0.f;
+                }
+                if (t == 0) {
+                    float2 *st = a.stats + (b * a.HH + h) * a.S;
+#pragma unroll
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const int64_t gr = wrow + g + 8 * hh;
+                        if (gr < a.S) st[gr] = make_float2(lse[hh], dsc[hh]);
+                    }
+                }
+            }
 #pragma unroll 1
             for (int p = 0; p < 4; ++p) {
                 const int kind = group_kind(k, p);
                 if (kind == 0) continue;
                 float s[2][4], dp[2][4];
-                group_products(p, s, dp);
-                if (kind == 2) {
+                group_products(y, p, s, dp);
+                if (n < nch) {
+                    if (kind == 2) {
+#pragma unroll
+                        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                if (!seen(k, p, 8 * nt + 2 * t + (e & 1), g + (e >> 1) * 8)) s[nt][e] = -INFINITY;
+                    }
+                    float gm[2] = {-INFINITY, -INFINITY}, msl[2];
 #pragma unroll
                     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            if (!seen(k, p, 8 * nt + 2 * t + (e & 1), g + (e >> 1) * 8)) s[nt][e] = -INFINITY;
-                }
-                float gm[2] = {-INFINITY, -INFINITY}, msl[2];
+                        for (int e = 0; e < 4; ++e) gm[e >> 1] = fmaxf(gm[e >> 1], s[nt][e]);
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) gm[e >> 1] = fmaxf(gm[e >> 1], s[nt][e]);
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const float m_new = fmaxf(mx[hh], quad_max(gm[hh]));
-                    const float alpha = mx[hh] == -INFINITY ? 0.f : ptx::ex2((mx[hh] - m_new) * sl);
-                    sum[hh] *= alpha;
-                    dr[hh] *= alpha;
-                    mx[hh] = m_new;
-                    msl[hh] = m_new == -INFINITY ? 0.f : m_new * sl;
-                }
-#pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float ex = ptx::ex2(fmaf(s[nt][e], sl, -msl[e >> 1]));
-                        sum[e >> 1] += ex;
-                        dr[e >> 1] = fmaf(ex, dp[nt][e], dr[e >> 1]);
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const float m_new = fmaxf(mx[hh], quad_max(gm[hh]));
+                        const float alpha = mx[hh] == -INFINITY ? 0.f : ptx::ex2((mx[hh] - m_new) * sl);
+                        sum[hh] *= alpha;
+                        dr[hh] *= alpha;
+                        mx[hh] = m_new;
+                        msl[hh] = m_new == -INFINITY ? 0.f : m_new * sl;
                     }
-            }
-        }
-        float lse[2], dsc[2];
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-            sum[hh] = quad_sum(sum[hh]);
-            dr[hh] = quad_sum(dr[hh]);            // every lane takes part in the shuffles, live row or not
-            const bool live = sum[hh] > 0.f;
-            lse[hh] = live ? mx[hh] * sl + log2f(sum[hh]) : 0.f;
-            dsc[hh] = live ? dr[hh] / sum[hh] * a.scale : 0.f;
-        }
-        if (t == 0) {
-            float2 *st = a.stats + (b * a.HH + h) * a.S;
+                    for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const int64_t gr = wrow + g + 8 * hh;
-                if (gr < a.S) st[gr] = make_float2(lse[hh], dsc[hh]);
-            }
-        }
-        float o[8][4];
+                        for (int e = 0; e < 4; ++e) {
+                            const float ex = ptx::ex2(fmaf(s[nt][e], sl, -msl[e >> 1]));
+                            sum[e >> 1] += ex;
+                            dr[e >> 1] = fmaf(ex, dp[nt][e], dr[e >> 1]);
+                        }
+                } else {
+                    uint32_t af[4];
 #pragma unroll
-        for (int dt = 0; dt < 8; ++dt)
+                    for (int nt = 0; nt < 2; ++nt) {
+                        float ds[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) o[dt][e] = 0.f;
-        for (int64_t k = k_first; k <= k_last; ++k) {
-            if (!load_chunk(k, false)) {
-                atomicExch(&g_bwd_status, 1);
-                return;
-            }
-#pragma unroll 1
-            for (int p = 0; p < 4; ++p) {
-                const int kind = group_kind(k, p);
-                if (kind == 0) continue;
-                float s[2][4], dp[2][4];
-                group_products(p, s, dp);
-                uint32_t af[4];
-#pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
-                    float ds[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        float pp = ptx::ex2(fmaf(s[nt][e], sl, -lse[e >> 1]));
-                        if (kind == 2 && !seen(k, p, 8 * nt + 2 * t + (e & 1), g + (e >> 1) * 8)) pp = 0.f;
-                        ds[e] = pp * fmaf(dp[nt][e], a.scale, -dsc[e >> 1]);
+                        for (int e = 0; e < 4; ++e) {
+                            float pp = ptx::ex2(fmaf(s[nt][e], sl, -lse[e >> 1]));
+                            if (kind == 2 && !seen(k, p, 8 * nt + 2 * t + (e & 1), g + (e >> 1) * 8)) pp = 0.f;
+                            ds[e] = pp * fmaf(dp[nt][e], a.scale, -dsc[e >> 1]);
+                        }
+                        af[2 * nt] = M::pack(ds[0], ds[1]);
+                        af[2 * nt + 1] = M::pack(ds[2], ds[3]);
                     }
-                    af[2 * nt] = M::pack(ds[0], ds[1]);
-                    af[2 * nt + 1] = M::pack(ds[2], ds[3]);
-                }
 #pragma unroll
-                for (int dn = 0; dn < 4; ++dn) {
-                    uint32_t bf[4];
-                    ptx::ldmatrix_x4_trans(bf, sbase + oY1 + swz(brow_t + 16 * p, 2 * dn + bchk_t));
-                    M::run(o[2 * dn], af, bf[0], bf[1]);
-                    M::run(o[2 * dn + 1], af, bf[2], bf[3]);
+                    for (int dn = 0; dn < 4; ++dn) {
+                        uint32_t bf[4];
+                        ptx::ldmatrix_x4_trans(bf, y + swz(brow_t + 16 * p, 2 * dn + bchk_t));
+                        M::run(o[2 * dn], af, bf[0], bf[1]);
+                        M::run(o[2 * dn + 1], af, bf[2], bf[3]);
+                    }
                 }
             }
-        }
-        store_tile<T>(smem, oX1, o, (T *)a.dq + head_off, r0, a.S, stride, warp, lane);
-    } else {
-        float ok_[8][4], ov[8][4];
-#pragma unroll
-        for (int dt = 0; dt < 8; ++dt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) ok_[dt][e] = ov[dt][e] = 0.f;
-        for (int64_t k = k_first; k <= k_last; ++k) {
-            if (!load_chunk(k, k == k_first)) {
-                atomicExch(&g_bwd_status, 1);
-                return;
-            }
-            if (k == k_first) load_a();
+        } else {
+            const float2 *sst = (const float2 *)(smem + oSt + (n & 1) * 512);
 #pragma unroll 1
             for (int p = 0; p < 4; ++p) {
                 const int kind = group_kind(k, p);
                 if (kind == 0) continue;
                 float st[2][4], dpt[2][4];
-                group_products(p, st, dpt);
+                group_products(y, p, st, dpt);
                 uint32_t ap[4], as[4];
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
@@ -710,8 +701,8 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
                     const float4 sd = *(const float4 *)&sst[16 * p + cb];   // (lse, delta scale) of two queries
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float lse = (e & 1) ? sd.z : sd.x, dl = (e & 1) ? sd.w : sd.y;
-                        float pp = ptx::ex2(fmaf(st[nt][e], sl, -lse));
+                        const float ls = (e & 1) ? sd.z : sd.x, dl = (e & 1) ? sd.w : sd.y;
+                        float pp = ptx::ex2(fmaf(st[nt][e], sl, -ls));
                         if (kind == 2 && !seen(k, p, cb + (e & 1), g + (e >> 1) * 8)) pp = 0.f;
                         st[nt][e] = pp;
                         dpt[nt][e] = pp * fmaf(dpt[nt][e], a.scale, -dl);
@@ -724,16 +715,20 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
 #pragma unroll
                 for (int dn = 0; dn < 4; ++dn) {
                     uint32_t bf[4];
-                    ptx::ldmatrix_x4_trans(bf, sbase + oY2 + swz(brow_t + 16 * p, 2 * dn + bchk_t));
+                    ptx::ldmatrix_x4_trans(bf, y + 8192 + swz(brow_t + 16 * p, 2 * dn + bchk_t));
                     M::run(ov[2 * dn], ap, bf[0], bf[1]);
                     M::run(ov[2 * dn + 1], ap, bf[2], bf[3]);
-                    ptx::ldmatrix_x4_trans(bf, sbase + oY1 + swz(brow_t + 16 * p, 2 * dn + bchk_t));
-                    M::run(ok_[2 * dn], as, bf[0], bf[1]);
-                    M::run(ok_[2 * dn + 1], as, bf[2], bf[3]);
+                    ptx::ldmatrix_x4_trans(bf, y + swz(brow_t + 16 * p, 2 * dn + bchk_t));
+                    M::run(o[2 * dn], as, bf[0], bf[1]);
+                    M::run(o[2 * dn + 1], as, bf[2], bf[3]);
                 }
             }
         }
-        store_tile<T>(smem, oX1, ok_, (T *)a.dk + head_off, r0, a.S, stride, warp, lane);
+    }
+    if constexpr (!COLS) {
+        store_tile<T>(smem, oX1, o, (T *)a.dq + head_off, r0, a.S, stride, warp, lane);
+    } else {
+        store_tile<T>(smem, oX1, o, (T *)a.dk + head_off, r0, a.S, stride, warp, lane);
         store_tile<T>(smem, oX2, ov, (T *)a.dv + head_off, r0, a.S, stride, warp, lane);
     }
 }
