@@ -730,9 +730,12 @@ int launch_t(const Problem &p) {
             return launch_kind<T, MAT_WINDOW, TQ, TQ + 64, 3, 1, true, 5>(p, fp, dil, "mma_window");
         if (fp.left + slack + fp.right <= 64 && pairs <= 5)
             return launch_kind<T, MAT_WINDOW, TQ, TQ + 64, 5, 1, true, 5>(p, fp, dil, "mma_window");
-        // up to 128 keys of reach (the reference's default window of +-64): 128-row tiles whose
-        // 256-key window is still one stage, two softmax steps per warp, no producer warp
-        // (102 us against 125 us on the ring path at the 64K-token shape)
+        // up to 128 keys of reach (the reference's default window of +-64): still one softmax step per
+        // warp over nine pairs of a 192-key stage (86 us at the 64K-token shape, 156 registers, 3 CTAs/SM)
+        if (fp.left + slack + fp.right <= 128 && pairs <= 9)
+            return launch_kind<T, MAT_WINDOW, TQ, TQ + 128, 9, 1, true, 3>(p, fp, dil, "mma_window");
+        // the same reach on a shard offset that costs a tenth pair: 128-row tiles whose 256-key window
+        // is one stage, two softmax steps per warp, no producer warp (102 us; 125 us on the ring path)
         if (fp.left + slack + fp.right <= 128 && (p.Sq / dil + 127) / 128 <= 65535)
             return launch_kind<T, MAT_WINDOW, 128, 256, 5, 1, false, 2>(p, fp, dil, "mma_window");
         return launch_kind<T, MAT_WINDOW, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_window");

@@ -808,7 +808,7 @@ bool umma_dense_supports(const Problem &p) {
     const int64_t left = std::min<int64_t>(p.pat.left, p.Skv - 1), right = std::min<int64_t>(p.pat.right, p.Skv - 1);
     const bool dense = left >= p.Skv - 1 && (right >= p.Skv - 1 || right == 0);
     if (!dense) {
-        if (left + right <= 128) return false;   // measured: the warp-level tiles win up to 128 taps (102 against 117 us at 64K x 8)
+        if (left + right <= 128) return false;   // measured: the warp-level tiles win up to 128 taps (86 against 117 us at 64K x 8)
         const char *force = std::getenv("MAT_WINDOW_KERNEL");
         if (force && std::strcmp(force, "mma") == 0) return false;
     }
