@@ -17,8 +17,8 @@
 //       P^T from the stored statistics, dV = P^T dO, dK = dS^T Q.
 //
 // Both passes share the structure "16 rows per warp against a band of at most 80 columns"
-// (144 for windows of more than 64 taps, where the rows pass sweeps the band twice instead of
-// holding it in registers):
+// (144 for windows of more than 64 taps, where the rows pass keeps only the scores in registers
+// and recomputes dP):
 // one thread stages the tile's rows and the band by TMA (64-row boxes, 128-byte swizzle, zeros
 // outside the sequence; the wait for them is bounded), the row operands are A fragments held in
 // registers, the band operands stay in shared memory (every ldmatrix conflict-free) and feed mma.sync.m16n8k16 as B fragments, plain for the score-shaped
@@ -195,14 +195,21 @@ bwd_window_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     };
     auto group_masked = [&](int p) -> bool { return clipped || p == 0 || 16 * p + 15 > W; };
 
-    if constexpr (!COLS && NP <= 5) {
-        float s[kPairs][2][4], dp[kPairs][2][4];
+    if constexpr (!COLS) {
+        // The scores of the whole band stay in registers.  dP stays too when the band is narrow (NP <= 5);
+        // a wide band recomputes it, once for delta and once for dS, which is cheaper than a second sweep
+        // over both products.
+        constexpr bool KEEP_DP = NP <= 5;
+        float s[kPairs][2][4], dp[KEEP_DP ? kPairs : 1][2][4];
 #pragma unroll
         for (int p = 0; p < kPairs; ++p)
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) s[p][nt][e] = dp[p][nt][e] = 0.f;
+                for (int e = 0; e < 4; ++e) {
+                    s[p][nt][e] = 0.f;
+                    if (KEEP_DP) dp[KEEP_DP ? p : 0][nt][e] = 0.f;
+                }
 #pragma unroll
         for (int p = 0; p < kPairs; ++p) {
             if (p < np) {
@@ -212,12 +219,27 @@ bwd_window_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
                     ptx::ldmatrix_x4(bf, sbase + oY1 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
                     M::run(s[p][0], a1[ks], bf[0], bf[1]);
                     M::run(s[p][1], a1[ks], bf[2], bf[3]);
-                    ptx::ldmatrix_x4(bf, sbase + oY2 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
-                    M::run(dp[p][0], a2[ks], bf[0], bf[1]);
-                    M::run(dp[p][1], a2[ks], bf[2], bf[3]);
+                    if (KEEP_DP) {
+                        ptx::ldmatrix_x4(bf, sbase + oY2 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
+                        M::run(dp[KEEP_DP ? p : 0][0], a2[ks], bf[0], bf[1]);
+                        M::run(dp[KEEP_DP ? p : 0][1], a2[ks], bf[2], bf[3]);
+                    }
                 }
             }
         }
+        auto dp_group = [&](int p, float (&d)[2][4]) {   // dP of one group, for bands whose dP is not kept
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) d[nt][e] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                uint32_t bf[4];
+                ptx::ldmatrix_x4(bf, sbase + oY2 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
+                M::run(d[0], a2[ks], bf[0], bf[1]);
+                M::run(d[1], a2[ks], bf[2], bf[3]);
+            }
+        };
         // softmax statistics of rows g and g + 8 (maximum of the raw scores: the scale is positive)
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -247,6 +269,8 @@ bwd_window_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
 #pragma unroll
         for (int p = 0; p < kPairs; ++p) {
             if (p < np) {
+                float dl[2][4];
+                if (!KEEP_DP) dp_group(p, dl);
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -254,7 +278,7 @@ bwd_window_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
                         const float ex = ptx::ex2(fmaf(s[p][nt][e], sl, -msl[e >> 1]));
                         s[p][nt][e] = ex;
                         sum[e >> 1] += ex;
-                        delta[e >> 1] = fmaf(ex, dp[p][nt][e], delta[e >> 1]);
+                        delta[e >> 1] = fmaf(ex, KEEP_DP ? dp[KEEP_DP ? p : 0][nt][e] : dl[nt][e], delta[e >> 1]);
                     }
             }
         }
@@ -285,11 +309,14 @@ bwd_window_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
         for (int p = 0; p < kPairs; ++p) {
             if (p < np) {
                 uint32_t af[4];
+                float dl[2][4];
+                if (!KEEP_DP) dp_group(p, dl);
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
                     float ds[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) ds[e] = s[p][nt][e] * fmaf(dp[p][nt][e], cs[e >> 1], -dcs[e >> 1]);
+                    for (int e = 0; e < 4; ++e)
+                        ds[e] = s[p][nt][e] * fmaf(KEEP_DP ? dp[KEEP_DP ? p : 0][nt][e] : dl[nt][e], cs[e >> 1], -dcs[e >> 1]);
                     af[2 * nt] = M::pack(ds[0], ds[1]);
                     af[2 * nt + 1] = M::pack(ds[2], ds[3]);
                 }
@@ -300,106 +327,6 @@ bwd_window_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
                     M::run(o[2 * dn], af, bf[0], bf[1]);
                     M::run(o[2 * dn + 1], af, bf[2], bf[3]);
                 }
-            }
-        }
-        store_tile<T>(smem, oX1, o, (T *)a.dq + head_off, r0, a.S, stride, warp, lane);
-    } else if constexpr (!COLS) {
-        // Wide bands do not fit in registers: one sweep for the row statistics with a running maximum
-        // (sum of e and of e dP rescaled together), a second sweep that recomputes S and dP group by
-        // group and feeds dS straight into the dQ products.
-        auto group_products = [&](int p, float (&s)[2][4], float (&dp)[2][4]) {
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) s[nt][e] = dp[nt][e] = 0.f;
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-                uint32_t bf[4];
-                ptx::ldmatrix_x4(bf, sbase + oY1 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
-                M::run(s[0], a1[ks], bf[0], bf[1]);
-                M::run(s[1], a1[ks], bf[2], bf[3]);
-                ptx::ldmatrix_x4(bf, sbase + oY2 + swz(brow_n + 16 * p, 2 * ks + bchk_n));
-                M::run(dp[0], a2[ks], bf[0], bf[1]);
-                M::run(dp[1], a2[ks], bf[2], bf[3]);
-            }
-            if (group_masked(p)) {
-#pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        if (!seen(16 * p + 8 * nt + 2 * t + (e & 1), g + (e >> 1) * 8)) s[nt][e] = -INFINITY;
-            }
-        };
-        float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f}, dr[2] = {0.f, 0.f};
-#pragma unroll 1
-        for (int p = 0; p < np; ++p) {
-            float s[2][4], dp[2][4];
-            group_products(p, s, dp);
-            float gm[2] = {-INFINITY, -INFINITY}, msl[2];
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) gm[e >> 1] = fmaxf(gm[e >> 1], s[nt][e]);
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const float m_new = fmaxf(mx[hh], quad_max(gm[hh]));
-                const float alpha = mx[hh] == -INFINITY ? 0.f : ptx::ex2((mx[hh] - m_new) * sl);
-                sum[hh] *= alpha;
-                dr[hh] *= alpha;
-                mx[hh] = m_new;
-                msl[hh] = m_new == -INFINITY ? 0.f : m_new * sl;
-            }
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float ex = ptx::ex2(fmaf(s[nt][e], sl, -msl[e >> 1]));
-                    sum[e >> 1] += ex;
-                    dr[e >> 1] = fmaf(ex, dp[nt][e], dr[e >> 1]);
-                }
-        }
-        float lse[2], dsc[2];   // log2-sum-exp of the scaled scores, delta scale
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-            sum[hh] = quad_sum(sum[hh]);
-            dr[hh] = quad_sum(dr[hh]);            // every lane takes part in the shuffles, live row or not
-            const bool live = sum[hh] > 0.f;      // false only for rows past the end of the sequence
-            lse[hh] = live ? mx[hh] * sl + log2f(sum[hh]) : 0.f;
-            dsc[hh] = live ? dr[hh] / sum[hh] * a.scale : 0.f;
-        }
-        if (t == 0) {
-            float2 *st = a.stats + (b * a.HH + h) * a.S;
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const int64_t gr = r0 + 16 * warp + g + 8 * hh;
-                if (gr < a.S) st[gr] = make_float2(lse[hh], dsc[hh]);
-            }
-        }
-        float o[8][4];
-#pragma unroll
-        for (int dt = 0; dt < 8; ++dt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) o[dt][e] = 0.f;
-#pragma unroll 1
-        for (int p = 0; p < np; ++p) {
-            float s[2][4], dp[2][4];
-            group_products(p, s, dp);
-            uint32_t af[4];
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                float ds[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    ds[e] = ptx::ex2(fmaf(s[nt][e], sl, -lse[e >> 1])) * fmaf(dp[nt][e], a.scale, -dsc[e >> 1]);
-                af[2 * nt] = M::pack(ds[0], ds[1]);
-                af[2 * nt + 1] = M::pack(ds[2], ds[3]);
-            }
-#pragma unroll
-            for (int dn = 0; dn < 4; ++dn) {
-                uint32_t bf[4];
-                ptx::ldmatrix_x4_trans(bf, sbase + oY1 + swz(brow_t + 16 * p, 2 * dn + bchk_t));
-                M::run(o[2 * dn], af, bf[0], bf[1]);
-                M::run(o[2 * dn + 1], af, bf[2], bf[3]);
             }
         }
         store_tile<T>(smem, oX1, o, (T *)a.dq + head_off, r0, a.S, stride, warp, lane);
