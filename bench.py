@@ -42,7 +42,7 @@ WORKLOAD = f"causal sliding-window fwd B={B} N={SEQ} H={H} d={D} taps={TAPS} bf1
 BYTES_PER_TOKEN = 4 * H * D * 2          # read Q,K,V + write O, bf16
 METRIC = "sparse-attn fwd tokens/s @N=64K,w=64,bf16"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the window kernel on this
-# workload, from the ncu capture summarised in profiles/mma_window_cfg2_n64k.md, per token
+# workload, from an ncu capture of that launch, per token
 NCU_TRAFFIC_PER_TOKEN = (201.354e6 + 49.839e6) / 65536
 
 
@@ -386,6 +386,29 @@ def gpu_arm(args):
     value = B * SEQ / (ms_per_step * 1e-3)
     status = nat.device_status()
 
+    # ---- after the timed region: this rank's first and last 128 output rows (the first ones need the
+    # previous shard's halo rows) of one more forward over input set 0 against the CPU oracle ----
+    import numpy as np
+    from oracle import oracle as O
+    step(0, out)
+    torch.cuda.synchronize()
+    worst = 0.0
+    for lo_row in (a, (a + b) // 2, b - 128):
+        k_lo = max(0, lo_row - (TAPS - 1))
+        pat = O.OraclePattern.causal_taps(TAPS)
+        pat.q_offset = lo_row - k_lo
+        want = O.sparse_attention(q_cpu[:, lo_row:lo_row + 128].float().numpy(), k_cpu[:, k_lo:lo_row + 128].float().numpy(),
+                                  v_cpu[:, k_lo:lo_row + 128].float().numpy(), pat)
+        got = out[:, lo_row - a:lo_row - a + 128].float().cpu().numpy()
+        worst = max(worst, float(np.abs(got - want).max()))
+    worst_t = torch.tensor([worst], device=dev)
+    if world > 1:
+        dist.all_reduce(worst_t, op=dist.ReduceOp.MAX)
+    worst = float(worst_t.item())
+    if not worst <= 2e-2:
+        raise SystemExit(f"parity check after the timed region failed: max-abs {worst} > 2e-2")
+    parity = {"rows_checked": 3 * 128 * world, "max_abs_vs_oracle": worst, "tolerance": 2e-2, "ok": True}
+
     # ---- end to end: pinned host tensors in, host tensor out, per rank its chunk plus halo ----
     if args.no_e2e:   # profiling runs: the device-resident leg only
         if rank == 0:
@@ -429,13 +452,37 @@ def gpu_arm(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC_PER_TOKEN * rows, "peak_source": f"{peak_kind} HBM copy bandwidth",
                          "kernel": nat.last_kernel(), "bytes_per_launch_algorithmic": per_rank_bytes},
-            "device_status": status,
+            "parity_check": parity, "device_status": status,
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_port()
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def sampled_parity(out, q, k, v, spec, starts, rows=128, tol=2e-2):
+    """After the timed region: a few blocks of output rows of the LAST timed launch against the CPU oracle
+    (the checker, never the thing measured).  q, k, v, out: device tensors [B, S, H, 64]; each block of
+    ``rows`` query rows runs against the whole key axis of its batch item, so window, block layout, global
+    keys and rows at global positions are all covered.  Raises if a block is off by more than ``tol``."""
+    import numpy as np
+    from oracle import oracle as O
+    kinds = {0: O.WINDOW, 1: O.BLOCK, 2: O.LONGFORMER}
+    worst, n = 0.0, 0
+    for b, a in starts:
+        a = max(0, min(a, q.shape[1] - rows))
+        pat = O.OraclePattern(kind=kinds[spec.kind], left=spec.left, right=spec.right, dilation=spec.dilation,
+                              causal=spec.causal, block=spec.block, blk_rowptr=spec.blk_rowptr,
+                              blk_colidx=spec.blk_colidx, global_idx=spec.global_idx, q_offset=a)
+        want = O.sparse_attention(q[b:b + 1, a:a + rows].float().cpu().numpy(), k[b:b + 1].float().cpu().numpy(),
+                                  v[b:b + 1].float().cpu().numpy(), pat)
+        got = out[b:b + 1, a:a + rows].float().cpu().numpy()
+        worst = max(worst, float(np.abs(got - want).max()))
+        n += rows
+    if not worst <= tol:
+        raise SystemExit(f"parity check after the timed region failed: max-abs {worst} > {tol}")
+    return {"rows_checked": n, "max_abs_vs_oracle": worst, "tolerance": tol, "ok": True}
 
 
 def other_workload_arm(args):
@@ -477,6 +524,8 @@ def other_workload_arm(args):
         with torch.no_grad():
             ms_model = timed(lambda: model(ticks), args.steps)
             ms_attn = timed(lambda: ext.forward_pattern(*qkv, model.pattern, out=out), args.steps)
+        torch.cuda.synchronize()
+        parity = sampled_parity(out, *qkv, model.pattern, [(0, 0), (Bw - 1, S - 128), (Bw // 2, S // 2 - 64)])
         peak, peak_kind = measured_peak_gbs()
         attn_bytes = 4 * Bw * S * 4 * 64 * 2
         print(json.dumps({
@@ -489,7 +538,7 @@ def other_workload_arm(args):
                           "roofline": {"bound": "hbm", "achieved": attn_bytes / (ms_attn * 1e-3) / 1e9, "peak": peak,
                                        "unit": "GB/s", "frac": attn_bytes / (ms_attn * 1e-3) / 1e9 / peak,
                                        "peak_source": f"{peak_kind} HBM copy bandwidth"}},
-            "device_status": nat.device_status()}), flush=True)
+            "parity_check": parity, "device_status": nat.device_status()}), flush=True)
         return
     if args.workload == "backward":
         # backward of the headline window (64 causal taps at the cfg-2 shape): dQ, dK, dV from Q, K, V, dO
@@ -523,7 +572,7 @@ def other_workload_arm(args):
             "clocks": clocks, "kernel": nat.last_kernel(), "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": f"{peak_kind} HBM copy bandwidth", "bytes_per_launch_algorithmic": nbytes,
-                         # dram bytes of the two passes from the ncu capture in profiles/bwd_window_mma_cfg2_n64k.md
+                         # dram bytes of the two passes, from an ncu capture of one backward
                          "traffic": 322e6 + 375e6,
                          "note": "per backward (two launches: rows pass and cols pass)"},
             "device_status": nat.device_status()}), flush=True)
@@ -566,6 +615,12 @@ def other_workload_arm(args):
     ms = ev0.elapsed_time(ev1) / args.steps
     peak, peak_kind = measured_peak_gbs()
     achieved = nbytes / (ms * 1e-3) / 1e9
+    # the output of the last timed launch, a few row blocks against the oracle
+    last = sets[(args.steps - 1) % 2]
+    starts = [(0, 0), (Bw - 1, S - 128), (Bw // 2, S // 2 - 64), (0, S // 4 + 64)]
+    if args.workload == "longformer":
+        starts += [(0, int(glob[0]) - 64), (Bw - 1, int(glob[-1]) - 64)]      # blocks that hold a global position
+    parity = sampled_parity(out, *last, spec, starts)
     if args.workload == "dense":
         tpeak, tkind = measured_peak_tflops()
         tf = flops / (ms * 1e-3) / 1e12
@@ -576,7 +631,7 @@ def other_workload_arm(args):
             "clocks": clocks, "kernel": nat.last_kernel(),
             "roofline": {"bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s", "frac": tf / tpeak,
                          "peak_source": f"{tkind} dense bf16 GEMM throughput", "flop_per_launch_algorithmic": flops},
-            "device_status": nat.device_status()}), flush=True)
+            "parity_check": parity, "device_status": nat.device_status()}), flush=True)
         return
     print(json.dumps({
         "metric": f"sparse-attn fwd tokens/s ({args.workload})", "value": Bw * S / (ms * 1e-3), "unit": "tokens/s",
@@ -586,7 +641,7 @@ def other_workload_arm(args):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": f"{peak_kind} HBM copy bandwidth", "bytes_per_launch_algorithmic": nbytes},
         "tensor": {"useful_flop_per_step": flops, "tflops": flops / (ms * 1e-3) / 1e12},
-        "device_status": nat.device_status()}), flush=True)
+        "parity_check": parity, "device_status": nat.device_status()}), flush=True)
 
 
 def main():
@@ -611,12 +666,14 @@ def main():
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) != 0:
             return
-        steps, warmup = max(1, args.steps), max(0, min(args.warmup, 3))
+        steps, warmup = max(1, args.steps), args.warmup
         val, ms, info = reference_arm(steps, warmup)
+        ran = (f"{WORKLOAD}; run by the reference's CPU engine in fp32 as its two-sided window +-{TAPS // 2} "
+               f"(65 keys per row: the engine has no causal mode)") if info["kind"] == "reference" else WORKLOAD
         print(json.dumps({
             "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD},
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"workload": ran},
             "cpu_baseline": info,
             "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }), flush=True)

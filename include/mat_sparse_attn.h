@@ -51,7 +51,11 @@ extern "C" {
  *   MAT_LONGFORMER  [p-left, p+right] united with the global positions; a query
  *                   at a global position takes every key
  *                   (src/csrc/sparse_attention.cpp:241-256, de-duplicated).
- *                   global_idx must be sorted ascending without repeats.
+ *                   global_idx must be sorted ascending without repeats, every
+ *                   entry in [0, S_kv): the list lives on the device, so the
+ *                   library cannot refuse a bad entry; the kernels never touch
+ *                   memory through one (such a position contributes a zero key
+ *                   and owns no output row), the result is then unspecified.
  * A row whose set is empty produces zeros.
  * blk_rowptr, blk_colidx and global_idx are DEVICE pointers for
  * mat_sparse_attn_fwd and HOST pointers for mat_pattern_rowset / mat_pattern_nnz.
@@ -154,8 +158,10 @@ size_t mat_sparse_attn_bwd_workspace_bytes(int64_t B, int64_t S, int64_t H);
  * start-up has nothing left to lend as a workspace, and a latency-critical loop
  * cannot afford the device-wide synchronisation an allocation implies.  The
  * per-split partial results of the global-row pass (the only scratch the forward
- * uses) go to an array built into the library, 4 MiB per GPU, held from the
- * moment the library is loaded until the process ends.
+ * uses) go to an array built into the library, 4 MiB per GPU, which a GPU holds
+ * from the moment the library's device code is loaded onto it (with CUDA's
+ * default lazy loading: at the library's first use on that GPU) until the
+ * process ends.
  *   - MAT_LONGFORMER patterns, 16-bit dtypes, D = 64, whole sequences
  *     (q, k, v, o all [B, S, H, D]; q_offset = 0).  The caller still owns inputs
  *     and output.  Same results as mat_sparse_attn_fwd up to summation order.
@@ -164,9 +170,14 @@ size_t mat_sparse_attn_bwd_workspace_bytes(int64_t B, int64_t S, int64_t H);
  *     mat_sparse_attn_fwd with a caller workspace.  Within the limit the key axis
  *     is cut into as many splits as fit, so very large B*H runs with less
  *     parallelism in the global-row pass than the workspace version.
- *   - The first call on each device looks up the array's device address (once);
- *     make that call outside any stream capture.  No cudaMalloc, cudaFree or
- *     other allocating routine is called, on the first call or later.
+ *   - The first call on each device looks up the array's device address (once)
+ *     and may be the moment the driver loads the library's device code: treat
+ *     it as a warm-up and make it outside any stream capture.  The library
+ *     itself calls no cudaMalloc, cudaFree or other allocating routine, on the
+ *     first call or later.
+ *   - Every refusal happens before anything is launched: a call that returns
+ *     an error has not touched o.
+ *   - global_idx entries must lie in [0, S) (as for mat_sparse_attn_fwd).
  *   - All calls on a device share the one array and nothing in it needs
  *     clearing (every slot that is read is written first by the same call), but
  *     two calls that overlap on the GPU, e.g. on different streams, race on it:

@@ -21,7 +21,9 @@ struct Pipe {
     std::vector<cudaEvent_t> ev_in, ev_out;
 };
 
-std::mutex g_mu;
+// one pipeline (and one lock) per device: calls for different GPUs run side by side, calls for the
+// same GPU take turns, since they share its three streams
+std::mutex g_mus[64];
 Pipe g_pipes[64];
 
 int get_pipe(int device, size_t n_events, Pipe **out) {
@@ -103,7 +105,8 @@ int mat_sparse_attn_fwd_host(const void *q_host, const void *k_host, const void 
         return fail(MAT_ERR_WORKSPACE, "device staging of %zu bytes (256-byte aligned) required, got %zu",
                     need, staging ? staging_bytes : (size_t)0);
 
-    std::lock_guard<std::mutex> lock(g_mu);
+    if (device < 0 || device >= 64) return fail(MAT_ERR_INVALID, "device ordinal %d out of range", device);
+    std::lock_guard<std::mutex> lock(g_mus[device]);
     int prev = 0;
     cudaError_t e = cudaGetDevice(&prev);
     if (e == cudaSuccess && prev != device) e = cudaSetDevice(device);
@@ -154,8 +157,13 @@ int mat_sparse_attn_fwd_host(const void *q_host, const void *k_host, const void 
             s.q_offset = c0;
             const size_t qoff = ((size_t)b * S + (size_t)c0) * row_bytes;
             const size_t koff = (size_t)b * S * row_bytes;
+            // The launch sees only the key rows whose copies it waited for.  The tiled kernels stage
+            // whole groups of keys, and a staged row that lies past the last landed chunk would be
+            // multiplied by a zero weight; whatever the staging memory held there (possibly a NaN
+            // pattern) must not reach that product, so those rows are outside the tensor and read as zeros.
+            const int64_t skv = std::min(S, (last + 1) * C);
             Problem p;
-            rc = make_problem(p, dq + qoff, dk + koff, dv + koff, dout + qoff, 1, c1 - c0, S, H, D,
+            rc = make_problem(p, dq + qoff, dk + koff, dv + koff, dout + qoff, 1, c1 - c0, skv, H, D,
                               dtype, &s, scale, ws, ws_bytes, pipe->comp);
             if (rc == MAT_OK) rc = run_problem(p);
             if (rc != MAT_OK) break;

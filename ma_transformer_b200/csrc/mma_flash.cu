@@ -527,10 +527,13 @@ __global__ void gather_global_rows_kernel(const uint4 *__restrict__ k, const uin
                                           uint4 *__restrict__ kg, uint4 *__restrict__ vg,
                                           const int64_t *__restrict__ gidx, int n_global, int64_t S, int HH) {
     const int e = blockIdx.x, b = blockIdx.y;
-    const int64_t src = ((int64_t)b * S + gidx[e]) * HH * 8, dst = ((int64_t)b * n_global + e) * HH * 8;
+    const int64_t row = gidx[e];
+    const bool in_range = row >= 0 && row < S;   // a position outside the sequence gathers zeros, never memory
+    const int64_t src = ((int64_t)b * S + (in_range ? row : 0)) * HH * 8, dst = ((int64_t)b * n_global + e) * HH * 8;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     for (int i = threadIdx.x; i < HH * 8; i += blockDim.x) {
-        kg[dst + i] = k[src + i];
-        vg[dst + i] = v[src + i];
+        kg[dst + i] = in_range ? k[src + i] : zero;
+        vg[dst + i] = in_range ? v[src + i] : zero;
     }
 }
 
@@ -545,6 +548,8 @@ merge_global_rows_kernel(const float *__restrict__ partial, T *__restrict__ out,
                          int n_splits, int ng_pad, int HH, int64_t Sq1, float sl2, int n_outer,
                          int64_t outer_stride, int e_first) {
     const int e = e_first + blockIdx.x, hh = blockIdx.y, b = blockIdx.z, d = threadIdx.x;
+    const int64_t row = gidx[e];
+    if (row < 0 || row >= Sq1) return;   // a position outside the sequence owns no output row
     const float *base = partial + (((int64_t)b * HH + hh) * n_splits * ng_pad + e) * kPartialStride;
     const int64_t split_stride = (int64_t)ng_pad * kPartialStride;
     float m = -INFINITY;
@@ -559,7 +564,6 @@ merge_global_rows_kernel(const float *__restrict__ partial, T *__restrict__ out,
                 l = fmaf(w, pr[1], l);
                 acc = fmaf(w, pr[2 + d], acc);
             }
-    const int64_t row = gidx[e];
     out[((b * Sq1 + row) * HH + hh) * 64 + d] = Elem<T>::from_f(l > 0.f ? acc / l : 0.f);
 }
 
@@ -886,6 +890,15 @@ int static_scratch_on_current_device(float **out) {
 template <typename T>
 int launch_longformer_static(const Problem &p, float *scratch) {
     constexpr int TQ = 64;
+    // every refusal comes before the first launch: a call that is turned away has enqueued nothing
+    // and leaves the caller's output untouched
+    const int tiles = (int)((p.pat.n_global + 63) / 64);
+    const size_t per_split = (size_t)p.B * p.H * tiles * 64 * kPartialStride * sizeof(float);
+    if (per_split > kStaticScratchBytes)
+        return fail(MAT_ERR_UNSUPPORTED,
+                    "B*H*global rows = %lld*%lld*%d needs %zu bytes of partials even unsplit; the built-in "
+                    "scratch holds %zu: use mat_sparse_attn_fwd with a workspace",
+                    (long long)p.B, (long long)p.H, tiles * 64, per_split, kStaticScratchBytes);
     FlashParams fp;
     fp.Sq1 = (int32_t)p.Sq;
     fp.Skv1 = (int32_t)p.Skv;
@@ -910,13 +923,6 @@ int launch_longformer_static(const Problem &p, float *scratch) {
     if (int rc = launch_kind<T, MAT_LONGFORMER, TQ, 128, 4, 2, false, 3>(p, fp, 1, "mma_longformer_static")) return rc;
     if (fp.n_global == 0) return MAT_OK;
 
-    const int tiles = (fp.n_global + 63) / 64;
-    const size_t per_split = (size_t)p.B * p.H * tiles * 64 * kPartialStride * sizeof(float);
-    if (per_split > kStaticScratchBytes)
-        return fail(MAT_ERR_UNSUPPORTED,
-                    "B*H*global rows = %lld*%lld*%d needs %zu bytes of partials even unsplit; the built-in "
-                    "scratch holds %zu: use mat_sparse_attn_fwd with a workspace",
-                    (long long)p.B, (long long)p.H, tiles * 64, per_split, kStaticScratchBytes);
     const GlobalRowPlan want = plan_global_rows(p);
     int64_t n_splits = std::min<int64_t>(want.n_splits, (int64_t)(kStaticScratchBytes / per_split));
     int64_t len = (p.Skv + n_splits - 1) / n_splits;

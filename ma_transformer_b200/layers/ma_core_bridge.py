@@ -11,6 +11,9 @@ What changes behind the unchanged surface:
     call raises.
   * ``MACoreAttention`` takes one additive keyword, ``pattern``, to select a
     causal / dilated / block-sparse / Longformer key set.
+  * CUDA tensors take the native forward AND backward kernels in training mode
+    too (the reference's ``fallback_training`` python path remains for host
+    tensors only).
 """
 from __future__ import annotations
 
@@ -152,13 +155,18 @@ class MACoreAttentionFunction(torch.autograd.Function):
             else:
                 dq, dk, dv = sparse_attention_cuda.dense_backward(*args, bool(ctx.use_causal_mask))
         else:
-            q = query.detach().requires_grad_(True)
-            k = key.detach().requires_grad_(True)
-            v = value.detach().requires_grad_(True)
-            with torch.enable_grad():
-                y = pytorch_sparse_attention(q, k, v, ctx.window_size) if ctx.sparse else \
-                    pytorch_dense_attention(q, k, v, ctx.use_causal_mask)
-            dq, dk, dv = torch.autograd.grad(y, (q, k, v), grad_output)
+            # host tensors: the gradients are computed on the GPU by the same kernels (copy in, run, copy
+            # back), as the forward was; there is no CPU arithmetic here
+            if not torch.cuda.is_available():
+                raise RuntimeError("this build computes on a B200 only: no GPU is visible and there is no CPU fallback")
+            dt = query.dtype
+            work = dt if dt in (torch.float32, torch.bfloat16, torch.float16) else torch.float32
+            args = tuple(t.detach().to("cuda", work).contiguous() for t in (query, key, value, grad_output))
+            if ctx.sparse:
+                grads = sparse_attention_cuda.backward(*args, int(ctx.window_size))
+            else:
+                grads = sparse_attention_cuda.dense_backward(*args, bool(ctx.use_causal_mask))
+            dq, dk, dv = (g.to("cpu", dt) for g in grads)
         need = ctx.needs_input_grad
         return (dq if need[0] else None, dk if need[1] else None, dv if need[2] else None,
                 None, None, None, None)
@@ -200,7 +208,14 @@ class MACoreAttention(nn.Module):
         if self.sparse and self.window_size <= 0:
             raise ValueError("window_size must be > 0 for sparse attention")
 
-        if self.training and self.fallback_training and self.pattern is None:
+        # Training mode.  The reference returns its differentiable python implementation here
+        # (ma_core_bridge.py:317-325) because its extension's backward was an afterthought.  This library
+        # has native backward kernels, so CUDA tensors always take the native forward and backward,
+        # training or not.  Host tensors in training mode keep the reference's behaviour (its torch
+        # implementation, whose graph supports double backward): that is the reference's own host-side
+        # training path, not a substitute for a kernel.
+        if (self.training and self.fallback_training and self.pattern is None
+                and not (query.is_cuda and key.is_cuda and value.is_cuda)):
             for t in (query, key, value):
                 if t.requires_grad and t.grad_fn is not None:
                     t.retain_grad()

@@ -1,5 +1,5 @@
 """Order-book transformer forward: the caller around the sparse-attention hot path
-for the fifth BASELINE configuration (ticks [B, N, 40] -> Linear(40->256) -> 4
+for the order-book configuration (ticks [B, N, 40] -> Linear(40->256) -> 4
 pre-LayerNorm blocks with 4 heads of width 64 and dilated causal window attention
 (64 taps, dilation 2), GELU feed-forward of width 1024 -> last-token Linear(256->3)).
 
@@ -84,25 +84,3 @@ class OrderBookTransformer(nn.Module):
         for blk in self.blocks:
             x = blk(x)
         return self.head(self.norm(x[:, -1]))
-
-
-def reference_forward(model: OrderBookTransformer, ticks: torch.Tensor) -> torch.Tensor:
-    """The same network in plain fp32 torch with a dense masked attention: the
-    numerics reference of the model tests (small sequences only)."""
-    spec = model.pattern
-    x = model.embed(ticks) * math.sqrt(model.d_model)
-    S = x.shape[1]
-    i = torch.arange(S, device=x.device)
-    d = i[:, None] - i[None, :]                      # query - key
-    keep = (d >= 0) & (d <= spec.left * spec.dilation) & (d % spec.dilation == 0)
-    for blk in model.blocks:
-        B, _, Dm = x.shape
-        y = blk.norm1(x)
-        shape = (B, S, blk.n_heads, blk.head_dim)
-        q, k, v = blk.q_proj(y).view(shape), blk.k_proj(y).view(shape), blk.v_proj(y).view(shape)
-        s = torch.einsum("bihd,bjhd->bhij", q, k) / math.sqrt(blk.head_dim)
-        s = s.masked_fill(~keep, float("-inf"))
-        a = torch.einsum("bhij,bjhd->bihd", torch.softmax(s, dim=-1), v).reshape(B, S, Dm)
-        x = x + blk.out_proj(a)
-        x = x + blk.ff2(F.gelu(blk.ff1(blk.norm2(x))))
-    return model.head(model.norm(x[:, -1]))

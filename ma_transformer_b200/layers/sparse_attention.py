@@ -1,7 +1,14 @@
 """``SparseAttention`` over [batch, seq_len, model_dim] tensors, the layer of
-src/layers/sparse_attention.py:26-110: one head of width model_dim, sliding
-window [i-w, i+w], native kernels in eval mode and the differentiable torch path
-in training mode (as the reference's fallback_training=True)."""
+src/layers/sparse_attention.py:26-110: sliding window [i-w, i+w] on the native
+kernels (forward and backward) for CUDA tensors.
+
+The reference treats the whole model width as ONE head (sparse_attention.py:63-78;
+its model passes ``num_heads`` and ignores it, src/model.py:31).  ``num_heads`` is
+an additive keyword here: the width is split into that many heads of equal size, a
+free view of the same memory ([B, S, H*Dh] is already the [B, S, H, Dh] layout the
+kernels read), and heads of width 64 in a 16-bit dtype land on the tensor-core
+kernels.  The default of 1 keeps the reference's arithmetic.
+"""
 from __future__ import annotations
 
 import torch
@@ -11,13 +18,16 @@ from .ma_core_bridge import MACoreAttention
 
 
 class SparseAttention(nn.Module):
-    def __init__(self, window_size: int = 3, use_ma_core: bool = True):
+    def __init__(self, window_size: int = 3, use_ma_core: bool = True, num_heads: int = 1):
         super().__init__()
         if not isinstance(window_size, int):
             raise TypeError("window_size must be an integer for SparseAttention")
         if window_size <= 0:
             raise ValueError("window_size must be > 0 for SparseAttention")
+        if not isinstance(num_heads, int) or num_heads <= 0:
+            raise ValueError("num_heads must be a positive integer")
         self.window_size = window_size
+        self.num_heads = num_heads
         self.use_ma_core = use_ma_core  # kept for signature compatibility; the native path is the only one
         self.ma_core_attention = MACoreAttention(sparse=True, window_size=window_size,
                                                  fallback_training=True)
@@ -25,5 +35,13 @@ class SparseAttention(nn.Module):
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
         if q.dim() != 3:
             raise ValueError("Expected tensors with shape [batch, seq_len, model_dim]")
-        out = self.ma_core_attention(q.unsqueeze(2), k.unsqueeze(2), v.unsqueeze(2))
-        return out.squeeze(2)
+        B, S, Dm = q.shape
+        if Dm % self.num_heads:
+            raise ValueError(f"model_dim {Dm} is not divisible by num_heads {self.num_heads}")
+        shape = (B, S, self.num_heads, Dm // self.num_heads)
+        if k.shape != q.shape or v.shape != q.shape:
+            # let the attention module word the mismatch as the reference does
+            out = self.ma_core_attention(q.unsqueeze(2), k.unsqueeze(2), v.unsqueeze(2))
+            return out.squeeze(2)
+        out = self.ma_core_attention(q.reshape(shape), k.reshape(shape), v.reshape(shape))
+        return out.reshape(B, S, Dm)

@@ -95,6 +95,17 @@ class PatternSpec:
         return PatternSpec(self.kind, self.left, self.right, self.dilation, self.causal, self.block,
                            self.blk_rowptr, self.blk_colidx, self.global_idx, int(q_offset))
 
+    def check_against(self, s_kv: int) -> None:
+        """Raises RuntimeError when the pattern names a key position outside ``[0, s_kv)``.
+
+        The library reads the global positions on the device, where it cannot refuse them; a
+        position past the sequence would name memory that is not the caller's.  (Block column ids
+        past the sequence are harmless: their keys are simply absent.)"""
+        if self.kind == LONGFORMER and self.global_idx is not None and len(self.global_idx):
+            if int(self.global_idx[-1]) >= int(s_kv) or int(self.global_idx[0]) < 0:
+                raise RuntimeError(f"global position {int(self.global_idx[-1])} lies outside the sequence of "
+                                   f"{int(s_kv)} keys: global positions must be in [0, S)")
+
     # ---- C structs -----------------------------------------------------------
     def _fill(self, s: nat.MatPatternSpec) -> None:
         s.kind, s.causal = int(self.kind), int(bool(self.causal))

@@ -22,7 +22,7 @@ from . import _native as nat
 from .patterns import PatternSpec, WINDOW
 
 _DTYPES = {torch.float32: nat.MAT_F32, torch.bfloat16: nat.MAT_BF16, torch.float16: nat.MAT_F16}
-_workspaces: Dict[str, torch.Tensor] = {}
+_workspaces: Dict[tuple, torch.Tensor] = {}
 
 
 def _check_inputs(*tensors: torch.Tensor) -> None:
@@ -42,10 +42,19 @@ def _check_inputs(*tensors: torch.Tensor) -> None:
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    key = str(device)
+    """Scratch buffer of at least ``nbytes`` for work on torch's current stream of ``device``.
+
+    One buffer per (device, stream): calls issued on one stream reuse it in stream order, calls on
+    different streams get different buffers and cannot race.  A buffer that has to grow is replaced;
+    the old one goes back to torch's allocator on the stream that used it, which orders its reuse
+    behind the kernels still reading it.
+    """
+    device = torch.device(device)
+    key = (device.type, device.index, torch.cuda.current_stream(device).cuda_stream)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        with torch.cuda.device(device):
+            buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf
 
@@ -65,6 +74,7 @@ def forward_pattern(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
         raise RuntimeError("Q,K,V must have same shape (key/value may only differ from query in length)")
     B, Sq, H, D = query.shape
     Skv = key.shape[1]
+    spec.check_against(Skv)
     if out is None:
         out = torch.empty_like(query)
     else:
@@ -139,6 +149,7 @@ def forward_longformer_noalloc(query: torch.Tensor, key: torch.Tensor, value: to
     if not (query.shape == key.shape == value.shape == out.shape):
         raise RuntimeError("Q,K,V and out must have same shape")
     B, S, H, D = query.shape
+    spec.check_against(S)
     with torch.cuda.device(query.device):
         s = spec.device_struct(query.device)
         stream = torch.cuda.current_stream(query.device).cuda_stream
@@ -204,6 +215,7 @@ def forward_host(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, sp
     if query.dtype not in _DTYPES or key.dtype != query.dtype or value.dtype != query.dtype:
         raise RuntimeError("Only float32, bfloat16 and float16 are supported")
     B, S, H, D = query.shape
+    spec.check_against(S)
     dt = _DTYPES[query.dtype]
     dev = torch.device("cuda", device)
     if out is None:

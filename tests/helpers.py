@@ -1,6 +1,9 @@
 """Shared helpers of the parity tests: seeded inputs, tolerances, pattern pairs."""
+import math
+
 import numpy as np
 import torch
+import torch.nn.functional as F
 
 from oracle import oracle as O
 from ma_transformer_b200.patterns import PatternSpec, WINDOW, BLOCK, LONGFORMER
@@ -59,3 +62,38 @@ def expected_window_kernel(spec: PatternSpec, Skv: int) -> str:
     if left >= Skv - 1 and (right >= Skv - 1 or right == 0):
         return "umma_dense"
     return "umma_window" if left + right > 128 else "mma_window"
+
+
+def orderbook_reference_forward(model, ticks: torch.Tensor) -> torch.Tensor:
+    """The order-book transformer (ma_transformer_b200.layers.orderbook_model) in plain fp32 torch with a dense masked attention: the
+    numerics reference of the model tests (small sequences only)."""
+    spec = model.pattern
+    x = model.embed(ticks) * math.sqrt(model.d_model)
+    S = x.shape[1]
+    i = torch.arange(S, device=x.device)
+    d = i[:, None] - i[None, :]                      # query - key
+    keep = (d >= 0) & (d <= spec.left * spec.dilation) & (d % spec.dilation == 0)
+    for blk in model.blocks:
+        B, _, Dm = x.shape
+        y = blk.norm1(x)
+        shape = (B, S, blk.n_heads, blk.head_dim)
+        q, k, v = blk.q_proj(y).view(shape), blk.k_proj(y).view(shape), blk.v_proj(y).view(shape)
+        s = torch.einsum("bihd,bjhd->bhij", q, k) / math.sqrt(blk.head_dim)
+        s = s.masked_fill(~keep, float("-inf"))
+        a = torch.einsum("bhij,bjhd->bihd", torch.softmax(s, dim=-1), v).reshape(B, S, Dm)
+        x = x + blk.out_proj(a)
+        x = x + blk.ff2(F.gelu(blk.ff1(blk.norm2(x))))
+    return model.head(model.norm(x[:, -1]))
+
+
+def masked_dense_attention(q, k, v, left, right, dilation=1):
+    """Window attention { p + t*dilation : -left <= t <= right } as a dense masked softmax in the
+    tensors' own dtype (use float64 inputs for an autograd reference): independent of every kernel
+    and of the banded torch implementation."""
+    S = q.shape[1]
+    i = torch.arange(S, device=q.device)
+    d = i[None, :] - i[:, None]                       # key - query
+    keep = (d % dilation == 0) & (d >= -left * dilation) & (d <= right * dilation)
+    s = torch.einsum("bihd,bjhd->bhij", q, k) / math.sqrt(q.shape[-1])
+    s = s.masked_fill(~keep, float("-inf"))
+    return torch.einsum("bhij,bjhd->bihd", torch.softmax(s, dim=-1), v)

@@ -158,6 +158,23 @@ def test_malformed_patterns_are_rejected():
     assert b"pattern kind" in nat.lib.mat_last_error()
 
 
+def test_global_positions_outside_the_sequence_are_refused_on_the_host():
+    """The list of global positions is read on the device, where nothing can refuse it, so the python
+    surface checks it before any launch (no GPU involved: the check is host arithmetic)."""
+    spec = PatternSpec.longformer(2, 2, [3, 64])
+    with pytest.raises(RuntimeError, match=r"\[0, S\)"):
+        spec.check_against(64)
+    spec.check_against(65)                       # in range: silent
+    PatternSpec.longformer(2, 2, []).check_against(1)
+    PatternSpec.causal_window(8).check_against(4)
+    with pytest.raises(ValueError):
+        PatternSpec.longformer(2, 2, [-1, 3])     # negative positions never pass the constructor
+    # host tensors through forward_host are refused before the library is entered
+    q = torch.zeros(1, 64, 1, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="outside the sequence"):
+        mt.sparse_attention_cuda.forward_host(q, q, q, spec)
+
+
 def test_module_validation_matches_reference_messages():
     # src/layers/ma_core_bridge.py:272-277, 297-314
     with pytest.raises(ValueError):

@@ -5,7 +5,8 @@ import pytest
 import torch
 
 from ma_transformer_b200 import _native as nat
-from ma_transformer_b200.layers.orderbook_model import OrderBookTransformer, reference_forward, synthetic_ticks
+from ma_transformer_b200.layers.orderbook_model import OrderBookTransformer, synthetic_ticks
+from helpers import orderbook_reference_forward as reference_forward
 
 pytestmark = pytest.mark.gpu
 
