@@ -120,6 +120,7 @@ int make_problem(Problem &p, const void *q, const void *k, const void *v, void *
 int run_problem(const Problem &p) {
     if (umma_block_supports(p)) return launch_umma_block(p);
     if (umma_dense_supports(p)) return launch_umma_dense(p);
+    if (umma_band_supports(p)) return launch_umma_band(p);
     if (mma_flash_supports(p)) {
         const size_t need = mma_flash_workspace_bytes(p);
         if (need > 0) {
@@ -183,11 +184,12 @@ const char *mat_last_kernel(void) { return g_last_kernel; }
 
 int mat_device_status(int *status_out) {
     if (!status_out) return fail(MAT_ERR_INVALID, "status_out is NULL");
-    int a = 0, b = 0, c = 0;
+    int a = 0, b = 0, c = 0, d = 0;
     if (int rc = flash_status_read_and_clear(&a)) return rc;
     if (int rc = umma_status_read_and_clear(&b)) return rc;
     if (int rc = bwd_status_read_and_clear(&c)) return rc;
-    *status_out = a | b | c;
+    if (int rc = band_status_read_and_clear(&d)) return rc;
+    *status_out = a | b | c | d;
     return MAT_OK;
 }
 
@@ -258,6 +260,7 @@ int mat_sparse_attn_fwd_sharded(const void *q, const void *k, const void *v, voi
     }
     p.k_prev = k_prev; p.v_prev = v_prev; p.S_prev = S_prev;
     p.k_next = k_next; p.v_next = v_next; p.S_next = S_next;
+    if (umma_band_supports(p)) return launch_umma_band(p);
     return launch_mma_flash(p);
 }
 

@@ -67,6 +67,9 @@ int launch_umma_block(const Problem &p);
 bool umma_dense_supports(const Problem &p);  // dense / causal dense on the same tcgen05 pipeline
 int launch_umma_dense(const Problem &p);
 int umma_status_read_and_clear(int *out);
+bool umma_band_supports(const Problem &p);   // umma_band.cu: windows of at most 128 taps, persistent, on tcgen05 / TMEM
+int launch_umma_band(const Problem &p);
+int band_status_read_and_clear(int *out);
 // Longformer global-row pass on tcgen05 (umma_block.cu): how the key axis is split, and the launch
 constexpr int kPartialStride = 66;   // floats per row of a partial: max, sum, 64 outputs
 struct GlobalRowSplit {

@@ -1,0 +1,465 @@
+// Narrow-window forward on the 5th-generation tensor cores: a persistent kernel that runs
+// both contractions of every 128-query tile as single tcgen05.mma sweeps over the tile's whole
+// key band, with the accumulators in tensor memory and the operands staged by TMA.
+//
+// Replaces sparse_attention_forward_warp (src/cuda/sparse_attention_kernel.cu:211-263) for
+// 16-bit inputs with head width 64 and windows that reach at most 128 keys
+// (left + right <= 128 taps, the reference's default window_size = 64 included).
+//
+// Why tcgen05 for a band that is mostly mask: the warp-level mma path feeds its operands through
+// ldmatrix, and at 64 taps per row the shared-memory traffic of those fragment loads (every warp
+// re-reads the K/V rows its neighbours read too) is what bounds it, not HBM.  tcgen05.mma reads
+// K and V from shared memory once per tile; P never touches shared memory at all (it is stored in
+// tensor memory and read from there as the A operand); the scores outside the band cost tensor
+// work, of which there is plenty to spare, and no memory traffic.
+//
+// Work decomposition
+//   - A dilated window over [B,S,H,64] is a plain window over the same memory viewed as
+//     [B, S/dil, dil*H, 64]; the kernel only ever sees dilation 1 and HH = dil*H heads.
+//   - Work item = (batch, 128-query tile, head), heads running fastest, so the CTAs resident at
+//     one time work on a short range of tokens across all heads (the 128-byte rows of a token's
+//     heads leave DRAM together).  One CTA per SM; CTA c takes items c, c + G, c + 2G, ...
+//   - Keys of an item: KT = 192 or 256 consecutive rows starting at the first key of the tile's
+//     first row, rounded down to a multiple of 16.  Row r of the tile attends the columns
+//     [r + cl, r + cl + left + right] of that range (cl = the rounding, 0..15).
+//   - Warp roles: one TMA lane fills two rings of stages ({Q, K} and V, separately released);
+//     one MMA lane issues S = Q K^T (4 instructions of N = KT) and [O | l] = P [V | 1]
+//     (KT/16 instructions of N = 80: V widened by a block of ones, so the row sums come out of
+//     the tensor core); eight softmax warps, four per TMEM slot, thread r owning query row r:
+//     read the row's band of scores from TMEM, mask, maximum, exponentials, store P (16-bit
+//     pairs) over the first KT/2 columns of the slot with zeros outside the band, then read the
+//     finished O row and the row sum, normalise and write the output row.
+//   - Two TMEM slots of 256 columns alternate between items, so the tensor core computes the
+//     scores of item i + 1 and the P V product of item i - 1 while the softmax warps of the other
+//     slot work on item i.  Inside a slot S (KT columns), then P (columns [0, KT/2)) and
+//     [O | l] (columns [KT/2, KT/2 + 80)) reuse the same columns in turn.
+//
+// Every wait is bounded; a wait that runs out sets the library's status word, every role leaves
+// its loop, and the CTA frees its tensor memory and returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "mat_common.cuh"
+#include "ptx.cuh"
+#include "umma.cuh"
+
+namespace mat {
+namespace {
+
+using namespace umma;
+
+constexpr int kRowBytes = 128;
+constexpr int kTQ = 128;          // query rows per item
+constexpr int kSumN = 16;         // extra B columns of the P V product: a block of ones
+constexpr int kSlotCols = 256;    // TMEM columns per slot
+constexpr int kSoftmaxWarps = 8;  // four per slot
+constexpr int kThreads = (kSoftmaxWarps + 3) * 32;   // + one MMA warp per slot + the TMA warp
+
+__device__ int g_band_status = 0;
+
+struct BandParams {
+    int32_t Sq1, Skv1, off1;       // query rows, key rows and q_offset of one sub-sequence
+    int32_t key_lo, key_hi;        // keys the kernel may touch: [key_lo, 0) previous shard, [Skv1, key_hi) next shard
+    int32_t prev_rows;
+    int32_t left, right;
+    int32_t cl;                    // column of row 0's first key inside an item's key range
+    int32_t HH, n_tiles;
+    uint32_t n_items;
+    float sl2;                     // scale * log2(e)
+};
+
+struct BandMaps {
+    CUtensorMap q, k, v, o;                                  // boxes of 128 (q, o) and KT rows
+    CUtensorMap k_own, v_own, k_prev, v_prev, k_next, v_next;   // 16-row boxes for stages that cross a shard edge
+};
+
+template <int KT> struct BandCfg {
+    static constexpr int kNQK = 2;                   // {Q, K} stages
+    static constexpr int kNV = KT == 192 ? 3 : 2;    // V stages (released later than K: after the P V product)
+    static constexpr int kQKBytes = kTQ * kRowBytes + KT * kRowBytes;
+    static constexpr int kVBytes = KT * kRowBytes;
+    static constexpr int kNCH = (KT - 96) / 32;      // 32-column chunks of a warp's band: 3 or 5
+    static constexpr int kBars = 2 * kNQK + 2 * kNV + 12;
+    static constexpr int kOutBytes = kTQ * kRowBytes;   // one output tile per slot, staged for its bulk store
+    static constexpr size_t kSmemBytes = 1024 + (size_t)kNQK * kQKBytes + (size_t)kNV * kVBytes + 2 * kOutBytes +
+                                         kSumN * kRowBytes + kBars * 8 + 16;
+};
+
+template <typename T, int KT>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
+    using C = BandCfg<KT>;
+    constexpr int NQK = C::kNQK, NV = C::kNV, NCH = C::kNCH;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *sQK = smem;                                  // stage s: Q at +0 (16 KB), K behind it
+    uint8_t *sV = sQK + NQK * C::kQKBytes;
+    uint8_t *sOut = sV + NV * C::kVBytes;                 // slot s: its output tile, 128-byte swizzled rows
+    uint8_t *sOnes = sOut + 2 * C::kOutBytes;             // 16 rows of ones
+    uint64_t *bars = (uint64_t *)(sOnes + kSumN * kRowBytes);
+    uint64_t *qk_full = bars, *qk_empty = qk_full + NQK, *v_full = qk_empty + NQK, *v_empty = v_full + NV;
+    uint64_t *s_ready = v_empty + NV, *p_ready = s_ready + 2, *o_ready = p_ready + 2, *slot_free = o_ready + 2;
+    uint64_t *out_full = slot_free + 2, *out_free = out_full + 2;   // the staged output tile of a slot
+    uint32_t *tmem_slot = (uint32_t *)(out_free + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NQK; ++i) { ptx::mbar_init(qk_full + i, 1); ptx::mbar_init(qk_empty + i, 1); }
+        for (int i = 0; i < NV; ++i) { ptx::mbar_init(v_full + i, 1); ptx::mbar_init(v_empty + i, 1); }
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(s_ready + i, 1);
+            ptx::mbar_init(p_ready + i, 4);
+            ptx::mbar_init(o_ready + i, 1);
+            ptx::mbar_init(slot_free + i, 4);
+            ptx::mbar_init(out_full + i, 4);
+            ptx::mbar_init(out_free + i, 1);
+        }
+        ptx::fence_barrier_init();
+    }
+    if (threadIdx.x < kSumN * kRowBytes / 16) {
+        const uint32_t one2 = ptx::Mma<T>::kOnes;
+        reinterpret_cast<uint4 *>(sOnes)[threadIdx.x] = make_uint4(one2, one2, one2, one2);
+        ptx::fence_proxy_async_smem();
+    }
+    if (warp == kSoftmaxWarps) {
+        tmem_alloc(tmem_slot, 2 * kSlotCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const uint32_t G = gridDim.x, HHu = (uint32_t)P.HH, n_tiles = (uint32_t)P.n_tiles;
+    // items of this CTA
+    const uint32_t n_mine = blockIdx.x < P.n_items ? (P.n_items - blockIdx.x + G - 1) / G : 0;
+
+    if (warp == kSoftmaxWarps + 2) {
+        // ================= TMA lane: {Q, K} and V of item it into their rings =================
+        if (lane == 0) {
+            for (uint32_t it = 0; it < n_mine; ++it) {
+                const uint32_t L = blockIdx.x + it * G;
+                const int hh = L % HHu, b = L / (HHu * n_tiles);
+                const int q0 = (int)((L / HHu) % n_tiles) * kTQ;
+                const int start = (q0 + P.off1 - P.left) - P.cl;   // first key row of the item (a multiple of 16)
+                const int sq = it % NQK, sv = it % NV;
+                // a stage that crosses into a neighbour shard's rows is fetched 16 rows at a time, each
+                // piece from the tensor that owns it
+                const bool pieces = (start < 0 && P.key_lo < 0) || (start + KT > P.Skv1 && P.key_hi > P.Skv1);
+                auto load_rows = [&](uint8_t *dst, uint64_t *bar, const CUtensorMap *whole, const CUtensorMap *own,
+                                     const CUtensorMap *prev, const CUtensorMap *next) {
+                    if (!pieces) {
+                        ptx::tma_load_4d(dst, whole, bar, 0, hh, start, b);
+                        return;
+                    }
+                    for (int i = 0; i < KT / 16; ++i) {
+                        const int a = start + 16 * i;
+                        const CUtensorMap *m = own;
+                        int row = a;
+                        if (a < 0 && P.key_lo < 0) { m = prev; row = P.prev_rows + a; }
+                        else if (a >= P.Skv1 && P.key_hi > P.Skv1) { m = next; row = a - P.Skv1; }
+                        ptx::tma_load_4d(dst + i * 16 * kRowBytes, m, bar, 0, hh, row, b);
+                    }
+                };
+                if (it >= (uint32_t)NQK && !ptx::mbar_wait(qk_empty + sq, (it / NQK - 1) & 1)) {
+                    atomicExch(&g_band_status, 1);
+                    break;
+                }
+                uint8_t *dq = sQK + sq * C::kQKBytes;
+                ptx::mbar_expect_tx(qk_full + sq, C::kQKBytes);
+                ptx::tma_load_4d(dq, &maps.q, qk_full + sq, 0, hh, q0, b);
+                load_rows(dq + kTQ * kRowBytes, qk_full + sq, &maps.k, &maps.k_own, &maps.k_prev, &maps.k_next);
+                if (it >= (uint32_t)NV && !ptx::mbar_wait(v_empty + sv, (it / NV - 1) & 1)) {
+                    atomicExch(&g_band_status, 1);
+                    break;
+                }
+                ptx::mbar_expect_tx(v_full + sv, C::kVBytes);
+                load_rows(sV + sv * C::kVBytes, v_full + sv, &maps.v, &maps.v_own, &maps.v_prev, &maps.v_next);
+            }
+        }
+    } else if (warp >= kSoftmaxWarps) {
+        // ================= MMA lanes, one per slot: S(i), then [O | l](i) once the weights are stored =================
+        // (two issuing lanes: an instruction costs its issuer about 125 cycles whatever its shape, and a slot's
+        // 4 + KT/16 instructions per item would otherwise sit on the other slot's critical path)
+        if (lane == 0) {
+            const int slot = warp - kSoftmaxWarps;
+            const uint32_t idesc_s = instr_desc<T>(false, KT), idesc_pv = instr_desc<T>(true, 64 + kSumN);
+            const uint32_t qk_addr = ptx::smem_u32(sQK), v_addr0 = ptx::smem_u32(sV), ones_addr = ptx::smem_u32(sOnes);
+            const uint32_t ts = tmem_base + slot * kSlotCols;      // S, then P in its columns [0, KT/2)
+            const uint32_t td = ts + KT / 2;                       // [O | l]: 80 columns behind P
+            bool ok = true;
+            for (uint32_t i = slot; ok && i < n_mine; i += 2) {
+                const int sq = i % NQK, sv = i % NV;
+                if (!(ok = ptx::mbar_wait(qk_full + sq, (i / NQK) & 1))) break;
+                // the slot's previous item (i - 2) has been read out by its softmax warps
+                if (i >= 2 && !(ok = ptx::mbar_wait(slot_free + slot, ((i >> 1) - 1) & 1))) break;
+                tc_fence_after();
+                const uint64_t dq = smem_desc(qk_addr + sq * C::kQKBytes);
+                const uint64_t dk = smem_desc(qk_addr + sq * C::kQKBytes + kTQ * kRowBytes);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)   // 16 of the 64 head columns per instruction (32 bytes along a row)
+                    umma_f16_ss(ts, dq + ks * 2, dk + ks * 2, idesc_s, ks > 0);
+                umma_commit(s_ready + slot);
+                umma_commit(qk_empty + sq);
+                if (!(ok = ptx::mbar_wait(v_full + sv, (i / NV) & 1))) break;
+                if (!(ok = ptx::mbar_wait(p_ready + slot, (i >> 1) & 1))) break;   // P(i) is in TMEM
+                tc_fence_after();
+                const uint32_t v_addr = v_addr0 + sv * C::kVBytes;
+#pragma unroll
+                for (int ks = 0; ks < KT / 16; ++ks) {
+                    // B = 16 keys x 80 columns: the 64 head columns from the V stage, then a second 64-wide
+                    // block (16 of it used) that the leading-dimension offset points at the ones
+                    const uint32_t vk = v_addr + ks * 16 * kRowBytes;
+                    umma_f16_ta(td, ts + ks * 8, smem_desc(vk, (ones_addr - vk) >> 4), idesc_pv, ks > 0);
+                }
+                umma_commit(o_ready + slot);
+                umma_commit(v_empty + sv);
+            }
+            if (!ok) atomicExch(&g_band_status, 1);
+        }
+    } else {
+        // ================= softmax warps: thread r owns query row r of its slot's item =================
+        const int slot = warp >> 2, quad = warp & 3;
+        const int r = quad * 32 + lane;
+        const uint32_t t_lane = tmem_base + slot * kSlotCols + ((uint32_t)(quad * 32) << 16);
+        const uint32_t span = (uint32_t)(P.left + P.right);
+        const int c0 = quad * 32;             // first column of this warp's band chunks
+        bool ok = true;
+        for (uint32_t i = slot; ok && i < n_mine; i += 2) {
+            const uint32_t u = i >> 1;
+            const uint32_t L = blockIdx.x + i * G;
+            const int hh = L % HHu, b = L / (HHu * n_tiles);
+            const int q0 = (int)((L / HHu) % n_tiles) * kTQ;
+            const int start = (q0 + P.off1 - P.left) - P.cl;
+            const bool edge = start < P.key_lo || start + KT > P.key_hi;   // some columns lie outside the key line
+            if (!(ok = ptx::mbar_wait(s_ready + slot, u & 1))) break;
+            tc_fence_after();
+            // Columns of this row that count: its band, cut to the keys that exist.  n_ok = 0: none.
+            int lo = r + P.cl, hi = r + P.cl + (int)span;
+            if (edge) {
+                lo = max(lo, P.key_lo - start);
+                hi = min(hi, P.key_hi - 1 - start);
+            }
+            const uint32_t n_ok = (uint32_t)max(0, hi - lo + 1);
+            // chunk ch (columns c0 + 32 ch ...) lies inside the band of every row of this warp iff
+            // 32 ch >= cl + 31 and 32 ch + 31 <= cl + span; such a chunk needs no mask
+            const int ch_free_lo = (P.cl + 31 + 31) >> 5, ch_free_hi = edge ? -1 : ((P.cl + (int)span - 31) >> 5);
+            // ---- pass 1: the row maximum over the band ----
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+            for (int ch = 0; ch < NCH; ++ch) {
+                uint32_t sraw[32];
+                tmem_ld32(t_lane + c0 + 32 * ch, sraw);
+                if (ch < ch_free_lo || ch > ch_free_hi) {
+                    const int d = c0 + 32 * ch - lo;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        if ((uint32_t)(d + e) >= n_ok) sraw[e] = 0xff800000u;   // -inf
+                }
+#pragma unroll
+                for (int e = 0; e < 32; e += 8) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        mx[q] = max3(mx[q], __uint_as_float(sraw[e + 2 * q]), __uint_as_float(sraw[e + 2 * q + 1]));
+                }
+            }
+            const float m = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            const float mus = (m == -INFINITY ? 0.f : m) * P.sl2;
+            // ---- pass 2: the weights, packed two to a column, stored as P over columns [0, KT/2) of this
+            // lane.  P column j holds keys 2j, 2j + 1 of the item, so the pairs of chunk ch go to the 16
+            // columns at 16 (quad + ch): always below the scores this thread has still to read.
+#pragma unroll 1
+            for (int ch = 0; ch < NCH; ++ch) {
+                uint32_t sraw[32];
+                tmem_ld32(t_lane + c0 + 32 * ch, sraw);
+                if (ch < ch_free_lo || ch > ch_free_hi) {
+                    const int d = c0 + 32 * ch - lo;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        if ((uint32_t)(d + e) >= n_ok) sraw[e] = 0xff800000u;
+                }
+                uint32_t pk[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    float x0, x1;
+                    ffma2(x0, x1, __uint_as_float(sraw[2 * e]), __uint_as_float(sraw[2 * e + 1]), P.sl2, -mus);
+                    pk[e] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
+                }
+                tmem_st16(t_lane + 16 * (quad + ch), pk);
+            }
+            // zeros in the P columns outside the band (the scores there belong to other rows' bands)
+            {
+                uint32_t z[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) z[e] = 0u;
+#pragma unroll 1
+                for (int piece = 0; piece < KT / 32; ++piece)
+                    if (piece < quad || piece >= quad + NCH) tmem_st16(t_lane + 16 * piece, z);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(p_ready + slot);
+
+            // ---- the finished row: O and its sum ----
+            if (!(ok = ptx::mbar_wait(o_ready + slot, u & 1))) break;
+            tc_fence_after();
+            float o[64], l_run;
+            tmem_ld64_and_1(t_lane + KT / 2, o, t_lane + KT / 2 + 64, l_run);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(slot_free + slot);   // the slot may take the scores of item i + 2
+            // normalise, stage the tile (128-byte swizzled rows, as the bulk store expects), store it
+            {
+                const float inv = l_run > 0.f ? __frcp_rn(l_run) : 0.f;
+                uint8_t *so = sOut + slot * C::kOutBytes;
+                // the bulk store of this slot's previous tile has finished reading the staging rows
+                // (every hand-over is an mbarrier with a bounded wait, never a bar.sync: a warp that gave
+                // up on a wait must not leave the others stuck)
+                if (u >= 1) {
+                    if (quad == 0 && lane == 0) {
+                        ptx::tma_store_wait_read();
+                        ptx::mbar_arrive(out_free + slot);
+                    }
+                    if (!(ok = ptx::mbar_wait(out_free + slot, (u - 1) & 1))) break;
+                }
+                uint8_t *row = so + r * kRowBytes;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    uint4 v;
+                    v.x = ptx::Mma<T>::pack(o[8 * q] * inv, o[8 * q + 1] * inv);
+                    v.y = ptx::Mma<T>::pack(o[8 * q + 2] * inv, o[8 * q + 3] * inv);
+                    v.z = ptx::Mma<T>::pack(o[8 * q + 4] * inv, o[8 * q + 5] * inv);
+                    v.w = ptx::Mma<T>::pack(o[8 * q + 6] * inv, o[8 * q + 7] * inv);
+                    *reinterpret_cast<uint4 *>(row + ((q ^ (r & 7)) << 4)) = v;
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(out_full + slot);
+                if (quad == 0 && lane == 0) {
+                    if (!ptx::mbar_wait(out_full + slot, u & 1)) {
+                        ok = false;
+                    } else {
+                        ptx::tma_store_4d(&maps.o, so, 0, hh, q0, b);   // rows past the sequence end are clipped
+                        ptx::tma_store_commit();
+                    }
+                }
+            }
+        }
+        if (quad == 0 && lane == 0) ptx::tma_store_wait_all();
+        if (!ok) atomicExch(&g_band_status, 1);
+    }
+    // every role has left its loop (each of its waits is bounded): free the tensor memory
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kSoftmaxWarps) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 2 * kSlotCols);
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+
+template <typename T, int KT>
+int launch_band(const Problem &p, const BandParams &bp_in, int64_t dil) {
+    BandParams bp = bp_in;
+    BandMaps m;
+    const int64_t HH = bp.HH;
+    if (int rc = make_row_tensor_map(&m.q, p.q, p.dtype, HH, p.Sq / dil, p.B, kTQ)) return rc;
+    if (int rc = make_row_tensor_map(&m.k, p.k, p.dtype, HH, p.Skv / dil, p.B, KT)) return rc;
+    if (int rc = make_row_tensor_map(&m.v, p.v, p.dtype, HH, p.Skv / dil, p.B, KT)) return rc;
+    if (int rc = make_row_tensor_map(&m.o, p.o, p.dtype, HH, p.Sq / dil, p.B, kTQ)) return rc;
+    if (int rc = make_row_tensor_map(&m.k_own, p.k, p.dtype, HH, p.Skv / dil, p.B, 16)) return rc;
+    if (int rc = make_row_tensor_map(&m.v_own, p.v, p.dtype, HH, p.Skv / dil, p.B, 16)) return rc;
+    m.k_prev = m.k_next = m.k_own;
+    m.v_prev = m.v_next = m.v_own;
+    if (p.k_prev) {
+        if (int rc = make_row_tensor_map(&m.k_prev, p.k_prev, p.dtype, HH, p.S_prev / dil, p.B, 16)) return rc;
+        if (int rc = make_row_tensor_map(&m.v_prev, p.v_prev, p.dtype, HH, p.S_prev / dil, p.B, 16)) return rc;
+    }
+    if (p.k_next) {
+        if (int rc = make_row_tensor_map(&m.k_next, p.k_next, p.dtype, HH, p.S_next / dil, p.B, 16)) return rc;
+        if (int rc = make_row_tensor_map(&m.v_next, p.v_next, p.dtype, HH, p.S_next / dil, p.B, 16)) return rc;
+    }
+    auto kern = umma_band_kernel<T, KT>;
+    constexpr size_t smem = BandCfg<KT>::kSmemBytes;
+    if (int rc = ensure_dynamic_smem((const void *)kern, smem, "cudaFuncSetAttribute(umma_band_kernel)")) return rc;
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return cuda_fail(e, "sizing the persistent grid");
+    const unsigned grid = (unsigned)std::min<uint64_t>(bp.n_items, (uint64_t)sms);   // one CTA per SM: it owns the SM's tensor memory
+    kern<<<grid, kThreads, smem, p.stream>>>(m, bp);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "umma_band_kernel launch");
+    note_kernel("umma_band");
+    return MAT_OK;
+}
+
+// Fills bp and returns the key-range width (192 or 256), or 0 when the window does not fit.
+int plan_band(const Problem &p, BandParams &bp) {
+    const int64_t dil = p.pat.dilation;
+    bp.Sq1 = (int32_t)(p.Sq / dil);
+    bp.Skv1 = (int32_t)(p.Skv / dil);
+    bp.off1 = (int32_t)(p.pat.q_offset / dil);
+    bp.prev_rows = p.k_prev ? (int32_t)(p.S_prev / dil) : 0;
+    const int32_t next_rows = p.k_next ? (int32_t)(p.S_next / dil) : 0;
+    bp.key_lo = -bp.prev_rows;
+    bp.key_hi = bp.Skv1 + next_rows;
+    bp.left = (int32_t)std::min<int64_t>(p.pat.left, bp.Skv1 + bp.prev_rows);
+    bp.right = (int32_t)std::min<int64_t>(p.pat.right, bp.Skv1 + next_rows);
+    bp.cl = (((bp.off1 - bp.left) % 16) + 16) % 16;
+    bp.HH = (int32_t)(p.H * dil);
+    bp.n_tiles = (bp.Sq1 + kTQ - 1) / kTQ;
+    bp.sl2 = p.scale * 1.4426950408889634f;
+    const uint64_t items = (uint64_t)p.B * bp.n_tiles * bp.HH;
+    if (items >= (1ull << 31)) return 0;
+    bp.n_items = (uint32_t)items;
+    const int need = bp.cl + bp.left + bp.right + kTQ;   // columns from row 0's first key to row 127's last
+    return need <= 192 ? 192 : need <= 256 ? 256 : 0;
+}
+
+}  // namespace
+
+// Windows of at most 128 taps between their two sides on 16-bit inputs with head width 64.
+// MAT_WINDOW_KERNEL=mma keeps them on the warp-level kernels (debugging and measurement aid).
+bool umma_band_supports(const Problem &p) {
+    if (p.pat.kind != MAT_WINDOW) return false;
+    if (p.dtype != MAT_BF16 && p.dtype != MAT_F16) return false;
+    if (p.D != 64) return false;
+    const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
+    if (al % 16) return false;
+    const int64_t dil = p.pat.dilation;
+    if (p.Sq % dil || p.Skv % dil || p.pat.q_offset % dil) return false;
+    if (p.Skv / dil >= (1LL << 28) || p.H * dil >= (1LL << 24) || p.B > 65535) return false;
+    const char *force = std::getenv("MAT_WINDOW_KERNEL");
+    if (force && std::strcmp(force, "mma") == 0) return false;
+    BandParams bp;
+    return plan_band(p, bp) != 0;
+}
+
+int launch_umma_band(const Problem &p) {
+    BandParams bp;
+    const int kt = plan_band(p, bp);
+    if (kt == 0) return fail(MAT_ERR_UNSUPPORTED, "window too wide for the band kernel");
+    const int64_t dil = p.pat.dilation;
+    if (p.dtype == MAT_BF16)
+        return kt == 192 ? launch_band<__nv_bfloat16, 192>(p, bp, dil) : launch_band<__nv_bfloat16, 256>(p, bp, dil);
+    return kt == 192 ? launch_band<__half, 192>(p, bp, dil) : launch_band<__half, 256>(p, bp, dil);
+}
+
+int band_status_read_and_clear(int *out) {
+    int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_band_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_band_status, &zero, sizeof(int));
+    return e == cudaSuccess ? MAT_OK : cuda_fail(e, "reading the kernel status word");
+}
+
+}  // namespace mat

@@ -52,16 +52,26 @@ def check_close(got: torch.Tensor, want: np.ndarray, dtype):
         assert e <= tol, f"max-abs {e:.3e} > {tol}"
 
 
-def expected_window_kernel(spec: PatternSpec, Skv: int) -> str:
+def expected_window_kernel(spec: PatternSpec, Skv: int, neighbours: bool = False) -> str:
     """Which kernel family the library picks for a 16-bit, D = 64 window call it can tile (the routing
-    of run_problem): dense and windows of more than 128 taps on tcgen05 when the sequence is long
-    enough and the shard offset is a multiple of 64, the warp-level tiled kernel otherwise."""
+    of run_problem): dense and windows of more than 128 taps on the tcgen05 walk when the sequence is long
+    enough and the shard offset is a multiple of 64; windows of at most 128 taps on the persistent
+    tcgen05 band kernel; the warp-level tiled kernel otherwise.  ``neighbours``: the call reads halo rows
+    from neighbouring shards' tensors (only the band and the warp-level kernels do)."""
+    dil = spec.dilation
     left, right = min(spec.left, Skv - 1), min(spec.right, Skv - 1)
-    if spec.dilation != 1 or spec.q_offset % 64 or Skv < 256:
-        return "mma_window"
-    if left >= Skv - 1 and (right >= Skv - 1 or right == 0):
-        return "umma_dense"
-    return "umma_window" if left + right > 128 else "mma_window"
+    if dil == 1 and spec.q_offset % 64 == 0 and Skv >= 256 and not neighbours:
+        if left >= Skv - 1 and (right >= Skv - 1 or right == 0):
+            return "umma_dense"
+        if left + right > 128:
+            return "umma_window"
+    skv1 = Skv // dil
+    reach = 2 * skv1 if neighbours else skv1           # taps clamp to the keys that exist (own rows plus a neighbour's)
+    l1, r1 = min(spec.left, reach), min(spec.right, reach)
+    cl = (spec.q_offset // dil - l1) % 16
+    if cl + l1 + r1 <= 128:
+        return "umma_band"
+    return "mma_window"
 
 
 def orderbook_reference_forward(model, ticks: torch.Tensor) -> torch.Tensor:

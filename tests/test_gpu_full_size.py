@@ -47,7 +47,7 @@ def test_cfg2_full_size_every_row():
     spec = PatternSpec.causal_window(64)
     q, k, v = seeded_qkv(2, 1, 65536, 8, 64, torch.bfloat16, scale=0.5)
     got = _run(spec, q, k, v)
-    assert nat.last_kernel() == "mma_window"
+    assert nat.last_kernel() == "umma_band"
     want = oracle_out(q, k, v, spec)
     assert np.isfinite(got).all()
     e = float(np.abs(got - want).max())
@@ -59,7 +59,7 @@ def test_cfg2_shape_reference_default_window_every_row():
     spec = PatternSpec.sliding_window(64)
     q, k, v = seeded_qkv(6, 1, 65536, 8, 64, torch.bfloat16, scale=0.5)
     got = _run(spec, q, k, v)
-    assert nat.last_kernel() == "mma_window"
+    assert nat.last_kernel() == "umma_band"
     want = oracle_out(q, k, v, spec)
     e = float(np.abs(got - want).max())
     assert e <= BF16_ABS, (e, _worst_rows(got, want))
@@ -105,7 +105,7 @@ def test_cfg5_attention_full_size_every_row():
     spec = PatternSpec.causal_window(64, dilation=2)
     q, k, v = seeded_qkv(5, 16, 8192, 4, 64, torch.bfloat16)
     got = _run(spec, q, k, v)
-    assert nat.last_kernel() == "mma_window"
+    assert nat.last_kernel() == "umma_band"
     want = oracle_out(q, k, v, spec)
     e = float(np.abs(got - want).max())
     assert e <= BF16_ABS, (e, _worst_rows(got, want))

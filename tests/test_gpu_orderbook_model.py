@@ -21,7 +21,7 @@ def test_orderbook_forward_matches_fp32_reference():
         got32 = model.cuda()(ticks.cuda())
         assert nat.last_kernel() == "rowwarp"                                   # fp32: the general kernel
         got16 = model.to(torch.bfloat16)(ticks.cuda().to(torch.bfloat16))
-        assert nat.last_kernel() == "mma_window"                                # bf16: the tiled window kernel
+        assert nat.last_kernel() == "umma_band"                                 # bf16: the tcgen05 band kernel
     assert got32.shape == (2, 3)
     assert (got32.cpu() - want).abs().max() <= 2e-3 * max(1.0, float(want.abs().max()))
     # bf16 weights and activations through 4 layers: compare loosely, relative to the logits' scale

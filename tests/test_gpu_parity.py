@@ -100,7 +100,7 @@ def test_wide_windows_on_tcgen05(spec, B, S, H):
     for dtype in (torch.bfloat16, torch.float16):
         q, k, v = seeded_qkv(15, B, S, H, 64, dtype)
         got = run(spec, q, k, v)
-        assert nat.last_kernel() == expected_window_kernel(spec, S) != "mma_window"
+        assert nat.last_kernel() == expected_window_kernel(spec, S) in ("umma_window", "umma_dense", "umma_band")
         check_close(got, oracle_out(q, k, v, spec), dtype)
 
 
@@ -140,7 +140,7 @@ def test_mma_window_dilated(spec0, dil):
     S = 96 * dil
     q, k, v = seeded_qkv(12, 2, S, 2, 64, torch.bfloat16)
     got = run(spec, q, k, v)
-    assert nat.last_kernel() == "mma_window"
+    assert nat.last_kernel() == "umma_band"
     check_close(got, oracle_out(q, k, v, spec), torch.bfloat16)
     # ragged against the dilation: the general kernel takes over, same answer
     q, k, v = seeded_qkv(13, 1, S + 1, 2, 64, torch.bfloat16)
@@ -154,7 +154,7 @@ def test_cfg2_shape_reduced_length_bf16():
     spec = PatternSpec.causal_window(64)
     q, k, v = seeded_qkv(2, 1, 4096, 8, 64, torch.bfloat16, scale=0.5)
     check_close(run(spec, q, k, v), oracle_out(q, k, v, spec), torch.bfloat16)
-    assert nat.last_kernel() == "mma_window"
+    assert nat.last_kernel() == "umma_band"
 
 
 def test_large_magnitudes_stay_finite():
@@ -211,7 +211,7 @@ def test_neighbour_shards_read_in_place(spec, B):
         next_kv = parts[r + 1][1:] if r < P - 1 and spec.right else None
         out = ext.forward_sharded(qr, kr, vr, spec, prev_kv, next_kv)
         torch.cuda.synchronize()
-        assert nat.last_kernel() == "mma_window"
+        assert nat.last_kernel() == expected_window_kernel(spec, chunk, neighbours=True)
         check_close(out, want[:, r * chunk:(r + 1) * chunk], torch.bfloat16)
 
 
@@ -447,7 +447,7 @@ def test_cfg2_full_size_properties():
     spec = PatternSpec.causal_window(64)
     q, k, v = (t.to(DEV) for t in seeded_qkv(2, B, S, H, D, torch.bfloat16, scale=0.5))
     out = ext.forward_pattern(q, k, v, spec)
-    assert nat.last_kernel() == "mma_window"
+    assert nat.last_kernel() == "umma_band"
     assert torch.isfinite(out.float()).all()
     # (a) linear in V: doubling V doubles the output exactly (power of two)
     assert torch.equal(ext.forward_pattern(q, k, v * 2, spec), out * 2)
