@@ -42,6 +42,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     objdir = CSRC / "build"
     objdir.mkdir(exist_ok=True)
     extra = ["-Xptxas", "-v"] if verbose else []
+    extra += os.environ.get("MAT_EXTRA_NVCC_FLAGS", "").split()   # e.g. -DMAT_BAND_TRACE for a timeline build
 
     def compile_one(src: Path) -> Path:
         obj = objdir / (src.stem + ".o")

@@ -58,9 +58,19 @@ constexpr int kTQ = 128;          // query rows per item
 constexpr int kSumN = 16;         // extra B columns of the P V product: a block of ones
 constexpr int kSlotCols = 256;    // TMEM columns per slot
 constexpr int kSoftmaxWarps = 8;  // four per slot
-constexpr int kThreads = (kSoftmaxWarps + 3) * 32;   // + one MMA warp per slot + the TMA warp
+constexpr int kEpilogueWarp0 = kSoftmaxWarps + 3;   // warps 11..14: warp w reads the TMEM lanes of quarter w % 4
+constexpr int kThreads = (kSoftmaxWarps + 3 + 4) * 32;   // + one MMA warp per slot + the TMA warp + four epilogue warps
 
 __device__ int g_band_status = 0;
+
+// Timeline of the first items of CTA 0 (build with -DMAT_BAND_TRACE; read with mat_debug_band_trace):
+// slot [role][item][event] = %globaltimer at that point.  Compiled out otherwise.
+#ifdef MAT_BAND_TRACE
+__device__ unsigned long long g_trace[3 * 24 * 8];
+#define TR(role, item, ev) do { if (blockIdx.x == 0 && (item) < 24) g_trace[((role) * 24 + (item)) * 8 + (ev)] = ptx::global_ns(); } while (0)
+#else
+#define TR(role, item, ev) do { } while (0)
+#endif
 
 struct BandParams {
     int32_t Sq1, Skv1, off1;       // query rows, key rows and q_offset of one sub-sequence
@@ -171,6 +181,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                     atomicExch(&g_band_status, 1);
                     break;
                 }
+                TR(0, it, 0);
                 uint8_t *dq = sQK + sq * C::kQKBytes;
                 ptx::mbar_expect_tx(qk_full + sq, C::kQKBytes);
                 ptx::tma_load_4d(dq, &maps.q, qk_full + sq, 0, hh, q0, b);
@@ -179,137 +190,28 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                     atomicExch(&g_band_status, 1);
                     break;
                 }
+                TR(0, it, 1);
                 ptx::mbar_expect_tx(v_full + sv, C::kVBytes);
                 load_rows(sV + sv * C::kVBytes, v_full + sv, &maps.v, &maps.v_own, &maps.v_prev, &maps.v_next);
             }
         }
-    } else if (warp >= kSoftmaxWarps) {
-        // ================= MMA lanes, one per slot: S(i), then [O | l](i) once the weights are stored =================
-        // (two issuing lanes: an instruction costs its issuer about 125 cycles whatever its shape, and a slot's
-        // 4 + KT/16 instructions per item would otherwise sit on the other slot's critical path)
-        if (lane == 0) {
-            const int slot = warp - kSoftmaxWarps;
-            const uint32_t idesc_s = instr_desc<T>(false, KT), idesc_pv = instr_desc<T>(true, 64 + kSumN);
-            const uint32_t qk_addr = ptx::smem_u32(sQK), v_addr0 = ptx::smem_u32(sV), ones_addr = ptx::smem_u32(sOnes);
-            const uint32_t ts = tmem_base + slot * kSlotCols;      // S, then P in its columns [0, KT/2)
-            const uint32_t td = ts + KT / 2;                       // [O | l]: 80 columns behind P
-            bool ok = true;
-            for (uint32_t i = slot; ok && i < n_mine; i += 2) {
-                const int sq = i % NQK, sv = i % NV;
-                if (!(ok = ptx::mbar_wait(qk_full + sq, (i / NQK) & 1))) break;
-                // the slot's previous item (i - 2) has been read out by its softmax warps
-                if (i >= 2 && !(ok = ptx::mbar_wait(slot_free + slot, ((i >> 1) - 1) & 1))) break;
-                tc_fence_after();
-                const uint64_t dq = smem_desc(qk_addr + sq * C::kQKBytes);
-                const uint64_t dk = smem_desc(qk_addr + sq * C::kQKBytes + kTQ * kRowBytes);
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks)   // 16 of the 64 head columns per instruction (32 bytes along a row)
-                    umma_f16_ss(ts, dq + ks * 2, dk + ks * 2, idesc_s, ks > 0);
-                umma_commit(s_ready + slot);
-                umma_commit(qk_empty + sq);
-                if (!(ok = ptx::mbar_wait(v_full + sv, (i / NV) & 1))) break;
-                if (!(ok = ptx::mbar_wait(p_ready + slot, (i >> 1) & 1))) break;   // P(i) is in TMEM
-                tc_fence_after();
-                const uint32_t v_addr = v_addr0 + sv * C::kVBytes;
-#pragma unroll
-                for (int ks = 0; ks < KT / 16; ++ks) {
-                    // B = 16 keys x 80 columns: the 64 head columns from the V stage, then a second 64-wide
-                    // block (16 of it used) that the leading-dimension offset points at the ones
-                    const uint32_t vk = v_addr + ks * 16 * kRowBytes;
-                    umma_f16_ta(td, ts + ks * 8, smem_desc(vk, (ones_addr - vk) >> 4), idesc_pv, ks > 0);
-                }
-                umma_commit(o_ready + slot);
-                umma_commit(v_empty + sv);
-            }
-            if (!ok) atomicExch(&g_band_status, 1);
-        }
-    } else {
-        // ================= softmax warps: thread r owns query row r of its slot's item =================
-        const int slot = warp >> 2, quad = warp & 3;
+    } else if (warp >= kEpilogueWarp0) {
+        // ================= epilogue warps: the finished rows of every item, both slots in turn =================
+        // (their own warps, so that the softmax warps of a slot go straight on to the slot's next item)
+        const int quad = warp & 3;
         const int r = quad * 32 + lane;
-        const uint32_t t_lane = tmem_base + slot * kSlotCols + ((uint32_t)(quad * 32) << 16);
-        const uint32_t span = (uint32_t)(P.left + P.right);
-        const int c0 = quad * 32;             // first column of this warp's band chunks
         bool ok = true;
-        for (uint32_t i = slot; ok && i < n_mine; i += 2) {
+        for (uint32_t i = 0; ok && i < n_mine; ++i) {
+            const int slot = i & 1;
             const uint32_t u = i >> 1;
             const uint32_t L = blockIdx.x + i * G;
             const int hh = L % HHu, b = L / (HHu * n_tiles);
             const int q0 = (int)((L / HHu) % n_tiles) * kTQ;
-            const int start = (q0 + P.off1 - P.left) - P.cl;
-            const bool edge = start < P.key_lo || start + KT > P.key_hi;   // some columns lie outside the key line
-            if (!(ok = ptx::mbar_wait(s_ready + slot, u & 1))) break;
-            tc_fence_after();
-            // Columns of this row that count: its band, cut to the keys that exist.  n_ok = 0: none.
-            int lo = r + P.cl, hi = r + P.cl + (int)span;
-            if (edge) {
-                lo = max(lo, P.key_lo - start);
-                hi = min(hi, P.key_hi - 1 - start);
-            }
-            const uint32_t n_ok = (uint32_t)max(0, hi - lo + 1);
-            // chunk ch (columns c0 + 32 ch ...) lies inside the band of every row of this warp iff
-            // 32 ch >= cl + 31 and 32 ch + 31 <= cl + span; such a chunk needs no mask
-            const int ch_free_lo = (P.cl + 31 + 31) >> 5, ch_free_hi = edge ? -1 : ((P.cl + (int)span - 31) >> 5);
-            // ---- pass 1: the row maximum over the band ----
-            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-            for (int ch = 0; ch < NCH; ++ch) {
-                uint32_t sraw[32];
-                tmem_ld32(t_lane + c0 + 32 * ch, sraw);
-                if (ch < ch_free_lo || ch > ch_free_hi) {
-                    const int d = c0 + 32 * ch - lo;
-#pragma unroll
-                    for (int e = 0; e < 32; ++e)
-                        if ((uint32_t)(d + e) >= n_ok) sraw[e] = 0xff800000u;   // -inf
-                }
-#pragma unroll
-                for (int e = 0; e < 32; e += 8) {
-#pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        mx[q] = max3(mx[q], __uint_as_float(sraw[e + 2 * q]), __uint_as_float(sraw[e + 2 * q + 1]));
-                }
-            }
-            const float m = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            const float mus = (m == -INFINITY ? 0.f : m) * P.sl2;
-            // ---- pass 2: the weights, packed two to a column, stored as P over columns [0, KT/2) of this
-            // lane.  P column j holds keys 2j, 2j + 1 of the item, so the pairs of chunk ch go to the 16
-            // columns at 16 (quad + ch): always below the scores this thread has still to read.
-#pragma unroll 1
-            for (int ch = 0; ch < NCH; ++ch) {
-                uint32_t sraw[32];
-                tmem_ld32(t_lane + c0 + 32 * ch, sraw);
-                if (ch < ch_free_lo || ch > ch_free_hi) {
-                    const int d = c0 + 32 * ch - lo;
-#pragma unroll
-                    for (int e = 0; e < 32; ++e)
-                        if ((uint32_t)(d + e) >= n_ok) sraw[e] = 0xff800000u;
-                }
-                uint32_t pk[16];
-#pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    float x0, x1;
-                    ffma2(x0, x1, __uint_as_float(sraw[2 * e]), __uint_as_float(sraw[2 * e + 1]), P.sl2, -mus);
-                    pk[e] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
-                }
-                tmem_st16(t_lane + 16 * (quad + ch), pk);
-            }
-            // zeros in the P columns outside the band (the scores there belong to other rows' bands)
-            {
-                uint32_t z[16];
-#pragma unroll
-                for (int e = 0; e < 16; ++e) z[e] = 0u;
-#pragma unroll 1
-                for (int piece = 0; piece < KT / 32; ++piece)
-                    if (piece < quad || piece >= quad + NCH) tmem_st16(t_lane + 16 * piece, z);
-            }
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(p_ready + slot);
-
+            const uint32_t t_lane = tmem_base + slot * kSlotCols + ((uint32_t)(quad * 32) << 16);
             // ---- the finished row: O and its sum ----
             if (!(ok = ptx::mbar_wait(o_ready + slot, u & 1))) break;
             tc_fence_after();
+            if (r == 0) TR(2, i, 3);
             float o[64], l_run;
             tmem_ld64_and_1(t_lane + KT / 2, o, t_lane + KT / 2 + 64, l_run);
             tc_fence_before();
@@ -329,6 +231,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                     }
                     if (!(ok = ptx::mbar_wait(out_free + slot, (u - 1) & 1))) break;
                 }
+                if (r == 0) TR(2, i, 4);
                 uint8_t *row = so + r * kRowBytes;
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
@@ -349,10 +252,182 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                         ptx::tma_store_4d(&maps.o, so, 0, hh, q0, b);   // rows past the sequence end are clipped
                         ptx::tma_store_commit();
                     }
+                    TR(2, i, 5);
                 }
             }
         }
         if (quad == 0 && lane == 0) ptx::tma_store_wait_all();
+        if (!ok) atomicExch(&g_band_status, 1);
+    } else if (warp >= kSoftmaxWarps) {
+        // ================= MMA lanes, one per slot: S(i), then [O | l](i) once the weights are stored =================
+        // (two issuing lanes: an instruction costs its issuer about 125 cycles whatever its shape, and a slot's
+        // 4 + KT/16 instructions per item would otherwise sit on the other slot's critical path)
+        if (lane == 0) {
+            const int slot = warp - kSoftmaxWarps;
+            const uint32_t idesc_s = instr_desc<T>(false, KT), idesc_pv = instr_desc<T>(true, 64 + kSumN);
+            const uint32_t qk_addr = ptx::smem_u32(sQK), v_addr0 = ptx::smem_u32(sV), ones_addr = ptx::smem_u32(sOnes);
+            const uint32_t ts = tmem_base + slot * kSlotCols;      // S, then P in its columns [0, KT/2)
+            const uint32_t td = ts + KT / 2;                       // [O | l]: 80 columns behind P
+            bool ok = true;
+            for (uint32_t i = slot; ok && i < n_mine; i += 2) {
+                const int sq = i % NQK, sv = i % NV;
+                TR(1, i, 0);
+                if (!(ok = ptx::mbar_wait(qk_full + sq, (i / NQK) & 1))) break;
+                TR(1, i, 1);
+                // the slot's previous item (i - 2) has been read out by its softmax warps
+                if (i >= 2 && !(ok = ptx::mbar_wait(slot_free + slot, ((i >> 1) - 1) & 1))) break;
+                tc_fence_after();
+                TR(1, i, 2);
+                const uint64_t dq = smem_desc(qk_addr + sq * C::kQKBytes);
+                const uint64_t dk = smem_desc(qk_addr + sq * C::kQKBytes + kTQ * kRowBytes);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)   // 16 of the 64 head columns per instruction (32 bytes along a row)
+                    umma_f16_ss(ts, dq + ks * 2, dk + ks * 2, idesc_s, ks > 0);
+                umma_commit(s_ready + slot);
+                umma_commit(qk_empty + sq);
+                TR(1, i, 3);
+                if (!(ok = ptx::mbar_wait(v_full + sv, (i / NV) & 1))) break;
+                TR(1, i, 4);
+                if (!(ok = ptx::mbar_wait(p_ready + slot, (i >> 1) & 1))) break;   // P(i) is in TMEM
+                tc_fence_after();
+                TR(1, i, 5);
+                const uint32_t v_addr = v_addr0 + sv * C::kVBytes;
+#pragma unroll
+                for (int ks = 0; ks < KT / 16; ++ks) {
+                    // B = 16 keys x 80 columns: the 64 head columns from the V stage, then a second 64-wide
+                    // block (16 of it used) that the leading-dimension offset points at the ones
+                    const uint32_t vk = v_addr + ks * 16 * kRowBytes;
+                    umma_f16_ta(td, ts + ks * 8, smem_desc(vk, (ones_addr - vk) >> 4), idesc_pv, ks > 0);
+                }
+                umma_commit(o_ready + slot);
+                umma_commit(v_empty + sv);
+                TR(1, i, 6);
+            }
+            if (!ok) atomicExch(&g_band_status, 1);
+        }
+    } else {
+        // ================= softmax warps: thread r owns query row r of its slot's item =================
+        const int slot = warp >> 2, quad = warp & 3;
+        const int r = quad * 32 + lane;
+        const uint32_t t_lane = tmem_base + slot * kSlotCols + ((uint32_t)(quad * 32) << 16);
+        const uint32_t span = (uint32_t)(P.left + P.right);
+        const int c0 = quad * 32;             // first column of this warp's band chunks
+        bool ok = true;
+        for (uint32_t i = slot; ok && i < n_mine; i += 2) {
+            const uint32_t u = i >> 1;
+            const uint32_t L = blockIdx.x + i * G;
+            const int hh = L % HHu, b = L / (HHu * n_tiles);
+            const int q0 = (int)((L / HHu) % n_tiles) * kTQ;
+            const int start = (q0 + P.off1 - P.left) - P.cl;
+            const bool edge = start < P.key_lo || start + KT > P.key_hi;   // some columns lie outside the key line
+            if (r == 0) TR(2, i, 0);
+            if (!(ok = ptx::mbar_wait(s_ready + slot, u & 1))) break;
+            tc_fence_after();
+            if (r == 0) TR(2, i, 1);
+            // Columns of this row that count: its band, cut to the keys that exist.  n_ok = 0: none.
+            int lo = r + P.cl, hi = r + P.cl + (int)span;
+            if (edge) {
+                lo = max(lo, P.key_lo - start);
+                hi = min(hi, P.key_hi - 1 - start);
+            }
+            const uint32_t n_ok = (uint32_t)max(0, hi - lo + 1);
+            // chunk ch (columns c0 + 32 ch ...) lies inside the band of every row of this warp iff
+            // 32 ch >= cl + 31 and 32 ch + 31 <= cl + span; such a chunk needs no mask
+            const int ch_free_lo = (P.cl + 31 + 31) >> 5, ch_free_hi = edge ? -1 : ((P.cl + (int)span - 31) >> 5);
+            // mask of one 32-column chunk (skipped when the chunk lies inside every row's band), its share of
+            // the row maximum, and its weights: packed two to a column and stored as P over columns [0, KT/2)
+            // of this lane.  P column j holds keys 2j, 2j + 1 of the item, so the pairs of chunk ch go to the
+            // 16 columns at 16 (quad + ch): always below the scores this thread has still to read.
+            auto mask_chunk = [&](uint32_t (&sr)[32], int ch) {
+                if (ch < ch_free_lo || ch > ch_free_hi) {
+                    const int d = c0 + 32 * ch - lo;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        if ((uint32_t)(d + e) >= n_ok) sr[e] = 0xff800000u;   // -inf
+                }
+            };
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            auto max_chunk = [&](const uint32_t (&sr)[32]) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 8) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        mx[q] = max3(mx[q], __uint_as_float(sr[e + 2 * q]), __uint_as_float(sr[e + 2 * q + 1]));
+                }
+            };
+            float mus = 0.f;
+            auto weights_chunk = [&](const uint32_t (&sr)[32], int ch) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    float x0, x1;
+                    ffma2(x0, x1, __uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1]), P.sl2, -mus);
+                    pk[e] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
+                }
+                tmem_st16(t_lane + 16 * (quad + ch), pk);
+            };
+            if constexpr (NCH == 3) {
+                // the whole band of a row fits the registers: one read of the scores
+                uint32_t s0[32], s1[32], s2[32];
+                tmem_ld32_issue(t_lane + c0, s0);
+                tmem_ld32_issue(t_lane + c0 + 32, s1);
+                tmem_ld32_issue(t_lane + c0 + 64, s2);
+                tmem_ld32_wait(s0);
+                mask_chunk(s0, 0);
+                max_chunk(s0);
+                tmem_ld32_wait(s1);
+                mask_chunk(s1, 1);
+                max_chunk(s1);
+                tmem_ld32_wait(s2);
+                mask_chunk(s2, 2);
+                max_chunk(s2);
+                const float m = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                mus = (m == -INFINITY ? 0.f : m) * P.sl2;
+                weights_chunk(s0, 0);
+                weights_chunk(s1, 1);
+                weights_chunk(s2, 2);
+            } else {
+                // two passes over the scores, the load of the next chunk in flight while one is worked on
+                uint32_t sa[32], sb[32];
+                tmem_ld32_issue(t_lane + c0, sa);
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch) {
+                    uint32_t (&cur)[32] = (ch & 1) ? sb : sa;
+                    uint32_t (&nxt)[32] = (ch & 1) ? sa : sb;
+                    tmem_ld32_wait(cur);
+                    tmem_ld32_issue(t_lane + c0 + 32 * ((ch + 1) % NCH), nxt);   // after the last chunk: chunk 0 again, for pass 2
+                    mask_chunk(cur, ch);
+                    max_chunk(cur);
+                }
+                const float m = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                mus = (m == -INFINITY ? 0.f : m) * P.sl2;
+#pragma unroll
+                for (int ch = 0; ch < NCH; ++ch) {
+                    // pass 1 ended on buffer (NCH - 1) & 1 and left chunk 0 loading into the other one
+                    uint32_t (&cur)[32] = ((ch + NCH) & 1) ? sb : sa;
+                    uint32_t (&nxt)[32] = ((ch + NCH) & 1) ? sa : sb;
+                    tmem_ld32_wait(cur);
+                    if (ch + 1 < NCH) tmem_ld32_issue(t_lane + c0 + 32 * (ch + 1), nxt);
+                    mask_chunk(cur, ch);
+                    weights_chunk(cur, ch);
+                }
+            }
+            // zeros in the P columns outside the band (the scores there belong to other rows' bands)
+            {
+                uint32_t z[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) z[e] = 0u;
+#pragma unroll 1
+                for (int piece = 0; piece < KT / 32; ++piece)
+                    if (piece < quad || piece >= quad + NCH) tmem_st16(t_lane + 16 * piece, z);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(p_ready + slot);
+            if (r == 0) TR(2, i, 2);
+
+        }
         if (!ok) atomicExch(&g_band_status, 1);
     }
     // every role has left its loop (each of its waits is bounded): free the tensor memory
@@ -455,6 +530,13 @@ int launch_umma_band(const Problem &p) {
     return kt == 192 ? launch_band<__half, 192>(p, bp, dil) : launch_band<__half, 256>(p, bp, dil);
 }
 
+}  // namespace mat
+#ifdef MAT_BAND_TRACE
+extern "C" int mat_debug_band_trace(unsigned long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, mat::g_trace, sizeof(mat::g_trace));
+}
+#endif
+namespace mat {
 int band_status_read_and_clear(int *out) {
     int zero = 0;
     cudaError_t e = cudaMemcpyFromSymbol(out, g_band_status, sizeof(int));
