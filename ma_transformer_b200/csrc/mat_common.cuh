@@ -70,6 +70,9 @@ int umma_status_read_and_clear(int *out);
 bool umma_band_supports(const Problem &p);   // umma_band.cu: windows of at most 128 taps, persistent, on tcgen05 / TMEM
 int launch_umma_band(const Problem &p);
 int band_status_read_and_clear(int *out);
+// first pass of a Longformer forward on the band kernel; kg, vg: the K/V rows at the global positions, gathered
+bool umma_band_longformer_supports(const Problem &p);
+int launch_umma_band_longformer(const Problem &p, const void *kg, const void *vg);
 // Longformer global-row pass on tcgen05 (umma_block.cu): how the key axis is split, and the launch
 constexpr int kPartialStride = 66;   // floats per row of a partial: max, sum, 64 outputs
 struct GlobalRowSplit {

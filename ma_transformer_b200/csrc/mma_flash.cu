@@ -774,7 +774,11 @@ int launch_t(const Problem &p) {
         // producer warp; otherwise the ring of stages
         const bool one_stage = fp.left + ((16 - fp.left % 16) % 16) + fp.right <= 128 && fp.n_global <= kSideRows &&
                                (fp.n_global == 0 || fp.kg) && (fp.Sq1 + 127) / 128 <= 65535;
-        if (one_stage) {
+        if (fp.kg && !p.shard_kg && umma_band_longformer_supports(p)) {
+            // at most 32 global positions and a window of at most 128 taps: the persistent tcgen05 band kernel,
+            // 96 query rows per item against 224 window keys and the gathered keys
+            if (int rc = launch_umma_band_longformer(p, fp.kg, fp.vg)) return rc;
+        } else if (one_stage) {
             if (int rc = launch_kind<T, MAT_LONGFORMER, 128, 256, 5, 1, false, 2>(p, fp, dil, "mma_longformer")) return rc;
         } else if (int rc = launch_kind<T, MAT_LONGFORMER, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_longformer")) return rc;
         if (fp.n_global == 0 || p.shard_kg) return MAT_OK;

@@ -81,30 +81,43 @@ struct BandParams {
     int32_t HH, n_tiles;
     uint32_t n_items;
     float sl2;                     // scale * log2(e)
+    // Longformer variant: the sorted global positions; every row attends them besides its window
+    int32_t n_global;
+    const int64_t *gidx;
 };
 
 struct BandMaps {
     CUtensorMap q, k, v, o;                                  // boxes of 128 (q, o) and KT rows
     CUtensorMap k_own, v_own, k_prev, v_prev, k_next, v_next;   // 16-row boxes for stages that cross a shard edge
+    CUtensorMap kg, vg;   // Longformer variant: the K/V rows at the global positions, [B, n_global, HH, 64], 32-row boxes
 };
+
+// Longformer variant: an item is 96 query rows, its key range 224 window keys followed by the (at most 32)
+// keys at the global positions, so that scores, weights and output still fit one 256-column slot and one
+// tcgen05.mma of N = 256 per slice.  The tile's rows 96..127 belong to the next item and are computed for nothing.
+constexpr int kLfRows = 96, kLfBand = 224, kLfGlobals = 32;
+constexpr int kNoGlobal = INT32_MIN;   // unused slot of the global-position list
 
 template <int KT> struct BandCfg {
     static constexpr int kNQK = 2;                   // {Q, K} stages
     static constexpr int kNV = KT == 192 ? 3 : 2;    // V stages (released later than K: after the P V product)
     static constexpr int kQKBytes = kTQ * kRowBytes + KT * kRowBytes;
     static constexpr int kVBytes = KT * kRowBytes;
-    static constexpr int kNCH = (KT - 96) / 32;      // 32-column chunks of a warp's band: 3 or 5
-    static constexpr int kBars = 2 * kNQK + 2 * kNV + 12;
+    static constexpr int kNCH = (KT - 96) / 32;      // 32-column chunks of a warp's band: 3 or 5 (Longformer: 5 and the globals)
+    static constexpr int kBars = 2 * kNQK + 2 * kNV + 12 + kLfGlobals / 2;   // (the global-position list sits behind the barriers)
     static constexpr int kOutBytes = kTQ * kRowBytes;   // one output tile per slot, staged for its bulk store
     static constexpr size_t kSmemBytes = 1024 + (size_t)kNQK * kQKBytes + (size_t)kNV * kVBytes + 2 * kOutBytes +
                                          kSumN * kRowBytes + kBars * 8 + 16;
 };
 
-template <typename T, int KT>
+template <typename T, int KT, bool LF>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
     using C = BandCfg<KT>;
     constexpr int NQK = C::kNQK, NV = C::kNV, NCH = C::kNCH;
+    static_assert(!LF || KT == 256, "the Longformer variant uses the 256-column slot");
+    constexpr int kRows = LF ? kLfRows : kTQ;       // query rows an item really owns
+    constexpr int kBandKT = LF ? kLfBand : KT;      // key rows of the window part of a stage
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *sQK = smem;                                  // stage s: Q at +0 (16 KB), K behind it
@@ -115,7 +128,8 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
     uint64_t *qk_full = bars, *qk_empty = qk_full + NQK, *v_full = qk_empty + NQK, *v_empty = v_full + NV;
     uint64_t *s_ready = v_empty + NV, *p_ready = s_ready + 2, *o_ready = p_ready + 2, *slot_free = o_ready + 2;
     uint64_t *out_full = slot_free + 2, *out_free = out_full + 2;   // the staged output tile of a slot
-    uint32_t *tmem_slot = (uint32_t *)(out_free + 2);
+    int32_t *sG = (int32_t *)(out_free + 2);             // Longformer variant: the global positions (kNoGlobal: unused)
+    uint32_t *tmem_slot = (uint32_t *)(sG + kLfGlobals);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -132,6 +146,8 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
         }
         ptx::fence_barrier_init();
     }
+    if (LF && threadIdx.x < kLfGlobals)
+        sG[threadIdx.x] = (int)threadIdx.x < P.n_global ? (int32_t)P.gidx[threadIdx.x] : kNoGlobal;
     if (threadIdx.x < kSumN * kRowBytes / 16) {
         const uint32_t one2 = ptx::Mma<T>::kOnes;
         reinterpret_cast<uint4 *>(sOnes)[threadIdx.x] = make_uint4(one2, one2, one2, one2);
@@ -156,16 +172,16 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
             for (uint32_t it = 0; it < n_mine; ++it) {
                 const uint32_t L = blockIdx.x + it * G;
                 const int hh = L % HHu, b = L / (HHu * n_tiles);
-                const int q0 = (int)((L / HHu) % n_tiles) * kTQ;
+                const int q0 = (int)((L / HHu) % n_tiles) * kRows;
                 const int start = (q0 + P.off1 - P.left) - P.cl;   // first key row of the item (a multiple of 16)
                 const int sq = it % NQK, sv = it % NV;
                 // a stage that crosses into a neighbour shard's rows is fetched 16 rows at a time, each
                 // piece from the tensor that owns it
-                const bool pieces = (start < 0 && P.key_lo < 0) || (start + KT > P.Skv1 && P.key_hi > P.Skv1);
+                const bool pieces = !LF && ((start < 0 && P.key_lo < 0) || (start + KT > P.Skv1 && P.key_hi > P.Skv1));
                 auto load_rows = [&](uint8_t *dst, uint64_t *bar, const CUtensorMap *whole, const CUtensorMap *own,
                                      const CUtensorMap *prev, const CUtensorMap *next) {
                     if (!pieces) {
-                        ptx::tma_load_4d(dst, whole, bar, 0, hh, start, b);
+                        ptx::tma_load_4d(dst, whole, bar, 0, hh, start, b);   // (Longformer variant: a box of 224 rows)
                         return;
                     }
                     for (int i = 0; i < KT / 16; ++i) {
@@ -186,6 +202,8 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                 ptx::mbar_expect_tx(qk_full + sq, C::kQKBytes);
                 ptx::tma_load_4d(dq, &maps.q, qk_full + sq, 0, hh, q0, b);
                 load_rows(dq + kTQ * kRowBytes, qk_full + sq, &maps.k, &maps.k_own, &maps.k_prev, &maps.k_next);
+                if (LF)   // the keys at the global positions behind the window keys (slots past the list: zeros)
+                    ptx::tma_load_4d(dq + (kTQ + kBandKT) * kRowBytes, &maps.kg, qk_full + sq, 0, hh, 0, b);
                 if (it >= (uint32_t)NV && !ptx::mbar_wait(v_empty + sv, (it / NV - 1) & 1)) {
                     atomicExch(&g_band_status, 1);
                     break;
@@ -193,6 +211,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                 TR(0, it, 1);
                 ptx::mbar_expect_tx(v_full + sv, C::kVBytes);
                 load_rows(sV + sv * C::kVBytes, v_full + sv, &maps.v, &maps.v_own, &maps.v_prev, &maps.v_next);
+                if (LF) ptx::tma_load_4d(sV + sv * C::kVBytes + kBandKT * kRowBytes, &maps.vg, v_full + sv, 0, hh, 0, b);
             }
         }
     } else if (warp >= kEpilogueWarp0) {
@@ -206,7 +225,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
             const uint32_t u = i >> 1;
             const uint32_t L = blockIdx.x + i * G;
             const int hh = L % HHu, b = L / (HHu * n_tiles);
-            const int q0 = (int)((L / HHu) % n_tiles) * kTQ;
+            const int q0 = (int)((L / HHu) % n_tiles) * kRows;
             const uint32_t t_lane = tmem_base + slot * kSlotCols + ((uint32_t)(quad * 32) << 16);
             // ---- the finished row: O and its sum ----
             if (!(ok = ptx::mbar_wait(o_ready + slot, u & 1))) break;
@@ -317,13 +336,21 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
             const uint32_t u = i >> 1;
             const uint32_t L = blockIdx.x + i * G;
             const int hh = L % HHu, b = L / (HHu * n_tiles);
-            const int q0 = (int)((L / HHu) % n_tiles) * kTQ;
+            const int q0 = (int)((L / HHu) % n_tiles) * kRows;
             const int start = (q0 + P.off1 - P.left) - P.cl;
-            const bool edge = start < P.key_lo || start + KT > P.key_hi;   // some columns lie outside the key line
+            const bool edge = start < P.key_lo || start + kBandKT > P.key_hi;   // some columns lie outside the key line
             if (r == 0) TR(2, i, 0);
             if (!(ok = ptx::mbar_wait(s_ready + slot, u & 1))) break;
             tc_fence_after();
             if (r == 0) TR(2, i, 1);
+            if (LF && quad == 3) {
+                // rows 96..127 of the tile belong to the next item: nothing to compute, their rows of P stay
+                // whatever the scores left there and their output rows are never stored
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(p_ready + slot);
+                continue;
+            }
             // Columns of this row that count: its band, cut to the keys that exist.  n_ok = 0: none.
             int lo = r + P.cl, hi = r + P.cl + (int)span;
             if (edge) {
@@ -356,7 +383,17 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                 }
             };
             float mus = 0.f;
-            auto weights_chunk = [&](const uint32_t (&sr)[32], int ch) {
+            // Longformer variant: chunk NCH is the scores against the keys at the global positions (columns
+            // 224..255); a slot counts unless it is unused or the row's window already holds that position
+            auto mask_globals = [&](uint32_t (&sr)[32]) {
+                const int p = q0 + r + P.off1;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const int gk = sG[e];
+                    if (gk == kNoGlobal || (uint32_t)(gk - p + P.left) <= span) sr[e] = 0xff800000u;
+                }
+            };
+            auto weights_chunk = [&](const uint32_t (&sr)[32], int piece) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
@@ -364,7 +401,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                     ffma2(x0, x1, __uint_as_float(sr[2 * e]), __uint_as_float(sr[2 * e + 1]), P.sl2, -mus);
                     pk[e] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
                 }
-                tmem_st16(t_lane + 16 * (quad + ch), pk);
+                tmem_st16(t_lane + 16 * piece, pk);
             };
             if constexpr (NCH == 3) {
                 // the whole band of a row fits the registers: one read of the scores
@@ -379,37 +416,89 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                 mask_chunk(s1, 1);
                 max_chunk(s1);
                 tmem_ld32_wait(s2);
+                if (r == 0) TR(0, i, 2);
                 mask_chunk(s2, 2);
                 max_chunk(s2);
                 const float m = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
                 mus = (m == -INFINITY ? 0.f : m) * P.sl2;
-                weights_chunk(s0, 0);
-                weights_chunk(s1, 1);
-                weights_chunk(s2, 2);
+                if (r == 0) TR(0, i, 3);
+                weights_chunk(s0, quad);
+                weights_chunk(s1, quad + 1);
+                weights_chunk(s2, quad + 2);
+                if (r == 0) TR(0, i, 4);
             } else {
-                // two passes over the scores, the load of the next chunk in flight while one is worked on
-                uint32_t sa[32], sb[32];
-                tmem_ld32_issue(t_lane + c0, sa);
-#pragma unroll
-                for (int ch = 0; ch < NCH; ++ch) {
-                    uint32_t (&cur)[32] = (ch & 1) ? sb : sa;
-                    uint32_t (&nxt)[32] = (ch & 1) ? sa : sb;
-                    tmem_ld32_wait(cur);
-                    tmem_ld32_issue(t_lane + c0 + 32 * ((ch + 1) % NCH), nxt);   // after the last chunk: chunk 0 again, for pass 2
-                    mask_chunk(cur, ch);
-                    max_chunk(cur);
+                // Two passes over the scores with three register buffers.  Every tcgen05.wait::ld covers all
+                // loads in flight, so the chunks are fetched in groups whose latency is paid once per group:
+                // pass 1 takes the high chunks first and ends on the low ones, which then stay in registers
+                // (masked) for pass 2; pass 2 goes upward, as the P stores must (a chunk's weights land on
+                // columns below every score still to be read), and re-reads only the high chunks.
+                constexpr int NC = LF ? NCH + 1 : NCH;   // the Longformer variant's last chunk: the global keys
+                constexpr int NL = NC - 3;               // low chunks 0..NL-1, high chunks NL..NC-1 (three of them)
+                static_assert(NL >= 1 && NL <= 3, "three buffers hold either group");
+                auto ccol = [&](int ch) { return LF && ch == NCH ? kLfBand : c0 + 32 * ch; };
+                auto piece_of = [&](int ch) { return LF && ch == NCH ? kLfBand / 32 : quad + ch; };
+                auto mask_any = [&](uint32_t (&sr)[32], int ch) {
+                    if (LF && ch == NCH) mask_globals(sr);
+                    else mask_chunk(sr, ch);
+                };
+                uint32_t b0[32], b1[32], b2[32];
+                tmem_ld32_issue(t_lane + ccol(NL), b0);
+                tmem_ld32_issue(t_lane + ccol(NL + 1), b1);
+                tmem_ld32_issue(t_lane + ccol(NL + 2), b2);
+                tmem_ld32_wait(b0);
+                tmem_ld32_wait(b1);
+                tmem_ld32_wait(b2);
+                mask_any(b0, NL);
+                max_chunk(b0);
+                tmem_ld32_issue(t_lane + ccol(0), b0);
+                mask_any(b1, NL + 1);
+                max_chunk(b1);
+                if (NL > 1) tmem_ld32_issue(t_lane + ccol(1), b1);
+                mask_any(b2, NL + 2);
+                max_chunk(b2);
+                if (NL > 2) tmem_ld32_issue(t_lane + ccol(2), b2);
+                tmem_ld32_wait(b0);
+                mask_any(b0, 0);
+                max_chunk(b0);
+                if (NL > 1) {
+                    tmem_ld32_wait(b1);
+                    mask_any(b1, 1);
+                    max_chunk(b1);
+                }
+                if (NL > 2) {
+                    tmem_ld32_wait(b2);
+                    mask_any(b2, 2);
+                    max_chunk(b2);
                 }
                 const float m = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
                 mus = (m == -INFINITY ? 0.f : m) * P.sl2;
-#pragma unroll
-                for (int ch = 0; ch < NCH; ++ch) {
-                    // pass 1 ended on buffer (NCH - 1) & 1 and left chunk 0 loading into the other one
-                    uint32_t (&cur)[32] = ((ch + NCH) & 1) ? sb : sa;
-                    uint32_t (&nxt)[32] = ((ch + NCH) & 1) ? sa : sb;
-                    tmem_ld32_wait(cur);
-                    if (ch + 1 < NCH) tmem_ld32_issue(t_lane + c0 + 32 * (ch + 1), nxt);
-                    mask_chunk(cur, ch);
-                    weights_chunk(cur, ch);
+                // pass 2: the low chunks from the registers, each buffer refilled with a high chunk as it frees
+                weights_chunk(b0, piece_of(0));
+                tmem_ld32_issue(t_lane + ccol(NL), b0);
+                if (NL > 1) {
+                    weights_chunk(b1, piece_of(1));
+                    tmem_ld32_issue(t_lane + ccol(NL + 1), b1);
+                }
+                if (NL > 2) {
+                    weights_chunk(b2, piece_of(2));
+                    tmem_ld32_issue(t_lane + ccol(NL + 2), b2);
+                }
+                tmem_ld32_wait(b0);
+                mask_any(b0, NL);
+                weights_chunk(b0, piece_of(NL));
+                if (NL > 1) {
+                    tmem_ld32_wait(b1);
+                    mask_any(b1, NL + 1);
+                    weights_chunk(b1, piece_of(NL + 1));
+                    if (NL > 2) {
+                        tmem_ld32_wait(b2);
+                        mask_any(b2, NL + 2);
+                    }
+                    weights_chunk(b2, piece_of(NL + 2));   // NL == 2: still in its register from pass 1, masked
+                } else {
+                    // NL == 1 does not occur (NC is 5 or 6); kept so that every NL compiles
+                    weights_chunk(b1, piece_of(NL + 1));
+                    weights_chunk(b2, piece_of(NL + 2));
                 }
             }
             // zeros in the P columns outside the band (the scores there belong to other rows' bands)
@@ -419,9 +508,12 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                 for (int e = 0; e < 16; ++e) z[e] = 0u;
 #pragma unroll 1
                 for (int piece = 0; piece < KT / 32; ++piece)
-                    if (piece < quad || piece >= quad + NCH) tmem_st16(t_lane + 16 * piece, z);
+                    if ((piece < quad || piece >= quad + NCH) && !(LF && piece == kLfBand / 32))
+                        tmem_st16(t_lane + 16 * piece, z);
             }
+            if (r == 0) TR(0, i, 5);
             tmem_wait_st();
+            if (r == 0) TR(0, i, 6);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(p_ready + slot);
@@ -442,15 +534,16 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
 
 // ---- host side --------------------------------------------------------------------------------
 
-template <typename T, int KT>
-int launch_band(const Problem &p, const BandParams &bp_in, int64_t dil) {
+template <typename T, int KT, bool LF>
+int launch_band(const Problem &p, const BandParams &bp_in, int64_t dil, const void *kg, const void *vg) {
     BandParams bp = bp_in;
     BandMaps m;
     const int64_t HH = bp.HH;
+    constexpr int kBandKT = LF ? kLfBand : KT;
     if (int rc = make_row_tensor_map(&m.q, p.q, p.dtype, HH, p.Sq / dil, p.B, kTQ)) return rc;
-    if (int rc = make_row_tensor_map(&m.k, p.k, p.dtype, HH, p.Skv / dil, p.B, KT)) return rc;
-    if (int rc = make_row_tensor_map(&m.v, p.v, p.dtype, HH, p.Skv / dil, p.B, KT)) return rc;
-    if (int rc = make_row_tensor_map(&m.o, p.o, p.dtype, HH, p.Sq / dil, p.B, kTQ)) return rc;
+    if (int rc = make_row_tensor_map(&m.k, p.k, p.dtype, HH, p.Skv / dil, p.B, kBandKT)) return rc;
+    if (int rc = make_row_tensor_map(&m.v, p.v, p.dtype, HH, p.Skv / dil, p.B, kBandKT)) return rc;
+    if (int rc = make_row_tensor_map(&m.o, p.o, p.dtype, HH, p.Sq / dil, p.B, LF ? kLfRows : kTQ)) return rc;
     if (int rc = make_row_tensor_map(&m.k_own, p.k, p.dtype, HH, p.Skv / dil, p.B, 16)) return rc;
     if (int rc = make_row_tensor_map(&m.v_own, p.v, p.dtype, HH, p.Skv / dil, p.B, 16)) return rc;
     m.k_prev = m.k_next = m.k_own;
@@ -463,7 +556,13 @@ int launch_band(const Problem &p, const BandParams &bp_in, int64_t dil) {
         if (int rc = make_row_tensor_map(&m.k_next, p.k_next, p.dtype, HH, p.S_next / dil, p.B, 16)) return rc;
         if (int rc = make_row_tensor_map(&m.v_next, p.v_next, p.dtype, HH, p.S_next / dil, p.B, 16)) return rc;
     }
-    auto kern = umma_band_kernel<T, KT>;
+    m.kg = m.k_own;
+    m.vg = m.v_own;
+    if (LF) {
+        if (int rc = make_row_tensor_map(&m.kg, kg, p.dtype, HH, bp.n_global, p.B, kLfGlobals)) return rc;
+        if (int rc = make_row_tensor_map(&m.vg, vg, p.dtype, HH, bp.n_global, p.B, kLfGlobals)) return rc;
+    }
+    auto kern = umma_band_kernel<T, KT, LF>;
     constexpr size_t smem = BandCfg<KT>::kSmemBytes;
     if (int rc = ensure_dynamic_smem((const void *)kern, smem, "cudaFuncSetAttribute(umma_band_kernel)")) return rc;
     int dev = 0, sms = 0;
@@ -474,13 +573,15 @@ int launch_band(const Problem &p, const BandParams &bp_in, int64_t dil) {
     kern<<<grid, kThreads, smem, p.stream>>>(m, bp);
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "umma_band_kernel launch");
-    note_kernel("umma_band");
+    note_kernel(LF ? "umma_longformer" : "umma_band");
     return MAT_OK;
 }
 
 // Fills bp and returns the key-range width (192 or 256), or 0 when the window does not fit.
-int plan_band(const Problem &p, BandParams &bp) {
-    const int64_t dil = p.pat.dilation;
+// rows = query rows per item, band_cols = columns available to the window part of an item's key range.
+int plan_band(const Problem &p, BandParams &bp, bool longformer) {
+    const int64_t dil = longformer ? 1 : p.pat.dilation;
+    const int rows = longformer ? kLfRows : kTQ;
     bp.Sq1 = (int32_t)(p.Sq / dil);
     bp.Skv1 = (int32_t)(p.Skv / dil);
     bp.off1 = (int32_t)(p.pat.q_offset / dil);
@@ -492,12 +593,15 @@ int plan_band(const Problem &p, BandParams &bp) {
     bp.right = (int32_t)std::min<int64_t>(p.pat.right, bp.Skv1 + next_rows);
     bp.cl = (((bp.off1 - bp.left) % 16) + 16) % 16;
     bp.HH = (int32_t)(p.H * dil);
-    bp.n_tiles = (bp.Sq1 + kTQ - 1) / kTQ;
+    bp.n_tiles = (bp.Sq1 + rows - 1) / rows;
     bp.sl2 = p.scale * 1.4426950408889634f;
+    bp.n_global = longformer ? (int32_t)p.pat.n_global : 0;
+    bp.gidx = longformer ? p.pat.gidx : nullptr;
     const uint64_t items = (uint64_t)p.B * bp.n_tiles * bp.HH;
     if (items >= (1ull << 31)) return 0;
     bp.n_items = (uint32_t)items;
-    const int need = bp.cl + bp.left + bp.right + kTQ;   // columns from row 0's first key to row 127's last
+    const int need = bp.cl + bp.left + bp.right + rows;   // columns from the first row's first key to the last row's last
+    if (longformer) return need <= kLfBand ? 256 : 0;
     return need <= 192 ? 192 : need <= 256 ? 256 : 0;
 }
 
@@ -517,17 +621,46 @@ bool umma_band_supports(const Problem &p) {
     const char *force = std::getenv("MAT_WINDOW_KERNEL");
     if (force && std::strcmp(force, "mma") == 0) return false;
     BandParams bp;
-    return plan_band(p, bp) != 0;
+    return plan_band(p, bp, false) != 0;
 }
 
 int launch_umma_band(const Problem &p) {
     BandParams bp;
-    const int kt = plan_band(p, bp);
+    const int kt = plan_band(p, bp, false);
     if (kt == 0) return fail(MAT_ERR_UNSUPPORTED, "window too wide for the band kernel");
     const int64_t dil = p.pat.dilation;
     if (p.dtype == MAT_BF16)
-        return kt == 192 ? launch_band<__nv_bfloat16, 192>(p, bp, dil) : launch_band<__nv_bfloat16, 256>(p, bp, dil);
-    return kt == 192 ? launch_band<__half, 192>(p, bp, dil) : launch_band<__half, 256>(p, bp, dil);
+        return kt == 192 ? launch_band<__nv_bfloat16, 192, false>(p, bp, dil, nullptr, nullptr)
+                         : launch_band<__nv_bfloat16, 256, false>(p, bp, dil, nullptr, nullptr);
+    return kt == 192 ? launch_band<__half, 192, false>(p, bp, dil, nullptr, nullptr)
+                     : launch_band<__half, 256, false>(p, bp, dil, nullptr, nullptr);
+}
+
+// First pass of a Longformer forward (every row over its window plus the keys at the global positions) on
+// the band kernel: whole sequences, 1 to 32 global positions whose K/V rows the caller has gathered into
+// [B, n_global, H, 64] buffers, a window of at most 128 taps whose first tap sits on a multiple of 16.
+// MAT_WINDOW_KERNEL=mma keeps the warp-level kernel.
+bool umma_band_longformer_supports(const Problem &p) {
+    if (p.pat.kind != MAT_LONGFORMER) return false;
+    if (p.dtype != MAT_BF16 && p.dtype != MAT_F16) return false;
+    if (p.D != 64 || p.pat.q_offset != 0 || p.Sq != p.Skv) return false;
+    if (p.pat.n_global < 1 || p.pat.n_global > kLfGlobals) return false;
+    if (p.k_prev || p.k_next) return false;
+    const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
+    if (al % 16) return false;
+    if (p.Skv >= (1LL << 28) || p.H >= (1LL << 24) || p.B > 65535) return false;
+    const char *force = std::getenv("MAT_WINDOW_KERNEL");
+    if (force && std::strcmp(force, "mma") == 0) return false;
+    BandParams bp;
+    return plan_band(p, bp, true) != 0;
+}
+
+int launch_umma_band_longformer(const Problem &p, const void *kg, const void *vg) {
+    BandParams bp;
+    if (plan_band(p, bp, true) == 0) return fail(MAT_ERR_UNSUPPORTED, "window too wide for the band kernel");
+    if (((uintptr_t)kg | (uintptr_t)vg) % 16) return fail(MAT_ERR_INVALID, "gathered rows must be 16-byte aligned");
+    return p.dtype == MAT_BF16 ? launch_band<__nv_bfloat16, 256, true>(p, bp, 1, kg, vg)
+                               : launch_band<__half, 256, true>(p, bp, 1, kg, vg);
 }
 
 }  // namespace mat

@@ -90,7 +90,7 @@ def test_cfg4_full_size_every_row():
     spec = PatternSpec.longformer(64, 64, glob)
     q, k, v = seeded_qkv(4, B, S, H, 64, torch.bfloat16)
     got = _run(spec, q, k, v)
-    assert nat.last_kernel() == "mma_longformer"
+    assert nat.last_kernel() == "umma_longformer"
     want = oracle_out(q, k, v, spec)
     assert np.isfinite(got).all()
     e = float(np.abs(got - want).max())

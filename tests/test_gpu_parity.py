@@ -287,21 +287,49 @@ def test_longformer_vs_oracle(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_longformer_cfg4_shape_reduced_length(dtype):
+def test_longformer_cfg4_shape_reduced_length(monkeypatch, dtype):
     # cfg-4's window (+-64), 32 seeded global positions, 12 heads, at a length the oracle finishes quickly
     g = torch.Generator().manual_seed(4)
     S = 4096
     glob = torch.randperm(S, generator=g)[:32].sort().values.numpy()
     spec = PatternSpec.longformer(64, 64, glob)
     q, k, v = seeded_qkv(43, 2, S, 12, 64, dtype)
+    want = oracle_out(q, k, v, spec)
+    got = run(spec, q, k, v)
+    assert nat.last_kernel() == "umma_longformer"      # window pass on the tcgen05 band kernel
+    check_close(got, want, dtype)
+    monkeypatch.setenv("MAT_WINDOW_KERNEL", "mma")      # and on the warp-level kernel
     got = run(spec, q, k, v)
     assert nat.last_kernel() == "mma_longformer"
-    check_close(got, oracle_out(q, k, v, spec), dtype)
+    check_close(got, want, dtype)
+    monkeypatch.delenv("MAT_WINDOW_KERNEL")
     # many global positions: several gathered chunks and several tiles of global rows
     glob = torch.randperm(1500, generator=g)[:200].sort().values.numpy()
     spec = PatternSpec.longformer(10, 3, glob)
     q, k, v = seeded_qkv(44, 1, 1500, 2, 64, dtype)
     check_close(run(spec, q, k, v), oracle_out(q, k, v, spec), dtype)
+    assert nat.last_kernel() == "mma_longformer"       # more than 32 global positions: the warp-level first pass
+
+
+@pytest.mark.parametrize("left,right,n_glob,S,B,H", [
+    (64, 64, 32, 1000, 2, 3),     # ragged against the 96-row items
+    (16, 16, 1, 96, 1, 1),        # one item, one global position
+    (0, 100, 7, 300, 1, 2),       # looking ahead
+    (112, 16, 32, 2048, 1, 2),    # lopsided, the widest window the 224 band columns hold
+    (3, 3, 5, 50, 1, 1),          # shorter than one item
+    (17, 30, 9, 700, 1, 2),       # first tap off a multiple of 16: the band starts inside its first column group
+])
+def test_longformer_window_pass_on_band_kernel(left, right, n_glob, S, B, H):
+    """The Longformer first pass on the persistent tcgen05 kernel: 96-row items, the keys at the global positions
+    as 32 extra columns (de-duplicated against each row's window), global rows finished by the split pass."""
+    g = torch.Generator().manual_seed(46)
+    glob = torch.randperm(S, generator=g)[:n_glob].sort().values.numpy()
+    spec = PatternSpec.longformer(left, right, glob)
+    for dtype in (torch.bfloat16, torch.float16):
+        q, k, v = seeded_qkv(47, B, S, H, 64, dtype)
+        got = run(spec, q, k, v)
+        assert nat.last_kernel() == "umma_longformer"
+        check_close(got, oracle_out(q, k, v, spec), dtype)
 
 
 # ---- index sets, recovered from the kernels themselves -----------------------------------------
