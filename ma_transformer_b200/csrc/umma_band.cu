@@ -608,7 +608,8 @@ int plan_band(const Problem &p, BandParams &bp, bool longformer) {
 }  // namespace
 
 // Windows of at most 128 taps between their two sides on 16-bit inputs with head width 64.
-// MAT_WINDOW_KERNEL=mma keeps them on the warp-level kernels (debugging and measurement aid).
+// MAT_WINDOW_KERNEL=mma keeps them on the warp-level kernels, MAT_WINDOW_KERNEL=band sends every window
+// the band kernel can take to it whatever the size (debugging and measurement aids).
 bool umma_band_supports(const Problem &p) {
     if (p.pat.kind != MAT_WINDOW) return false;
     if (p.dtype != MAT_BF16 && p.dtype != MAT_F16) return false;
@@ -621,7 +622,17 @@ bool umma_band_supports(const Problem &p) {
     const char *force = std::getenv("MAT_WINDOW_KERNEL");
     if (force && std::strcmp(force, "mma") == 0) return false;
     BandParams bp;
-    return plan_band(p, bp, false) != 0;
+    const int kt = plan_band(p, bp, false);
+    if (kt == 0) return false;
+    if (force && std::strcmp(force, "band") == 0) return true;
+    // Small problems: a persistent CTA pays about 4.5 us of start-up and drain and works in 128-row items of
+    // about 1.4 us, so with few items per SM the one-tile-per-CTA warp-level kernel finishes sooner (a shard
+    // of 8192 tokens x 8 heads: 7.0 against 9.6 us; 16384 tokens: 12.6 against 14.4 us; 32768 tokens: 24.6
+    // against 23.3 us).  Windows of more than 64 taps always come here: there the warp-level kernel is
+    // bound by its shared-memory traffic and loses at every size.
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return kt == 256 || bp.n_items >= 10u * (uint32_t)sms;
 }
 
 int launch_umma_band(const Problem &p) {

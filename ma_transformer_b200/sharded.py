@@ -179,8 +179,10 @@ class SequenceShardedAttention:
             finish()
             self._run(q, k_ext, v_ext, out, 0, L.rows)
             return out
-        # interior rows first: their windows never leave the chunk
-        self._run(q, k_ext, v_ext, out, front, L.rows - back)
+        # interior rows first: their windows never leave the chunk.  They are handed the chunk's own key rows
+        # only: the tiled kernels stage whole groups of keys around a window, and a halo row that has not been
+        # received yet (arbitrary bits, possibly NaN) must not sit in such a group, not even under a zero weight.
+        self._run(q, k_ext, v_ext, out, front, L.rows - back, own_rows_only=True)
         finish()
         if front:
             self._run(q, k_ext, v_ext, out, 0, front)
@@ -188,10 +190,15 @@ class SequenceShardedAttention:
             self._run(q, k_ext, v_ext, out, L.rows - back, L.rows)
         return out
 
-    def _run(self, q, k_ext, v_ext, out, a: int, b: int) -> None:
+    def _run(self, q, k_ext, v_ext, out, a: int, b: int, own_rows_only: bool = False) -> None:
         if b <= a:
             return
-        spec = self.spec.shifted(self.layout.halo_front + a)
+        L = self.layout
+        if own_rows_only:   # batch 1 here, so a row range of the extended buffer is still contiguous
+            k_ext, v_ext = k_ext[:, L.halo_front:L.halo_front + L.rows], v_ext[:, L.halo_front:L.halo_front + L.rows]
+            spec = self.spec.shifted(a)
+        else:
+            spec = self.spec.shifted(L.halo_front + a)
         whole = a == 0 and b == q.shape[1]
         self.forward_fn(q if whole else q[:, a:b], k_ext, v_ext, spec,
                         out=out if whole else out[:, a:b])

@@ -89,6 +89,40 @@ def test_mma_window_vs_oracle(spec, dtype, B, S, H):
     check_close(got, oracle_out(q, k, v, spec), dtype)
 
 
+def test_window_kernel_choice_by_size(monkeypatch):
+    """Without MAT_WINDOW_KERNEL the library sends small narrow-window problems to the warp-level kernel (the
+    persistent kernel's start-up and drain would dominate) and large ones to the persistent tcgen05 kernel;
+    windows of more than 64 taps go to the tcgen05 kernel at every size.  Same answers either way."""
+    monkeypatch.delenv("MAT_WINDOW_KERNEL", raising=False)
+    spec = PatternSpec.causal_window(64)
+    q, k, v = seeded_qkv(17, 1, 2048, 2, 64, torch.bfloat16)
+    want = oracle_out(q, k, v, spec)
+    check_close(run(spec, q, k, v), want, torch.bfloat16)
+    assert nat.last_kernel() == "mma_window"
+    qb, kb, vb = (t.repeat(1, 24, 4, 1) for t in (q, k, v))            # 49152 tokens x 8 heads: 3072 items
+    run(spec, qb, kb, vb)
+    assert nat.last_kernel() == "umma_band"
+    check_close(run(PatternSpec.sliding_window(64), q, k, v), oracle_out(q, k, v, PatternSpec.sliding_window(64)), torch.bfloat16)
+    assert nat.last_kernel() == "umma_band"
+    monkeypatch.setenv("MAT_WINDOW_KERNEL", "mma")
+    for s in (spec, PatternSpec.sliding_window(64), PatternSpec.sliding_window(20)):
+        check_close(run(s, q, k, v), oracle_out(q, k, v, s), torch.bfloat16)
+        assert nat.last_kernel() == "mma_window"
+
+
+@pytest.mark.parametrize("kernel", ["band", "mma"])
+@pytest.mark.parametrize("spec", [PatternSpec.causal_window(64), PatternSpec.causal_window(33), PatternSpec.sliding_window(17),
+                                  PatternSpec.sliding_window(64), PatternSpec(left=5, right=90), PatternSpec.causal_window(128)],
+                         ids=lambda s: f"l{s.left}r{s.right}")
+def test_both_window_kernels_vs_oracle(monkeypatch, kernel, spec):
+    monkeypatch.setenv("MAT_WINDOW_KERNEL", kernel)
+    for B, S, H in [(2, 1000, 3), (1, 130, 2)]:
+        q, k, v = seeded_qkv(18, B, S, H, 64, torch.bfloat16)
+        got = run(spec, q, k, v)
+        assert nat.last_kernel() == ("umma_band" if kernel == "band" else "mma_window")
+        check_close(got, oracle_out(q, k, v, spec), torch.bfloat16)
+
+
 @pytest.mark.parametrize("spec", [PatternSpec.sliding_window(65), PatternSpec.causal_window(130),
                                   PatternSpec.causal_window(200), PatternSpec(left=40, right=90),
                                   PatternSpec(left=300, right=17), PatternSpec.sliding_window(1000),
