@@ -41,9 +41,9 @@ SEED = 2
 WORKLOAD = f"causal sliding-window fwd B={B} N={SEQ} H={H} d={D} taps={TAPS} bf16"
 BYTES_PER_TOKEN = 4 * H * D * 2          # read Q,K,V + write O, bf16
 METRIC = "sparse-attn fwd tokens/s @N=64K,w=64,bf16"
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the window kernel on this
-# workload, from an ncu capture of that launch, per token
-NCU_TRAFFIC_PER_TOKEN = (201.354e6 + 49.839e6) / 65536
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of each window kernel on this
+# workload, from ncu captures of those launches, per token
+NCU_TRAFFIC_PER_TOKEN = {"umma_band": (201.378e6 + 41.432e6) / 65536, "mma_window": (201.354e6 + 49.839e6) / 65536}
 
 
 def measured_peak_gbs():
@@ -450,7 +450,8 @@ def gpu_arm(args):
                     "steps": e2e_steps, "api": "sparse_attention_cuda.forward_host (mat_sparse_attn_fwd_host)"},
             "gpu_launches": int(n_launch.item()),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC_PER_TOKEN * rows, "peak_source": f"{peak_kind} HBM copy bandwidth",
+                         "traffic": NCU_TRAFFIC_PER_TOKEN.get(nat.last_kernel(), NCU_TRAFFIC_PER_TOKEN["umma_band"]) * rows,
+                         "peak_source": f"{peak_kind} HBM copy bandwidth",
                          "kernel": nat.last_kernel(), "bytes_per_launch_algorithmic": per_rank_bytes},
             "parity_check": parity, "device_status": status,
         }
