@@ -97,6 +97,24 @@ int mat_sparse_attn_fwd(const void *q, const void *k, const void *v, void *o,
                         int dtype, const mat_pattern_spec *spec, float scale,
                         void *workspace, size_t workspace_bytes, void *stream);
 
+/*
+ * Forward pass on device tensors whose tokens are not packed: q, k, v and o keep D contiguous and the H heads
+ * of a token contiguous, but consecutive tokens lie *_token_stride ELEMENTS apart (0 = packed, H*D), and
+ * batch item b starts b * S * stride elements after item 0.  This is how q, k and v sit inside the output
+ * [B, S, 3, H, D] of one fused projection: the caller passes three views of it (stride 3*H*D) and no copy is
+ * made.  The reference's integration example projects q, k and v separately and reshapes each
+ * (examples/pytorch_integration_example.py:65-107), and its extension refuses anything but packed tensors
+ * (src/cuda/sparse_attention_kernel.cu:430); this entry point is the additive relaxation.
+ * MAT_WINDOW patterns of at most 128 taps between their two sides, 16-bit dtypes, D = 64, strides multiples
+ * of 8 elements; other requests with real strides get MAT_ERR_UNSUPPORTED.  Packed strides behave exactly as
+ * mat_sparse_attn_fwd (without a workspace).
+ */
+int mat_sparse_attn_fwd_strided(const void *q, const void *k, const void *v, void *o,
+                                int64_t B, int64_t S_q, int64_t S_kv, int64_t H, int64_t D,
+                                int dtype, const mat_pattern_spec *spec, float scale,
+                                int64_t q_token_stride, int64_t k_token_stride,
+                                int64_t v_token_stride, int64_t o_token_stride, void *stream);
+
 /* Scratch bytes mat_sparse_attn_fwd needs for this problem (0 for most). */
 size_t mat_sparse_attn_workspace_bytes(int64_t B, int64_t S_q, int64_t S_kv, int64_t H,
                                        int64_t D, int dtype, const mat_pattern_spec *spec);

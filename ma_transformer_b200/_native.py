@@ -17,7 +17,7 @@ MAT_WINDOW, MAT_BLOCK, MAT_LONGFORMER = 0, 1, 2
 # every symbol include/mat_sparse_attn.h declares
 EXPORTS = (
     "mat_version", "mat_last_error", "mat_last_kernel", "mat_device_status",
-    "mat_sparse_attn_fwd", "mat_sparse_attn_workspace_bytes", "mat_sparse_attn_fwd_window",
+    "mat_sparse_attn_fwd", "mat_sparse_attn_fwd_strided", "mat_sparse_attn_workspace_bytes", "mat_sparse_attn_fwd_window",
     "mat_sparse_attn_fwd_host", "mat_sparse_attn_host_staging_bytes", "mat_sparse_attn_fwd_sharded",
     "mat_pattern_rowset", "mat_pattern_nnz", "mat_enable_peer_access",
     "mat_ipc_export", "mat_ipc_open", "mat_ipc_close", "mat_sparse_attn_fwd_longformer_noalloc",
@@ -59,6 +59,9 @@ def _load() -> C.CDLL:
     lib.mat_sparse_attn_fwd.restype = C.c_int
     lib.mat_sparse_attn_fwd.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, C.c_int, spec_p,
                                         C.c_float, vp, sz, vp]
+    lib.mat_sparse_attn_fwd_strided.restype = C.c_int
+    lib.mat_sparse_attn_fwd_strided.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, C.c_int, spec_p,
+                                                C.c_float, i64, i64, i64, i64, vp]
     lib.mat_sparse_attn_workspace_bytes.restype = sz
     lib.mat_sparse_attn_workspace_bytes.argtypes = [i64, i64, i64, i64, i64, C.c_int, spec_p]
     lib.mat_sparse_attn_fwd_window.restype = C.c_int

@@ -204,6 +204,32 @@ int mat_sparse_attn_fwd(const void *q, const void *k, const void *v, void *o, in
     return run_problem(p);
 }
 
+int mat_sparse_attn_fwd_strided(const void *q, const void *k, const void *v, void *o, int64_t B,
+                                int64_t S_q, int64_t S_kv, int64_t H, int64_t D, int dtype,
+                                const mat_pattern_spec *spec, float scale, int64_t q_token_stride,
+                                int64_t k_token_stride, int64_t v_token_stride, int64_t o_token_stride,
+                                void *stream) {
+    Problem p;
+    if (int rc = make_problem(p, q, k, v, o, B, S_q, S_kv, H, D, dtype, spec, scale, nullptr, 0, stream))
+        return rc;
+    const int64_t row = H * D;
+    const int64_t ts[4] = {q_token_stride, k_token_stride, v_token_stride, o_token_stride};
+    bool strided = false;
+    for (int64_t t : ts) {
+        if (t != 0 && t < row) return fail(MAT_ERR_INVALID, "a token stride of %lld elements is shorter than a token (%lld)", (long long)t, (long long)row);
+        if (t % 8) return fail(MAT_ERR_INVALID, "token strides must be multiples of 8 elements (16 bytes)");
+        strided = strided || (t != 0 && t != row);
+    }
+    if (!strided) return run_problem(p);
+    p.q_ts = q_token_stride; p.k_ts = k_token_stride; p.v_ts = v_token_stride; p.o_ts = o_token_stride;
+    // strided tensors are read by the band kernel only (whatever the problem's size)
+    if (spec->kind != MAT_WINDOW || (dtype != MAT_BF16 && dtype != MAT_F16) || D != 64 || !umma_band_fits(p))
+        return fail(MAT_ERR_UNSUPPORTED,
+                    "token-strided tensors are supported for window patterns of at most 128 taps on 16-bit inputs "
+                    "with head width 64 (sequence lengths divisible by the dilation): pass contiguous tensors");
+    return launch_umma_band(p);
+}
+
 size_t mat_sparse_attn_workspace_bytes(int64_t B, int64_t S_q, int64_t S_kv, int64_t H, int64_t D,
                                        int dtype, const mat_pattern_spec *spec) {
     Problem p;

@@ -39,6 +39,10 @@ struct Problem {
     // neighbouring sequence shards read in place (peer memory); NULL when absent
     const void *k_prev = nullptr, *v_prev = nullptr, *k_next = nullptr, *v_next = nullptr;
     int64_t S_prev = 0, S_next = 0;
+    // Token strides of q, k, v, o in elements (0: contiguous, i.e. H * D).  Heads of a token stay contiguous and
+    // a batch item is S tokens of that stride: the layout of q, k, v inside a fused projection output
+    // [B, S, 3, H, D].  Only the band kernel reads strided tensors.
+    int64_t q_ts = 0, k_ts = 0, v_ts = 0, o_ts = 0;
     // Longformer shard of a sequence spread over GPUs: K/V rows at all global positions, gathered by the caller
     const void *shard_kg = nullptr, *shard_vg = nullptr;
 };
@@ -68,6 +72,7 @@ bool umma_dense_supports(const Problem &p);  // dense / causal dense on the same
 int launch_umma_dense(const Problem &p);
 int umma_status_read_and_clear(int *out);
 bool umma_band_supports(const Problem &p);   // umma_band.cu: windows of at most 128 taps, persistent, on tcgen05 / TMEM
+bool umma_band_fits(const Problem &p);       // can run it at all (umma_band_supports also weighs the problem's size)
 int launch_umma_band(const Problem &p);
 int band_status_read_and_clear(int *out);
 // first pass of a Longformer forward on the band kernel; kg, vg: the K/V rows at the global positions, gathered
@@ -88,6 +93,9 @@ int launch_umma_global_rows(const Problem &p, const GlobalRowSplit &g, float *pa
 // 128-byte swizzle, zeros for rows outside the tensor.
 int make_row_tensor_map(CUtensorMap *m, const void *base, int dtype, int64_t HH, int64_t S1, int64_t B,
                         int box_rows);
+// The same rows as a 5-D map {64, H, dil, S/dil, B} with an explicit token stride (bytes): box {64, 1, 1, box_rows, 1}.
+int make_row_tensor_map5(CUtensorMap *m, const void *base, int dtype, int64_t H, int64_t dil, int64_t S1, int64_t B,
+                         int box_rows, int64_t token_stride_bytes);
 int bwd_status_read_and_clear(int *out);     // bwd_mma.cu
 // tensor-core backward of window patterns, dense included (bwd_mma.cu): 16-bit types, D = 64, S a multiple of the dilation
 bool bwd_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t left, int64_t right,

@@ -966,6 +966,23 @@ int make_row_tensor_map(CUtensorMap *m, const void *base, int dtype, int64_t HH,
     return make_map(m, base, dtype, HH, S1, B, box_rows);
 }
 
+int make_row_tensor_map5(CUtensorMap *m, const void *base, int dtype, int64_t H, int64_t dil, int64_t S1, int64_t B,
+                         int box_rows, int64_t token_stride_bytes) {
+    PFN_cuTensorMapEncodeTiled enc = encode_fn();
+    if (!enc) return fail(MAT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t ts = (cuuint64_t)token_stride_bytes;
+    const cuuint64_t dims[5] = {64, (cuuint64_t)H, (cuuint64_t)dil, (cuuint64_t)S1, (cuuint64_t)B};
+    const cuuint64_t strides[4] = {(cuuint64_t)kRowBytes, ts, (cuuint64_t)dil * ts, (cuuint64_t)S1 * dil * ts};
+    const cuuint32_t box[5] = {64, 1, 1, (cuuint32_t)box_rows, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = enc(m, dtype == MAT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                     5, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(MAT_ERR_CUDA, "cuTensorMapEncodeTiled (5-D) failed with code %d", (int)r);
+    return MAT_OK;
+}
+
 int flash_status_read_and_clear(int *out) {
     int zero = 0;
     cudaError_t e = cudaMemcpyFromSymbol(out, g_flash_status, sizeof(int));

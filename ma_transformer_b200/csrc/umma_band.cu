@@ -79,6 +79,7 @@ struct BandParams {
     int32_t left, right;
     int32_t cl;                    // column of row 0's first key inside an item's key range
     int32_t HH, n_tiles;
+    int32_t H;                     // heads of the tensor itself: head hh of the kernel's view is head hh % H, residue hh / H
     uint32_t n_items;
     float sl2;                     // scale * log2(e)
     // Longformer variant: the sorted global positions; every row attends them besides its window
@@ -172,6 +173,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
             for (uint32_t it = 0; it < n_mine; ++it) {
                 const uint32_t L = blockIdx.x + it * G;
                 const int hh = L % HHu, b = L / (HHu * n_tiles);
+                const int hd = hh % P.H, rs = hh / P.H;
                 const int q0 = (int)((L / HHu) % n_tiles) * kRows;
                 const int start = (q0 + P.off1 - P.left) - P.cl;   // first key row of the item (a multiple of 16)
                 const int sq = it % NQK, sv = it % NV;
@@ -181,7 +183,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                 auto load_rows = [&](uint8_t *dst, uint64_t *bar, const CUtensorMap *whole, const CUtensorMap *own,
                                      const CUtensorMap *prev, const CUtensorMap *next) {
                     if (!pieces) {
-                        ptx::tma_load_4d(dst, whole, bar, 0, hh, start, b);   // (Longformer variant: a box of 224 rows)
+                        ptx::tma_load_5d(dst, whole, bar, 0, hd, rs, start, b);   // (Longformer variant: a box of 224 rows)
                         return;
                     }
                     for (int i = 0; i < KT / 16; ++i) {
@@ -190,7 +192,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                         int row = a;
                         if (a < 0 && P.key_lo < 0) { m = prev; row = P.prev_rows + a; }
                         else if (a >= P.Skv1 && P.key_hi > P.Skv1) { m = next; row = a - P.Skv1; }
-                        ptx::tma_load_4d(dst + i * 16 * kRowBytes, m, bar, 0, hh, row, b);
+                        ptx::tma_load_5d(dst + i * 16 * kRowBytes, m, bar, 0, hd, rs, row, b);
                     }
                 };
                 if (it >= (uint32_t)NQK && !ptx::mbar_wait(qk_empty + sq, (it / NQK - 1) & 1)) {
@@ -200,10 +202,10 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                 TR(0, it, 0);
                 uint8_t *dq = sQK + sq * C::kQKBytes;
                 ptx::mbar_expect_tx(qk_full + sq, C::kQKBytes);
-                ptx::tma_load_4d(dq, &maps.q, qk_full + sq, 0, hh, q0, b);
+                ptx::tma_load_5d(dq, &maps.q, qk_full + sq, 0, hd, rs, q0, b);
                 load_rows(dq + kTQ * kRowBytes, qk_full + sq, &maps.k, &maps.k_own, &maps.k_prev, &maps.k_next);
                 if (LF)   // the keys at the global positions behind the window keys (slots past the list: zeros)
-                    ptx::tma_load_4d(dq + (kTQ + kBandKT) * kRowBytes, &maps.kg, qk_full + sq, 0, hh, 0, b);
+                    ptx::tma_load_5d(dq + (kTQ + kBandKT) * kRowBytes, &maps.kg, qk_full + sq, 0, hd, rs, 0, b);
                 if (it >= (uint32_t)NV && !ptx::mbar_wait(v_empty + sv, (it / NV - 1) & 1)) {
                     atomicExch(&g_band_status, 1);
                     break;
@@ -211,7 +213,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                 TR(0, it, 1);
                 ptx::mbar_expect_tx(v_full + sv, C::kVBytes);
                 load_rows(sV + sv * C::kVBytes, v_full + sv, &maps.v, &maps.v_own, &maps.v_prev, &maps.v_next);
-                if (LF) ptx::tma_load_4d(sV + sv * C::kVBytes + kBandKT * kRowBytes, &maps.vg, v_full + sv, 0, hh, 0, b);
+                if (LF) ptx::tma_load_5d(sV + sv * C::kVBytes + kBandKT * kRowBytes, &maps.vg, v_full + sv, 0, hd, rs, 0, b);
             }
         }
     } else if (warp >= kEpilogueWarp0) {
@@ -225,6 +227,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
             const uint32_t u = i >> 1;
             const uint32_t L = blockIdx.x + i * G;
             const int hh = L % HHu, b = L / (HHu * n_tiles);
+                const int hd = hh % P.H, rs = hh / P.H;
             const int q0 = (int)((L / HHu) % n_tiles) * kRows;
             const uint32_t t_lane = tmem_base + slot * kSlotCols + ((uint32_t)(quad * 32) << 16);
             // ---- the finished row: O and its sum ----
@@ -268,7 +271,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                     if (!ptx::mbar_wait(out_full + slot, u & 1)) {
                         ok = false;
                     } else {
-                        ptx::tma_store_4d(&maps.o, so, 0, hh, q0, b);   // rows past the sequence end are clipped
+                        ptx::tma_store_5d(&maps.o, so, 0, hd, rs, q0, b);   // rows past the sequence end are clipped
                         ptx::tma_store_commit();
                     }
                     TR(2, i, 5);
@@ -335,7 +338,6 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
         for (uint32_t i = slot; ok && i < n_mine; i += 2) {
             const uint32_t u = i >> 1;
             const uint32_t L = blockIdx.x + i * G;
-            const int hh = L % HHu, b = L / (HHu * n_tiles);
             const int q0 = (int)((L / HHu) % n_tiles) * kRows;
             const int start = (q0 + P.off1 - P.left) - P.cl;
             const bool edge = start < P.key_lo || start + kBandKT > P.key_hi;   // some columns lie outside the key line
@@ -538,29 +540,34 @@ template <typename T, int KT, bool LF>
 int launch_band(const Problem &p, const BandParams &bp_in, int64_t dil, const void *kg, const void *vg) {
     BandParams bp = bp_in;
     BandMaps m;
-    const int64_t HH = bp.HH;
     constexpr int kBandKT = LF ? kLfBand : KT;
-    if (int rc = make_row_tensor_map(&m.q, p.q, p.dtype, HH, p.Sq / dil, p.B, kTQ)) return rc;
-    if (int rc = make_row_tensor_map(&m.k, p.k, p.dtype, HH, p.Skv / dil, p.B, kBandKT)) return rc;
-    if (int rc = make_row_tensor_map(&m.v, p.v, p.dtype, HH, p.Skv / dil, p.B, kBandKT)) return rc;
-    if (int rc = make_row_tensor_map(&m.o, p.o, p.dtype, HH, p.Sq / dil, p.B, LF ? kLfRows : kTQ)) return rc;
-    if (int rc = make_row_tensor_map(&m.k_own, p.k, p.dtype, HH, p.Skv / dil, p.B, 16)) return rc;
-    if (int rc = make_row_tensor_map(&m.v_own, p.v, p.dtype, HH, p.Skv / dil, p.B, 16)) return rc;
+    // token strides in bytes: the caller's, or contiguous heads
+    const int64_t contiguous = p.H * 64 * 2;
+    const int64_t TS_q = p.q_ts ? p.q_ts * 2 : contiguous, TS_k = p.k_ts ? p.k_ts * 2 : contiguous;
+    const int64_t TS_v = p.v_ts ? p.v_ts * 2 : contiguous, TS_o = p.o_ts ? p.o_ts * 2 : contiguous;
+    const int64_t TS_k_own = TS_k, TS_v_own = TS_v;
+    const int64_t TS_k_prev = contiguous, TS_v_prev = contiguous, TS_k_next = contiguous, TS_v_next = contiguous;
+    if (int rc = make_row_tensor_map5(&m.q, p.q, p.dtype, p.H, dil, p.Sq / dil, p.B, kTQ, TS_q)) return rc;
+    if (int rc = make_row_tensor_map5(&m.k, p.k, p.dtype, p.H, dil, p.Skv / dil, p.B, kBandKT, TS_k)) return rc;
+    if (int rc = make_row_tensor_map5(&m.v, p.v, p.dtype, p.H, dil, p.Skv / dil, p.B, kBandKT, TS_v)) return rc;
+    if (int rc = make_row_tensor_map5(&m.o, p.o, p.dtype, p.H, dil, p.Sq / dil, p.B, LF ? kLfRows : kTQ, TS_o)) return rc;
+    if (int rc = make_row_tensor_map5(&m.k_own, p.k, p.dtype, p.H, dil, p.Skv / dil, p.B, 16, TS_k_own)) return rc;
+    if (int rc = make_row_tensor_map5(&m.v_own, p.v, p.dtype, p.H, dil, p.Skv / dil, p.B, 16, TS_v_own)) return rc;
     m.k_prev = m.k_next = m.k_own;
     m.v_prev = m.v_next = m.v_own;
     if (p.k_prev) {
-        if (int rc = make_row_tensor_map(&m.k_prev, p.k_prev, p.dtype, HH, p.S_prev / dil, p.B, 16)) return rc;
-        if (int rc = make_row_tensor_map(&m.v_prev, p.v_prev, p.dtype, HH, p.S_prev / dil, p.B, 16)) return rc;
+        if (int rc = make_row_tensor_map5(&m.k_prev, p.k_prev, p.dtype, p.H, dil, p.S_prev / dil, p.B, 16, TS_k_prev)) return rc;
+        if (int rc = make_row_tensor_map5(&m.v_prev, p.v_prev, p.dtype, p.H, dil, p.S_prev / dil, p.B, 16, TS_v_prev)) return rc;
     }
     if (p.k_next) {
-        if (int rc = make_row_tensor_map(&m.k_next, p.k_next, p.dtype, HH, p.S_next / dil, p.B, 16)) return rc;
-        if (int rc = make_row_tensor_map(&m.v_next, p.v_next, p.dtype, HH, p.S_next / dil, p.B, 16)) return rc;
+        if (int rc = make_row_tensor_map5(&m.k_next, p.k_next, p.dtype, p.H, dil, p.S_next / dil, p.B, 16, TS_k_next)) return rc;
+        if (int rc = make_row_tensor_map5(&m.v_next, p.v_next, p.dtype, p.H, dil, p.S_next / dil, p.B, 16, TS_v_next)) return rc;
     }
     m.kg = m.k_own;
     m.vg = m.v_own;
     if (LF) {
-        if (int rc = make_row_tensor_map(&m.kg, kg, p.dtype, HH, bp.n_global, p.B, kLfGlobals)) return rc;
-        if (int rc = make_row_tensor_map(&m.vg, vg, p.dtype, HH, bp.n_global, p.B, kLfGlobals)) return rc;
+        if (int rc = make_row_tensor_map5(&m.kg, kg, p.dtype, p.H, 1, bp.n_global, p.B, kLfGlobals, contiguous)) return rc;
+        if (int rc = make_row_tensor_map5(&m.vg, vg, p.dtype, p.H, 1, bp.n_global, p.B, kLfGlobals, contiguous)) return rc;
     }
     auto kern = umma_band_kernel<T, KT, LF>;
     constexpr size_t smem = BandCfg<KT>::kSmemBytes;
@@ -593,6 +600,7 @@ int plan_band(const Problem &p, BandParams &bp, bool longformer) {
     bp.right = (int32_t)std::min<int64_t>(p.pat.right, bp.Skv1 + next_rows);
     bp.cl = (((bp.off1 - bp.left) % 16) + 16) % 16;
     bp.HH = (int32_t)(p.H * dil);
+    bp.H = (int32_t)p.H;
     bp.n_tiles = (bp.Sq1 + rows - 1) / rows;
     bp.sl2 = p.scale * 1.4426950408889634f;
     bp.n_global = longformer ? (int32_t)p.pat.n_global : 0;
@@ -607,10 +615,9 @@ int plan_band(const Problem &p, BandParams &bp, bool longformer) {
 
 }  // namespace
 
-// Windows of at most 128 taps between their two sides on 16-bit inputs with head width 64.
-// MAT_WINDOW_KERNEL=mma keeps them on the warp-level kernels, MAT_WINDOW_KERNEL=band sends every window
-// the band kernel can take to it whatever the size (debugging and measurement aids).
-bool umma_band_supports(const Problem &p) {
+// Whether the band kernel can run the problem at all (shape, dtype, alignment, window width), leaving aside
+// which kernel is the faster one for its size.
+bool umma_band_fits(const Problem &p) {
     if (p.pat.kind != MAT_WINDOW) return false;
     if (p.dtype != MAT_BF16 && p.dtype != MAT_F16) return false;
     if (p.D != 64) return false;
@@ -619,6 +626,15 @@ bool umma_band_supports(const Problem &p) {
     const int64_t dil = p.pat.dilation;
     if (p.Sq % dil || p.Skv % dil || p.pat.q_offset % dil) return false;
     if (p.Skv / dil >= (1LL << 28) || p.H * dil >= (1LL << 24) || p.B > 65535) return false;
+    BandParams bp;
+    return plan_band(p, bp, false) != 0;
+}
+
+// Windows of at most 128 taps between their two sides on 16-bit inputs with head width 64.
+// MAT_WINDOW_KERNEL=mma keeps them on the warp-level kernels, MAT_WINDOW_KERNEL=band sends every window
+// the band kernel can take to it whatever the size (debugging and measurement aids).
+bool umma_band_supports(const Problem &p) {
+    if (!umma_band_fits(p)) return false;
     const char *force = std::getenv("MAT_WINDOW_KERNEL");
     if (force && std::strcmp(force, "mma") == 0) return false;
     BandParams bp;

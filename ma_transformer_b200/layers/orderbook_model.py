@@ -7,9 +7,11 @@ The block follows the reference's integration example
 (examples/pytorch_integration_example.py:21-107: q/k/v/out projections around
 ``MACoreAttention`` on [batch, seq, heads, head_dim]) and its model skeleton
 (src/model.py:55-87: input projection, encoder layers, head on the last token).
-The projections are plain library GEMMs; their outputs are already the
-[B, S, H, 64] layout the attention kernels read, so no transpose or copy sits
-between a projection and the attention.
+The projections are plain library GEMMs.  Q, K and V come out of ONE fused projection
+[d_model -> 3*d_model]; its output [B, S, 3, H, 64] is handed to the attention kernel as three
+views (token stride 3*H*64), so no split, transpose or copy sits between the projection and the
+attention, and the attention output [B, S, H, 64] is already the [B, S, d_model] the output
+projection reads.
 """
 from __future__ import annotations
 
@@ -20,6 +22,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .. import sparse_attention_cuda
 from ..patterns import PatternSpec
 from .ma_core_bridge import MACoreAttention
 
@@ -46,9 +49,7 @@ class DilatedAttentionBlock(nn.Module):
         super().__init__()
         assert d_model % n_heads == 0
         self.n_heads, self.head_dim = n_heads, d_model // n_heads
-        self.q_proj = nn.Linear(d_model, d_model)
-        self.k_proj = nn.Linear(d_model, d_model)
-        self.v_proj = nn.Linear(d_model, d_model)
+        self.qkv_proj = nn.Linear(d_model, 3 * d_model)   # rows [0, d) -> Q, [d, 2d) -> K, [2d, 3d) -> V
         self.out_proj = nn.Linear(d_model, d_model)
         self.attention = MACoreAttention(sparse=True, window_size=max(1, pattern.left), pattern=pattern,
                                          fallback_training=False)
@@ -60,9 +61,15 @@ class DilatedAttentionBlock(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         B, S, Dm = x.shape
         y = self.norm1(x)
-        shape = (B, S, self.n_heads, self.head_dim)
-        q, k, v = self.q_proj(y).view(shape), self.k_proj(y).view(shape), self.v_proj(y).view(shape)
-        x = x + self.out_proj(self.attention(q, k, v).view(B, S, Dm))
+        qkv = self.qkv_proj(y).view(B, S, 3, self.n_heads, self.head_dim)
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]      # views: token stride 3 * d_model
+        strided_ok = (q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and self.head_dim == 64
+                      and not (torch.is_grad_enabled() and qkv.requires_grad))
+        if strided_ok:   # the kernel reads the three views in place
+            a = sparse_attention_cuda.forward_strided(q, k, v, self.attention.pattern)
+        else:            # fp32, other head widths, or a graph to differentiate: the module (packed copies)
+            a = self.attention(q, k, v)
+        x = x + self.out_proj(a.reshape(B, S, Dm))
         return x + self.ff2(F.gelu(self.ff1(self.norm2(x))))
 
 

@@ -95,6 +95,51 @@ def forward_pattern(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
     return out
 
 
+def _token_stride(t: torch.Tensor) -> Optional[int]:
+    """Elements between consecutive tokens of a [B, S, H, D] tensor whose heads and head columns are packed
+    and whose batch items follow each other (a view of a fused projection output), or None."""
+    B, S, H, D = t.shape
+    if t.stride(3) != 1 or t.stride(2) != D:
+        return None
+    ts = t.stride(1)
+    if ts < H * D or ts % 8 or (B > 1 and t.stride(0) != S * ts):
+        return None
+    return int(ts)
+
+
+def forward_strided(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, spec: PatternSpec,
+                    scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``forward_pattern`` for tensors whose tokens are not packed: views of one fused projection output
+    [B, S, 3, H, D] (``qkv[:, :, 0]`` and so on) go to the kernels as they are, without the copy that
+    ``.contiguous()`` would make.  Heads and head columns must be packed; window patterns of at most 128 taps,
+    16-bit dtypes, D = 64.  ``out`` defaults to a packed tensor."""
+    for t in (query, key, value):
+        if not t.is_cuda:
+            raise RuntimeError("Inputs must be CUDA tensors")
+        if t.dim() != 4:
+            raise RuntimeError("Expected shape [B, S, H, D]")
+    if query.dtype not in _DTYPES or key.dtype != query.dtype or value.dtype != query.dtype:
+        raise RuntimeError("Only float32, bfloat16 and float16 are supported in CUDA path (all inputs of one dtype)")
+    if key.shape != value.shape or query.shape[0] != key.shape[0] or query.shape[2:] != key.shape[2:]:
+        raise RuntimeError("Q,K,V must have same shape (key/value may only differ from query in length)")
+    B, Sq, H, D = query.shape
+    Skv = key.shape[1]
+    spec.check_against(Skv)
+    if out is None:
+        out = torch.empty((B, Sq, H, D), dtype=query.dtype, device=query.device)
+    strides = [_token_stride(t) for t in (query, key, value, out)]
+    if any(s is None for s in strides):
+        raise RuntimeError("Inputs must be contiguous, or views with packed heads and a uniform token stride "
+                           "that is a multiple of 8 elements")
+    with torch.cuda.device(query.device):
+        s = spec.device_struct(query.device)
+        stream = torch.cuda.current_stream(query.device).cuda_stream
+        nat.check(nat.lib.mat_sparse_attn_fwd_strided(
+            query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(), B, Sq, Skv, H, D,
+            _DTYPES[query.dtype], C.byref(s), float(scale) if scale else 0.0, *strides, C.c_void_p(stream)))
+    return out
+
+
 def forward_sharded(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, spec: PatternSpec,
                     prev_kv=None, next_kv=None, scale: Optional[float] = None,
                     out: Optional[torch.Tensor] = None) -> torch.Tensor:

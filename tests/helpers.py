@@ -86,8 +86,7 @@ def orderbook_reference_forward(model, ticks: torch.Tensor) -> torch.Tensor:
     for blk in model.blocks:
         B, _, Dm = x.shape
         y = blk.norm1(x)
-        shape = (B, S, blk.n_heads, blk.head_dim)
-        q, k, v = blk.q_proj(y).view(shape), blk.k_proj(y).view(shape), blk.v_proj(y).view(shape)
+        q, k, v = blk.qkv_proj(y).view(B, S, 3, blk.n_heads, blk.head_dim).unbind(2)
         s = torch.einsum("bihd,bjhd->bhij", q, k) / math.sqrt(blk.head_dim)
         s = s.masked_fill(~keep, float("-inf"))
         a = torch.einsum("bhij,bjhd->bihd", torch.softmax(s, dim=-1), v).reshape(B, S, Dm)

@@ -89,6 +89,35 @@ def test_mma_window_vs_oracle(spec, dtype, B, S, H):
     check_close(got, oracle_out(q, k, v, spec), dtype)
 
 
+@pytest.mark.parametrize("spec", [PatternSpec.causal_window(64), PatternSpec.causal_window(64, dilation=2),
+                                  PatternSpec.sliding_window(64), PatternSpec(left=3, right=40, dilation=3)],
+                         ids=["causal64", "dil2", "pm64", "dil3"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_views_of_a_fused_projection_are_read_in_place(spec, dtype):
+    """q, k, v as views of one [B, S, 3, H, 64] tensor (token stride 3*H*64) through the strided entry point:
+    bit-identical to the same values passed as packed tensors, and right against the oracle; a strided
+    output view as well."""
+    B, S, H = 2, 768, 3
+    g = torch.Generator().manual_seed(19)
+    qkv = torch.randn(B, S, 3, H, 64, generator=g).to(dtype).to(DEV)
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    assert not q.is_contiguous()
+    got = ext.forward_strided(q, k, v, spec)
+    torch.cuda.synchronize()
+    assert nat.last_kernel() == "umma_band"
+    packed = ext.forward_pattern(q.contiguous(), k.contiguous(), v.contiguous(), spec)
+    assert torch.equal(got, packed)
+    check_close(got, oracle_out(q.cpu().contiguous(), k.cpu().contiguous(), v.cpu().contiguous(), spec), dtype)
+    wide = torch.full((B, S, 2, H, 64), float("nan"), dtype=dtype, device=DEV)
+    ext.forward_strided(q, k, v, spec, out=wide[:, :, 1])
+    assert torch.equal(wide[:, :, 1], packed) and bool(torch.isnan(wide[:, :, 0]).all())
+    # what the strided entry point does not take is refused, not copied behind the caller's back
+    with pytest.raises(RuntimeError, match="token-strided"):
+        ext.forward_strided(q, k, v, PatternSpec.sliding_window(300))
+    with pytest.raises(RuntimeError):
+        ext.forward_strided(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), spec)
+
+
 def test_window_kernel_choice_by_size(monkeypatch):
     """Without MAT_WINDOW_KERNEL the library sends small narrow-window problems to the warp-level kernel (the
     persistent kernel's start-up and drain would dominate) and large ones to the persistent tcgen05 kernel;
