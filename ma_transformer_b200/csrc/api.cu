@@ -131,6 +131,7 @@ int run_problem(const Problem &p) {
         }
         return launch_mma_flash(p);
     }
+    if (tiled_f32_supports(p)) return launch_tiled_f32(p);
     return launch_rowwarp(p);
 }
 
@@ -189,6 +190,9 @@ int mat_device_status(int *status_out) {
     if (int rc = umma_status_read_and_clear(&b)) return rc;
     if (int rc = bwd_status_read_and_clear(&c)) return rc;
     if (int rc = band_status_read_and_clear(&d)) return rc;
+    int e = 0;
+    if (int rc = tiled_status_read_and_clear(&e)) return rc;
+    d |= e;
     *status_out = a | b | c | d;
     return MAT_OK;
 }

@@ -44,7 +44,32 @@ def test_cfg1_causal_window_fp32():
     spec = PatternSpec.causal_window(32)
     q, k, v = seeded_qkv(1, 1, 1024, 4, 64)
     check_close(run(spec, q, k, v), oracle_out(q, k, v, spec), torch.float32)
+    assert nat.last_kernel() == "tiled_f32"
     check_close(run(spec, q, k, v, scale=0.125), oracle_out(q, k, v, spec, 0.125), torch.float32)
+
+
+@pytest.mark.parametrize("D", [32, 64, 128])
+@pytest.mark.parametrize("spec", [PatternSpec.causal_window(32), PatternSpec.sliding_window(64), PatternSpec.sliding_window(3),
+                                  PatternSpec(left=0, right=60), PatternSpec.causal_window(64, dilation=2),
+                                  PatternSpec(left=100, right=28), PatternSpec.causal_window(1)],
+                         ids=lambda s: f"l{s.left}r{s.right}d{s.dilation}")
+def test_tiled_fp32_kernel_vs_oracle(spec, D):
+    """fp32 windows of at most 128 taps with head width 32, 64 or 128 on the tiled kernel (64- or 128-row tiles,
+    K/V window staged once per tile), ragged lengths and shard offsets included; fp32 bar 1e-5."""
+    for B, S, H, off in [(1, 1024, 2, 0), (2, 330, 3, 0), (1, 64, 1, 0), (1, 200, 2, 48), (1, 7, 1, 0)]:
+        S = S - S % spec.dilation if S >= spec.dilation else spec.dilation
+        off = off - off % spec.dilation
+        sp = spec.shifted(off)
+        q, k, v = seeded_qkv(23, B, S, H, D, torch.float32, Skv=S + off + 3 * spec.dilation)
+        got = run(sp, q, k, v)
+        skv1 = (S + off + 3 * spec.dilation) // spec.dilation          # taps clamp to the keys that exist
+        wide_here = min(spec.left, skv1) + min(spec.right, skv1) > 64
+        assert nat.last_kernel() == ("rowwarp" if D == 128 and wide_here else "tiled_f32")
+        check_close(got, oracle_out(q, k, v, sp), torch.float32)
+    # inputs x100 stay finite and close (tests/integration/test_cuda_extensive.py:77-92)
+    q, k, v = seeded_qkv(24, 1, 130, 2, D, torch.float32, scale=100.0)
+    got = run(spec, q, k, v).cpu().numpy()
+    assert np.isfinite(got).all() and np.abs(got - oracle_out(q, k, v, spec)).max() <= 0.5
 
 
 @pytest.mark.parametrize("B,S,H,D", [(1, 1, 1, 1), (1, 7, 2, 5), (2, 33, 1, 13), (1, 100, 3, 40), (1, 65, 2, 96),
@@ -247,8 +272,8 @@ def test_shard_with_halo_equals_full_run(spec, dtype):
         part = run(spec.shifted(r * chunk - lo), q[:, r * chunk:(r + 1) * chunk].contiguous(),
                    k[:, lo:hi].contiguous(), v[:, lo:hi].contiguous())
         ref = full[:, r * chunk:(r + 1) * chunk]
-        if dtype == torch.float32:   # row-warp kernel: same key order per row, bit-identical
-            assert torch.equal(part, ref), f"shard {r}"
+        if dtype == torch.float32:   # same key order per row; the row sums regroup with the shard's origin (last-bit effects)
+            assert (part - ref).abs().max() <= 1e-6 * float(ref.abs().max()), f"shard {r}"
         else:  # tiled kernel: key chunks align to the shard's own origin, so sums regroup (a few bf16 ulps)
             assert (part.float() - ref.float()).abs().max() <= 2 ** -6, f"shard {r}"
     check_close(full, oracle_out(q, k, v, spec), dtype)
