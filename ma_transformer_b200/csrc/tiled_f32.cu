@@ -47,6 +47,23 @@ struct TiledParams {
     float sl2;                 // scale * log2(e)
 };
 
+// Two fp32 FMAs in one instruction on a pair of registers: d = a * b + d, lane-wise on (lo, hi).
+// Half the issue slots of scalar FMAs; this kernel is bound by instruction issue.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ void fma2(f32x2 &d, f32x2 a, f32x2 b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
+}
+__device__ __forceinline__ f32x2 dup2(float x) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float2 unpack2(f32x2 v) {
+    float2 r;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+    return r;
+}
+
 // byte offset of float f (0..31) of row r inside a 128-byte-swizzled sub-tile
 __device__ __forceinline__ uint32_t swz_f(int r, int f) {
     return (uint32_t)(r * kSubBytes + (((f >> 2) ^ (r & 7)) << 4) + ((f & 3) << 2));
@@ -108,35 +125,53 @@ tiled_f32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
     for (int s = 0; s < NS; ++s) kr[s] = min(row0 + lane + 32 * s, KBOX - 1);   // beyond the tile: masked below
 
-    // ---- scores: acc[r][s] = q_(row0 + r) . k_(kr[s]) ----
+    // ---- scores: acc[r][s] = q_(row0 + r) . k_(kr[s]); even and odd head columns are summed apart (packed
+    // FMAs on the (x, y) and (z, w) halves of every 16-byte load) and joined at the end ----
     float acc[R][NS];
+    {
+        f32x2 acc2[R][NS];
 #pragma unroll
-    for (int r = 0; r < R; ++r)
+        for (int r = 0; r < R; ++r)
 #pragma unroll
-        for (int s = 0; s < NS; ++s) acc[r][s] = 0.f;
+            for (int s = 0; s < NS; ++s) acc2[r][s] = 0ull;
+        // row kr[s] of sub-tile `sub`, 16-byte chunk c: base + c * 16 xor (kr & 7) * 16
+        const uint8_t *kbase[NS];
+        uint32_t kx[NS];
 #pragma unroll
-    for (int sub = 0; sub < NSUB; ++sub) {
-        const uint8_t *kq = sK + sub * KBOX * kSubBytes;
-        const uint8_t *qq = sQ + sub * kTQ * kSubBytes + row0 * kSubBytes;
-#pragma unroll 2
-        for (int c = 0; c < 8; ++c) {          // 4 head columns per step
-            float4 kf[NS];
+        for (int s = 0; s < NS; ++s) {
+            kbase[s] = sK + kr[s] * kSubBytes;
+            kx[s] = (uint32_t)(kr[s] & 7) << 4;
+        }
+        // (the sub-tile loop stays rolled and the key loop below is unrolled by 8 only: the loop bodies must stay
+        // well inside the instruction cache)
+#pragma unroll 1
+        for (int sub = 0; sub < NSUB; ++sub) {
+            const uint8_t *qq = sQ + sub * kTQ * kSubBytes + row0 * kSubBytes;
 #pragma unroll
-            for (int s = 0; s < NS; ++s)
-                kf[s] = *reinterpret_cast<const float4 *>(kq + kr[s] * kSubBytes + ((c ^ (kr[s] & 7)) << 4));
+            for (int c = 0; c < 8; ++c) {          // 4 head columns per step
+                ulonglong2 kf[NS];
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                // row0 is a multiple of 8, so (row0 + r) & 7 == r & 7; every lane reads the same 16 bytes (a broadcast)
-                const float4 qf = *reinterpret_cast<const float4 *>(qq + r * kSubBytes + ((c ^ (r & 7)) << 4));
+                for (int s = 0; s < NS; ++s)
+                    kf[s] = *reinterpret_cast<const ulonglong2 *>(kbase[s] + sub * KBOX * kSubBytes + (((uint32_t)c << 4) ^ kx[s]));
 #pragma unroll
-                for (int s = 0; s < NS; ++s) {
-                    acc[r][s] = fmaf(qf.x, kf[s].x, acc[r][s]);
-                    acc[r][s] = fmaf(qf.y, kf[s].y, acc[r][s]);
-                    acc[r][s] = fmaf(qf.z, kf[s].z, acc[r][s]);
-                    acc[r][s] = fmaf(qf.w, kf[s].w, acc[r][s]);
+                for (int r = 0; r < R; ++r) {
+                    // row0 is a multiple of 8, so (row0 + r) & 7 == r & 7; every lane reads the same 16 bytes (a broadcast)
+                    const ulonglong2 qf = *reinterpret_cast<const ulonglong2 *>(qq + r * kSubBytes + ((c ^ (r & 7)) << 4));
+#pragma unroll
+                    for (int s = 0; s < NS; ++s) {
+                        fma2(acc2[r][s], qf.x, kf[s].x);
+                        fma2(acc2[r][s], qf.y, kf[s].y);
+                    }
                 }
             }
         }
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int s = 0; s < NS; ++s) {
+                const float2 h = unpack2(acc2[r][s]);
+                acc[r][s] = h.x + h.y;
+            }
     }
 
     // ---- mask, softmax statistics; the weights replace the scores ----
@@ -169,55 +204,71 @@ tiled_f32_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         inv_l[r] = l > 0.f ? 1.f / l : 0.f;
     }
 
-    // ---- the weights to shared memory (over the Q and K tiles where they fit): pw[r][32 s + lane] ----
+    // ---- the weights to shared memory (over the Q and K tiles where they fit), key-major: pw[32 s + lane][r],
+    // so that one 16-byte load brings one key's weights for four rows, already paired for the packed FMAs ----
+    static_assert(R == 8, "the weight layout below is written for 8 rows per warp");
     __syncthreads();   // every warp has read its last Q and K row
     float *pw = reinterpret_cast<float *>(weights_alias<D, TQ, NS, KBOX>() ? sQ : (uint8_t *)(bar + 2)) +
                 warp * (R * NS * 32);
 #pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int s = 0; s < NS; ++s) pw[r * (NS * 32) + 32 * s + lane] = acc[r][s];
+    for (int s = 0; s < NS; ++s) {
+        float4 *dst = reinterpret_cast<float4 *>(pw + (32 * s + lane) * R);
+        dst[0] = make_float4(acc[0][s], acc[1][s], acc[2][s], acc[3][s]);
+        dst[1] = make_float4(acc[4][s], acc[5][s], acc[6][s], acc[7][s]);
+    }
     __syncwarp();
 
-    // ---- output: o[r][.] = sum_j w[r][j] v_(row0 + j), lane l owns columns DPL l .. DPL l + DPL - 1 ----
+    // ---- output: o[r][.] = sum_j w[j][r] v_(row0 + j); lane l owns columns DPL l .. DPL l + DPL - 1 of all 8
+    // rows, held as pairs of rows ----
+    f32x2 o2[R / 2][DPL];
+#pragma unroll
+    for (int rp = 0; rp < R / 2; ++rp)
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) o2[rp][e] = 0ull;
+    const int d0 = lane * DPL;
+    const int f0 = d0 & 31;
+    // staged row row0 + j of the lane's sub-tile: vrow + j * 128 + (chunk xor (j & 7)) * 16, row0 a multiple of 8
+    const uint8_t *vrow = sV + (d0 >> 5) * KBOX * kSubBytes + row0 * kSubBytes + ((f0 & 3) << 2);
+    uint32_t vx[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) vx[t] = (uint32_t)(((f0 >> 2) ^ t) << 4);
+    const int n_keys = R + span;      // staged rows this warp's rows can see (never past the tile: KBOX >= TQ + span)
+#pragma unroll 1
+    for (int j8 = 0; j8 < n_keys; j8 += 8) {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        const int j = j8 + t;                        // (j & 7) == t; keys past the window carry zero weights
+        const float *src = reinterpret_cast<const float *>(vrow + j * kSubBytes + vx[t]);
+        f32x2 vv[DPL];
+        if constexpr (DPL == 1) {
+            vv[0] = dup2(src[0]);
+        } else if constexpr (DPL == 2) {
+            const float2 x = *reinterpret_cast<const float2 *>(src);
+            vv[0] = dup2(x.x); vv[1] = dup2(x.y);
+        } else {
+            const float4 x = *reinterpret_cast<const float4 *>(src);
+            vv[0] = dup2(x.x); vv[1] = dup2(x.y); vv[2] = dup2(x.z); vv[3] = dup2(x.w);
+        }
+        const ulonglong2 wa = *reinterpret_cast<const ulonglong2 *>(pw + j * R);       // rows 0..3 (broadcast)
+        const ulonglong2 wb = *reinterpret_cast<const ulonglong2 *>(pw + j * R + 4);   // rows 4..7
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+            fma2(o2[0][e], wa.x, vv[e]);
+            fma2(o2[1][e], wa.y, vv[e]);
+            fma2(o2[2][e], wb.x, vv[e]);
+            fma2(o2[3][e], wb.y, vv[e]);
+        }
+      }
+    }
     float o[R][DPL];
 #pragma unroll
-    for (int r = 0; r < R; ++r)
+    for (int rp = 0; rp < R / 2; ++rp)
 #pragma unroll
-        for (int e = 0; e < DPL; ++e) o[r][e] = 0.f;
-    const int d0 = lane * DPL;
-    const uint8_t *vq = sV + (d0 >> 5) * KBOX * kSubBytes;
-    const int f0 = d0 & 31;
-    const int n_keys = min(R + span, KBOX - row0);      // staged rows this warp's rows can see
-#pragma unroll 1
-    for (int j4 = 0; j4 < n_keys; j4 += 4) {
-        float vv[4][DPL];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            const int j = min(row0 + j4 + t, KBOX - 1);   // past the tile: its weight is zero
-            const float *src = reinterpret_cast<const float *>(vq + swz_f(j, f0));
-            if constexpr (DPL == 1) {
-                vv[t][0] = src[0];
-            } else if constexpr (DPL == 2) {
-                const float2 x = *reinterpret_cast<const float2 *>(src);
-                vv[t][0] = x.x; vv[t][1] = x.y;
-            } else {
-                const float4 x = *reinterpret_cast<const float4 *>(src);
-                vv[t][0] = x.x; vv[t][1] = x.y; vv[t][2] = x.z; vv[t][3] = x.w;
-            }
+        for (int e = 0; e < DPL; ++e) {
+            const float2 h = unpack2(o2[rp][e]);
+            o[2 * rp][e] = h.x;
+            o[2 * rp + 1][e] = h.y;
         }
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const float4 w4 = *reinterpret_cast<const float4 *>(pw + r * (NS * 32) + j4);   // broadcast
-#pragma unroll
-            for (int e = 0; e < DPL; ++e) {
-                o[r][e] = fmaf(w4.x, vv[0][e], o[r][e]);
-                o[r][e] = fmaf(w4.y, vv[1][e], o[r][e]);
-                o[r][e] = fmaf(w4.z, vv[2][e], o[r][e]);
-                o[r][e] = fmaf(w4.w, vv[3][e], o[r][e]);
-            }
-        }
-    }
 
     // ---- normalise and store: a row is D contiguous floats, the warp writes it whole ----
 #pragma unroll
