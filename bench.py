@@ -12,7 +12,9 @@ K/V rows they need from the neighbouring GPU inside the kernel (``--halo nccl``
 exchanges them by send/recv instead).  Steps are independent forwards over
 rotating input sets; they are captured in CUDA graphs and alternate over two
 streams (``--lanes``), each with its own output buffer.
-``--workload block|longformer|orderbook|dense|backward`` time the other configurations on one GPU.
+``--workload block|longformer|orderbook|dense|backward|fp32|refwindow`` time the other configurations on one GPU
+(refwindow: the reference's default window_size = 64, i.e. keys i-64 .. i+64, at the headline shape); each of them
+compares sampled row blocks of its last timed launch with the CPU oracle after the timed region.
 
 Prints ONE JSON line.  ``value`` is tokens/s with inputs resident in HBM, timed
 with CUDA events over exactly K steps (max over ranks); ``e2e`` is the same
@@ -629,6 +631,14 @@ def other_workload_arm(args):
         spec = PatternSpec.block_sparse(64, rp, ci, causal=True)
         flops = Bw * Hw * int(rp[-1]) * 4 * 64 ** 3
         name = f"block-sparse fwd B={Bw} N={S} H={Hw} d=64 block=64 band4+2 random causal bf16"
+    elif args.workload == "refwindow":
+        # the window every unmodified caller of the reference gets: window_size = 64, keys i-64 .. i+64
+        # (src/layers/ma_core_bridge.py:259), at the headline shape; --left / --right / --dilation change it
+        Bw, S, Hw = B, SEQ, H
+        spec = PatternSpec(left=args.left, right=args.right, dilation=args.dilation)
+        flops = Bw * Hw * S * (args.left + args.right + 1) * 4 * 64
+        name = (f"window fwd B={Bw} N={S} H={Hw} d=64 taps -{args.left}..+{args.right}"
+                + (f" dilation {args.dilation}" if args.dilation > 1 else "") + " bf16")
     elif args.workload == "dense":
         # the reference's dense_forward (every query over every key), the tensor-bound end of the path
         Bw, S, Hw = 2, 8192, 8
@@ -692,9 +702,12 @@ def other_workload_arm(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="window", choices=["window", "block", "longformer", "orderbook", "dense", "backward", "fp32"],
+    ap.add_argument("--workload", default="window", choices=["window", "block", "longformer", "orderbook", "dense", "backward", "fp32", "refwindow"],
                     help="window = the headline configuration; block / longformer / orderbook / dense = one-GPU timing "
                          "of the block-sparse, Longformer, order-book-transformer and dense configurations")
+    ap.add_argument("--left", type=int, default=64, help="refwindow: taps before the query")
+    ap.add_argument("--right", type=int, default=64, help="refwindow: taps after the query")
+    ap.add_argument("--dilation", type=int, default=1, help="refwindow: dilation")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)

@@ -134,7 +134,60 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    if (threadIdx.x == 0) {
+    // ---- the TMA lane's work for item `it` of this CTA: {Q, K} and V into their rings ----
+    const uint32_t G = gridDim.x, HHu = (uint32_t)P.HH, n_tiles = (uint32_t)P.n_tiles;
+    const uint32_t n_mine = blockIdx.x < P.n_items ? (P.n_items - blockIdx.x + G - 1) / G : 0;   // items of this CTA
+    auto produce = [&](uint32_t it) -> bool {
+        const uint32_t L = blockIdx.x + it * G;
+        const int hh = L % HHu, b = L / (HHu * n_tiles);
+        const int hd = hh % P.H, rs = hh / P.H;
+        const int q0 = (int)((L / HHu) % n_tiles) * kRows;
+        const int start = (q0 + P.off1 - P.left) - P.cl;   // first key row of the item (a multiple of 16)
+        const int sq = it % NQK, sv = it % NV;
+        // a stage that crosses into a neighbour shard's rows is fetched 16 rows at a time, each
+        // piece from the tensor that owns it
+        const bool pieces = !LF && ((start < 0 && P.key_lo < 0) || (start + KT > P.Skv1 && P.key_hi > P.Skv1));
+        auto load_rows = [&](uint8_t *dst, uint64_t *bar, const CUtensorMap *whole, const CUtensorMap *own,
+                             const CUtensorMap *prev, const CUtensorMap *next) {
+            if (!pieces) {
+                ptx::tma_load_5d(dst, whole, bar, 0, hd, rs, start, b);   // (Longformer variant: a box of 224 rows)
+                return;
+            }
+            for (int i = 0; i < KT / 16; ++i) {
+                const int a = start + 16 * i;
+                const CUtensorMap *m = own;
+                int row = a;
+                if (a < 0 && P.key_lo < 0) { m = prev; row = P.prev_rows + a; }
+                else if (a >= P.Skv1 && P.key_hi > P.Skv1) { m = next; row = a - P.Skv1; }
+                ptx::tma_load_5d(dst + i * 16 * kRowBytes, m, bar, 0, hd, rs, row, b);
+            }
+        };
+        if (it >= (uint32_t)NQK && !ptx::mbar_wait(qk_empty + sq, (it / NQK - 1) & 1)) {
+            atomicExch(&g_band_status, 1);
+            return false;
+        }
+        TR(0, it, 0);
+        uint8_t *dq = sQK + sq * C::kQKBytes;
+        ptx::mbar_expect_tx(qk_full + sq, C::kQKBytes);
+        ptx::tma_load_5d(dq, &maps.q, qk_full + sq, 0, hd, rs, q0, b);
+        load_rows(dq + kTQ * kRowBytes, qk_full + sq, &maps.k, &maps.k_own, &maps.k_prev, &maps.k_next);
+        if (LF)   // the keys at the global positions behind the window keys (slots past the list: zeros)
+            ptx::tma_load_5d(dq + (kTQ + kBandKT) * kRowBytes, &maps.kg, qk_full + sq, 0, hd, rs, 0, b);
+        if (it >= (uint32_t)NV && !ptx::mbar_wait(v_empty + sv, (it / NV - 1) & 1)) {
+            atomicExch(&g_band_status, 1);
+            return false;
+        }
+        TR(0, it, 1);
+        ptx::mbar_expect_tx(v_full + sv, C::kVBytes);
+        load_rows(sV + sv * C::kVBytes, v_full + sv, &maps.v, &maps.v_own, &maps.v_prev, &maps.v_next);
+        if (LF) ptx::tma_load_5d(sV + sv * C::kVBytes + kBandKT * kRowBytes, &maps.vg, v_full + sv, 0, hd, rs, 0, b);
+        return true;
+    };
+    constexpr uint32_t kEarly = NQK < NV ? NQK : NV;   // items whose copies need no stage to be handed back first
+
+    if (warp == kSoftmaxWarps + 2 && lane == 0) {
+        // The TMA lane sets the barriers up itself and starts the copies of its first items at once: they are in
+        // flight while the rest of the CTA allocates tensor memory and meets at the barrier below.
         for (int i = 0; i < NQK; ++i) { ptx::mbar_init(qk_full + i, 1); ptx::mbar_init(qk_empty + i, 1); }
         for (int i = 0; i < NV; ++i) { ptx::mbar_init(v_full + i, 1); ptx::mbar_init(v_empty + i, 1); }
         for (int i = 0; i < 2; ++i) {
@@ -146,6 +199,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
             ptx::mbar_init(out_free + i, 1);
         }
         ptx::fence_barrier_init();
+        for (uint32_t it = 0; it < kEarly && it < n_mine; ++it) produce(it);
     }
     if (LF && threadIdx.x < kLfGlobals)
         sG[threadIdx.x] = (int)threadIdx.x < P.n_global ? (int32_t)P.gidx[threadIdx.x] : kNoGlobal;
@@ -163,58 +217,11 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const uint32_t G = gridDim.x, HHu = (uint32_t)P.HH, n_tiles = (uint32_t)P.n_tiles;
-    // items of this CTA
-    const uint32_t n_mine = blockIdx.x < P.n_items ? (P.n_items - blockIdx.x + G - 1) / G : 0;
-
     if (warp == kSoftmaxWarps + 2) {
-        // ================= TMA lane: {Q, K} and V of item it into their rings =================
+        // ================= TMA lane: the items after the ones it started before the CTA was set up =================
         if (lane == 0) {
-            for (uint32_t it = 0; it < n_mine; ++it) {
-                const uint32_t L = blockIdx.x + it * G;
-                const int hh = L % HHu, b = L / (HHu * n_tiles);
-                const int hd = hh % P.H, rs = hh / P.H;
-                const int q0 = (int)((L / HHu) % n_tiles) * kRows;
-                const int start = (q0 + P.off1 - P.left) - P.cl;   // first key row of the item (a multiple of 16)
-                const int sq = it % NQK, sv = it % NV;
-                // a stage that crosses into a neighbour shard's rows is fetched 16 rows at a time, each
-                // piece from the tensor that owns it
-                const bool pieces = !LF && ((start < 0 && P.key_lo < 0) || (start + KT > P.Skv1 && P.key_hi > P.Skv1));
-                auto load_rows = [&](uint8_t *dst, uint64_t *bar, const CUtensorMap *whole, const CUtensorMap *own,
-                                     const CUtensorMap *prev, const CUtensorMap *next) {
-                    if (!pieces) {
-                        ptx::tma_load_5d(dst, whole, bar, 0, hd, rs, start, b);   // (Longformer variant: a box of 224 rows)
-                        return;
-                    }
-                    for (int i = 0; i < KT / 16; ++i) {
-                        const int a = start + 16 * i;
-                        const CUtensorMap *m = own;
-                        int row = a;
-                        if (a < 0 && P.key_lo < 0) { m = prev; row = P.prev_rows + a; }
-                        else if (a >= P.Skv1 && P.key_hi > P.Skv1) { m = next; row = a - P.Skv1; }
-                        ptx::tma_load_5d(dst + i * 16 * kRowBytes, m, bar, 0, hd, rs, row, b);
-                    }
-                };
-                if (it >= (uint32_t)NQK && !ptx::mbar_wait(qk_empty + sq, (it / NQK - 1) & 1)) {
-                    atomicExch(&g_band_status, 1);
-                    break;
-                }
-                TR(0, it, 0);
-                uint8_t *dq = sQK + sq * C::kQKBytes;
-                ptx::mbar_expect_tx(qk_full + sq, C::kQKBytes);
-                ptx::tma_load_5d(dq, &maps.q, qk_full + sq, 0, hd, rs, q0, b);
-                load_rows(dq + kTQ * kRowBytes, qk_full + sq, &maps.k, &maps.k_own, &maps.k_prev, &maps.k_next);
-                if (LF)   // the keys at the global positions behind the window keys (slots past the list: zeros)
-                    ptx::tma_load_5d(dq + (kTQ + kBandKT) * kRowBytes, &maps.kg, qk_full + sq, 0, hd, rs, 0, b);
-                if (it >= (uint32_t)NV && !ptx::mbar_wait(v_empty + sv, (it / NV - 1) & 1)) {
-                    atomicExch(&g_band_status, 1);
-                    break;
-                }
-                TR(0, it, 1);
-                ptx::mbar_expect_tx(v_full + sv, C::kVBytes);
-                load_rows(sV + sv * C::kVBytes, v_full + sv, &maps.v, &maps.v_own, &maps.v_prev, &maps.v_next);
-                if (LF) ptx::tma_load_5d(sV + sv * C::kVBytes + kBandKT * kRowBytes, &maps.vg, v_full + sv, 0, hd, rs, 0, b);
-            }
+            for (uint32_t it = kEarly; it < n_mine; ++it)
+                if (!produce(it)) break;
         }
     } else if (warp >= kEpilogueWarp0) {
         // ================= epilogue warps: the finished rows of every item, both slots in turn =================
