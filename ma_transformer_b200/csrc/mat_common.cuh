@@ -80,7 +80,11 @@ int launch_umma_band(const Problem &p);
 int band_status_read_and_clear(int *out);
 // first pass of a Longformer forward on the band kernel; kg, vg: the K/V rows at the global positions, gathered
 bool umma_band_longformer_supports(const Problem &p);
-int launch_umma_band_longformer(const Problem &p, const void *kg, const void *vg);
+int launch_umma_band_longformer(const Problem &p, const void *kg, const void *vg, const void *qg, float *partial);
+// lanes per head when that pass also accumulates the rows AT the global positions (0: it does not), and the
+// bytes of the partials it then leaves: [B, H, lanes, 32, kPartialStride] floats
+int umma_band_longformer_lanes(const Problem &p);
+size_t umma_band_longformer_partial_bytes(const Problem &p);
 // Longformer global-row pass on tcgen05 (umma_block.cu): how the key axis is split, and the launch
 constexpr int kPartialStride = 66;   // floats per row of a partial: max, sum, 64 outputs
 struct GlobalRowSplit {

@@ -525,7 +525,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 // grid = (global position, batch), threads stride over the HH * 8 16-byte pieces of a row set.
 __global__ void gather_global_rows_kernel(const uint4 *__restrict__ k, const uint4 *__restrict__ v,
                                           uint4 *__restrict__ kg, uint4 *__restrict__ vg,
-                                          const int64_t *__restrict__ gidx, int n_global, int64_t S, int HH) {
+                                          const int64_t *__restrict__ gidx, int n_global, int64_t S, int HH,
+                                          const uint4 *__restrict__ q = nullptr, uint4 *__restrict__ qg = nullptr) {
     const int e = blockIdx.x, b = blockIdx.y;
     const int64_t row = gidx[e];
     const bool in_range = row >= 0 && row < S;   // a position outside the sequence gathers zeros, never memory
@@ -534,6 +535,7 @@ __global__ void gather_global_rows_kernel(const uint4 *__restrict__ k, const uin
     for (int i = threadIdx.x; i < HH * 8; i += blockDim.x) {
         kg[dst + i] = in_range ? k[src + i] : zero;
         vg[dst + i] = in_range ? v[src + i] : zero;
+        if (qg) qg[dst + i] = in_range ? q[src + i] : zero;   // (callers pass q only when it has as many rows as k)
     }
 }
 
@@ -684,9 +686,10 @@ int prefetch_distance() {
 }
 
 size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
-// workspace layout of a Longformer forward: [partials of the global-row pass][K at globals][V at globals]
+// workspace layout of a Longformer forward: [partials of the global rows][K at globals][V at globals][Q at globals]
 size_t partial_region_bytes(const Problem &p) {
-    return align256(std::max(plan_global_rows(p).bytes, plan_umma_global_rows(p).bytes));
+    return align256(std::max({plan_global_rows(p).bytes, plan_umma_global_rows(p).bytes,
+                              umma_band_longformer_partial_bytes(p)}));
 }
 size_t gathered_region_bytes(const Problem &p) { return align256((size_t)p.B * p.pat.n_global * p.H * kRowBytes); }
 
@@ -749,6 +752,8 @@ int launch_t(const Problem &p) {
         fp.right = fp.mask_right = (int32_t)std::min<int64_t>(p.pat.right, fp.Skv1 + fp.next_rows);
         fp.n_global = (int32_t)p.pat.n_global;
         fp.gidx = p.pat.gidx;
+        bool fold = false;       // the band kernel's first pass also accumulates the rows AT the global positions
+        uint8_t *qg = nullptr;   // the Q rows there
         if (p.shard_kg) {
             // one shard of a sequence spread over GPUs: the caller gathered the K/V rows at ALL global
             // positions (gidx holds their positions relative to this shard's first row); only the first
@@ -760,9 +765,11 @@ int launch_t(const Problem &p) {
             const size_t part = partial_region_bytes(p);
             const size_t gbytes = gathered_region_bytes(p);
             uint8_t *kg = (uint8_t *)p.workspace + part, *vg = kg + gbytes;
+            fold = umma_band_longformer_supports(p) && umma_band_longformer_lanes(p) > 0;
+            qg = fold ? vg + gbytes : nullptr;
             gather_global_rows_kernel<<<dim3((unsigned)fp.n_global, (unsigned)p.B), 128, 0, p.stream>>>(
                 (const uint4 *)p.k, (const uint4 *)p.v, (uint4 *)kg, (uint4 *)vg, fp.gidx, fp.n_global, p.Skv,
-                fp.HH);
+                fp.HH, fold ? (const uint4 *)p.q : nullptr, (uint4 *)qg);
             cudaError_t e0 = cudaGetLastError();
             if (e0 != cudaSuccess) return cuda_fail(e0, "gather_global_rows_kernel launch");
             fp.kg = kg;
@@ -777,7 +784,17 @@ int launch_t(const Problem &p) {
         if (fp.kg && !p.shard_kg && umma_band_longformer_supports(p)) {
             // at most 32 global positions and a window of at most 128 taps: the persistent tcgen05 band kernel,
             // 96 query rows per item against 224 window keys and the gathered keys
-            if (int rc = launch_umma_band_longformer(p, fp.kg, fp.vg)) return rc;
+            // (fold: rows 96..127 of every query tile are the queries at the global positions; their partials, one
+            // per lane of CTAs, go through the merge kernel like the splits of the separate pass)
+            if (int rc = launch_umma_band_longformer(p, fp.kg, fp.vg, qg, fold ? (float *)p.workspace : nullptr)) return rc;
+            if (fold) {
+                const dim3 grid_m((unsigned)fp.n_global, (unsigned)fp.HH, (unsigned)p.B);
+                merge_global_rows_kernel<T><<<grid_m, 64, 0, p.stream>>>((const float *)p.workspace, (T *)p.o, fp.gidx,
+                                                                        umma_band_longformer_lanes(p), 32, fp.HH, fp.Sq1,
+                                                                        fp.sl2, 1, 0, 0);
+                cudaError_t e2 = cudaGetLastError();
+                return e2 == cudaSuccess ? MAT_OK : cuda_fail(e2, "merge_global_rows_kernel launch");
+            }
         } else if (one_stage) {
             if (int rc = launch_kind<T, MAT_LONGFORMER, 128, 256, 5, 1, false, 2>(p, fp, dil, "mma_longformer")) return rc;
         } else if (int rc = launch_kind<T, MAT_LONGFORMER, TQ, 128, 4, 2, false, 3>(p, fp, dil, "mma_longformer")) return rc;
@@ -849,7 +866,7 @@ bool mma_flash_supports(const Problem &p) {
 
 size_t mma_flash_workspace_bytes(const Problem &p) {
     if (p.pat.kind != MAT_LONGFORMER || p.pat.n_global == 0) return 0;
-    return partial_region_bytes(p) + 2 * gathered_region_bytes(p);
+    return partial_region_bytes(p) + 3 * gathered_region_bytes(p);
 }
 
 int launch_mma_flash(const Problem &p) {

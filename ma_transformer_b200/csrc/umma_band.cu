@@ -85,17 +85,30 @@ struct BandParams {
     // Longformer variant: the sorted global positions; every row attends them besides its window
     int32_t n_global;
     const int64_t *gidx;
+    // Longformer variant with the rows AT the global positions folded in (lanes > 0): CTA c works on head
+    // c % HH only and on every lanes-th tile of it, starting at tile c / HH, batches following one another;
+    // rows 96..127 of its query tile are the queries at the global positions, whose scores against the keys
+    // an item owns are accumulated over the CTA's items and left in `partial`
+    // ([B, HH, lanes, 32, kPartialStride]: maximum, sum, 64 unnormalised outputs) for the merge kernel.
+    int32_t lanes, B;
+    float *partial;
 };
 
 struct BandMaps {
     CUtensorMap q, k, v, o;                                  // boxes of 128 (q, o) and KT rows
     CUtensorMap k_own, v_own, k_prev, v_prev, k_next, v_next;   // 16-row boxes for stages that cross a shard edge
     CUtensorMap kg, vg;   // Longformer variant: the K/V rows at the global positions, [B, n_global, HH, 64], 32-row boxes
+    CUtensorMap qg;       // and, with the global rows folded in, the Q rows there (q then has 96-row boxes)
 };
 
 // Longformer variant: an item is 96 query rows, its key range 224 window keys followed by the (at most 32)
 // keys at the global positions, so that scores, weights and output still fit one 256-column slot and one
-// tcgen05.mma of N = 256 per slice.  The tile's rows 96..127 belong to the next item and are computed for nothing.
+// tcgen05.mma of N = 256 per slice.  The tile's rows 96..127 are the queries AT the global positions (which attend
+// every key): each item adds their scores against the 96 keys its own rows sit on, the epilogue warp of that
+// quarter keeps the running maximum, sum and output of the 32 rows over the CTA's items in registers (a CTA stays
+// on one head), and the per-CTA partials are merged by merge_global_rows_kernel.  The whole Longformer forward is
+// then gather (Q, K, V at the global positions) -> this kernel -> merge, and K and V leave DRAM once.
+// (Without the fold - more heads than half the SMs - rows 96..127 are the next item's and computed for nothing.)
 constexpr int kLfRows = 96, kLfBand = 224, kLfGlobals = 32;
 constexpr int kNoGlobal = INT32_MIN;   // unused slot of the global-position list
 
@@ -105,7 +118,8 @@ template <int KT> struct BandCfg {
     static constexpr int kQKBytes = kTQ * kRowBytes + KT * kRowBytes;
     static constexpr int kVBytes = KT * kRowBytes;
     static constexpr int kNCH = (KT - 96) / 32;      // 32-column chunks of a warp's band: 3 or 5 (Longformer: 5 and the globals)
-    static constexpr int kBars = 2 * kNQK + 2 * kNV + 12 + kLfGlobals / 2;   // (the global-position list sits behind the barriers)
+    // (behind the barriers: the global-position list, then per slot the 32 item maxima of the global rows)
+    static constexpr int kBars = 2 * kNQK + 2 * kNV + 12 + kLfGlobals / 2 + kLfGlobals;
     static constexpr int kOutBytes = kTQ * kRowBytes;   // one output tile per slot, staged for its bulk store
     static constexpr size_t kSmemBytes = 1024 + (size_t)kNQK * kQKBytes + (size_t)kNV * kVBytes + 2 * kOutBytes +
                                          kSumN * kRowBytes + kBars * 8 + 16;
@@ -130,18 +144,35 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
     uint64_t *s_ready = v_empty + NV, *p_ready = s_ready + 2, *o_ready = p_ready + 2, *slot_free = o_ready + 2;
     uint64_t *out_full = slot_free + 2, *out_free = out_full + 2;   // the staged output tile of a slot
     int32_t *sG = (int32_t *)(out_free + 2);             // Longformer variant: the global positions (kNoGlobal: unused)
-    uint32_t *tmem_slot = (uint32_t *)(sG + kLfGlobals);
+    float *sM = (float *)(sG + kLfGlobals);              // [slot][global row]: maximum of the row's scores in the slot's item
+    uint32_t *tmem_slot = (uint32_t *)(sM + 2 * kLfGlobals);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // ---- the TMA lane's work for item `it` of this CTA: {Q, K} and V into their rings ----
     const uint32_t G = gridDim.x, HHu = (uint32_t)P.HH, n_tiles = (uint32_t)P.n_tiles;
-    const uint32_t n_mine = blockIdx.x < P.n_items ? (P.n_items - blockIdx.x + G - 1) / G : 0;   // items of this CTA
+    const bool fold = LF && P.lanes > 0;   // the rows at the global positions ride along (see BandParams)
+    const uint32_t my_lane = blockIdx.x / HHu, n_slots = (uint32_t)P.B * n_tiles;
+    const uint32_t n_mine = fold ? (my_lane < (uint32_t)P.lanes && my_lane < n_slots ? (n_slots - my_lane + P.lanes - 1) / P.lanes : 0)
+                                 : (blockIdx.x < P.n_items ? (P.n_items - blockIdx.x + G - 1) / G : 0);   // items of this CTA
+    // item `it` of this CTA: head of the kernel's view, batch, first query row
+    auto item_at = [&](uint32_t it, int &hh, int &b, int &q0) {
+        if (fold) {
+            const uint32_t t = my_lane + it * (uint32_t)P.lanes;
+            hh = blockIdx.x % HHu;
+            b = t / n_tiles;
+            q0 = (int)(t % n_tiles) * kRows;
+        } else {
+            const uint32_t L = blockIdx.x + it * G;
+            hh = L % HHu;
+            b = L / (HHu * n_tiles);
+            q0 = (int)((L / HHu) % n_tiles) * kRows;
+        }
+    };
     auto produce = [&](uint32_t it) -> bool {
-        const uint32_t L = blockIdx.x + it * G;
-        const int hh = L % HHu, b = L / (HHu * n_tiles);
+        int hh, b, q0;
+        item_at(it, hh, b, q0);
         const int hd = hh % P.H, rs = hh / P.H;
-        const int q0 = (int)((L / HHu) % n_tiles) * kRows;
         const int start = (q0 + P.off1 - P.left) - P.cl;   // first key row of the item (a multiple of 16)
         const int sq = it % NQK, sv = it % NV;
         // a stage that crosses into a neighbour shard's rows is fetched 16 rows at a time, each
@@ -169,7 +200,8 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
         TR(0, it, 0);
         uint8_t *dq = sQK + sq * C::kQKBytes;
         ptx::mbar_expect_tx(qk_full + sq, C::kQKBytes);
-        ptx::tma_load_5d(dq, &maps.q, qk_full + sq, 0, hd, rs, q0, b);
+        ptx::tma_load_5d(dq, &maps.q, qk_full + sq, 0, hd, rs, q0, b);   // (fold: a box of 96 rows)
+        if (fold) ptx::tma_load_5d(dq + kLfRows * kRowBytes, &maps.qg, qk_full + sq, 0, hd, rs, 0, b);
         load_rows(dq + kTQ * kRowBytes, qk_full + sq, &maps.k, &maps.k_own, &maps.k_prev, &maps.k_next);
         if (LF)   // the keys at the global positions behind the window keys (slots past the list: zeros)
             ptx::tma_load_5d(dq + (kTQ + kBandKT) * kRowBytes, &maps.kg, qk_full + sq, 0, hd, rs, 0, b);
@@ -195,7 +227,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
             ptx::mbar_init(p_ready + i, 4);
             ptx::mbar_init(o_ready + i, 1);
             ptx::mbar_init(slot_free + i, 4);
-            ptx::mbar_init(out_full + i, 4);
+            ptx::mbar_init(out_full + i, fold ? 3 : 4);   // (fold: quarter 3 stages no rows)
             ptx::mbar_init(out_free + i, 1);
         }
         ptx::fence_barrier_init();
@@ -229,64 +261,115 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
         const int quad = warp & 3;
         const int r = quad * 32 + lane;
         bool ok = true;
-        for (uint32_t i = 0; ok && i < n_mine; ++i) {
-            const int slot = i & 1;
-            const uint32_t u = i >> 1;
-            const uint32_t L = blockIdx.x + i * G;
-            const int hh = L % HHu, b = L / (HHu * n_tiles);
-                const int hd = hh % P.H, rs = hh / P.H;
-            const int q0 = (int)((L / HHu) % n_tiles) * kRows;
-            const uint32_t t_lane = tmem_base + slot * kSlotCols + ((uint32_t)(quad * 32) << 16);
-            // ---- the finished row: O and its sum ----
-            if (!(ok = ptx::mbar_wait(o_ready + slot, u & 1))) break;
-            tc_fence_after();
-            if (r == 0) TR(2, i, 3);
-            float o[64], l_run;
-            tmem_ld64_and_1(t_lane + KT / 2, o, t_lane + KT / 2 + 64, l_run);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(slot_free + slot);   // the slot may take the scores of item i + 2
-            // normalise, stage the tile (128-byte swizzled rows, as the bulk store expects), store it
-            {
-                const float inv = l_run > 0.f ? __frcp_rn(l_run) : 0.f;
-                uint8_t *so = sOut + slot * C::kOutBytes;
-                // the bulk store of this slot's previous tile has finished reading the staging rows
-                // (every hand-over is an mbarrier with a bounded wait, never a bar.sync: a warp that gave
-                // up on a wait must not leave the others stuck)
-                if (u >= 1) {
-                    if (quad == 0 && lane == 0) {
-                        ptx::tma_store_wait_read();
-                        ptx::mbar_arrive(out_free + slot);
-                    }
-                    if (!(ok = ptx::mbar_wait(out_free + slot, (u - 1) & 1))) break;
-                }
-                if (r == 0) TR(2, i, 4);
-                uint8_t *row = so + r * kRowBytes;
+        if (fold && quad == 3) {
+            // fold, quarter 3: lane e carries the row at global position e of the head this CTA works on: the
+            // running maximum, sum and unnormalised output over the keys of the CTA's items so far in the batch
+            float g_m = -INFINITY, g_l = 0.f, g_acc[64];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    uint4 v;
-                    v.x = ptx::Mma<T>::pack(o[8 * q] * inv, o[8 * q + 1] * inv);
-                    v.y = ptx::Mma<T>::pack(o[8 * q + 2] * inv, o[8 * q + 3] * inv);
-                    v.z = ptx::Mma<T>::pack(o[8 * q + 4] * inv, o[8 * q + 5] * inv);
-                    v.w = ptx::Mma<T>::pack(o[8 * q + 6] * inv, o[8 * q + 7] * inv);
-                    *reinterpret_cast<uint4 *>(row + ((q ^ (r & 7)) << 4)) = v;
+            for (int c = 0; c < 64; ++c) g_acc[c] = 0.f;
+            int g_b = 0;   // batch the running values belong to
+            auto flush_rows = [&](int b_end) {   // leaves the partial of batch g_b, and empty ones up to b_end
+                for (; g_b < b_end; ++g_b) {
+                    float *pr = P.partial + ((((int64_t)g_b * P.HH + blockIdx.x % HHu) * P.lanes + my_lane) * kLfGlobals + lane) * kPartialStride;
+                    pr[0] = g_m;
+                    pr[1] = g_l;
+#pragma unroll
+                    for (int c = 0; c < 64; c += 2) *reinterpret_cast<float2 *>(pr + 2 + c) = make_float2(g_acc[c], g_acc[c + 1]);
+                    g_m = -INFINITY;
+                    g_l = 0.f;
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) g_acc[c] = 0.f;
                 }
-                ptx::fence_proxy_async_smem();
+            };
+            for (uint32_t i = 0; ok && i < n_mine; ++i) {
+                const int slot = i & 1;
+                int hh, b, q0;
+                item_at(i, hh, b, q0);
+                const uint32_t t_lane = tmem_base + slot * kSlotCols + ((uint32_t)(quad * 32) << 16);
+                if (!(ok = ptx::mbar_wait(o_ready + slot, (i >> 1) & 1))) break;
+                tc_fence_after();
+                if (b != g_b) flush_rows(b);
+                const float m_it = sM[slot * kLfGlobals + lane];   // maximum of the row's scores in this item
+                const float m_new = fmaxf(g_m, m_it);
+                // (an item none of whose keys the row may use: maximum -inf, weights and sum zero)
+                const float a = m_new == -INFINITY ? 0.f : ptx::ex2((g_m - m_new) * P.sl2);
+                const float w = m_new == -INFINITY ? 0.f : ptx::ex2((m_it - m_new) * P.sl2);
+                uint32_t part[32];
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    tmem_ld32(t_lane + KT / 2 + 32 * hf, part);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        g_acc[32 * hf + c] = fmaf(g_acc[32 * hf + c], a, w * __uint_as_float(part[c]));
+                }
+                tmem_ld32(t_lane + KT / 2 + 64, part);   // its first column: the row sum
+                g_l = fmaf(g_l, a, w * __uint_as_float(part[0]));
+                g_m = m_new;
+                tc_fence_before();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(out_full + slot);
-                if (quad == 0 && lane == 0) {
-                    if (!ptx::mbar_wait(out_full + slot, u & 1)) {
-                        ok = false;
-                    } else {
-                        ptx::tma_store_5d(&maps.o, so, 0, hd, rs, q0, b);   // rows past the sequence end are clipped
-                        ptx::tma_store_commit();
+                if (lane == 0) ptx::mbar_arrive(slot_free + slot);
+            }
+            if (ok) flush_rows(P.B);
+            if (!ok) atomicExch(&g_band_status, 1);
+        } else {
+            for (uint32_t i = 0; ok && i < n_mine; ++i) {
+                const int slot = i & 1;
+                const uint32_t u = i >> 1;
+                int hh, b, q0;
+                item_at(i, hh, b, q0);
+                const int hd = hh % P.H, rs = hh / P.H;
+                const uint32_t t_lane = tmem_base + slot * kSlotCols + ((uint32_t)(quad * 32) << 16);
+                // ---- the finished row: O and its sum ----
+                if (!(ok = ptx::mbar_wait(o_ready + slot, u & 1))) break;
+                tc_fence_after();
+                if (r == 0) TR(2, i, 3);
+                float o[64], l_run;
+                tmem_ld64_and_1(t_lane + KT / 2, o, t_lane + KT / 2 + 64, l_run);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(slot_free + slot);   // the slot may take the scores of item i + 2
+                // normalise, stage the tile (128-byte swizzled rows, as the bulk store expects), store it
+                {
+                    const float inv = l_run > 0.f ? __frcp_rn(l_run) : 0.f;
+                    uint8_t *so = sOut + slot * C::kOutBytes;
+                    // the bulk store of this slot's previous tile has finished reading the staging rows
+                    // (every hand-over is an mbarrier with a bounded wait, never a bar.sync: a warp that gave
+                    // up on a wait must not leave the others stuck)
+                    if (u >= 1) {
+                        if (quad == 0 && lane == 0) {
+                            ptx::tma_store_wait_read();
+                            ptx::mbar_arrive(out_free + slot);
+                        }
+                        if (!(ok = ptx::mbar_wait(out_free + slot, (u - 1) & 1))) break;
                     }
-                    TR(2, i, 5);
+                    if (r == 0) TR(2, i, 4);
+                    uint8_t *row = so + r * kRowBytes;
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        uint4 v;
+                        v.x = ptx::Mma<T>::pack(o[8 * q] * inv, o[8 * q + 1] * inv);
+                        v.y = ptx::Mma<T>::pack(o[8 * q + 2] * inv, o[8 * q + 3] * inv);
+                        v.z = ptx::Mma<T>::pack(o[8 * q + 4] * inv, o[8 * q + 5] * inv);
+                        v.w = ptx::Mma<T>::pack(o[8 * q + 6] * inv, o[8 * q + 7] * inv);
+                        *reinterpret_cast<uint4 *>(row + ((q ^ (r & 7)) << 4)) = v;
+                    }
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(out_full + slot);
+                    if (quad == 0 && lane == 0) {
+                        if (!ptx::mbar_wait(out_full + slot, u & 1)) {
+                            ok = false;
+                        } else {
+                            ptx::tma_store_5d(&maps.o, so, 0, hd, rs, q0, b);   // rows past the sequence end are clipped
+                            ptx::tma_store_commit();
+                        }
+                        TR(2, i, 5);
+                    }
                 }
             }
+            if (quad == 0 && lane == 0) ptx::tma_store_wait_all();
+            if (!ok) atomicExch(&g_band_status, 1);
         }
-        if (quad == 0 && lane == 0) ptx::tma_store_wait_all();
-        if (!ok) atomicExch(&g_band_status, 1);
     } else if (warp >= kSoftmaxWarps) {
         // ================= MMA lanes, one per slot: S(i), then [O | l](i) once the weights are stored =================
         // (two issuing lanes: an instruction costs its issuer about 125 cycles whatever its shape, and a slot's
@@ -340,19 +423,24 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
         const int r = quad * 32 + lane;
         const uint32_t t_lane = tmem_base + slot * kSlotCols + ((uint32_t)(quad * 32) << 16);
         const uint32_t span = (uint32_t)(P.left + P.right);
-        const int c0 = quad * 32;             // first column of this warp's band chunks
+        // fold: quarter 3 holds the rows at the global positions, which take the keys the item's own 96 rows sit
+        // on (every key belongs to exactly one item): columns left + cl ... + 95, inside the five chunks that
+        // start at the chunk of column left + cl (at the third chunk when that would reach past the window keys)
+        const bool grow = fold && quad == 3;
+        const int pq = grow ? min(2, (P.left + P.cl) >> 5) : quad;   // first 32-column chunk of this warp's band
+        const int c0 = pq * 32;
         bool ok = true;
         for (uint32_t i = slot; ok && i < n_mine; i += 2) {
             const uint32_t u = i >> 1;
-            const uint32_t L = blockIdx.x + i * G;
-            const int q0 = (int)((L / HHu) % n_tiles) * kRows;
+            int hh_, b_, q0;
+            item_at(i, hh_, b_, q0);
             const int start = (q0 + P.off1 - P.left) - P.cl;
             const bool edge = start < P.key_lo || start + kBandKT > P.key_hi;   // some columns lie outside the key line
             if (r == 0) TR(2, i, 0);
             if (!(ok = ptx::mbar_wait(s_ready + slot, u & 1))) break;
             tc_fence_after();
             if (r == 0) TR(2, i, 1);
-            if (LF && quad == 3) {
+            if (LF && quad == 3 && !fold) {
                 // rows 96..127 of the tile belong to the next item: nothing to compute, their rows of P stay
                 // whatever the scores left there and their output rows are never stored
                 tc_fence_before();
@@ -362,21 +450,26 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
             }
             // Columns of this row that count: its band, cut to the keys that exist.  n_ok = 0: none.
             int lo = r + P.cl, hi = r + P.cl + (int)span;
-            if (edge) {
+            if (grow) {
+                lo = P.left + P.cl;
+                hi = lo + kLfRows - 1;
+            }
+            if (edge || grow) {
                 lo = max(lo, P.key_lo - start);
                 hi = min(hi, P.key_hi - 1 - start);
             }
             const uint32_t n_ok = (uint32_t)max(0, hi - lo + 1);
             // chunk ch (columns c0 + 32 ch ...) lies inside the band of every row of this warp iff
             // 32 ch >= cl + 31 and 32 ch + 31 <= cl + span; such a chunk needs no mask
-            const int ch_free_lo = (P.cl + 31 + 31) >> 5, ch_free_hi = edge ? -1 : ((P.cl + (int)span - 31) >> 5);
+            const int ch_free_lo = (P.cl + 31 + 31) >> 5, ch_free_hi = edge || grow ? -1 : ((P.cl + (int)span - 31) >> 5);
             // mask of one 32-column chunk (skipped when the chunk lies inside every row's band), its share of
             // the row maximum, and its weights: packed two to a column and stored as P over columns [0, KT/2)
             // of this lane.  P column j holds keys 2j, 2j + 1 of the item, so the pairs of chunk ch go to the
-            // 16 columns at 16 (quad + ch): always below the scores this thread has still to read.
+            // 16 columns at 16 (pq + ch): always below the scores this thread has still to read.
             auto mask_chunk = [&](uint32_t (&sr)[32], int ch) {
-                if (ch < ch_free_lo || ch > ch_free_hi) {
-                    const int d = c0 + 32 * ch - lo;
+                const int d = c0 + 32 * ch - lo;
+                // (the rows at the global positions all take the same columns: a chunk inside them needs no mask either)
+                if (grow ? (d < 0 || d + 31 >= (int)n_ok) : (ch < ch_free_lo || ch > ch_free_hi)) {
 #pragma unroll
                     for (int e = 0; e < 32; ++e)
                         if ((uint32_t)(d + e) >= n_ok) sr[e] = 0xff800000u;   // -inf
@@ -391,7 +484,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                         mx[q] = max3(mx[q], __uint_as_float(sr[e + 2 * q]), __uint_as_float(sr[e + 2 * q + 1]));
                 }
             };
-            float mus = 0.f;
+            float mus = 0.f, m_row = -INFINITY;
             // Longformer variant: chunk NCH is the scores against the keys at the global positions (columns
             // 224..255); a slot counts unless it is unused or the row's window already holds that position
             auto mask_globals = [&](uint32_t (&sr)[32]) {
@@ -399,7 +492,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
                     const int gk = sG[e];
-                    if (gk == kNoGlobal || (uint32_t)(gk - p + P.left) <= span) sr[e] = 0xff800000u;
+                    if (gk == kNoGlobal || (uint32_t)(gk - p + P.left) <= span || grow) sr[e] = 0xff800000u;
                 }
             };
             auto weights_chunk = [&](const uint32_t (&sr)[32], int piece) {
@@ -428,12 +521,12 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                 if (r == 0) TR(0, i, 2);
                 mask_chunk(s2, 2);
                 max_chunk(s2);
-                const float m = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-                mus = (m == -INFINITY ? 0.f : m) * P.sl2;
+                m_row = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                mus = (m_row == -INFINITY ? 0.f : m_row) * P.sl2;
                 if (r == 0) TR(0, i, 3);
-                weights_chunk(s0, quad);
-                weights_chunk(s1, quad + 1);
-                weights_chunk(s2, quad + 2);
+                weights_chunk(s0, pq);
+                weights_chunk(s1, pq + 1);
+                weights_chunk(s2, pq + 2);
                 if (r == 0) TR(0, i, 4);
             } else {
                 // Two passes over the scores with three register buffers.  Every tcgen05.wait::ld covers all
@@ -445,7 +538,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                 constexpr int NL = NC - 3;               // low chunks 0..NL-1, high chunks NL..NC-1 (three of them)
                 static_assert(NL >= 1 && NL <= 3, "three buffers hold either group");
                 auto ccol = [&](int ch) { return LF && ch == NCH ? kLfBand : c0 + 32 * ch; };
-                auto piece_of = [&](int ch) { return LF && ch == NCH ? kLfBand / 32 : quad + ch; };
+                auto piece_of = [&](int ch) { return LF && ch == NCH ? kLfBand / 32 : pq + ch; };
                 auto mask_any = [&](uint32_t (&sr)[32], int ch) {
                     if (LF && ch == NCH) mask_globals(sr);
                     else mask_chunk(sr, ch);
@@ -457,6 +550,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                 tmem_ld32_wait(b0);
                 tmem_ld32_wait(b1);
                 tmem_ld32_wait(b2);
+                if (r == 0) TR(0, i, 2);
                 mask_any(b0, NL);
                 max_chunk(b0);
                 tmem_ld32_issue(t_lane + ccol(0), b0);
@@ -479,8 +573,9 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                     mask_any(b2, 2);
                     max_chunk(b2);
                 }
-                const float m = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-                mus = (m == -INFINITY ? 0.f : m) * P.sl2;
+                m_row = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                mus = (m_row == -INFINITY ? 0.f : m_row) * P.sl2;
+                if (r == 0) TR(0, i, 3);
                 // pass 2: the low chunks from the registers, each buffer refilled with a high chunk as it frees
                 weights_chunk(b0, piece_of(0));
                 tmem_ld32_issue(t_lane + ccol(NL), b0);
@@ -493,6 +588,7 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                     tmem_ld32_issue(t_lane + ccol(NL + 2), b2);
                 }
                 tmem_ld32_wait(b0);
+                if (r == 0) TR(0, i, 4);
                 mask_any(b0, NL);
                 weights_chunk(b0, piece_of(NL));
                 if (NL > 1) {
@@ -511,15 +607,17 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
                 }
             }
             // zeros in the P columns outside the band (the scores there belong to other rows' bands)
+            if (r == 0) TR(0, i, 7);
             {
                 uint32_t z[16];
 #pragma unroll
                 for (int e = 0; e < 16; ++e) z[e] = 0u;
-#pragma unroll 1
+#pragma unroll
                 for (int piece = 0; piece < KT / 32; ++piece)
-                    if ((piece < quad || piece >= quad + NCH) && !(LF && piece == kLfBand / 32))
+                    if ((piece < pq || piece >= pq + NCH) && !(LF && piece == kLfBand / 32))
                         tmem_st16(t_lane + 16 * piece, z);
             }
+            if (grow) sM[slot * kLfGlobals + lane] = m_row;   // read by the epilogue warp once the P V product is done
             if (r == 0) TR(0, i, 5);
             tmem_wait_st();
             if (r == 0) TR(0, i, 6);
@@ -544,7 +642,8 @@ umma_band_kernel(const __grid_constant__ BandMaps maps, const BandParams P) {
 // ---- host side --------------------------------------------------------------------------------
 
 template <typename T, int KT, bool LF>
-int launch_band(const Problem &p, const BandParams &bp_in, int64_t dil, const void *kg, const void *vg) {
+int launch_band(const Problem &p, const BandParams &bp_in, int64_t dil, const void *kg, const void *vg,
+                const void *qg = nullptr) {
     BandParams bp = bp_in;
     BandMaps m;
     constexpr int kBandKT = LF ? kLfBand : KT;
@@ -554,7 +653,8 @@ int launch_band(const Problem &p, const BandParams &bp_in, int64_t dil, const vo
     const int64_t TS_v = p.v_ts ? p.v_ts * 2 : contiguous, TS_o = p.o_ts ? p.o_ts * 2 : contiguous;
     const int64_t TS_k_own = TS_k, TS_v_own = TS_v;
     const int64_t TS_k_prev = contiguous, TS_v_prev = contiguous, TS_k_next = contiguous, TS_v_next = contiguous;
-    if (int rc = make_row_tensor_map5(&m.q, p.q, p.dtype, p.H, dil, p.Sq / dil, p.B, kTQ, TS_q)) return rc;
+    const bool fold = LF && bp.lanes > 0;
+    if (int rc = make_row_tensor_map5(&m.q, p.q, p.dtype, p.H, dil, p.Sq / dil, p.B, fold ? kLfRows : kTQ, TS_q)) return rc;
     if (int rc = make_row_tensor_map5(&m.k, p.k, p.dtype, p.H, dil, p.Skv / dil, p.B, kBandKT, TS_k)) return rc;
     if (int rc = make_row_tensor_map5(&m.v, p.v, p.dtype, p.H, dil, p.Skv / dil, p.B, kBandKT, TS_v)) return rc;
     if (int rc = make_row_tensor_map5(&m.o, p.o, p.dtype, p.H, dil, p.Sq / dil, p.B, LF ? kLfRows : kTQ, TS_o)) return rc;
@@ -576,6 +676,9 @@ int launch_band(const Problem &p, const BandParams &bp_in, int64_t dil, const vo
         if (int rc = make_row_tensor_map5(&m.kg, kg, p.dtype, p.H, 1, bp.n_global, p.B, kLfGlobals, contiguous)) return rc;
         if (int rc = make_row_tensor_map5(&m.vg, vg, p.dtype, p.H, 1, bp.n_global, p.B, kLfGlobals, contiguous)) return rc;
     }
+    m.qg = m.kg;
+    if (fold)
+        if (int rc = make_row_tensor_map5(&m.qg, qg, p.dtype, p.H, 1, bp.n_global, p.B, kLfGlobals, contiguous)) return rc;
     auto kern = umma_band_kernel<T, KT, LF>;
     constexpr size_t smem = BandCfg<KT>::kSmemBytes;
     if (int rc = ensure_dynamic_smem((const void *)kern, smem, "cudaFuncSetAttribute(umma_band_kernel)")) return rc;
@@ -583,7 +686,9 @@ int launch_band(const Problem &p, const BandParams &bp_in, int64_t dil, const vo
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return cuda_fail(e, "sizing the persistent grid");
-    const unsigned grid = (unsigned)std::min<uint64_t>(bp.n_items, (uint64_t)sms);   // one CTA per SM: it owns the SM's tensor memory
+    // one CTA per SM: it owns the SM's tensor memory (fold: one per head and lane, see BandParams)
+    const unsigned grid = fold ? (unsigned)(bp.HH * bp.lanes) : (unsigned)std::min<uint64_t>(bp.n_items, (uint64_t)sms);
+    if (fold && (int)grid > sms) return fail(MAT_ERR_INVALID, "more lanes than the device has SMs");
     kern<<<grid, kThreads, smem, p.stream>>>(m, bp);
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "umma_band_kernel launch");
@@ -612,6 +717,9 @@ int plan_band(const Problem &p, BandParams &bp, bool longformer) {
     bp.sl2 = p.scale * 1.4426950408889634f;
     bp.n_global = longformer ? (int32_t)p.pat.n_global : 0;
     bp.gidx = longformer ? p.pat.gidx : nullptr;
+    bp.lanes = 0;
+    bp.B = (int32_t)p.B;
+    bp.partial = nullptr;
     const uint64_t items = (uint64_t)p.B * bp.n_tiles * bp.HH;
     if (items >= (1ull << 31)) return 0;
     bp.n_items = (uint32_t)items;
@@ -689,12 +797,34 @@ bool umma_band_longformer_supports(const Problem &p) {
     return plan_band(p, bp, true) != 0;
 }
 
-int launch_umma_band_longformer(const Problem &p, const void *kg, const void *vg) {
+// Lanes per head when the rows at the global positions are folded into the first pass: as many as the SMs
+// hold with one CTA per (head, lane); 0 = not folded (more heads than half the SMs would leave too many SMs
+// without a CTA, and MAT_LONGFORMER_FOLD=0 keeps the separate global-row pass: a measurement aid).
+int umma_band_longformer_lanes(const Problem &p) {
+    const char *e = std::getenv("MAT_LONGFORMER_FOLD");
+    if (e && e[0] == '0') return 0;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (p.H > sms / 2) return 0;
+    return (int)(sms / p.H);
+}
+
+size_t umma_band_longformer_partial_bytes(const Problem &p) {
+    return (size_t)p.B * p.H * umma_band_longformer_lanes(p) * kLfGlobals * kPartialStride * sizeof(float);
+}
+
+// qg and partial given: the rows at the global positions are folded in (lanes from umma_band_longformer_lanes),
+// and the caller merges `partial` as lanes splits of 32 rows
+int launch_umma_band_longformer(const Problem &p, const void *kg, const void *vg, const void *qg, float *partial) {
     BandParams bp;
     if (plan_band(p, bp, true) == 0) return fail(MAT_ERR_UNSUPPORTED, "window too wide for the band kernel");
-    if (((uintptr_t)kg | (uintptr_t)vg) % 16) return fail(MAT_ERR_INVALID, "gathered rows must be 16-byte aligned");
-    return p.dtype == MAT_BF16 ? launch_band<__nv_bfloat16, 256, true>(p, bp, 1, kg, vg)
-                               : launch_band<__half, 256, true>(p, bp, 1, kg, vg);
+    if (((uintptr_t)kg | (uintptr_t)vg | (uintptr_t)qg) % 16) return fail(MAT_ERR_INVALID, "gathered rows must be 16-byte aligned");
+    if (qg && partial) {
+        bp.lanes = umma_band_longformer_lanes(p);
+        bp.partial = partial;
+    }
+    return p.dtype == MAT_BF16 ? launch_band<__nv_bfloat16, 256, true>(p, bp, 1, kg, vg, qg)
+                               : launch_band<__half, 256, true>(p, bp, 1, kg, vg, qg);
 }
 
 }  // namespace mat

@@ -406,10 +406,17 @@ def test_longformer_cfg4_shape_reduced_length(monkeypatch, dtype):
     (112, 16, 32, 2048, 1, 2),    # lopsided, the widest window the 224 band columns hold
     (3, 3, 5, 50, 1, 1),          # shorter than one item
     (17, 30, 9, 700, 1, 2),       # first tap off a multiple of 16: the band starts inside its first column group
+    (64, 64, 32, 3000, 3, 5),     # folded: every lane of CTAs crosses batch boundaries (32 tiles, 29 lanes per head)
+    (8, 8, 3, 60, 5, 2),          # folded: fewer tiles than lanes, so most CTAs only leave empty partials
+    (32, 32, 4, 400, 1, 80),      # more heads than half the SMs: never folded
 ])
-def test_longformer_window_pass_on_band_kernel(left, right, n_glob, S, B, H):
+@pytest.mark.parametrize("fold", ["1", "0"])
+def test_longformer_window_pass_on_band_kernel(monkeypatch, fold, left, right, n_glob, S, B, H):
     """The Longformer first pass on the persistent tcgen05 kernel: 96-row items, the keys at the global positions
-    as 32 extra columns (de-duplicated against each row's window), global rows finished by the split pass."""
+    as 32 extra columns (de-duplicated against each row's window).  The rows AT the global positions ride along
+    as rows 96..127 of every query tile and are merged over the CTAs (fold = 1, the default), or are finished
+    by the separate split pass (fold = 0)."""
+    monkeypatch.setenv("MAT_LONGFORMER_FOLD", fold)
     g = torch.Generator().manual_seed(46)
     glob = torch.randperm(S, generator=g)[:n_glob].sort().values.numpy()
     spec = PatternSpec.longformer(left, right, glob)
