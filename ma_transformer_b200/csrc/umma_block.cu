@@ -78,6 +78,9 @@ struct UmmaParams {
     const int64_t *gidx;
     int32_t split_len, n_splits, ng_pad;
     float *partial;   // [B, H, n_splits, ng_pad, kPartialStride]: max, sum, unnormalised output
+    // work items of the persistent grid: (head, y, batch) with heads running fastest; y = 128-row tile
+    // (global-row pass: tile of the global-position list x key split)
+    uint32_t n_work, grid_y;
 };
 
 constexpr int kModeBlock = 0, kModeGlobalRows = 1, kModeDense = 2;   // kModeDense: every key (up to the query when causal)
@@ -201,18 +204,33 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     uint32_t *tmem_slot = (uint32_t *)(tile_bars + 9 * NT);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = blockIdx.x, b = blockIdx.z;
-    // global-row pass: blockIdx.y = (128-row tile of the global-position list) * n_splits + key split
-    const int split = MODE == kModeGlobalRows ? blockIdx.y % P.n_splits : 0;
-    const int q0 = (MODE == kModeGlobalRows ? blockIdx.y / P.n_splits : blockIdx.y) * (NT * kTileQ);
-    // key range of the CTA: a split of the sequence (global rows), or everything / everything up to
-    // the CTA's last row (dense and causal dense)
-    // (a window: from the 64-key chunk that holds the first row's first key to the last row's last key)
-    const int range_lo = MODE == kModeGlobalRows ? split * P.split_len
-                       : MODE == kModeDense ? (max(0, q0 + P.off - P.win_left) & ~(kTileK - 1)) : 0;
-    const int range_hi = MODE == kModeGlobalRows ? min(range_lo + P.split_len, P.Skv)
-                       : MODE == kModeDense ? min(P.Skv, q0 + P.off + NT * kTileQ + P.win_right)
-                       : P.Skv;
+    // Persistent: CTA c works on items c, c + G, c + 2G, ...; every barrier's phase runs on across items
+    // (per-item barriers flip once per item, per-step barriers count the steps of all items so far).
+    const uint32_t G = gridDim.x;
+    const uint32_t n_mine = blockIdx.x < P.n_work ? (P.n_work - blockIdx.x + G - 1) / G : 0;
+    struct Item {
+        int h, b, q0, split;
+        int lo, hi;   // key range: a split of the sequence (global rows), or what the tile's rows can see (dense, windows)
+    };
+    auto item_at = [&](uint32_t n) {
+        const uint32_t L = blockIdx.x + n * G, H = (uint32_t)P.H;
+        Item I;
+        I.h = (int)(L % H);
+        uint32_t y = (L / H) % P.grid_y;
+        I.b = (int)(L / (H * P.grid_y));
+        // causal walks grow with the tile index: the long ones first, so that the CTAs finish together
+        if (MODE == kModeDense) y = P.grid_y - 1 - y;
+        // global-row pass: y = (128-row tile of the global-position list) * n_splits + key split
+        I.split = MODE == kModeGlobalRows ? (int)(y % (uint32_t)P.n_splits) : 0;
+        I.q0 = (int)(MODE == kModeGlobalRows ? y / (uint32_t)P.n_splits : y) * (NT * kTileQ);
+        // (a window: from the 64-key chunk that holds the first row's first key to the last row's last key)
+        I.lo = MODE == kModeGlobalRows ? I.split * P.split_len
+             : MODE == kModeDense ? (max(0, I.q0 + P.off - P.win_left) & ~(kTileK - 1)) : 0;
+        I.hi = MODE == kModeGlobalRows ? min(I.lo + P.split_len, P.Skv)
+             : MODE == kModeDense ? min(P.Skv, I.q0 + P.off + NT * kTileQ + P.win_right)
+             : P.Skv;
+        return I;
+    };
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(bar_q, 1);
@@ -252,43 +270,49 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     // row sums at kColSum, Q at kColQ
 
     if (warp == kSoftmaxWarps + NT) {
-        // ================= load warp: Q once, then K and V chunk by chunk =================
+        // ================= load warp: per item Q, then K and V chunk by chunk =================
         if (lane == 0) {
             bool ok = true;
-            ChunkWalk<NH> w_k, w_v;   // K runs one chunk ahead of V: its stage is free earlier (after S, not after P V)
-            if (MODE != kModeBlock) w_k.init_range(range_lo, range_hi);
-            else w_k.init(P, q0);
-            w_v = w_k;
-            ptx::mbar_expect_tx(bar_q, NT * kTileQ * kRowBytes);
-            if (MODE == kModeGlobalRows) {
-                // map_q is a one-row view here: row r of the tile is the query at global position
-                // gidx[q0 + r]; slots past the list read out of bounds, i.e. zeros
-                for (int r = 0; r < NT * kTileQ; ++r) {
-                    const int e = q0 + r;
-                    const int row = e < P.n_global ? (P.gidx ? (int)P.gidx[e] : e) : P.Sq;   // no list: already gathered
-                    ptx::tma_load_4d(sQ + r * kRowBytes, &map_q, bar_q, 0, h, row, b);
+            int c_k = 0, c_v = 0;   // K and V chunks fetched so far, all items: they name the stage and its phase
+            for (uint32_t n = 0; ok && n < n_mine; ++n) {
+                const Item I = item_at(n);
+                ChunkWalk<NH> w_k, w_v;   // K runs one chunk ahead of V: its stage is free earlier (after S, not after P V)
+                if (MODE != kModeBlock) w_k.init_range(I.lo, I.hi);
+                else w_k.init(P, I.q0);
+                w_v = w_k;
+                // the softmax warps have copied the previous item's Q out of shared memory
+                for (int tl = 0; n >= 1 && tl < NT; ++tl) ok = ok && ptx::mbar_wait(tile_bars + 9 * tl, (n - 1) & 1);
+                if (!ok) break;
+                ptx::mbar_expect_tx(bar_q, NT * kTileQ * kRowBytes);
+                if (MODE == kModeGlobalRows) {
+                    // map_q is a one-row view here: row r of the tile is the query at global position
+                    // gidx[q0 + r]; slots past the list read out of bounds, i.e. zeros
+                    for (int r = 0; r < NT * kTileQ; ++r) {
+                        const int e = I.q0 + r;
+                        const int row = e < P.n_global ? (P.gidx ? (int)P.gidx[e] : e) : P.Sq;   // no list: already gathered
+                        ptx::tma_load_4d(sQ + r * kRowBytes, &map_q, bar_q, 0, I.h, row, I.b);
+                    }
+                } else {
+                    for (int tl = 0; tl < NT; ++tl)
+                        ptx::tma_load_4d(sQ + tl * kTileQ * kRowBytes, &map_q, bar_q, 0, I.h, I.q0 + tl * kTileQ, I.b);
                 }
-            } else {
-                for (int tl = 0; tl < NT; ++tl)
-                    ptx::tma_load_4d(sQ + tl * kTileQ * kRowBytes, &map_q, bar_q, 0, h, q0 + tl * kTileQ, b);
-            }
-            int c_k = 0;
-            auto load_k = [&]() -> bool {   // K(c_k) once S(c_k - kKvStages) has left the stage
-                const int s = c_k % kKvStages;
-                if (c_k >= kKvStages && !ptx::mbar_wait(bar_kfree + s, (c_k / kKvStages - 1) & 1)) return false;
-                ptx::mbar_expect_tx(bar_k + s, kTileK * kRowBytes);
-                ptx::tma_load_4d(sKV + s * kStage, &map_k, bar_k + s, 0, h, w_k.key_base(), b);
-                ++c_k;
-                w_k.next();
-                return true;
-            };
-            if (!w_k.done()) ok = load_k();
-            for (int c = 0; ok && !w_v.done(); ++c, w_v.next()) {
-                if (!w_k.done() && !(ok = load_k())) break;
-                const int s = c % kKvStages;   // V(c) once P V(c - kKvStages) has left the stage
-                if (c >= kKvStages && !(ok = ptx::mbar_wait(bar_vfree + s, (c / kKvStages - 1) & 1))) break;
-                ptx::mbar_expect_tx(bar_v + s, kTileK * kRowBytes);
-                ptx::tma_load_4d(sKV + s * kStage + kTileK * kRowBytes, &map_v, bar_v + s, 0, h, w_v.key_base(), b);
+                auto load_k = [&]() -> bool {   // the next K chunk once the S product kKvStages chunks back has left the stage
+                    const int s = c_k % kKvStages;
+                    if (c_k >= kKvStages && !ptx::mbar_wait(bar_kfree + s, (c_k / kKvStages - 1) & 1)) return false;
+                    ptx::mbar_expect_tx(bar_k + s, kTileK * kRowBytes);
+                    ptx::tma_load_4d(sKV + s * kStage, &map_k, bar_k + s, 0, I.h, w_k.key_base(), I.b);
+                    ++c_k;
+                    w_k.next();
+                    return true;
+                };
+                if (!w_k.done()) ok = load_k();
+                for (; ok && !w_v.done(); ++c_v, w_v.next()) {
+                    if (!w_k.done() && !(ok = load_k())) break;
+                    const int s = c_v % kKvStages;   // V once the P V product kKvStages chunks back has left the stage
+                    if (c_v >= kKvStages && !(ok = ptx::mbar_wait(bar_vfree + s, (c_v / kKvStages - 1) & 1))) break;
+                    ptx::mbar_expect_tx(bar_v + s, kTileK * kRowBytes);
+                    ptx::tma_load_4d(sKV + s * kStage + kTileK * kRowBytes, &map_v, bar_v + s, 0, I.h, w_v.key_base(), I.b);
+                }
             }
             if (!ok) atomicExch(&g_umma_status, 1);
         }
@@ -304,57 +328,65 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         // ================= MMA warp of the tile: one lane issues every tcgen05.mma =================
         if (lane == 0) {
             bool ok = true;
-            ChunkWalk<NH> w_s;     // only counts the chunks here
-            if (MODE != kModeBlock) w_s.init_range(range_lo, range_hi);
-            else w_s.init(P, q0);
             const uint32_t idesc_s = instr_desc<T>(false, kTileK), idesc_pv = instr_desc<T>(true, kTileK + kSumN);
             // descriptors differ from step to step only in the start address field (16-byte units)
             const uint32_t kv_addr = ptx::smem_u32(sKV), ones_addr = ptx::smem_u32(sOnes);
             const uint64_t dkv = smem_desc(kv_addr);
-            int t_s = 0;
-            auto issue_s = [&]() -> bool {   // S(t_s) = Q K^T into S buffer t_s & 1
-                const int s = t_s % kKvStages;
-                if (!ptx::mbar_wait(bar_k + s, (t_s / kKvStages) & 1)) return false;
-                tc_fence_after();
-                const uint64_t dk = dkv + (uint64_t)(s * (kStage >> 4));
+            int base = 0;   // steps of the items before this one: step t of the item is step base + t of the barriers
+            for (uint32_t n = 0; ok && n < n_mine; ++n) {
+                const Item I = item_at(n);
+                ChunkWalk<NH> w_s;     // only counts the chunks here
+                if (MODE != kModeBlock) w_s.init_range(I.lo, I.hi);
+                else w_s.init(P, I.q0);
+                int t_s = 0;   // S products issued for this item
+                auto issue_s = [&]() -> bool {   // the next S = Q K^T, into S buffer (base + t_s) & 1
+                    const int g = base + t_s, s = g % kKvStages;
+                    if (!ptx::mbar_wait(bar_k + s, (g / kKvStages) & 1)) return false;
+                    tc_fence_after();
+                    const uint64_t dk = dkv + (uint64_t)(s * (kStage >> 4));
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)   // 16 of the 64 head columns (8 TMEM columns of Q) per instruction
-                    umma_f16_ta(tmem + (t_s & 1) * kTileK, tmem + kColQ + ks * 8, dk + ks * 2, idesc_s, ks > 0);
-                umma_commit(bar_s + (t_s & 1));
-                umma_commit(bar_kfree + s);
-                ++t_s;
-                w_s.next();
-                return true;
-            };
-            ok = ptx::mbar_wait(bar_qt, 0);   // Q is in TMEM
-            tc_fence_after();
-            if (ok && !w_s.done()) ok = issue_s();
-            for (int t = 0; ok && t < t_s; ++t) {
-                // the next scores first: their S buffer was released by p(t-1), waited for last round
-                if (!w_s.done() && !(ok = issue_s())) break;
-                const int s = t % kKvStages;
-                if (!(ok = ptx::mbar_wait(bar_v + s, (t / kKvStages) & 1))) break;
-                if (!(ok = ptx::mbar_wait(bar_p + (t & 1), (t >> 1) & 1))) break;   // P(t) is in TMEM
+                    for (int ks = 0; ks < 4; ++ks)   // 16 of the 64 head columns (8 TMEM columns of Q) per instruction
+                        umma_f16_ta(tmem + (g & 1) * kTileK, tmem + kColQ + ks * 8, dk + ks * 2, idesc_s, ks > 0);
+                    umma_commit(bar_s + (g & 1));
+                    umma_commit(bar_kfree + s);
+                    ++t_s;
+                    w_s.next();
+                    return true;
+                };
+                // Q is in TMEM.  (A softmax warp stores it after reading the previous item's O, so the first
+                // P V product below, which overwrites O, cannot run ahead of that read either.)
+                if (!(ok = ptx::mbar_wait(bar_qt, n & 1))) break;
                 tc_fence_after();
-                const uint32_t v_addr = kv_addr + s * kStage + kTileK * kRowBytes;
-                const uint32_t tp = tmem + (t & 1) * kTileK;   // P(t): 64 weights of a row in 32 columns
+                if (!w_s.done()) ok = issue_s();
+                for (int t = 0; ok && t < t_s; ++t) {
+                    // the next scores first: their S buffer was released by the P V product two steps back,
+                    // issued before this point (the tensor core runs them in order)
+                    if (!w_s.done() && !(ok = issue_s())) break;
+                    const int g = base + t, s = g % kKvStages;
+                    if (!(ok = ptx::mbar_wait(bar_v + s, (g / kKvStages) & 1))) break;
+                    if (!(ok = ptx::mbar_wait(bar_p + (g & 1), (g >> 1) & 1))) break;   // P(t) is in TMEM
+                    tc_fence_after();
+                    const uint32_t v_addr = kv_addr + s * kStage + kTileK * kRowBytes;
+                    const uint32_t tp = tmem + (g & 1) * kTileK;   // P(t): 64 weights of a row in 32 columns
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {   // [O | l] += P [V | 1], 16 of the 64 keys per instruction
-                    // B is 16 keys x 80 columns: the 64 head columns from the V stage, then a second
-                    // 64-wide block (16 of it used) that the leading-dimension offset points at the ones
-                    const uint32_t vk = v_addr + ks * 16 * kRowBytes;
-                    umma_f16_ta(tmem + kColO, tp + ks * 8, smem_desc(vk, (ones_addr - vk) >> 4), idesc_pv, t > 0 || ks > 0);
+                    for (int ks = 0; ks < 4; ++ks) {   // [O | l] += P [V | 1], 16 of the 64 keys per instruction
+                        // B is 16 keys x 80 columns: the 64 head columns from the V stage, then a second
+                        // 64-wide block (16 of it used) that the leading-dimension offset points at the ones
+                        const uint32_t vk = v_addr + ks * 16 * kRowBytes;
+                        umma_f16_ta(tmem + kColO, tp + ks * 8, smem_desc(vk, (ones_addr - vk) >> 4), idesc_pv, t > 0 || ks > 0);
+                    }
+                    umma_commit(bar_o + (g & 1));
+                    umma_commit(bar_vfree + s);
                 }
-                umma_commit(bar_o + (t & 1));
-                umma_commit(bar_vfree + s);
+                // each bar_o barrier sees every other product, so its parity names one product for a
+                // waiter that is at most one product behind; the end of an item's walk gets a barrier of its own
+                if (ok) umma_commit(bar_fin);
+                base += t_s;
             }
-            // each bar_o barrier sees every other product, so its parity names one product for a
-            // waiter that is at most one product behind; the end of the walk gets a barrier of its own
-            if (ok) umma_commit(bar_fin);
             if (!ok) atomicExch(&g_umma_status, 1);
             // every softmax warp of every tile has read its last TMEM values before the columns are freed
-            for (int tl = 0; tl < NT; ++tl)
-                if (warp == kSoftmaxWarps && !ptx::mbar_wait(tile_bars + 9 * tl + 2, 0)) atomicExch(&g_umma_status, 1);
+            for (int tl = 0; n_mine >= 1 && tl < NT; ++tl)
+                if (warp == kSoftmaxWarps && !ptx::mbar_wait(tile_bars + 9 * tl + 2, (n_mine - 1) & 1)) atomicExch(&g_umma_status, 1);
         }
         __syncwarp();
         if (warp == kSoftmaxWarps) {   // the allocating warp frees
@@ -367,16 +399,11 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     // ================= softmax warps: thread r owns query row r of its tile =================
     const int quad = warp % kSoftmaxWarpsPerTile;   // == warp % 4: the TMEM lanes this warp may access
     const int r = quad * 32 + lane;        // row of the tile == TMEM lane
-    const int tq0 = q0 + tile * kTileQ;    // first row of the tile
-    const int half = tile * 2 + (r >> 6);
-    const int p = tq0 + r + P.off;         // key-coordinate position of this row
     const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
-    float m_run = -INFINITY;   // reference maximum of the row's weights (raw score units); -inf: no key yet
     bool ok = true;
-
-    // the query row, from the swizzled tile the TMA wrote, into TMEM: the A operand of every S product
-    ok = ptx::mbar_wait(bar_q, 0);
-    {
+    // the query row, from the swizzled tile the TMA wrote, into TMEM: the A operand of every S product of item n
+    auto stage_q = [&](uint32_t n) {
+        if (!(ok = ptx::mbar_wait(bar_q, n & 1))) return;
         const uint8_t *q_row = sQ + (tile * kTileQ + r) * kRowBytes;
         uint32_t qv[32];
 #pragma unroll
@@ -388,128 +415,140 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0 && ok) ptx::mbar_arrive(bar_qt);
-    }
-
-    ChunkWalk<NH> w;
-    if (MODE != kModeBlock) w.init_range(range_lo, range_hi);
-    else w.init(P, q0);
-    // global-row pass: a warp takes part iff any of its 32 rows is a real global position
-    const bool warp_has_rows = MODE != kModeGlobalRows || tq0 + quad * 32 < P.n_global;
-    int t = 0;
-    for (; ok && !w.done(); ++t) {
-        const int kb = w.key_base();
-        const bool mine = MODE == kModeGlobalRows ? warp_has_rows : (w.flags >> half) & 1;   // uniform within a warp (dense: always)
-        w.next();   // the layout reads for the next step are in flight during this one
-        if (!(ok = ptx::mbar_wait(bar_s + (t & 1), (t >> 1) & 1))) break;
+        if (lane == 0) ptx::mbar_arrive(bar_qt);
+    };
+    if (n_mine >= 1) stage_q(0);
+    int base = 0;   // steps of the items before this one (see the MMA warp)
+    for (uint32_t n = 0; ok && n < n_mine; ++n) {
+        const Item I = item_at(n);
+        const int tq0 = I.q0 + tile * kTileQ;    // first row of the tile
+        const int half = tile * 2 + (r >> 6);
+        const int p = tq0 + r + P.off;         // key-coordinate position of this row
+        float m_run = -INFINITY;   // reference maximum of the row's weights (raw score units); -inf: no key yet
+        ChunkWalk<NH> w;
+        if (MODE != kModeBlock) w.init_range(I.lo, I.hi);
+        else w.init(P, I.q0);
+        // global-row pass: a warp takes part iff any of its 32 rows is a real global position
+        const bool warp_has_rows = MODE != kModeGlobalRows || tq0 + quad * 32 < P.n_global;
+        int t = 0;
+        for (; ok && !w.done(); ++t) {
+            const int g = base + t;
+                const int kb = w.key_base();
+            const bool mine = MODE == kModeGlobalRows ? warp_has_rows : (w.flags >> half) & 1;   // uniform within a warp (dense: always)
+            w.next();   // the layout reads for the next step are in flight during this one
+            if (!(ok = ptx::mbar_wait(bar_s + (g & 1), (g >> 1) & 1))) break;
+            tc_fence_after();
+            const uint32_t s_addr = t_lane + (g & 1) * kTileK;   // S(t), and P(t) over its first 32 columns
+            if (mine) {
+                // keys this row may use in the chunk: j < j_end
+                int j_end = min(kTileK, (MODE == kModeGlobalRows ? I.hi : P.Skv) - kb);
+                if (MODE == kModeBlock && P.causal) j_end = min(j_end, p - kb + 1);
+                int j_begin = 0;   // and j >= j_begin (a window's left edge)
+                if (MODE == kModeDense) {
+                    j_end = min(j_end, p + P.win_right - kb + 1);
+                    j_begin = p - P.win_left - kb;
+                }
+                float s[64];
+                tmem_ld64(s_addr, s);
+                if (j_end < kTileK || j_begin > 0) {   // only the chunks on an edge of the window or at the sequence end
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) if (i >= j_end || i < j_begin) s[i] = -INFINITY;
+                }
+                float mq[4];   // four independent chains of three-input maxima
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    mq[q] = max3(s[16 * q], s[16 * q + 1], s[16 * q + 2]);
+#pragma unroll
+                    for (int i = 3; i < 15; i += 2) mq[q] = max3(mq[q], s[16 * q + i], s[16 * q + i + 1]);
+                    mq[q] = fmaxf(mq[q], s[16 * q + 15]);
+                }
+                const float mx = fmaxf(max3(mq[0], mq[1], mq[2]), mq[3]);
+                // move the reference maximum only when the scores outgrow it by 2^kLazyLog2
+                const bool seen = m_run != -INFINITY;
+                const bool grow = seen ? (mx - m_run) * P.sl2 > kLazyLog2 : mx != -INFINITY;
+                const bool rescale = seen && grow;
+                const float alpha = rescale ? ptx::ex2((m_run - mx) * P.sl2) : 1.f;
+                if (grow) m_run = mx;
+                const float mus = (m_run == -INFINITY ? 0.f : m_run) * P.sl2;
+                // weights, packed to the operand type two at a time: column i of P holds keys 2i and 2i+1
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float x0, x1;
+                    ffma2(x0, x1, s[2 * i], s[2 * i + 1], P.sl2, -mus);
+                    pk[i] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
+                }
+                tmem_st32(s_addr, pk);
+                if (__any_sync(0xffffffffu, rescale)) {
+                    // O and l hold the chunks up to t-1: wait for P V(t-1), then scale this row in place
+                    if (!(ok = ptx::mbar_wait(bar_o + ((g - 1) & 1), ((g - 1) >> 1) & 1))) break;
+                    tc_fence_after();
+                    float part[64], l_part;
+                    tmem_ld64_and_1(t_lane + kColO, part, t_lane + kColSum, l_part);
+#pragma unroll
+                    for (int i = 0; i < 64; i += 2) fmul2(part[i], part[i + 1], part[i], part[i + 1], alpha);
+                    tmem_st64(t_lane + kColO, part);
+                    tmem_st1(t_lane + kColSum, l_part * alpha);
+                }
+                tmem_wait_st();
+            } else {
+                // this half sits the chunk out: its rows of P (scores at this point) must add nothing to O and l
+                uint32_t z[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) z[i] = 0u;
+                tmem_st32(s_addr, z);
+                tmem_wait_st();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_p + (g & 1));
+        }
+        if (!ok) break;
+        base += t;
+        // the accumulated row and its sum, once the item's last P V product has completed
+        float o[64];
+        float l_run = 0.f;
+        if (!(ok = ptx::mbar_wait(bar_fin, n & 1))) break;
         tc_fence_after();
-        const uint32_t s_addr = t_lane + (t & 1) * kTileK;   // S(t), and P(t) over its first 32 columns
-        if (mine) {
-            // keys this row may use in the chunk: j < j_end
-            int j_end = min(kTileK, (MODE == kModeGlobalRows ? range_hi : P.Skv) - kb);
-            if (MODE == kModeBlock && P.causal) j_end = min(j_end, p - kb + 1);
-            int j_begin = 0;   // and j >= j_begin (a window's left edge)
-            if (MODE == kModeDense) {
-                j_end = min(j_end, p + P.win_right - kb + 1);
-                j_begin = p - P.win_left - kb;
-            }
-            float s[64];
-            tmem_ld64(s_addr, s);
-            if (j_end < kTileK || j_begin > 0) {   // only the chunks on an edge of the window or at the sequence end
-#pragma unroll
-                for (int i = 0; i < 64; ++i) if (i >= j_end || i < j_begin) s[i] = -INFINITY;
-            }
-            float mq[4];   // four independent chains of three-input maxima
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                mq[q] = max3(s[16 * q], s[16 * q + 1], s[16 * q + 2]);
-#pragma unroll
-                for (int i = 3; i < 15; i += 2) mq[q] = max3(mq[q], s[16 * q + i], s[16 * q + i + 1]);
-                mq[q] = fmaxf(mq[q], s[16 * q + 15]);
-            }
-            const float mx = fmaxf(max3(mq[0], mq[1], mq[2]), mq[3]);
-            // move the reference maximum only when the scores outgrow it by 2^kLazyLog2
-            const bool seen = m_run != -INFINITY;
-            const bool grow = seen ? (mx - m_run) * P.sl2 > kLazyLog2 : mx != -INFINITY;
-            const bool rescale = seen && grow;
-            const float alpha = rescale ? ptx::ex2((m_run - mx) * P.sl2) : 1.f;
-            if (grow) m_run = mx;
-            const float mus = (m_run == -INFINITY ? 0.f : m_run) * P.sl2;
-            // weights, packed to the operand type two at a time: column i of P holds keys 2i and 2i+1
-            uint32_t pk[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                float x0, x1;
-                ffma2(x0, x1, s[2 * i], s[2 * i + 1], P.sl2, -mus);
-                pk[i] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
-            }
-            tmem_st32(s_addr, pk);
-            if (__any_sync(0xffffffffu, rescale)) {
-                // O and l hold the chunks up to t-1: wait for P V(t-1), then scale this row in place
-                if (!(ok = ptx::mbar_wait(bar_o + ((t - 1) & 1), ((t - 1) >> 1) & 1))) break;
-                tc_fence_after();
-                float part[64], l_part;
-                tmem_ld64_and_1(t_lane + kColO, part, t_lane + kColSum, l_part);
-#pragma unroll
-                for (int i = 0; i < 64; i += 2) fmul2(part[i], part[i + 1], part[i], part[i + 1], alpha);
-                tmem_st64(t_lane + kColO, part);
-                tmem_st1(t_lane + kColSum, l_part * alpha);
-            }
-            tmem_wait_st();
+        if (t >= 1) {
+            tmem_ld64_and_1(t_lane + kColO, o, t_lane + kColSum, l_run);
         } else {
-            // this half sits the chunk out: its rows of P (scores at this point) must add nothing to O and l
-            uint32_t z[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) z[i] = 0u;
-            tmem_st32(s_addr, z);
-            tmem_wait_st();
+            for (int i = 0; i < 64; ++i) o[i] = 0.f;
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar_p + (t & 1));
-    }
-    // the accumulated row and its sum, once the last P V has completed
-    float o[64];
-    float l_run = 0.f;
-    if (ok && t >= 1) {
-        ok = ptx::mbar_wait(bar_fin, 0);
-        tc_fence_after();
-        if (ok) tmem_ld64_and_1(t_lane + kColO, o, t_lane + kColSum, l_run);
-    }
-    if (!ok || t == 0) {
+        if (lane == 0) ptx::mbar_arrive(bar_done);
+        // the next item's queries go to TMEM before this item's rows are written out: the tensor core
+        // starts on its scores while the stores below are under way
+        if (n + 1 < n_mine) {
+            stage_q(n + 1);
+            if (!ok) break;
+        }
+        if (MODE == kModeGlobalRows) {
+            if (tq0 + r < P.n_global) {
+                float *pr = P.partial +
+                            ((((int64_t)I.b * P.H + I.h) * P.n_splits + I.split) * P.ng_pad + tq0 + r) * kPartialStride;
+                pr[0] = m_run;
+                pr[1] = l_run;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) o[i] = 0.f;
-        l_run = 0.f;
+                for (int i = 0; i < 64; i += 2) *reinterpret_cast<float2 *>(pr + 2 + i) = make_float2(o[i], o[i + 1]);
+            }
+        } else if (tq0 + r < P.Sq) {
+            const float inv = l_run > 0.f ? __frcp_rn(l_run) : 0.f;
+            T *dst = out + (((int64_t)I.b * P.Sq + tq0 + r) * P.H + I.h) * 64;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                uint4 v;
+                v.x = ptx::Mma<T>::pack(o[8 * q] * inv, o[8 * q + 1] * inv);
+                v.y = ptx::Mma<T>::pack(o[8 * q + 2] * inv, o[8 * q + 3] * inv);
+                v.z = ptx::Mma<T>::pack(o[8 * q + 4] * inv, o[8 * q + 5] * inv);
+                v.w = ptx::Mma<T>::pack(o[8 * q + 6] * inv, o[8 * q + 7] * inv);
+                *reinterpret_cast<uint4 *>(dst + 8 * q) = v;
+            }
+        }
     }
     if (!ok) atomicExch(&g_umma_status, 1);
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(bar_done);
-
-    if (MODE == kModeGlobalRows) {
-        if (ok && tq0 + r < P.n_global) {
-            float *pr = P.partial +
-                        ((((int64_t)b * P.H + h) * P.n_splits + split) * P.ng_pad + tq0 + r) * kPartialStride;
-            pr[0] = m_run;
-            pr[1] = l_run;
-#pragma unroll
-            for (int i = 0; i < 64; i += 2) *reinterpret_cast<float2 *>(pr + 2 + i) = make_float2(o[i], o[i + 1]);
-        }
-        return;
-    }
-    if (ok && tq0 + r < P.Sq) {
-        const float inv = l_run > 0.f ? __frcp_rn(l_run) : 0.f;
-        T *dst = out + (((int64_t)b * P.Sq + tq0 + r) * P.H + h) * 64;
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            uint4 v;
-            v.x = ptx::Mma<T>::pack(o[8 * q] * inv, o[8 * q + 1] * inv);
-            v.y = ptx::Mma<T>::pack(o[8 * q + 2] * inv, o[8 * q + 3] * inv);
-            v.z = ptx::Mma<T>::pack(o[8 * q + 4] * inv, o[8 * q + 5] * inv);
-            v.w = ptx::Mma<T>::pack(o[8 * q + 6] * inv, o[8 * q + 7] * inv);
-            *reinterpret_cast<uint4 *>(dst + 8 * q) = v;
-        }
-    }
 }
 
 // ---- host side --------------------------------------------------------------------------------
@@ -552,12 +591,23 @@ int tiles_per_cta() {
     return e && e[0] == '2' ? 2 : 1;
 }
 
+// grid = (heads, y, batch) of work items; the launch is a persistent grid of at most as many CTAs as are
+// resident at one time (the tensor memory holds two one-tile CTAs or one two-tile CTA per SM)
 template <typename T, int MODE, int NT>
-int launch_mode(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, T *out, const UmmaParams &up,
+int launch_mode(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, T *out, const UmmaParams &up_in,
                 dim3 grid, cudaStream_t stream, const char *what) {
     auto kern = umma_block_fwd_kernel<T, MODE, NT>;
     if (int rc = ensure_dynamic_smem((const void *)kern, Cfg<NT>::kSmemBytes, what)) return rc;
-    kern<<<grid, Cfg<NT>::kThreads, Cfg<NT>::kSmemBytes, stream>>>(mq, mk, mv, out, up);
+    const uint64_t n_work = (uint64_t)grid.x * grid.y * grid.z;
+    if (n_work == 0) return MAT_OK;
+    if (n_work >= (1ull << 31)) return fail(MAT_ERR_UNSUPPORTED, "%s: too many tiles", what);
+    UmmaParams up = up_in;
+    up.n_work = (uint32_t)n_work;
+    up.grid_y = grid.y;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const unsigned ctas = (unsigned)std::min<uint64_t>(n_work, (uint64_t)sms * (NT == 1 ? 2 : 1));
+    kern<<<ctas, Cfg<NT>::kThreads, Cfg<NT>::kSmemBytes, stream>>>(mq, mk, mv, out, up);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? MAT_OK : cuda_fail(e, what);
 }
