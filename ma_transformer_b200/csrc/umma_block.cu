@@ -58,7 +58,11 @@ constexpr int kTileK = 64;      // keys per step (UMMA N for S, K extent for P V
 // TMEM columns of one tile (256 allocated): S buffers in [0,128), O in [128,192), row sums in [192,208), Q in [208,240)
 constexpr int kColO = 128, kColSum = 192, kColQ = 208;   // Q: 64 values of a row in 32 columns
 constexpr int kSumN = 16;       // N grows in steps of 16 for M = 128; column 0 of the extra 16 is read
-constexpr float kLazyLog2 = 1.f;  // a row's reference maximum moves when the scores outgrow it by 2^1
+// A row's reference maximum moves (and O and l are rescaled) only when the scores outgrow it by 2^8: until then
+// the weights are at most 256, well inside both 16-bit formats, and the sums are fp32.  With a threshold of 2 nearly
+// every early step of a walk rescaled (some row of the warp always grew), which cost a wait for the previous P V
+// product and a round trip of O through the registers per step.
+constexpr float kLazyLog2 = 8.f;
 
 __device__ int g_umma_status = 0;
 
@@ -99,8 +103,9 @@ struct ChunkWalk {
     int cur;             // current key block, -1 when exhausted
     int hit;             // bit i: half i's own cursor stands on the current block
     int flags;           // bit i: half i holds the current block
-    __device__ __forceinline__ void init(const UmmaParams &P, int q0) {
-        colidx = P.colidx;
+    // rowptr / colidx: the layout, in global memory or the CTA's copy of it in shared memory
+    __device__ __forceinline__ void init(const UmmaParams &P, const int32_t *rowptr, const int32_t *colidx_, int q0) {
+        colidx = colidx_;
         per_blk = P.per_blk;
         block = P.block;
         int64_t prev_row = -1;
@@ -111,7 +116,7 @@ struct ChunkWalk {
             rep[i] = i;
             const int64_t row = (int64_t)((uint32_t)(q0 + 64 * i + P.off) / (uint32_t)P.block);
             if (i > 0 && row == prev_row) { rep[i] = prev_i; continue; }
-            if (q0 + 64 * i < P.Sq && row < P.n_qblocks) { it[i] = P.rowptr[row]; en[i] = P.rowptr[row + 1]; }
+            if (q0 + 64 * i < P.Sq && row < P.n_qblocks) { it[i] = rowptr[row]; en[i] = rowptr[row + 1]; }
             prev_row = row;
             prev_i = i;
         }
@@ -123,7 +128,7 @@ struct ChunkWalk {
         int c = INT32_MAX;
 #pragma unroll
         for (int i = 0; i < NH; ++i) {
-            col[i] = it[i] < en[i] ? __ldg(colidx + it[i]) : INT32_MAX;
+            col[i] = it[i] < en[i] ? colidx[it[i]] : INT32_MAX;
             c = min(c, col[i]);
         }
         if (c == INT32_MAX) { cur = -1; hit = flags = 0; return; }
@@ -161,16 +166,21 @@ struct ChunkWalk {
 // NT = 128-row query tiles per CTA.  One tile: 256 TMEM columns, two CTAs per SM.  Two tiles: all 512
 // columns, one CTA per SM, and every K/V chunk fetched from L2 serves 256 query rows instead of 128.
 constexpr int kSoftmaxWarpsPerTile = 4;
-template <int NT> struct Cfg {
+// QS = query tiles held in shared memory: 1 when the softmax warps copy Q into TMEM (the A operand of the S
+// products comes from there), 2 when the S products read Q from shared memory, double-buffered over items.
+template <int NT, int QS> struct Cfg {
     static constexpr int kSoftmaxWarps = kSoftmaxWarpsPerTile * NT;
     static constexpr int kThreads = (kSoftmaxWarps + NT + 1) * 32;   // softmax warps, one MMA warp per tile, load warp
-    static constexpr int kKvStages = NT == 1 ? 5 : 8;
+    static constexpr int kKvStages = NT == 1 ? (QS == 2 ? 4 : 5) : 8;   // (two CTAs of one tile share an SM's shared memory)
     static constexpr int kTmemCols = 256 * NT;
-    static constexpr int kBars = 2 + NT * 9 + 4 * kKvStages;
-    static constexpr size_t kSmemBytes = 1024 + (size_t)NT * kTileQ * kRowBytes /*Q*/ +
+    static constexpr int kBars = 2 + NT * 9 + 4 * kKvStages + 2;
+    // block layouts: the CTA's copy of the layout (row pointers, then column ids) when it fits
+    static constexpr int kLayoutInts = QS == 2 ? 3072 : 0;
+    static constexpr size_t kSmemBytes = 1024 + (size_t)QS * NT * kTileQ * kRowBytes /*Q*/ +
                                          (size_t)kKvStages * 2 * kTileK * kRowBytes + kSumN * kRowBytes +
-                                         kBars * 8 + 16 /*tmem address*/;
+                                         kBars * 8 + 16 /*tmem address*/ + kLayoutInts * 4;
 };
+__host__ __device__ constexpr int qs_of(int mode) { return mode == 0 /* kModeBlock */ ? 2 : 1; }
 constexpr int kStage = 2 * kTileK * kRowBytes;  // one K/V stage: K then V
 constexpr int kOnesBytes = kSumN * kRowBytes;   // the second 64-wide block of the P V product's B operand: ones
 
@@ -186,14 +196,23 @@ constexpr int kOnesBytes = kSumN * kRowBytes;   // the second 64-wide block of t
 //              first chunk overwrites).
 //   softmax:   softmax(t) -> store P(t) -> (rarely: wait for P V(t-1), rescale O and l) -> publish.
 template <typename T, int MODE, int NT>
-__global__ void __launch_bounds__(Cfg<NT>::kThreads)
+__global__ void __launch_bounds__(Cfg<NT, qs_of(MODE)>::kThreads)
 umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, T *__restrict__ out, const UmmaParams P) {
-    constexpr int kSoftmaxWarps = Cfg<NT>::kSoftmaxWarps, kKvStages = Cfg<NT>::kKvStages, NH = 2 * NT;
+    // Block layouts (short walks, so what happens between two items counts): the S products read Q from shared
+    // memory, where the next item's tile lands while this one's is in use, and nothing of the hand-over from
+    // one item to the next runs through the softmax warps.  The long walks (dense, wide windows, global rows)
+    // keep Q in TMEM: there the shared-memory reads per step are what matters.
+    constexpr bool kQsmem = MODE == kModeBlock;
+    constexpr int QS = qs_of(MODE);
+    static_assert(!kQsmem || NT == 1, "the shared-memory Q path is written for one tile per CTA");
+    using C = Cfg<NT, QS>;
+    constexpr int kSoftmaxWarps = C::kSoftmaxWarps, kKvStages = C::kKvStages, NH = 2 * NT;
+    constexpr int kQBytes = NT * kTileQ * kRowBytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t *sQ = smem;                                // NT tiles of 128 rows
-    uint8_t *sKV = sQ + NT * kTileQ * kRowBytes;       // stage s: K at +0, V at +8 KB
+    uint8_t *sQ = smem;                                // QS buffers of NT tiles of 128 rows
+    uint8_t *sKV = sQ + QS * kQBytes;                  // stage s: K at +0, V at +8 KB
     uint8_t *sOnes = sKV + kKvStages * kStage;         // 16 rows of ones
     uint64_t *bars = (uint64_t *)(sOnes + kOnesBytes);
     // shared by the tiles: Q arrival, K/V arrival and release per stage
@@ -201,7 +220,9 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
              *bar_vfree = bar_kfree + kKvStages;
     // per tile (9 each): Q in TMEM, end of walk, TMEM reads done, S ready [2], P ready [2], P V done [2]
     uint64_t *tile_bars = bar_vfree + kKvStages;
-    uint32_t *tmem_slot = (uint32_t *)(tile_bars + 9 * NT);
+    uint64_t *bar_qfree = tile_bars + 9 * NT;   // [2]: the S products of an item have left its Q buffer
+    uint32_t *tmem_slot = (uint32_t *)(bar_qfree + 2);
+    int32_t *sLayout = (int32_t *)(tmem_slot + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // Persistent: CTA c works on items c, c + G, c + 2G, ...; every barrier's phase runs on across items
@@ -233,7 +254,10 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     };
 
     if (threadIdx.x == 0) {
-        ptx::mbar_init(bar_q, 1);
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(bar_q + i, 1);
+            ptx::mbar_init(bar_qfree + i, NT);
+        }
         for (int i = 0; i < kKvStages; ++i) {
             ptx::mbar_init(bar_k + i, 1);
             ptx::mbar_init(bar_v + i, 1);
@@ -253,13 +277,27 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         ptx::fence_barrier_init();
     }
+    // Block layouts: every role walks the layout rows of its items, and the walk's reads sit on its critical
+    // path (each is a row pointer, then a column id per step).  A persistent CTA sees many rows, so it copies
+    // the whole layout into shared memory once when that fits; a larger layout is read from global memory.
+    const int32_t *rowptr = P.rowptr, *colidx = P.colidx;
+    if (MODE == kModeBlock && P.n_qblocks + 1 <= C::kLayoutInts) {
+        const int n_row = (int)P.n_qblocks + 1;
+        const int nnz = P.rowptr[P.n_qblocks];
+        if (nnz >= 0 && n_row + nnz <= C::kLayoutInts) {
+            for (int i = threadIdx.x; i < n_row; i += blockDim.x) sLayout[i] = P.rowptr[i];
+            for (int i = threadIdx.x; i < nnz; i += blockDim.x) sLayout[n_row + i] = P.colidx[i];
+            rowptr = sLayout;
+            colidx = sLayout + n_row;
+        }
+    }
     if (threadIdx.x < kOnesBytes / 16) {
         const uint32_t one2 = ptx::Mma<T>::kOnes;
         reinterpret_cast<uint4 *>(sOnes)[threadIdx.x] = make_uint4(one2, one2, one2, one2);
         ptx::fence_proxy_async_smem();
     }
     if (warp == kSoftmaxWarps) {
-        tmem_alloc(tmem_slot, Cfg<NT>::kTmemCols);
+        tmem_alloc(tmem_slot, C::kTmemCols);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -278,23 +316,31 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 const Item I = item_at(n);
                 ChunkWalk<NH> w_k, w_v;   // K runs one chunk ahead of V: its stage is free earlier (after S, not after P V)
                 if (MODE != kModeBlock) w_k.init_range(I.lo, I.hi);
-                else w_k.init(P, I.q0);
+                else w_k.init(P, rowptr, colidx, I.q0);
                 w_v = w_k;
-                // the softmax warps have copied the previous item's Q out of shared memory
-                for (int tl = 0; n >= 1 && tl < NT; ++tl) ok = ok && ptx::mbar_wait(tile_bars + 9 * tl, (n - 1) & 1);
-                if (!ok) break;
-                ptx::mbar_expect_tx(bar_q, NT * kTileQ * kRowBytes);
-                if (MODE == kModeGlobalRows) {
-                    // map_q is a one-row view here: row r of the tile is the query at global position
-                    // gidx[q0 + r]; slots past the list read out of bounds, i.e. zeros
-                    for (int r = 0; r < NT * kTileQ; ++r) {
-                        const int e = I.q0 + r;
-                        const int row = e < P.n_global ? (P.gidx ? (int)P.gidx[e] : e) : P.Sq;   // no list: already gathered
-                        ptx::tma_load_4d(sQ + r * kRowBytes, &map_q, bar_q, 0, I.h, row, I.b);
-                    }
+                if (kQsmem) {
+                    // buffer n & 1, once the S products of item n - 2 have left it
+                    const int qb = n & 1;
+                    if (n >= 2 && !(ok = ptx::mbar_wait(bar_qfree + qb, ((n >> 1) - 1) & 1))) break;
+                    ptx::mbar_expect_tx(bar_q + qb, kQBytes);
+                    ptx::tma_load_4d(sQ + qb * kQBytes, &map_q, bar_q + qb, 0, I.h, I.q0, I.b);
                 } else {
-                    for (int tl = 0; tl < NT; ++tl)
-                        ptx::tma_load_4d(sQ + tl * kTileQ * kRowBytes, &map_q, bar_q, 0, I.h, I.q0 + tl * kTileQ, I.b);
+                    // the softmax warps have copied the previous item's Q out of shared memory
+                    for (int tl = 0; n >= 1 && tl < NT; ++tl) ok = ok && ptx::mbar_wait(tile_bars + 9 * tl, (n - 1) & 1);
+                    if (!ok) break;
+                    ptx::mbar_expect_tx(bar_q, kQBytes);
+                    if (MODE == kModeGlobalRows) {
+                        // map_q is a one-row view here: row r of the tile is the query at global position
+                        // gidx[q0 + r]; slots past the list read out of bounds, i.e. zeros
+                        for (int r = 0; r < NT * kTileQ; ++r) {
+                            const int e = I.q0 + r;
+                            const int row = e < P.n_global ? (P.gidx ? (int)P.gidx[e] : e) : P.Sq;   // no list: already gathered
+                            ptx::tma_load_4d(sQ + r * kRowBytes, &map_q, bar_q, 0, I.h, row, I.b);
+                        }
+                    } else {
+                        for (int tl = 0; tl < NT; ++tl)
+                            ptx::tma_load_4d(sQ + tl * kTileQ * kRowBytes, &map_q, bar_q, 0, I.h, I.q0 + tl * kTileQ, I.b);
+                    }
                 }
                 auto load_k = [&]() -> bool {   // the next K chunk once the S product kKvStages chunks back has left the stage
                     const int s = c_k % kKvStages;
@@ -337,25 +383,32 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 const Item I = item_at(n);
                 ChunkWalk<NH> w_s;     // only counts the chunks here
                 if (MODE != kModeBlock) w_s.init_range(I.lo, I.hi);
-                else w_s.init(P, I.q0);
+                else w_s.init(P, rowptr, colidx, I.q0);
                 int t_s = 0;   // S products issued for this item
+                const uint64_t dq = smem_desc(ptx::smem_u32(sQ) + (n & 1) * (kQsmem ? kQBytes : 0));   // (Q in shared memory)
                 auto issue_s = [&]() -> bool {   // the next S = Q K^T, into S buffer (base + t_s) & 1
                     const int g = base + t_s, s = g % kKvStages;
                     if (!ptx::mbar_wait(bar_k + s, (g / kKvStages) & 1)) return false;
                     tc_fence_after();
                     const uint64_t dk = dkv + (uint64_t)(s * (kStage >> 4));
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks)   // 16 of the 64 head columns (8 TMEM columns of Q) per instruction
-                        umma_f16_ta(tmem + (g & 1) * kTileK, tmem + kColQ + ks * 8, dk + ks * 2, idesc_s, ks > 0);
+                    for (int ks = 0; ks < 4; ++ks) {   // 16 of the 64 head columns per instruction (8 TMEM columns, or 32 bytes of a row, of Q)
+                        if (kQsmem) umma_f16_ss(tmem + (g & 1) * kTileK, dq + ks * 2, dk + ks * 2, idesc_s, ks > 0);
+                        else umma_f16_ta(tmem + (g & 1) * kTileK, tmem + kColQ + ks * 8, dk + ks * 2, idesc_s, ks > 0);
+                    }
                     umma_commit(bar_s + (g & 1));
                     umma_commit(bar_kfree + s);
                     ++t_s;
                     w_s.next();
                     return true;
                 };
-                // Q is in TMEM.  (A softmax warp stores it after reading the previous item's O, so the first
-                // P V product below, which overwrites O, cannot run ahead of that read either.)
-                if (!(ok = ptx::mbar_wait(bar_qt, n & 1))) break;
+                if (kQsmem) {
+                    if (!(ok = ptx::mbar_wait(bar_q + (n & 1), (n >> 1) & 1))) break;   // Q has landed in its buffer
+                } else {
+                    // Q is in TMEM.  (A softmax warp stores it after reading the previous item's O, so the first
+                    // P V product below, which overwrites O, cannot run ahead of that read either.)
+                    if (!(ok = ptx::mbar_wait(bar_qt, n & 1))) break;
+                }
                 tc_fence_after();
                 if (!w_s.done()) ok = issue_s();
                 for (int t = 0; ok && t < t_s; ++t) {
@@ -365,6 +418,8 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     const int g = base + t, s = g % kKvStages;
                     if (!(ok = ptx::mbar_wait(bar_v + s, (g / kKvStages) & 1))) break;
                     if (!(ok = ptx::mbar_wait(bar_p + (g & 1), (g >> 1) & 1))) break;   // P(t) is in TMEM
+                    // the item's first product overwrites O: the previous item's rows have been read out of it
+                    if (kQsmem && t == 0 && n >= 1 && !(ok = ptx::mbar_wait(bar_done, (n - 1) & 1))) break;
                     tc_fence_after();
                     const uint32_t v_addr = kv_addr + s * kStage + kTileK * kRowBytes;
                     const uint32_t tp = tmem + (g & 1) * kTileK;   // P(t): 64 weights of a row in 32 columns
@@ -381,6 +436,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 // each bar_o barrier sees every other product, so its parity names one product for a
                 // waiter that is at most one product behind; the end of an item's walk gets a barrier of its own
                 if (ok) umma_commit(bar_fin);
+                if (ok && kQsmem) umma_commit(bar_qfree + (n & 1));
                 base += t_s;
             }
             if (!ok) atomicExch(&g_umma_status, 1);
@@ -391,7 +447,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         __syncwarp();
         if (warp == kSoftmaxWarps) {   // the allocating warp frees
             tc_fence_after();
-            tmem_dealloc(tmem_base, Cfg<NT>::kTmemCols);
+            tmem_dealloc(tmem_base, C::kTmemCols);
         }
         return;
     }
@@ -417,8 +473,65 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(bar_qt);
     };
-    if (n_mine >= 1) stage_q(0);
+    if (!kQsmem && n_mine >= 1) stage_q(0);
+    // what the read-out of an item needs once its walk is over
+    struct Finished {
+        Item I;
+        uint32_t n;
+        int steps;
+        float m_run;
+    };
+    // The accumulated row and its sum, once the item's last P V product has completed; then the row is written out.
+    // Q in TMEM: the next item's queries go there before the rows are written, so that the tensor core starts
+    // on its scores while the stores are under way.
+    auto read_out = [&](const Finished &f) {
+        const int tq0 = f.I.q0 + tile * kTileQ;
+        float o[64];
+        float l_run = 0.f;
+        if (!(ok = ptx::mbar_wait(bar_fin, f.n & 1))) return;
+        tc_fence_after();
+        if (f.steps >= 1) {
+            tmem_ld64_and_1(t_lane + kColO, o, t_lane + kColSum, l_run);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) o[i] = 0.f;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar_done);
+        if (!kQsmem && f.n + 1 < n_mine) {
+            stage_q(f.n + 1);
+            if (!ok) return;
+        }
+        if (MODE == kModeGlobalRows) {
+            if (tq0 + r < P.n_global) {
+                float *pr = P.partial +
+                            ((((int64_t)f.I.b * P.H + f.I.h) * P.n_splits + f.I.split) * P.ng_pad + tq0 + r) * kPartialStride;
+                pr[0] = f.m_run;
+                pr[1] = l_run;
+#pragma unroll
+                for (int i = 0; i < 64; i += 2) *reinterpret_cast<float2 *>(pr + 2 + i) = make_float2(o[i], o[i + 1]);
+            }
+        } else if (tq0 + r < P.Sq) {
+            const float inv = l_run > 0.f ? __frcp_rn(l_run) : 0.f;
+            T *dst = out + (((int64_t)f.I.b * P.Sq + tq0 + r) * P.H + f.I.h) * 64;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                uint4 v;
+                v.x = ptx::Mma<T>::pack(o[8 * q] * inv, o[8 * q + 1] * inv);
+                v.y = ptx::Mma<T>::pack(o[8 * q + 2] * inv, o[8 * q + 3] * inv);
+                v.z = ptx::Mma<T>::pack(o[8 * q + 4] * inv, o[8 * q + 5] * inv);
+                v.w = ptx::Mma<T>::pack(o[8 * q + 6] * inv, o[8 * q + 7] * inv);
+                *reinterpret_cast<uint4 *>(dst + 8 * q) = v;
+            }
+        }
+    };
     int base = 0;   // steps of the items before this one (see the MMA warp)
+    // Q in shared memory: an item's read-out waits until the weights of the NEXT item's first step are stored (its
+    // scores were computed while this item's last steps ran, and that step never touches O), so the wait for the
+    // last P V product and the read of O sit behind useful work instead of between two items.
+    bool pending = false;
+    Finished fin;
     for (uint32_t n = 0; ok && n < n_mine; ++n) {
         const Item I = item_at(n);
         const int tq0 = I.q0 + tile * kTileQ;    // first row of the tile
@@ -427,13 +540,13 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         float m_run = -INFINITY;   // reference maximum of the row's weights (raw score units); -inf: no key yet
         ChunkWalk<NH> w;
         if (MODE != kModeBlock) w.init_range(I.lo, I.hi);
-        else w.init(P, I.q0);
+        else w.init(P, rowptr, colidx, I.q0);
         // global-row pass: a warp takes part iff any of its 32 rows is a real global position
         const bool warp_has_rows = MODE != kModeGlobalRows || tq0 + quad * 32 < P.n_global;
         int t = 0;
         for (; ok && !w.done(); ++t) {
             const int g = base + t;
-                const int kb = w.key_base();
+            const int kb = w.key_base();
             const bool mine = MODE == kModeGlobalRows ? warp_has_rows : (w.flags >> half) & 1;   // uniform within a warp (dense: always)
             w.next();   // the layout reads for the next step are in flight during this one
             if (!(ok = ptx::mbar_wait(bar_s + (g & 1), (g >> 1) & 1))) break;
@@ -502,52 +615,25 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar_p + (g & 1));
+            if (pending) {   // (only with Q in shared memory, and only at an item's first step)
+                pending = false;
+                read_out(fin);
+            }
+        }
+        if (ok && pending) {   // an item without a step
+            pending = false;
+            read_out(fin);
         }
         if (!ok) break;
         base += t;
-        // the accumulated row and its sum, once the item's last P V product has completed
-        float o[64];
-        float l_run = 0.f;
-        if (!(ok = ptx::mbar_wait(bar_fin, n & 1))) break;
-        tc_fence_after();
-        if (t >= 1) {
-            tmem_ld64_and_1(t_lane + kColO, o, t_lane + kColSum, l_run);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 64; ++i) o[i] = 0.f;
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar_done);
-        // the next item's queries go to TMEM before this item's rows are written out: the tensor core
-        // starts on its scores while the stores below are under way
-        if (n + 1 < n_mine) {
-            stage_q(n + 1);
-            if (!ok) break;
-        }
-        if (MODE == kModeGlobalRows) {
-            if (tq0 + r < P.n_global) {
-                float *pr = P.partial +
-                            ((((int64_t)I.b * P.H + I.h) * P.n_splits + I.split) * P.ng_pad + tq0 + r) * kPartialStride;
-                pr[0] = m_run;
-                pr[1] = l_run;
-#pragma unroll
-                for (int i = 0; i < 64; i += 2) *reinterpret_cast<float2 *>(pr + 2 + i) = make_float2(o[i], o[i + 1]);
-            }
-        } else if (tq0 + r < P.Sq) {
-            const float inv = l_run > 0.f ? __frcp_rn(l_run) : 0.f;
-            T *dst = out + (((int64_t)I.b * P.Sq + tq0 + r) * P.H + I.h) * 64;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                uint4 v;
-                v.x = ptx::Mma<T>::pack(o[8 * q] * inv, o[8 * q + 1] * inv);
-                v.y = ptx::Mma<T>::pack(o[8 * q + 2] * inv, o[8 * q + 3] * inv);
-                v.z = ptx::Mma<T>::pack(o[8 * q + 4] * inv, o[8 * q + 5] * inv);
-                v.w = ptx::Mma<T>::pack(o[8 * q + 6] * inv, o[8 * q + 7] * inv);
-                *reinterpret_cast<uint4 *>(dst + 8 * q) = v;
-            }
-        }
+        fin.I = I;
+        fin.n = n;
+        fin.steps = t;
+        fin.m_run = m_run;
+        if (kQsmem) pending = true;
+        else read_out(fin);
     }
+    if (ok && pending) read_out(fin);
     if (!ok) atomicExch(&g_umma_status, 1);
 }
 
@@ -585,7 +671,8 @@ int make_map(CUtensorMap *m, const void *base, int dtype, int64_t H, int64_t S, 
 // One 128-row tile per CTA (two CTAs per SM) is the measured optimum: two tiles per CTA sharing the
 // K/V stages fetch every chunk from L2 half as often but came out slower (dense 16K tokens x 8 heads:
 // 0.91 ms against 0.83 ms; the 16K block-sparse workload 267 us against 193 us), so the L2 -> shared
-// memory traffic is not what bounds the walk.  MAT_UMMA_TILES=2 selects the two-tile variant.
+// memory traffic is not what bounds the walk.  MAT_UMMA_TILES=2 selects the two-tile variant for the dense
+// walks (a measurement aid; block layouts always run one tile per CTA).
 int tiles_per_cta() {
     const char *e = std::getenv("MAT_UMMA_TILES");
     return e && e[0] == '2' ? 2 : 1;
@@ -597,7 +684,8 @@ template <typename T, int MODE, int NT>
 int launch_mode(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, T *out, const UmmaParams &up_in,
                 dim3 grid, cudaStream_t stream, const char *what) {
     auto kern = umma_block_fwd_kernel<T, MODE, NT>;
-    if (int rc = ensure_dynamic_smem((const void *)kern, Cfg<NT>::kSmemBytes, what)) return rc;
+    using C = Cfg<NT, qs_of(MODE)>;
+    if (int rc = ensure_dynamic_smem((const void *)kern, C::kSmemBytes, what)) return rc;
     const uint64_t n_work = (uint64_t)grid.x * grid.y * grid.z;
     if (n_work == 0) return MAT_OK;
     if (n_work >= (1ull << 31)) return fail(MAT_ERR_UNSUPPORTED, "%s: too many tiles", what);
@@ -607,7 +695,7 @@ int launch_mode(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap 
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const unsigned ctas = (unsigned)std::min<uint64_t>(n_work, (uint64_t)sms * (NT == 1 ? 2 : 1));
-    kern<<<ctas, Cfg<NT>::kThreads, Cfg<NT>::kSmemBytes, stream>>>(mq, mk, mv, out, up);
+    kern<<<ctas, C::kThreads, C::kSmemBytes, stream>>>(mq, mk, mv, out, up);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? MAT_OK : cuda_fail(e, what);
 }
@@ -632,10 +720,8 @@ int launch_t(const Problem &p) {
     up.colidx = p.pat.colidx;
     up.sl2 = p.scale * 1.4426950408889634f;
     up.n_global = 0; up.gidx = nullptr; up.split_len = up.n_splits = up.ng_pad = 0; up.partial = nullptr;
-    const int nt = tiles_per_cta();
-    const dim3 grid((unsigned)p.H, (unsigned)((p.Sq + nt * kTileQ - 1) / (nt * kTileQ)), (unsigned)p.B);
-    const int rc = nt == 2 ? launch_mode<T, kModeBlock, 2>(mq, mk, mv, (T *)p.o, up, grid, p.stream, "umma block kernel")
-                           : launch_mode<T, kModeBlock, 1>(mq, mk, mv, (T *)p.o, up, grid, p.stream, "umma block kernel");
+    const dim3 grid((unsigned)p.H, (unsigned)((p.Sq + kTileQ - 1) / kTileQ), (unsigned)p.B);
+    const int rc = launch_mode<T, kModeBlock, 1>(mq, mk, mv, (T *)p.o, up, grid, p.stream, "umma block kernel");
     if (rc == MAT_OK) note_kernel("umma_block");
     return rc;
 }
