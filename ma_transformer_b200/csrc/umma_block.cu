@@ -66,6 +66,15 @@ constexpr float kLazyLog2 = 8.f;
 
 __device__ int g_umma_status = 0;
 
+// Timeline of the first steps of CTA 0 (build with -DMAT_BLOCK_TRACE; read with mat_debug_block_trace):
+// slot [role][step][event] = %globaltimer at that point.  Compiled out otherwise.
+#ifdef MAT_BLOCK_TRACE
+__device__ unsigned long long g_btrace[2 * 48 * 8];
+#define BTR(role, step, ev) do { if (blockIdx.x == 0 && (step) < 48) g_btrace[((role) * 48 + (step)) * 8 + (ev)] = ptx::global_ns(); } while (0)
+#else
+#define BTR(role, step, ev) do { } while (0)
+#endif
+
 struct UmmaParams {
     int32_t Sq, Skv, off;  // query rows, key rows, q_offset
     int32_t H;
@@ -388,8 +397,10 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 const uint64_t dq = smem_desc(ptx::smem_u32(sQ) + (n & 1) * (kQsmem ? kQBytes : 0));   // (Q in shared memory)
                 auto issue_s = [&]() -> bool {   // the next S = Q K^T, into S buffer (base + t_s) & 1
                     const int g = base + t_s, s = g % kKvStages;
+                    BTR(1, g, 0);
                     if (!ptx::mbar_wait(bar_k + s, (g / kKvStages) & 1)) return false;
                     tc_fence_after();
+                    BTR(1, g, 1);
                     const uint64_t dk = dkv + (uint64_t)(s * (kStage >> 4));
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {   // 16 of the 64 head columns per instruction (8 TMEM columns, or 32 bytes of a row, of Q)
@@ -398,6 +409,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     }
                     umma_commit(bar_s + (g & 1));
                     umma_commit(bar_kfree + s);
+                    BTR(1, g, 2);
                     ++t_s;
                     w_s.next();
                     return true;
@@ -416,8 +428,11 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     // issued before this point (the tensor core runs them in order)
                     if (!w_s.done() && !(ok = issue_s())) break;
                     const int g = base + t, s = g % kKvStages;
+                    BTR(1, g, 3);
                     if (!(ok = ptx::mbar_wait(bar_v + s, (g / kKvStages) & 1))) break;
+                    BTR(1, g, 4);
                     if (!(ok = ptx::mbar_wait(bar_p + (g & 1), (g >> 1) & 1))) break;   // P(t) is in TMEM
+                    BTR(1, g, 5);
                     // the item's first product overwrites O: the previous item's rows have been read out of it
                     if (kQsmem && t == 0 && n >= 1 && !(ok = ptx::mbar_wait(bar_done, (n - 1) & 1))) break;
                     tc_fence_after();
@@ -432,6 +447,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     }
                     umma_commit(bar_o + (g & 1));
                     umma_commit(bar_vfree + s);
+                    BTR(1, g, 6);
                 }
                 // each bar_o barrier sees every other product, so its parity names one product for a
                 // waiter that is at most one product behind; the end of an item's walk gets a barrier of its own
@@ -549,8 +565,10 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const int kb = w.key_base();
             const bool mine = MODE == kModeGlobalRows ? warp_has_rows : (w.flags >> half) & 1;   // uniform within a warp (dense: always)
             w.next();   // the layout reads for the next step are in flight during this one
+            if (threadIdx.x == 0) BTR(0, g, 0);
             if (!(ok = ptx::mbar_wait(bar_s + (g & 1), (g >> 1) & 1))) break;
             tc_fence_after();
+            if (threadIdx.x == 0) BTR(0, g, 1);
             const uint32_t s_addr = t_lane + (g & 1) * kTileK;   // S(t), and P(t) over its first 32 columns
             if (mine) {
                 // keys this row may use in the chunk: j < j_end
@@ -563,6 +581,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 }
                 float s[64];
                 tmem_ld64(s_addr, s);
+                if (threadIdx.x == 0) BTR(0, g, 2);
                 if (j_end < kTileK || j_begin > 0) {   // only the chunks on an edge of the window or at the sequence end
 #pragma unroll
                     for (int i = 0; i < 64; ++i) if (i >= j_end || i < j_begin) s[i] = -INFINITY;
@@ -576,6 +595,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     mq[q] = fmaxf(mq[q], s[16 * q + 15]);
                 }
                 const float mx = fmaxf(max3(mq[0], mq[1], mq[2]), mq[3]);
+                if (threadIdx.x == 0) BTR(0, g, 3);
                 // move the reference maximum only when the scores outgrow it by 2^kLazyLog2
                 const bool seen = m_run != -INFINITY;
                 const bool grow = seen ? (mx - m_run) * P.sl2 > kLazyLog2 : mx != -INFINITY;
@@ -583,7 +603,12 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 const float alpha = rescale ? ptx::ex2((m_run - mx) * P.sl2) : 1.f;
                 if (grow) m_run = mx;
                 const float mus = (m_run == -INFINITY ? 0.f : m_run) * P.sl2;
-                // weights, packed to the operand type two at a time: column i of P holds keys 2i and 2i+1
+                // weights, packed to the operand type two at a time: column i of P holds keys 2i and 2i+1.
+                // (The exponentials bound the step: the special-function unit gives 16 results per clock and SM,
+                // packed 16-bit forms included, so the 8192 of a step take 512 clocks against about 290 of tensor
+                // work.  Moving a share of them to the FMA pipe as a cubic - rounding trick, three packed FMAs,
+                // an integer add into the exponent - was measured slower at every share: about 23 issue clocks
+                // per pair against 16 on the unit.)
                 uint32_t pk[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
@@ -592,6 +617,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     pk[i] = ptx::Mma<T>::ex2_packed(ptx::Mma<T>::pack(x0, x1));
                 }
                 tmem_st32(s_addr, pk);
+                if (threadIdx.x == 0) BTR(0, g, 4);
                 if (__any_sync(0xffffffffu, rescale)) {
                     // O and l hold the chunks up to t-1: wait for P V(t-1), then scale this row in place
                     if (!(ok = ptx::mbar_wait(bar_o + ((g - 1) & 1), ((g - 1) >> 1) & 1))) break;
@@ -615,6 +641,7 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar_p + (g & 1));
+            if (threadIdx.x == 0) BTR(0, g, 5);
             if (pending) {   // (only with Q in shared memory, and only at an item's first step)
                 pending = false;
                 read_out(fin);
@@ -849,6 +876,13 @@ int launch_umma_block(const Problem &p) {
     return p.dtype == MAT_BF16 ? launch_t<__nv_bfloat16>(p) : launch_t<__half>(p);
 }
 
+}  // namespace mat
+#ifdef MAT_BLOCK_TRACE
+extern "C" int mat_debug_block_trace(unsigned long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, mat::g_btrace, sizeof(mat::g_btrace));
+}
+#endif
+namespace mat {
 int umma_status_read_and_clear(int *out) {
     int zero = 0;
     cudaError_t e = cudaMemcpyFromSymbol(out, g_umma_status, sizeof(int));
