@@ -1,0 +1,249 @@
+// 16-bit window attention for head widths other than 64 (32 and 128) on the warp-level tensor-core
+// instructions.
+//
+// The reference kernel takes any head width (sparse_attention_forward_warp,
+// src/cuda/sparse_attention_kernel.cu:238-262: `d = lane; d < D; d += 32`), and its layer calls it with
+// D = model_dim (src/layers/sparse_attention.py:71-78).  The TMA / tcgen05 kernels of this library are
+// laid out for 128-byte rows (D = 64); this kernel covers the two other common widths so that they do
+// not fall to the one-warp-per-row kernel.
+//
+// One CTA = 64 query rows of one (batch, head), four warps of 16 rows.  The keys the tile can see
+// (first row's first tap to last row's last tap) are walked 64 at a time: K and V chunks arrive in shared
+// memory by cp.async (two buffers, rows padded by 16 bytes so that ldmatrix is conflict-free; rows past the
+// sequence end are zero-filled, so a masked weight never multiplies stale shared memory), S = Q K^T by
+// mma.sync m16n8k16 with Q held in registers, masks, an online softmax in registers, P re-used in place
+// as the A fragments of O += P V.  A dilated window is a plain window over the tensor viewed as
+// [B, S/dil, dil*H, D], as everywhere in this library.  (Skipping, per warp, the 16-key groups none of its rows
+// can use was measured slower - 117 against 93 us at 64K tokens x 4 heads of 128: the branches inside the unrolled
+// products cost more than the masked work they save.)
+#include <algorithm>
+#include <cstring>
+
+#include "mat_common.cuh"
+#include "ptx.cuh"
+
+namespace mat {
+namespace {
+
+constexpr int kTQ = 64, kTK = 64, kThreads = 128;
+
+struct WinDParams {
+    int32_t Sq1, Skv1, off1;   // query rows, key rows, q_offset of one sub-sequence
+    int32_t HH;                // heads of the view
+    int32_t left, right;
+    float sl2;                 // scale * log2(e)
+};
+
+__device__ __forceinline__ void cp_async16(void *dst, const void *src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ptx::smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads)
+window_d_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v, T *__restrict__ o,
+                const WinDParams P) {
+    constexpr int LD = D + 8;          // padded row, elements
+    constexpr int KS = D / 16;         // k-steps of S = Q K^T; pairs of 8-wide output tiles of O
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    T *sK = reinterpret_cast<T *>(smem_raw);          // [2][kTK][LD]
+    T *sV = sK + 2 * kTK * LD;                        // [2][kTK][LD]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int hh = blockIdx.x, b = blockIdx.z, q0 = blockIdx.y * kTQ;
+    const int p_first = q0 + P.off1;   // key-coordinate position of the tile's first row
+    const int last_row = min(q0 + kTQ, P.Sq1) - 1;
+    const int key_lo = max(0, p_first - P.left);
+    const int key_hi = min(P.Skv1 - 1, last_row + P.off1 + P.right);
+    const int n_chunks = key_hi >= key_lo ? (key_hi - key_lo) / kTK + 1 : 0;
+    const int64_t tok = (int64_t)P.HH * D;   // elements per token
+    const T *kb_ptr = k + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+    const T *vb_ptr = v + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+
+    auto load_chunk = [&](int c, int buf) {
+        constexpr int kPieces = D / 8;   // 16-byte pieces per row
+        const int base = key_lo + c * kTK;
+        for (int i = threadIdx.x; i < kTK * kPieces; i += kThreads) {
+            const int r = i / kPieces, pc = i % kPieces;
+            const int j = base + r;
+            const bool in = j < P.Skv1;
+            const int64_t src = (int64_t)(in ? j : 0) * tok + pc * 8;
+            cp_async16(sK + (buf * kTK + r) * LD + pc * 8, kb_ptr + src, in ? 16 : 0);
+            cp_async16(sV + (buf * kTK + r) * LD + pc * 8, vb_ptr + src, in ? 16 : 0);
+        }
+    };
+    if (n_chunks > 0) load_chunk(0, 0);
+    cp_async_commit();
+
+    // the warp's 16 query rows as A fragments: thread (g, t) holds rows g and g + 8, columns 2t, 2t+1 (+8)
+    const int row_a = q0 + warp * 16 + g, row_b = row_a + 8;
+    uint32_t qf[KS][4];
+    {
+        const T *qa = q + (((int64_t)b * P.Sq1 + row_a) * P.HH + hh) * D;
+        const T *qb = q + (((int64_t)b * P.Sq1 + row_b) * P.HH + hh) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int c = ks * 16 + 2 * t;
+            qf[ks][0] = row_a < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qa + c) : 0u;
+            qf[ks][1] = row_b < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qb + c) : 0u;
+            qf[ks][2] = row_a < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qa + c + 8) : 0u;
+            qf[ks][3] = row_b < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qb + c + 8) : 0u;
+        }
+    }
+    const int pos[2] = {row_a + P.off1, row_b + P.off1};
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float acc[2 * KS][4];
+#pragma unroll
+    for (int n = 0; n < 2 * KS; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+
+    for (int c = 0; c < n_chunks; ++c) {
+        const int buf = c & 1;
+        if (c + 1 < n_chunks) {
+            load_chunk(c + 1, buf ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int kb = key_lo + c * kTK;
+        const uint32_t k_addr = ptx::smem_u32(sK + buf * kTK * LD), v_addr = ptx::smem_u32(sV + buf * kTK * LD);
+        const int m4 = lane >> 3, r8 = lane & 7;
+
+        // ---- S = Q K^T: eight 8-key tiles per warp ----
+        float s[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int n2 = 0; n2 < 4; ++n2) {
+                // matrices: (keys n2*16 + 0..7, dims +0), (same keys, dims +8), (keys +8, dims +0), (keys +8, dims +8)
+                uint32_t kf[4];
+                ptx::ldmatrix_x4(kf, k_addr + (uint32_t)(((n2 * 16 + r8 + (m4 >> 1) * 8) * LD + ks * 16 + (m4 & 1) * 8) * 2));
+                ptx::Mma<T>::run(s[2 * n2], qf[ks], kf[0], kf[1]);
+                ptx::Mma<T>::run(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
+            }
+        }
+        // ---- mask, online softmax (raw scores; the scale enters the exponent) ----
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = kb + n * 8 + 2 * t + (e & 1), p = pos[e >> 1];
+                const bool ok = j >= p - P.left && j <= p + P.right && j < P.Skv1;
+                s[n][e] = ok ? s[n][e] : -INFINITY;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+            }
+        float alpha[2], mus[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float m_new = fmaxf(m_run[i], mx[i]);
+            alpha[i] = m_new == -INFINITY ? 1.f : ptx::ex2((m_run[i] - m_new) * P.sl2);
+            m_run[i] = m_new;
+            mus[i] = m_new == -INFINITY ? 0.f : m_new * P.sl2;
+            l_run[i] *= alpha[i];
+        }
+#pragma unroll
+        for (int n = 0; n < 2 * KS; ++n) {
+            acc[n][0] *= alpha[0]; acc[n][1] *= alpha[0];
+            acc[n][2] *= alpha[1]; acc[n][3] *= alpha[1];
+        }
+        uint32_t pa[4][4];   // the weights as A fragments of the 16-key steps of P V
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            float w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                w[e] = ptx::ex2(fmaf(s[n][e], P.sl2, -mus[e >> 1]));
+                l_run[e >> 1] += w[e];
+            }
+            pa[n >> 1][(n & 1) * 2] = ptx::Mma<T>::pack(w[0], w[1]);
+            pa[n >> 1][(n & 1) * 2 + 1] = ptx::Mma<T>::pack(w[2], w[3]);
+        }
+        // ---- O += P V ----
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+            for (int d2 = 0; d2 < KS; ++d2) {
+                // matrices (transposed on load): (keys kk*16 + 0..7, dims d2*16 + 0..7), (keys +8, same dims),
+                // (keys + 0, dims + 8), (keys + 8, dims + 8)
+                uint32_t vf[4];
+                ptx::ldmatrix_x4_trans(vf, v_addr + (uint32_t)(((kk * 16 + r8 + (m4 & 1) * 8) * LD + d2 * 16 + (m4 >> 1) * 8) * 2));
+                ptx::Mma<T>::run(acc[2 * d2], pa[kk], vf[0], vf[1]);
+                ptx::Mma<T>::run(acc[2 * d2 + 1], pa[kk], vf[2], vf[3]);
+            }
+        }
+        __syncthreads();   // the buffer is free for the chunk after the next
+    }
+
+    // ---- normalise and write the two rows of this thread ----
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float l = l_run[i];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const int row = i == 0 ? row_a : row_b;
+        if (row < P.Sq1) {
+            T *dst = o + (((int64_t)b * P.Sq1 + row) * P.HH + hh) * D + 2 * t;
+#pragma unroll
+            for (int n = 0; n < 2 * KS; ++n)
+                *reinterpret_cast<uint32_t *>(dst + n * 8) = ptx::Mma<T>::pack(acc[n][2 * i] * inv, acc[n][2 * i + 1] * inv);
+        }
+    }
+}
+
+template <typename T, int D>
+int launch_d(const Problem &p) {
+    const int64_t dil = p.pat.dilation;
+    WinDParams wp;
+    wp.Sq1 = (int32_t)(p.Sq / dil);
+    wp.Skv1 = (int32_t)(p.Skv / dil);
+    wp.off1 = (int32_t)(p.pat.q_offset / dil);
+    wp.HH = (int32_t)(p.H * dil);
+    wp.left = (int32_t)std::min<int64_t>(p.pat.left, wp.Skv1);
+    wp.right = (int32_t)std::min<int64_t>(p.pat.right, wp.Skv1);
+    wp.sl2 = p.scale * 1.4426950408889634f;
+    auto kern = window_d_kernel<T, D>;
+    constexpr size_t smem = (size_t)4 * kTK * (D + 8) * sizeof(T);
+    if (int rc = ensure_dynamic_smem((const void *)kern, smem, "cudaFuncSetAttribute(window_d_kernel)")) return rc;
+    const dim3 grid((unsigned)wp.HH, (unsigned)((wp.Sq1 + kTQ - 1) / kTQ), (unsigned)p.B);
+    kern<<<grid, kThreads, smem, p.stream>>>((const T *)p.q, (const T *)p.k, (const T *)p.v, (T *)p.o, wp);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "window_d_kernel launch");
+    note_kernel("mma_window_d");
+    return MAT_OK;
+}
+
+}  // namespace
+
+// 16-bit window patterns (any taps, any dilation that divides the lengths) with head width 32 or 128, whole
+// tensors (no neighbour shards), 16-byte aligned.  MAT_WINDOW_D_KERNEL=rowwarp keeps the one-warp-per-row
+// kernel (a measurement aid).
+bool mma_window_d_supports(const Problem &p) {
+    if (p.pat.kind != MAT_WINDOW) return false;
+    if (p.dtype != MAT_BF16 && p.dtype != MAT_F16) return false;
+    if (p.D != 32 && p.D != 128) return false;
+    if (p.k_prev || p.k_next || p.q_ts || p.k_ts || p.v_ts || p.o_ts) return false;
+    const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
+    if (al % 16) return false;
+    const int64_t dil = p.pat.dilation;
+    if (dil < 1 || p.Sq % dil || p.Skv % dil || p.pat.q_offset % dil) return false;
+    if (p.Skv / dil >= (1LL << 30) || p.Sq / dil >= (1LL << 30) || p.H * dil > 0x7fffffffLL || p.B > 65535) return false;
+    if ((p.Sq / dil + kTQ - 1) / kTQ > 65535) return false;
+    const char *force = std::getenv("MAT_WINDOW_D_KERNEL");
+    return !(force && std::strcmp(force, "rowwarp") == 0);
+}
+
+int launch_mma_window_d(const Problem &p) {
+    if (p.dtype == MAT_BF16)
+        return p.D == 32 ? launch_d<__nv_bfloat16, 32>(p) : launch_d<__nv_bfloat16, 128>(p);
+    return p.D == 32 ? launch_d<__half, 32>(p) : launch_d<__half, 128>(p);
+}
+
+}  // namespace mat

@@ -72,6 +72,32 @@ def test_tiled_fp32_kernel_vs_oracle(spec, D):
     assert np.isfinite(got).all() and np.abs(got - oracle_out(q, k, v, spec)).max() <= 0.5
 
 
+@pytest.mark.parametrize("D", [32, 128])
+@pytest.mark.parametrize("spec", [PatternSpec.causal_window(64), PatternSpec.sliding_window(32), PatternSpec.sliding_window(64),
+                                  PatternSpec(left=0, right=60), PatternSpec.causal_window(16, dilation=2),
+                                  PatternSpec(left=5, right=90), PatternSpec.causal_window(300), PatternSpec.sliding_window(5000),
+                                  PatternSpec.causal_window(1)],
+                         ids=lambda s: f"l{s.left}r{s.right}d{s.dilation}")
+def test_16bit_windows_with_head_width_32_and_128(monkeypatch, spec, D):
+    """16-bit windows with head width 32 or 128 on the warp-level tensor-core kernel (64-row tiles, 64-key chunks
+    through cp.async, online softmax): narrow, wide (several chunks), dense-as-window, dilated, ragged lengths,
+    shard offsets; and the one-warp-per-row kernel on the same inputs."""
+    for dtype in (torch.bfloat16, torch.float16):
+        for B, S, H, off in [(1, 1024, 2, 0), (2, 330, 3, 0), (1, 64, 1, 0), (1, 200, 2, 48), (1, 7, 1, 0)]:
+            S = S - S % spec.dilation if S >= spec.dilation else spec.dilation
+            off = off - off % spec.dilation
+            sp = spec.shifted(off)
+            q, k, v = seeded_qkv(29, B, S, H, D, dtype, Skv=S + off + 3 * spec.dilation)
+            got = run(sp, q, k, v)
+            assert nat.last_kernel() == "mma_window_d"
+            check_close(got, oracle_out(q, k, v, sp), dtype)
+    monkeypatch.setenv("MAT_WINDOW_D_KERNEL", "rowwarp")
+    q, k, v = seeded_qkv(30, 1, 330, 2, D, torch.bfloat16)
+    got = run(spec, q, k, v)
+    assert nat.last_kernel() == "rowwarp"
+    check_close(got, oracle_out(q, k, v, spec), torch.bfloat16)
+
+
 @pytest.mark.parametrize("B,S,H,D", [(1, 1, 1, 1), (1, 7, 2, 5), (2, 33, 1, 13), (1, 100, 3, 40), (1, 65, 2, 96),
                                      (1, 40, 1, 200), (1, 18, 1, 512)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
