@@ -65,7 +65,7 @@ int launch_rowwarp(const Problem &p);        // rowwarp.cu: any pattern, any D <
 bool tiled_f32_supports(const Problem &p);   // tiled_f32.cu: fp32 windows of at most 128 taps, D = 32, 64 or 128
 int launch_tiled_f32(const Problem &p);
 int tiled_status_read_and_clear(int *out);
-bool mma_window_d_supports(const Problem &p);   // mma_window_d.cu: 16-bit windows with head width 32 or 128
+bool mma_window_d_supports(const Problem &p);   // mma_window_d.cu: 16-bit windows, head widths 16..128 in steps of 16 other than 64
 int launch_mma_window_d(const Problem &p);
 bool mma_flash_supports(const Problem &p);   // mma_flash.cu
 int launch_mma_flash(const Problem &p);

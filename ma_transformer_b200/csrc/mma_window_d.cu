@@ -1,11 +1,11 @@
-// 16-bit window attention for head widths other than 64 (32 and 128) on the warp-level tensor-core
-// instructions.
+// 16-bit window attention for head widths other than 64 (the multiples of 16 up to 128) on the warp-level
+// tensor-core instructions.
 //
 // The reference kernel takes any head width (sparse_attention_forward_warp,
 // src/cuda/sparse_attention_kernel.cu:238-262: `d = lane; d < D; d += 32`), and its layer calls it with
 // D = model_dim (src/layers/sparse_attention.py:71-78).  The TMA / tcgen05 kernels of this library are
-// laid out for 128-byte rows (D = 64); this kernel covers the two other common widths so that they do
-// not fall to the one-warp-per-row kernel.
+// laid out for 128-byte rows (D = 64); this kernel covers the other common widths so that they do not fall
+// to the one-warp-per-row kernel.
 //
 // One CTA = 64 query rows of one (batch, head), four warps of 16 rows.  The keys the tile can see
 // (first row's first tap to last row's last tap) are walked 64 at a time: K and V chunks arrive in shared
@@ -222,13 +222,14 @@ int launch_d(const Problem &p) {
 
 }  // namespace
 
-// 16-bit window patterns (any taps, any dilation that divides the lengths) with head width 32 or 128, whole
+// 16-bit window patterns (any taps, any dilation that divides the lengths) with head width 16, 32, 48, 80, 96, 112
+// or 128, whole
 // tensors (no neighbour shards), 16-byte aligned.  MAT_WINDOW_D_KERNEL=rowwarp keeps the one-warp-per-row
 // kernel (a measurement aid).
 bool mma_window_d_supports(const Problem &p) {
     if (p.pat.kind != MAT_WINDOW) return false;
     if (p.dtype != MAT_BF16 && p.dtype != MAT_F16) return false;
-    if (p.D != 32 && p.D != 128) return false;
+    if (p.D % 16 || p.D < 16 || p.D > 128 || p.D == 64) return false;   // (64: the TMA / tcgen05 kernels)
     if (p.k_prev || p.k_next || p.q_ts || p.k_ts || p.v_ts || p.o_ts) return false;
     const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
     if (al % 16) return false;
@@ -240,10 +241,22 @@ bool mma_window_d_supports(const Problem &p) {
     return !(force && std::strcmp(force, "rowwarp") == 0);
 }
 
+template <typename T>
+int launch_any_d(const Problem &p) {
+    switch (p.D) {
+        case 16: return launch_d<T, 16>(p);
+        case 32: return launch_d<T, 32>(p);
+        case 48: return launch_d<T, 48>(p);
+        case 80: return launch_d<T, 80>(p);
+        case 96: return launch_d<T, 96>(p);
+        case 112: return launch_d<T, 112>(p);
+        case 128: return launch_d<T, 128>(p);
+    }
+    return fail(MAT_ERR_UNSUPPORTED, "head width %lld has no instantiation of the warp-level window kernel", (long long)p.D);
+}
+
 int launch_mma_window_d(const Problem &p) {
-    if (p.dtype == MAT_BF16)
-        return p.D == 32 ? launch_d<__nv_bfloat16, 32>(p) : launch_d<__nv_bfloat16, 128>(p);
-    return p.D == 32 ? launch_d<__half, 32>(p) : launch_d<__half, 128>(p);
+    return p.dtype == MAT_BF16 ? launch_any_d<__nv_bfloat16>(p) : launch_any_d<__half>(p);
 }
 
 }  // namespace mat

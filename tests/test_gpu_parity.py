@@ -72,14 +72,14 @@ def test_tiled_fp32_kernel_vs_oracle(spec, D):
     assert np.isfinite(got).all() and np.abs(got - oracle_out(q, k, v, spec)).max() <= 0.5
 
 
-@pytest.mark.parametrize("D", [32, 128])
+@pytest.mark.parametrize("D", [16, 32, 48, 80, 96, 112, 128])
 @pytest.mark.parametrize("spec", [PatternSpec.causal_window(64), PatternSpec.sliding_window(32), PatternSpec.sliding_window(64),
                                   PatternSpec(left=0, right=60), PatternSpec.causal_window(16, dilation=2),
                                   PatternSpec(left=5, right=90), PatternSpec.causal_window(300), PatternSpec.sliding_window(5000),
                                   PatternSpec.causal_window(1)],
                          ids=lambda s: f"l{s.left}r{s.right}d{s.dilation}")
 def test_16bit_windows_with_head_width_32_and_128(monkeypatch, spec, D):
-    """16-bit windows with head width 32 or 128 on the warp-level tensor-core kernel (64-row tiles, 64-key chunks
+    """16-bit windows with a head width that is a multiple of 16 up to 128 (other than 64) on the warp-level tensor-core kernel (64-row tiles, 64-key chunks
     through cp.async, online softmax): narrow, wide (several chunks), dense-as-window, dilated, ragged lengths,
     shard offsets; and the one-warp-per-row kernel on the same inputs."""
     for dtype in (torch.bfloat16, torch.float16):
@@ -106,7 +106,8 @@ def test_rowwarp_odd_shapes(B, S, H, D, dtype):
                  PatternSpec(left=2, right=5, dilation=2)):
         q, k, v = seeded_qkv(7, B, S, H, D, dtype)
         check_close(run(spec, q, k, v), oracle_out(q, k, v, spec), dtype)
-        assert nat.last_kernel() == "rowwarp"
+        on_mma = dtype != torch.float32 and D % 16 == 0 and D <= 128 and S % spec.dilation == 0
+        assert nat.last_kernel() == ("mma_window_d" if on_mma else "rowwarp")
 
 
 def test_head_width_beyond_maximum_is_refused_loudly():
