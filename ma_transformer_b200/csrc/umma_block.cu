@@ -179,7 +179,8 @@ constexpr int kSoftmaxWarpsPerTile = 4;
 // products comes from there), 2 when the S products read Q from shared memory, double-buffered over items.
 template <int NT, int QS> struct Cfg {
     static constexpr int kSoftmaxWarps = kSoftmaxWarpsPerTile * NT;
-    static constexpr int kThreads = (kSoftmaxWarps + NT + 1) * 32;   // softmax warps, one MMA warp per tile, load warp
+    // softmax warps, one MMA warp per tile, load warp; with Q in shared memory a second issuing warp (the P V products)
+    static constexpr int kThreads = (kSoftmaxWarps + NT + 1 + (QS == 2 ? 1 : 0)) * 32;
     static constexpr int kKvStages = NT == 1 ? (QS == 2 ? 4 : 5) : 8;   // (two CTAs of one tile share an SM's shared memory)
     static constexpr int kTmemCols = 256 * NT;
     static constexpr int kBars = 2 + NT * 9 + 4 * kKvStages + 2;
@@ -373,6 +374,51 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         return;
     }
+    if (kQsmem && warp == kSoftmaxWarps + NT + 1) {
+        // ================= second issuing warp (Q in shared memory): the P V products =================
+        // Block layouts have short walks, and one lane that issues both products of every step (4 + 4
+        // tcgen05.mma, four commits, three or four barrier waits and the layout walk: about 0.9 us per step)
+        // was what bounded them.  Here one lane issues the S products, running ahead over item boundaries, and
+        // this one the P V products; what used to be program order between them is explicit: S(g) waits for
+        // P V(g - 2), whose weights sit in the score buffer it overwrites.
+        if (lane == 0) {
+            bool ok = true;
+            const uint32_t tmem = tmem_base;
+            uint64_t *tb = tile_bars;
+            uint64_t *bar_fin = tb + 1, *bar_done = tb + 2, *bar_p = tb + 5, *bar_o = tb + 7;
+            const uint32_t idesc_pv = instr_desc<T>(true, kTileK + kSumN);
+            const uint32_t kv_addr = ptx::smem_u32(sKV), ones_addr = ptx::smem_u32(sOnes);
+            int g = 0;   // step, counted over all items
+            for (uint32_t n = 0; ok && n < n_mine; ++n) {
+                ChunkWalk<NH> w_p;   // counts the item's steps
+                w_p.init(P, rowptr, colidx, item_at(n).q0);
+                for (bool first = true; ok && !w_p.done(); w_p.next(), first = false, ++g) {
+                    const int s = g % kKvStages;
+                    BTR(1, g, 3);
+                    if (!(ok = ptx::mbar_wait(bar_v + s, (g / kKvStages) & 1))) break;
+                    BTR(1, g, 4);
+                    if (!(ok = ptx::mbar_wait(bar_p + (g & 1), (g >> 1) & 1))) break;   // P is in TMEM
+                    BTR(1, g, 5);
+                    // the item's first product overwrites O: the previous item's rows have been read out of it
+                    if (first && n >= 1 && !(ok = ptx::mbar_wait(bar_done, (n - 1) & 1))) break;
+                    tc_fence_after();
+                    const uint32_t v_addr = kv_addr + s * kStage + kTileK * kRowBytes;
+                    const uint32_t tp = tmem + (g & 1) * kTileK;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint32_t vk = v_addr + ks * 16 * kRowBytes;
+                        umma_f16_ta(tmem + kColO, tp + ks * 8, smem_desc(vk, (ones_addr - vk) >> 4), idesc_pv, !first || ks > 0);
+                    }
+                    umma_commit(bar_o + (g & 1));
+                    umma_commit(bar_vfree + s);
+                    BTR(1, g, 6);
+                }
+                if (ok) umma_commit(bar_fin);
+            }
+            if (!ok) atomicExch(&g_umma_status, 1);
+        }
+        return;
+    }
     // everything below belongs to one tile
     const int tile = warp >= kSoftmaxWarps ? warp - kSoftmaxWarps : warp / kSoftmaxWarpsPerTile;
     const uint32_t tmem = tmem_base + 256 * tile;
@@ -387,8 +433,35 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             // descriptors differ from step to step only in the start address field (16-byte units)
             const uint32_t kv_addr = ptx::smem_u32(sKV), ones_addr = ptx::smem_u32(sOnes);
             const uint64_t dkv = smem_desc(kv_addr);
+            if constexpr (kQsmem) {
+                // the S products of every item, as far ahead as the K ring and the two score buffers allow
+                int g = 0;
+                for (uint32_t n = 0; ok && n < n_mine; ++n) {
+                    ChunkWalk<NH> w_s;
+                    w_s.init(P, rowptr, colidx, item_at(n).q0);
+                    if (!(ok = ptx::mbar_wait(bar_q + (n & 1), (n >> 1) & 1))) break;   // Q has landed in its buffer
+                    const uint64_t dq = smem_desc(ptx::smem_u32(sQ) + (n & 1) * kQBytes);
+                    for (; ok && !w_s.done(); w_s.next(), ++g) {
+                        const int s = g % kKvStages;
+                        BTR(1, g, 0);
+                        if (!(ok = ptx::mbar_wait(bar_k + s, (g / kKvStages) & 1))) break;
+                        // the weights of step g - 2 have been read out of this score buffer by their P V product
+                        if (g >= 2 && !(ok = ptx::mbar_wait(bar_o + (g & 1), ((g - 2) >> 1) & 1))) break;
+                        tc_fence_after();
+                        BTR(1, g, 1);
+                        const uint64_t dk = dkv + (uint64_t)(s * (kStage >> 4));
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks)
+                            umma_f16_ss(tmem + (g & 1) * kTileK, dq + ks * 2, dk + ks * 2, idesc_s, ks > 0);
+                        umma_commit(bar_s + (g & 1));
+                        umma_commit(bar_kfree + s);
+                        BTR(1, g, 2);
+                    }
+                    if (ok) umma_commit(bar_qfree + (n & 1));
+                }
+            }
             int base = 0;   // steps of the items before this one: step t of the item is step base + t of the barriers
-            for (uint32_t n = 0; ok && n < n_mine; ++n) {
+            for (uint32_t n = 0; !kQsmem && ok && n < n_mine; ++n) {
                 const Item I = item_at(n);
                 ChunkWalk<NH> w_s;     // only counts the chunks here
                 if (MODE != kModeBlock) w_s.init_range(I.lo, I.hi);
