@@ -190,7 +190,9 @@ template <int NT, int QS> struct Cfg {
                                          (size_t)kKvStages * 2 * kTileK * kRowBytes + kSumN * kRowBytes +
                                          kBars * 8 + 16 /*tmem address*/ + kLayoutInts * 4;
 };
-__host__ __device__ constexpr int qs_of(int mode) { return mode == 0 /* kModeBlock */ ? 2 : 1; }
+// Block layouts only.  (The dense walk on the same path - Q from shared memory, two issuing lanes - was measured
+// slower than with Q in TMEM and one lane: 423.7 against 411.1 us at 2 x 8192 x 8 heads.)
+__host__ __device__ constexpr int qs_of(int mode, int nt) { return mode == 0 /* kModeBlock */ && nt == 1 ? 2 : 1; }
 constexpr int kStage = 2 * kTileK * kRowBytes;  // one K/V stage: K then V
 constexpr int kOnesBytes = kSumN * kRowBytes;   // the second 64-wide block of the P V product's B operand: ones
 
@@ -206,15 +208,15 @@ constexpr int kOnesBytes = kSumN * kRowBytes;   // the second 64-wide block of t
 //              first chunk overwrites).
 //   softmax:   softmax(t) -> store P(t) -> (rarely: wait for P V(t-1), rescale O and l) -> publish.
 template <typename T, int MODE, int NT>
-__global__ void __launch_bounds__(Cfg<NT, qs_of(MODE)>::kThreads)
+__global__ void __launch_bounds__(Cfg<NT, qs_of(MODE, NT)>::kThreads)
 umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, T *__restrict__ out, const UmmaParams P) {
     // Block layouts (short walks, so what happens between two items counts): the S products read Q from shared
     // memory, where the next item's tile lands while this one's is in use, and nothing of the hand-over from
     // one item to the next runs through the softmax warps.  The long walks (dense, wide windows, global rows)
     // keep Q in TMEM: there the shared-memory reads per step are what matters.
-    constexpr bool kQsmem = MODE == kModeBlock;
-    constexpr int QS = qs_of(MODE);
+    constexpr int QS = qs_of(MODE, NT);
+    constexpr bool kQsmem = QS == 2;
     static_assert(!kQsmem || NT == 1, "the shared-memory Q path is written for one tile per CTA");
     using C = Cfg<NT, QS>;
     constexpr int kSoftmaxWarps = C::kSoftmaxWarps, kKvStages = C::kKvStages, NH = 2 * NT;
@@ -391,7 +393,11 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             int g = 0;   // step, counted over all items
             for (uint32_t n = 0; ok && n < n_mine; ++n) {
                 ChunkWalk<NH> w_p;   // counts the item's steps
-                w_p.init(P, rowptr, colidx, item_at(n).q0);
+                {
+                    const Item I = item_at(n);
+                    if (MODE != kModeBlock) w_p.init_range(I.lo, I.hi);
+                    else w_p.init(P, rowptr, colidx, I.q0);
+                }
                 for (bool first = true; ok && !w_p.done(); w_p.next(), first = false, ++g) {
                     const int s = g % kKvStages;
                     BTR(1, g, 3);
@@ -438,7 +444,11 @@ umma_block_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 int g = 0;
                 for (uint32_t n = 0; ok && n < n_mine; ++n) {
                     ChunkWalk<NH> w_s;
-                    w_s.init(P, rowptr, colidx, item_at(n).q0);
+                    {
+                        const Item I = item_at(n);
+                        if (MODE != kModeBlock) w_s.init_range(I.lo, I.hi);
+                        else w_s.init(P, rowptr, colidx, I.q0);
+                    }
                     if (!(ok = ptx::mbar_wait(bar_q + (n & 1), (n >> 1) & 1))) break;   // Q has landed in its buffer
                     const uint64_t dq = smem_desc(ptx::smem_u32(sQ) + (n & 1) * kQBytes);
                     for (; ok && !w_s.done(); w_s.next(), ++g) {
@@ -784,7 +794,7 @@ template <typename T, int MODE, int NT>
 int launch_mode(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, T *out, const UmmaParams &up_in,
                 dim3 grid, cudaStream_t stream, const char *what) {
     auto kern = umma_block_fwd_kernel<T, MODE, NT>;
-    using C = Cfg<NT, qs_of(MODE)>;
+    using C = Cfg<NT, qs_of(MODE, NT)>;
     if (int rc = ensure_dynamic_smem((const void *)kern, C::kSmemBytes, what)) return rc;
     const uint64_t n_work = (uint64_t)grid.x * grid.y * grid.z;
     if (n_work == 0) return MAT_OK;
