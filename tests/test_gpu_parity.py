@@ -546,7 +546,7 @@ def test_module_surface_on_gpu():
 @pytest.mark.parametrize("spec", [PatternSpec.causal_window(64), PatternSpec.sliding_window(30),
                                   PatternSpec.causal_window(8, dilation=2)], ids=["causal64", "pm30", "dil2"])
 def test_host_entry_point_equals_device_entry_point(spec):
-    # long enough for several pipeline chunks (about 4 MiB each)
+    # long enough for several pipeline chunks (an eighth of a batch item each: 2.5 MB)
     q, k, v = seeded_qkv(61, 2, 20000, 8, 64, torch.bfloat16)
     qp, kp, vp = (t.pin_memory() for t in (q, k, v))
     got = ext.forward_host(qp, kp, vp, spec)
