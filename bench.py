@@ -625,6 +625,7 @@ def other_workload_arm(args):
                          "note": "per backward (two launches: rows pass and cols pass)"},
             "device_status": nat.device_status()}), flush=True)
         return
+    Dw = 64
     if args.workload == "block":
         Bw, S, Hw = 4, 16384, 8
         rp, ci = band_random_block_layout(S // 64, 4, 2, seed=SEED)
@@ -634,10 +635,12 @@ def other_workload_arm(args):
     elif args.workload == "refwindow":
         # the window every unmodified caller of the reference gets: window_size = 64, keys i-64 .. i+64
         # (src/layers/ma_core_bridge.py:259), at the headline shape; --left / --right / --dilation change it
-        Bw, S, Hw = B, SEQ, H
+        # (--head-dim changes the head width at the same bytes per token: H * d stays 512)
+        Dw = args.head_dim
+        Bw, S, Hw = B, SEQ, H * 64 // Dw
         spec = PatternSpec(left=args.left, right=args.right, dilation=args.dilation)
-        flops = Bw * Hw * S * (args.left + args.right + 1) * 4 * 64
-        name = (f"window fwd B={Bw} N={S} H={Hw} d=64 taps -{args.left}..+{args.right}"
+        flops = Bw * Hw * S * (args.left + args.right + 1) * 4 * Dw
+        name = (f"window fwd B={Bw} N={S} H={Hw} d={Dw} taps -{args.left}..+{args.right}"
                 + (f" dilation {args.dilation}" if args.dilation > 1 else "") + " bf16")
     elif args.workload == "dense":
         # the reference's dense_forward (every query over every key), the tensor-bound end of the path
@@ -651,8 +654,8 @@ def other_workload_arm(args):
         spec = PatternSpec.longformer(64, 64, glob)
         flops = Bw * Hw * (S * 129 + 2 * 32 * S) * 4 * 64
         name = f"Longformer fwd B={Bw} N={S} H={Hw} d=64 window +-64, 32 global tokens bf16"
-    nbytes = 4 * Bw * S * Hw * 64 * 2
-    sets = [tuple(torch.randn(Bw, S, Hw, 64, generator=g).to(torch.bfloat16).to(dev) for _ in range(3))
+    nbytes = 4 * Bw * S * Hw * Dw * 2
+    sets = [tuple(torch.randn(Bw, S, Hw, Dw, generator=g).to(torch.bfloat16).to(dev) for _ in range(3))
             for _ in range(2)]
     out = torch.empty_like(sets[0][0])
     for i in range(args.warmup):
@@ -708,6 +711,8 @@ def main():
     ap.add_argument("--left", type=int, default=64, help="refwindow: taps before the query")
     ap.add_argument("--right", type=int, default=64, help="refwindow: taps after the query")
     ap.add_argument("--dilation", type=int, default=1, help="refwindow: dilation")
+    ap.add_argument("--head-dim", type=int, default=64, choices=[16, 32, 64, 128],
+                    help="refwindow: head width (the number of heads changes with it, 512 columns per token)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
