@@ -154,7 +154,8 @@ int mat_sparse_attn_fwd_sharded(const void *q, const void *k, const void *v, voi
  * all [B, S, H, D].  Replaces sparse_backward_cuda / dense_backward_cuda and their
  * kernels (src/cuda/sparse_attention_kernel.cu:460-497, 384-421, 265-346, 104-208):
  * the reference's window is left = right = window_size, its dense call is the
- * window that covers S (right = 0 when causal).  MAT_WINDOW patterns, q_offset = 0.
+ * window that covers S (right = 0 when causal).  MAT_WINDOW (and MAT_LONGFORMER, see
+ * mat_sparse_attn_bwd_general) patterns, q_offset = 0.
  * Deterministic (no atomics).  workspace: mat_sparse_attn_bwd_workspace_bytes()
  * bytes of device scratch, 256-byte aligned (per-row log-sum-exp and delta).
  * 16-bit inputs with D = 64 and S a multiple of the dilation run on tensor-core
@@ -168,6 +169,26 @@ int mat_sparse_attn_bwd(const void *q, const void *k, const void *v, const void 
                         int dtype, const mat_pattern_spec *spec, float scale,
                         void *workspace, size_t workspace_bytes, void *stream);
 size_t mat_sparse_attn_bwd_workspace_bytes(int64_t B, int64_t S, int64_t H);
+
+/*
+ * The same backward for every pattern kind.  The reference has no backward for
+ * its generic masked patterns (src/csrc/attention_interface.hpp:14-52: backward
+ * throws); this one exists so that block layouts and the Longformer pattern can
+ * be trained through the same module.  MAT_WINDOW: as mat_sparse_attn_bwd (which
+ * forwards here; t_rowptr / t_colidx unused).  MAT_LONGFORMER: dilation 1,
+ * global_idx sorted and unique (device pointer); also accepted by
+ * mat_sparse_attn_bwd.  MAT_BLOCK: blk_rowptr / blk_colidx as for the forward,
+ * plus the TRANSPOSED layout t_rowptr [n_qblocks + 1] / t_colidx (device
+ * pointers): for every key block the ascending list of query blocks whose
+ * layout row holds it; n_qblocks * block must cover S.  These two kinds run on
+ * the warp-level kernels (fp32 math, any D <= 512, deterministic); same
+ * workspace as mat_sparse_attn_bwd.
+ */
+int mat_sparse_attn_bwd_general(const void *q, const void *k, const void *v, const void *dout,
+                                void *dq, void *dk, void *dv, int64_t B, int64_t S, int64_t H, int64_t D,
+                                int dtype, const mat_pattern_spec *spec, const int32_t *t_rowptr,
+                                const int32_t *t_colidx, float scale, void *workspace,
+                                size_t workspace_bytes, void *stream);
 
 /*
  * Longformer forward that allocates nothing and takes no workspace.  It has no

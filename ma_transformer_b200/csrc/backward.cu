@@ -17,6 +17,11 @@
 //
 // Written for clarity and exactness (fp32 math for every dtype), any head width up
 // to 512.  16-bit inputs with head width 64 go to the tensor-core kernels of bwd_mma.cu instead.
+//
+// The same two kernels run block-sparse layouts and the Longformer pattern (the reference has no
+// backward for those: src/csrc/attention_interface.hpp:14-52 throws): a row's keys and a key's queries
+// are enumerated by PartnerSet below instead of by window arithmetic.  The queries of a key need the
+// transposed block layout, which the caller passes in (mat_sparse_attn_bwd_general).
 #include "mat_common.cuh"
 
 namespace mat {
@@ -47,16 +52,85 @@ struct WindowArgs {
     int D;
     int64_t left, right, dil;
     float scale;
+    // other patterns (kind != MAT_WINDOW)
+    int kind = MAT_WINDOW;
+    int causal = 0;
+    int64_t block = 0, n_blocks = 0;          // block layouts: block edge, blocks along the sequence
+    const int32_t *rowptr = nullptr, *colidx = nullptr;      // query block -> its key blocks (ascending)
+    const int32_t *t_rowptr = nullptr, *t_colidx = nullptr;  // key block -> the query blocks that hold it
+    int64_t n_global = 0;
+    const int64_t *gidx = nullptr;            // Longformer: sorted global positions
 };
 
-// first tap index and tap count of row p (keys p + t*dil, t in [t_lo, t_lo + n))
-__device__ __forceinline__ void taps_of(const WindowArgs &a, int64_t p, int64_t &t_lo, int64_t &n) {
-    int64_t lo = -a.left, hi = a.right;
-    if (p + lo * a.dil < 0) lo = -(p / a.dil);
-    if (p + hi * a.dil >= a.S) hi = (a.S - 1 - p) / a.dil;
-    t_lo = lo;
-    n = hi >= lo ? hi - lo + 1 : 0;
-}
+// The partners of position x: the keys of query x (COLS = false) or the queries of key x (COLS = true), as a
+// count n and at(idx) for idx in [0, n), which returns the partner's position or -1 for a slot that holds none
+// (a key past the causal diagonal of a block, a global position the window already covers).
+template <bool COLS>
+struct PartnerSet {
+    int64_t n, first, dil;       // window part: first + idx * dil for idx < n_win
+    int64_t n_win;
+    int64_t x;
+    const WindowArgs *a;
+    int64_t e0;                  // block layouts: first entry of x's layout row
+    int64_t w_lo, w_hi;          // Longformer: the window part as a closed range, for the de-duplication
+    bool all;                    // Longformer: x is a global position, every position is a partner
+
+    __device__ bool is_global(int64_t p) const {
+        int64_t lo = 0, hi = a->n_global;
+        while (lo < hi) {
+            const int64_t mid = (lo + hi) >> 1;
+            if (a->gidx[mid] < p) lo = mid + 1; else hi = mid;
+        }
+        return lo < a->n_global && a->gidx[lo] == p;
+    }
+    __device__ void init(const WindowArgs &args, int64_t pos) {
+        a = &args;
+        x = pos;
+        all = false;
+        e0 = 0;
+        dil = args.dil;
+        if (args.kind == MAT_BLOCK) {
+            const int64_t r = x / args.block;
+            const int32_t *ptr = COLS ? args.t_rowptr : args.rowptr;
+            e0 = r < args.n_blocks ? ptr[r] : 0;
+            n_win = 0;
+            first = 0;
+            n = r < args.n_blocks ? (int64_t)(ptr[r + 1] - e0) * args.block : 0;
+            return;
+        }
+        // window part: query x sees keys x + t*dil, -left <= t <= right; key x is seen by queries x - t*dil
+        int64_t lo = COLS ? -args.right : -args.left, hi = COLS ? args.left : args.right;
+        if (x + lo * dil < 0) lo = -(x / dil);
+        if (x + hi * dil >= args.S) hi = (args.S - 1 - x) / dil;
+        n_win = hi >= lo ? hi - lo + 1 : 0;
+        first = x + lo * dil;
+        n = n_win;
+        if (args.kind == MAT_LONGFORMER) {
+            w_lo = first;
+            w_hi = first + (n_win - 1);
+            // a global query attends every key, and every query attends a global key
+            if (is_global(x)) {
+                all = true;
+                n = args.S;
+            } else {
+                n = n_win + args.n_global;   // keys: the global keys; queries: the global rows
+            }
+        }
+    }
+    __device__ int64_t at(int64_t idx) const {
+        if (a->kind == MAT_BLOCK) {
+            const int32_t *ci = COLS ? a->t_colidx : a->colidx;
+            const int64_t p = (int64_t)ci[e0 + idx / a->block] * a->block + idx % a->block;
+            if (p >= a->S) return -1;
+            if (a->causal && (COLS ? p < x : p > x)) return -1;   // key <= query
+            return p;
+        }
+        if (all) return idx;
+        if (idx < n_win) return first + idx * dil;
+        const int64_t g = a->gidx[idx - n_win];
+        return (g < 0 || g >= a->S || (g >= w_lo && g <= w_hi)) ? -1 : g;
+    }
+};
 
 template <typename T, int MAXR>
 __global__ void __launch_bounds__(kWarps * 32)
@@ -77,26 +151,29 @@ bwd_rows_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__res
     const int64_t stride = a.H * (int64_t)a.D;
     const T *kb = k + (b * a.S * a.H + h) * (int64_t)a.D;
     const T *vb = v + (b * a.S * a.H + h) * (int64_t)a.D;
-    int64_t t_lo, n;
-    taps_of(a, i, t_lo, n);
-    const int64_t first = i + t_lo * a.dil;
+    PartnerSet<false> keys;
+    keys.init(a, i);
+    const int64_t n = keys.n;
 
     // pass A: log-sum-exp of the scaled scores
     float m = -INFINITY, l = 0.f;
     for (int64_t c = 0; c < n; c += 32) {
         const int64_t idx = c + lane;
-        const float s = idx < n ? dot_row(qs, kb + (first + idx * a.dil) * stride, a.D) * a.scale : -INFINITY;
+        const int64_t j = idx < n ? keys.at(idx) : -1;
+        const float s = j >= 0 ? dot_row(qs, kb + j * stride, a.D) * a.scale : -INFINITY;
         const float m_new = fmaxf(m, wmax(s));
-        l = l * expf(m - m_new) + wsum(idx < n ? expf(s - m_new) : 0.f);
-        m = m_new;
+        if (m_new != -INFINITY) {   // (a chunk of empty slots before the first key leaves the sums untouched)
+            l = l * expf(m - m_new) + wsum(j >= 0 ? expf(s - m_new) : 0.f);
+            m = m_new;
+        }
     }
-    const float lse = n > 0 ? m + logf(l) : 0.f;
+    const float lse = m != -INFINITY ? m + logf(l) : 0.f;
     // pass B: delta = sum_j p_j (dO . v_j)
     float delta = 0.f;
     for (int64_t c = 0; c < n; c += 32) {
         const int64_t idx = c + lane;
-        if (idx < n) {
-            const int64_t j = first + idx * a.dil;
+        const int64_t j = idx < n ? keys.at(idx) : -1;
+        if (j >= 0) {
             const float p = expf(dot_row(qs, kb + j * stride, a.D) * a.scale - lse);
             delta += p * dot_row(gs, vb + j * stride, a.D);
         }
@@ -110,9 +187,8 @@ bwd_rows_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__res
     for (int64_t c = 0; c < n; c += 32) {
         const int64_t idx = c + lane;
         float ds = 0.f;
-        int64_t j = -1;
-        if (idx < n) {
-            j = first + idx * a.dil;
+        const int64_t j = idx < n ? keys.at(idx) : -1;
+        if (j >= 0) {
             const float p = expf(dot_row(qs, kb + j * stride, a.D) * a.scale - lse);
             ds = p * (dot_row(gs, vb + j * stride, a.D) - delta) * a.scale;
         }
@@ -120,6 +196,7 @@ bwd_rows_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__res
         for (int t = 0; t < steps; ++t) {
             const int64_t jt = __shfl_sync(0xffffffffu, j, t);
             const float dst = __shfl_sync(0xffffffffu, ds, t);
+            if (jt < 0) continue;   // an empty slot (the same for every lane)
             const T *kr = kb + jt * stride;
 #pragma unroll
             for (int r = 0; r < MAXR; ++r) {
@@ -156,12 +233,10 @@ bwd_cols_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__res
     const T *qb = q + (b * a.S * a.H + h) * (int64_t)a.D;
     const T *gb = dout + (b * a.S * a.H + h) * (int64_t)a.D;
     const float2 *st = stats + (b * a.H + h) * a.S;   // stats are stored per (b, h, i) with i fastest
-    // query i attends key j iff j = i + t*dil with -left <= t <= right, i.e. i = j - t*dil
-    int64_t u_lo = -a.right, u_hi = a.left;           // i = j + u*dil
-    if (j + u_lo * a.dil < 0) u_lo = -(j / a.dil);
-    if (j + u_hi * a.dil >= a.S) u_hi = (a.S - 1 - j) / a.dil;
-    const int64_t n = u_hi >= u_lo ? u_hi - u_lo + 1 : 0;
-    const int64_t first = j + u_lo * a.dil;
+    // the queries that attend key j (a window: i = j - t*dil with -left <= t <= right)
+    PartnerSet<true> rows;
+    rows.init(a, j);
+    const int64_t n = rows.n;
 
     float ak[MAXR], av[MAXR];
 #pragma unroll
@@ -169,9 +244,8 @@ bwd_cols_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__res
     for (int64_t c = 0; c < n; c += 32) {
         const int64_t idx = c + lane;
         float p = 0.f, ds = 0.f;
-        int64_t i = -1;
-        if (idx < n) {
-            i = first + idx * a.dil;
+        const int64_t i = idx < n ? rows.at(idx) : -1;
+        if (i >= 0) {
             const float2 s2 = st[i];
             p = expf(dot_row(ks, qb + i * stride, a.D) * a.scale - s2.x);
             ds = p * (dot_row(vs, gb + i * stride, a.D) - s2.y) * a.scale;
@@ -181,6 +255,7 @@ bwd_cols_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__res
             const int64_t it = __shfl_sync(0xffffffffu, i, t);
             const float pt = __shfl_sync(0xffffffffu, p, t);
             const float dst = __shfl_sync(0xffffffffu, ds, t);
+            if (it < 0) continue;
             const T *qr = qb + it * stride;
             const T *gr = gb + it * stride;
 #pragma unroll
@@ -216,7 +291,7 @@ int launch_r(const void *q, const void *k, const void *v, const void *dout, void
         (const T *)q, (const T *)k, (const T *)v, (const T *)dout, (T *)dk, (T *)dv, stats, a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "backward launch");
-    note_kernel("bwd_window");
+    note_kernel(a.kind == MAT_WINDOW ? "bwd_window" : "bwd_general");
     return MAT_OK;
 }
 
@@ -245,10 +320,29 @@ int mat_sparse_attn_bwd(const void *q, const void *k, const void *v, const void 
                         void *dv, int64_t B, int64_t S, int64_t H, int64_t D, int dtype,
                         const mat_pattern_spec *spec, float scale, void *workspace, size_t workspace_bytes,
                         void *stream) {
+    if (spec && spec->kind == MAT_BLOCK)
+        return fail(MAT_ERR_UNSUPPORTED, "the backward of a block layout needs the transposed layout: mat_sparse_attn_bwd_general");
+    return mat_sparse_attn_bwd_general(q, k, v, dout, dq, dk, dv, B, S, H, D, dtype, spec, nullptr, nullptr, scale,
+                                       workspace, workspace_bytes, stream);
+}
+
+int mat_sparse_attn_bwd_general(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk,
+                                void *dv, int64_t B, int64_t S, int64_t H, int64_t D, int dtype,
+                                const mat_pattern_spec *spec, const int32_t *t_rowptr, const int32_t *t_colidx,
+                                float scale, void *workspace, size_t workspace_bytes, void *stream) {
     if (!spec) return fail(MAT_ERR_INVALID, "pattern description is NULL");
-    if (spec->kind != MAT_WINDOW) return fail(MAT_ERR_UNSUPPORTED, "backward is defined for window patterns");
-    if (spec->left < 0 || spec->right < 0 || spec->dilation < 1 || spec->q_offset != 0)
+    if (spec->kind != MAT_WINDOW && spec->kind != MAT_BLOCK && spec->kind != MAT_LONGFORMER)
+        return fail(MAT_ERR_INVALID, "unknown pattern kind %d", spec->kind);
+    if (spec->q_offset != 0) return fail(MAT_ERR_INVALID, "q_offset must be 0 for the backward pass");
+    if (spec->kind != MAT_BLOCK && (spec->left < 0 || spec->right < 0 || spec->dilation < 1))
         return fail(MAT_ERR_INVALID, "bad window description for the backward pass");
+    if (spec->kind == MAT_LONGFORMER && (spec->dilation != 1 || spec->n_global < 0 || (spec->n_global > 0 && !spec->global_idx)))
+        return fail(MAT_ERR_INVALID, "bad Longformer description for the backward pass");
+    if (spec->kind == MAT_BLOCK) {
+        if (spec->block < 1 || spec->n_qblocks < 1 || !spec->blk_rowptr || !spec->blk_colidx || !t_rowptr || !t_colidx)
+            return fail(MAT_ERR_INVALID, "block layout and its transpose (device pointers) are required");
+        if (spec->n_qblocks * spec->block < S) return fail(MAT_ERR_INVALID, "the block layout does not cover the sequence");
+    }
     if (!q || !k || !v || !dout || !dq || !dk || !dv) return fail(MAT_ERR_INVALID, "tensor pointers must be non-NULL");
     if (B <= 0 || S <= 0 || H <= 0 || D <= 0) return fail(MAT_ERR_INVALID, "all tensor dimensions must be > 0");
     const size_t need = mat_sparse_attn_bwd_workspace_bytes(B, S, H);
@@ -259,14 +353,24 @@ int mat_sparse_attn_bwd(const void *q, const void *k, const void *v, const void 
     a.B = B; a.S = S; a.H = H; a.D = (int)D;
     a.left = spec->left > S ? S : spec->left;
     a.right = spec->right > S ? S : spec->right;
-    a.dil = spec->dilation;
+    a.dil = spec->kind == MAT_BLOCK ? 1 : spec->dilation;
     a.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)D);
+    a.kind = spec->kind;
+    a.causal = spec->causal;
+    a.block = spec->block;
+    a.n_blocks = spec->n_qblocks;
+    a.rowptr = spec->blk_rowptr;
+    a.colidx = spec->blk_colidx;
+    a.t_rowptr = t_rowptr;
+    a.t_colidx = t_colidx;
+    a.n_global = spec->kind == MAT_LONGFORMER ? spec->n_global : 0;
+    a.gidx = spec->global_idx;
     float2 *stats = (float2 *)workspace;
     cudaStream_t st = (cudaStream_t)stream;
     // the tensor-core kernels move 16-byte vectors and TMA boxes: unaligned tensors stay on the warp-level kernels
     const uintptr_t al = (uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)dout | (uintptr_t)dq | (uintptr_t)dk |
                          (uintptr_t)dv;
-    if (al % 16 == 0 && bwd_mma_supports(B, S, H, D, dtype, a.left, a.right, a.dil))
+    if (spec->kind == MAT_WINDOW && al % 16 == 0 && bwd_mma_supports(B, S, H, D, dtype, a.left, a.right, a.dil))
         return launch_bwd_mma(q, k, v, dout, dq, dk, dv, stats, B, S, H, dtype, a.left, a.right, a.dil, a.scale, st);
     switch (dtype) {
         case MAT_F32: return launch_t<float>(q, k, v, dout, dq, dk, dv, stats, a, st);

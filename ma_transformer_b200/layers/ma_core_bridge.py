@@ -144,8 +144,6 @@ class MACoreAttentionFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output: torch.Tensor):
         query, key, value = ctx.saved_tensors
-        if ctx.pattern is not None and not (query.is_cuda and ctx.pattern.kind == 0):
-            raise NotImplementedError("backward is defined for window patterns (and on CUDA tensors for custom ones)")
         if query.is_cuda:
             args = (query.contiguous(), key.contiguous(), value.contiguous(), grad_output.contiguous())
             if ctx.pattern is not None:
@@ -162,7 +160,9 @@ class MACoreAttentionFunction(torch.autograd.Function):
             dt = query.dtype
             work = dt if dt in (torch.float32, torch.bfloat16, torch.float16) else torch.float32
             args = tuple(t.detach().to("cuda", work).contiguous() for t in (query, key, value, grad_output))
-            if ctx.sparse:
+            if ctx.pattern is not None:
+                grads = sparse_attention_cuda.backward_pattern(*args, ctx.pattern)
+            elif ctx.sparse:
                 grads = sparse_attention_cuda.backward(*args, int(ctx.window_size))
             else:
                 grads = sparse_attention_cuda.dense_backward(*args, bool(ctx.use_causal_mask))

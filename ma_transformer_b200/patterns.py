@@ -146,6 +146,32 @@ class PatternSpec:
             s.global_idx = g.data_ptr()
         return s
 
+    def transposed_layout(self):
+        """Block layouts: (rowptr, colidx) of the transposed layout as int32 numpy arrays: for every key
+        block the ascending query blocks whose layout row holds it (what the backward's dK / dV pass walks)."""
+        if self.kind != BLOCK:
+            raise ValueError("only block layouts have a transposed layout")
+        n = len(self.blk_rowptr) - 1
+        rows = np.repeat(np.arange(n, dtype=np.int64), np.diff(self.blk_rowptr))
+        cols = self.blk_colidx.astype(np.int64)
+        if len(cols) and int(cols.max()) >= n:
+            raise ValueError("the backward needs a square layout (key blocks within the sequence)")
+        order = np.lexsort((rows, cols))
+        t_colidx = rows[order].astype(np.int32)
+        t_rowptr = np.zeros(n + 1, dtype=np.int32)
+        np.cumsum(np.bincount(cols, minlength=n), out=t_rowptr[1:])
+        return t_rowptr, t_colidx
+
+    def device_transposed_layout(self, device):
+        """The transposed layout on ``device`` (uploaded once, cached) as two int32 tensors."""
+        import torch
+        key = "T" + str(torch.device(device))
+        if key not in self._dev:
+            rp, ci = self.transposed_layout()
+            self._dev[key] = (torch.from_numpy(rp).to(device),
+                              torch.from_numpy(ci).to(device) if len(ci) else torch.zeros(1, dtype=torch.int32, device=device))
+        return self._dev[key]
+
     # ---- host index sets -------------------------------------------------------
     def rowset(self, s_kv: int, i: int) -> np.ndarray:
         """Sorted unique key positions of query row ``i`` (int64)."""

@@ -19,7 +19,7 @@ from typing import Dict, List, Optional
 import torch
 
 from . import _native as nat
-from .patterns import PatternSpec, WINDOW
+from .patterns import PatternSpec, WINDOW, BLOCK
 
 _DTYPES = {torch.float32: nat.MAT_F32, torch.bfloat16: nat.MAT_BF16, torch.float16: nat.MAT_F16}
 _workspaces: Dict[tuple, torch.Tensor] = {}
@@ -278,8 +278,9 @@ def forward_host(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, sp
 
 def backward_pattern(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, grad_out: torch.Tensor,
                      spec: PatternSpec, scale: Optional[float] = None) -> List[torch.Tensor]:
-    """[dQ, dK, dV] of a window pattern (sliding, causal, dilated, dense-as-window) by the
-    library's backward kernels: deterministic, no atomics, fp32 math for every dtype."""
+    """[dQ, dK, dV] of any pattern by the library's backward kernels: deterministic, no atomics.  Window
+    patterns (sliding, causal, dilated, dense-as-window) with 16-bit inputs and D = 64 run on tensor-core
+    kernels; block layouts and the Longformer pattern on the warp-level kernels with fp32 math."""
     _check_inputs(query, key, value, grad_out)
     if not (query.shape == key.shape == value.shape == grad_out.shape):
         raise RuntimeError("All tensors must have same shape")
@@ -289,10 +290,14 @@ def backward_pattern(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor
         s = spec.device_struct(query.device)
         ws = _workspace(query.device, nat.lib.mat_sparse_attn_bwd_workspace_bytes(B, S, H))
         stream = torch.cuda.current_stream(query.device).cuda_stream
-        nat.check(nat.lib.mat_sparse_attn_bwd(
+        t_rp = t_ci = None
+        if spec.kind == BLOCK:   # the dK / dV pass walks the transposed layout
+            t_rp, t_ci = spec.device_transposed_layout(query.device)
+        nat.check(nat.lib.mat_sparse_attn_bwd_general(
             query.data_ptr(), key.data_ptr(), value.data_ptr(), grad_out.data_ptr(), dq.data_ptr(), dk.data_ptr(),
-            dv.data_ptr(), B, S, H, D, _DTYPES[query.dtype], C.byref(s), float(scale) if scale else 0.0,
-            ws.data_ptr(), ws.numel(), C.c_void_p(stream)))
+            dv.data_ptr(), B, S, H, D, _DTYPES[query.dtype], C.byref(s),
+            t_rp.data_ptr() if t_rp is not None else None, t_ci.data_ptr() if t_ci is not None else None,
+            float(scale) if scale else 0.0, ws.data_ptr(), ws.numel(), C.c_void_p(stream)))
     return [dq, dk, dv]
 
 

@@ -106,3 +106,20 @@ def masked_dense_attention(q, k, v, left, right, dilation=1):
     s = torch.einsum("bihd,bjhd->bhij", q, k) / math.sqrt(q.shape[-1])
     s = s.masked_fill(~keep, float("-inf"))
     return torch.einsum("bhij,bjhd->bihd", torch.softmax(s, dim=-1), v)
+
+
+def pattern_mask(spec, S):
+    """[S, S] boolean: entry (i, j) is set iff query row i of the pattern attends key j.  Built row by row from
+    the library's host index sets (mat_pattern_rowset), which are pinned to the oracle bit for bit and share no
+    code with the backward kernels."""
+    keep = torch.zeros(S, S, dtype=torch.bool)
+    for i in range(S):
+        keep[i, torch.from_numpy(spec.rowset(S, i))] = True
+    return keep
+
+
+def masked_attention_with(q, k, v, keep):
+    """Dense masked softmax attention over an explicit [S, S] mask, in the tensors' own dtype."""
+    s = torch.einsum("bihd,bjhd->bhij", q, k) / math.sqrt(q.shape[-1])
+    s = s.masked_fill(~keep.to(q.device), float("-inf"))
+    return torch.einsum("bhij,bjhd->bihd", torch.softmax(s, dim=-1), v)

@@ -227,3 +227,20 @@ def test_torch_oracle_functions_match_oracle(oracle):
         np.testing.assert_allclose(mt.pytorch_sparse_attention(q, k, v, w).numpy(), want, rtol=1e-5, atol=1e-6)
     want = oracle.sparse_attention(q.numpy(), k.numpy(), v.numpy(), oracle.OraclePattern(left=21, right=0))
     np.testing.assert_allclose(mt.pytorch_dense_attention(q, k, v, True).numpy(), want, rtol=1e-5, atol=1e-6)
+
+
+def test_transposed_block_layout_round_trip():
+    """The layout the backward's dK / dV pass walks: for every key block the ascending query blocks that hold it.
+    Transposing twice gives the layout back; entries are the same (row, column) pairs."""
+    from ma_transformer_b200.patterns import PatternSpec, band_random_block_layout
+    rp, ci = band_random_block_layout(17, 3, 2, seed=11)
+    spec = PatternSpec.block_sparse(64, rp, ci, causal=True)
+    t_rp, t_ci = spec.transposed_layout()
+    assert t_rp.dtype == np.int32 and t_ci.dtype == np.int32 and t_rp[-1] == len(ci) and len(t_rp) == len(rp)
+    pairs = {(r, int(c)) for r in range(len(rp) - 1) for c in ci[rp[r]:rp[r + 1]]}
+    t_pairs = {(int(r), c) for c in range(len(t_rp) - 1) for r in t_ci[t_rp[c]:t_rp[c + 1]]}
+    assert pairs == t_pairs
+    for c in range(len(t_rp) - 1):
+        assert list(t_ci[t_rp[c]:t_rp[c + 1]]) == sorted(t_ci[t_rp[c]:t_rp[c + 1]])
+    back = PatternSpec.block_sparse(64, t_rp, t_ci).transposed_layout()
+    assert np.array_equal(back[0], spec.blk_rowptr) and np.array_equal(back[1], spec.blk_colidx)

@@ -10,7 +10,8 @@ import ma_transformer_b200 as mt
 from ma_transformer_b200 import _native as nat
 from ma_transformer_b200 import sparse_attention_cuda as ext
 from ma_transformer_b200.patterns import PatternSpec, band_random_block_layout, tridiagonal_block_layout
-from helpers import (check_close, expected_window_kernel, masked_dense_attention, oracle_out, rel_err, seeded_qkv,
+from helpers import (check_close, expected_window_kernel, masked_attention_with, masked_dense_attention, oracle_out,
+                     pattern_mask, rel_err, seeded_qkv,
                      to_oracle)
 
 pytestmark = pytest.mark.gpu
@@ -720,6 +721,50 @@ def test_tensor_core_backward_matches_fp64_autograd_and_fp32_math_kernels(monkey
     monkeypatch.delenv("MAT_BWD_KERNEL")
     again = ext.backward_pattern(qd, kd, vd, god, spec)
     for a, b in zip(got, again):
+        assert torch.equal(a, b)
+
+
+def _general_backward_cases():
+    rp, ci = band_random_block_layout(5, 2, 2, seed=3)            # 5 blocks of 64: band of 2 + 2 random earlier ones
+    rp32, ci32 = band_random_block_layout(9, 3, 1, seed=4)        # 9 blocks of 32
+    full_rp, full_ci = np.arange(0, 17, 4), np.tile(np.arange(4), 4)   # every block: dense through a layout
+    return [
+        ("block64-causal", PatternSpec.block_sparse(64, rp, ci, causal=True), 320),
+        ("block64-ragged", PatternSpec.block_sparse(64, rp, ci, causal=True), 300),      # the last block is partly filled
+        ("block32", PatternSpec.block_sparse(32, rp32, ci32, causal=False), 288),
+        ("block64-dense", PatternSpec.block_sparse(64, full_rp, full_ci, causal=False), 256),
+        ("longformer", PatternSpec.longformer(8, 8, [0, 17, 100, 199]), 200),
+        ("longformer-lopsided", PatternSpec.longformer(20, 3, [5, 6, 7, 150]), 211),
+        ("longformer-no-globals", PatternSpec.longformer(4, 0, []), 70),
+    ]
+
+
+@pytest.mark.parametrize("name,spec,S", _general_backward_cases(), ids=[c[0] for c in _general_backward_cases()])
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 64), (torch.bfloat16, 64), (torch.float32, 40)])
+def test_backward_of_block_layouts_and_longformer_against_fp64_autograd(name, spec, S, dtype, D):
+    """dQ, dK, dV of block layouts and of the Longformer pattern (the reference's interface has no backward for
+    them: src/csrc/attention_interface.hpp:14-52) against autograd in fp64 through a dense softmax masked with
+    the pattern's own index sets; and through the autograd function of the module."""
+    B, H = 2, 2
+    q, k, v = seeded_qkv(97, B, S, H, D, dtype)
+    go = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(98)).to(dtype)
+    got = ext.backward_pattern(q.to(DEV), k.to(DEV), v.to(DEV), go.to(DEV), spec)
+    torch.cuda.synchronize()
+    assert nat.last_kernel() == "bwd_general" and nat.device_status() == 0
+    keep = pattern_mask(spec, S)
+    ref = [t.double().requires_grad_(True) for t in (q, k, v)]
+    masked_attention_with(*ref, keep).backward(go.double())
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -7      # fp32 math; 16-bit outputs are rounded once
+    for nm, a, r in zip(("dQ", "dK", "dV"), got, ref):
+        a = a.cpu().double()
+        assert torch.isfinite(a).all(), nm
+        err = float((a - r.grad).abs().max())
+        assert err <= tol * max(1.0, float(r.grad.abs().max())), f"{name} {nm}: {err}"
+    # the same gradients through torch.autograd and the module's function (forward on the native kernels too)
+    qd, kd, vd = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+    out = mt.MACoreAttentionFunction.apply(qd, kd, vd, True, 0, False, spec)
+    out.backward(go.to(DEV))
+    for a, b in zip(got, (qd.grad, kd.grad, vd.grad)):
         assert torch.equal(a, b)
 
 
