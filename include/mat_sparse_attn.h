@@ -180,9 +180,11 @@ size_t mat_sparse_attn_bwd_workspace_bytes(int64_t B, int64_t S, int64_t H);
  * mat_sparse_attn_bwd.  MAT_BLOCK: blk_rowptr / blk_colidx as for the forward,
  * plus the TRANSPOSED layout t_rowptr [n_qblocks + 1] / t_colidx (device
  * pointers): for every key block the ascending list of query blocks whose
- * layout row holds it; n_qblocks * block must cover S.  These two kinds run on
- * the warp-level kernels (fp32 math, any D <= 512, deterministic); same
- * workspace as mat_sparse_attn_bwd.
+ * layout row holds it; n_qblocks * block must cover S.  16-bit block layouts
+ * with D = 64 and block a multiple of 64 run on the streamed tensor-core kernels
+ * (a tile walks the chunks of its layout row's blocks); other block layouts and
+ * the Longformer pattern on the warp-level kernels (fp32 math, any D <= 512).
+ * Deterministic; same workspace as mat_sparse_attn_bwd.
  */
 int mat_sparse_attn_bwd_general(const void *q, const void *k, const void *v, const void *dout,
                                 void *dq, void *dk, void *dv, int64_t B, int64_t S, int64_t H, int64_t D,

@@ -370,6 +370,9 @@ int mat_sparse_attn_bwd_general(const void *q, const void *k, const void *v, con
     // the tensor-core kernels move 16-byte vectors and TMA boxes: unaligned tensors stay on the warp-level kernels
     const uintptr_t al = (uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)dout | (uintptr_t)dq | (uintptr_t)dk |
                          (uintptr_t)dv;
+    if (spec->kind == MAT_BLOCK && al % 16 == 0 && bwd_block_mma_supports(B, S, H, D, dtype, spec->block))
+        return launch_bwd_block_mma(q, k, v, dout, dq, dk, dv, stats, B, S, H, dtype, spec->block, spec->causal,
+                                    spec->blk_rowptr, spec->blk_colidx, t_rowptr, t_colidx, a.scale, st);
     if (spec->kind == MAT_WINDOW && al % 16 == 0 && bwd_mma_supports(B, S, H, D, dtype, a.left, a.right, a.dil))
         return launch_bwd_mma(q, k, v, dout, dq, dk, dv, stats, B, S, H, dtype, a.left, a.right, a.dil, a.scale, st);
     switch (dtype) {

@@ -51,6 +51,11 @@ struct BwdArgs {
     int left, right;
     float scale;
     int prefetch_ahead;       // resident-band kernels: L2-prefetch the tile this many CTAs ahead (0 = off)
+    // Block layouts (streamed kernel only): a 64-row tile walks the 64-column chunks of its layout row's blocks
+    // (rows pass: query block -> key blocks; cols pass: the transposed layout, key block -> query blocks)
+    int block_mode = 0, causal = 0;
+    int per_blk = 1;          // 64-column chunks per layout block
+    const int32_t *rowptr = nullptr, *colidx = nullptr, *t_rowptr = nullptr, *t_colidx = nullptr;
 };
 
 __device__ __forceinline__ uint32_t swz(int row, int chunk) {
@@ -441,9 +446,36 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     const int64_t lo = r0 - back > 0 ? r0 - back : 0;
     const int64_t hi = r0 + 63 + fwd < a.S - 1 ? r0 + 63 + fwd : a.S - 1;
     const int64_t k_first = lo / 64;
-    const int nch = (int)(hi / 64 - k_first) + 1;        // chunks per walk of the band
+    const bool blk = a.block_mode != 0;
+    const int32_t *blk_idx = COLS ? a.t_colidx : a.colidx;
+    int64_t e0 = 0;
+    int nch = (int)(hi / 64 - k_first) + 1;              // chunks per walk of the band
+    if (blk) {
+        const int32_t *ptr = COLS ? a.t_rowptr : a.rowptr;
+        const int64_t lr = r0 / (64 * a.per_blk);        // the tile's layout row
+        e0 = ptr[lr];
+        nch = (ptr[lr + 1] - (int)e0) * a.per_blk;
+    }
+    // chunk m of the walk: 64 columns starting at 64 * chunk_at(m)
+    auto chunk_at = [&](int m) -> int64_t {
+        return blk ? (int64_t)blk_idx[e0 + m / a.per_blk] * a.per_blk + m % a.per_blk : k_first + m;
+    };
     const int total = COLS ? nch : 2 * nch;              // the rows pass walks it twice
     const int64_t wrow = r0 + 16 * warp;                 // the warp's first row
+    if (nch == 0) {
+        // a layout row without a block: no gradient flows through these rows
+        float zero[8][4];
+#pragma unroll
+        for (int dt = 0; dt < 8; ++dt) zero[dt][0] = zero[dt][1] = zero[dt][2] = zero[dt][3] = 0.f;
+        if constexpr (!COLS) {
+            if (tid < 64 && r0 + tid < a.S) a.stats[(b * a.HH + h) * a.S + r0 + tid] = make_float2(0.f, 0.f);
+            store_tile<T>(smem, oX1, zero, (T *)a.dq + head_off, r0, a.S, stride, warp, lane);
+        } else {
+            store_tile<T>(smem, oX1, zero, (T *)a.dk + head_off, r0, a.S, stride, warp, lane);
+            store_tile<T>(smem, oX2, zero, (T *)a.dv + head_off, r0, a.S, stride, warp, lane);
+        }
+        return;
+    }
 
     if (tid == 0) {
         ptx::mbar_init(bar, 1);
@@ -454,7 +486,7 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     // Step n of the flat walk (chunk k_first + n % nch) goes to stage n & 1.  It is issued while step n - 1 is
     // being computed, after the barrier that says every warp has left step n - 2, the stage's previous tenant.
     auto issue = [&](int n) {
-        const int64_t k = k_first + n % nch;
+        const int64_t k = chunk_at(n % nch);
         const int st = n & 1;
         if (tid == 0) {
             ptx::mbar_expect_tx(bar + st, n == 0 ? 32768u : 16384u);
@@ -481,13 +513,25 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     // group p of chunk k: 0 = none of the warp's rows sees it, 1 = every (row, column) pair is seen, 2 = mask it
     auto group_kind = [&](int64_t k, int p) -> int {
         const int64_t c = 64 * k + 16 * p;      // the group's first column
+        if (blk) {
+            // every (row, column) pair of a block counts, except past the causal diagonal (a key after its query:
+            // the rows pass has queries as rows, the cols pass keys) and past the end of the sequence
+            if (c >= a.S) return 0;
+            bool full = c + 15 < a.S;
+            if (a.causal) {
+                if (COLS ? c + 15 < wrow : c > wrow + 15) return 0;
+                full = full && (COLS ? c >= wrow + 15 : c + 15 <= wrow);
+            }
+            return full ? 1 : 2;
+        }
         if (c + 15 < wrow - back || c > wrow + 15 + fwd || c >= a.S) return 0;
         return (c - (wrow + 15) >= -back && c + 15 - wrow <= fwd && c + 15 < a.S) ? 1 : 2;
     };
     // column 64k + 16p + cc of row wrow + r is seen iff -back <= column - row <= fwd and the column exists
     auto seen = [&](int64_t k, int p, int cc, int r) -> bool {
         const int64_t c = 64 * k + 16 * p;
-        const int d = (int)(c - wrow) + cc - r;
+        const int d = (int)(c - wrow) + cc - r;     // column - row
+        if (blk) return c + cc < a.S && (!a.causal || (COLS ? d >= 0 : d <= 0));
         return (unsigned)(d + (int)back) <= W && c + cc < a.S;
     };
     auto group_products = [&](uint32_t y, int p, float (&s)[2][4], float (&dp)[2][4]) {
@@ -533,7 +577,7 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
                 ptx::ldmatrix_x4(a2[ks], sbase + oX2 + swz(row, 2 * ks + cadd));
             }
         }
-        const int64_t k = k_first + n % nch;
+        const int64_t k = chunk_at(n % nch);
         const uint32_t y = sbase + oY + (n & 1) * 16384;
         if constexpr (!COLS) {
             if (n == nch) {   // between the sweeps: the statistics are complete
@@ -676,7 +720,7 @@ int launch_bwd_stream(const BwdArgs &a, int dtype, cudaStream_t stream) {
     bwd_stream_mma_kernel<T, true><<<grid, kThreads, kStreamSmemBytes, stream>>>(mq, mk, mv, mgo, a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "tensor-core backward launch");
-    note_kernel("bwd_stream_mma");
+    note_kernel(a.block_mode ? "bwd_block_mma" : "bwd_stream_mma");
     return MAT_OK;
 }
 
@@ -729,6 +773,35 @@ int launch_bwd_mma(const void *q, const void *k, const void *v, const void *dout
         return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16, 5>(a, dtype, stream) : launch_bwd<__half, 5>(a, dtype, stream);
     if (a.left + a.right <= 128)
         return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16, 9>(a, dtype, stream) : launch_bwd<__half, 9>(a, dtype, stream);
+    return dtype == MAT_BF16 ? launch_bwd_stream<__nv_bfloat16>(a, dtype, stream) : launch_bwd_stream<__half>(a, dtype, stream);
+}
+
+// Block layouts on the streamed tensor-core kernels: 16-bit, D = 64, block a multiple of 64, both the layout and
+// its transpose on the device.
+bool bwd_block_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t block) {
+    if (dtype != MAT_BF16 && dtype != MAT_F16) return false;
+    if (D != 64 || block < 64 || block % 64 != 0 || block / 64 > 0x7fffffffLL) return false;
+    const char *env = getenv("MAT_BWD_KERNEL");
+    if (env && strcmp(env, "warp") == 0) return false;
+    return H < (1LL << 31) && (S + kTile - 1) / kTile <= 65535 && B <= 65535;
+}
+
+int launch_bwd_block_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk, void *dv,
+                         float2 *stats, int64_t B, int64_t S, int64_t H, int dtype, int64_t block, int causal,
+                         const int32_t *rowptr, const int32_t *colidx, const int32_t *t_rowptr, const int32_t *t_colidx,
+                         float scale, cudaStream_t stream) {
+    BwdArgs a;
+    a.q = q; a.k = k; a.v = v; a.go = dout;
+    a.dq = dq; a.dk = dk; a.dv = dv;
+    a.stats = stats;
+    a.B = B; a.S = S; a.HH = H;
+    a.left = a.right = 0;
+    a.scale = scale;
+    a.prefetch_ahead = 0;
+    a.block_mode = 1;
+    a.causal = causal;
+    a.per_blk = (int)(block / 64);
+    a.rowptr = rowptr; a.colidx = colidx; a.t_rowptr = t_rowptr; a.t_colidx = t_colidx;
     return dtype == MAT_BF16 ? launch_bwd_stream<__nv_bfloat16>(a, dtype, stream) : launch_bwd_stream<__half>(a, dtype, stream);
 }
 

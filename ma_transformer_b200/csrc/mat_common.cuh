@@ -112,6 +112,11 @@ bool bwd_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int
 int launch_bwd_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk, void *dv,
                    float2 *stats, int64_t B, int64_t S, int64_t H, int dtype, int64_t left, int64_t right,
                    int64_t dil, float scale, cudaStream_t stream);
+bool bwd_block_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t block);
+int launch_bwd_block_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk, void *dv,
+                         float2 *stats, int64_t B, int64_t S, int64_t H, int dtype, int64_t block, int causal,
+                         const int32_t *rowptr, const int32_t *colidx, const int32_t *t_rowptr, const int32_t *t_colidx,
+                         float scale, cudaStream_t stream);
 
 template <typename T> struct Elem;
 template <> struct Elem<float> {

@@ -740,8 +740,8 @@ def _general_backward_cases():
 
 
 @pytest.mark.parametrize("name,spec,S", _general_backward_cases(), ids=[c[0] for c in _general_backward_cases()])
-@pytest.mark.parametrize("dtype,D", [(torch.float32, 64), (torch.bfloat16, 64), (torch.float32, 40)])
-def test_backward_of_block_layouts_and_longformer_against_fp64_autograd(name, spec, S, dtype, D):
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 64), (torch.bfloat16, 64), (torch.float16, 64), (torch.float32, 40)])
+def test_backward_of_block_layouts_and_longformer_against_fp64_autograd(monkeypatch, name, spec, S, dtype, D):
     """dQ, dK, dV of block layouts and of the Longformer pattern (the reference's interface has no backward for
     them: src/csrc/attention_interface.hpp:14-52) against autograd in fp64 through a dense softmax masked with
     the pattern's own index sets; and through the autograd function of the module."""
@@ -750,11 +750,14 @@ def test_backward_of_block_layouts_and_longformer_against_fp64_autograd(name, sp
     go = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(98)).to(dtype)
     got = ext.backward_pattern(q.to(DEV), k.to(DEV), v.to(DEV), go.to(DEV), spec)
     torch.cuda.synchronize()
-    assert nat.last_kernel() == "bwd_general" and nat.device_status() == 0
+    # block layouts whose blocks are multiples of 64 run on the streamed tensor-core kernels (16-bit, D = 64)
+    on_mma = spec.kind == 1 and spec.block % 64 == 0 and dtype != torch.float32 and D == 64
+    assert nat.last_kernel() == ("bwd_block_mma" if on_mma else "bwd_general") and nat.device_status() == 0
     keep = pattern_mask(spec, S)
     ref = [t.double().requires_grad_(True) for t in (q, k, v)]
     masked_attention_with(*ref, keep).backward(go.double())
-    tol = 1e-5 if dtype == torch.float32 else 2 ** -7      # fp32 math; 16-bit outputs are rounded once
+    # fp32 math with 16-bit outputs rounded once; the tensor-core kernels also round P and dS to the input type
+    tol = 1e-5 if dtype == torch.float32 else (2e-2 if dtype == torch.bfloat16 else 5e-3) if on_mma else 2 ** -7
     for nm, a, r in zip(("dQ", "dK", "dV"), got, ref):
         a = a.cpu().double()
         assert torch.isfinite(a).all(), nm
@@ -766,6 +769,13 @@ def test_backward_of_block_layouts_and_longformer_against_fp64_autograd(name, sp
     out.backward(go.to(DEV))
     for a, b in zip(got, (qd.grad, kd.grad, vd.grad)):
         assert torch.equal(a, b)
+    if on_mma:   # and the fp32-math kernels on the same inputs
+        monkeypatch.setenv("MAT_BWD_KERNEL", "warp")
+        want = ext.backward_pattern(q.to(DEV), k.to(DEV), v.to(DEV), go.to(DEV), spec)
+        assert nat.last_kernel() == "bwd_general"
+        for nm, a, b in zip(("dQ", "dK", "dV"), got, want):
+            err = float((a.float() - b.float()).abs().max())
+            assert err <= tol * max(1.0, float(b.float().abs().max())), f"{name} {nm} vs warp-level: {err}"
 
 
 def test_backward_of_unaligned_tensors_stays_on_warp_kernels():
