@@ -182,10 +182,16 @@ size_t mat_sparse_attn_bwd_workspace_bytes(int64_t B, int64_t S, int64_t H);
  * pointers): for every key block the ascending list of query blocks whose
  * layout row holds it; n_qblocks * block must cover S.  16-bit block layouts
  * with D = 64 and block a multiple of 64 run on the streamed tensor-core kernels
- * (a tile walks the chunks of its layout row's blocks); other block layouts and
- * the Longformer pattern on the warp-level kernels (fp32 math, any D <= 512).
- * Deterministic; same workspace as mat_sparse_attn_bwd.
+ * (a tile walks the chunks of its layout row's blocks), and so does the
+ * Longformer pattern with 1 to 64 global positions (window band plus a chunk of
+ * gathered global rows per tile, then the gathered global rows and keys against
+ * the whole sequence); other shapes on the warp-level kernels (fp32 math, any
+ * D <= 512).  Deterministic.  workspace: mat_sparse_attn_bwd_general_workspace_bytes()
+ * bytes (what mat_sparse_attn_bwd wants, plus the gathered rows of a Longformer
+ * call), 256-byte aligned.
  */
+size_t mat_sparse_attn_bwd_general_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t D, int dtype,
+                                                   const mat_pattern_spec *spec);
 int mat_sparse_attn_bwd_general(const void *q, const void *k, const void *v, const void *dout,
                                 void *dq, void *dk, void *dv, int64_t B, int64_t S, int64_t H, int64_t D,
                                 int dtype, const mat_pattern_spec *spec, const int32_t *t_rowptr,

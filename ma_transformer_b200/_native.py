@@ -21,7 +21,7 @@ EXPORTS = (
     "mat_sparse_attn_fwd_host", "mat_sparse_attn_host_staging_bytes", "mat_sparse_attn_fwd_sharded",
     "mat_pattern_rowset", "mat_pattern_nnz", "mat_enable_peer_access",
     "mat_ipc_export", "mat_ipc_open", "mat_ipc_close", "mat_sparse_attn_fwd_longformer_noalloc",
-    "mat_sparse_attn_bwd", "mat_sparse_attn_bwd_workspace_bytes", "mat_sparse_attn_bwd_general",
+    "mat_sparse_attn_bwd", "mat_sparse_attn_bwd_workspace_bytes", "mat_sparse_attn_bwd_general", "mat_sparse_attn_bwd_general_workspace_bytes",
     "mat_longformer_shard_fwd", "mat_global_rows_partial_layout", "mat_global_rows_partial", "mat_global_rows_merge",
 )
 
@@ -76,6 +76,8 @@ def _load() -> C.CDLL:
     lib.mat_sparse_attn_bwd.argtypes = [vp] * 7 + [i64, i64, i64, i64, C.c_int, spec_p, C.c_float, vp, sz, vp]
     lib.mat_sparse_attn_bwd_general.restype = C.c_int
     lib.mat_sparse_attn_bwd_general.argtypes = [vp] * 7 + [i64, i64, i64, i64, C.c_int, spec_p, vp, vp, C.c_float, vp, sz, vp]
+    lib.mat_sparse_attn_bwd_general_workspace_bytes.restype = sz
+    lib.mat_sparse_attn_bwd_general_workspace_bytes.argtypes = [i64, i64, i64, i64, C.c_int, spec_p]
     lib.mat_sparse_attn_bwd_workspace_bytes.restype = sz
     lib.mat_sparse_attn_bwd_workspace_bytes.argtypes = [i64, i64, i64]
     lib.mat_longformer_shard_fwd.restype = C.c_int

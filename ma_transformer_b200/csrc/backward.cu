@@ -316,6 +316,16 @@ size_t mat_sparse_attn_bwd_workspace_bytes(int64_t B, int64_t S, int64_t H) {
     return B > 0 && S > 0 && H > 0 ? (size_t)B * S * H * sizeof(float2) : 0;
 }
 
+size_t mat_sparse_attn_bwd_general_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t D, int dtype,
+                                                   const mat_pattern_spec *spec) {
+    size_t n = mat_sparse_attn_bwd_workspace_bytes(B, S, H);
+    if (n == 0 || !spec) return n;
+    n = (n + 255) & ~(size_t)255;
+    if (spec->kind == MAT_LONGFORMER && bwd_longformer_mma_supports(B, S, H, D, dtype, spec->n_global))
+        n += bwd_longformer_mma_extra_bytes(B, H, spec->n_global);
+    return n;
+}
+
 int mat_sparse_attn_bwd(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk,
                         void *dv, int64_t B, int64_t S, int64_t H, int64_t D, int dtype,
                         const mat_pattern_spec *spec, float scale, void *workspace, size_t workspace_bytes,
@@ -345,7 +355,7 @@ int mat_sparse_attn_bwd_general(const void *q, const void *k, const void *v, con
     }
     if (!q || !k || !v || !dout || !dq || !dk || !dv) return fail(MAT_ERR_INVALID, "tensor pointers must be non-NULL");
     if (B <= 0 || S <= 0 || H <= 0 || D <= 0) return fail(MAT_ERR_INVALID, "all tensor dimensions must be > 0");
-    const size_t need = mat_sparse_attn_bwd_workspace_bytes(B, S, H);
+    const size_t need = mat_sparse_attn_bwd_general_workspace_bytes(B, S, H, D, dtype, spec);
     if (!workspace || workspace_bytes < need || ((uintptr_t)workspace % 256) != 0)
         return fail(MAT_ERR_WORKSPACE, "workspace of %zu bytes (256-byte aligned) required, got %zu", need,
                     workspace ? workspace_bytes : (size_t)0);
@@ -370,6 +380,14 @@ int mat_sparse_attn_bwd_general(const void *q, const void *k, const void *v, con
     // the tensor-core kernels move 16-byte vectors and TMA boxes: unaligned tensors stay on the warp-level kernels
     const uintptr_t al = (uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)dout | (uintptr_t)dq | (uintptr_t)dk |
                          (uintptr_t)dv;
+    if (spec->kind == MAT_LONGFORMER && al % 16 == 0 && bwd_longformer_mma_supports(B, S, H, D, dtype, spec->n_global)) {
+        const size_t stats_bytes = (mat_sparse_attn_bwd_workspace_bytes(B, S, H) + 255) & ~(size_t)255;
+        return launch_bwd_longformer_mma(q, k, v, dout, dq, dk, dv, stats, (uint8_t *)workspace + stats_bytes, B, S, H, dtype,
+                                         a.left, a.right, spec->n_global, spec->global_idx, a.scale, st);
+    }
+    if (spec->kind == MAT_LONGFORMER && spec->n_global == 0 && al % 16 == 0 &&
+        bwd_mma_supports(B, S, H, D, dtype, a.left, a.right, 1))   // no global position: a plain window
+        return launch_bwd_mma(q, k, v, dout, dq, dk, dv, stats, B, S, H, dtype, a.left, a.right, 1, a.scale, st);
     if (spec->kind == MAT_BLOCK && al % 16 == 0 && bwd_block_mma_supports(B, S, H, D, dtype, spec->block))
         return launch_bwd_block_mma(q, k, v, dout, dq, dk, dv, stats, B, S, H, dtype, spec->block, spec->causal,
                                     spec->blk_rowptr, spec->blk_colidx, t_rowptr, t_colidx, a.scale, st);

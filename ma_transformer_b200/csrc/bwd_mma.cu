@@ -56,6 +56,20 @@ struct BwdArgs {
     int block_mode = 0, causal = 0;
     int per_blk = 1;          // 64-column chunks per layout block
     const int32_t *rowptr = nullptr, *colidx = nullptr, *t_rowptr = nullptr, *t_colidx = nullptr;
+    // Longformer (streamed kernel only; at most 64 global positions, whose Q, K, V, dO rows the launcher gathers
+    // into [B, n_global, HH, 64] tensors).  lf_mode 1, every tile: the window band plus one chunk that holds the
+    // gathered rows (the global keys in the rows pass, the global queries in the cols pass), less the positions
+    // the window already holds.  lf_mode 2, one tile per (batch, head): the gathered rows themselves against
+    // every chunk of the sequence (a global query attends every key, a global key is attended by every query);
+    // its results overwrite what the lf_mode 1 passes left for those positions.
+    int lf_mode = 0, n_global = 0;
+    const int64_t *gidx = nullptr;
+    float2 *stats_g = nullptr;   // [B, HH, 64]: the statistics of the global rows in gathered order
+};
+
+// the gathered counterparts of the four tensors
+struct LfMaps {
+    CUtensorMap q, k, v, go;
 };
 
 __device__ __forceinline__ uint32_t swz(int row, int chunk) {
@@ -76,7 +90,8 @@ __device__ __forceinline__ float quad_sum(float x) {
 // a warp's 16 x 64 fp32 accumulator tile -> its own 16 rows of a swizzled shared tile -> global, 16 bytes per lane
 template <typename T>
 __device__ __forceinline__ void store_tile(uint8_t *smem, uint32_t tile_off, const float (&o)[8][4], T *head,
-                                           int64_t row0, int64_t S, int64_t stride, int warp, int lane) {
+                                           int64_t row0, int64_t S, int64_t stride, int warp, int lane,
+                                           const int32_t *scatter = nullptr) {
     const int g = lane >> 2, t = lane & 3;
     __syncwarp();
 #pragma unroll
@@ -88,8 +103,9 @@ __device__ __forceinline__ void store_tile(uint8_t *smem, uint32_t tile_off, con
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int idx = lane + 32 * i, row = idx >> 3, chunk = idx & 7;
-        const int64_t gr = row0 + 16 * warp + row;
-        if (gr < S) {
+        // scatter: row i of the tile belongs at sequence position scatter[i] (negative: no such row)
+        const int64_t gr = scatter ? (int64_t)scatter[16 * warp + row] : row0 + 16 * warp + row;
+        if (gr >= 0 && gr < S) {
             const uint4 val = *(const uint4 *)(smem + tile_off + swz(16 * warp + row, chunk));
             *(uint4 *)(head + gr * stride + chunk * 8) = val;
         }
@@ -422,12 +438,13 @@ int launch_bwd(const BwdArgs &a, int dtype, cudaStream_t stream) {
 // while the previous chunk is being computed).  The rows pass walks it twice, once for the row statistics with a running maximum and once for
 // dQ; the cols pass walks it once.  A warp skips the 16-column groups none of its rows can see and masks only
 // the groups that straddle an edge of the window or the end of the sequence.
-constexpr int kStreamSmemBytes = 2 * 8192 + 2 * 16384 + 2 * 64 * (int)sizeof(float2) + 16;
+constexpr int kStreamSmemBytes = 2 * 8192 + 2 * 16384 + 2 * 64 * (int)sizeof(float2) + 16 + 64 * (int)sizeof(int32_t);
 
 template <typename T, bool COLS>
 __global__ void __launch_bounds__(kThreads, COLS ? 3 : 4)
 bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
-                      const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mgo, BwdArgs a) {
+                      const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mgo,
+                      const __grid_constant__ LfMaps lf, BwdArgs a) {
     extern __shared__ __align__(1024) uint8_t smem[];
     using M = ptx::Mma<T>;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
@@ -437,12 +454,17 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     const unsigned W = (unsigned)(back + fwd);
     const int64_t stride = a.HH * 64;
     const int64_t head_off = (b * a.S * a.HH + h) * 64;
-    const CUtensorMap *x1 = COLS ? &mk : &mq, *x2 = COLS ? &mv : &mgo;
+    const bool lf_tile = a.lf_mode == 2;   // the tile is the gathered global rows (queries) or keys
+    const CUtensorMap *x1 = lf_tile ? (COLS ? &lf.k : &lf.q) : (COLS ? &mk : &mq);
+    const CUtensorMap *x2 = lf_tile ? (COLS ? &lf.v : &lf.go) : (COLS ? &mv : &mgo);
     const CUtensorMap *y1 = COLS ? &mq : &mk, *y2 = COLS ? &mgo : &mv;
-    // tile rows | two stages of (band operand 1, band operand 2) | two stages of statistics | two barriers
-    constexpr uint32_t oX1 = 0, oX2 = 8192, oY = 16384, oSt = oY + 2 * 16384, oBar = oSt + 2 * 512;
+    const CUtensorMap *y1g = COLS ? &lf.q : &lf.k, *y2g = COLS ? &lf.go : &lf.v;   // lf_mode 1: the gathered chunk
+    // tile rows | two stages of (band operand 1, band operand 2) | two stages of statistics | two barriers | global positions
+    constexpr uint32_t oX1 = 0, oX2 = 8192, oY = 16384, oSt = oY + 2 * 16384, oBar = oSt + 2 * 512, oG = oBar + 16;
     const uint32_t sbase = ptx::smem_u32(smem);
     uint64_t *bar = (uint64_t *)(smem + oBar);
+    int32_t *sG = (int32_t *)(smem + oG);   // Longformer: the global positions (slots past the list: -1)
+    if (a.lf_mode != 0 && tid < 64) sG[tid] = tid < a.n_global ? (int32_t)a.gidx[tid] : -1;
     const int64_t lo = r0 - back > 0 ? r0 - back : 0;
     const int64_t hi = r0 + 63 + fwd < a.S - 1 ? r0 + 63 + fwd : a.S - 1;
     const int64_t k_first = lo / 64;
@@ -456,8 +478,11 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
         e0 = ptr[lr];
         nch = (ptr[lr + 1] - (int)e0) * a.per_blk;
     }
-    // chunk m of the walk: 64 columns starting at 64 * chunk_at(m)
+    const int nch_band = nch;
+    if (a.lf_mode == 1 && a.n_global > 0) ++nch;         // + the chunk of gathered rows
+    // chunk m of the walk: 64 columns starting at 64 * chunk_at(m); -1: the gathered chunk
     auto chunk_at = [&](int m) -> int64_t {
+        if (a.lf_mode == 1 && m >= nch_band) return -1;
         return blk ? (int64_t)blk_idx[e0 + m / a.per_blk] * a.per_blk + m % a.per_blk : k_first + m;
     };
     const int total = COLS ? nch : 2 * nch;              // the rows pass walks it twice
@@ -494,13 +519,15 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
                 ptx::tma_load_4d(smem + oX1, x1, bar, 0, (int)h, (int)r0, (int)b);
                 ptx::tma_load_4d(smem + oX2, x2, bar, 0, (int)h, (int)r0, (int)b);
             }
-            ptx::tma_load_4d(smem + oY + st * 16384, y1, bar + st, 0, (int)h, (int)(64 * k), (int)b);
-            ptx::tma_load_4d(smem + oY + st * 16384 + 8192, y2, bar + st, 0, (int)h, (int)(64 * k), (int)b);
+            ptx::tma_load_4d(smem + oY + st * 16384, k < 0 ? y1g : y1, bar + st, 0, (int)h, k < 0 ? 0 : (int)(64 * k), (int)b);
+            ptx::tma_load_4d(smem + oY + st * 16384 + 8192, k < 0 ? y2g : y2, bar + st, 0, (int)h, k < 0 ? 0 : (int)(64 * k), (int)b);
         }
         if (COLS && tid < 64) {
             const int64_t gi = 64 * k + tid;
-            ((float2 *)(smem + oSt + st * 512))[tid] =
-                gi < a.S ? a.stats[(b * a.HH + h) * a.S + gi] : make_float2(0.f, 0.f);
+            float2 sv = make_float2(0.f, 0.f);
+            if (k < 0) sv = a.stats_g[(b * a.HH + h) * 64 + tid];
+            else if (gi < a.S) sv = a.stats[(b * a.HH + h) * a.S + gi];
+            ((float2 *)(smem + oSt + st * 512))[tid] = sv;
         }
     };
     issue(0);
@@ -512,6 +539,7 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     uint32_t a1[4][4], a2[4][4];
     // group p of chunk k: 0 = none of the warp's rows sees it, 1 = every (row, column) pair is seen, 2 = mask it
     auto group_kind = [&](int64_t k, int p) -> int {
+        if (k < 0) return 16 * p < a.n_global ? 2 : 0;   // the gathered chunk: always masked (window positions, unused slots)
         const int64_t c = 64 * k + 16 * p;      // the group's first column
         if (blk) {
             // every (row, column) pair of a block counts, except past the causal diagonal (a key after its query:
@@ -529,6 +557,12 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
     };
     // column 64k + 16p + cc of row wrow + r is seen iff -back <= column - row <= fwd and the column exists
     auto seen = [&](int64_t k, int p, int cc, int r) -> bool {
+        if (k < 0) {
+            // slot 16p + cc of the gathered chunk: a global position counts unless the row's window holds it already
+            const int pos = sG[16 * p + cc];
+            const int d = pos - (int)(wrow + r);
+            return pos >= 0 && (unsigned)(d + (int)back) > W;
+        }
         const int64_t c = 64 * k + 16 * p;
         const int d = (int)(c - wrow) + cc - r;     // column - row
         if (blk) return c + cc < a.S && (!a.causal || (COLS ? d >= 0 : d <= 0));
@@ -594,7 +628,16 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
 #pragma unroll
                     for (int hh = 0; hh < 2; ++hh) {
                         const int64_t gr = wrow + g + 8 * hh;
-                        if (gr < a.S) st[gr] = make_float2(lse[hh], dsc[hh]);
+                        if (lf_tile) {
+                            // the gathered rows: their statistics go to their positions and, in gathered order, to
+                            // where the cols pass reads its chunk of global queries from
+                            const int pos = sG[gr];
+                            const float2 sv = pos >= 0 ? make_float2(lse[hh], dsc[hh]) : make_float2(0.f, 0.f);
+                            a.stats_g[(b * a.HH + h) * 64 + gr] = sv;
+                            if (pos >= 0) st[pos] = sv;
+                        } else if (gr < a.S) {
+                            st[gr] = make_float2(lse[hh], dsc[hh]);
+                        }
                     }
                 }
             }
@@ -696,11 +739,12 @@ bwd_stream_mma_kernel(const __grid_constant__ CUtensorMap mq, const __grid_const
             }
         }
     }
+    const int32_t *scatter = lf_tile ? sG : nullptr;   // the gathered tile's rows go to their positions
     if constexpr (!COLS) {
-        store_tile<T>(smem, oX1, o, (T *)a.dq + head_off, r0, a.S, stride, warp, lane);
+        store_tile<T>(smem, oX1, o, (T *)a.dq + head_off, r0, a.S, stride, warp, lane, scatter);
     } else {
-        store_tile<T>(smem, oX1, o, (T *)a.dk + head_off, r0, a.S, stride, warp, lane);
-        store_tile<T>(smem, oX2, ov, (T *)a.dv + head_off, r0, a.S, stride, warp, lane);
+        store_tile<T>(smem, oX1, o, (T *)a.dk + head_off, r0, a.S, stride, warp, lane, scatter);
+        store_tile<T>(smem, oX2, ov, (T *)a.dv + head_off, r0, a.S, stride, warp, lane, scatter);
     }
 }
 
@@ -716,11 +760,78 @@ int launch_bwd_stream(const BwdArgs &a, int dtype, cudaStream_t stream) {
     if ((rc = make_row_tensor_map(&mv, a.v, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
     if ((rc = make_row_tensor_map(&mgo, a.go, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
     const dim3 grid((unsigned)a.HH, (unsigned)((a.S + kTile - 1) / kTile), (unsigned)a.B);
-    bwd_stream_mma_kernel<T, false><<<grid, kThreads, kStreamSmemBytes, stream>>>(mq, mk, mv, mgo, a);
-    bwd_stream_mma_kernel<T, true><<<grid, kThreads, kStreamSmemBytes, stream>>>(mq, mk, mv, mgo, a);
+    LfMaps lf;
+    lf.q = mq; lf.k = mk; lf.v = mv; lf.go = mgo;   // unused outside the Longformer modes
+    bwd_stream_mma_kernel<T, false><<<grid, kThreads, kStreamSmemBytes, stream>>>(mq, mk, mv, mgo, lf, a);
+    bwd_stream_mma_kernel<T, true><<<grid, kThreads, kStreamSmemBytes, stream>>>(mq, mk, mv, mgo, lf, a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "tensor-core backward launch");
     note_kernel(a.block_mode ? "bwd_block_mma" : "bwd_stream_mma");
+    return MAT_OK;
+}
+
+// rows of four [B, S, HH, 64] tensors at the global positions -> four [B, n_global, HH, 64] tensors;
+// grid = (global position, batch), threads stride over the HH * 8 16-byte pieces of a row set
+__global__ void gather4_kernel(const uint4 *__restrict__ s0, const uint4 *__restrict__ s1, const uint4 *__restrict__ s2,
+                               const uint4 *__restrict__ s3, uint4 *__restrict__ d0, uint4 *__restrict__ d1,
+                               uint4 *__restrict__ d2, uint4 *__restrict__ d3, const int64_t *__restrict__ gidx,
+                               int n_global, int64_t S, int64_t HH) {
+    const int e = blockIdx.x, b = blockIdx.y;
+    const int64_t row = gidx[e];
+    const bool in = row >= 0 && row < S;   // a position outside the sequence gathers zeros, never memory
+    const int64_t src = ((int64_t)b * S + (in ? row : 0)) * HH * 8, dst = ((int64_t)b * n_global + e) * HH * 8;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int64_t i = threadIdx.x; i < HH * 8; i += blockDim.x) {
+        d0[dst + i] = in ? s0[src + i] : zero;
+        d1[dst + i] = in ? s1[src + i] : zero;
+        d2[dst + i] = in ? s2[src + i] : zero;
+        d3[dst + i] = in ? s3[src + i] : zero;
+    }
+}
+
+size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+// Longformer on the streamed kernels: gather, rows pass over every tile (window band + the chunk of global keys),
+// rows pass over the gathered global queries (every key), cols pass over every tile (mirrored band + the chunk of
+// global queries), cols pass over the gathered global keys (every query).  The two gathered passes overwrite what
+// the tile passes left at the global positions.
+template <typename T>
+int launch_bwd_longformer(BwdArgs a, int dtype, void *extra_ws, cudaStream_t stream) {
+    int rc = ensure_dynamic_smem((const void *)bwd_stream_mma_kernel<T, false>, kStreamSmemBytes, "bwd_stream_mma rows");
+    if (rc != MAT_OK) return rc;
+    rc = ensure_dynamic_smem((const void *)bwd_stream_mma_kernel<T, true>, kStreamSmemBytes, "bwd_stream_mma cols");
+    if (rc != MAT_OK) return rc;
+    const size_t gbytes = align256((size_t)a.B * a.n_global * a.HH * 128);
+    uint8_t *w = (uint8_t *)extra_ws;
+    a.stats_g = (float2 *)w;
+    w += align256((size_t)a.B * a.HH * 64 * sizeof(float2));
+    void *qg = w, *kg = w + gbytes, *vg = w + 2 * gbytes, *gog = w + 3 * gbytes;
+    gather4_kernel<<<dim3((unsigned)a.n_global, (unsigned)a.B), 128, 0, stream>>>(
+        (const uint4 *)a.q, (const uint4 *)a.k, (const uint4 *)a.v, (const uint4 *)a.go, (uint4 *)qg, (uint4 *)kg,
+        (uint4 *)vg, (uint4 *)gog, a.gidx, a.n_global, a.S, a.HH);
+    CUtensorMap mq, mk, mv, mgo;
+    LfMaps lf;
+    if ((rc = make_row_tensor_map(&mq, a.q, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
+    if ((rc = make_row_tensor_map(&mk, a.k, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
+    if ((rc = make_row_tensor_map(&mv, a.v, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
+    if ((rc = make_row_tensor_map(&mgo, a.go, dtype, a.HH, a.S, a.B, kTile)) != MAT_OK) return rc;
+    if ((rc = make_row_tensor_map(&lf.q, qg, dtype, a.HH, a.n_global, a.B, kTile)) != MAT_OK) return rc;
+    if ((rc = make_row_tensor_map(&lf.k, kg, dtype, a.HH, a.n_global, a.B, kTile)) != MAT_OK) return rc;
+    if ((rc = make_row_tensor_map(&lf.v, vg, dtype, a.HH, a.n_global, a.B, kTile)) != MAT_OK) return rc;
+    if ((rc = make_row_tensor_map(&lf.go, gog, dtype, a.HH, a.n_global, a.B, kTile)) != MAT_OK) return rc;
+    const dim3 grid((unsigned)a.HH, (unsigned)((a.S + kTile - 1) / kTile), (unsigned)a.B);
+    const dim3 grid_g((unsigned)a.HH, 1, (unsigned)a.B);
+    BwdArgs tiles = a, rows_g = a;
+    tiles.lf_mode = 1;
+    rows_g.lf_mode = 2;
+    rows_g.left = rows_g.right = (int)a.S;   // the gathered rows against every chunk
+    bwd_stream_mma_kernel<T, false><<<grid, kThreads, kStreamSmemBytes, stream>>>(mq, mk, mv, mgo, lf, tiles);
+    bwd_stream_mma_kernel<T, false><<<grid_g, kThreads, kStreamSmemBytes, stream>>>(mq, mk, mv, mgo, lf, rows_g);
+    bwd_stream_mma_kernel<T, true><<<grid, kThreads, kStreamSmemBytes, stream>>>(mq, mk, mv, mgo, lf, tiles);
+    bwd_stream_mma_kernel<T, true><<<grid_g, kThreads, kStreamSmemBytes, stream>>>(mq, mk, mv, mgo, lf, rows_g);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "tensor-core Longformer backward launch");
+    note_kernel("bwd_longformer_mma");
     return MAT_OK;
 }
 
@@ -774,6 +885,41 @@ int launch_bwd_mma(const void *q, const void *k, const void *v, const void *dout
     if (a.left + a.right <= 128)
         return dtype == MAT_BF16 ? launch_bwd<__nv_bfloat16, 9>(a, dtype, stream) : launch_bwd<__half, 9>(a, dtype, stream);
     return dtype == MAT_BF16 ? launch_bwd_stream<__nv_bfloat16>(a, dtype, stream) : launch_bwd_stream<__half>(a, dtype, stream);
+}
+
+// The Longformer pattern on the streamed tensor-core kernels: 16-bit, D = 64, 1 to 64 global positions.
+bool bwd_longformer_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t n_global) {
+    if (dtype != MAT_BF16 && dtype != MAT_F16) return false;
+    if (D != 64 || n_global < 1 || n_global > 64 || S >= (1LL << 30)) return false;
+    const char *env = getenv("MAT_BWD_KERNEL");
+    if (env && strcmp(env, "warp") == 0) return false;
+    return H < (1LL << 31) && (S + kTile - 1) / kTile <= 65535 && B <= 65535;
+}
+
+// bytes behind the per-row statistics: the global rows' statistics and the four gathered tensors
+size_t bwd_longformer_mma_extra_bytes(int64_t B, int64_t H, int64_t n_global) {
+    return align256((size_t)B * H * 64 * sizeof(float2)) + 4 * align256((size_t)B * n_global * H * 128);
+}
+
+int launch_bwd_longformer_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk,
+                              void *dv, float2 *stats, void *extra_ws, int64_t B, int64_t S, int64_t H, int dtype,
+                              int64_t left, int64_t right, int64_t n_global, const int64_t *gidx, float scale,
+                              cudaStream_t stream) {
+    BwdArgs a;
+    a.q = q; a.k = k; a.v = v; a.go = dout;
+    a.dq = dq; a.dk = dk; a.dv = dv;
+    a.stats = stats;
+    a.B = B; a.S = S; a.HH = H;
+    a.left = (int)(left < S - 1 ? left : S - 1);
+    a.right = (int)(right < S - 1 ? right : S - 1);
+    if (a.left < 0) a.left = 0;
+    if (a.right < 0) a.right = 0;
+    a.scale = scale;
+    a.prefetch_ahead = 0;
+    a.n_global = (int)n_global;
+    a.gidx = gidx;
+    return dtype == MAT_BF16 ? launch_bwd_longformer<__nv_bfloat16>(a, dtype, extra_ws, stream)
+                             : launch_bwd_longformer<__half>(a, dtype, extra_ws, stream);
 }
 
 // Block layouts on the streamed tensor-core kernels: 16-bit, D = 64, block a multiple of 64, both the layout and

@@ -288,7 +288,8 @@ def backward_pattern(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor
     dq, dk, dv = torch.empty_like(query), torch.empty_like(key), torch.empty_like(value)
     with torch.cuda.device(query.device):
         s = spec.device_struct(query.device)
-        ws = _workspace(query.device, nat.lib.mat_sparse_attn_bwd_workspace_bytes(B, S, H))
+        ws = _workspace(query.device, nat.lib.mat_sparse_attn_bwd_general_workspace_bytes(
+            B, S, H, D, _DTYPES[query.dtype], C.byref(s)))
         stream = torch.cuda.current_stream(query.device).cuda_stream
         t_rp = t_ci = None
         if spec.kind == BLOCK:   # the dK / dV pass walks the transposed layout

@@ -736,6 +736,8 @@ def _general_backward_cases():
         ("longformer", PatternSpec.longformer(8, 8, [0, 17, 100, 199]), 200),
         ("longformer-lopsided", PatternSpec.longformer(20, 3, [5, 6, 7, 150]), 211),
         ("longformer-no-globals", PatternSpec.longformer(4, 0, []), 70),
+        ("longformer-cfg4-like", PatternSpec.longformer(64, 64, list(range(3, 600, 19))), 600),   # 32 globals, several tiles
+        ("longformer-70-globals", PatternSpec.longformer(5, 5, list(range(0, 140, 2))), 150),     # more than one chunk holds
     ]
 
 
@@ -751,8 +753,14 @@ def test_backward_of_block_layouts_and_longformer_against_fp64_autograd(monkeypa
     got = ext.backward_pattern(q.to(DEV), k.to(DEV), v.to(DEV), go.to(DEV), spec)
     torch.cuda.synchronize()
     # block layouts whose blocks are multiples of 64 run on the streamed tensor-core kernels (16-bit, D = 64)
-    on_mma = spec.kind == 1 and spec.block % 64 == 0 and dtype != torch.float32 and D == 64
-    assert nat.last_kernel() == ("bwd_block_mma" if on_mma else "bwd_general") and nat.device_status() == 0
+    # and so does the Longformer pattern with 1 to 64 global positions (none: a plain window)
+    n_glob = len(spec.global_idx) if spec.kind == 2 else 0
+    sixteen = dtype != torch.float32 and D == 64
+    on_mma = sixteen and ((spec.kind == 1 and spec.block % 64 == 0) or (spec.kind == 2 and n_glob <= 64))
+    want_kernel = "bwd_general"
+    if on_mma:
+        want_kernel = "bwd_block_mma" if spec.kind == 1 else ("bwd_longformer_mma" if n_glob else "bwd_window_mma")
+    assert nat.last_kernel() == want_kernel and nat.device_status() == 0
     keep = pattern_mask(spec, S)
     ref = [t.double().requires_grad_(True) for t in (q, k, v)]
     masked_attention_with(*ref, keep).backward(go.double())
