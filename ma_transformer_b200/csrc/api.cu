@@ -132,6 +132,7 @@ int run_problem(const Problem &p) {
         return launch_mma_flash(p);
     }
     if (mma_window_d_supports(p)) return launch_mma_window_d(p);
+    if (mma_window_f32_supports(p)) return launch_mma_window_f32(p);
     if (tiled_f32_supports(p)) return launch_tiled_f32(p);
     return launch_rowwarp(p);
 }

@@ -1,0 +1,284 @@
+// fp32 window attention on the tensor cores at fp32 accuracy: every product is evaluated as three TF32
+// products of error-compensated halves (x = hi + lo with hi = x rounded to TF32 and lo = x - hi, exact in fp32;
+// a * b ~ a_lo b_hi + a_hi b_lo + a_hi b_hi, the missing a_lo b_lo being 2^-22 of the product), accumulated in
+// fp32 by mma.sync.m16n8k8.  The reference computes in fp32 (src/csrc/ma_core.cpp:195-240 and the CUDA
+// kernel src/cuda/sparse_attention_kernel.cu:211-263), and fp32 is what an unmodified caller of its module
+// passes; the parity bar for it (max |gpu - oracle| / max |oracle| <= 1e-5) rules out plain TF32 or 16-bit
+// operands but not this.  The FMA-pipe kernel (tiled_f32.cu) needs one FMA per multiply-add of the band; here
+// the tensor pipe does three m16n8k8 per 1024 of them.
+//
+// Same shape as the 16-bit kernel for other head widths (mma_window_d.cu): one CTA = 64 query rows of one
+// (batch, head), four warps of 16 rows, the keys the tile can see walked 64 at a time through two cp.async
+// buffers, online softmax in registers.  Operands are read from shared memory as scalars (rows padded by four
+// floats, which makes both the K and the V fragment loads conflict-free).  The key order inside an 8-key step of
+// P V is chosen so that a thread's A fragment is exactly the four weights it already holds (virtual key t is
+// key 2t of the step, virtual key t + 4 is key 2t + 1): no shuffles between the two products.
+#include <algorithm>
+#include <cstring>
+
+#include "mat_common.cuh"
+#include "ptx.cuh"
+
+namespace mat {
+namespace {
+
+constexpr int kTQ = 64, kTK = 64, kThreads = 128;
+
+struct WinFParams {
+    int32_t Sq1, Skv1, off1;   // query rows, key rows, q_offset of one sub-sequence
+    int32_t HH;                // heads of the view
+    int32_t left, right;
+    float sl2;                 // scale * log2(e)
+};
+
+__device__ __forceinline__ void cp_async16(void *dst, const void *src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ptx::smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// d += a b, TF32 operands (the low 13 mantissa bits of the 32-bit operands are not used), fp32 accumulation
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// x = hi + lo.  ROUND = true: hi is x rounded to TF32 (to nearest, by adding half a TF32 ulp to the bit pattern
+// and cutting), lo the rest (exact).  A cut hi leaves a lo of x's own sign, and the tensor core cuts lo in turn,
+// so every product errs the same way.
+// ROUND = false: hi is x itself (the tensor core cuts the low 13 bits) and lo = x - cut(x): two operations instead
+// of three per element and no register for hi, 15 % faster, errors up to 5e-6 on a 1000-key row against 2.5e-6;
+// used for windows of at most 512 taps, where the sums are short.
+template <bool ROUND>
+__device__ __forceinline__ void split_tf32(uint32_t x, uint32_t &hi, uint32_t &lo) {
+    if (ROUND) {
+        hi = (x + 0x1000u) & 0xffffe000u;
+        lo = __float_as_uint(__uint_as_float(x) - __uint_as_float(hi));
+    } else {
+        hi = x;
+        lo = __float_as_uint(__uint_as_float(x) - __uint_as_float(x & 0xffffe000u));
+    }
+}
+// d += a b at fp32 accuracy from the halves of a and the raw b
+template <bool ROUND>
+__device__ __forceinline__ void mma_3x(float (&d)[4], const uint32_t (&a_hi)[4], const uint32_t (&a_lo)[4], uint32_t b0,
+                                       uint32_t b1) {
+    uint32_t h0, l0, h1, l1;
+    split_tf32<ROUND>(b0, h0, l0);
+    split_tf32<ROUND>(b1, h1, l1);
+    mma_tf32(d, a_lo, h0, h1);
+    mma_tf32(d, a_hi, l0, l1);
+    mma_tf32(d, a_hi, h0, h1);
+}
+
+template <int D, bool ROUND>
+__global__ void __launch_bounds__(kThreads)
+window_f32_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                  float *__restrict__ o, const WinFParams P) {
+    constexpr int LD = D + 4;          // padded row, floats
+    constexpr int KS = D / 8;          // k-steps of S = Q K^T; 8-wide output tiles of O
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    float *sK = reinterpret_cast<float *>(smem_raw);   // [2][kTK][LD]
+    float *sV = sK + 2 * kTK * LD;                     // [2][kTK][LD]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int hh = blockIdx.x, b = blockIdx.z, q0 = blockIdx.y * kTQ;
+    const int p_first = q0 + P.off1;   // key-coordinate position of the tile's first row
+    const int last_row = min(q0 + kTQ, P.Sq1) - 1;
+    const int key_lo = max(0, p_first - P.left);
+    const int key_hi = min(P.Skv1 - 1, last_row + P.off1 + P.right);
+    const int n_chunks = key_hi >= key_lo ? (key_hi - key_lo) / kTK + 1 : 0;
+    const int64_t tok = (int64_t)P.HH * D;   // elements per token
+    const float *kb_ptr = k + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+    const float *vb_ptr = v + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+
+    auto load_chunk = [&](int c, int buf) {
+        constexpr int kPieces = D / 4;   // 16-byte pieces per row
+        const int base = key_lo + c * kTK;
+        for (int i = threadIdx.x; i < kTK * kPieces; i += kThreads) {
+            const int r = i / kPieces, pc = i % kPieces;
+            const int j = base + r;
+            const bool in = j < P.Skv1;   // rows past the sequence end are zero-filled: a masked weight never meets stale memory
+            const int64_t src = (int64_t)(in ? j : 0) * tok + pc * 4;
+            cp_async16(sK + (buf * kTK + r) * LD + pc * 4, kb_ptr + src, in ? 16 : 0);
+            cp_async16(sV + (buf * kTK + r) * LD + pc * 4, vb_ptr + src, in ? 16 : 0);
+        }
+    };
+    if (n_chunks > 0) load_chunk(0, 0);
+    cp_async_commit();
+
+    // the warp's 16 query rows as A fragments: thread (g, t) holds rows g and g + 8, columns t and t + 4 of each 8
+    const int row_a = q0 + warp * 16 + g, row_b = row_a + 8;
+    uint32_t qf[KS][4];
+    {
+        const float *qa = q + (((int64_t)b * P.Sq1 + row_a) * P.HH + hh) * D;
+        const float *qb = q + (((int64_t)b * P.Sq1 + row_b) * P.HH + hh) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int c = ks * 8 + t;
+            qf[ks][0] = row_a < P.Sq1 ? __float_as_uint(qa[c]) : 0u;
+            qf[ks][1] = row_b < P.Sq1 ? __float_as_uint(qb[c]) : 0u;
+            qf[ks][2] = row_a < P.Sq1 ? __float_as_uint(qa[c + 4]) : 0u;
+            qf[ks][3] = row_b < P.Sq1 ? __float_as_uint(qb[c + 4]) : 0u;
+        }
+    }
+    const int pos[2] = {row_a + P.off1, row_b + P.off1};
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float acc[KS][4];
+#pragma unroll
+    for (int n = 0; n < KS; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+
+    for (int c = 0; c < n_chunks; ++c) {
+        const int buf = c & 1;
+        if (c + 1 < n_chunks) {
+            load_chunk(c + 1, buf ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int kb = key_lo + c * kTK;
+        const uint32_t *ck = reinterpret_cast<const uint32_t *>(sK + buf * kTK * LD);
+        const uint32_t *cv = reinterpret_cast<const uint32_t *>(sV + buf * kTK * LD);
+
+        // ---- S = Q K^T: eight 8-key tiles per warp ----
+        float s[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            uint32_t q_hi[4], q_lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) split_tf32<ROUND>(qf[ks][e], q_hi[e], q_lo[e]);
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                // B = K^T: element (k = dim, n = key): b0 = K[key g][dim t], b1 = K[key g][dim t + 4] of the step
+                const uint32_t *kr = ck + (n * 8 + g) * LD + ks * 8 + t;
+                mma_3x<ROUND>(s[n], q_hi, q_lo, kr[0], kr[4]);
+            }
+        }
+        // ---- mask, online softmax (raw scores; the scale enters the exponent) ----
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = kb + n * 8 + 2 * t + (e & 1), p = pos[e >> 1];
+                const bool ok = j >= p - P.left && j <= p + P.right && j < P.Skv1;
+                s[n][e] = ok ? s[n][e] : -INFINITY;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+            }
+        float alpha[2], mus[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float m_new = fmaxf(m_run[i], mx[i]);
+            alpha[i] = m_new == -INFINITY ? 1.f : ptx::ex2((m_run[i] - m_new) * P.sl2);
+            m_run[i] = m_new;
+            mus[i] = m_new == -INFINITY ? 0.f : m_new * P.sl2;
+            l_run[i] *= alpha[i];
+        }
+        // ---- the chunk's P V, one 8-key step per score tile, into accumulators of its own ----
+        // (The tensor core does not round its fp32 sums to nearest, so a long chain of accumulating MMAs drifts:
+        // 9e-6 relative on a 1000-key row with one chain per output tile.  The chains end with the chunk; the
+        // chunks are combined by ordinary FMAs, which is also where the running maximum's rescale goes.)
+        float part[KS][4];
+#pragma unroll
+        for (int n = 0; n < KS; ++n) part[n][0] = part[n][1] = part[n][2] = part[n][3] = 0.f;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            float w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                w[e] = ptx::ex2(fmaf(s[n][e], P.sl2, -mus[e >> 1]));
+                l_run[e >> 1] += w[e];
+            }
+            // A fragment in the step's own key order (virtual key t = key 2t, virtual key t + 4 = key 2t + 1):
+            // rows g and g + 8 at virtual keys t and t + 4 are the four weights this thread holds
+            const uint32_t pa[4] = {__float_as_uint(w[0]), __float_as_uint(w[2]), __float_as_uint(w[1]), __float_as_uint(w[3])};
+            uint32_t p_hi[4], p_lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) split_tf32<ROUND>(pa[e], p_hi[e], p_lo[e]);
+            const uint32_t *vr = cv + (n * 8 + 2 * t) * LD + g;
+#pragma unroll
+            for (int d = 0; d < KS; ++d)   // B: element (k = virtual key, n = dim): rows 2t and 2t + 1 of the step
+                mma_3x<ROUND>(part[d], p_hi, p_lo, vr[d * 8], vr[LD + d * 8]);
+        }
+#pragma unroll
+        for (int n = 0; n < KS; ++n) {
+            acc[n][0] = fmaf(acc[n][0], alpha[0], part[n][0]);
+            acc[n][1] = fmaf(acc[n][1], alpha[0], part[n][1]);
+            acc[n][2] = fmaf(acc[n][2], alpha[1], part[n][2]);
+            acc[n][3] = fmaf(acc[n][3], alpha[1], part[n][3]);
+        }
+        __syncthreads();   // the buffer is free for the chunk after the next
+    }
+
+    // ---- normalise and write the two rows of this thread ----
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float l = l_run[i];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const int row = i == 0 ? row_a : row_b;
+        if (row < P.Sq1) {
+            float *dst = o + (((int64_t)b * P.Sq1 + row) * P.HH + hh) * D + 2 * t;
+#pragma unroll
+            for (int n = 0; n < KS; ++n)
+                *reinterpret_cast<float2 *>(dst + n * 8) = make_float2(acc[n][2 * i] * inv, acc[n][2 * i + 1] * inv);
+        }
+    }
+}
+
+template <int D, bool ROUND>
+int launch_f(const Problem &p) {
+    const int64_t dil = p.pat.dilation;
+    WinFParams wp;
+    wp.Sq1 = (int32_t)(p.Sq / dil);
+    wp.Skv1 = (int32_t)(p.Skv / dil);
+    wp.off1 = (int32_t)(p.pat.q_offset / dil);
+    wp.HH = (int32_t)(p.H * dil);
+    wp.left = (int32_t)std::min<int64_t>(p.pat.left, wp.Skv1);
+    wp.right = (int32_t)std::min<int64_t>(p.pat.right, wp.Skv1);
+    wp.sl2 = p.scale * 1.4426950408889634f;
+    auto kern = window_f32_kernel<D, ROUND>;
+    constexpr size_t smem = (size_t)4 * kTK * (D + 4) * sizeof(float);
+    if (int rc = ensure_dynamic_smem((const void *)kern, smem, "cudaFuncSetAttribute(window_f32_kernel)")) return rc;
+    const dim3 grid((unsigned)wp.HH, (unsigned)((wp.Sq1 + kTQ - 1) / kTQ), (unsigned)p.B);
+    kern<<<grid, kThreads, smem, p.stream>>>((const float *)p.q, (const float *)p.k, (const float *)p.v, (float *)p.o, wp);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "window_f32_kernel launch");
+    note_kernel("mma_window_f32");
+    return MAT_OK;
+}
+
+}  // namespace
+
+// fp32 window patterns (any taps, any dilation that divides the lengths) with head width 32 or 64, whole tensors,
+// 16-byte aligned.  MAT_F32_KERNEL=tiled keeps them on the FMA-pipe kernel (a measurement aid).
+bool mma_window_f32_supports(const Problem &p) {
+    if (p.pat.kind != MAT_WINDOW || p.dtype != MAT_F32) return false;
+    if (p.D != 32 && p.D != 64) return false;
+    if (p.k_prev || p.k_next || p.q_ts || p.k_ts || p.v_ts || p.o_ts) return false;
+    const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
+    if (al % 16) return false;
+    const int64_t dil = p.pat.dilation;
+    if (dil < 1 || p.Sq % dil || p.Skv % dil || p.pat.q_offset % dil) return false;
+    if (p.Skv / dil >= (1LL << 30) || p.Sq / dil >= (1LL << 30) || p.H * dil > 0x7fffffffLL || p.B > 65535) return false;
+    if ((p.Sq / dil + kTQ - 1) / kTQ > 65535) return false;
+    const char *force = std::getenv("MAT_F32_KERNEL");
+    return !(force && std::strcmp(force, "tiled") == 0);
+}
+
+int launch_mma_window_f32(const Problem &p) {
+    const int64_t dil = p.pat.dilation, skv1 = p.Skv / dil;
+    const bool wide = std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) > 512;
+    if (wide) return p.D == 32 ? launch_f<32, true>(p) : launch_f<64, true>(p);
+    return p.D == 32 ? launch_f<32, false>(p) : launch_f<64, false>(p);
+}
+
+}  // namespace mat

@@ -19,7 +19,7 @@ def test_orderbook_forward_matches_fp32_reference():
     with torch.no_grad():
         want = reference_forward(model, ticks)
         got32 = model.cuda()(ticks.cuda())
-        assert nat.last_kernel() == "tiled_f32"                                 # fp32: the tiled fp32 kernel
+        assert nat.last_kernel() == "mma_window_f32"                            # fp32: three TF32 products per product
         got16 = model.to(torch.bfloat16)(ticks.cuda().to(torch.bfloat16))
         assert nat.last_kernel() == "umma_band"                                 # bf16: the tcgen05 band kernel
     assert got32.shape == (2, 3)

@@ -45,7 +45,7 @@ def test_cfg1_causal_window_fp32():
     spec = PatternSpec.causal_window(32)
     q, k, v = seeded_qkv(1, 1, 1024, 4, 64)
     check_close(run(spec, q, k, v), oracle_out(q, k, v, spec), torch.float32)
-    assert nat.last_kernel() == "tiled_f32"
+    assert nat.last_kernel() == "mma_window_f32"
     check_close(run(spec, q, k, v, scale=0.125), oracle_out(q, k, v, spec, 0.125), torch.float32)
 
 
@@ -54,9 +54,14 @@ def test_cfg1_causal_window_fp32():
                                   PatternSpec(left=0, right=60), PatternSpec.causal_window(64, dilation=2),
                                   PatternSpec(left=100, right=28), PatternSpec.causal_window(1)],
                          ids=lambda s: f"l{s.left}r{s.right}d{s.dilation}")
-def test_tiled_fp32_kernel_vs_oracle(spec, D):
-    """fp32 windows of at most 128 taps with head width 32, 64 or 128 on the tiled kernel (64- or 128-row tiles,
-    K/V window staged once per tile), ragged lengths and shard offsets included; fp32 bar 1e-5."""
+@pytest.mark.parametrize("kernel", ["default", "tiled"])
+def test_fp32_window_kernels_vs_oracle(monkeypatch, kernel, spec, D):
+    """fp32 windows of at most 128 taps with head width 32, 64 or 128, ragged lengths and shard offsets included,
+    at the fp32 bar of 1e-5: on the tensor cores as three TF32 products of error-compensated halves (head widths 32
+    and 64: the default), and on the tiled FMA-pipe kernel (64- or 128-row tiles, K/V window staged once per tile;
+    head width 128, and MAT_F32_KERNEL=tiled)."""
+    if kernel == "tiled":
+        monkeypatch.setenv("MAT_F32_KERNEL", "tiled")
     for B, S, H, off in [(1, 1024, 2, 0), (2, 330, 3, 0), (1, 64, 1, 0), (1, 200, 2, 48), (1, 7, 1, 0)]:
         S = S - S % spec.dilation if S >= spec.dilation else spec.dilation
         off = off - off % spec.dilation
@@ -65,12 +70,30 @@ def test_tiled_fp32_kernel_vs_oracle(spec, D):
         got = run(sp, q, k, v)
         skv1 = (S + off + 3 * spec.dilation) // spec.dilation          # taps clamp to the keys that exist
         wide_here = min(spec.left, skv1) + min(spec.right, skv1) > 64
-        assert nat.last_kernel() == ("rowwarp" if D == 128 and wide_here else "tiled_f32")
+        if kernel == "default" and D != 128:
+            assert nat.last_kernel() == "mma_window_f32"
+        else:
+            assert nat.last_kernel() == ("rowwarp" if D == 128 and wide_here else "tiled_f32")
         check_close(got, oracle_out(q, k, v, sp), torch.float32)
     # inputs x100 stay finite and close (tests/integration/test_cuda_extensive.py:77-92)
     q, k, v = seeded_qkv(24, 1, 130, 2, D, torch.float32, scale=100.0)
     got = run(spec, q, k, v).cpu().numpy()
     assert np.isfinite(got).all() and np.abs(got - oracle_out(q, k, v, spec)).max() <= 0.5
+
+
+@pytest.mark.parametrize("S,spec", [(1000, PatternSpec.sliding_window(3000)), (1000, PatternSpec.causal_window(3000)),
+                                    (1500, PatternSpec.sliding_window(400)), (2100, PatternSpec(left=513, right=0)),
+                                    (4096, PatternSpec.sliding_window(4096))],
+                         ids=["dense1000", "causal1000", "pm400", "l513", "dense4096"])
+@pytest.mark.parametrize("D", [32, 64])
+def test_fp32_wide_windows_on_tensor_cores(S, spec, D):
+    """fp32 windows of any width, dense and causal dense included, as three TF32 products per product: the fp32 bar
+    holds on rows of thousands of keys (the sums of a chunk end with the chunk, and chunks are combined by
+    ordinary FMAs: the tensor core's own fp32 accumulation does not round to nearest)."""
+    q, k, v = seeded_qkv(31, 1, S, 2, D, torch.float32)
+    got = run(spec, q, k, v)
+    assert nat.last_kernel() == "mma_window_f32"
+    check_close(got, oracle_out(q, k, v, spec), torch.float32)
 
 
 @pytest.mark.parametrize("D", [16, 32, 48, 80, 96, 112, 128])
