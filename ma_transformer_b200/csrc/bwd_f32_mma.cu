@@ -1,0 +1,330 @@
+// fp32 backward of window attention on the tensor cores at fp32 accuracy.
+//
+// The reference computes its backward in fp32 (sparse_attention_backward_kernel,
+// src/cuda/sparse_attention_kernel.cu:265-346; dense: 104-208), and fp32 is what an unmodified caller of
+// its module trains in.  The warp-level kernels of backward.cu hold that accuracy but run one warp per row
+// (55 ms at 65536 tokens x 8 heads x 64 taps); the 16-bit tensor-core kernels of bwd_mma.cu do not take
+// fp32.  Here every product is three TF32 products of error-compensated halves, as in the forward
+// (mma_window_f32.cu), with the same shape: 64-row tiles, four warps of 16 rows, the band walked in 64-column
+// chunks through two cp.async buffers, scalar fragment loads from rows padded by four floats, and the
+// accumulator layout of one product reused as the A operand of the next by ordering the 8 columns of a step
+// as (0, 2, 4, 6, 1, 3, 5, 7).  An accumulating chain of MMAs ends with each chunk (the tensor core's fp32
+// sums are not rounded to nearest); chunks are combined by ordinary additions.
+//
+// Three launches, no atomics, deterministic:
+//   rows pass   one CTA per 64 queries, two sweeps over the keys they see: S = Q K^T and dP = dO V^T give the
+//               row statistics (log2-sum-exp, delta * scale; left in the workspace), then dS and dQ = dS K.
+//   dV pass     one CTA per 64 keys over the queries that see them: P^T from the statistics, dV = P^T dO.
+//   dK pass     the same walk with dP^T = V dO^T: dS^T, dK = dS^T Q.
+// (dK and dV in one launch would need both accumulators, their per-chunk partials and both operand tiles in
+// registers at once.)
+#include <algorithm>
+#include <cstring>
+
+#include "mat_common.cuh"
+#include "ptx.cuh"
+
+namespace mat {
+namespace {
+
+constexpr int kT = 64, kThreads = 128;
+
+struct BwdFArgs {
+    const float *q, *k, *v, *go;
+    float *dq, *dk, *dv;
+    float2 *stats;             // [B, HH, S]: (log2-sum-exp of the scaled scores, delta * scale)
+    int32_t S, HH;             // rows and heads of the (possibly dilated) view
+    int32_t left, right;
+    float scale;
+};
+
+__device__ __forceinline__ void cp_async16(void *dst, const void *src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ptx::smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// x = hi + lo, hi = x rounded to TF32 (half a TF32 ulp added to the bit pattern, then cut), lo exact
+__device__ __forceinline__ void split_tf32(uint32_t x, uint32_t &hi, uint32_t &lo) {
+    hi = (x + 0x1000u) & 0xffffe000u;
+    lo = __float_as_uint(__uint_as_float(x) - __uint_as_float(hi));
+}
+// d += a b at fp32 accuracy from the halves of a and the raw b
+__device__ __forceinline__ void mma_3x(float (&d)[4], const uint32_t (&a_hi)[4], const uint32_t (&a_lo)[4], uint32_t b0,
+                                       uint32_t b1) {
+    uint32_t h0, l0, h1, l1;
+    split_tf32(b0, h0, l0);
+    split_tf32(b1, h1, l1);
+    mma_tf32(d, a_lo, h0, h1);
+    mma_tf32(d, a_hi, l0, l1);
+    mma_tf32(d, a_hi, h0, h1);
+}
+__device__ __forceinline__ float quad_max(float x) {
+    x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 1));
+    return fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 2));
+}
+__device__ __forceinline__ float quad_sum(float x) {
+    x += __shfl_xor_sync(0xffffffffu, x, 1);
+    return x + __shfl_xor_sync(0xffffffffu, x, 2);
+}
+
+constexpr int kRows = 0, kColsV = 1, kColsK = 2;
+
+// PASS = kRows: tile rows are queries, columns keys.  kColsV / kColsK: tile rows are keys, columns queries.
+template <int D, int PASS>
+__global__ void __launch_bounds__(kThreads)
+bwd_f32_kernel(const BwdFArgs a) {
+    constexpr int LD = D + 4, KS = D / 8;
+    constexpr bool COLS = PASS != kRows;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    float *sY1 = reinterpret_cast<float *>(smem_raw);   // [2][kT][LD]: rows pass K, cols passes Q
+    float *sY2 = sY1 + 2 * kT * LD;                     // [2][kT][LD]: rows pass V, cols passes dO
+    float2 *sSt = reinterpret_cast<float2 *>(sY2 + 2 * kT * LD);   // cols passes: [2][kT] statistics of a chunk's queries
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int hh = blockIdx.x, b = blockIdx.z, r0 = blockIdx.y * kT;
+    const int back = COLS ? a.right : a.left, fwd = COLS ? a.left : a.right;   // row r sees columns r - back .. r + fwd
+    const int col_lo = max(0, r0 - back);
+    const int col_hi = min(a.S - 1, min(r0 + kT, a.S) - 1 + fwd);
+    const int n_chunks = col_hi >= col_lo ? (col_hi - col_lo) / kT + 1 : 0;
+    const int64_t tok = (int64_t)a.HH * D;
+    const int64_t head = ((int64_t)b * a.S * a.HH + hh) * D;
+    const float *x1 = (COLS ? a.k : a.q) + head, *x2 = (COLS ? a.v : a.go) + head;
+    const float *y1 = (COLS ? a.q : a.k) + head, *y2 = (COLS ? a.go : a.v) + head;
+    const float2 *st_in = a.stats + ((int64_t)b * a.HH + hh) * a.S;
+
+    auto load_chunk = [&](int c, int buf) {
+        constexpr int kPieces = D / 4;
+        const int base = col_lo + c * kT;
+        for (int i = threadIdx.x; i < kT * kPieces; i += kThreads) {
+            const int r = i / kPieces, pc = i % kPieces;
+            const int j = base + r;
+            const bool in = j < a.S;   // rows past the end are zero-filled
+            const int64_t src = (int64_t)(in ? j : 0) * tok + pc * 4;
+            cp_async16(sY1 + (buf * kT + r) * LD + pc * 4, y1 + src, in ? 16 : 0);
+            cp_async16(sY2 + (buf * kT + r) * LD + pc * 4, y2 + src, in ? 16 : 0);
+        }
+        if (COLS && threadIdx.x < kT) {
+            const int j = base + threadIdx.x;
+            sSt[buf * kT + threadIdx.x] = j < a.S ? st_in[j] : make_float2(0.f, 0.f);
+        }
+    };
+    if (n_chunks > 0) load_chunk(0, 0);
+    cp_async_commit();
+
+    // the warp's 16 tile rows as A fragments (rows g and g + 8, columns t and t + 4 of each 8)
+    const int row_a = r0 + 16 * warp + g, row_b = row_a + 8;
+    uint32_t xf1[KS][4], xf2[PASS == kColsV ? 1 : KS][4];
+    {
+        const float *pa = x1 + (int64_t)row_a * tok, *pb = x1 + (int64_t)row_b * tok;
+        const float *qa = x2 + (int64_t)row_a * tok, *qb = x2 + (int64_t)row_b * tok;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int c = ks * 8 + t;
+            xf1[ks][0] = row_a < a.S ? __float_as_uint(pa[c]) : 0u;
+            xf1[ks][1] = row_b < a.S ? __float_as_uint(pb[c]) : 0u;
+            xf1[ks][2] = row_a < a.S ? __float_as_uint(pa[c + 4]) : 0u;
+            xf1[ks][3] = row_b < a.S ? __float_as_uint(pb[c + 4]) : 0u;
+            if constexpr (PASS != kColsV) {
+                xf2[ks][0] = row_a < a.S ? __float_as_uint(qa[c]) : 0u;
+                xf2[ks][1] = row_b < a.S ? __float_as_uint(qb[c]) : 0u;
+                xf2[ks][2] = row_a < a.S ? __float_as_uint(qa[c + 4]) : 0u;
+                xf2[ks][3] = row_b < a.S ? __float_as_uint(qb[c + 4]) : 0u;
+            }
+        }
+    }
+    const float sl = a.scale * 1.4426950408889634f;
+    const int rows[2] = {row_a, row_b};
+    // column j of row r counts iff -back <= j - r <= fwd and j exists
+    auto seen = [&](int j, int r) { return (unsigned)(j - r + back) <= (unsigned)(back + fwd) && j < a.S; };
+
+    float acc[KS][4];   // dQ, dV or dK of the warp's rows
+#pragma unroll
+    for (int n = 0; n < KS; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+    float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f}, dr[2] = {0.f, 0.f}, lse[2] = {0.f, 0.f}, dsc[2] = {0.f, 0.f};
+
+    // the tile's product with the chunk's rows: out[n] (16 x 8) = X (16 x D) . Y[n*8 .. n*8+7]^T
+    auto product = [&](float (&out)[4], const uint32_t (&xf)[KS][4], const uint32_t *y, int n) {
+        out[0] = out[1] = out[2] = out[3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            uint32_t x_hi[4], x_lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) split_tf32(xf[ks][e], x_hi[e], x_lo[e]);
+            const uint32_t *yr = y + (n * 8 + g) * LD + ks * 8 + t;   // B: (k = dim, n = column)
+            mma_3x(out, x_hi, x_lo, yr[0], yr[4]);
+        }
+    };
+    // part[d] += W (16 x 8, held as an accumulator tile: columns 2t, 2t+1 of rows g, g+8) . Y[n*8 .. n*8+7] (8 x D);
+    // the step's columns are taken in the order the accumulator holds them, so W is its own A fragment
+    auto accumulate = [&](float (&part)[KS][4], const float (&w)[4], const uint32_t *y, int n) {
+        const uint32_t wa[4] = {__float_as_uint(w[0]), __float_as_uint(w[2]), __float_as_uint(w[1]), __float_as_uint(w[3])};
+        uint32_t w_hi[4], w_lo[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) split_tf32(wa[e], w_hi[e], w_lo[e]);
+        const uint32_t *yr = y + (n * 8 + 2 * t) * LD + g;   // B: (k = column 2t / 2t + 1, n = dim)
+#pragma unroll
+        for (int d = 0; d < KS; ++d) mma_3x(part[d], w_hi, w_lo, yr[d * 8], yr[LD + d * 8]);
+    };
+
+    const int total = PASS == kRows ? 2 * n_chunks : n_chunks;   // the rows pass walks the keys twice
+    for (int n = 0; n < total; ++n) {
+        const int c = n_chunks ? n % n_chunks : 0, buf = n & 1;
+        if (n + 1 < total) {
+            load_chunk((n + 1) % n_chunks, buf ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int cb = col_lo + c * kT;   // the chunk's first column
+        const uint32_t *cy1 = reinterpret_cast<const uint32_t *>(sY1 + buf * kT * LD);
+        const uint32_t *cy2 = reinterpret_cast<const uint32_t *>(sY2 + buf * kT * LD);
+
+        if (PASS == kRows && n == n_chunks) {   // between the sweeps: the statistics are complete
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                sum[i] = quad_sum(sum[i]);
+                dr[i] = quad_sum(dr[i]);
+                const bool live = sum[i] > 0.f;
+                lse[i] = live ? mx[i] * sl + log2f(sum[i]) : 0.f;
+                dsc[i] = live ? dr[i] / sum[i] * a.scale : 0.f;
+                if (t == 0 && rows[i] < a.S) a.stats[((int64_t)b * a.HH + hh) * a.S + rows[i]] = make_float2(lse[i], dsc[i]);
+            }
+        }
+        float part[KS][4];
+#pragma unroll
+        for (int d = 0; d < KS; ++d) part[d][0] = part[d][1] = part[d][2] = part[d][3] = 0.f;
+
+        bool sweep_one = false;
+        if constexpr (PASS == kRows) sweep_one = n < n_chunks;
+        if (sweep_one) {
+          if constexpr (PASS == kRows) {
+            // ---- sweep one: running maximum, sum of exponentials, sum of exponentials x dP ----
+            float s[8][4];
+            float cm[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                product(s[nt], xf1, cy1, nt);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (!seen(cb + nt * 8 + 2 * t + (e & 1), rows[e >> 1])) s[nt][e] = -INFINITY;
+                    cm[e >> 1] = fmaxf(cm[e >> 1], s[nt][e]);
+                }
+            }
+            float msl[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float m_new = fmaxf(mx[i], quad_max(cm[i]));
+                const float alpha = mx[i] == -INFINITY ? 0.f : ptx::ex2((mx[i] - m_new) * sl);
+                sum[i] *= alpha;
+                dr[i] *= alpha;
+                mx[i] = m_new;
+                msl[i] = m_new == -INFINITY ? 0.f : m_new * sl;
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                float dp[4];
+                product(dp, xf2, cy2, nt);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float ex = ptx::ex2(fmaf(s[nt][e], sl, -msl[e >> 1]));
+                    sum[e >> 1] += ex;
+                    dr[e >> 1] = fmaf(ex, dp[e], dr[e >> 1]);
+                }
+            }
+          }
+        } else {
+            // ---- rows pass, sweep two: dS, dQ += dS K.  cols passes: P^T (and dS^T), dV += P^T dO / dK += dS^T Q ----
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                float s[4], w[4];
+                product(s, xf1, cy1, nt);
+                float dp[4] = {0.f, 0.f, 0.f, 0.f};
+                if constexpr (PASS != kColsV) product(dp, xf2, cy2, nt);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int col = nt * 8 + 2 * t + (e & 1);
+                    // the query's statistics: the row's own (rows pass) or the column's (cols passes)
+                    const float2 sq = COLS ? sSt[buf * kT + col] : make_float2(lse[e >> 1], dsc[e >> 1]);
+                    float p = ptx::ex2(fmaf(s[e], sl, -sq.x));
+                    if (!seen(cb + col, rows[e >> 1])) p = 0.f;
+                    w[e] = PASS == kColsV ? p : p * fmaf(dp[e], a.scale, -sq.y);
+                }
+                accumulate(part, w, PASS == kColsV ? cy2 : cy1, nt);
+            }
+#pragma unroll
+            for (int d = 0; d < KS; ++d)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[d][e] += part[d][e];
+        }
+        __syncthreads();   // the buffer is free for the chunk after the next
+    }
+    if (PASS == kRows && n_chunks == 0 && t == 0) {   // rows that see no key
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+            if (rows[i] < a.S) a.stats[((int64_t)b * a.HH + hh) * a.S + rows[i]] = make_float2(0.f, 0.f);
+    }
+    float *out = (PASS == kRows ? a.dq : PASS == kColsV ? a.dv : a.dk) + head;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (rows[i] < a.S) {
+            float *dst = out + (int64_t)rows[i] * tok + 2 * t;
+#pragma unroll
+            for (int d = 0; d < KS; ++d) *reinterpret_cast<float2 *>(dst + d * 8) = make_float2(acc[d][2 * i], acc[d][2 * i + 1]);
+        }
+    }
+}
+
+template <int D>
+int launch_f(const BwdFArgs &a, int64_t B, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)4 * kT * (D + 4) * sizeof(float) + 2 * kT * sizeof(float2);
+    int rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_kernel<D, kRows>, smem, "bwd_f32 rows")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_kernel<D, kColsV>, smem, "bwd_f32 dV")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_kernel<D, kColsK>, smem, "bwd_f32 dK")) != MAT_OK) return rc;
+    const dim3 grid((unsigned)a.HH, (unsigned)((a.S + kT - 1) / kT), (unsigned)B);
+    bwd_f32_kernel<D, kRows><<<grid, kThreads, smem, stream>>>(a);
+    bwd_f32_kernel<D, kColsV><<<grid, kThreads, smem, stream>>>(a);
+    bwd_f32_kernel<D, kColsK><<<grid, kThreads, smem, stream>>>(a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "fp32 tensor-core backward launch");
+    note_kernel("bwd_f32_mma");
+    return MAT_OK;
+}
+
+}  // namespace
+
+// fp32 window patterns with head width 32 or 64, lengths a multiple of the dilation, 16-byte aligned tensors.
+// MAT_BWD_KERNEL=warp keeps the warp-level kernels.
+bool bwd_f32_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil) {
+    if (dtype != MAT_F32 || (D != 32 && D != 64) || dil < 1 || S % dil != 0) return false;
+    const char *env = std::getenv("MAT_BWD_KERNEL");
+    if (env && std::strcmp(env, "warp") == 0) return false;
+    const int64_t Sv = S / dil;
+    return Sv < (1LL << 30) && H * dil < (1LL << 31) && (Sv + kT - 1) / kT <= 65535 && B <= 65535;
+}
+
+int launch_bwd_f32_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk, void *dv,
+                       float2 *stats, int64_t B, int64_t S, int64_t H, int64_t D, int64_t left, int64_t right,
+                       int64_t dil, float scale, cudaStream_t stream) {
+    BwdFArgs a;
+    a.q = (const float *)q; a.k = (const float *)k; a.v = (const float *)v; a.go = (const float *)dout;
+    a.dq = (float *)dq; a.dk = (float *)dk; a.dv = (float *)dv;
+    a.stats = stats;
+    a.S = (int32_t)(S / dil);
+    a.HH = (int32_t)(H * dil);
+    a.left = (int32_t)std::min<int64_t>(left, a.S);
+    a.right = (int32_t)std::min<int64_t>(right, a.S);
+    a.scale = scale;
+    return D == 32 ? launch_f<32>(a, B, stream) : launch_f<64>(a, B, stream);
+}
+
+}  // namespace mat

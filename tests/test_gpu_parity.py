@@ -653,11 +653,44 @@ def test_backward_matches_autograd_of_reference_oracle(B, S, H, D, W):
     q, k, v = (t.to(DEV) for t in seeded_qkv(81, B, S, H, D))
     go = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(82)).to(DEV)
     dq, dk, dv = ext.backward(q, k, v, go, W)
-    assert nat.last_kernel() == "bwd_window"
+    assert nat.last_kernel() == ("bwd_f32_mma" if D in (32, 64) else "bwd_window")   # head widths 32, 64: tensor cores
     qr, kr, vr = (t.detach().cpu().double().requires_grad_(True) for t in (q, k, v))
     mt.pytorch_sparse_attention(qr, kr, vr, W).backward(go.cpu().double())
     for got, ref in ((dq, qr), (dk, kr), (dv, vr)):
         assert (got.cpu().double() - ref.grad).abs().max() < 2e-5 * max(1.0, float(ref.grad.abs().max()))
+
+
+@pytest.mark.parametrize("D", [32, 64])
+@pytest.mark.parametrize("B,S,H,left,right,dil", [
+    (1, 512, 2, 63, 0, 1), (2, 200, 3, 32, 32, 1), (1, 33, 1, 8, 8, 1), (1, 130, 2, 10, 3, 1), (1, 70, 1, 40, 41, 1),
+    (1, 300, 2, 64, 64, 1), (1, 256, 2, 15, 0, 2), (2, 96, 1, 5, 5, 3), (1, 1000, 2, 1000, 1000, 1), (1, 1000, 1, 1000, 0, 1),
+    (1, 700, 2, 300, 100, 1),
+])
+def test_fp32_backward_on_tensor_cores(monkeypatch, B, S, H, left, right, dil, D):
+    """The fp32 backward as three TF32 products per product (head widths 32 and 64): against autograd in fp64
+    through a dense masked softmax at the fp32 kernels' bar (2e-5 of the gradient's scale), windows narrow, wide,
+    dilated, dense and causal dense, ragged lengths; and against the warp-level fp32 kernels."""
+    spec = PatternSpec(left=left, right=right, dilation=dil)
+    q, k, v = seeded_qkv(87, B, S, H, D, torch.float32)
+    go = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(88))
+    args = tuple(t.to(DEV) for t in (q, k, v, go))
+    got = ext.backward_pattern(*args, spec)
+    torch.cuda.synchronize()
+    assert nat.last_kernel() == "bwd_f32_mma" and nat.device_status() == 0
+    ref = [t.double().requires_grad_(True) for t in (q, k, v)]
+    masked_dense_attention(*ref, left, right, dil).backward(go.double())
+    for name, a, r in zip(("dQ", "dK", "dV"), got, ref):
+        err = float((a.cpu().double() - r.grad).abs().max())
+        assert err <= 2e-5 * max(1.0, float(r.grad.abs().max())), f"{name} vs fp64 autograd: {err}"
+    monkeypatch.setenv("MAT_BWD_KERNEL", "warp")
+    want = ext.backward_pattern(*args, spec)
+    assert nat.last_kernel() == "bwd_window"
+    for name, a, b in zip(("dQ", "dK", "dV"), got, want):
+        assert float((a - b).abs().max()) <= 2e-5 * max(1.0, float(b.abs().max())), name
+    monkeypatch.delenv("MAT_BWD_KERNEL")
+    again = ext.backward_pattern(*args, spec)
+    for a, b in zip(got, again):
+        assert torch.equal(a, b)
 
 
 @pytest.mark.parametrize("causal", [False, True])
