@@ -1,0 +1,318 @@
+// 16-bit backward of window attention for head widths other than 64 on the warp-level tensor-core
+// instructions.
+//
+// The reference's backward takes any head width (sparse_attention_backward_kernel,
+// src/cuda/sparse_attention_kernel.cu:265-346).  The TMA-staged kernels of bwd_mma.cu are laid out for 128-byte
+// rows (D = 64); other widths used to fall to the one-warp-per-row kernels of backward.cu.  This file has the
+// control flow of the fp32 tensor-core backward (bwd_f32_mma.cu: 64-row tiles, the band walked in 64-column
+// chunks through two cp.async buffers, a rows pass with two sweeps, a dV pass and a dK pass, statistics in the
+// workspace) with the products of the 16-bit forward for these widths (mma_window_d.cu: ldmatrix from rows padded
+// by 16 bytes, mma.sync.m16n8k16, the accumulator tiles of one product packed into the A fragments of the next;
+// P and dS rounded to the input type for the second products, as in bwd_mma.cu).
+#include <algorithm>
+#include <cstring>
+
+#include "mat_common.cuh"
+#include "ptx.cuh"
+
+namespace mat {
+namespace {
+
+constexpr int kT = 64, kThreads = 128;
+
+struct BwdDArgs {
+    const void *q, *k, *v, *go;
+    void *dq, *dk, *dv;
+    float2 *stats;             // [B, HH, S]: (log2-sum-exp of the scaled scores, delta * scale)
+    int32_t S, HH;             // rows and heads of the (possibly dilated) view
+    int32_t left, right;
+    float scale;
+};
+
+__device__ __forceinline__ void cp_async16(void *dst, const void *src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ptx::smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ float quad_max(float x) {
+    x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 1));
+    return fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 2));
+}
+__device__ __forceinline__ float quad_sum(float x) {
+    x += __shfl_xor_sync(0xffffffffu, x, 1);
+    return x + __shfl_xor_sync(0xffffffffu, x, 2);
+}
+
+constexpr int kRows = 0, kColsV = 1, kColsK = 2;
+
+// PASS = kRows: tile rows are queries, columns keys.  kColsV / kColsK: tile rows are keys, columns queries.
+template <typename T, int D, int PASS>
+__global__ void __launch_bounds__(kThreads)
+bwd_d_kernel(const BwdDArgs a) {
+    using M = ptx::Mma<T>;
+    constexpr int LD = D + 8, KS = D / 16;   // padded row (elements); 16-wide steps of the head dimension
+    constexpr bool COLS = PASS != kRows;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    T *sY1 = reinterpret_cast<T *>(smem_raw);          // [2][kT][LD]: rows pass K, cols passes Q
+    T *sY2 = sY1 + 2 * kT * LD;                        // [2][kT][LD]: rows pass V, cols passes dO
+    float2 *sSt = reinterpret_cast<float2 *>(sY2 + 2 * kT * LD);   // cols passes: [2][kT] statistics of a chunk's queries
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int m4 = lane >> 3, r8 = lane & 7;
+    const int hh = blockIdx.x, b = blockIdx.z, r0 = blockIdx.y * kT;
+    const int back = COLS ? a.right : a.left, fwd = COLS ? a.left : a.right;   // row r sees columns r - back .. r + fwd
+    const int col_lo = max(0, r0 - back);
+    const int col_hi = min(a.S - 1, min(r0 + kT, a.S) - 1 + fwd);
+    const int n_chunks = col_hi >= col_lo ? (col_hi - col_lo) / kT + 1 : 0;
+    const int64_t tok = (int64_t)a.HH * D;
+    const int64_t head = ((int64_t)b * a.S * a.HH + hh) * D;
+    const T *x1 = (const T *)(COLS ? a.k : a.q) + head, *x2 = (const T *)(COLS ? a.v : a.go) + head;
+    const T *y1 = (const T *)(COLS ? a.q : a.k) + head, *y2 = (const T *)(COLS ? a.go : a.v) + head;
+    const float2 *st_in = a.stats + ((int64_t)b * a.HH + hh) * a.S;
+
+    auto load_chunk = [&](int c, int buf) {
+        constexpr int kPieces = D / 8;
+        const int base = col_lo + c * kT;
+        for (int i = threadIdx.x; i < kT * kPieces; i += kThreads) {
+            const int r = i / kPieces, pc = i % kPieces;
+            const int j = base + r;
+            const bool in = j < a.S;   // rows past the end are zero-filled
+            const int64_t src = (int64_t)(in ? j : 0) * tok + pc * 8;
+            cp_async16(sY1 + (buf * kT + r) * LD + pc * 8, y1 + src, in ? 16 : 0);
+            cp_async16(sY2 + (buf * kT + r) * LD + pc * 8, y2 + src, in ? 16 : 0);
+        }
+        if (COLS && threadIdx.x < kT) {
+            const int j = base + threadIdx.x;
+            sSt[buf * kT + threadIdx.x] = j < a.S ? st_in[j] : make_float2(0.f, 0.f);
+        }
+    };
+    if (n_chunks > 0) load_chunk(0, 0);
+    cp_async_commit();
+
+    // the warp's 16 tile rows as A fragments: rows g and g + 8, columns 2t, 2t+1 (+8) of each 16
+    const int row_a = r0 + 16 * warp + g, row_b = row_a + 8;
+    uint32_t xf1[KS][4], xf2[PASS == kColsV ? 1 : KS][4];
+    {
+        const T *pa = x1 + (int64_t)row_a * tok, *pb = x1 + (int64_t)row_b * tok;
+        const T *qa = x2 + (int64_t)row_a * tok, *qb = x2 + (int64_t)row_b * tok;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int c = ks * 16 + 2 * t;
+            xf1[ks][0] = row_a < a.S ? *reinterpret_cast<const uint32_t *>(pa + c) : 0u;
+            xf1[ks][1] = row_b < a.S ? *reinterpret_cast<const uint32_t *>(pb + c) : 0u;
+            xf1[ks][2] = row_a < a.S ? *reinterpret_cast<const uint32_t *>(pa + c + 8) : 0u;
+            xf1[ks][3] = row_b < a.S ? *reinterpret_cast<const uint32_t *>(pb + c + 8) : 0u;
+            if constexpr (PASS != kColsV) {
+                xf2[ks][0] = row_a < a.S ? *reinterpret_cast<const uint32_t *>(qa + c) : 0u;
+                xf2[ks][1] = row_b < a.S ? *reinterpret_cast<const uint32_t *>(qb + c) : 0u;
+                xf2[ks][2] = row_a < a.S ? *reinterpret_cast<const uint32_t *>(qa + c + 8) : 0u;
+                xf2[ks][3] = row_b < a.S ? *reinterpret_cast<const uint32_t *>(qb + c + 8) : 0u;
+            }
+        }
+    }
+    const float sl = a.scale * 1.4426950408889634f;
+    const int rows[2] = {row_a, row_b};
+    // column j of row r counts iff -back <= j - r <= fwd and j exists
+    auto seen = [&](int j, int r) { return (unsigned)(j - r + back) <= (unsigned)(back + fwd) && j < a.S; };
+
+    float acc[2 * KS][4];   // dQ, dV or dK of the warp's rows
+#pragma unroll
+    for (int n = 0; n < 2 * KS; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+    float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f}, dr[2] = {0.f, 0.f}, lse[2] = {0.f, 0.f}, dsc[2] = {0.f, 0.f};
+
+    // the tile's product with 16 of the chunk's rows: (out0 | out1) (16 x 16) = X (16 x D) . Y[n2*16 .. n2*16+15]^T
+    auto product = [&](float (&out0)[4], float (&out1)[4], const uint32_t (&xf)[KS][4], uint32_t y_addr, int n2) {
+        out0[0] = out0[1] = out0[2] = out0[3] = 0.f;
+        out1[0] = out1[1] = out1[2] = out1[3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            // matrices: (columns n2*16 + 0..7, dims +0), (same columns, dims +8), (columns +8, dims +0), (columns +8, dims +8)
+            uint32_t yf[4];
+            ptx::ldmatrix_x4(yf, y_addr + (uint32_t)(((n2 * 16 + r8 + (m4 >> 1) * 8) * LD + ks * 16 + (m4 & 1) * 8) * 2));
+            M::run(out0, xf[ks], yf[0], yf[1]);
+            M::run(out1, xf[ks], yf[2], yf[3]);
+        }
+    };
+    // acc += W (16 x 16: two accumulator tiles, rounded to the input type) . Y[n2*16 .. n2*16+15] (16 x D)
+    auto accumulate = [&](const float (&w0)[4], const float (&w1)[4], uint32_t y_addr, int n2) {
+        const uint32_t wa[4] = {M::pack(w0[0], w0[1]), M::pack(w0[2], w0[3]), M::pack(w1[0], w1[1]), M::pack(w1[2], w1[3])};
+#pragma unroll
+        for (int d2 = 0; d2 < KS; ++d2) {
+            // matrices (transposed on load): (columns n2*16 + 0..7, dims d2*16 + 0..7), (columns +8, same dims),
+            // (columns + 0, dims + 8), (columns + 8, dims + 8)
+            uint32_t yf[4];
+            ptx::ldmatrix_x4_trans(yf, y_addr + (uint32_t)(((n2 * 16 + r8 + (m4 & 1) * 8) * LD + d2 * 16 + (m4 >> 1) * 8) * 2));
+            M::run(acc[2 * d2], wa, yf[0], yf[1]);
+            M::run(acc[2 * d2 + 1], wa, yf[2], yf[3]);
+        }
+    };
+
+    const int total = PASS == kRows ? 2 * n_chunks : n_chunks;   // the rows pass walks the keys twice
+    for (int n = 0; n < total; ++n) {
+        const int c = n_chunks ? n % n_chunks : 0, buf = n & 1;
+        if (n + 1 < total) {
+            load_chunk((n + 1) % n_chunks, buf ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int cb = col_lo + c * kT;   // the chunk's first column
+        const uint32_t cy1 = ptx::smem_u32(sY1 + buf * kT * LD), cy2 = ptx::smem_u32(sY2 + buf * kT * LD);
+
+        if (PASS == kRows && n == n_chunks) {   // between the sweeps: the statistics are complete
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                sum[i] = quad_sum(sum[i]);
+                dr[i] = quad_sum(dr[i]);
+                const bool live = sum[i] > 0.f;
+                lse[i] = live ? mx[i] * sl + log2f(sum[i]) : 0.f;
+                dsc[i] = live ? dr[i] / sum[i] * a.scale : 0.f;
+                if (t == 0 && rows[i] < a.S) a.stats[((int64_t)b * a.HH + hh) * a.S + rows[i]] = make_float2(lse[i], dsc[i]);
+            }
+        }
+        bool sweep_one = false;
+        if constexpr (PASS == kRows) sweep_one = n < n_chunks;
+        if (sweep_one) {
+          if constexpr (PASS == kRows) {
+            // ---- sweep one: running maximum, sum of exponentials, sum of exponentials x dP ----
+            float s[8][4];
+            float cm[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n2 = 0; n2 < 4; ++n2) {
+                product(s[2 * n2], s[2 * n2 + 1], xf1, cy1, n2);
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int nt = 2 * n2 + h2;
+                        if (!seen(cb + nt * 8 + 2 * t + (e & 1), rows[e >> 1])) s[nt][e] = -INFINITY;
+                        cm[e >> 1] = fmaxf(cm[e >> 1], s[nt][e]);
+                    }
+            }
+            float msl[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float m_new = fmaxf(mx[i], quad_max(cm[i]));
+                const float alpha = mx[i] == -INFINITY ? 0.f : ptx::ex2((mx[i] - m_new) * sl);
+                sum[i] *= alpha;
+                dr[i] *= alpha;
+                mx[i] = m_new;
+                msl[i] = m_new == -INFINITY ? 0.f : m_new * sl;
+            }
+#pragma unroll
+            for (int n2 = 0; n2 < 4; ++n2) {
+                float dp[2][4];
+                product(dp[0], dp[1], xf2, cy2, n2);
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float ex = ptx::ex2(fmaf(s[2 * n2 + h2][e], sl, -msl[e >> 1]));
+                        sum[e >> 1] += ex;
+                        dr[e >> 1] = fmaf(ex, dp[h2][e], dr[e >> 1]);
+                    }
+            }
+          }
+        } else {
+            // ---- rows pass, sweep two: dS, dQ += dS K.  cols passes: P^T (and dS^T), dV += P^T dO / dK += dS^T Q ----
+#pragma unroll
+            for (int n2 = 0; n2 < 4; ++n2) {
+                float s[2][4], w[2][4];
+                product(s[0], s[1], xf1, cy1, n2);
+                float dp[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                if constexpr (PASS != kColsV) product(dp[0], dp[1], xf2, cy2, n2);
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int col = (2 * n2 + h2) * 8 + 2 * t + (e & 1);
+                        // the query's statistics: the row's own (rows pass) or the column's (cols passes)
+                        const float2 sq = COLS ? sSt[buf * kT + col] : make_float2(lse[e >> 1], dsc[e >> 1]);
+                        float p = ptx::ex2(fmaf(s[h2][e], sl, -sq.x));
+                        if (!seen(cb + col, rows[e >> 1])) p = 0.f;
+                        w[h2][e] = PASS == kColsV ? p : p * fmaf(dp[h2][e], a.scale, -sq.y);
+                    }
+                accumulate(w[0], w[1], PASS == kColsV ? cy2 : cy1, n2);
+            }
+        }
+        __syncthreads();   // the buffer is free for the chunk after the next
+    }
+    if (PASS == kRows && n_chunks == 0 && t == 0) {   // rows that see no key
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+            if (rows[i] < a.S) a.stats[((int64_t)b * a.HH + hh) * a.S + rows[i]] = make_float2(0.f, 0.f);
+    }
+    T *out = (T *)(PASS == kRows ? a.dq : PASS == kColsV ? a.dv : a.dk) + head;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (rows[i] < a.S) {
+            T *dst = out + (int64_t)rows[i] * tok + 2 * t;
+#pragma unroll
+            for (int d = 0; d < 2 * KS; ++d)
+                *reinterpret_cast<uint32_t *>(dst + d * 8) = M::pack(acc[d][2 * i], acc[d][2 * i + 1]);
+        }
+    }
+}
+
+template <typename T, int D>
+int launch_d(const BwdDArgs &a, int64_t B, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)4 * kT * (D + 8) * sizeof(T) + 2 * kT * sizeof(float2);
+    int rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_d_kernel<T, D, kRows>, smem, "bwd_d rows")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_d_kernel<T, D, kColsV>, smem, "bwd_d dV")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_d_kernel<T, D, kColsK>, smem, "bwd_d dK")) != MAT_OK) return rc;
+    const dim3 grid((unsigned)a.HH, (unsigned)((a.S + kT - 1) / kT), (unsigned)B);
+    bwd_d_kernel<T, D, kRows><<<grid, kThreads, smem, stream>>>(a);
+    bwd_d_kernel<T, D, kColsV><<<grid, kThreads, smem, stream>>>(a);
+    bwd_d_kernel<T, D, kColsK><<<grid, kThreads, smem, stream>>>(a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "16-bit backward (other head widths) launch");
+    note_kernel("bwd_d_mma");
+    return MAT_OK;
+}
+
+template <typename T>
+int launch_any_d(const BwdDArgs &a, int64_t B, int64_t D, cudaStream_t stream) {
+    switch (D) {
+        case 16: return launch_d<T, 16>(a, B, stream);
+        case 32: return launch_d<T, 32>(a, B, stream);
+        case 48: return launch_d<T, 48>(a, B, stream);
+        case 80: return launch_d<T, 80>(a, B, stream);
+        case 96: return launch_d<T, 96>(a, B, stream);
+        case 112: return launch_d<T, 112>(a, B, stream);
+        case 128: return launch_d<T, 128>(a, B, stream);
+    }
+    return fail(MAT_ERR_UNSUPPORTED, "head width %lld has no instantiation of the warp-level backward", (long long)D);
+}
+
+}  // namespace
+
+// 16-bit window patterns with a head width that is a multiple of 16 up to 128 other than 64, lengths a multiple of
+// the dilation, 16-byte aligned tensors.  MAT_BWD_KERNEL=warp keeps the one-warp-per-row kernels.
+bool bwd_d_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil) {
+    if (dtype != MAT_BF16 && dtype != MAT_F16) return false;
+    if (D % 16 || D < 16 || D > 128 || D == 64 || dil < 1 || S % dil != 0) return false;
+    const char *env = std::getenv("MAT_BWD_KERNEL");
+    if (env && std::strcmp(env, "warp") == 0) return false;
+    const int64_t Sv = S / dil;
+    return Sv < (1LL << 30) && H * dil < (1LL << 31) && (Sv + kT - 1) / kT <= 65535 && B <= 65535;
+}
+
+int launch_bwd_d_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk, void *dv,
+                     float2 *stats, int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t left, int64_t right,
+                     int64_t dil, float scale, cudaStream_t stream) {
+    BwdDArgs a;
+    a.q = q; a.k = k; a.v = v; a.go = dout;
+    a.dq = dq; a.dk = dk; a.dv = dv;
+    a.stats = stats;
+    a.S = (int32_t)(S / dil);
+    a.HH = (int32_t)(H * dil);
+    a.left = (int32_t)std::min<int64_t>(left, a.S);
+    a.right = (int32_t)std::min<int64_t>(right, a.S);
+    a.scale = scale;
+    return dtype == MAT_BF16 ? launch_any_d<__nv_bfloat16>(a, B, D, stream) : launch_any_d<__half>(a, B, D, stream);
+}
+
+}  // namespace mat

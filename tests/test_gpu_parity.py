@@ -693,6 +693,37 @@ def test_fp32_backward_on_tensor_cores(monkeypatch, B, S, H, left, right, dil, D
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D", [16, 32, 96, 128])
+@pytest.mark.parametrize("B,S,H,left,right,dil", [
+    (1, 512, 2, 63, 0, 1), (2, 200, 3, 32, 32, 1), (1, 33, 1, 8, 8, 1), (1, 70, 1, 40, 41, 1), (1, 300, 2, 64, 64, 1),
+    (1, 256, 2, 15, 0, 2), (1, 600, 2, 600, 600, 1), (1, 600, 1, 600, 0, 1),
+])
+def test_16bit_backward_for_other_head_widths(monkeypatch, dtype, D, B, S, H, left, right, dil):
+    """The 16-bit backward for head widths that are multiples of 16 up to 128 other than 64 (the reference's
+    kernel takes any width: src/cuda/sparse_attention_kernel.cu:265-346) on the warp-level tensor-core kernels:
+    against autograd in fp64 through a dense masked softmax on the same rounded inputs, and against the
+    one-warp-per-row kernels."""
+    spec = PatternSpec(left=left, right=right, dilation=dil)
+    q, k, v = seeded_qkv(89, B, S, H, D, dtype)
+    go = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(90)).to(dtype)
+    args = tuple(t.to(DEV) for t in (q, k, v, go))
+    got = ext.backward_pattern(*args, spec)
+    torch.cuda.synchronize()
+    assert nat.last_kernel() == "bwd_d_mma" and nat.device_status() == 0
+    tol = 2e-2 if dtype == torch.bfloat16 else 5e-3
+    ref = [t.double().requires_grad_(True) for t in (q, k, v)]
+    masked_dense_attention(*ref, left, right, dil).backward(go.double())
+    for name, a, r in zip(("dQ", "dK", "dV"), got, ref):
+        err = float((a.cpu().double() - r.grad).abs().max())
+        assert err <= tol * max(1.0, float(r.grad.abs().max())), f"{name} vs fp64 autograd: {err}"
+    monkeypatch.setenv("MAT_BWD_KERNEL", "warp")
+    want = ext.backward_pattern(*args, spec)
+    assert nat.last_kernel() == "bwd_window"
+    for name, a, b in zip(("dQ", "dK", "dV"), got, want):
+        assert float((a.float() - b.float()).abs().max()) <= tol * max(1.0, float(b.float().abs().max())), name
+
+
 @pytest.mark.parametrize("causal", [False, True])
 def test_dense_backward_and_custom_windows(causal):
     q, k, v = (t.to(DEV) for t in seeded_qkv(83, 2, 40, 2, 24))
