@@ -14,8 +14,9 @@
 // mma.sync m16n8k16 with Q held in registers, masks, an online softmax in registers, P re-used in place
 // as the A fragments of O += P V.  A dilated window is a plain window over the tensor viewed as
 // [B, S/dil, dil*H, D], as everywhere in this library.  (Skipping, per warp, the 16-key groups none of its rows
-// can use was measured slower - 117 against 93 us at 64K tokens x 4 heads of 128: the branches inside the unrolled
-// products cost more than the masked work they save.)
+// can use by a branch per group was measured slower - 117 against 93 us at 64K tokens x 4 heads of 128: the branches
+// inside the unrolled products cost more than the masked work they save.  Narrow windows take the second kernel
+// below, which gets rid of those groups without a branch.)
 #include <algorithm>
 #include <cstring>
 
@@ -198,7 +199,162 @@ window_d_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__res
     }
 }
 
-template <typename T, int D>
+// Narrow windows: every warp walks the keys from a base of its own, the first key its first row can see, in passes
+// of NS 16-key steps, so that no step is without a visible key but the last of the walk (at 64 causal taps 5 steps
+// instead of the 8 of two chunks), and the code is the same straight line for every warp.  The CTA stages the
+// 48 + 16 NS rows the four warps' passes span.
+template <typename T, int D, int NS>
+__global__ void __launch_bounds__(kThreads)
+window_d_diag_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v, T *__restrict__ o,
+                     const WinDParams P) {
+    constexpr int LD = D + 8, KS = D / 16;
+    constexpr int kStage = 48 + 16 * NS;   // rows of K and of V in shared memory
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    T *sK = reinterpret_cast<T *>(smem_raw);   // [kStage][LD]
+    T *sV = sK + kStage * LD;                  // [kStage][LD]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int hh = blockIdx.x, b = blockIdx.z, q0 = blockIdx.y * kTQ;
+    const int p_first = q0 + P.off1;
+    const int key_lo = max(0, p_first - P.left);
+    const int key_hi = min(P.Skv1 - 1, min(q0 + kTQ, P.Sq1) - 1 + P.off1 + P.right);
+    const int base_w = max(key_lo, p_first + 16 * warp - P.left);   // the warp's first key
+    int n_pass = 0;   // passes of the warp with the longest walk
+    if (key_hi >= key_lo) {
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) {
+            const int keys_w = min(key_hi, p_first + 16 * w + 15 + P.right) - max(key_lo, p_first + 16 * w - P.left) + 1;
+            n_pass = max(n_pass, (keys_w + 16 * NS - 1) / (16 * NS));
+        }
+    }
+    const int64_t tok = (int64_t)P.HH * D;
+    const T *kb_ptr = k + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+    const T *vb_ptr = v + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+
+    const int row_a = q0 + warp * 16 + g, row_b = row_a + 8;
+    uint32_t qf[KS][4];
+    {
+        const T *qa = q + (((int64_t)b * P.Sq1 + row_a) * P.HH + hh) * D;
+        const T *qb = q + (((int64_t)b * P.Sq1 + row_b) * P.HH + hh) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int c = ks * 16 + 2 * t;
+            qf[ks][0] = row_a < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qa + c) : 0u;
+            qf[ks][1] = row_b < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qb + c) : 0u;
+            qf[ks][2] = row_a < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qa + c + 8) : 0u;
+            qf[ks][3] = row_b < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qb + c + 8) : 0u;
+        }
+    }
+    const int pos[2] = {row_a + P.off1, row_b + P.off1};
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float acc[2 * KS][4];
+#pragma unroll
+    for (int n = 0; n < 2 * KS; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+    const int m4 = lane >> 3, r8 = lane & 7;
+
+    for (int c = 0; c < n_pass; ++c) {
+        const int stage_lo = key_lo + c * 16 * NS;   // warp 0's base is key_lo
+        if (stage_lo > key_hi) break;
+        if (c) __syncthreads();   // the previous pass has been read
+        {
+            constexpr int kPieces = D / 8;
+            for (int i = threadIdx.x; i < kStage * kPieces; i += kThreads) {
+                const int r = i / kPieces, pc = i % kPieces;
+                const int j = stage_lo + r;
+                const bool in = j <= key_hi;   // rows past the tile's last key are zero-filled
+                const int64_t src = (int64_t)(in ? j : 0) * tok + pc * 8;
+                cp_async16(sK + r * LD + pc * 8, kb_ptr + src, in ? 16 : 0);
+                cp_async16(sV + r * LD + pc * 8, vb_ptr + src, in ? 16 : 0);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int kb = base_w + c * 16 * NS;   // the warp's first key of the pass
+        const uint32_t k_addr = ptx::smem_u32(sK + (kb - stage_lo) * LD), v_addr = ptx::smem_u32(sV + (kb - stage_lo) * LD);
+
+        float s[2 * NS][4];
+#pragma unroll
+        for (int n = 0; n < 2 * NS; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int n2 = 0; n2 < NS; ++n2) {
+                uint32_t kf[4];
+                ptx::ldmatrix_x4(kf, k_addr + (uint32_t)(((n2 * 16 + r8 + (m4 >> 1) * 8) * LD + ks * 16 + (m4 & 1) * 8) * 2));
+                ptx::Mma<T>::run(s[2 * n2], qf[ks], kf[0], kf[1]);
+                ptx::Mma<T>::run(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
+            }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 2 * NS; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = kb + n * 8 + 2 * t + (e & 1), p = pos[e >> 1];
+                const bool ok = j >= p - P.left && j <= p + P.right && j < P.Skv1;
+                s[n][e] = ok ? s[n][e] : -INFINITY;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+            }
+        float alpha[2], mus[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float m_new = fmaxf(m_run[i], mx[i]);
+            alpha[i] = m_new == -INFINITY ? 1.f : ptx::ex2((m_run[i] - m_new) * P.sl2);
+            m_run[i] = m_new;
+            mus[i] = m_new == -INFINITY ? 0.f : m_new * P.sl2;
+            l_run[i] *= alpha[i];
+        }
+        if (c) {
+#pragma unroll
+            for (int n = 0; n < 2 * KS; ++n) {
+                acc[n][0] *= alpha[0]; acc[n][1] *= alpha[0];
+                acc[n][2] *= alpha[1]; acc[n][3] *= alpha[1];
+            }
+        }
+        uint32_t pa[NS][4];
+#pragma unroll
+        for (int n = 0; n < 2 * NS; ++n) {
+            float w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                w[e] = ptx::ex2(fmaf(s[n][e], P.sl2, -mus[e >> 1]));
+                l_run[e >> 1] += w[e];
+            }
+            pa[n >> 1][(n & 1) * 2] = ptx::Mma<T>::pack(w[0], w[1]);
+            pa[n >> 1][(n & 1) * 2 + 1] = ptx::Mma<T>::pack(w[2], w[3]);
+        }
+#pragma unroll
+        for (int kk = 0; kk < NS; ++kk) {
+#pragma unroll
+            for (int d2 = 0; d2 < KS; ++d2) {
+                uint32_t vf[4];
+                ptx::ldmatrix_x4_trans(vf, v_addr + (uint32_t)(((kk * 16 + r8 + (m4 & 1) * 8) * LD + d2 * 16 + (m4 >> 1) * 8) * 2));
+                ptx::Mma<T>::run(acc[2 * d2], pa[kk], vf[0], vf[1]);
+                ptx::Mma<T>::run(acc[2 * d2 + 1], pa[kk], vf[2], vf[3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float l = l_run[i];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const int row = i == 0 ? row_a : row_b;
+        if (row < P.Sq1) {
+            T *dst = o + (((int64_t)b * P.Sq1 + row) * P.HH + hh) * D + 2 * t;
+#pragma unroll
+            for (int n = 0; n < 2 * KS; ++n)
+                *reinterpret_cast<uint32_t *>(dst + n * 8) = ptx::Mma<T>::pack(acc[n][2 * i] * inv, acc[n][2 * i + 1] * inv);
+        }
+    }
+}
+
+// NS = 0: the 64-key chunks; otherwise the per-warp walk in passes of NS 16-key steps
+template <typename T, int D, int NS>
 int launch_d(const Problem &p) {
     const int64_t dil = p.pat.dilation;
     WinDParams wp;
@@ -209,8 +365,10 @@ int launch_d(const Problem &p) {
     wp.left = (int32_t)std::min<int64_t>(p.pat.left, wp.Skv1);
     wp.right = (int32_t)std::min<int64_t>(p.pat.right, wp.Skv1);
     wp.sl2 = p.scale * 1.4426950408889634f;
-    auto kern = window_d_kernel<T, D>;
-    constexpr size_t smem = (size_t)4 * kTK * (D + 8) * sizeof(T);
+    void (*kern)(const T *, const T *, const T *, T *, WinDParams);
+    if constexpr (NS > 0) kern = window_d_diag_kernel<T, D, (NS > 0 ? NS : 1)>;
+    else kern = window_d_kernel<T, D>;
+    constexpr size_t smem = (size_t)(NS > 0 ? 2 * (48 + 16 * NS) : 4 * kTK) * (D + 8) * sizeof(T);
     if (int rc = ensure_dynamic_smem((const void *)kern, smem, "cudaFuncSetAttribute(window_d_kernel)")) return rc;
     const dim3 grid((unsigned)wp.HH, (unsigned)((wp.Sq1 + kTQ - 1) / kTQ), (unsigned)p.B);
     kern<<<grid, kThreads, smem, p.stream>>>((const T *)p.q, (const T *)p.k, (const T *)p.v, (T *)p.o, wp);
@@ -241,16 +399,30 @@ bool mma_window_d_supports(const Problem &p) {
     return !(force && std::strcmp(force, "rowwarp") == 0);
 }
 
+template <typename T, int D>
+int launch_span(const Problem &p) {
+    // Keys a warp's 16 rows can see: up to 80 (64 causal taps) the warp walks its own range in 5 steps of 16, up to
+    // 144 (the reference's default window of 64 either side) in 9; wider windows keep the double-buffered chunks.
+    // MAT_WINDOW_D_KERNEL=chunks forces those (a measurement aid).
+    const int64_t skv1 = p.Skv / p.pat.dilation;
+    const int64_t span = std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16;
+    const char *force = std::getenv("MAT_WINDOW_D_KERNEL");
+    if (force && std::strcmp(force, "chunks") == 0) return launch_d<T, D, 0>(p);
+    if (span <= 80) return launch_d<T, D, 5>(p);
+    if (span <= 144) return launch_d<T, D, 9>(p);
+    return launch_d<T, D, 0>(p);
+}
+
 template <typename T>
 int launch_any_d(const Problem &p) {
     switch (p.D) {
-        case 16: return launch_d<T, 16>(p);
-        case 32: return launch_d<T, 32>(p);
-        case 48: return launch_d<T, 48>(p);
-        case 80: return launch_d<T, 80>(p);
-        case 96: return launch_d<T, 96>(p);
-        case 112: return launch_d<T, 112>(p);
-        case 128: return launch_d<T, 128>(p);
+        case 16: return launch_span<T, 16>(p);
+        case 32: return launch_span<T, 32>(p);
+        case 48: return launch_span<T, 48>(p);
+        case 80: return launch_span<T, 80>(p);
+        case 96: return launch_span<T, 96>(p);
+        case 112: return launch_span<T, 112>(p);
+        case 128: return launch_span<T, 128>(p);
     }
     return fail(MAT_ERR_UNSUPPORTED, "head width %lld has no instantiation of the warp-level window kernel", (long long)p.D);
 }

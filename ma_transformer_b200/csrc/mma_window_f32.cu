@@ -234,8 +234,175 @@ window_f32_kernel(const float *__restrict__ q, const float *__restrict__ k, cons
     }
 }
 
-template <int D, bool ROUND>
+// Narrow windows.  In the kernel above a warp multiplies its 16 rows with all 64 keys of every chunk, although the
+// band crosses the tile as a parallelogram: at 64 causal taps a warp needs 79 of the 127 keys the tile sees, 10 of
+// the 16 score tiles it computes.  Skipping the others by a branch per tile was measured slower (the branches keep
+// the compiler from overlapping the tiles).  Here every warp walks keys from a base of its own, the first key its
+// first row can see, in passes of NT 8-key tiles: the same straight-line code for every warp, no tile without a
+// visible key but the last of the walk.  The CTA stages the 48 + 8 NT rows the four warps' passes span.
+template <int D, bool ROUND, int NT>
+__global__ void __launch_bounds__(kThreads)
+window_f32_diag_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                       float *__restrict__ o, const WinFParams P) {
+    constexpr int LD = D + 4, KS = D / 8;
+    constexpr int kStage = 48 + 8 * NT;   // rows of K and of V in shared memory
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    float *sK = reinterpret_cast<float *>(smem_raw);   // [kStage][LD]
+    float *sV = sK + kStage * LD;                      // [kStage][LD]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int hh = blockIdx.x, b = blockIdx.z, q0 = blockIdx.y * kTQ;
+    const int p_first = q0 + P.off1;
+    const int key_lo = max(0, p_first - P.left);
+    const int key_hi = min(P.Skv1 - 1, min(q0 + kTQ, P.Sq1) - 1 + P.off1 + P.right);
+    const int base_w = max(key_lo, p_first + 16 * warp - P.left);   // the warp's first key
+    int n_pass = 0;   // passes of the warp with the longest walk (the bases of a sequence's first tiles are clamped)
+    if (key_hi >= key_lo) {
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) {
+            const int keys_w = min(key_hi, p_first + 16 * w + 15 + P.right) - max(key_lo, p_first + 16 * w - P.left) + 1;
+            n_pass = max(n_pass, (keys_w + 8 * NT - 1) / (8 * NT));
+        }
+    }
+    const int64_t tok = (int64_t)P.HH * D;
+    const float *kb_ptr = k + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+    const float *vb_ptr = v + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+
+    const int row_a = q0 + warp * 16 + g, row_b = row_a + 8;
+    uint32_t qf[KS][4];
+    {
+        const float *qa = q + (((int64_t)b * P.Sq1 + row_a) * P.HH + hh) * D;
+        const float *qb = q + (((int64_t)b * P.Sq1 + row_b) * P.HH + hh) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int c = ks * 8 + t;
+            qf[ks][0] = row_a < P.Sq1 ? __float_as_uint(qa[c]) : 0u;
+            qf[ks][1] = row_b < P.Sq1 ? __float_as_uint(qb[c]) : 0u;
+            qf[ks][2] = row_a < P.Sq1 ? __float_as_uint(qa[c + 4]) : 0u;
+            qf[ks][3] = row_b < P.Sq1 ? __float_as_uint(qb[c + 4]) : 0u;
+        }
+    }
+    const int pos[2] = {row_a + P.off1, row_b + P.off1};
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float acc[KS][4];
+#pragma unroll
+    for (int n = 0; n < KS; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+
+    for (int c = 0; c < n_pass; ++c) {
+        const int stage_lo = key_lo + c * 8 * NT;   // warp 0's base is key_lo
+        if (stage_lo > key_hi) break;
+        if (c) __syncthreads();   // the previous pass has been read
+        {
+            constexpr int kPieces = D / 4;
+            for (int i = threadIdx.x; i < kStage * kPieces; i += kThreads) {
+                const int r = i / kPieces, pc = i % kPieces;
+                const int j = stage_lo + r;
+                const bool in = j <= key_hi;   // rows past the tile's last key are zero-filled
+                const int64_t src = (int64_t)(in ? j : 0) * tok + pc * 4;
+                cp_async16(sK + r * LD + pc * 4, kb_ptr + src, in ? 16 : 0);
+                cp_async16(sV + r * LD + pc * 4, vb_ptr + src, in ? 16 : 0);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int kb = base_w + c * 8 * NT;   // the warp's first key of the pass
+        const uint32_t *ck = reinterpret_cast<const uint32_t *>(sK + (kb - stage_lo) * LD);
+        const uint32_t *cv = reinterpret_cast<const uint32_t *>(sV + (kb - stage_lo) * LD);
+
+        float s[NT][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            uint32_t q_hi[4], q_lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) split_tf32<ROUND>(qf[ks][e], q_hi[e], q_lo[e]);
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const uint32_t *kr = ck + (n * 8 + g) * LD + ks * 8 + t;
+                mma_3x<ROUND>(s[n], q_hi, q_lo, kr[0], kr[4]);
+            }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = kb + n * 8 + 2 * t + (e & 1), p = pos[e >> 1];
+                const bool ok = j >= p - P.left && j <= p + P.right && j < P.Skv1;
+                s[n][e] = ok ? s[n][e] : -INFINITY;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+            }
+        float alpha[2], mus[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float m_new = fmaxf(m_run[i], mx[i]);
+            alpha[i] = m_new == -INFINITY ? 1.f : ptx::ex2((m_run[i] - m_new) * P.sl2);
+            m_run[i] = m_new;
+            mus[i] = m_new == -INFINITY ? 0.f : m_new * P.sl2;
+            l_run[i] *= alpha[i];
+        }
+        float part[KS][4];   // the pass's P V in accumulators of its own (short chains, see above)
+#pragma unroll
+        for (int n = 0; n < KS; ++n) part[n][0] = part[n][1] = part[n][2] = part[n][3] = 0.f;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            float w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                w[e] = ptx::ex2(fmaf(s[n][e], P.sl2, -mus[e >> 1]));
+                l_run[e >> 1] += w[e];
+            }
+            const uint32_t pa[4] = {__float_as_uint(w[0]), __float_as_uint(w[2]), __float_as_uint(w[1]), __float_as_uint(w[3])};
+            uint32_t p_hi[4], p_lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) split_tf32<ROUND>(pa[e], p_hi[e], p_lo[e]);
+            const uint32_t *vr = cv + (n * 8 + 2 * t) * LD + g;
+#pragma unroll
+            for (int d = 0; d < KS; ++d) mma_3x<ROUND>(part[d], p_hi, p_lo, vr[d * 8], vr[LD + d * 8]);
+            if (NT > 10 && n == NT / 2 - 1) {   // a long pass ends its accumulation chains half way, like a chunk
+#pragma unroll
+                for (int d = 0; d < KS; ++d) {
+                    acc[d][0] = fmaf(acc[d][0], alpha[0], part[d][0]);
+                    acc[d][1] = fmaf(acc[d][1], alpha[0], part[d][1]);
+                    acc[d][2] = fmaf(acc[d][2], alpha[1], part[d][2]);
+                    acc[d][3] = fmaf(acc[d][3], alpha[1], part[d][3]);
+                    part[d][0] = part[d][1] = part[d][2] = part[d][3] = 0.f;
+                }
+                alpha[0] = alpha[1] = 1.f;
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < KS; ++n) {
+            acc[n][0] = fmaf(acc[n][0], alpha[0], part[n][0]);
+            acc[n][1] = fmaf(acc[n][1], alpha[0], part[n][1]);
+            acc[n][2] = fmaf(acc[n][2], alpha[1], part[n][2]);
+            acc[n][3] = fmaf(acc[n][3], alpha[1], part[n][3]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float l = l_run[i];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const int row = i == 0 ? row_a : row_b;
+        if (row < P.Sq1) {
+            float *dst = o + (((int64_t)b * P.Sq1 + row) * P.HH + hh) * D + 2 * t;
+#pragma unroll
+            for (int n = 0; n < KS; ++n)
+                *reinterpret_cast<float2 *>(dst + n * 8) = make_float2(acc[n][2 * i] * inv, acc[n][2 * i + 1] * inv);
+        }
+    }
+}
+
+// NT = 0: the 64-key chunks; otherwise the per-warp walk in passes of NT tiles
+template <int D, bool ROUND, int NT>
 int launch_f(const Problem &p) {
+    constexpr bool DIAG = NT > 0;
     const int64_t dil = p.pat.dilation;
     WinFParams wp;
     wp.Sq1 = (int32_t)(p.Sq / dil);
@@ -245,8 +412,10 @@ int launch_f(const Problem &p) {
     wp.left = (int32_t)std::min<int64_t>(p.pat.left, wp.Skv1);
     wp.right = (int32_t)std::min<int64_t>(p.pat.right, wp.Skv1);
     wp.sl2 = p.scale * 1.4426950408889634f;
-    auto kern = window_f32_kernel<D, ROUND>;
-    constexpr size_t smem = (size_t)4 * kTK * (D + 4) * sizeof(float);
+    void (*kern)(const float *, const float *, const float *, float *, WinFParams);
+    if constexpr (DIAG) kern = window_f32_diag_kernel<D, ROUND, DIAG ? NT : 1>;
+    else kern = window_f32_kernel<D, ROUND>;
+    constexpr size_t smem = (size_t)(DIAG ? 2 * (48 + 8 * NT) : 4 * kTK) * (D + 4) * sizeof(float);
     if (int rc = ensure_dynamic_smem((const void *)kern, smem, "cudaFuncSetAttribute(window_f32_kernel)")) return rc;
     const dim3 grid((unsigned)wp.HH, (unsigned)((wp.Sq1 + kTQ - 1) / kTQ), (unsigned)p.B);
     kern<<<grid, kThreads, smem, p.stream>>>((const float *)p.q, (const float *)p.k, (const float *)p.v, (float *)p.o, wp);
@@ -277,8 +446,22 @@ bool mma_window_f32_supports(const Problem &p) {
 int launch_mma_window_f32(const Problem &p) {
     const int64_t dil = p.pat.dilation, skv1 = p.Skv / dil;
     const bool wide = std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) > 512;
-    if (wide) return p.D == 32 ? launch_f<32, true>(p) : launch_f<64, true>(p);
-    return p.D == 32 ? launch_f<32, false>(p) : launch_f<64, false>(p);
+    if (wide) return p.D == 32 ? launch_f<32, true, 0>(p) : launch_f<64, true, 0>(p);
+    // Keys a warp's 16 rows can see.  Up to 144 the warp walks its own range in one pass (6, 10 or 18 tiles: 32
+    // causal taps, 64 causal taps, the reference's default window of 64 either side), up to 160 in two passes of 10;
+    // wider windows keep the double-buffered chunks.  MAT_F32_KERNEL=chunks forces those (a measurement aid),
+    // MAT_F32_TILES=6|10|18 the pass length.
+    const int64_t span = std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16;
+    const char *force = std::getenv("MAT_F32_KERNEL");
+    int nt = span <= 48 ? 6 : span <= 80 ? 10 : span <= 144 ? 18 : span <= 160 ? 10 : 0;
+    if (force && std::strcmp(force, "chunks") == 0) nt = 0;
+    if (const char *t = std::getenv("MAT_F32_TILES"); t && nt) nt = std::atoi(t);
+    switch (nt) {
+    case 6: return p.D == 32 ? launch_f<32, false, 6>(p) : launch_f<64, false, 6>(p);
+    case 10: return p.D == 32 ? launch_f<32, false, 10>(p) : launch_f<64, false, 10>(p);
+    case 18: return p.D == 32 ? launch_f<32, false, 18>(p) : launch_f<64, false, 18>(p);
+    default: return p.D == 32 ? launch_f<32, false, 0>(p) : launch_f<64, false, 0>(p);
+    }
 }
 
 }  // namespace mat

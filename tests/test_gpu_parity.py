@@ -54,14 +54,15 @@ def test_cfg1_causal_window_fp32():
                                   PatternSpec(left=0, right=60), PatternSpec.causal_window(64, dilation=2),
                                   PatternSpec(left=100, right=28), PatternSpec.causal_window(1)],
                          ids=lambda s: f"l{s.left}r{s.right}d{s.dilation}")
-@pytest.mark.parametrize("kernel", ["default", "tiled"])
+@pytest.mark.parametrize("kernel", ["default", "chunks", "tiled"])
 def test_fp32_window_kernels_vs_oracle(monkeypatch, kernel, spec, D):
     """fp32 windows of at most 128 taps with head width 32, 64 or 128, ragged lengths and shard offsets included,
     at the fp32 bar of 1e-5: on the tensor cores as three TF32 products of error-compensated halves (head widths 32
-    and 64: the default), and on the tiled FMA-pipe kernel (64- or 128-row tiles, K/V window staged once per tile;
-    head width 128, and MAT_F32_KERNEL=tiled)."""
-    if kernel == "tiled":
-        monkeypatch.setenv("MAT_F32_KERNEL", "tiled")
+    and 64: the default, with every warp walking its own key range; MAT_F32_KERNEL=chunks keeps these windows on the
+    variant that walks 64-key chunks per tile, which wider windows use), and on the tiled FMA-pipe kernel (64- or
+    128-row tiles, K/V window staged once per tile; head width 128, and MAT_F32_KERNEL=tiled)."""
+    if kernel != "default":
+        monkeypatch.setenv("MAT_F32_KERNEL", kernel)
     for B, S, H, off in [(1, 1024, 2, 0), (2, 330, 3, 0), (1, 64, 1, 0), (1, 200, 2, 48), (1, 7, 1, 0)]:
         S = S - S % spec.dilation if S >= spec.dilation else spec.dilation
         off = off - off % spec.dilation
@@ -70,7 +71,7 @@ def test_fp32_window_kernels_vs_oracle(monkeypatch, kernel, spec, D):
         got = run(sp, q, k, v)
         skv1 = (S + off + 3 * spec.dilation) // spec.dilation          # taps clamp to the keys that exist
         wide_here = min(spec.left, skv1) + min(spec.right, skv1) > 64
-        if kernel == "default" and D != 128:
+        if kernel != "tiled" and D != 128:
             assert nat.last_kernel() == "mma_window_f32"
         else:
             assert nat.last_kernel() == ("rowwarp" if D == 128 and wide_here else "tiled_f32")
@@ -103,8 +104,8 @@ def test_fp32_wide_windows_on_tensor_cores(S, spec, D):
                                   PatternSpec.causal_window(1)],
                          ids=lambda s: f"l{s.left}r{s.right}d{s.dilation}")
 def test_16bit_windows_with_head_width_32_and_128(monkeypatch, spec, D):
-    """16-bit windows with a head width that is a multiple of 16 up to 128 (other than 64) on the warp-level tensor-core kernel (64-row tiles, 64-key chunks
-    through cp.async, online softmax): narrow, wide (several chunks), dense-as-window, dilated, ragged lengths,
+    """16-bit windows with a head width that is a multiple of 16 up to 128 (other than 64) on the warp-level tensor-core kernel (64-row tiles, keys
+    through cp.async, online softmax; per-warp key ranges for narrow windows, 64-key chunks for wide ones): narrow, wide (several chunks), dense-as-window, dilated, ragged lengths,
     shard offsets; and the one-warp-per-row kernel on the same inputs."""
     for dtype in (torch.bfloat16, torch.float16):
         for B, S, H, off in [(1, 1024, 2, 0), (2, 330, 3, 0), (1, 64, 1, 0), (1, 200, 2, 48), (1, 7, 1, 0)]:
@@ -115,6 +116,15 @@ def test_16bit_windows_with_head_width_32_and_128(monkeypatch, spec, D):
             got = run(sp, q, k, v)
             assert nat.last_kernel() == "mma_window_d"
             check_close(got, oracle_out(q, k, v, sp), dtype)
+    # narrow windows default to the variant in which every warp walks its own key range; the 64-key chunks on them
+    monkeypatch.setenv("MAT_WINDOW_D_KERNEL", "chunks")
+    for B, S, H, off in [(2, 330, 3, 0), (1, 200, 2, 48)]:
+        S, off = S - S % spec.dilation, off - off % spec.dilation
+        sp = spec.shifted(off)
+        q, k, v = seeded_qkv(29, B, S, H, D, torch.bfloat16, Skv=S + off + 3 * spec.dilation)
+        got = run(sp, q, k, v)
+        assert nat.last_kernel() == "mma_window_d"
+        check_close(got, oracle_out(q, k, v, sp), torch.bfloat16)
     monkeypatch.setenv("MAT_WINDOW_D_KERNEL", "rowwarp")
     q, k, v = seeded_qkv(30, 1, 330, 2, D, torch.bfloat16)
     got = run(spec, q, k, v)
