@@ -46,16 +46,22 @@ __device__ __forceinline__ float quad_sum(float x) {
 constexpr int kRows = 0, kColsV = 1, kColsK = 2;
 
 // PASS = kRows: tile rows are queries, columns keys.  kColsV / kColsK: tile rows are keys, columns queries.
-template <typename T, int D, int PASS>
+// NS = 0: the band is walked in 64-column chunks shared by the four warps (two buffers).  NS > 0, for narrow windows:
+// every warp walks the columns from a base of its own, the first column its first row meets, in passes of NS
+// 16-column steps, so that no step is without a visible column but the last of the walk (5 steps instead of 8 at 64
+// causal taps); the CTA stages the 48 + 16 NS rows the four warps' passes span, in one buffer.
+template <typename T, int D, int PASS, int NS>
 __global__ void __launch_bounds__(kThreads)
 bwd_d_kernel(const BwdDArgs a) {
     using M = ptx::Mma<T>;
     constexpr int LD = D + 8, KS = D / 16;   // padded row (elements); 16-wide steps of the head dimension
-    constexpr bool COLS = PASS != kRows;
+    constexpr bool COLS = PASS != kRows, DIAG = NS > 0;
+    constexpr int STEPS = DIAG ? NS : 4;                        // 16-column steps a warp takes per chunk or pass
+    constexpr int kRowsStaged = DIAG ? 48 + 16 * NS : 2 * kT;   // rows of each operand in shared memory
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    T *sY1 = reinterpret_cast<T *>(smem_raw);          // [2][kT][LD]: rows pass K, cols passes Q
-    T *sY2 = sY1 + 2 * kT * LD;                        // [2][kT][LD]: rows pass V, cols passes dO
-    float2 *sSt = reinterpret_cast<float2 *>(sY2 + 2 * kT * LD);   // cols passes: [2][kT] statistics of a chunk's queries
+    T *sY1 = reinterpret_cast<T *>(smem_raw);          // rows pass K, cols passes Q
+    T *sY2 = sY1 + kRowsStaged * LD;                   // rows pass V, cols passes dO
+    float2 *sSt = reinterpret_cast<float2 *>(sY2 + kRowsStaged * LD);   // cols passes: statistics of the staged queries
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int m4 = lane >> 3, r8 = lane & 7;
@@ -63,17 +69,32 @@ bwd_d_kernel(const BwdDArgs a) {
     const int back = COLS ? a.right : a.left, fwd = COLS ? a.left : a.right;   // row r sees columns r - back .. r + fwd
     const int col_lo = max(0, r0 - back);
     const int col_hi = min(a.S - 1, min(r0 + kT, a.S) - 1 + fwd);
-    const int n_chunks = col_hi >= col_lo ? (col_hi - col_lo) / kT + 1 : 0;
+    const int base_w = max(col_lo, r0 + 16 * warp - back);   // (NS > 0) the warp's first column
+    int n_chunks = 0;                                        // chunks, or passes of the warp with the longest walk
+    if (col_hi >= col_lo) {
+        if constexpr (DIAG) {
+#pragma unroll
+            for (int w = 0; w < kThreads / 32; ++w) {
+                const int cols_w = min(col_hi, r0 + 16 * w + 15 + fwd) - max(col_lo, r0 + 16 * w - back) + 1;
+                n_chunks = max(n_chunks, (cols_w + 16 * NS - 1) / (16 * NS));
+            }
+            n_chunks = min(n_chunks, (col_hi - col_lo) / (16 * NS) + 1);
+        } else {
+            n_chunks = (col_hi - col_lo) / kT + 1;
+        }
+    }
     const int64_t tok = (int64_t)a.HH * D;
     const int64_t head = ((int64_t)b * a.S * a.HH + hh) * D;
     const T *x1 = (const T *)(COLS ? a.k : a.q) + head, *x2 = (const T *)(COLS ? a.v : a.go) + head;
     const T *y1 = (const T *)(COLS ? a.q : a.k) + head, *y2 = (const T *)(COLS ? a.go : a.v) + head;
     const float2 *st_in = a.stats + ((int64_t)b * a.HH + hh) * a.S;
 
+    // chunk c into buffer buf (NS = 0), or the rows of pass c (warp 0's base is col_lo) into the one buffer
     auto load_chunk = [&](int c, int buf) {
         constexpr int kPieces = D / 8;
-        const int base = col_lo + c * kT;
-        for (int i = threadIdx.x; i < kT * kPieces; i += kThreads) {
+        constexpr int kStage = DIAG ? kRowsStaged : kT;
+        const int base = col_lo + c * (DIAG ? 16 * NS : kT);
+        for (int i = threadIdx.x; i < kStage * kPieces; i += kThreads) {
             const int r = i / kPieces, pc = i % kPieces;
             const int j = base + r;
             const bool in = j < a.S;   // rows past the end are zero-filled
@@ -81,12 +102,12 @@ bwd_d_kernel(const BwdDArgs a) {
             cp_async16(sY1 + (buf * kT + r) * LD + pc * 8, y1 + src, in ? 16 : 0);
             cp_async16(sY2 + (buf * kT + r) * LD + pc * 8, y2 + src, in ? 16 : 0);
         }
-        if (COLS && threadIdx.x < kT) {
+        if (COLS && threadIdx.x < kStage) {
             const int j = base + threadIdx.x;
             sSt[buf * kT + threadIdx.x] = j < a.S ? st_in[j] : make_float2(0.f, 0.f);
         }
     };
-    if (n_chunks > 0) load_chunk(0, 0);
+    if (!DIAG && n_chunks > 0) load_chunk(0, 0);
     cp_async_commit();
 
     // the warp's 16 tile rows as A fragments: rows g and g + 8, columns 2t, 2t+1 (+8) of each 16
@@ -149,17 +170,28 @@ bwd_d_kernel(const BwdDArgs a) {
 
     const int total = PASS == kRows ? 2 * n_chunks : n_chunks;   // the rows pass walks the keys twice
     for (int n = 0; n < total; ++n) {
-        const int c = n_chunks ? n % n_chunks : 0, buf = n & 1;
-        if (n + 1 < total) {
-            load_chunk((n + 1) % n_chunks, buf ^ 1);
-            cp_async_commit();
-            cp_async_wait<1>();
+        const int c = n_chunks ? n % n_chunks : 0, buf = DIAG ? 0 : n & 1;
+        if constexpr (DIAG) {
+            if (n == 0 || n_chunks > 1) {   // a one-pass walk keeps its rows for the second sweep
+                if (n) __syncthreads();     // the previous pass has been read
+                load_chunk(c, 0);
+                cp_async_commit();
+                cp_async_wait<0>();
+                __syncthreads();
+            }
         } else {
-            cp_async_wait<0>();
+            if (n + 1 < total) {
+                load_chunk((n + 1) % n_chunks, buf ^ 1);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncthreads();
         }
-        __syncthreads();
-        const int cb = col_lo + c * kT;   // the chunk's first column
-        const uint32_t cy1 = ptx::smem_u32(sY1 + buf * kT * LD), cy2 = ptx::smem_u32(sY2 + buf * kT * LD);
+        const int cb = DIAG ? base_w + c * 16 * NS : col_lo + c * kT;       // the first column of the warp's steps
+        const int st_off = DIAG ? cb - (col_lo + c * 16 * NS) : buf * kT;   // its row in shared memory
+        const uint32_t cy1 = ptx::smem_u32(sY1 + st_off * LD), cy2 = ptx::smem_u32(sY2 + st_off * LD);
 
         if (PASS == kRows && n == n_chunks) {   // between the sweeps: the statistics are complete
 #pragma unroll
@@ -177,10 +209,10 @@ bwd_d_kernel(const BwdDArgs a) {
         if (sweep_one) {
           if constexpr (PASS == kRows) {
             // ---- sweep one: running maximum, sum of exponentials, sum of exponentials x dP ----
-            float s[8][4];
+            float s[2 * STEPS][4];
             float cm[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int n2 = 0; n2 < 4; ++n2) {
+            for (int n2 = 0; n2 < STEPS; ++n2) {
                 product(s[2 * n2], s[2 * n2 + 1], xf1, cy1, n2);
 #pragma unroll
                 for (int h2 = 0; h2 < 2; ++h2)
@@ -202,7 +234,7 @@ bwd_d_kernel(const BwdDArgs a) {
                 msl[i] = m_new == -INFINITY ? 0.f : m_new * sl;
             }
 #pragma unroll
-            for (int n2 = 0; n2 < 4; ++n2) {
+            for (int n2 = 0; n2 < STEPS; ++n2) {
                 float dp[2][4];
                 product(dp[0], dp[1], xf2, cy2, n2);
 #pragma unroll
@@ -218,7 +250,7 @@ bwd_d_kernel(const BwdDArgs a) {
         } else {
             // ---- rows pass, sweep two: dS, dQ += dS K.  cols passes: P^T (and dS^T), dV += P^T dO / dK += dS^T Q ----
 #pragma unroll
-            for (int n2 = 0; n2 < 4; ++n2) {
+            for (int n2 = 0; n2 < STEPS; ++n2) {
                 float s[2][4], w[2][4];
                 product(s[0], s[1], xf1, cy1, n2);
                 float dp[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -229,7 +261,7 @@ bwd_d_kernel(const BwdDArgs a) {
                     for (int e = 0; e < 4; ++e) {
                         const int col = (2 * n2 + h2) * 8 + 2 * t + (e & 1);
                         // the query's statistics: the row's own (rows pass) or the column's (cols passes)
-                        const float2 sq = COLS ? sSt[buf * kT + col] : make_float2(lse[e >> 1], dsc[e >> 1]);
+                        const float2 sq = COLS ? sSt[st_off + col] : make_float2(lse[e >> 1], dsc[e >> 1]);
                         float p = ptx::ex2(fmaf(s[h2][e], sl, -sq.x));
                         if (!seen(cb + col, rows[e >> 1])) p = 0.f;
                         w[h2][e] = PASS == kColsV ? p : p * fmaf(dp[h2][e], a.scale, -sq.y);
@@ -237,7 +269,7 @@ bwd_d_kernel(const BwdDArgs a) {
                 accumulate(w[0], w[1], PASS == kColsV ? cy2 : cy1, n2);
             }
         }
-        __syncthreads();   // the buffer is free for the chunk after the next
+        if (!DIAG) __syncthreads();   // the buffer is free for the chunk after the next
     }
     if (PASS == kRows && n_chunks == 0 && t == 0) {   // rows that see no key
 #pragma unroll
@@ -256,33 +288,43 @@ bwd_d_kernel(const BwdDArgs a) {
     }
 }
 
-template <typename T, int D>
+template <typename T, int D, int NS>
 int launch_d(const BwdDArgs &a, int64_t B, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)4 * kT * (D + 8) * sizeof(T) + 2 * kT * sizeof(float2);
+    constexpr int kStaged = NS > 0 ? 48 + 16 * NS : 2 * kT;
+    constexpr size_t smem = (size_t)2 * kStaged * (D + 8) * sizeof(T) + kStaged * sizeof(float2);
     int rc;
-    if ((rc = ensure_dynamic_smem((const void *)bwd_d_kernel<T, D, kRows>, smem, "bwd_d rows")) != MAT_OK) return rc;
-    if ((rc = ensure_dynamic_smem((const void *)bwd_d_kernel<T, D, kColsV>, smem, "bwd_d dV")) != MAT_OK) return rc;
-    if ((rc = ensure_dynamic_smem((const void *)bwd_d_kernel<T, D, kColsK>, smem, "bwd_d dK")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_d_kernel<T, D, kRows, NS>, smem, "bwd_d rows")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_d_kernel<T, D, kColsV, NS>, smem, "bwd_d dV")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_d_kernel<T, D, kColsK, NS>, smem, "bwd_d dK")) != MAT_OK) return rc;
     const dim3 grid((unsigned)a.HH, (unsigned)((a.S + kT - 1) / kT), (unsigned)B);
-    bwd_d_kernel<T, D, kRows><<<grid, kThreads, smem, stream>>>(a);
-    bwd_d_kernel<T, D, kColsV><<<grid, kThreads, smem, stream>>>(a);
-    bwd_d_kernel<T, D, kColsK><<<grid, kThreads, smem, stream>>>(a);
+    bwd_d_kernel<T, D, kRows, NS><<<grid, kThreads, smem, stream>>>(a);
+    bwd_d_kernel<T, D, kColsV, NS><<<grid, kThreads, smem, stream>>>(a);
+    bwd_d_kernel<T, D, kColsK, NS><<<grid, kThreads, smem, stream>>>(a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "16-bit backward (other head widths) launch");
     note_kernel("bwd_d_mma");
     return MAT_OK;
 }
 
+// columns a warp's 16 rows meet: up to 160 the warp walks its own range in passes of 5 steps (one pass at 64 causal
+// taps); wider windows walk the 64-column chunks.  MAT_BWD_D_WALK=chunks forces those (a measurement aid).
+template <typename T, int D>
+int launch_walk(const BwdDArgs &a, int64_t B, cudaStream_t stream) {
+    const char *walk = std::getenv("MAT_BWD_D_WALK");
+    const bool own = a.left + a.right + 16 <= 160 && !(walk && std::strcmp(walk, "chunks") == 0);
+    return own ? launch_d<T, D, 5>(a, B, stream) : launch_d<T, D, 0>(a, B, stream);
+}
+
 template <typename T>
 int launch_any_d(const BwdDArgs &a, int64_t B, int64_t D, cudaStream_t stream) {
     switch (D) {
-        case 16: return launch_d<T, 16>(a, B, stream);
-        case 32: return launch_d<T, 32>(a, B, stream);
-        case 48: return launch_d<T, 48>(a, B, stream);
-        case 80: return launch_d<T, 80>(a, B, stream);
-        case 96: return launch_d<T, 96>(a, B, stream);
-        case 112: return launch_d<T, 112>(a, B, stream);
-        case 128: return launch_d<T, 128>(a, B, stream);
+        case 16: return launch_walk<T, 16>(a, B, stream);
+        case 32: return launch_walk<T, 32>(a, B, stream);
+        case 48: return launch_walk<T, 48>(a, B, stream);
+        case 80: return launch_walk<T, 80>(a, B, stream);
+        case 96: return launch_walk<T, 96>(a, B, stream);
+        case 112: return launch_walk<T, 112>(a, B, stream);
+        case 128: return launch_walk<T, 128>(a, B, stream);
     }
     return fail(MAT_ERR_UNSUPPORTED, "head width %lld has no instantiation of the warp-level backward", (long long)D);
 }

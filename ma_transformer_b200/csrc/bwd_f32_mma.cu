@@ -77,32 +77,53 @@ __device__ __forceinline__ float quad_sum(float x) {
 constexpr int kRows = 0, kColsV = 1, kColsK = 2;
 
 // PASS = kRows: tile rows are queries, columns keys.  kColsV / kColsK: tile rows are keys, columns queries.
-template <int D, int PASS>
+// NT = 0: the band is walked in 64-column chunks shared by the four warps (two buffers).  NT > 0, for narrow windows:
+// every warp walks the columns from a base of its own, the first column its first row meets, in passes of NT 8-column
+// tiles, so that no tile is without a visible column but the last of the walk (10 tiles instead of 16 at 64 causal
+// taps); the CTA stages the 48 + 8 NT rows the four warps' passes span, in one buffer.
+template <int D, int PASS, int NT>
 __global__ void __launch_bounds__(kThreads)
 bwd_f32_kernel(const BwdFArgs a) {
     constexpr int LD = D + 4, KS = D / 8;
-    constexpr bool COLS = PASS != kRows;
+    constexpr bool COLS = PASS != kRows, DIAG = NT > 0;
+    constexpr int TILES = DIAG ? NT : 8;                       // 8-column tiles a warp takes per chunk or pass
+    constexpr int kRowsStaged = DIAG ? 48 + 8 * NT : 2 * kT;   // rows of each operand in shared memory
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    float *sY1 = reinterpret_cast<float *>(smem_raw);   // [2][kT][LD]: rows pass K, cols passes Q
-    float *sY2 = sY1 + 2 * kT * LD;                     // [2][kT][LD]: rows pass V, cols passes dO
-    float2 *sSt = reinterpret_cast<float2 *>(sY2 + 2 * kT * LD);   // cols passes: [2][kT] statistics of a chunk's queries
+    float *sY1 = reinterpret_cast<float *>(smem_raw);   // rows pass K, cols passes Q
+    float *sY2 = sY1 + kRowsStaged * LD;                // rows pass V, cols passes dO
+    float2 *sSt = reinterpret_cast<float2 *>(sY2 + kRowsStaged * LD);   // cols passes: statistics of the staged queries
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int hh = blockIdx.x, b = blockIdx.z, r0 = blockIdx.y * kT;
     const int back = COLS ? a.right : a.left, fwd = COLS ? a.left : a.right;   // row r sees columns r - back .. r + fwd
     const int col_lo = max(0, r0 - back);
     const int col_hi = min(a.S - 1, min(r0 + kT, a.S) - 1 + fwd);
-    const int n_chunks = col_hi >= col_lo ? (col_hi - col_lo) / kT + 1 : 0;
+    const int base_w = max(col_lo, r0 + 16 * warp - back);   // (NT > 0) the warp's first column
+    int n_chunks = 0;                                        // chunks, or passes of the warp with the longest walk
+    if (col_hi >= col_lo) {
+        if constexpr (DIAG) {
+#pragma unroll
+            for (int w = 0; w < kThreads / 32; ++w) {
+                const int cols_w = min(col_hi, r0 + 16 * w + 15 + fwd) - max(col_lo, r0 + 16 * w - back) + 1;
+                n_chunks = max(n_chunks, (cols_w + 8 * NT - 1) / (8 * NT));
+            }
+            n_chunks = min(n_chunks, (col_hi - col_lo) / (8 * NT) + 1);
+        } else {
+            n_chunks = (col_hi - col_lo) / kT + 1;
+        }
+    }
     const int64_t tok = (int64_t)a.HH * D;
     const int64_t head = ((int64_t)b * a.S * a.HH + hh) * D;
     const float *x1 = (COLS ? a.k : a.q) + head, *x2 = (COLS ? a.v : a.go) + head;
     const float *y1 = (COLS ? a.q : a.k) + head, *y2 = (COLS ? a.go : a.v) + head;
     const float2 *st_in = a.stats + ((int64_t)b * a.HH + hh) * a.S;
 
+    // chunk c into buffer buf (NT = 0), or the rows of pass c (warp 0's base is col_lo) into the one buffer
     auto load_chunk = [&](int c, int buf) {
         constexpr int kPieces = D / 4;
-        const int base = col_lo + c * kT;
-        for (int i = threadIdx.x; i < kT * kPieces; i += kThreads) {
+        constexpr int kStage = DIAG ? kRowsStaged : kT;
+        const int base = col_lo + c * (DIAG ? 8 * NT : kT);
+        for (int i = threadIdx.x; i < kStage * kPieces; i += kThreads) {
             const int r = i / kPieces, pc = i % kPieces;
             const int j = base + r;
             const bool in = j < a.S;   // rows past the end are zero-filled
@@ -110,12 +131,12 @@ bwd_f32_kernel(const BwdFArgs a) {
             cp_async16(sY1 + (buf * kT + r) * LD + pc * 4, y1 + src, in ? 16 : 0);
             cp_async16(sY2 + (buf * kT + r) * LD + pc * 4, y2 + src, in ? 16 : 0);
         }
-        if (COLS && threadIdx.x < kT) {
+        if (COLS && threadIdx.x < kStage) {
             const int j = base + threadIdx.x;
             sSt[buf * kT + threadIdx.x] = j < a.S ? st_in[j] : make_float2(0.f, 0.f);
         }
     };
-    if (n_chunks > 0) load_chunk(0, 0);
+    if (!DIAG && n_chunks > 0) load_chunk(0, 0);
     cp_async_commit();
 
     // the warp's 16 tile rows as A fragments (rows g and g + 8, columns t and t + 4 of each 8)
@@ -175,18 +196,29 @@ bwd_f32_kernel(const BwdFArgs a) {
 
     const int total = PASS == kRows ? 2 * n_chunks : n_chunks;   // the rows pass walks the keys twice
     for (int n = 0; n < total; ++n) {
-        const int c = n_chunks ? n % n_chunks : 0, buf = n & 1;
-        if (n + 1 < total) {
-            load_chunk((n + 1) % n_chunks, buf ^ 1);
-            cp_async_commit();
-            cp_async_wait<1>();
+        const int c = n_chunks ? n % n_chunks : 0, buf = DIAG ? 0 : n & 1;
+        if constexpr (DIAG) {
+            if (n == 0 || n_chunks > 1) {   // a one-pass walk keeps its rows for the second sweep
+                if (n) __syncthreads();     // the previous pass has been read
+                load_chunk(c, 0);
+                cp_async_commit();
+                cp_async_wait<0>();
+                __syncthreads();
+            }
         } else {
-            cp_async_wait<0>();
+            if (n + 1 < total) {
+                load_chunk((n + 1) % n_chunks, buf ^ 1);
+                cp_async_commit();
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncthreads();
         }
-        __syncthreads();
-        const int cb = col_lo + c * kT;   // the chunk's first column
-        const uint32_t *cy1 = reinterpret_cast<const uint32_t *>(sY1 + buf * kT * LD);
-        const uint32_t *cy2 = reinterpret_cast<const uint32_t *>(sY2 + buf * kT * LD);
+        const int cb = DIAG ? base_w + c * 8 * NT : col_lo + c * kT;       // the first column of the warp's tiles
+        const int st_off = DIAG ? cb - (col_lo + c * 8 * NT) : buf * kT;   // its row in shared memory
+        const uint32_t *cy1 = reinterpret_cast<const uint32_t *>(sY1 + st_off * LD);
+        const uint32_t *cy2 = reinterpret_cast<const uint32_t *>(sY2 + st_off * LD);
 
         if (PASS == kRows && n == n_chunks) {   // between the sweeps: the statistics are complete
 #pragma unroll
@@ -208,10 +240,10 @@ bwd_f32_kernel(const BwdFArgs a) {
         if (sweep_one) {
           if constexpr (PASS == kRows) {
             // ---- sweep one: running maximum, sum of exponentials, sum of exponentials x dP ----
-            float s[8][4];
+            float s[TILES][4];
             float cm[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
+            for (int nt = 0; nt < TILES; ++nt) {
                 product(s[nt], xf1, cy1, nt);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -230,7 +262,7 @@ bwd_f32_kernel(const BwdFArgs a) {
                 msl[i] = m_new == -INFINITY ? 0.f : m_new * sl;
             }
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
+            for (int nt = 0; nt < TILES; ++nt) {
                 float dp[4];
                 product(dp, xf2, cy2, nt);
 #pragma unroll
@@ -244,7 +276,7 @@ bwd_f32_kernel(const BwdFArgs a) {
         } else {
             // ---- rows pass, sweep two: dS, dQ += dS K.  cols passes: P^T (and dS^T), dV += P^T dO / dK += dS^T Q ----
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
+            for (int nt = 0; nt < TILES; ++nt) {
                 float s[4], w[4];
                 product(s, xf1, cy1, nt);
                 float dp[4] = {0.f, 0.f, 0.f, 0.f};
@@ -253,7 +285,7 @@ bwd_f32_kernel(const BwdFArgs a) {
                 for (int e = 0; e < 4; ++e) {
                     const int col = nt * 8 + 2 * t + (e & 1);
                     // the query's statistics: the row's own (rows pass) or the column's (cols passes)
-                    const float2 sq = COLS ? sSt[buf * kT + col] : make_float2(lse[e >> 1], dsc[e >> 1]);
+                    const float2 sq = COLS ? sSt[st_off + col] : make_float2(lse[e >> 1], dsc[e >> 1]);
                     float p = ptx::ex2(fmaf(s[e], sl, -sq.x));
                     if (!seen(cb + col, rows[e >> 1])) p = 0.f;
                     w[e] = PASS == kColsV ? p : p * fmaf(dp[e], a.scale, -sq.y);
@@ -265,7 +297,7 @@ bwd_f32_kernel(const BwdFArgs a) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) acc[d][e] += part[d][e];
         }
-        __syncthreads();   // the buffer is free for the chunk after the next
+        if (!DIAG) __syncthreads();   // the buffer is free for the chunk after the next
     }
     if (PASS == kRows && n_chunks == 0 && t == 0) {   // rows that see no key
 #pragma unroll
@@ -283,17 +315,18 @@ bwd_f32_kernel(const BwdFArgs a) {
     }
 }
 
-template <int D>
+template <int D, int NT>
 int launch_f(const BwdFArgs &a, int64_t B, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)4 * kT * (D + 4) * sizeof(float) + 2 * kT * sizeof(float2);
+    constexpr int kStaged = NT > 0 ? 48 + 8 * NT : 2 * kT;
+    constexpr size_t smem = (size_t)2 * kStaged * (D + 4) * sizeof(float) + kStaged * sizeof(float2);
     int rc;
-    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_kernel<D, kRows>, smem, "bwd_f32 rows")) != MAT_OK) return rc;
-    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_kernel<D, kColsV>, smem, "bwd_f32 dV")) != MAT_OK) return rc;
-    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_kernel<D, kColsK>, smem, "bwd_f32 dK")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_kernel<D, kRows, NT>, smem, "bwd_f32 rows")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_kernel<D, kColsV, NT>, smem, "bwd_f32 dV")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_kernel<D, kColsK, NT>, smem, "bwd_f32 dK")) != MAT_OK) return rc;
     const dim3 grid((unsigned)a.HH, (unsigned)((a.S + kT - 1) / kT), (unsigned)B);
-    bwd_f32_kernel<D, kRows><<<grid, kThreads, smem, stream>>>(a);
-    bwd_f32_kernel<D, kColsV><<<grid, kThreads, smem, stream>>>(a);
-    bwd_f32_kernel<D, kColsK><<<grid, kThreads, smem, stream>>>(a);
+    bwd_f32_kernel<D, kRows, NT><<<grid, kThreads, smem, stream>>>(a);
+    bwd_f32_kernel<D, kColsV, NT><<<grid, kThreads, smem, stream>>>(a);
+    bwd_f32_kernel<D, kColsK, NT><<<grid, kThreads, smem, stream>>>(a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "fp32 tensor-core backward launch");
     note_kernel("bwd_f32_mma");
@@ -324,7 +357,12 @@ int launch_bwd_f32_mma(const void *q, const void *k, const void *v, const void *
     a.left = (int32_t)std::min<int64_t>(left, a.S);
     a.right = (int32_t)std::min<int64_t>(right, a.S);
     a.scale = scale;
-    return D == 32 ? launch_f<32>(a, B, stream) : launch_f<64>(a, B, stream);
+    // columns a warp's 16 rows meet: up to 160 the warp walks its own range in passes of 10 tiles (one pass at 64
+    // causal taps); wider windows walk the 64-column chunks.  MAT_BWD_F32_WALK=chunks forces those (a measurement aid).
+    const char *walk = std::getenv("MAT_BWD_F32_WALK");
+    const bool own = a.left + a.right + 16 <= 160 && !(walk && std::strcmp(walk, "chunks") == 0);
+    if (own) return D == 32 ? launch_f<32, 10>(a, B, stream) : launch_f<64, 10>(a, B, stream);
+    return D == 32 ? launch_f<32, 0>(a, B, stream) : launch_f<64, 0>(a, B, stream);
 }
 
 }  // namespace mat

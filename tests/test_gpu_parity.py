@@ -676,10 +676,15 @@ def test_backward_matches_autograd_of_reference_oracle(B, S, H, D, W):
     (1, 300, 2, 64, 64, 1), (1, 256, 2, 15, 0, 2), (2, 96, 1, 5, 5, 3), (1, 1000, 2, 1000, 1000, 1), (1, 1000, 1, 1000, 0, 1),
     (1, 700, 2, 300, 100, 1),
 ])
-def test_fp32_backward_on_tensor_cores(monkeypatch, B, S, H, left, right, dil, D):
+@pytest.mark.parametrize("walk", ["default", "chunks"])
+def test_fp32_backward_on_tensor_cores(monkeypatch, walk, B, S, H, left, right, dil, D):
     """The fp32 backward as three TF32 products per product (head widths 32 and 64): against autograd in fp64
     through a dense masked softmax at the fp32 kernels' bar (2e-5 of the gradient's scale), windows narrow, wide,
-    dilated, dense and causal dense, ragged lengths; and against the warp-level fp32 kernels."""
+    dilated, dense and causal dense, ragged lengths; and against the warp-level fp32 kernels.  Narrow windows
+    default to the walk in which every warp takes its own column range; MAT_BWD_F32_WALK=chunks keeps them on
+    the 64-column chunks the wide ones use."""
+    if walk == "chunks":
+        monkeypatch.setenv("MAT_BWD_F32_WALK", "chunks")
     spec = PatternSpec(left=left, right=right, dilation=dil)
     q, k, v = seeded_qkv(87, B, S, H, D, torch.float32)
     go = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(88))
@@ -709,11 +714,15 @@ def test_fp32_backward_on_tensor_cores(monkeypatch, B, S, H, left, right, dil, D
     (1, 512, 2, 63, 0, 1), (2, 200, 3, 32, 32, 1), (1, 33, 1, 8, 8, 1), (1, 70, 1, 40, 41, 1), (1, 300, 2, 64, 64, 1),
     (1, 256, 2, 15, 0, 2), (1, 600, 2, 600, 600, 1), (1, 600, 1, 600, 0, 1),
 ])
-def test_16bit_backward_for_other_head_widths(monkeypatch, dtype, D, B, S, H, left, right, dil):
+@pytest.mark.parametrize("walk", ["default", "chunks"])
+def test_16bit_backward_for_other_head_widths(monkeypatch, walk, dtype, D, B, S, H, left, right, dil):
     """The 16-bit backward for head widths that are multiples of 16 up to 128 other than 64 (the reference's
     kernel takes any width: src/cuda/sparse_attention_kernel.cu:265-346) on the warp-level tensor-core kernels:
     against autograd in fp64 through a dense masked softmax on the same rounded inputs, and against the
-    one-warp-per-row kernels."""
+    one-warp-per-row kernels.  Narrow windows default to the walk in which every warp takes its own column range;
+    MAT_BWD_D_WALK=chunks keeps them on the 64-column chunks the wide ones use."""
+    if walk == "chunks":
+        monkeypatch.setenv("MAT_BWD_D_WALK", "chunks")
     spec = PatternSpec(left=left, right=right, dilation=dil)
     q, k, v = seeded_qkv(89, B, S, H, D, dtype)
     go = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(90)).to(dtype)
