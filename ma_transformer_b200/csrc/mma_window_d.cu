@@ -204,7 +204,7 @@ window_d_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__res
 // instead of the 8 of two chunks), and the code is the same straight line for every warp.  The CTA stages the
 // 48 + 16 NS rows the four warps' passes span.
 template <typename T, int D, int NS>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, NS <= 5 ? 3 : 2)
 window_d_diag_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v, T *__restrict__ o,
                      const WinDParams P) {
     constexpr int LD = D + 8, KS = D / 16;
