@@ -29,6 +29,7 @@ struct WinFParams {
     int32_t HH;                // heads of the view
     int32_t left, right;
     float sl2;                 // scale * log2(e)
+    int32_t D;                 // head width (read by the kernel for wide heads only)
 };
 
 __device__ __forceinline__ void cp_async16(void *dst, const void *src, int bytes) {
@@ -399,6 +400,187 @@ window_f32_diag_kernel(const float *__restrict__ q, const float *__restrict__ k,
     }
 }
 
+// Wide heads (D = 128, 192, ... 512: the reference's layer passes one head of width model_dim,
+// src/layers/sparse_attention.py:71-78) with narrow windows: the per-warp walk of the kernel above in a single pass,
+// the head dimension taken 64 columns at a time.  The K slices stream through two buffers while the scores
+// accumulate, then the V slices while each 64-column slice of the output is formed from the finished weights,
+// normalised and written; the copy of the next slice is in flight during the products of the current one.
+// Registers hold the scores / weights of the pass (NT tiles) and one slice's operands, whatever D is.
+template <int NT>
+__global__ void __launch_bounds__(kThreads)
+window_f32_wide_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                       float *__restrict__ o, const WinFParams P) {
+    constexpr int LD = 64 + 4, KS = 8;
+    constexpr int kStage = 48 + 8 * NT;   // rows of a slice in shared memory
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    float *sBuf = reinterpret_cast<float *>(smem_raw);   // [2][kStage][LD]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int hh = blockIdx.x, b = blockIdx.z, q0 = blockIdx.y * kTQ;
+    const int D = P.D, n_slices = D >> 6;
+    const int p_first = q0 + P.off1;
+    const int key_lo = max(0, p_first - P.left);
+    const int key_hi = min(P.Skv1 - 1, min(q0 + kTQ, P.Sq1) - 1 + P.off1 + P.right);
+    const int base_w = max(key_lo, p_first + 16 * warp - P.left);   // the warp's first key
+    const int64_t tok = (int64_t)P.HH * D;
+    const float *kb_ptr = k + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+    const float *vb_ptr = v + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+    const int row_a = q0 + warp * 16 + g, row_b = row_a + 8;
+    const float *qa = q + (((int64_t)b * P.Sq1 + row_a) * P.HH + hh) * D;
+    const float *qb = q + (((int64_t)b * P.Sq1 + row_b) * P.HH + hh) * D;
+    float *oa = o + (((int64_t)b * P.Sq1 + row_a) * P.HH + hh) * D + 2 * t;
+    float *ob = o + (((int64_t)b * P.Sq1 + row_b) * P.HH + hh) * D + 2 * t;
+
+    if (key_hi < key_lo) {   // a tile whose rows see no key (the whole CTA alike): zeros
+        for (int c = 0; c < D; c += 8) {
+            if (row_a < P.Sq1) *reinterpret_cast<float2 *>(oa + c) = make_float2(0.f, 0.f);
+            if (row_b < P.Sq1) *reinterpret_cast<float2 *>(ob + c) = make_float2(0.f, 0.f);
+        }
+        return;
+    }
+    // copy i of the pass: K slice i, then V slice i - n_slices, into buffer i & 1
+    auto issue = [&](int i) {
+        const float *src_base = (i < n_slices ? kb_ptr : vb_ptr) + (i < n_slices ? i : i - n_slices) * 64;
+        float *dst = sBuf + (i & 1) * kStage * LD;
+        for (int x = threadIdx.x; x < kStage * 16; x += kThreads) {
+            const int r = x >> 4, pc = x & 15;
+            const int j = key_lo + r;
+            const bool in = j <= key_hi;   // rows past the tile's last key are zero-filled
+            cp_async16(dst + r * LD + pc * 4, src_base + (int64_t)(in ? j : 0) * tok + pc * 4, in ? 16 : 0);
+        }
+        cp_async_commit();
+    };
+    issue(0);
+    const int row_off = (base_w - key_lo) * LD;   // the warp's first key inside a buffer
+
+    float s[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    for (int sl = 0; sl < n_slices; ++sl) {
+        uint32_t qf[KS][4];
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int c = sl * 64 + ks * 8 + t;
+            qf[ks][0] = row_a < P.Sq1 ? __float_as_uint(qa[c]) : 0u;
+            qf[ks][1] = row_b < P.Sq1 ? __float_as_uint(qb[c]) : 0u;
+            qf[ks][2] = row_a < P.Sq1 ? __float_as_uint(qa[c + 4]) : 0u;
+            qf[ks][3] = row_b < P.Sq1 ? __float_as_uint(qb[c + 4]) : 0u;
+        }
+        issue(sl + 1);   // the next K slice, or the first V slice
+        cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t *ck = reinterpret_cast<const uint32_t *>(sBuf + (sl & 1) * kStage * LD + row_off);
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            uint32_t q_hi[4], q_lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) split_tf32<false>(qf[ks][e], q_hi[e], q_lo[e]);
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const uint32_t *kr = ck + (n * 8 + g) * LD + ks * 8 + t;
+                mma_3x<false>(s[n], q_hi, q_lo, kr[0], kr[4]);
+            }
+        }
+        __syncthreads();   // the buffer is free for the copy after the next
+    }
+    // ---- mask and softmax of the whole row (one pass: no running maximum) ----
+    const int pos[2] = {row_a + P.off1, row_b + P.off1};
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int j = base_w + n * 8 + 2 * t + (e & 1), p = pos[e >> 1];
+            const bool ok = j >= p - P.left && j <= p + P.right && j < P.Skv1;
+            s[n][e] = ok ? s[n][e] : -INFINITY;
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+        }
+    float l[2] = {0.f, 0.f}, mus[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+        mus[i] = mx[i] == -INFINITY ? 0.f : mx[i] * P.sl2;
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            s[n][e] = ptx::ex2(fmaf(s[n][e], P.sl2, -mus[e >> 1]));
+            l[e >> 1] += s[n][e];
+        }
+    float inv[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+        inv[i] = l[i] > 0.f ? 1.f / l[i] : 0.f;
+    }
+    // ---- the output, 64 columns at a time ----
+    for (int sl = 0; sl < n_slices; ++sl) {
+        const int i = n_slices + sl;
+        if (sl + 1 < n_slices) {
+            issue(i + 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t *cv = reinterpret_cast<const uint32_t *>(sBuf + (i & 1) * kStage * LD + row_off);
+        // two accumulation chains per output tile (the tensor core's fp32 sums are not rounded to nearest: chains
+        // stay at most 72 keys long), added at the end
+        float part[2][KS][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int d = 0; d < KS; ++d) part[h][d][0] = part[h][d][1] = part[h][d][2] = part[h][d][3] = 0.f;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            const uint32_t pa[4] = {__float_as_uint(s[n][0]), __float_as_uint(s[n][2]), __float_as_uint(s[n][1]),
+                                    __float_as_uint(s[n][3])};
+            uint32_t p_hi[4], p_lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) split_tf32<false>(pa[e], p_hi[e], p_lo[e]);
+            const uint32_t *vr = cv + (n * 8 + 2 * t) * LD + g;
+#pragma unroll
+            for (int d = 0; d < KS; ++d) mma_3x<false>(part[n < NT / 2 ? 0 : 1][d], p_hi, p_lo, vr[d * 8], vr[LD + d * 8]);
+        }
+#pragma unroll
+        for (int d = 0; d < KS; ++d) {
+            if (row_a < P.Sq1)
+                *reinterpret_cast<float2 *>(oa + sl * 64 + d * 8) =
+                    make_float2((part[0][d][0] + part[1][d][0]) * inv[0], (part[0][d][1] + part[1][d][1]) * inv[0]);
+            if (row_b < P.Sq1)
+                *reinterpret_cast<float2 *>(ob + sl * 64 + d * 8) =
+                    make_float2((part[0][d][2] + part[1][d][2]) * inv[1], (part[0][d][3] + part[1][d][3]) * inv[1]);
+        }
+        __syncthreads();   // the buffer is free for the copy after the next
+    }
+}
+
+template <int NT>
+int launch_wide(const Problem &p) {
+    const int64_t dil = p.pat.dilation;
+    WinFParams wp;
+    wp.Sq1 = (int32_t)(p.Sq / dil);
+    wp.Skv1 = (int32_t)(p.Skv / dil);
+    wp.off1 = (int32_t)(p.pat.q_offset / dil);
+    wp.HH = (int32_t)(p.H * dil);
+    wp.left = (int32_t)std::min<int64_t>(p.pat.left, wp.Skv1);
+    wp.right = (int32_t)std::min<int64_t>(p.pat.right, wp.Skv1);
+    wp.sl2 = p.scale * 1.4426950408889634f;
+    wp.D = (int32_t)p.D;
+    auto kern = window_f32_wide_kernel<NT>;
+    constexpr size_t smem = (size_t)2 * (48 + 8 * NT) * 68 * sizeof(float);
+    if (int rc = ensure_dynamic_smem((const void *)kern, smem, "cudaFuncSetAttribute(window_f32_wide_kernel)")) return rc;
+    const dim3 grid((unsigned)wp.HH, (unsigned)((wp.Sq1 + kTQ - 1) / kTQ), (unsigned)p.B);
+    kern<<<grid, kThreads, smem, p.stream>>>((const float *)p.q, (const float *)p.k, (const float *)p.v, (float *)p.o, wp);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "window_f32_wide_kernel launch");
+    note_kernel("mma_window_f32");
+    return MAT_OK;
+}
+
 // NT = 0: the 64-key chunks; otherwise the per-warp walk in passes of NT tiles
 template <int D, bool ROUND, int NT>
 int launch_f(const Problem &p) {
@@ -412,6 +594,7 @@ int launch_f(const Problem &p) {
     wp.left = (int32_t)std::min<int64_t>(p.pat.left, wp.Skv1);
     wp.right = (int32_t)std::min<int64_t>(p.pat.right, wp.Skv1);
     wp.sl2 = p.scale * 1.4426950408889634f;
+    wp.D = (int32_t)p.D;
     void (*kern)(const float *, const float *, const float *, float *, WinFParams);
     if constexpr (DIAG) kern = window_f32_diag_kernel<D, ROUND, DIAG ? NT : 1>;
     else kern = window_f32_kernel<D, ROUND>;
@@ -427,11 +610,20 @@ int launch_f(const Problem &p) {
 
 }  // namespace
 
-// fp32 window patterns (any taps, any dilation that divides the lengths) with head width 32 or 64, whole tensors,
-// 16-byte aligned.  MAT_F32_KERNEL=tiled keeps them on the FMA-pipe kernel (a measurement aid).
+// keys a warp's 16 rows can see
+static int64_t warp_span(const Problem &p) {
+    const int64_t skv1 = p.Skv / p.pat.dilation;
+    return std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16;
+}
+
+// fp32 window patterns (any taps, any dilation that divides the lengths) with head width 32 or 64, and windows of at
+// most 128 taps between their two sides with a head width of 128, 192, ... 512; whole tensors, 16-byte aligned.
+// MAT_F32_KERNEL=tiled keeps them on the FMA-pipe kernels (a measurement aid).
 bool mma_window_f32_supports(const Problem &p) {
     if (p.pat.kind != MAT_WINDOW || p.dtype != MAT_F32) return false;
-    if (p.D != 32 && p.D != 64) return false;
+    const bool wide_head = p.D > 64 && p.D <= 512 && p.D % 64 == 0;
+    if (p.D != 32 && p.D != 64 && !wide_head) return false;
+    if (wide_head && (p.pat.dilation < 1 || warp_span(p) > 144)) return false;
     if (p.k_prev || p.k_next || p.q_ts || p.k_ts || p.v_ts || p.o_ts) return false;
     const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
     if (al % 16) return false;
@@ -444,6 +636,9 @@ bool mma_window_f32_supports(const Problem &p) {
 }
 
 int launch_mma_window_f32(const Problem &p) {
+    if (p.D > 64) return warp_span(p) <= 80 ? launch_wide<10>(p) : launch_wide<18>(p);
+    if (const char *f = std::getenv("MAT_F32_KERNEL"); f && std::strcmp(f, "sliced") == 0 && p.D == 64 && warp_span(p) <= 144)
+        return warp_span(p) <= 80 ? launch_wide<10>(p) : launch_wide<18>(p);   // (a measurement aid)
     const int64_t dil = p.pat.dilation, skv1 = p.Skv / dil;
     const bool wide = std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) > 512;
     if (wide) return p.D == 32 ? launch_f<32, true, 0>(p) : launch_f<64, true, 0>(p);

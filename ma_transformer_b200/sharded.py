@@ -240,8 +240,11 @@ class PeerHaloAttention:
     ``register`` is collective: every rank passes its own contiguous [B, rows, H, 64]
     K and V once; CUDA IPC handles go to the neighbours, which map them.  The tensors
     must then be updated in place.  Ordering is the caller's: a rank may launch
-    ``forward`` only when its neighbours' K/V for that step are complete (a
-    ``dist.barrier()`` or a stream-ordered flag in a pipeline; static K/V need nothing).
+    ``forward`` only when its neighbours' K/V for that step are complete, and may rewrite
+    its own K/V only when its neighbours' kernels of the previous step have read them.
+    Static K/V need nothing; a pipeline that rewrites K/V in place calls ``step_barrier``
+    after the writes and again after the forward (or orders the steps some other way, e.g.
+    with a stream-ordered flag).
     """
 
     def __init__(self, spec: PatternSpec, seq_len: int, group: Optional[dist.ProcessGroup] = None):
@@ -295,6 +298,14 @@ class PeerHaloAttention:
         next_kv = open_neighbour(self.rank + 1) if self.rank < self.world - 1 and self.spec.right else None
         dist.barrier(group=self.group)   # every mapping exists before anyone may free or reuse memory
         return PeerShard(k_local, v_local, prev_kv, next_kv)
+
+    def step_barrier(self) -> None:
+        """Collective.  Everything this rank has enqueued on its current stream (writes of its K/V
+        chunk, or a ``forward`` that reads the neighbours' chunks) completes, then all ranks meet:
+        after it a neighbour's rows are safe to read, or this rank's rows are safe to rewrite.
+        Host-side (a stream synchronise and a barrier of the group), so it costs a launch gap."""
+        torch.cuda.current_stream().synchronize()
+        dist.barrier(group=self.group)
 
     def close(self) -> None:
         """Unmaps every neighbour allocation this object opened (collective use not required)."""

@@ -49,16 +49,16 @@ def test_cfg1_causal_window_fp32():
     check_close(run(spec, q, k, v, scale=0.125), oracle_out(q, k, v, spec, 0.125), torch.float32)
 
 
-@pytest.mark.parametrize("D", [32, 64, 128])
+@pytest.mark.parametrize("D", [32, 64, 128, 256])
 @pytest.mark.parametrize("spec", [PatternSpec.causal_window(32), PatternSpec.sliding_window(64), PatternSpec.sliding_window(3),
                                   PatternSpec(left=0, right=60), PatternSpec.causal_window(64, dilation=2),
                                   PatternSpec(left=100, right=28), PatternSpec.causal_window(1)],
                          ids=lambda s: f"l{s.left}r{s.right}d{s.dilation}")
 @pytest.mark.parametrize("kernel", ["default", "chunks", "tiled"])
 def test_fp32_window_kernels_vs_oracle(monkeypatch, kernel, spec, D):
-    """fp32 windows of at most 128 taps with head width 32, 64 or 128, ragged lengths and shard offsets included,
-    at the fp32 bar of 1e-5: on the tensor cores as three TF32 products of error-compensated halves (head widths 32
-    and 64: the default, with every warp walking its own key range; MAT_F32_KERNEL=chunks keeps these windows on the
+    """fp32 windows of at most 128 taps with head width 32, 64, 128 or 256, ragged lengths and shard offsets included,
+    at the fp32 bar of 1e-5: on the tensor cores as three TF32 products of error-compensated halves (the default, with
+    every warp walking its own key range, wide heads 64 columns at a time; MAT_F32_KERNEL=chunks keeps these windows on the
     variant that walks 64-key chunks per tile, which wider windows use), and on the tiled FMA-pipe kernel (64- or
     128-row tiles, K/V window staged once per tile; head width 128, and MAT_F32_KERNEL=tiled)."""
     if kernel != "default":
@@ -71,10 +71,10 @@ def test_fp32_window_kernels_vs_oracle(monkeypatch, kernel, spec, D):
         got = run(sp, q, k, v)
         skv1 = (S + off + 3 * spec.dilation) // spec.dilation          # taps clamp to the keys that exist
         wide_here = min(spec.left, skv1) + min(spec.right, skv1) > 64
-        if kernel != "tiled" and D != 128:
+        if kernel != "tiled":   # (head widths 128 and 256: 64 columns at a time, these windows in one pass per warp)
             assert nat.last_kernel() == "mma_window_f32"
         else:
-            assert nat.last_kernel() == ("rowwarp" if D == 128 and wide_here else "tiled_f32")
+            assert nat.last_kernel() == ("rowwarp" if (D == 128 and wide_here) or D == 256 else "tiled_f32")
         check_close(got, oracle_out(q, k, v, sp), torch.float32)
     # inputs x100 stay finite and close (tests/integration/test_cuda_extensive.py:77-92)
     q, k, v = seeded_qkv(24, 1, 130, 2, D, torch.float32, scale=100.0)
