@@ -33,6 +33,7 @@ struct WinDParams {
     int32_t HH;                // heads of the view
     int32_t left, right;
     float sl2;                 // scale * log2(e)
+    int32_t D;                 // head width (read by the kernel for wide heads only)
 };
 
 __device__ __forceinline__ void cp_async16(void *dst, const void *src, int bytes) {
@@ -353,6 +354,184 @@ window_d_diag_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
     }
 }
 
+// Wide heads (D = 192, 256, ... 512) with narrow windows: the per-warp walk of the kernel above in a single pass, the
+// head dimension taken 64 columns at a time.  The K slices stream through two buffers while the scores accumulate,
+// then the V slices while each 64-column slice of the output is formed from the finished weights, normalised and
+// written; the copy of the next slice is in flight during the products of the current one.  Registers hold the
+// scores / weights of the pass and one slice's operands, whatever D is.
+template <typename T, int NS>
+__global__ void __launch_bounds__(kThreads)
+window_d_wide_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v, T *__restrict__ o,
+                     const WinDParams P) {
+    constexpr int LD = 64 + 8, KS = 4;
+    constexpr int kStage = 48 + 16 * NS;   // rows of a slice in shared memory
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    T *sBuf = reinterpret_cast<T *>(smem_raw);   // [2][kStage][LD]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int m4 = lane >> 3, r8 = lane & 7;
+    const int hh = blockIdx.x, b = blockIdx.z, q0 = blockIdx.y * kTQ;
+    const int D = P.D, n_slices = D >> 6;
+    const int p_first = q0 + P.off1;
+    const int key_lo = max(0, p_first - P.left);
+    const int key_hi = min(P.Skv1 - 1, min(q0 + kTQ, P.Sq1) - 1 + P.off1 + P.right);
+    const int base_w = max(key_lo, p_first + 16 * warp - P.left);   // the warp's first key
+    const int64_t tok = (int64_t)P.HH * D;
+    const T *kb_ptr = k + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+    const T *vb_ptr = v + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+    const int row_a = q0 + warp * 16 + g, row_b = row_a + 8;
+    const T *qa = q + (((int64_t)b * P.Sq1 + row_a) * P.HH + hh) * D;
+    const T *qb = q + (((int64_t)b * P.Sq1 + row_b) * P.HH + hh) * D;
+    T *oa = o + (((int64_t)b * P.Sq1 + row_a) * P.HH + hh) * D + 2 * t;
+    T *ob = o + (((int64_t)b * P.Sq1 + row_b) * P.HH + hh) * D + 2 * t;
+
+    if (key_hi < key_lo) {   // a tile whose rows see no key (the whole CTA alike): zeros
+        for (int c = 0; c < D; c += 8) {
+            if (row_a < P.Sq1) *reinterpret_cast<uint32_t *>(oa + c) = 0u;
+            if (row_b < P.Sq1) *reinterpret_cast<uint32_t *>(ob + c) = 0u;
+        }
+        return;
+    }
+    // copy i of the pass: K slice i, then V slice i - n_slices, into buffer i & 1
+    auto issue = [&](int i) {
+        const T *src_base = (i < n_slices ? kb_ptr : vb_ptr) + (i < n_slices ? i : i - n_slices) * 64;
+        T *dst = sBuf + (i & 1) * kStage * LD;
+        for (int x = threadIdx.x; x < kStage * 8; x += kThreads) {
+            const int r = x >> 3, pc = x & 7;
+            const int j = key_lo + r;
+            const bool in = j <= key_hi;   // rows past the tile's last key are zero-filled
+            cp_async16(dst + r * LD + pc * 8, src_base + (int64_t)(in ? j : 0) * tok + pc * 8, in ? 16 : 0);
+        }
+        cp_async_commit();
+    };
+    issue(0);
+    const int row_off = (base_w - key_lo) * LD;   // the warp's first key inside a buffer
+
+    float s[2 * NS][4];
+#pragma unroll
+    for (int n = 0; n < 2 * NS; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    for (int sl = 0; sl < n_slices; ++sl) {
+        uint32_t qf[KS][4];
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int c = sl * 64 + ks * 16 + 2 * t;
+            qf[ks][0] = row_a < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qa + c) : 0u;
+            qf[ks][1] = row_b < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qb + c) : 0u;
+            qf[ks][2] = row_a < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qa + c + 8) : 0u;
+            qf[ks][3] = row_b < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qb + c + 8) : 0u;
+        }
+        issue(sl + 1);   // the next K slice, or the first V slice
+        cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t k_addr = ptx::smem_u32(sBuf + (sl & 1) * kStage * LD + row_off);
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int n2 = 0; n2 < NS; ++n2) {
+                uint32_t kf[4];
+                ptx::ldmatrix_x4(kf, k_addr + (uint32_t)(((n2 * 16 + r8 + (m4 >> 1) * 8) * LD + ks * 16 + (m4 & 1) * 8) * 2));
+                ptx::Mma<T>::run(s[2 * n2], qf[ks], kf[0], kf[1]);
+                ptx::Mma<T>::run(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
+            }
+        }
+        __syncthreads();   // the buffer is free for the copy after the next
+    }
+    // ---- mask and softmax of the whole row (one pass: no running maximum) ----
+    const int pos[2] = {row_a + P.off1, row_b + P.off1};
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 2 * NS; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int j = base_w + n * 8 + 2 * t + (e & 1), p = pos[e >> 1];
+            const bool ok = j >= p - P.left && j <= p + P.right && j < P.Skv1;
+            s[n][e] = ok ? s[n][e] : -INFINITY;
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+        }
+    float l[2] = {0.f, 0.f}, mus[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+        mus[i] = mx[i] == -INFINITY ? 0.f : mx[i] * P.sl2;
+    }
+    uint32_t pa[NS][4];   // the weights as A fragments of the 16-key steps of P V
+#pragma unroll
+    for (int n = 0; n < 2 * NS; ++n) {
+        float w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            w[e] = ptx::ex2(fmaf(s[n][e], P.sl2, -mus[e >> 1]));
+            l[e >> 1] += w[e];
+        }
+        pa[n >> 1][(n & 1) * 2] = ptx::Mma<T>::pack(w[0], w[1]);
+        pa[n >> 1][(n & 1) * 2 + 1] = ptx::Mma<T>::pack(w[2], w[3]);
+    }
+    float inv[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+        inv[i] = l[i] > 0.f ? 1.f / l[i] : 0.f;
+    }
+    // ---- the output, 64 columns at a time ----
+    for (int sl = 0; sl < n_slices; ++sl) {
+        const int i = n_slices + sl;
+        if (sl + 1 < n_slices) {
+            issue(i + 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t v_addr = ptx::smem_u32(sBuf + (i & 1) * kStage * LD + row_off);
+        float acc[2 * KS][4];
+#pragma unroll
+        for (int n = 0; n < 2 * KS; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < NS; ++kk) {
+#pragma unroll
+            for (int d2 = 0; d2 < KS; ++d2) {
+                uint32_t vf[4];
+                ptx::ldmatrix_x4_trans(vf, v_addr + (uint32_t)(((kk * 16 + r8 + (m4 & 1) * 8) * LD + d2 * 16 + (m4 >> 1) * 8) * 2));
+                ptx::Mma<T>::run(acc[2 * d2], pa[kk], vf[0], vf[1]);
+                ptx::Mma<T>::run(acc[2 * d2 + 1], pa[kk], vf[2], vf[3]);
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < 2 * KS; ++n) {
+            if (row_a < P.Sq1)
+                *reinterpret_cast<uint32_t *>(oa + sl * 64 + n * 8) = ptx::Mma<T>::pack(acc[n][0] * inv[0], acc[n][1] * inv[0]);
+            if (row_b < P.Sq1)
+                *reinterpret_cast<uint32_t *>(ob + sl * 64 + n * 8) = ptx::Mma<T>::pack(acc[n][2] * inv[1], acc[n][3] * inv[1]);
+        }
+        __syncthreads();   // the buffer is free for the copy after the next
+    }
+}
+
+template <typename T, int NS>
+int launch_wide(const Problem &p) {
+    const int64_t dil = p.pat.dilation;
+    WinDParams wp;
+    wp.Sq1 = (int32_t)(p.Sq / dil);
+    wp.Skv1 = (int32_t)(p.Skv / dil);
+    wp.off1 = (int32_t)(p.pat.q_offset / dil);
+    wp.HH = (int32_t)(p.H * dil);
+    wp.left = (int32_t)std::min<int64_t>(p.pat.left, wp.Skv1);
+    wp.right = (int32_t)std::min<int64_t>(p.pat.right, wp.Skv1);
+    wp.sl2 = p.scale * 1.4426950408889634f;
+    wp.D = (int32_t)p.D;
+    auto kern = window_d_wide_kernel<T, NS>;
+    constexpr size_t smem = (size_t)2 * (48 + 16 * NS) * 72 * sizeof(T);
+    if (int rc = ensure_dynamic_smem((const void *)kern, smem, "cudaFuncSetAttribute(window_d_wide_kernel)")) return rc;
+    const dim3 grid((unsigned)wp.HH, (unsigned)((wp.Sq1 + kTQ - 1) / kTQ), (unsigned)p.B);
+    kern<<<grid, kThreads, smem, p.stream>>>((const T *)p.q, (const T *)p.k, (const T *)p.v, (T *)p.o, wp);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "window_d_wide_kernel launch");
+    note_kernel("mma_window_d");
+    return MAT_OK;
+}
+
 // NS = 0: the 64-key chunks; otherwise the per-warp walk in passes of NS 16-key steps
 template <typename T, int D, int NS>
 int launch_d(const Problem &p) {
@@ -365,6 +544,7 @@ int launch_d(const Problem &p) {
     wp.left = (int32_t)std::min<int64_t>(p.pat.left, wp.Skv1);
     wp.right = (int32_t)std::min<int64_t>(p.pat.right, wp.Skv1);
     wp.sl2 = p.scale * 1.4426950408889634f;
+    wp.D = (int32_t)p.D;
     void (*kern)(const T *, const T *, const T *, T *, WinDParams);
     if constexpr (NS > 0) kern = window_d_diag_kernel<T, D, (NS > 0 ? NS : 1)>;
     else kern = window_d_kernel<T, D>;
@@ -387,7 +567,12 @@ int launch_d(const Problem &p) {
 bool mma_window_d_supports(const Problem &p) {
     if (p.pat.kind != MAT_WINDOW) return false;
     if (p.dtype != MAT_BF16 && p.dtype != MAT_F16) return false;
-    if (p.D % 16 || p.D < 16 || p.D > 128 || p.D == 64) return false;   // (64: the TMA / tcgen05 kernels)
+    if (p.D % 16 || p.D < 16 || p.D == 64) return false;   // (64: the TMA / tcgen05 kernels)
+    if (p.D > 128) {   // wide heads: multiples of 64 up to 512, windows one pass of a warp covers (at most 128 taps between the sides)
+        if (p.D > 512 || p.D % 64 || p.pat.dilation < 1) return false;
+        const int64_t skv1 = p.Skv / p.pat.dilation;
+        if (std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16 > 144) return false;
+    }
     if (p.k_prev || p.k_next || p.q_ts || p.k_ts || p.v_ts || p.o_ts) return false;
     const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
     if (al % 16) return false;
@@ -428,6 +613,18 @@ int launch_any_d(const Problem &p) {
 }
 
 int launch_mma_window_d(const Problem &p) {
+    // a head of 128 columns with a narrow window also goes 64 columns at a time: 79 against 86 us at 65536 tokens x 4
+    // heads, 64 causal taps (124 registers instead of 168); MAT_WINDOW_D_KERNEL=whole or chunks keeps it in one piece
+    const char *force = std::getenv("MAT_WINDOW_D_KERNEL");
+    const bool sliced128 = p.D == 128 && !(force && (std::strcmp(force, "whole") == 0 || std::strcmp(force, "chunks") == 0)) &&
+                           std::min<int64_t>(p.pat.left, p.Skv / p.pat.dilation) +
+                               std::min<int64_t>(p.pat.right, p.Skv / p.pat.dilation) + 16 <= 144;
+    if (p.D > 128 || sliced128) {
+        const int64_t skv1 = p.Skv / p.pat.dilation;
+        const bool five = std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16 <= 80;
+        if (p.dtype == MAT_BF16) return five ? launch_wide<__nv_bfloat16, 5>(p) : launch_wide<__nv_bfloat16, 9>(p);
+        return five ? launch_wide<__half, 5>(p) : launch_wide<__half, 9>(p);
+    }
     return p.dtype == MAT_BF16 ? launch_any_d<__nv_bfloat16>(p) : launch_any_d<__half>(p);
 }
 

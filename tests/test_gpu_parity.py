@@ -116,20 +116,47 @@ def test_16bit_windows_with_head_width_32_and_128(monkeypatch, spec, D):
             got = run(sp, q, k, v)
             assert nat.last_kernel() == "mma_window_d"
             check_close(got, oracle_out(q, k, v, sp), dtype)
-    # narrow windows default to the variant in which every warp walks its own key range; the 64-key chunks on them
-    monkeypatch.setenv("MAT_WINDOW_D_KERNEL", "chunks")
-    for B, S, H, off in [(2, 330, 3, 0), (1, 200, 2, 48)]:
-        S, off = S - S % spec.dilation, off - off % spec.dilation
-        sp = spec.shifted(off)
-        q, k, v = seeded_qkv(29, B, S, H, D, torch.bfloat16, Skv=S + off + 3 * spec.dilation)
-        got = run(sp, q, k, v)
-        assert nat.last_kernel() == "mma_window_d"
-        check_close(got, oracle_out(q, k, v, sp), torch.bfloat16)
+    # narrow windows default to the variant in which every warp walks its own key range (a head of 128 columns 64
+    # columns at a time; "whole" keeps it in one piece); the 64-key chunks on them
+    for force in ("chunks", "whole"):
+        monkeypatch.setenv("MAT_WINDOW_D_KERNEL", force)
+        for B, S, H, off in [(2, 330, 3, 0), (1, 200, 2, 48)]:
+            S, off = S - S % spec.dilation, off - off % spec.dilation
+            sp = spec.shifted(off)
+            q, k, v = seeded_qkv(29, B, S, H, D, torch.bfloat16, Skv=S + off + 3 * spec.dilation)
+            got = run(sp, q, k, v)
+            assert nat.last_kernel() == "mma_window_d"
+            check_close(got, oracle_out(q, k, v, sp), torch.bfloat16)
     monkeypatch.setenv("MAT_WINDOW_D_KERNEL", "rowwarp")
     q, k, v = seeded_qkv(30, 1, 330, 2, D, torch.bfloat16)
     got = run(spec, q, k, v)
     assert nat.last_kernel() == "rowwarp"
     check_close(got, oracle_out(q, k, v, spec), torch.bfloat16)
+
+
+@pytest.mark.parametrize("D", [192, 256, 512])
+@pytest.mark.parametrize("spec", [PatternSpec.causal_window(64), PatternSpec.sliding_window(64), PatternSpec.sliding_window(3),
+                                  PatternSpec(left=0, right=60), PatternSpec.causal_window(32, dilation=2),
+                                  PatternSpec(left=100, right=28), PatternSpec.causal_window(1)],
+                         ids=lambda s: f"l{s.left}r{s.right}d{s.dilation}")
+def test_16bit_windows_with_wide_heads(spec, D):
+    """16-bit windows of at most 128 taps between their sides with one wide head (the reference's layer passes
+    D = model_dim, src/layers/sparse_attention.py:71-78): the head dimension goes through the warp-level tensor-core
+    kernel 64 columns at a time.  Wider windows on such heads stay on the one-warp-per-row kernel."""
+    for dtype in (torch.bfloat16, torch.float16):
+        for B, S, H, off in [(1, 1024, 1, 0), (2, 330, 2, 0), (1, 64, 1, 0), (1, 200, 2, 48), (1, 7, 1, 0)]:
+            S = S - S % spec.dilation if S >= spec.dilation else spec.dilation
+            off = off - off % spec.dilation
+            sp = spec.shifted(off)
+            q, k, v = seeded_qkv(33, B, S, H, D, dtype, Skv=S + off + 3 * spec.dilation)
+            got = run(sp, q, k, v)
+            assert nat.last_kernel() == "mma_window_d"
+            check_close(got, oracle_out(q, k, v, sp), dtype)
+    q, k, v = seeded_qkv(34, 1, 330, 1, D, torch.bfloat16)
+    wide = PatternSpec.causal_window(300)
+    got = run(wide, q, k, v)
+    assert nat.last_kernel() == "rowwarp"
+    check_close(got, oracle_out(q, k, v, wide), torch.bfloat16)
 
 
 @pytest.mark.parametrize("B,S,H,D", [(1, 1, 1, 1), (1, 7, 2, 5), (2, 33, 1, 13), (1, 100, 3, 40), (1, 65, 2, 96),
@@ -140,8 +167,12 @@ def test_rowwarp_odd_shapes(B, S, H, D, dtype):
                  PatternSpec(left=2, right=5, dilation=2)):
         q, k, v = seeded_qkv(7, B, S, H, D, dtype)
         check_close(run(spec, q, k, v), oracle_out(q, k, v, spec), dtype)
-        on_mma = dtype != torch.float32 and D % 16 == 0 and D <= 128 and S % spec.dilation == 0
-        assert nat.last_kernel() == ("mma_window_d" if on_mma else "rowwarp")
+        whole = S % spec.dilation == 0   # (these windows are narrow: wide heads in multiples of 64 go 64 columns at a time)
+        if dtype == torch.float32:
+            want = "mma_window_f32" if whole and D % 64 == 0 else "rowwarp"
+        else:
+            want = "mma_window_d" if whole and (D % 64 == 0 or (D % 16 == 0 and D <= 128)) else "rowwarp"
+        assert nat.last_kernel() == want
 
 
 def test_head_width_beyond_maximum_is_refused_loudly():
