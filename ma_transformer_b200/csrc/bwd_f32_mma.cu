@@ -36,6 +36,7 @@ struct BwdFArgs {
     int32_t S, HH;             // rows and heads of the (possibly dilated) view
     int32_t left, right;
     float scale;
+    int32_t D;                 // head width (read by the kernel for wide heads only)
 };
 
 __device__ __forceinline__ void cp_async16(void *dst, const void *src, int bytes) {
@@ -315,6 +316,259 @@ bwd_f32_kernel(const BwdFArgs a) {
     }
 }
 
+// Wide heads (D = 128, 192, ... 512: the reference's layer passes one head of width model_dim,
+// src/layers/sparse_attention.py:71-78).  The same three passes and the same per-warp column ranges (passes of ten
+// 8-column tiles from the warp's own first column), with the head dimension taken 64 columns at a time: the two
+// score-shaped products of a pass (S and dP, or their transposes) accumulate in registers over the slices of their
+// operands, which are staged one slice at a time; the weights (P^T or dS) are formed once, and every 64-column slice
+// of the output is their product with one more staged slice, written out - added to what an earlier pass of the
+// same rows wrote, which needs no atomics: a row of dQ, dK or dV belongs to one thread pair of one CTA.  Registers
+// hold one pass's two score tiles and one slice's fragments whatever D is.  When the walk is a single pass (windows
+// of at most 64 taps) the rows pass keeps S and dP from its first sweep instead of recomputing them.
+template <int PASS>
+__global__ void __launch_bounds__(kThreads)
+bwd_f32_wide_kernel(const BwdFArgs a) {
+    constexpr int NT = 10, LD = 64 + 4, KS = 8;
+    constexpr int kStage = 48 + 8 * NT;
+    constexpr bool COLS = PASS != kRows;
+    constexpr bool kTwo = PASS != kColsV;   // two score-shaped products (S and dP); the dV pass needs only S^T
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    float *sY1 = reinterpret_cast<float *>(smem_raw);   // a slice of: rows pass K, cols passes Q
+    float *sY2 = sY1 + kStage * LD;                     // a slice of: rows pass V, cols passes dO
+    float2 *sSt = reinterpret_cast<float2 *>(sY2 + kStage * LD);   // cols passes: statistics of the staged queries
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int hh = blockIdx.x, b = blockIdx.z, r0 = blockIdx.y * kT;
+    const int D = a.D, n_slices = D >> 6;
+    const int back = COLS ? a.right : a.left, fwd = COLS ? a.left : a.right;   // row r sees columns r - back .. r + fwd
+    const int col_lo = max(0, r0 - back);
+    const int col_hi = min(a.S - 1, min(r0 + kT, a.S) - 1 + fwd);
+    const int base_w = max(col_lo, r0 + 16 * warp - back);   // the warp's first column
+    int n_pass = 0;
+    if (col_hi >= col_lo) {
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) {
+            const int cols_w = min(col_hi, r0 + 16 * w + 15 + fwd) - max(col_lo, r0 + 16 * w - back) + 1;
+            n_pass = max(n_pass, (cols_w + 8 * NT - 1) / (8 * NT));
+        }
+        n_pass = min(n_pass, (col_hi - col_lo) / (8 * NT) + 1);
+    }
+    const int64_t tok = (int64_t)a.HH * D;
+    const int64_t head = ((int64_t)b * a.S * a.HH + hh) * D;
+    const float *x1 = (COLS ? a.k : a.q) + head, *x2 = (COLS ? a.v : a.go) + head;
+    const float *y1 = (COLS ? a.q : a.k) + head, *y2 = (COLS ? a.go : a.v) + head;
+    const float2 *st_in = a.stats + ((int64_t)b * a.HH + hh) * a.S;
+    const int row_a = r0 + 16 * warp + g, row_b = row_a + 8;
+    const int rows[2] = {row_a, row_b};
+    const float sl = a.scale * 1.4426950408889634f;
+    auto seen = [&](int j, int r) { return (unsigned)(j - r + back) <= (unsigned)(back + fwd) && j < a.S; };
+
+    // 64 columns (slice) of the kStage rows from `first` on, of one operand, into one buffer; rows past the end are zeros
+    auto stage = [&](float *dst, const float *src, int first, int slice) {
+        for (int x = threadIdx.x; x < kStage * 16; x += kThreads) {
+            const int r = x >> 4, pc = x & 15;
+            const int j = first + r;
+            const bool in = j < a.S;
+            cp_async16(dst + r * LD + pc * 4, src + (int64_t)(in ? j : 0) * tok + slice * 64 + pc * 4, in ? 16 : 0);
+        }
+    };
+    // the warp's 16 rows of a slice as A fragments (rows g and g + 8, columns t and t + 4 of each 8)
+    auto load_x = [&](uint32_t (&xf)[KS][4], const float *x, int slice) {
+        const float *pa = x + (int64_t)row_a * tok + slice * 64, *pb = x + (int64_t)row_b * tok + slice * 64;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int c = ks * 8 + t;
+            xf[ks][0] = row_a < a.S ? __float_as_uint(pa[c]) : 0u;
+            xf[ks][1] = row_b < a.S ? __float_as_uint(pb[c]) : 0u;
+            xf[ks][2] = row_a < a.S ? __float_as_uint(pa[c + 4]) : 0u;
+            xf[ks][3] = row_b < a.S ? __float_as_uint(pb[c + 4]) : 0u;
+        }
+    };
+    // pass c: s[nt] (and dp[nt]) = the warp's rows against its NT tiles of columns, summed over the slices
+    auto scores = [&](int c, float (&s)[NT][4], float (&dp)[NT][4], int st_off) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[nt][e] = dp[nt][e] = 0.f;
+        const int first = col_lo + c * 8 * NT;
+        for (int slice = 0; slice < n_slices; ++slice) {
+            uint32_t xf1[KS][4], xf2[kTwo ? KS : 1][4];
+            load_x(xf1, x1, slice);
+            if constexpr (kTwo) load_x(xf2, x2, slice);
+            __syncthreads();   // whoever still read the buffers is done
+            stage(sY1, y1, first, slice);
+            if constexpr (kTwo) stage(sY2, y2, first, slice);
+            if (COLS && slice == 0 && threadIdx.x < kStage) {
+                const int j = first + threadIdx.x;
+                sSt[threadIdx.x] = j < a.S ? st_in[j] : make_float2(0.f, 0.f);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncthreads();
+            const uint32_t *cy1 = reinterpret_cast<const uint32_t *>(sY1 + st_off * LD);
+            const uint32_t *cy2 = reinterpret_cast<const uint32_t *>(sY2 + st_off * LD);
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                uint32_t h1[4], l1[4], h2[4], l2[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    split_tf32(xf1[ks][e], h1[e], l1[e]);
+                    if constexpr (kTwo) split_tf32(xf2[ks][e], h2[e], l2[e]);
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int off = (nt * 8 + g) * LD + ks * 8 + t;   // B: (k = dim, n = column)
+                    mma_3x(s[nt], h1, l1, cy1[off], cy1[off + 4]);
+                    if constexpr (kTwo) mma_3x(dp[nt], h2, l2, cy2[off], cy2[off + 4]);
+                }
+            }
+        }
+    };
+    // out rows (+)= W (the pass's weights, held as accumulator tiles) . Y, 64 columns of Y at a time
+    auto emit = [&](int c, const float (&w)[NT][4], const float *y, float *out, int st_off) {
+        const int first = col_lo + c * 8 * NT;
+        for (int slice = 0; slice < n_slices; ++slice) {
+            __syncthreads();
+            stage(sY1, y, first, slice);
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncthreads();
+            const uint32_t *cy = reinterpret_cast<const uint32_t *>(sY1 + st_off * LD);
+            float part[KS][4];
+#pragma unroll
+            for (int d = 0; d < KS; ++d) part[d][0] = part[d][1] = part[d][2] = part[d][3] = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                // the tile's columns in the order the accumulator holds them, so W is its own A fragment
+                const uint32_t wa[4] = {__float_as_uint(w[nt][0]), __float_as_uint(w[nt][2]), __float_as_uint(w[nt][1]),
+                                        __float_as_uint(w[nt][3])};
+                uint32_t w_hi[4], w_lo[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) split_tf32(wa[e], w_hi[e], w_lo[e]);
+                const uint32_t *yr = cy + (nt * 8 + 2 * t) * LD + g;   // B: (k = column 2t / 2t + 1, n = dim)
+#pragma unroll
+                for (int d = 0; d < KS; ++d) mma_3x(part[d], w_hi, w_lo, yr[d * 8], yr[LD + d * 8]);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                if (rows[i] >= a.S) continue;
+                float *dst = out + (int64_t)rows[i] * tok + slice * 64 + 2 * t;
+#pragma unroll
+                for (int d = 0; d < KS; ++d) {
+                    float2 val = make_float2(part[d][2 * i], part[d][2 * i + 1]);
+                    if (c > 0) {   // an earlier pass of these rows wrote here
+                        const float2 old = *reinterpret_cast<const float2 *>(dst + d * 8);
+                        val.x += old.x;
+                        val.y += old.y;
+                    }
+                    *reinterpret_cast<float2 *>(dst + d * 8) = val;
+                }
+            }
+        }
+    };
+    float *out = (PASS == kRows ? a.dq : PASS == kColsV ? a.dv : a.dk) + head;
+    if (n_pass == 0) {   // rows that meet no column: zero gradient (and zero statistics)
+        for (int i = 0; i < 2; ++i) {
+            if (rows[i] >= a.S) continue;
+            for (int c = 2 * t; c < D; c += 8) *reinterpret_cast<float2 *>(out + (int64_t)rows[i] * tok + c) = make_float2(0.f, 0.f);
+            if (PASS == kRows && t == 0) a.stats[((int64_t)b * a.HH + hh) * a.S + rows[i]] = make_float2(0.f, 0.f);
+        }
+        return;
+    }
+
+    float s[NT][4], dp[NT][4];
+    if constexpr (PASS == kRows) {
+        float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f}, dr[2] = {0.f, 0.f}, lse[2], dsc[2];
+        // sweep one: running maximum, sum of exponentials, sum of exponentials x dP
+        for (int c = 0; c < n_pass; ++c) {
+            const int cb = base_w + c * 8 * NT;
+            scores(c, s, dp, base_w - col_lo);
+            float cm[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (!seen(cb + nt * 8 + 2 * t + (e & 1), rows[e >> 1])) s[nt][e] = -INFINITY;
+                    cm[e >> 1] = fmaxf(cm[e >> 1], s[nt][e]);
+                }
+            float msl[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float m_new = fmaxf(mx[i], quad_max(cm[i]));
+                const float alpha = mx[i] == -INFINITY ? 0.f : ptx::ex2((mx[i] - m_new) * sl);
+                sum[i] *= alpha;
+                dr[i] *= alpha;
+                mx[i] = m_new;
+                msl[i] = m_new == -INFINITY ? 0.f : m_new * sl;
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float ex = ptx::ex2(fmaf(s[nt][e], sl, -msl[e >> 1]));
+                    sum[e >> 1] += ex;
+                    dr[e >> 1] = fmaf(ex, dp[nt][e], dr[e >> 1]);
+                }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            sum[i] = quad_sum(sum[i]);
+            dr[i] = quad_sum(dr[i]);
+            const bool live = sum[i] > 0.f;
+            lse[i] = live ? mx[i] * sl + log2f(sum[i]) : 0.f;
+            dsc[i] = live ? dr[i] / sum[i] * a.scale : 0.f;
+            if (t == 0 && rows[i] < a.S) a.stats[((int64_t)b * a.HH + hh) * a.S + rows[i]] = make_float2(lse[i], dsc[i]);
+        }
+        // sweep two: dS, dQ (+)= dS K; a one-pass walk still holds S (masked) and dP
+        for (int c = 0; c < n_pass; ++c) {
+            const int cb = base_w + c * 8 * NT;
+            if (n_pass > 1) scores(c, s, dp, base_w - col_lo);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float p = ptx::ex2(fmaf(s[nt][e], sl, -lse[e >> 1]));
+                    if (!seen(cb + nt * 8 + 2 * t + (e & 1), rows[e >> 1])) p = 0.f;
+                    s[nt][e] = p * fmaf(dp[nt][e], a.scale, -dsc[e >> 1]);
+                }
+            emit(c, s, y1, out, base_w - col_lo);
+        }
+    } else {
+        for (int c = 0; c < n_pass; ++c) {
+            const int cb = base_w + c * 8 * NT, st_off = base_w - col_lo;
+            scores(c, s, dp, st_off);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int col = nt * 8 + 2 * t + (e & 1);
+                    const float2 sq = sSt[st_off + col];   // the query's statistics
+                    float p = ptx::ex2(fmaf(s[nt][e], sl, -sq.x));
+                    if (!seen(cb + col, rows[e >> 1])) p = 0.f;
+                    s[nt][e] = PASS == kColsV ? p : p * fmaf(dp[nt][e], a.scale, -sq.y);
+                }
+            emit(c, s, PASS == kColsV ? y2 : y1, out, st_off);
+        }
+    }
+}
+
+int launch_wide(const BwdFArgs &a, int64_t B, cudaStream_t stream) {
+    constexpr int kStaged = 48 + 8 * 10;
+    constexpr size_t smem = (size_t)2 * kStaged * 68 * sizeof(float) + kStaged * sizeof(float2);
+    int rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_wide_kernel<kRows>, smem, "bwd_f32 wide rows")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_wide_kernel<kColsV>, smem, "bwd_f32 wide dV")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_wide_kernel<kColsK>, smem, "bwd_f32 wide dK")) != MAT_OK) return rc;
+    const dim3 grid((unsigned)a.HH, (unsigned)((a.S + kT - 1) / kT), (unsigned)B);
+    bwd_f32_wide_kernel<kRows><<<grid, kThreads, smem, stream>>>(a);
+    bwd_f32_wide_kernel<kColsV><<<grid, kThreads, smem, stream>>>(a);
+    bwd_f32_wide_kernel<kColsK><<<grid, kThreads, smem, stream>>>(a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "fp32 tensor-core backward (wide heads) launch");
+    note_kernel("bwd_f32_mma");
+    return MAT_OK;
+}
+
 template <int D, int NT>
 int launch_f(const BwdFArgs &a, int64_t B, cudaStream_t stream) {
     constexpr int kStaged = NT > 0 ? 48 + 8 * NT : 2 * kT;
@@ -335,10 +589,12 @@ int launch_f(const BwdFArgs &a, int64_t B, cudaStream_t stream) {
 
 }  // namespace
 
-// fp32 window patterns with head width 32 or 64, lengths a multiple of the dilation, 16-byte aligned tensors.
+// fp32 window patterns with head width 32, 64 or a multiple of 64 up to 512, lengths a multiple of the dilation,
+// 16-byte aligned tensors.
 // MAT_BWD_KERNEL=warp keeps the warp-level kernels.
 bool bwd_f32_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil) {
-    if (dtype != MAT_F32 || (D != 32 && D != 64) || dil < 1 || S % dil != 0) return false;
+    const bool wide_head = D > 64 && D <= 512 && D % 64 == 0;
+    if (dtype != MAT_F32 || (D != 32 && D != 64 && !wide_head) || dil < 1 || S % dil != 0) return false;
     const char *env = std::getenv("MAT_BWD_KERNEL");
     if (env && std::strcmp(env, "warp") == 0) return false;
     const int64_t Sv = S / dil;
@@ -357,9 +613,14 @@ int launch_bwd_f32_mma(const void *q, const void *k, const void *v, const void *
     a.left = (int32_t)std::min<int64_t>(left, a.S);
     a.right = (int32_t)std::min<int64_t>(right, a.S);
     a.scale = scale;
+    a.D = (int32_t)D;
+    if (D > 64) return launch_wide(a, B, stream);
+    const char *walk = std::getenv("MAT_BWD_F32_WALK");
+    // (a 64-wide head whose walk is one pass takes that kernel too: its rows pass keeps S and dP instead of
+    // recomputing them; MAT_BWD_F32_WALK=recompute or chunks keeps it on the kernels below)
+    if (D == 64 && a.left + a.right + 16 <= 80 && !walk) return launch_wide(a, B, stream);
     // columns a warp's 16 rows meet: up to 160 the warp walks its own range in passes of 10 tiles (one pass at 64
     // causal taps); wider windows walk the 64-column chunks.  MAT_BWD_F32_WALK=chunks forces those (a measurement aid).
-    const char *walk = std::getenv("MAT_BWD_F32_WALK");
     const bool own = a.left + a.right + 16 <= 160 && !(walk && std::strcmp(walk, "chunks") == 0);
     if (own) return D == 32 ? launch_f<32, 10>(a, B, stream) : launch_f<64, 10>(a, B, stream);
     return D == 32 ? launch_f<32, 0>(a, B, stream) : launch_f<64, 0>(a, B, stream);

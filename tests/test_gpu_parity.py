@@ -701,21 +701,24 @@ def test_backward_matches_autograd_of_reference_oracle(B, S, H, D, W):
         assert (got.cpu().double() - ref.grad).abs().max() < 2e-5 * max(1.0, float(ref.grad.abs().max()))
 
 
-@pytest.mark.parametrize("D", [32, 64])
+@pytest.mark.parametrize("D", [32, 64, 128, 256])
 @pytest.mark.parametrize("B,S,H,left,right,dil", [
     (1, 512, 2, 63, 0, 1), (2, 200, 3, 32, 32, 1), (1, 33, 1, 8, 8, 1), (1, 130, 2, 10, 3, 1), (1, 70, 1, 40, 41, 1),
     (1, 300, 2, 64, 64, 1), (1, 256, 2, 15, 0, 2), (2, 96, 1, 5, 5, 3), (1, 1000, 2, 1000, 1000, 1), (1, 1000, 1, 1000, 0, 1),
     (1, 700, 2, 300, 100, 1),
 ])
-@pytest.mark.parametrize("walk", ["default", "chunks"])
+@pytest.mark.parametrize("walk", ["default", "chunks", "recompute"])
 def test_fp32_backward_on_tensor_cores(monkeypatch, walk, B, S, H, left, right, dil, D):
     """The fp32 backward as three TF32 products per product (head widths 32 and 64): against autograd in fp64
     through a dense masked softmax at the fp32 kernels' bar (2e-5 of the gradient's scale), windows narrow, wide,
     dilated, dense and causal dense, ragged lengths; and against the warp-level fp32 kernels.  Narrow windows
     default to the walk in which every warp takes its own column range; MAT_BWD_F32_WALK=chunks keeps them on
-    the 64-column chunks the wide ones use."""
-    if walk == "chunks":
-        monkeypatch.setenv("MAT_BWD_F32_WALK", "chunks")
+    the 64-column chunks the wide ones use.  Head widths 128 and 256 (one head of width model_dim is what the
+    reference's layer passes) run the same passes 64 columns at a time."""
+    if walk != "default":   # ("recompute": one-pass walks of a 64-wide head on the kernel that recomputes S and dP)
+        if D > 64 or (walk == "recompute" and (D != 64 or left + right + 16 > 80)):
+            pytest.skip("no such variant for this shape")
+        monkeypatch.setenv("MAT_BWD_F32_WALK", walk)
     spec = PatternSpec(left=left, right=right, dilation=dil)
     q, k, v = seeded_qkv(87, B, S, H, D, torch.float32)
     go = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(88))
