@@ -391,7 +391,7 @@ int mat_sparse_attn_bwd_general(const void *q, const void *k, const void *v, con
     if (spec->kind == MAT_BLOCK && al % 16 == 0 && bwd_block_mma_supports(B, S, H, D, dtype, spec->block))
         return launch_bwd_block_mma(q, k, v, dout, dq, dk, dv, stats, B, S, H, dtype, spec->block, spec->causal,
                                     spec->blk_rowptr, spec->blk_colidx, t_rowptr, t_colidx, a.scale, st);
-    if (spec->kind == MAT_WINDOW && al % 16 == 0 && bwd_d_mma_supports(B, S, H, D, dtype, a.dil))
+    if (spec->kind == MAT_WINDOW && al % 16 == 0 && bwd_d_mma_supports(B, S, H, D, dtype, a.dil, a.left, a.right))
         return launch_bwd_d_mma(q, k, v, dout, dq, dk, dv, stats, B, S, H, D, dtype, a.left, a.right, a.dil, a.scale, st);
     if (spec->kind == MAT_WINDOW && al % 16 == 0 && bwd_f32_mma_supports(B, S, H, D, dtype, a.dil))
         return launch_bwd_f32_mma(q, k, v, dout, dq, dk, dv, stats, B, S, H, D, a.left, a.right, a.dil, a.scale, st);

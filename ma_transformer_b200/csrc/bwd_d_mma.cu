@@ -27,6 +27,7 @@ struct BwdDArgs {
     int32_t S, HH;             // rows and heads of the (possibly dilated) view
     int32_t left, right;
     float scale;
+    int32_t D;                 // head width (read by the kernel for wide heads only)
 };
 
 __device__ __forceinline__ void cp_async16(void *dst, const void *src, int bytes) {
@@ -288,6 +289,270 @@ bwd_d_kernel(const BwdDArgs a) {
     }
 }
 
+// Wide heads (D = 128, 192, ... 512) with narrow windows.  The same three passes and per-warp column ranges (passes
+// of five 16-column steps from the warp's own first column), with the head dimension taken 64 columns at a time:
+// the two score-shaped products of a pass (S and dP, or their transposes) accumulate in registers over the slices
+// of their operands, staged one slice at a time; the weights (P^T or dS, rounded to the input type) are formed once,
+// and every 64-column slice of the output is their product with one more staged slice, written out - added to what
+// the first pass of the same rows wrote when the walk has a second one (a row of dQ, dK or dV belongs to one thread
+// pair of one CTA: no atomics).  Registers hold one pass's two score tiles and one slice's fragments whatever D is.
+// A one-pass walk (windows of at most 64 taps) keeps S and dP from the statistics sweep instead of recomputing them.
+template <typename T, int PASS>
+__global__ void __launch_bounds__(kThreads)
+bwd_d_wide_kernel(const BwdDArgs a) {
+    using M = ptx::Mma<T>;
+    constexpr int NS = 5, LD = 64 + 8, KS = 4;
+    constexpr int kStage = 48 + 16 * NS;
+    constexpr bool COLS = PASS != kRows;
+    constexpr bool kTwo = PASS != kColsV;   // two score-shaped products (S and dP); the dV pass needs only S^T
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    T *sY1 = reinterpret_cast<T *>(smem_raw);   // a slice of: rows pass K, cols passes Q
+    T *sY2 = sY1 + kStage * LD;                 // a slice of: rows pass V, cols passes dO
+    float2 *sSt = reinterpret_cast<float2 *>(sY2 + kStage * LD);   // cols passes: statistics of the staged queries
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int m4 = lane >> 3, r8 = lane & 7;
+    const int hh = blockIdx.x, b = blockIdx.z, r0 = blockIdx.y * kT;
+    const int D = a.D, n_slices = D >> 6;
+    const int back = COLS ? a.right : a.left, fwd = COLS ? a.left : a.right;   // row r sees columns r - back .. r + fwd
+    const int col_lo = max(0, r0 - back);
+    const int col_hi = min(a.S - 1, min(r0 + kT, a.S) - 1 + fwd);
+    const int base_w = max(col_lo, r0 + 16 * warp - back);   // the warp's first column
+    int n_pass = 0;
+    if (col_hi >= col_lo) {
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) {
+            const int cols_w = min(col_hi, r0 + 16 * w + 15 + fwd) - max(col_lo, r0 + 16 * w - back) + 1;
+            n_pass = max(n_pass, (cols_w + 16 * NS - 1) / (16 * NS));
+        }
+        n_pass = min(n_pass, (col_hi - col_lo) / (16 * NS) + 1);
+    }
+    const int64_t tok = (int64_t)a.HH * D;
+    const int64_t head = ((int64_t)b * a.S * a.HH + hh) * D;
+    const T *x1 = (const T *)(COLS ? a.k : a.q) + head, *x2 = (const T *)(COLS ? a.v : a.go) + head;
+    const T *y1 = (const T *)(COLS ? a.q : a.k) + head, *y2 = (const T *)(COLS ? a.go : a.v) + head;
+    const float2 *st_in = a.stats + ((int64_t)b * a.HH + hh) * a.S;
+    const int row_a = r0 + 16 * warp + g, row_b = row_a + 8;
+    const int rows[2] = {row_a, row_b};
+    const float sl = a.scale * 1.4426950408889634f;
+    auto seen = [&](int j, int r) { return (unsigned)(j - r + back) <= (unsigned)(back + fwd) && j < a.S; };
+
+    // 64 columns (slice) of the kStage rows from `first` on, of one operand, into one buffer; rows past the end are zeros
+    auto stage = [&](T *dst, const T *src, int first, int slice) {
+        for (int x = threadIdx.x; x < kStage * 8; x += kThreads) {
+            const int r = x >> 3, pc = x & 7;
+            const int j = first + r;
+            const bool in = j < a.S;
+            cp_async16(dst + r * LD + pc * 8, src + (int64_t)(in ? j : 0) * tok + slice * 64 + pc * 8, in ? 16 : 0);
+        }
+    };
+    // the warp's 16 rows of a slice as A fragments: rows g and g + 8, columns 2t, 2t+1 (+8) of each 16
+    auto load_x = [&](uint32_t (&xf)[KS][4], const T *x, int slice) {
+        const T *pa = x + (int64_t)row_a * tok + slice * 64, *pb = x + (int64_t)row_b * tok + slice * 64;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int c = ks * 16 + 2 * t;
+            xf[ks][0] = row_a < a.S ? *reinterpret_cast<const uint32_t *>(pa + c) : 0u;
+            xf[ks][1] = row_b < a.S ? *reinterpret_cast<const uint32_t *>(pb + c) : 0u;
+            xf[ks][2] = row_a < a.S ? *reinterpret_cast<const uint32_t *>(pa + c + 8) : 0u;
+            xf[ks][3] = row_b < a.S ? *reinterpret_cast<const uint32_t *>(pb + c + 8) : 0u;
+        }
+    };
+    // pass c: s (and dp) = the warp's rows against its NS steps of 16 columns, summed over the slices
+    auto scores = [&](int c, float (&s)[2 * NS][4], float (&dp)[2 * NS][4], int st_off) {
+#pragma unroll
+        for (int n = 0; n < 2 * NS; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[n][e] = dp[n][e] = 0.f;
+        const int first = col_lo + c * 16 * NS;
+        for (int slice = 0; slice < n_slices; ++slice) {
+            uint32_t xf1[KS][4], xf2[kTwo ? KS : 1][4];
+            load_x(xf1, x1, slice);
+            if constexpr (kTwo) load_x(xf2, x2, slice);
+            __syncthreads();   // whoever still read the buffers is done
+            stage(sY1, y1, first, slice);
+            if constexpr (kTwo) stage(sY2, y2, first, slice);
+            if (COLS && slice == 0 && threadIdx.x < kStage) {
+                const int j = first + threadIdx.x;
+                sSt[threadIdx.x] = j < a.S ? st_in[j] : make_float2(0.f, 0.f);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncthreads();
+            const uint32_t cy1 = ptx::smem_u32(sY1 + st_off * LD), cy2 = ptx::smem_u32(sY2 + st_off * LD);
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+                for (int n2 = 0; n2 < NS; ++n2) {
+                    // matrices: (columns n2*16 + 0..7, dims +0), (same columns, dims +8), (columns +8, dims +0), (columns +8, dims +8)
+                    const uint32_t off = (uint32_t)(((n2 * 16 + r8 + (m4 >> 1) * 8) * LD + ks * 16 + (m4 & 1) * 8) * 2);
+                    uint32_t yf[4];
+                    ptx::ldmatrix_x4(yf, cy1 + off);
+                    M::run(s[2 * n2], xf1[ks], yf[0], yf[1]);
+                    M::run(s[2 * n2 + 1], xf1[ks], yf[2], yf[3]);
+                    if constexpr (kTwo) {
+                        ptx::ldmatrix_x4(yf, cy2 + off);
+                        M::run(dp[2 * n2], xf2[ks], yf[0], yf[1]);
+                        M::run(dp[2 * n2 + 1], xf2[ks], yf[2], yf[3]);
+                    }
+                }
+        }
+    };
+    // out rows (+)= W (the pass's weights as A fragments) . Y, 64 columns of Y at a time
+    auto emit = [&](int c, const uint32_t (&wa)[NS][4], const T *y, T *out, int st_off) {
+        const int first = col_lo + c * 16 * NS;
+        for (int slice = 0; slice < n_slices; ++slice) {
+            __syncthreads();
+            stage(sY1, y, first, slice);
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncthreads();
+            const uint32_t cy = ptx::smem_u32(sY1 + st_off * LD);
+            float acc[2 * KS][4];
+#pragma unroll
+            for (int n = 0; n < 2 * KS; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+#pragma unroll
+            for (int n2 = 0; n2 < NS; ++n2)
+#pragma unroll
+                for (int d2 = 0; d2 < KS; ++d2) {
+                    // matrices (transposed on load): (columns n2*16 + 0..7, dims d2*16 + 0..7), (columns +8, same dims),
+                    // (columns + 0, dims + 8), (columns + 8, dims + 8)
+                    uint32_t yf[4];
+                    ptx::ldmatrix_x4_trans(yf, cy + (uint32_t)(((n2 * 16 + r8 + (m4 & 1) * 8) * LD + d2 * 16 + (m4 >> 1) * 8) * 2));
+                    M::run(acc[2 * d2], wa[n2], yf[0], yf[1]);
+                    M::run(acc[2 * d2 + 1], wa[n2], yf[2], yf[3]);
+                }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                if (rows[i] >= a.S) continue;
+                T *dst = out + (int64_t)rows[i] * tok + slice * 64 + 2 * t;
+#pragma unroll
+                for (int n = 0; n < 2 * KS; ++n) {
+                    float vx = acc[n][2 * i], vy = acc[n][2 * i + 1];
+                    if (c > 0) {   // the first pass of these rows wrote here
+                        const uint32_t old = *reinterpret_cast<const uint32_t *>(dst + n * 8);
+                        vx += M::lo(old);
+                        vy += M::hi(old);
+                    }
+                    *reinterpret_cast<uint32_t *>(dst + n * 8) = M::pack(vx, vy);
+                }
+            }
+        }
+    };
+    T *out = (T *)(PASS == kRows ? a.dq : PASS == kColsV ? a.dv : a.dk) + head;
+    if (n_pass == 0) {   // rows that meet no column: zero gradient (and zero statistics)
+        for (int i = 0; i < 2; ++i) {
+            if (rows[i] >= a.S) continue;
+            for (int c = 2 * t; c < D; c += 8) *reinterpret_cast<uint32_t *>(out + (int64_t)rows[i] * tok + c) = 0u;
+            if (PASS == kRows && t == 0) a.stats[((int64_t)b * a.HH + hh) * a.S + rows[i]] = make_float2(0.f, 0.f);
+        }
+        return;
+    }
+
+    float s[2 * NS][4], dp[2 * NS][4];
+    uint32_t wa[NS][4];
+    const int st_off = base_w - col_lo;
+    if constexpr (PASS == kRows) {
+        float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f}, dr[2] = {0.f, 0.f}, lse[2], dsc[2];
+        // sweep one: running maximum, sum of exponentials, sum of exponentials x dP
+        for (int c = 0; c < n_pass; ++c) {
+            const int cb = base_w + c * 16 * NS;
+            scores(c, s, dp, st_off);
+            float cm[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < 2 * NS; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (!seen(cb + n * 8 + 2 * t + (e & 1), rows[e >> 1])) s[n][e] = -INFINITY;
+                    cm[e >> 1] = fmaxf(cm[e >> 1], s[n][e]);
+                }
+            float msl[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float m_new = fmaxf(mx[i], quad_max(cm[i]));
+                const float alpha = mx[i] == -INFINITY ? 0.f : ptx::ex2((mx[i] - m_new) * sl);
+                sum[i] *= alpha;
+                dr[i] *= alpha;
+                mx[i] = m_new;
+                msl[i] = m_new == -INFINITY ? 0.f : m_new * sl;
+            }
+#pragma unroll
+            for (int n = 0; n < 2 * NS; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float ex = ptx::ex2(fmaf(s[n][e], sl, -msl[e >> 1]));
+                    sum[e >> 1] += ex;
+                    dr[e >> 1] = fmaf(ex, dp[n][e], dr[e >> 1]);
+                }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            sum[i] = quad_sum(sum[i]);
+            dr[i] = quad_sum(dr[i]);
+            const bool live = sum[i] > 0.f;
+            lse[i] = live ? mx[i] * sl + log2f(sum[i]) : 0.f;
+            dsc[i] = live ? dr[i] / sum[i] * a.scale : 0.f;
+            if (t == 0 && rows[i] < a.S) a.stats[((int64_t)b * a.HH + hh) * a.S + rows[i]] = make_float2(lse[i], dsc[i]);
+        }
+        // sweep two: dS, dQ (+)= dS K; a one-pass walk still holds S (masked) and dP
+        for (int c = 0; c < n_pass; ++c) {
+            const int cb = base_w + c * 16 * NS;
+            if (n_pass > 1) scores(c, s, dp, st_off);
+#pragma unroll
+            for (int n = 0; n < 2 * NS; ++n) {
+                float w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float p = ptx::ex2(fmaf(s[n][e], sl, -lse[e >> 1]));
+                    if (!seen(cb + n * 8 + 2 * t + (e & 1), rows[e >> 1])) p = 0.f;
+                    w[e] = p * fmaf(dp[n][e], a.scale, -dsc[e >> 1]);
+                }
+                wa[n >> 1][(n & 1) * 2] = M::pack(w[0], w[1]);
+                wa[n >> 1][(n & 1) * 2 + 1] = M::pack(w[2], w[3]);
+            }
+            emit(c, wa, y1, out, st_off);
+        }
+    } else {
+        for (int c = 0; c < n_pass; ++c) {
+            const int cb = base_w + c * 16 * NS;
+            scores(c, s, dp, st_off);
+#pragma unroll
+            for (int n = 0; n < 2 * NS; ++n) {
+                float w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int col = n * 8 + 2 * t + (e & 1);
+                    const float2 sq = sSt[st_off + col];   // the query's statistics
+                    float p = ptx::ex2(fmaf(s[n][e], sl, -sq.x));
+                    if (!seen(cb + col, rows[e >> 1])) p = 0.f;
+                    w[e] = PASS == kColsV ? p : p * fmaf(dp[n][e], a.scale, -sq.y);
+                }
+                wa[n >> 1][(n & 1) * 2] = M::pack(w[0], w[1]);
+                wa[n >> 1][(n & 1) * 2 + 1] = M::pack(w[2], w[3]);
+            }
+            emit(c, wa, PASS == kColsV ? y2 : y1, out, st_off);
+        }
+    }
+}
+
+template <typename T>
+int launch_wide(const BwdDArgs &a, int64_t B, cudaStream_t stream) {
+    constexpr int kStaged = 48 + 16 * 5;
+    constexpr size_t smem = (size_t)2 * kStaged * 72 * sizeof(T) + kStaged * sizeof(float2);
+    int rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_d_wide_kernel<T, kRows>, smem, "bwd_d wide rows")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_d_wide_kernel<T, kColsV>, smem, "bwd_d wide dV")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_d_wide_kernel<T, kColsK>, smem, "bwd_d wide dK")) != MAT_OK) return rc;
+    const dim3 grid((unsigned)a.HH, (unsigned)((a.S + kT - 1) / kT), (unsigned)B);
+    bwd_d_wide_kernel<T, kRows><<<grid, kThreads, smem, stream>>>(a);
+    bwd_d_wide_kernel<T, kColsV><<<grid, kThreads, smem, stream>>>(a);
+    bwd_d_wide_kernel<T, kColsK><<<grid, kThreads, smem, stream>>>(a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "16-bit backward (wide heads) launch");
+    note_kernel("bwd_d_mma");
+    return MAT_OK;
+}
+
 template <typename T, int D, int NS>
 int launch_d(const BwdDArgs &a, int64_t B, cudaStream_t stream) {
     constexpr int kStaged = NS > 0 ? 48 + 16 * NS : 2 * kT;
@@ -331,11 +596,17 @@ int launch_any_d(const BwdDArgs &a, int64_t B, int64_t D, cudaStream_t stream) {
 
 }  // namespace
 
-// 16-bit window patterns with a head width that is a multiple of 16 up to 128 other than 64, lengths a multiple of
-// the dilation, 16-byte aligned tensors.  MAT_BWD_KERNEL=warp keeps the one-warp-per-row kernels.
-bool bwd_d_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil) {
+// 16-bit window patterns with a head width that is a multiple of 16 up to 128 other than 64, and windows of at most
+// 144 taps with a head width of 192, 256, ... 512 (two passes of a warp's walk at most: the second pass adds to 16-bit
+// values the first one wrote); lengths a multiple of the dilation, 16-byte aligned tensors.  MAT_BWD_KERNEL=warp
+// keeps the one-warp-per-row kernels.
+bool bwd_d_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil, int64_t left, int64_t right) {
     if (dtype != MAT_BF16 && dtype != MAT_F16) return false;
-    if (D % 16 || D < 16 || D > 128 || D == 64 || dil < 1 || S % dil != 0) return false;
+    if (D % 16 || D < 16 || D == 64 || dil < 1 || S % dil != 0) return false;
+    if (D > 128) {
+        const int64_t Sv1 = S / dil;
+        if (D > 512 || D % 64 || std::min(left, Sv1) + std::min(right, Sv1) + 16 > 160) return false;
+    }
     const char *env = std::getenv("MAT_BWD_KERNEL");
     if (env && std::strcmp(env, "warp") == 0) return false;
     const int64_t Sv = S / dil;
@@ -354,6 +625,13 @@ int launch_bwd_d_mma(const void *q, const void *k, const void *v, const void *do
     a.left = (int32_t)std::min<int64_t>(left, a.S);
     a.right = (int32_t)std::min<int64_t>(right, a.S);
     a.scale = scale;
+    a.D = (int32_t)D;
+    // heads wider than 128 columns go 64 columns at a time (a head of 128 gains nothing from it: 0.353 against
+    // 0.339 ms at 65536 tokens x 4 heads x 64 taps; MAT_BWD_D_WALK=sliced sends its one-pass walks there, a
+    // measurement aid)
+    const char *walk = std::getenv("MAT_BWD_D_WALK");
+    if (D > 128 || (D == 128 && a.left + a.right + 16 <= 80 && walk && std::strcmp(walk, "sliced") == 0))
+        return dtype == MAT_BF16 ? launch_wide<__nv_bfloat16>(a, B, stream) : launch_wide<__half>(a, B, stream);
     return dtype == MAT_BF16 ? launch_any_d<__nv_bfloat16>(a, B, D, stream) : launch_any_d<__half>(a, B, D, stream);
 }
 

@@ -168,6 +168,8 @@ template <> struct Mma<__nv_bfloat16> {
         __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
         return *reinterpret_cast<uint32_t *>(&v);
     }
+    static __device__ __forceinline__ float lo(uint32_t x) { return __uint_as_float(x << 16); }
+    static __device__ __forceinline__ float hi(uint32_t x) { return __uint_as_float(x & 0xffff0000u); }
     static __device__ __forceinline__ uint32_t ex2_packed(uint32_t x) { return ex2_bf16x2(x); }
     static constexpr uint32_t kOnes = 0x3F803F80u;  // (1.0, 1.0)
 };
@@ -192,6 +194,8 @@ template <> struct Mma<__half> {
         __half2 v = __floats2half2_rn(lo, hi);
         return *reinterpret_cast<uint32_t *>(&v);
     }
+    static __device__ __forceinline__ float lo(uint32_t x) { return __low2float(*reinterpret_cast<const __half2 *>(&x)); }
+    static __device__ __forceinline__ float hi(uint32_t x) { return __high2float(*reinterpret_cast<const __half2 *>(&x)); }
     static __device__ __forceinline__ uint32_t ex2_packed(uint32_t x) { return ex2_f16x2(x); }
     static constexpr uint32_t kOnes = 0x3C003C00u;  // (1.0, 1.0)
 };

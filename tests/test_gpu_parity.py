@@ -743,6 +743,40 @@ def test_fp32_backward_on_tensor_cores(monkeypatch, walk, B, S, H, left, right, 
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D", [192, 256, 512])
+@pytest.mark.parametrize("B,S,H,left,right,dil", [
+    (1, 512, 2, 63, 0, 1), (2, 200, 2, 32, 32, 1), (1, 33, 1, 8, 8, 1), (1, 70, 1, 40, 41, 1), (1, 300, 2, 64, 64, 1),
+    (1, 256, 1, 15, 0, 2), (1, 130, 1, 0, 100, 1),
+])
+def test_16bit_backward_for_wide_heads(monkeypatch, dtype, D, B, S, H, left, right, dil):
+    """The 16-bit backward for one wide head (192 to 512 columns; the reference's layer passes D = model_dim) with a
+    window of at most 144 taps: the tensor-core passes with the head dimension 64 columns at a time, against autograd
+    in fp64 through a dense masked softmax on the same rounded inputs and against the one-warp-per-row kernels.
+    Wider windows on such heads stay on the one-warp-per-row kernels."""
+    spec = PatternSpec(left=left, right=right, dilation=dil)
+    q, k, v = seeded_qkv(91, B, S, H, D, dtype)
+    go = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(92)).to(dtype)
+    args = tuple(t.to(DEV) for t in (q, k, v, go))
+    got = ext.backward_pattern(*args, spec)
+    torch.cuda.synchronize()
+    assert nat.last_kernel() == "bwd_d_mma" and nat.device_status() == 0
+    tol = 2e-2 if dtype == torch.bfloat16 else 5e-3
+    ref = [t.double().requires_grad_(True) for t in (q, k, v)]
+    masked_dense_attention(*ref, left, right, dil).backward(go.double())
+    for name, a, r in zip(("dQ", "dK", "dV"), got, ref):
+        err = float((a.cpu().double() - r.grad).abs().max())
+        assert err <= tol * max(1.0, float(r.grad.abs().max())), f"{name} vs fp64 autograd: {err}"
+    if S // dil >= 200:   # (a window clamps to the sequence, so a short sequence makes every window narrow)
+        ext.backward_pattern(*args, PatternSpec(left=100, right=100, dilation=dil))
+        assert nat.last_kernel() == "bwd_window"
+    monkeypatch.setenv("MAT_BWD_KERNEL", "warp")
+    want = ext.backward_pattern(*args, spec)
+    assert nat.last_kernel() == "bwd_window"
+    for name, a, b in zip(("dQ", "dK", "dV"), got, want):
+        assert float((a.float() - b.float()).abs().max()) <= tol * max(1.0, float(b.float().abs().max())), name
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("D", [16, 32, 96, 128])
 @pytest.mark.parametrize("B,S,H,left,right,dil", [
     (1, 512, 2, 63, 0, 1), (2, 200, 3, 32, 32, 1), (1, 33, 1, 8, 8, 1), (1, 70, 1, 40, 41, 1), (1, 300, 2, 64, 64, 1),
