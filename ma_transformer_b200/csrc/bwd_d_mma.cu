@@ -103,6 +103,7 @@ bwd_d_kernel(const BwdDArgs a) {
             cp_async16(sY1 + (buf * kT + r) * LD + pc * 8, y1 + src, in ? 16 : 0);
             cp_async16(sY2 + (buf * kT + r) * LD + pc * 8, y2 + src, in ? 16 : 0);
         }
+        static_assert(kStage <= kThreads, "one thread per staged row's statistics");
         if (COLS && threadIdx.x < kStage) {
             const int j = base + threadIdx.x;
             sSt[buf * kT + threadIdx.x] = j < a.S ? st_in[j] : make_float2(0.f, 0.f);
@@ -372,6 +373,7 @@ bwd_d_wide_kernel(const BwdDArgs a) {
             __syncthreads();   // whoever still read the buffers is done
             stage(sY1, y1, first, slice);
             if constexpr (kTwo) stage(sY2, y2, first, slice);
+            static_assert(kStage <= kThreads, "one thread per staged row's statistics");
             if (COLS && slice == 0 && threadIdx.x < kStage) {
                 const int j = first + threadIdx.x;
                 sSt[threadIdx.x] = j < a.S ? st_in[j] : make_float2(0.f, 0.f);

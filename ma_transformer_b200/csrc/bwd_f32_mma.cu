@@ -132,6 +132,7 @@ bwd_f32_kernel(const BwdFArgs a) {
             cp_async16(sY1 + (buf * kT + r) * LD + pc * 4, y1 + src, in ? 16 : 0);
             cp_async16(sY2 + (buf * kT + r) * LD + pc * 4, y2 + src, in ? 16 : 0);
         }
+        static_assert(kStage <= kThreads, "one thread per staged row's statistics");
         if (COLS && threadIdx.x < kStage) {
             const int j = base + threadIdx.x;
             sSt[buf * kT + threadIdx.x] = j < a.S ? st_in[j] : make_float2(0.f, 0.f);
@@ -325,10 +326,10 @@ bwd_f32_kernel(const BwdFArgs a) {
 // same rows wrote, which needs no atomics: a row of dQ, dK or dV belongs to one thread pair of one CTA.  Registers
 // hold one pass's two score tiles and one slice's fragments whatever D is.  When the walk is a single pass (windows
 // of at most 64 taps) the rows pass keeps S and dP from its first sweep instead of recomputing them.
-template <int PASS>
+template <int PASS, int NT>
 __global__ void __launch_bounds__(kThreads)
 bwd_f32_wide_kernel(const BwdFArgs a) {
-    constexpr int NT = 10, LD = 64 + 4, KS = 8;
+    constexpr int LD = 64 + 4, KS = 8;
     constexpr int kStage = 48 + 8 * NT;
     constexpr bool COLS = PASS != kRows;
     constexpr bool kTwo = PASS != kColsV;   // two score-shaped products (S and dP); the dV pass needs only S^T
@@ -398,9 +399,11 @@ bwd_f32_wide_kernel(const BwdFArgs a) {
             __syncthreads();   // whoever still read the buffers is done
             stage(sY1, y1, first, slice);
             if constexpr (kTwo) stage(sY2, y2, first, slice);
-            if (COLS && slice == 0 && threadIdx.x < kStage) {
-                const int j = first + threadIdx.x;
-                sSt[threadIdx.x] = j < a.S ? st_in[j] : make_float2(0.f, 0.f);
+            if (COLS && slice == 0) {
+                for (int x = threadIdx.x; x < kStage; x += kThreads) {
+                    const int j = first + x;
+                    sSt[x] = j < a.S ? st_in[j] : make_float2(0.f, 0.f);
+                }
             }
             cp_async_commit();
             cp_async_wait<0>();
@@ -552,17 +555,18 @@ bwd_f32_wide_kernel(const BwdFArgs a) {
     }
 }
 
+template <int NT>
 int launch_wide(const BwdFArgs &a, int64_t B, cudaStream_t stream) {
-    constexpr int kStaged = 48 + 8 * 10;
+    constexpr int kStaged = 48 + 8 * NT;
     constexpr size_t smem = (size_t)2 * kStaged * 68 * sizeof(float) + kStaged * sizeof(float2);
     int rc;
-    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_wide_kernel<kRows>, smem, "bwd_f32 wide rows")) != MAT_OK) return rc;
-    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_wide_kernel<kColsV>, smem, "bwd_f32 wide dV")) != MAT_OK) return rc;
-    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_wide_kernel<kColsK>, smem, "bwd_f32 wide dK")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_wide_kernel<kRows, NT>, smem, "bwd_f32 wide rows")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_wide_kernel<kColsV, NT>, smem, "bwd_f32 wide dV")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_f32_wide_kernel<kColsK, NT>, smem, "bwd_f32 wide dK")) != MAT_OK) return rc;
     const dim3 grid((unsigned)a.HH, (unsigned)((a.S + kT - 1) / kT), (unsigned)B);
-    bwd_f32_wide_kernel<kRows><<<grid, kThreads, smem, stream>>>(a);
-    bwd_f32_wide_kernel<kColsV><<<grid, kThreads, smem, stream>>>(a);
-    bwd_f32_wide_kernel<kColsK><<<grid, kThreads, smem, stream>>>(a);
+    bwd_f32_wide_kernel<kRows, NT><<<grid, kThreads, smem, stream>>>(a);
+    bwd_f32_wide_kernel<kColsV, NT><<<grid, kThreads, smem, stream>>>(a);
+    bwd_f32_wide_kernel<kColsK, NT><<<grid, kThreads, smem, stream>>>(a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "fp32 tensor-core backward (wide heads) launch");
     note_kernel("bwd_f32_mma");
@@ -614,11 +618,14 @@ int launch_bwd_f32_mma(const void *q, const void *k, const void *v, const void *
     a.right = (int32_t)std::min<int64_t>(right, a.S);
     a.scale = scale;
     a.D = (int32_t)D;
-    if (D > 64) return launch_wide(a, B, stream);
+    // (a walk of 81 to 144 columns - the reference's default window of 64 either side - in one pass of 18 tiles)
+    const bool one18 = a.left + a.right + 16 > 80 && a.left + a.right + 16 <= 144;
+    if (D > 64) return one18 ? launch_wide<18>(a, B, stream) : launch_wide<10>(a, B, stream);
     const char *walk = std::getenv("MAT_BWD_F32_WALK");
     // (a 64-wide head whose walk is one pass takes that kernel too: its rows pass keeps S and dP instead of
     // recomputing them; MAT_BWD_F32_WALK=recompute or chunks keeps it on the kernels below)
-    if (D == 64 && a.left + a.right + 16 <= 80 && !walk) return launch_wide(a, B, stream);
+    if (D == 64 && a.left + a.right + 16 <= 80 && !walk) return launch_wide<10>(a, B, stream);
+    if (D == 64 && one18 && !walk) return launch_wide<18>(a, B, stream);
     // columns a warp's 16 rows meet: up to 160 the warp walks its own range in passes of 10 tiles (one pass at 64
     // causal taps); wider windows walk the 64-column chunks.  MAT_BWD_F32_WALK=chunks forces those (a measurement aid).
     const bool own = a.left + a.right + 16 <= 160 && !(walk && std::strcmp(walk, "chunks") == 0);
