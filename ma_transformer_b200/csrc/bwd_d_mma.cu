@@ -298,11 +298,11 @@ bwd_d_kernel(const BwdDArgs a) {
 // the first pass of the same rows wrote when the walk has a second one (a row of dQ, dK or dV belongs to one thread
 // pair of one CTA: no atomics).  Registers hold one pass's two score tiles and one slice's fragments whatever D is.
 // A one-pass walk (windows of at most 64 taps) keeps S and dP from the statistics sweep instead of recomputing them.
-template <typename T, int PASS>
+template <typename T, int PASS, int NS>
 __global__ void __launch_bounds__(kThreads)
 bwd_d_wide_kernel(const BwdDArgs a) {
     using M = ptx::Mma<T>;
-    constexpr int NS = 5, LD = 64 + 8, KS = 4;
+    constexpr int LD = 64 + 8, KS = 4;
     constexpr int kStage = 48 + 16 * NS;
     constexpr bool COLS = PASS != kRows;
     constexpr bool kTwo = PASS != kColsV;   // two score-shaped products (S and dP); the dV pass needs only S^T
@@ -373,10 +373,11 @@ bwd_d_wide_kernel(const BwdDArgs a) {
             __syncthreads();   // whoever still read the buffers is done
             stage(sY1, y1, first, slice);
             if constexpr (kTwo) stage(sY2, y2, first, slice);
-            static_assert(kStage <= kThreads, "one thread per staged row's statistics");
-            if (COLS && slice == 0 && threadIdx.x < kStage) {
-                const int j = first + threadIdx.x;
-                sSt[threadIdx.x] = j < a.S ? st_in[j] : make_float2(0.f, 0.f);
+            if (COLS && slice == 0) {
+                for (int x = threadIdx.x; x < kStage; x += kThreads) {
+                    const int j = first + x;
+                    sSt[x] = j < a.S ? st_in[j] : make_float2(0.f, 0.f);
+                }
             }
             cp_async_commit();
             cp_async_wait<0>();
@@ -537,18 +538,18 @@ bwd_d_wide_kernel(const BwdDArgs a) {
     }
 }
 
-template <typename T>
+template <typename T, int NS>
 int launch_wide(const BwdDArgs &a, int64_t B, cudaStream_t stream) {
-    constexpr int kStaged = 48 + 16 * 5;
+    constexpr int kStaged = 48 + 16 * NS;
     constexpr size_t smem = (size_t)2 * kStaged * 72 * sizeof(T) + kStaged * sizeof(float2);
     int rc;
-    if ((rc = ensure_dynamic_smem((const void *)bwd_d_wide_kernel<T, kRows>, smem, "bwd_d wide rows")) != MAT_OK) return rc;
-    if ((rc = ensure_dynamic_smem((const void *)bwd_d_wide_kernel<T, kColsV>, smem, "bwd_d wide dV")) != MAT_OK) return rc;
-    if ((rc = ensure_dynamic_smem((const void *)bwd_d_wide_kernel<T, kColsK>, smem, "bwd_d wide dK")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_d_wide_kernel<T, kRows, NS>, smem, "bwd_d wide rows")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_d_wide_kernel<T, kColsV, NS>, smem, "bwd_d wide dV")) != MAT_OK) return rc;
+    if ((rc = ensure_dynamic_smem((const void *)bwd_d_wide_kernel<T, kColsK, NS>, smem, "bwd_d wide dK")) != MAT_OK) return rc;
     const dim3 grid((unsigned)a.HH, (unsigned)((a.S + kT - 1) / kT), (unsigned)B);
-    bwd_d_wide_kernel<T, kRows><<<grid, kThreads, smem, stream>>>(a);
-    bwd_d_wide_kernel<T, kColsV><<<grid, kThreads, smem, stream>>>(a);
-    bwd_d_wide_kernel<T, kColsK><<<grid, kThreads, smem, stream>>>(a);
+    bwd_d_wide_kernel<T, kRows, NS><<<grid, kThreads, smem, stream>>>(a);
+    bwd_d_wide_kernel<T, kColsV, NS><<<grid, kThreads, smem, stream>>>(a);
+    bwd_d_wide_kernel<T, kColsK, NS><<<grid, kThreads, smem, stream>>>(a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "16-bit backward (wide heads) launch");
     note_kernel("bwd_d_mma");
@@ -628,12 +629,20 @@ int launch_bwd_d_mma(const void *q, const void *k, const void *v, const void *do
     a.right = (int32_t)std::min<int64_t>(right, a.S);
     a.scale = scale;
     a.D = (int32_t)D;
-    // heads wider than 128 columns go 64 columns at a time (a head of 128 gains nothing from it: 0.353 against
-    // 0.339 ms at 65536 tokens x 4 heads x 64 taps; MAT_BWD_D_WALK=sliced sends its one-pass walks there, a
-    // measurement aid)
+    // heads wider than 128 columns go 64 columns at a time.  A head of 128 does so where that makes its walk one pass
+    // instead of two (81 to 144 columns: the rows pass then keeps S and dP); with 64 taps it gains nothing from it
+    // (0.353 against 0.339 ms at 65536 tokens x 4 heads; MAT_BWD_D_WALK=sliced sends those there too, chunks or whole
+    // keeps every window on the kernels above: measurement aids)
     const char *walk = std::getenv("MAT_BWD_D_WALK");
-    if (D > 128 || (D == 128 && a.left + a.right + 16 <= 80 && walk && std::strcmp(walk, "sliced") == 0))
-        return dtype == MAT_BF16 ? launch_wide<__nv_bfloat16>(a, B, stream) : launch_wide<__half>(a, B, stream);
+    const bool sliced128 = D == 128 && (walk ? std::strcmp(walk, "sliced") == 0 && a.left + a.right + 16 <= 144
+                                             : a.left + a.right + 16 > 80 && a.left + a.right + 16 <= 144);
+    if (D > 128 || sliced128)
+    {
+        // (a walk of 81 to 144 columns - the reference's default window of 64 either side - in one pass of 9 steps)
+        if (a.left + a.right + 16 > 80 && a.left + a.right + 16 <= 144)
+            return dtype == MAT_BF16 ? launch_wide<__nv_bfloat16, 9>(a, B, stream) : launch_wide<__half, 9>(a, B, stream);
+        return dtype == MAT_BF16 ? launch_wide<__nv_bfloat16, 5>(a, B, stream) : launch_wide<__half, 5>(a, B, stream);
+    }
     return dtype == MAT_BF16 ? launch_any_d<__nv_bfloat16>(a, B, D, stream) : launch_any_d<__half>(a, B, D, stream);
 }
 

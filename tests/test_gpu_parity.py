@@ -782,15 +782,17 @@ def test_16bit_backward_for_wide_heads(monkeypatch, dtype, D, B, S, H, left, rig
     (1, 512, 2, 63, 0, 1), (2, 200, 3, 32, 32, 1), (1, 33, 1, 8, 8, 1), (1, 70, 1, 40, 41, 1), (1, 300, 2, 64, 64, 1),
     (1, 256, 2, 15, 0, 2), (1, 600, 2, 600, 600, 1), (1, 600, 1, 600, 0, 1),
 ])
-@pytest.mark.parametrize("walk", ["default", "chunks"])
+@pytest.mark.parametrize("walk", ["default", "chunks", "whole"])
 def test_16bit_backward_for_other_head_widths(monkeypatch, walk, dtype, D, B, S, H, left, right, dil):
     """The 16-bit backward for head widths that are multiples of 16 up to 128 other than 64 (the reference's
     kernel takes any width: src/cuda/sparse_attention_kernel.cu:265-346) on the warp-level tensor-core kernels:
     against autograd in fp64 through a dense masked softmax on the same rounded inputs, and against the
     one-warp-per-row kernels.  Narrow windows default to the walk in which every warp takes its own column range;
     MAT_BWD_D_WALK=chunks keeps them on the 64-column chunks the wide ones use."""
-    if walk == "chunks":
-        monkeypatch.setenv("MAT_BWD_D_WALK", "chunks")
+    if walk != "default":   # ("whole": a head of 128 columns in one piece where the default takes it 64 columns at a time)
+        if walk == "whole" and (D != 128 or not 80 < left + right + 16 <= 144):
+            pytest.skip("no such variant for this shape")
+        monkeypatch.setenv("MAT_BWD_D_WALK", walk)
     spec = PatternSpec(left=left, right=right, dilation=dil)
     q, k, v = seeded_qkv(89, B, S, H, D, dtype)
     go = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(90)).to(dtype)
