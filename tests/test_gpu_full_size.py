@@ -109,3 +109,39 @@ def test_cfg5_attention_full_size_every_row():
     want = oracle_out(q, k, v, spec)
     e = float(np.abs(got - want).max())
     assert e <= BF16_ABS, (e, _worst_rows(got, want))
+
+
+@pytest.mark.parametrize("D,H", [(64, 8), (128, 4), (256, 2)])
+def test_reference_precision_default_window_long_sequence_every_row(D, H):
+    # what an unmodified caller of the reference passes: fp32, window_size=64 (keys i-64..i+64); 65536 tokens x 512
+    # columns as 8 heads of 64, 4 of 128, 2 of 256 (its layer passes one head of width model_dim)
+    spec = PatternSpec.sliding_window(64)
+    q, k, v = seeded_qkv(8, 1, 65536, H, D)
+    got = _run(spec, q, k, v)
+    assert nat.last_kernel() == "mma_window_f32"
+    assert np.isfinite(got).all()
+    assert rel_err(got, oracle_out(q, k, v, spec)) <= FP32_REL
+
+
+@pytest.mark.parametrize("D,H,dtype", [(128, 4, torch.float32), (256, 2, torch.float32), (256, 2, torch.bfloat16)])
+@pytest.mark.parametrize("left,right", [(63, 0), (64, 64)])
+def test_wide_head_backward_long_sequence_against_warp_kernels(monkeypatch, D, H, dtype, left, right):
+    # 65536 tokens: tile indices and offsets of full size; the one-warp-per-row kernels (fp32 arithmetic, no tensor
+    # cores, no slicing of the head) are the independent implementation at a size autograd through a dense mask
+    # cannot reach
+    spec = PatternSpec(left=left, right=right)
+    q, k, v = seeded_qkv(9, 1, 65536, H, D, dtype, scale=0.5)
+    go = torch.randn(1, 65536, H, D, generator=torch.Generator().manual_seed(10)).to(dtype)
+    args = tuple(t.to(DEV) for t in (q, k, v, go))
+    got = ext.backward_pattern(*args, spec)
+    torch.cuda.synchronize()
+    assert nat.last_kernel() == ("bwd_f32_mma" if dtype == torch.float32 else "bwd_d_mma") and nat.device_status() == 0
+    monkeypatch.setenv("MAT_BWD_KERNEL", "warp")
+    want = ext.backward_pattern(*args, spec)
+    torch.cuda.synchronize()
+    assert nat.last_kernel() == "bwd_window"
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    for name, a, b in zip(("dQ", "dK", "dV"), got, want):
+        assert torch.isfinite(a).all(), name
+        err = float((a.float() - b.float()).abs().max())
+        assert err <= tol * max(1.0, float(b.float().abs().max())), f"{name}: {err}"
