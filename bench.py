@@ -13,8 +13,9 @@ exchanges them by send/recv instead).  Steps are independent forwards over
 rotating input sets; they are captured in CUDA graphs and alternate over two
 streams (``--lanes``), each with its own output buffer.
 ``--workload block|longformer|orderbook|dense|backward|fp32|refwindow`` time the other configurations on one GPU
-(refwindow: the reference's default window_size = 64, i.e. keys i-64 .. i+64, at the headline shape); each of them
-compares sampled row blocks of its last timed launch with the CPU oracle after the timed region.
+(refwindow: the reference's default window_size = 64, i.e. keys i-64 .. i+64, at the headline shape; with
+``--head-dim`` and ``--dtype fp32`` it and ``backward`` run other head widths and the reference's own precision);
+each forward workload compares sampled row blocks of its last timed launch with the CPU oracle after the timed region.
 
 Prints ONE JSON line.  ``value`` is tokens/s with inputs resident in HBM, timed
 with CUDA events over exactly K steps (max over ranks); ``e2e`` is the same
@@ -590,10 +591,17 @@ def other_workload_arm(args):
         return
     if args.workload == "backward":
         # backward of the headline window (64 causal taps at the cfg-2 shape): dQ, dK, dV from Q, K, V, dO
-        Bw, S, Hw = B, SEQ, H
-        spec = PatternSpec.causal_window(TAPS)
-        nbytes = 7 * Bw * S * Hw * 64 * 2      # four tensors read once, three written once
-        sets = [tuple((torch.randn(Bw, S, Hw, 64, generator=g) * 0.5).to(torch.bfloat16).to(dev) for _ in range(4))
+        # (--head-dim, --dtype: other head widths at the same 512 columns per token, the reference's precision;
+        # --left / --right given together with one of them: another window)
+        Dw = args.head_dim
+        tdt = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+        esz = 2 if args.dtype == "bf16" else 4
+        Bw, S, Hw = B, SEQ, H * 64 // Dw
+        other = Dw != 64 or args.dtype != "bf16"
+        spec = PatternSpec(left=args.left, right=args.right) if other and (args.left, args.right) != (64, 64) \
+            else PatternSpec.causal_window(TAPS)
+        nbytes = 7 * Bw * S * Hw * Dw * esz      # four tensors read once, three written once
+        sets = [tuple((torch.randn(Bw, S, Hw, Dw, generator=g) * 0.5).to(tdt).to(dev) for _ in range(4))
                 for _ in range(3)]
         for i in range(args.warmup):
             ext.backward_pattern(*sets[i % 3], spec)
@@ -614,15 +622,16 @@ def other_workload_arm(args):
         print(json.dumps({
             "metric": "sparse-attn bwd tokens/s (backward)", "value": Bw * S / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"causal sliding-window bwd B={Bw} N={S} H={Hw} d=64 taps={TAPS} bf16",
+            "dtype": "bf16" if args.dtype == "bf16" else "f32", "data": "synthetic",
+            "config": {"workload": f"sliding-window bwd B={Bw} N={S} H={Hw} d={Dw} taps -{spec.left}..+{spec.right} {args.dtype}",
                        "l2": "3 rotating input sets"},
-            "clocks": clocks, "kernel": nat.last_kernel(), "gpu_launches": 2 * args.steps,
+            "clocks": clocks, "kernel": nat.last_kernel(),
+            "gpu_launches": (2 if nat.last_kernel() == "bwd_window_mma" else 3) * args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": f"{peak_kind} HBM copy bandwidth", "bytes_per_launch_algorithmic": nbytes,
-                         # dram bytes of the two passes, from an ncu capture of one backward
-                         "traffic": 322e6 + 375e6,
-                         "note": "per backward (two launches: rows pass and cols pass)"},
+                         # dram bytes of the two passes, from an ncu capture of one backward (headline shape only)
+                         "traffic": None if other else 322e6 + 375e6,
+                         "note": "per backward (rows pass and cols pass; a dV and a dK pass for fp32 and other head widths)"},
             "device_status": nat.device_status()}), flush=True)
         return
     Dw = 64
@@ -641,7 +650,7 @@ def other_workload_arm(args):
         spec = PatternSpec(left=args.left, right=args.right, dilation=args.dilation)
         flops = Bw * Hw * S * (args.left + args.right + 1) * 4 * Dw
         name = (f"window fwd B={Bw} N={S} H={Hw} d={Dw} taps -{args.left}..+{args.right}"
-                + (f" dilation {args.dilation}" if args.dilation > 1 else "") + " bf16")
+                + (f" dilation {args.dilation}" if args.dilation > 1 else "") + f" {args.dtype}")
     elif args.workload == "dense":
         # the reference's dense_forward (every query over every key), the tensor-bound end of the path
         Bw, S, Hw = 2, 8192, 8
@@ -654,9 +663,10 @@ def other_workload_arm(args):
         spec = PatternSpec.longformer(64, 64, glob)
         flops = Bw * Hw * (S * 129 + 2 * 32 * S) * 4 * 64
         name = f"Longformer fwd B={Bw} N={S} H={Hw} d=64 window +-64, 32 global tokens bf16"
-    nbytes = 4 * Bw * S * Hw * Dw * 2
-    sets = [tuple(torch.randn(Bw, S, Hw, Dw, generator=g).to(torch.bfloat16).to(dev) for _ in range(3))
-            for _ in range(2)]
+    f32 = args.workload == "refwindow" and args.dtype == "fp32"
+    nbytes = 4 * Bw * S * Hw * Dw * (4 if f32 else 2)
+    sets = [tuple(torch.randn(Bw, S, Hw, Dw, generator=g).to(torch.float32 if f32 else torch.bfloat16).to(dev)
+                  for _ in range(3)) for _ in range(2)]
     out = torch.empty_like(sets[0][0])
     for i in range(args.warmup):
         ext.forward_pattern(*sets[i % 2], spec, out=out)
@@ -679,7 +689,7 @@ def other_workload_arm(args):
     starts = [(0, 0), (Bw - 1, S - 128), (Bw // 2, S // 2 - 64), (0, S // 4 + 64)]
     if args.workload == "longformer":
         starts += [(0, int(glob[0]) - 64), (Bw - 1, int(glob[-1]) - 64)]      # blocks that hold a global position
-    parity = sampled_parity(out, *last, spec, starts)
+    parity = sampled_parity(out, *last, spec, starts, tol=None if f32 else 2e-2)
     if args.workload == "dense":
         tpeak, tkind = measured_peak_tflops()
         tf = flops / (ms * 1e-3) / 1e12
@@ -695,7 +705,7 @@ def other_workload_arm(args):
     print(json.dumps({
         "metric": f"sparse-attn fwd tokens/s ({args.workload})", "value": Bw * S / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "dtype": "bf16", "data": "synthetic", "config": {"workload": name, "l2": "2 rotating input sets"},
+        "dtype": "f32" if f32 else "bf16", "data": "synthetic", "config": {"workload": name, "l2": "2 rotating input sets"},
         "clocks": clocks, "kernel": nat.last_kernel(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": f"{peak_kind} HBM copy bandwidth", "bytes_per_launch_algorithmic": nbytes},
@@ -711,8 +721,10 @@ def main():
     ap.add_argument("--left", type=int, default=64, help="refwindow: taps before the query")
     ap.add_argument("--right", type=int, default=64, help="refwindow: taps after the query")
     ap.add_argument("--dilation", type=int, default=1, help="refwindow: dilation")
-    ap.add_argument("--head-dim", type=int, default=64, choices=[16, 32, 64, 128],
-                    help="refwindow: head width (the number of heads changes with it, 512 columns per token)")
+    ap.add_argument("--head-dim", type=int, default=64, choices=[16, 32, 64, 128, 256, 512],
+                    help="refwindow, backward: head width (the number of heads changes with it, 512 columns per token)")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"],
+                    help="refwindow, backward: element type (fp32 is the reference's own precision)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
