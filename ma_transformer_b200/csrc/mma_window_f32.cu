@@ -558,7 +558,195 @@ window_f32_wide_kernel(const float *__restrict__ q, const float *__restrict__ k,
     }
 }
 
+// Wide heads with windows that take a warp more than one pass (up to dense): two sweeps over the passes, the head
+// dimension 64 columns at a time in both.  Sweep one accumulates each pass's scores over the K slices and keeps the
+// running maximum and sum of the rows; sweep two forms the scores again, turns them into normalised weights, and adds
+// their product with every V slice to the output rows, which the first pass of a row wrote (a row of the output
+// belongs to one thread pair of one CTA, so the read-modify-write needs no atomics).  One buffer per operand: the
+// three CTAs of an SM cover each other's copies.
 template <int NT>
+__global__ void __launch_bounds__(kThreads)
+window_f32_wide_passes_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                              float *__restrict__ o, const WinFParams P) {
+    constexpr int LD = 64 + 4, KS = 8;
+    constexpr int kStage = 48 + 8 * NT;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    float *sBuf = reinterpret_cast<float *>(smem_raw);   // [kStage][LD]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int hh = blockIdx.x, b = blockIdx.z, q0 = blockIdx.y * kTQ;
+    const int D = P.D, n_slices = D >> 6;
+    const int p_first = q0 + P.off1;
+    const int key_lo = max(0, p_first - P.left);
+    const int key_hi = min(P.Skv1 - 1, min(q0 + kTQ, P.Sq1) - 1 + P.off1 + P.right);
+    const int base_w = max(key_lo, p_first + 16 * warp - P.left);   // the warp's first key
+    const int st_off = (base_w - key_lo) * LD;                      // its row inside the staged range of a pass
+    int n_pass = 0;
+    if (key_hi >= key_lo) {
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) {
+            const int keys_w = min(key_hi, p_first + 16 * w + 15 + P.right) - max(key_lo, p_first + 16 * w - P.left) + 1;
+            n_pass = max(n_pass, (keys_w + 8 * NT - 1) / (8 * NT));
+        }
+        n_pass = min(n_pass, (key_hi - key_lo) / (8 * NT) + 1);
+    }
+    const int64_t tok = (int64_t)P.HH * D;
+    const float *kb_ptr = k + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+    const float *vb_ptr = v + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+    const int row_a = q0 + warp * 16 + g, row_b = row_a + 8;
+    const float *qa = q + (((int64_t)b * P.Sq1 + row_a) * P.HH + hh) * D;
+    const float *qb = q + (((int64_t)b * P.Sq1 + row_b) * P.HH + hh) * D;
+    float *oa = o + (((int64_t)b * P.Sq1 + row_a) * P.HH + hh) * D + 2 * t;
+    float *ob = o + (((int64_t)b * P.Sq1 + row_b) * P.HH + hh) * D + 2 * t;
+    const int pos[2] = {row_a + P.off1, row_b + P.off1};
+
+    if (n_pass == 0) {   // a tile whose rows see no key (the whole CTA alike): zeros
+        for (int c = 0; c < D; c += 8) {
+            if (row_a < P.Sq1) *reinterpret_cast<float2 *>(oa + c) = make_float2(0.f, 0.f);
+            if (row_b < P.Sq1) *reinterpret_cast<float2 *>(ob + c) = make_float2(0.f, 0.f);
+        }
+        return;
+    }
+    // one 64-column slice of the kStage rows of pass c, of K or V; rows past the tile's last key are zeros
+    auto stage = [&](const float *src, int c, int slice) {
+        const int first = key_lo + c * 8 * NT;
+        __syncthreads();   // whoever still read the buffer is done
+        for (int x = threadIdx.x; x < kStage * 16; x += kThreads) {
+            const int r = x >> 4, pc = x & 15;
+            const int j = first + r;
+            const bool in = j <= key_hi;
+            cp_async16(sBuf + r * LD + pc * 4, src + (int64_t)(in ? j : 0) * tok + slice * 64 + pc * 4, in ? 16 : 0);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+    };
+    // the masked scores of pass c
+    auto scores = [&](int c, float (&s)[NT][4]) {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+        for (int sl = 0; sl < n_slices; ++sl) {
+            uint32_t qf[KS][4];
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                const int col = sl * 64 + ks * 8 + t;
+                qf[ks][0] = row_a < P.Sq1 ? __float_as_uint(qa[col]) : 0u;
+                qf[ks][1] = row_b < P.Sq1 ? __float_as_uint(qb[col]) : 0u;
+                qf[ks][2] = row_a < P.Sq1 ? __float_as_uint(qa[col + 4]) : 0u;
+                qf[ks][3] = row_b < P.Sq1 ? __float_as_uint(qb[col + 4]) : 0u;
+            }
+            stage(kb_ptr, c, sl);
+            const uint32_t *ck = reinterpret_cast<const uint32_t *>(sBuf + st_off);
+            // a slice's share of the scores in accumulators of its own, added by ordinary additions: the tensor
+            // core's fp32 sums are not rounded to nearest, and a chain over 256 or 512 columns drifts (1.04e-5 on
+            // dense rows of 4096 keys at D = 256 with one chain)
+            float ss[NT][4];
+#pragma unroll
+            for (int n = 0; n < NT; ++n) ss[n][0] = ss[n][1] = ss[n][2] = ss[n][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                uint32_t q_hi[4], q_lo[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) split_tf32<true>(qf[ks][e], q_hi[e], q_lo[e]);
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    const uint32_t *kr = ck + (n * 8 + g) * LD + ks * 8 + t;
+                    mma_3x<true>(ss[n], q_hi, q_lo, kr[0], kr[4]);
+                }
+            }
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[n][e] += ss[n][e];
+        }
+        const int kb = base_w + c * 8 * NT;
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = kb + n * 8 + 2 * t + (e & 1), p = pos[e >> 1];
+                const bool ok = j >= p - P.left && j <= p + P.right && j < P.Skv1;
+                s[n][e] = ok ? s[n][e] : -INFINITY;
+            }
+    };
+    float s[NT][4];
+    // ---- sweep one: the rows' maximum and sum ----
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    for (int c = 0; c < n_pass; ++c) {
+        scores(c, s);
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+        float mus[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float m_new = fmaxf(m_run[i], mx[i]);
+            l_run[i] *= m_new == -INFINITY ? 1.f : ptx::ex2((m_run[i] - m_new) * P.sl2);
+            m_run[i] = m_new;
+            mus[i] = m_new == -INFINITY ? 0.f : m_new * P.sl2;
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) l_run[e >> 1] += ptx::ex2(fmaf(s[n][e], P.sl2, -mus[e >> 1]));
+    }
+    float inv[2], mus[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float l = l_run[i];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        inv[i] = l > 0.f ? 1.f / l : 0.f;
+        mus[i] = m_run[i] == -INFINITY ? 0.f : m_run[i] * P.sl2;
+    }
+    // ---- sweep two: normalised weights, output rows (+)= W V, 64 columns at a time ----
+    for (int c = 0; c < n_pass; ++c) {
+        scores(c, s);
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[n][e] = ptx::ex2(fmaf(s[n][e], P.sl2, -mus[e >> 1])) * inv[e >> 1];
+        for (int sl = 0; sl < n_slices; ++sl) {
+            stage(vb_ptr, c, sl);
+            const uint32_t *cv = reinterpret_cast<const uint32_t *>(sBuf + st_off);
+            float part[KS][4];
+#pragma unroll
+            for (int d = 0; d < KS; ++d) part[d][0] = part[d][1] = part[d][2] = part[d][3] = 0.f;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const uint32_t pa[4] = {__float_as_uint(s[n][0]), __float_as_uint(s[n][2]), __float_as_uint(s[n][1]),
+                                        __float_as_uint(s[n][3])};
+                uint32_t p_hi[4], p_lo[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) split_tf32<true>(pa[e], p_hi[e], p_lo[e]);
+                const uint32_t *vr = cv + (n * 8 + 2 * t) * LD + g;
+#pragma unroll
+                for (int d = 0; d < KS; ++d) mma_3x<true>(part[d], p_hi, p_lo, vr[d * 8], vr[LD + d * 8]);
+            }
+#pragma unroll
+            for (int d = 0; d < KS; ++d) {
+                if (row_a < P.Sq1) {
+                    float2 val = make_float2(part[d][0], part[d][1]);
+                    float2 *dst = reinterpret_cast<float2 *>(oa + sl * 64 + d * 8);
+                    if (c > 0) { const float2 old = *dst; val.x += old.x; val.y += old.y; }
+                    *dst = val;
+                }
+                if (row_b < P.Sq1) {
+                    float2 val = make_float2(part[d][2], part[d][3]);
+                    float2 *dst = reinterpret_cast<float2 *>(ob + sl * 64 + d * 8);
+                    if (c > 0) { const float2 old = *dst; val.x += old.x; val.y += old.y; }
+                    *dst = val;
+                }
+            }
+        }
+    }
+}
+
+template <int NT, bool PASSES = false>
 int launch_wide(const Problem &p) {
     const int64_t dil = p.pat.dilation;
     WinFParams wp;
@@ -570,8 +758,8 @@ int launch_wide(const Problem &p) {
     wp.right = (int32_t)std::min<int64_t>(p.pat.right, wp.Skv1);
     wp.sl2 = p.scale * 1.4426950408889634f;
     wp.D = (int32_t)p.D;
-    auto kern = window_f32_wide_kernel<NT>;
-    constexpr size_t smem = (size_t)2 * (48 + 8 * NT) * 68 * sizeof(float);
+    auto kern = PASSES ? window_f32_wide_passes_kernel<NT> : window_f32_wide_kernel<NT>;
+    constexpr size_t smem = (size_t)(PASSES ? 1 : 2) * (48 + 8 * NT) * 68 * sizeof(float);
     if (int rc = ensure_dynamic_smem((const void *)kern, smem, "cudaFuncSetAttribute(window_f32_wide_kernel)")) return rc;
     const dim3 grid((unsigned)wp.HH, (unsigned)((wp.Sq1 + kTQ - 1) / kTQ), (unsigned)p.B);
     kern<<<grid, kThreads, smem, p.stream>>>((const float *)p.q, (const float *)p.k, (const float *)p.v, (float *)p.o, wp);
@@ -616,14 +804,14 @@ static int64_t warp_span(const Problem &p) {
     return std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16;
 }
 
-// fp32 window patterns (any taps, any dilation that divides the lengths) with head width 32 or 64, and windows of at
-// most 128 taps between their two sides with a head width of 128, 192, ... 512; whole tensors, 16-byte aligned.
+// fp32 window patterns (any taps, any dilation that divides the lengths) with head width 32, 64, 128, 192, ... 512;
+// whole tensors, 16-byte aligned.
 // MAT_F32_KERNEL=tiled keeps them on the FMA-pipe kernels (a measurement aid).
 bool mma_window_f32_supports(const Problem &p) {
     if (p.pat.kind != MAT_WINDOW || p.dtype != MAT_F32) return false;
     const bool wide_head = p.D > 64 && p.D <= 512 && p.D % 64 == 0;
     if (p.D != 32 && p.D != 64 && !wide_head) return false;
-    if (wide_head && (p.pat.dilation < 1 || warp_span(p) > 144)) return false;
+    if (wide_head && p.pat.dilation < 1) return false;
     if (p.k_prev || p.k_next || p.q_ts || p.k_ts || p.v_ts || p.o_ts) return false;
     const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
     if (al % 16) return false;
@@ -636,7 +824,8 @@ bool mma_window_f32_supports(const Problem &p) {
 }
 
 int launch_mma_window_f32(const Problem &p) {
-    if (p.D > 64) return warp_span(p) <= 80 ? launch_wide<10>(p) : launch_wide<18>(p);
+    if (p.D > 64)   // (one pass of 10 or 18 tiles per warp; wider windows, up to dense: passes of 10)
+        return warp_span(p) <= 80 ? launch_wide<10>(p) : warp_span(p) <= 144 ? launch_wide<18>(p) : launch_wide<10, true>(p);
     if (const char *f = std::getenv("MAT_F32_KERNEL"); f && std::strcmp(f, "sliced") == 0 && p.D == 64 && warp_span(p) <= 144)
         return warp_span(p) <= 80 ? launch_wide<10>(p) : launch_wide<18>(p);   // (a measurement aid)
     const int64_t dil = p.pat.dilation, skv1 = p.Skv / dil;

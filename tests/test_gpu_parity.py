@@ -86,7 +86,7 @@ def test_fp32_window_kernels_vs_oracle(monkeypatch, kernel, spec, D):
                                     (1500, PatternSpec.sliding_window(400)), (2100, PatternSpec(left=513, right=0)),
                                     (4096, PatternSpec.sliding_window(4096))],
                          ids=["dense1000", "causal1000", "pm400", "l513", "dense4096"])
-@pytest.mark.parametrize("D", [32, 64])
+@pytest.mark.parametrize("D", [32, 64, 128, 256])
 def test_fp32_wide_windows_on_tensor_cores(S, spec, D):
     """fp32 windows of any width, dense and causal dense included, as three TF32 products per product: the fp32 bar
     holds on rows of thousands of keys (the sums of a chunk end with the chunk, and chunks are combined by
