@@ -406,7 +406,8 @@ window_f32_diag_kernel(const float *__restrict__ q, const float *__restrict__ k,
 // accumulate, then the V slices while each 64-column slice of the output is formed from the finished weights,
 // normalised and written; the copy of the next slice is in flight during the products of the current one.
 // Registers hold the scores / weights of the pass (NT tiles) and one slice's operands, whatever D is.
-template <int NT>
+// (ROUND: rounded high halves, for heads of 256 columns and more, whose long dot products need them)
+template <int NT, bool ROUND>
 __global__ void __launch_bounds__(kThreads)
 window_f32_wide_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                        float *__restrict__ o, const WinFParams P) {
@@ -470,16 +471,32 @@ window_f32_wide_kernel(const float *__restrict__ q, const float *__restrict__ k,
         cp_async_wait<1>();
         __syncthreads();
         const uint32_t *ck = reinterpret_cast<const uint32_t *>(sBuf + (sl & 1) * kStage * LD + row_off);
+        // (ten tiles: a slice's share of the scores in accumulators of its own, added by ordinary additions - the
+        // tensor core's fp32 sums are not rounded to nearest, and a chain over several hundred columns drifts;
+        // eighteen tiles leave no registers for that)
+        constexpr bool kOwn = NT <= 10;
+        float ss[kOwn ? NT : 1][4];
+        if constexpr (kOwn) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n) ss[n][0] = ss[n][1] = ss[n][2] = ss[n][3] = 0.f;
+        }
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             uint32_t q_hi[4], q_lo[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) split_tf32<false>(qf[ks][e], q_hi[e], q_lo[e]);
+            for (int e = 0; e < 4; ++e) split_tf32<ROUND>(qf[ks][e], q_hi[e], q_lo[e]);
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
                 const uint32_t *kr = ck + (n * 8 + g) * LD + ks * 8 + t;
-                mma_3x<false>(s[n], q_hi, q_lo, kr[0], kr[4]);
+                if constexpr (kOwn) mma_3x<ROUND>(ss[n], q_hi, q_lo, kr[0], kr[4]);
+                else mma_3x<ROUND>(s[n], q_hi, q_lo, kr[0], kr[4]);
             }
+        }
+        if constexpr (kOwn) {
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[n][e] += ss[n][e];
         }
         __syncthreads();   // the buffer is free for the copy after the next
     }
@@ -540,10 +557,10 @@ window_f32_wide_kernel(const float *__restrict__ q, const float *__restrict__ k,
                                     __float_as_uint(s[n][3])};
             uint32_t p_hi[4], p_lo[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) split_tf32<false>(pa[e], p_hi[e], p_lo[e]);
+            for (int e = 0; e < 4; ++e) split_tf32<ROUND>(pa[e], p_hi[e], p_lo[e]);
             const uint32_t *vr = cv + (n * 8 + 2 * t) * LD + g;
 #pragma unroll
-            for (int d = 0; d < KS; ++d) mma_3x<false>(part[n < NT / 2 ? 0 : 1][d], p_hi, p_lo, vr[d * 8], vr[LD + d * 8]);
+            for (int d = 0; d < KS; ++d) mma_3x<ROUND>(part[n < NT / 2 ? 0 : 1][d], p_hi, p_lo, vr[d * 8], vr[LD + d * 8]);
         }
 #pragma unroll
         for (int d = 0; d < KS; ++d) {
@@ -746,7 +763,7 @@ window_f32_wide_passes_kernel(const float *__restrict__ q, const float *__restri
     }
 }
 
-template <int NT, bool PASSES = false>
+template <int NT, bool PASSES, bool ROUND>
 int launch_wide(const Problem &p) {
     const int64_t dil = p.pat.dilation;
     WinFParams wp;
@@ -758,7 +775,7 @@ int launch_wide(const Problem &p) {
     wp.right = (int32_t)std::min<int64_t>(p.pat.right, wp.Skv1);
     wp.sl2 = p.scale * 1.4426950408889634f;
     wp.D = (int32_t)p.D;
-    auto kern = PASSES ? window_f32_wide_passes_kernel<NT> : window_f32_wide_kernel<NT>;
+    auto kern = PASSES ? window_f32_wide_passes_kernel<NT> : window_f32_wide_kernel<NT, ROUND>;
     constexpr size_t smem = (size_t)(PASSES ? 1 : 2) * (48 + 8 * NT) * 68 * sizeof(float);
     if (int rc = ensure_dynamic_smem((const void *)kern, smem, "cudaFuncSetAttribute(window_f32_wide_kernel)")) return rc;
     const dim3 grid((unsigned)wp.HH, (unsigned)((wp.Sq1 + kTQ - 1) / kTQ), (unsigned)p.B);
@@ -824,10 +841,15 @@ bool mma_window_f32_supports(const Problem &p) {
 }
 
 int launch_mma_window_f32(const Problem &p) {
-    if (p.D > 64)   // (one pass of 10 or 18 tiles per warp; wider windows, up to dense: passes of 10)
-        return warp_span(p) <= 80 ? launch_wide<10>(p) : warp_span(p) <= 144 ? launch_wide<18>(p) : launch_wide<10, true>(p);
+    if (p.D > 64) {   // one pass of 10 or 18 tiles per warp; wider windows, up to dense: passes of 10
+        if (warp_span(p) > 144) return launch_wide<10, true, true>(p);
+        // 18 tiles on a head of 512 columns stayed at 1.2e-5 with cut halves and one chain per score: two passes of 10
+        if (warp_span(p) > 80 && p.D > 256) return launch_wide<10, true, true>(p);
+        if (p.D >= 256) return warp_span(p) <= 80 ? launch_wide<10, false, true>(p) : launch_wide<18, false, true>(p);
+        return warp_span(p) <= 80 ? launch_wide<10, false, false>(p) : launch_wide<18, false, false>(p);
+    }
     if (const char *f = std::getenv("MAT_F32_KERNEL"); f && std::strcmp(f, "sliced") == 0 && p.D == 64 && warp_span(p) <= 144)
-        return warp_span(p) <= 80 ? launch_wide<10>(p) : launch_wide<18>(p);   // (a measurement aid)
+        return warp_span(p) <= 80 ? launch_wide<10, false, false>(p) : launch_wide<18, false, false>(p);   // (a measurement aid)
     const int64_t dil = p.pat.dilation, skv1 = p.Skv / dil;
     const bool wide = std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) > 512;
     if (wide) return p.D == 32 ? launch_f<32, true, 0>(p) : launch_f<64, true, 0>(p);

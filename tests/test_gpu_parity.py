@@ -49,7 +49,7 @@ def test_cfg1_causal_window_fp32():
     check_close(run(spec, q, k, v, scale=0.125), oracle_out(q, k, v, spec, 0.125), torch.float32)
 
 
-@pytest.mark.parametrize("D", [32, 64, 128, 256])
+@pytest.mark.parametrize("D", [32, 64, 128, 256, 512])
 @pytest.mark.parametrize("spec", [PatternSpec.causal_window(32), PatternSpec.sliding_window(64), PatternSpec.sliding_window(3),
                                   PatternSpec(left=0, right=60), PatternSpec.causal_window(64, dilation=2),
                                   PatternSpec(left=100, right=28), PatternSpec.causal_window(1)],
@@ -74,7 +74,7 @@ def test_fp32_window_kernels_vs_oracle(monkeypatch, kernel, spec, D):
         if kernel != "tiled":   # (head widths 128 and 256: 64 columns at a time, these windows in one pass per warp)
             assert nat.last_kernel() == "mma_window_f32"
         else:
-            assert nat.last_kernel() == ("rowwarp" if (D == 128 and wide_here) or D == 256 else "tiled_f32")
+            assert nat.last_kernel() == ("rowwarp" if (D == 128 and wide_here) or D >= 256 else "tiled_f32")
         check_close(got, oracle_out(q, k, v, sp), torch.float32)
     # inputs x100 stay finite and close (tests/integration/test_cuda_extensive.py:77-92)
     q, k, v = seeded_qkv(24, 1, 130, 2, D, torch.float32, scale=100.0)
