@@ -79,7 +79,9 @@ def test_fp32_window_kernels_vs_oracle(monkeypatch, kernel, spec, D):
     # inputs x100 stay finite and close (tests/integration/test_cuda_extensive.py:77-92)
     q, k, v = seeded_qkv(24, 1, 130, 2, D, torch.float32, scale=100.0)
     got = run(spec, q, k, v).cpu().numpy()
-    assert np.isfinite(got).all() and np.abs(got - oracle_out(q, k, v, spec)).max() <= 0.5
+    # (scores of this size sit where fp32 rounding of a dot product decides between neighbouring keys; the longer the
+    # dot product, the further two correct evaluation orders can be apart)
+    assert np.isfinite(got).all() and np.abs(got - oracle_out(q, k, v, spec)).max() <= 0.5 * max(1.0, D / 256)
 
 
 @pytest.mark.parametrize("S,spec", [(1000, PatternSpec.sliding_window(3000)), (1000, PatternSpec.causal_window(3000)),
@@ -701,7 +703,7 @@ def test_backward_matches_autograd_of_reference_oracle(B, S, H, D, W):
         assert (got.cpu().double() - ref.grad).abs().max() < 2e-5 * max(1.0, float(ref.grad.abs().max()))
 
 
-@pytest.mark.parametrize("D", [32, 64, 128, 256])
+@pytest.mark.parametrize("D", [32, 64, 128, 256, 512])
 @pytest.mark.parametrize("B,S,H,left,right,dil", [
     (1, 512, 2, 63, 0, 1), (2, 200, 3, 32, 32, 1), (1, 33, 1, 8, 8, 1), (1, 130, 2, 10, 3, 1), (1, 70, 1, 40, 41, 1),
     (1, 300, 2, 64, 64, 1), (1, 256, 2, 15, 0, 2), (2, 96, 1, 5, 5, 3), (1, 1000, 2, 1000, 1000, 1), (1, 1000, 1, 1000, 0, 1),
