@@ -593,12 +593,13 @@ int launch_f(const BwdFArgs &a, int64_t B, cudaStream_t stream) {
 
 }  // namespace
 
-// fp32 window patterns with head width 32, 64 or a multiple of 64 up to 512, lengths a multiple of the dilation,
+// fp32 window patterns with head width 16, 32, 48, 64 or a multiple of 64 up to 512, lengths a multiple of the dilation,
 // 16-byte aligned tensors.
 // MAT_BWD_KERNEL=warp keeps the warp-level kernels.
 bool bwd_f32_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil) {
     const bool wide_head = D > 64 && D <= 512 && D % 64 == 0;
-    if (dtype != MAT_F32 || (D != 32 && D != 64 && !wide_head) || dil < 1 || S % dil != 0) return false;
+    const bool narrow_head = D == 16 || D == 32 || D == 48 || D == 64;
+    if (dtype != MAT_F32 || (!narrow_head && !wide_head) || dil < 1 || S % dil != 0) return false;
     const char *env = std::getenv("MAT_BWD_KERNEL");
     if (env && std::strcmp(env, "warp") == 0) return false;
     const int64_t Sv = S / dil;
@@ -629,8 +630,12 @@ int launch_bwd_f32_mma(const void *q, const void *k, const void *v, const void *
     // columns a warp's 16 rows meet: up to 160 the warp walks its own range in passes of 10 tiles (one pass at 64
     // causal taps); wider windows walk the 64-column chunks.  MAT_BWD_F32_WALK=chunks forces those (a measurement aid).
     const bool own = a.left + a.right + 16 <= 160 && !(walk && std::strcmp(walk, "chunks") == 0);
-    if (own) return D == 32 ? launch_f<32, 10>(a, B, stream) : launch_f<64, 10>(a, B, stream);
-    return D == 32 ? launch_f<32, 0>(a, B, stream) : launch_f<64, 0>(a, B, stream);
+    switch (D) {
+    case 16: return own ? launch_f<16, 10>(a, B, stream) : launch_f<16, 0>(a, B, stream);
+    case 32: return own ? launch_f<32, 10>(a, B, stream) : launch_f<32, 0>(a, B, stream);
+    case 48: return own ? launch_f<48, 10>(a, B, stream) : launch_f<48, 0>(a, B, stream);
+    default: return own ? launch_f<64, 10>(a, B, stream) : launch_f<64, 0>(a, B, stream);
+    }
 }
 
 }  // namespace mat

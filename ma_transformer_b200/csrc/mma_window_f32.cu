@@ -815,19 +815,33 @@ int launch_f(const Problem &p) {
 
 }  // namespace
 
+// the instantiation for the problem's head width (16, 32, 48, 64 or 96 columns)
+template <bool ROUND, int NT>
+static int launch_head(const Problem &p) {
+    switch (p.D) {
+    case 16: return launch_f<16, ROUND, NT>(p);
+    case 32: return launch_f<32, ROUND, NT>(p);
+    case 48: return launch_f<48, ROUND, NT>(p);
+    case 96: return launch_f<96, ROUND, (NT == 18 ? 10 : NT)>(p);
+    default: return launch_f<64, ROUND, NT>(p);
+    }
+}
+
 // keys a warp's 16 rows can see
 static int64_t warp_span(const Problem &p) {
     const int64_t skv1 = p.Skv / p.pat.dilation;
     return std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16;
 }
 
-// fp32 window patterns (any taps, any dilation that divides the lengths) with head width 32, 64, 128, 192, ... 512;
+// fp32 window patterns (any taps, any dilation that divides the lengths) with head width 16, 32, 48, 64, 96, 128, 192,
+// ... 512;
 // whole tensors, 16-byte aligned.
 // MAT_F32_KERNEL=tiled keeps them on the FMA-pipe kernels (a measurement aid).
 bool mma_window_f32_supports(const Problem &p) {
     if (p.pat.kind != MAT_WINDOW || p.dtype != MAT_F32) return false;
     const bool wide_head = p.D > 64 && p.D <= 512 && p.D % 64 == 0;
-    if (p.D != 32 && p.D != 64 && !wide_head) return false;
+    const bool narrow_head = p.D == 16 || p.D == 32 || p.D == 48 || p.D == 64 || p.D == 96;   // (96: 768 columns in 8 heads)
+    if (!narrow_head && !wide_head) return false;
     if (wide_head && p.pat.dilation < 1) return false;
     if (p.k_prev || p.k_next || p.q_ts || p.k_ts || p.v_ts || p.o_ts) return false;
     const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
@@ -841,7 +855,7 @@ bool mma_window_f32_supports(const Problem &p) {
 }
 
 int launch_mma_window_f32(const Problem &p) {
-    if (p.D > 64) {   // one pass of 10 or 18 tiles per warp; wider windows, up to dense: passes of 10
+    if (p.D > 64 && p.D % 64 == 0) {   // one pass of 10 or 18 tiles per warp; wider windows, up to dense: passes of 10
         if (warp_span(p) > 144) return launch_wide<10, true, true>(p);
         // 18 tiles on a head of 512 columns stayed at 1.2e-5 with cut halves and one chain per score: two passes of 10
         if (warp_span(p) > 80 && p.D > 256) return launch_wide<10, true, true>(p);
@@ -852,7 +866,7 @@ int launch_mma_window_f32(const Problem &p) {
         return warp_span(p) <= 80 ? launch_wide<10, false, false>(p) : launch_wide<18, false, false>(p);   // (a measurement aid)
     const int64_t dil = p.pat.dilation, skv1 = p.Skv / dil;
     const bool wide = std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) > 512;
-    if (wide) return p.D == 32 ? launch_f<32, true, 0>(p) : launch_f<64, true, 0>(p);
+    if (wide) return launch_head<true, 0>(p);
     // Keys a warp's 16 rows can see.  Up to 144 the warp walks its own range in one pass (6, 10 or 18 tiles: 32
     // causal taps, 64 causal taps, the reference's default window of 64 either side), up to 160 in two passes of 10;
     // wider windows keep the double-buffered chunks.  MAT_F32_KERNEL=chunks forces those (a measurement aid),
@@ -862,11 +876,12 @@ int launch_mma_window_f32(const Problem &p) {
     int nt = span <= 48 ? 6 : span <= 80 ? 10 : span <= 144 ? 18 : span <= 160 ? 10 : 0;
     if (force && std::strcmp(force, "chunks") == 0) nt = 0;
     if (const char *t = std::getenv("MAT_F32_TILES"); t && nt) nt = std::atoi(t);
+    if (nt == 18 && p.D == 96) nt = span <= 160 ? 10 : 0;   // (18 tiles of a 96-wide head do not fit the registers: two passes of 10)
     switch (nt) {
-    case 6: return p.D == 32 ? launch_f<32, false, 6>(p) : launch_f<64, false, 6>(p);
-    case 10: return p.D == 32 ? launch_f<32, false, 10>(p) : launch_f<64, false, 10>(p);
-    case 18: return p.D == 32 ? launch_f<32, false, 18>(p) : launch_f<64, false, 18>(p);
-    default: return p.D == 32 ? launch_f<32, false, 0>(p) : launch_f<64, false, 0>(p);
+    case 6: return launch_head<false, 6>(p);
+    case 10: return launch_head<false, 10>(p);
+    case 18: return launch_head<false, 18>(p);
+    default: return launch_head<false, 0>(p);
     }
 }
 
