@@ -327,7 +327,7 @@ bwd_f32_kernel(const BwdFArgs a) {
 // hold one pass's two score tiles and one slice's fragments whatever D is.  When the walk is a single pass (windows
 // of at most 64 taps) the rows pass keeps S and dP from its first sweep instead of recomputing them.
 template <int PASS, int NT>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, NT <= 10 ? 3 : 2)
 bwd_f32_wide_kernel(const BwdFArgs a) {
     constexpr int LD = 64 + 4, KS = 8;
     constexpr int kStage = 48 + 8 * NT;
@@ -385,6 +385,14 @@ bwd_f32_wide_kernel(const BwdFArgs a) {
             xf[ks][3] = row_b < a.S ? __float_as_uint(pb[c + 4]) : 0u;
         }
     };
+    // one 8-column step of those fragments
+    auto load_x8 = [&](uint32_t (&xf)[4], const float *x, int slice, int ks) {
+        const float *pa = x + (int64_t)row_a * tok + slice * 64 + ks * 8 + t, *pb = x + (int64_t)row_b * tok + slice * 64 + ks * 8 + t;
+        xf[0] = row_a < a.S ? __float_as_uint(pa[0]) : 0u;
+        xf[1] = row_b < a.S ? __float_as_uint(pb[0]) : 0u;
+        xf[2] = row_a < a.S ? __float_as_uint(pa[4]) : 0u;
+        xf[3] = row_b < a.S ? __float_as_uint(pb[4]) : 0u;
+    };
     // pass c: s[nt] (and dp[nt]) = the warp's rows against its NT tiles of columns, summed over the slices
     auto scores = [&](int c, float (&s)[NT][4], float (&dp)[NT][4], int st_off) {
 #pragma unroll
@@ -393,9 +401,18 @@ bwd_f32_wide_kernel(const BwdFArgs a) {
             for (int e = 0; e < 4; ++e) s[nt][e] = dp[nt][e] = 0.f;
         const int first = col_lo + c * 8 * NT;
         for (int slice = 0; slice < n_slices; ++slice) {
-            uint32_t xf1[KS][4], xf2[kTwo ? KS : 1][4];
-            load_x(xf1, x1, slice);
-            if constexpr (kTwo) load_x(xf2, x2, slice);
+            // the rows' fragments: the whole slice in registers, or (the rows pass with its two score tiles: no room)
+            // one 8-column step at a time, the next step's loads in flight under the current step's products
+            constexpr bool kStream = PASS == kRows;
+            uint32_t xf1[kStream ? 1 : KS][4], xf2[kTwo && !kStream ? KS : 1][4];
+            uint32_t xa[4], xb[4];
+            if constexpr (kStream) {
+                load_x8(xa, x1, slice, 0);
+                load_x8(xb, x2, slice, 0);
+            } else {
+                load_x(xf1, x1, slice);
+                if constexpr (kTwo) load_x(xf2, x2, slice);
+            }
             __syncthreads();   // whoever still read the buffers is done
             stage(sY1, y1, first, slice);
             if constexpr (kTwo) stage(sY2, y2, first, slice);
@@ -413,16 +430,29 @@ bwd_f32_wide_kernel(const BwdFArgs a) {
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
                 uint32_t h1[4], l1[4], h2[4], l2[4];
+                uint32_t na[4], nb[4];
+                if constexpr (kStream) {
+                    if (ks + 1 < KS) {
+                        load_x8(na, x1, slice, ks + 1);
+                        load_x8(nb, x2, slice, ks + 1);
+                    }
+                }
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    split_tf32(xf1[ks][e], h1[e], l1[e]);
-                    if constexpr (kTwo) split_tf32(xf2[ks][e], h2[e], l2[e]);
+                    split_tf32(kStream ? xa[e] : xf1[ks][e], h1[e], l1[e]);
+                    if constexpr (kTwo) split_tf32(kStream ? xb[e] : xf2[ks][e], h2[e], l2[e]);
                 }
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     const int off = (nt * 8 + g) * LD + ks * 8 + t;   // B: (k = dim, n = column)
                     mma_3x(s[nt], h1, l1, cy1[off], cy1[off + 4]);
                     if constexpr (kTwo) mma_3x(dp[nt], h2, l2, cy2[off], cy2[off + 4]);
+                }
+                if constexpr (kStream) {
+                    if (ks + 1 < KS) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) { xa[e] = na[e]; xb[e] = nb[e]; }
+                    }
                 }
             }
         }
