@@ -62,7 +62,7 @@ int run_problem(const Problem &p);
 
 // kernel families; each returns MAT_OK or a MAT_ERR_* after recording the text
 int launch_rowwarp(const Problem &p);        // rowwarp.cu: any pattern, any D <= 512
-bool mma_window_f32_supports(const Problem &p);   // mma_window_f32.cu: fp32 windows as three TF32 products, D = 32 or 64 (narrow windows: 128 to 512 too)
+bool mma_window_f32_supports(const Problem &p);   // mma_window_f32.cu: fp32 windows as three TF32 products, D = 16, 32, 48, 64, 96, 128, 192, ... 512
 int launch_mma_window_f32(const Problem &p);
 bool tiled_f32_supports(const Problem &p);   // tiled_f32.cu: fp32 windows of at most 128 taps, D = 32, 64 or 128
 int launch_tiled_f32(const Problem &p);
