@@ -314,7 +314,7 @@ bwd_d_wide_kernel(const BwdDArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int m4 = lane >> 3, r8 = lane & 7;
     const int hh = blockIdx.x, b = blockIdx.z, r0 = blockIdx.y * kT;
-    const int D = a.D, n_slices = D >> 6;
+    const int D = a.D, n_slices = (D + 63) >> 6;   // (the last slice may be partly beyond D: zeros in, nothing out)
     const int back = COLS ? a.right : a.left, fwd = COLS ? a.left : a.right;   // row r sees columns r - back .. r + fwd
     const int col_lo = max(0, r0 - back);
     const int col_hi = min(a.S - 1, min(r0 + kT, a.S) - 1 + fwd);
@@ -343,7 +343,7 @@ bwd_d_wide_kernel(const BwdDArgs a) {
         for (int x = threadIdx.x; x < kStage * 8; x += kThreads) {
             const int r = x >> 3, pc = x & 7;
             const int j = first + r;
-            const bool in = j < a.S;
+            const bool in = j < a.S && slice * 64 + pc * 8 < D;
             cp_async16(dst + r * LD + pc * 8, src + (int64_t)(in ? j : 0) * tok + slice * 64 + pc * 8, in ? 16 : 0);
         }
     };
@@ -352,11 +352,12 @@ bwd_d_wide_kernel(const BwdDArgs a) {
         const T *pa = x + (int64_t)row_a * tok + slice * 64, *pb = x + (int64_t)row_b * tok + slice * 64;
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
-            const int c = ks * 16 + 2 * t;
-            xf[ks][0] = row_a < a.S ? *reinterpret_cast<const uint32_t *>(pa + c) : 0u;
-            xf[ks][1] = row_b < a.S ? *reinterpret_cast<const uint32_t *>(pb + c) : 0u;
-            xf[ks][2] = row_a < a.S ? *reinterpret_cast<const uint32_t *>(pa + c + 8) : 0u;
-            xf[ks][3] = row_b < a.S ? *reinterpret_cast<const uint32_t *>(pb + c + 8) : 0u;
+            const int c = ks * 16 + 2 * t;   // (D is a multiple of 16: a 16-column step is inside D or beyond it)
+            const bool ca = row_a < a.S && slice * 64 + c < D, cb = row_b < a.S && slice * 64 + c < D;
+            xf[ks][0] = ca ? *reinterpret_cast<const uint32_t *>(pa + c) : 0u;
+            xf[ks][1] = cb ? *reinterpret_cast<const uint32_t *>(pb + c) : 0u;
+            xf[ks][2] = ca ? *reinterpret_cast<const uint32_t *>(pa + c + 8) : 0u;
+            xf[ks][3] = cb ? *reinterpret_cast<const uint32_t *>(pb + c + 8) : 0u;
         }
     };
     // pass c: s (and dp) = the warp's rows against its NS steps of 16 columns, summed over the slices
@@ -431,6 +432,7 @@ bwd_d_wide_kernel(const BwdDArgs a) {
                 T *dst = out + (int64_t)rows[i] * tok + slice * 64 + 2 * t;
 #pragma unroll
                 for (int n = 0; n < 2 * KS; ++n) {
+                    if (slice * 64 + n * 8 >= D) continue;
                     float vx = acc[n][2 * i], vy = acc[n][2 * i + 1];
                     if (c > 0) {   // the first pass of these rows wrote here
                         const uint32_t old = *reinterpret_cast<const uint32_t *>(dst + n * 8);
@@ -608,7 +610,7 @@ bool bwd_d_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, i
     if (D % 16 || D < 16 || D == 64 || dil < 1 || S % dil != 0) return false;
     if (D > 128) {
         const int64_t Sv1 = S / dil;
-        if (D > 512 || D % 64 || std::min(left, Sv1) + std::min(right, Sv1) + 16 > 160) return false;
+        if (D > 512 || std::min(left, Sv1) + std::min(right, Sv1) + 16 > 160) return false;
     }
     const char *env = std::getenv("MAT_BWD_KERNEL");
     if (env && std::strcmp(env, "warp") == 0) return false;

@@ -340,7 +340,7 @@ bwd_f32_wide_kernel(const BwdFArgs a) {
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int hh = blockIdx.x, b = blockIdx.z, r0 = blockIdx.y * kT;
-    const int D = a.D, n_slices = D >> 6;
+    const int D = a.D, n_slices = (D + 63) >> 6;   // (the last slice may be partly beyond D: zeros in, nothing out)
     const int back = COLS ? a.right : a.left, fwd = COLS ? a.left : a.right;   // row r sees columns r - back .. r + fwd
     const int col_lo = max(0, r0 - back);
     const int col_hi = min(a.S - 1, min(r0 + kT, a.S) - 1 + fwd);
@@ -369,7 +369,7 @@ bwd_f32_wide_kernel(const BwdFArgs a) {
         for (int x = threadIdx.x; x < kStage * 16; x += kThreads) {
             const int r = x >> 4, pc = x & 15;
             const int j = first + r;
-            const bool in = j < a.S;
+            const bool in = j < a.S && slice * 64 + pc * 4 < D;
             cp_async16(dst + r * LD + pc * 4, src + (int64_t)(in ? j : 0) * tok + slice * 64 + pc * 4, in ? 16 : 0);
         }
     };
@@ -379,19 +379,21 @@ bwd_f32_wide_kernel(const BwdFArgs a) {
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             const int c = ks * 8 + t;
-            xf[ks][0] = row_a < a.S ? __float_as_uint(pa[c]) : 0u;
-            xf[ks][1] = row_b < a.S ? __float_as_uint(pb[c]) : 0u;
-            xf[ks][2] = row_a < a.S ? __float_as_uint(pa[c + 4]) : 0u;
-            xf[ks][3] = row_b < a.S ? __float_as_uint(pb[c + 4]) : 0u;
+            const bool ca = row_a < a.S && slice * 64 + c < D, cb = row_b < a.S && slice * 64 + c < D;
+            xf[ks][0] = ca ? __float_as_uint(pa[c]) : 0u;
+            xf[ks][1] = cb ? __float_as_uint(pb[c]) : 0u;
+            xf[ks][2] = ca ? __float_as_uint(pa[c + 4]) : 0u;
+            xf[ks][3] = cb ? __float_as_uint(pb[c + 4]) : 0u;
         }
     };
     // one 8-column step of those fragments
     auto load_x8 = [&](uint32_t (&xf)[4], const float *x, int slice, int ks) {
         const float *pa = x + (int64_t)row_a * tok + slice * 64 + ks * 8 + t, *pb = x + (int64_t)row_b * tok + slice * 64 + ks * 8 + t;
-        xf[0] = row_a < a.S ? __float_as_uint(pa[0]) : 0u;
-        xf[1] = row_b < a.S ? __float_as_uint(pb[0]) : 0u;
-        xf[2] = row_a < a.S ? __float_as_uint(pa[4]) : 0u;
-        xf[3] = row_b < a.S ? __float_as_uint(pb[4]) : 0u;
+        const bool ca = row_a < a.S && slice * 64 + ks * 8 < D, cb = row_b < a.S && slice * 64 + ks * 8 < D;
+        xf[0] = ca ? __float_as_uint(pa[0]) : 0u;
+        xf[1] = cb ? __float_as_uint(pb[0]) : 0u;
+        xf[2] = ca ? __float_as_uint(pa[4]) : 0u;
+        xf[3] = cb ? __float_as_uint(pb[4]) : 0u;
     };
     // pass c: s[nt] (and dp[nt]) = the warp's rows against its NT tiles of columns, summed over the slices
     auto scores = [&](int c, float (&s)[NT][4], float (&dp)[NT][4], int st_off) {
@@ -488,6 +490,7 @@ bwd_f32_wide_kernel(const BwdFArgs a) {
                 float *dst = out + (int64_t)rows[i] * tok + slice * 64 + 2 * t;
 #pragma unroll
                 for (int d = 0; d < KS; ++d) {
+                    if (slice * 64 + d * 8 >= D) continue;
                     float2 val = make_float2(part[d][2 * i], part[d][2 * i + 1]);
                     if (c > 0) {   // an earlier pass of these rows wrote here
                         const float2 old = *reinterpret_cast<const float2 *>(dst + d * 8);
@@ -627,7 +630,7 @@ int launch_f(const BwdFArgs &a, int64_t B, cudaStream_t stream) {
 // 16-byte aligned tensors.
 // MAT_BWD_KERNEL=warp keeps the warp-level kernels.
 bool bwd_f32_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil) {
-    const bool wide_head = D > 64 && D <= 512 && D % 64 == 0;
+    const bool wide_head = D > 64 && D <= 512 && D % 16 == 0;   // 64 columns at a time
     const bool narrow_head = D == 16 || D == 32 || D == 48 || D == 64;
     if (dtype != MAT_F32 || (!narrow_head && !wide_head) || dil < 1 || S % dil != 0) return false;
     const char *env = std::getenv("MAT_BWD_KERNEL");

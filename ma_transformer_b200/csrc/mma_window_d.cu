@@ -371,7 +371,7 @@ window_d_wide_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int m4 = lane >> 3, r8 = lane & 7;
     const int hh = blockIdx.x, b = blockIdx.z, q0 = blockIdx.y * kTQ;
-    const int D = P.D, n_slices = D >> 6;
+    const int D = P.D, n_slices = (D + 63) >> 6;   // (the last slice may be partly beyond D: zeros in, nothing out)
     const int p_first = q0 + P.off1;
     const int key_lo = max(0, p_first - P.left);
     const int key_hi = min(P.Skv1 - 1, min(q0 + kTQ, P.Sq1) - 1 + P.off1 + P.right);
@@ -394,12 +394,13 @@ window_d_wide_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
     }
     // copy i of the pass: K slice i, then V slice i - n_slices, into buffer i & 1
     auto issue = [&](int i) {
-        const T *src_base = (i < n_slices ? kb_ptr : vb_ptr) + (i < n_slices ? i : i - n_slices) * 64;
+        const int col0 = (i < n_slices ? i : i - n_slices) * 64;
+        const T *src_base = (i < n_slices ? kb_ptr : vb_ptr) + col0;
         T *dst = sBuf + (i & 1) * kStage * LD;
         for (int x = threadIdx.x; x < kStage * 8; x += kThreads) {
             const int r = x >> 3, pc = x & 7;
             const int j = key_lo + r;
-            const bool in = j <= key_hi;   // rows past the tile's last key are zero-filled
+            const bool in = j <= key_hi && col0 + pc * 8 < D;   // rows past the tile's last key and columns past D are zero-filled
             cp_async16(dst + r * LD + pc * 8, src_base + (int64_t)(in ? j : 0) * tok + pc * 8, in ? 16 : 0);
         }
         cp_async_commit();
@@ -414,11 +415,12 @@ window_d_wide_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
         uint32_t qf[KS][4];
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
-            const int c = sl * 64 + ks * 16 + 2 * t;
-            qf[ks][0] = row_a < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qa + c) : 0u;
-            qf[ks][1] = row_b < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qb + c) : 0u;
-            qf[ks][2] = row_a < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qa + c + 8) : 0u;
-            qf[ks][3] = row_b < P.Sq1 ? *reinterpret_cast<const uint32_t *>(qb + c + 8) : 0u;
+            const int c = sl * 64 + ks * 16 + 2 * t;   // (D is a multiple of 16: a 16-column step is inside D or beyond it)
+            const bool ca = row_a < P.Sq1 && c < D, cb = row_b < P.Sq1 && c < D;
+            qf[ks][0] = ca ? *reinterpret_cast<const uint32_t *>(qa + c) : 0u;
+            qf[ks][1] = cb ? *reinterpret_cast<const uint32_t *>(qb + c) : 0u;
+            qf[ks][2] = ca ? *reinterpret_cast<const uint32_t *>(qa + c + 8) : 0u;
+            qf[ks][3] = cb ? *reinterpret_cast<const uint32_t *>(qb + c + 8) : 0u;
         }
         issue(sl + 1);   // the next K slice, or the first V slice
         cp_async_wait<1>();
@@ -500,6 +502,7 @@ window_d_wide_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
         }
 #pragma unroll
         for (int n = 0; n < 2 * KS; ++n) {
+            if (sl * 64 + n * 8 >= D) continue;
             if (row_a < P.Sq1)
                 *reinterpret_cast<uint32_t *>(oa + sl * 64 + n * 8) = ptx::Mma<T>::pack(acc[n][0] * inv[0], acc[n][1] * inv[0]);
             if (row_b < P.Sq1)
@@ -569,7 +572,7 @@ bool mma_window_d_supports(const Problem &p) {
     if (p.dtype != MAT_BF16 && p.dtype != MAT_F16) return false;
     if (p.D % 16 || p.D < 16 || p.D == 64) return false;   // (64: the TMA / tcgen05 kernels)
     if (p.D > 128) {   // wide heads: multiples of 64 up to 512, windows one pass of a warp covers (at most 128 taps between the sides)
-        if (p.D > 512 || p.D % 64 || p.pat.dilation < 1) return false;
+        if (p.D > 512 || p.pat.dilation < 1) return false;
         const int64_t skv1 = p.Skv / p.pat.dilation;
         if (std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16 > 144) return false;
     }

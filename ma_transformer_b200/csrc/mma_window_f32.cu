@@ -418,7 +418,7 @@ window_f32_wide_kernel(const float *__restrict__ q, const float *__restrict__ k,
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int hh = blockIdx.x, b = blockIdx.z, q0 = blockIdx.y * kTQ;
-    const int D = P.D, n_slices = D >> 6;
+    const int D = P.D, n_slices = (D + 63) >> 6;   // (the last slice may be partly beyond D: zeros in, nothing out)
     const int p_first = q0 + P.off1;
     const int key_lo = max(0, p_first - P.left);
     const int key_hi = min(P.Skv1 - 1, min(q0 + kTQ, P.Sq1) - 1 + P.off1 + P.right);
@@ -441,12 +441,13 @@ window_f32_wide_kernel(const float *__restrict__ q, const float *__restrict__ k,
     }
     // copy i of the pass: K slice i, then V slice i - n_slices, into buffer i & 1
     auto issue = [&](int i) {
-        const float *src_base = (i < n_slices ? kb_ptr : vb_ptr) + (i < n_slices ? i : i - n_slices) * 64;
+        const int col0 = (i < n_slices ? i : i - n_slices) * 64;
+        const float *src_base = (i < n_slices ? kb_ptr : vb_ptr) + col0;
         float *dst = sBuf + (i & 1) * kStage * LD;
         for (int x = threadIdx.x; x < kStage * 16; x += kThreads) {
             const int r = x >> 4, pc = x & 15;
             const int j = key_lo + r;
-            const bool in = j <= key_hi;   // rows past the tile's last key are zero-filled
+            const bool in = j <= key_hi && col0 + pc * 4 < D;   // rows past the tile's last key and columns past D are zero-filled
             cp_async16(dst + r * LD + pc * 4, src_base + (int64_t)(in ? j : 0) * tok + pc * 4, in ? 16 : 0);
         }
         cp_async_commit();
@@ -461,11 +462,12 @@ window_f32_wide_kernel(const float *__restrict__ q, const float *__restrict__ k,
         uint32_t qf[KS][4];
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
-            const int c = sl * 64 + ks * 8 + t;
-            qf[ks][0] = row_a < P.Sq1 ? __float_as_uint(qa[c]) : 0u;
-            qf[ks][1] = row_b < P.Sq1 ? __float_as_uint(qb[c]) : 0u;
-            qf[ks][2] = row_a < P.Sq1 ? __float_as_uint(qa[c + 4]) : 0u;
-            qf[ks][3] = row_b < P.Sq1 ? __float_as_uint(qb[c + 4]) : 0u;
+            const int c = sl * 64 + ks * 8 + t;   // (D is a multiple of 16: an 8-column step is inside D or beyond it)
+            const bool ca = row_a < P.Sq1 && c < D, cb = row_b < P.Sq1 && c < D;
+            qf[ks][0] = ca ? __float_as_uint(qa[c]) : 0u;
+            qf[ks][1] = cb ? __float_as_uint(qb[c]) : 0u;
+            qf[ks][2] = ca ? __float_as_uint(qa[c + 4]) : 0u;
+            qf[ks][3] = cb ? __float_as_uint(qb[c + 4]) : 0u;
         }
         issue(sl + 1);   // the next K slice, or the first V slice
         cp_async_wait<1>();
@@ -564,6 +566,7 @@ window_f32_wide_kernel(const float *__restrict__ q, const float *__restrict__ k,
         }
 #pragma unroll
         for (int d = 0; d < KS; ++d) {
+            if (sl * 64 + d * 8 >= D) continue;
             if (row_a < P.Sq1)
                 *reinterpret_cast<float2 *>(oa + sl * 64 + d * 8) =
                     make_float2((part[0][d][0] + part[1][d][0]) * inv[0], (part[0][d][1] + part[1][d][1]) * inv[0]);
@@ -592,7 +595,7 @@ window_f32_wide_passes_kernel(const float *__restrict__ q, const float *__restri
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int hh = blockIdx.x, b = blockIdx.z, q0 = blockIdx.y * kTQ;
-    const int D = P.D, n_slices = D >> 6;
+    const int D = P.D, n_slices = (D + 63) >> 6;   // (the last slice may be partly beyond D: zeros in, nothing out)
     const int p_first = q0 + P.off1;
     const int key_lo = max(0, p_first - P.left);
     const int key_hi = min(P.Skv1 - 1, min(q0 + kTQ, P.Sq1) - 1 + P.off1 + P.right);
@@ -631,7 +634,7 @@ window_f32_wide_passes_kernel(const float *__restrict__ q, const float *__restri
         for (int x = threadIdx.x; x < kStage * 16; x += kThreads) {
             const int r = x >> 4, pc = x & 15;
             const int j = first + r;
-            const bool in = j <= key_hi;
+            const bool in = j <= key_hi && slice * 64 + pc * 4 < D;
             cp_async16(sBuf + r * LD + pc * 4, src + (int64_t)(in ? j : 0) * tok + slice * 64 + pc * 4, in ? 16 : 0);
         }
         cp_async_commit();
@@ -647,10 +650,11 @@ window_f32_wide_passes_kernel(const float *__restrict__ q, const float *__restri
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
                 const int col = sl * 64 + ks * 8 + t;
-                qf[ks][0] = row_a < P.Sq1 ? __float_as_uint(qa[col]) : 0u;
-                qf[ks][1] = row_b < P.Sq1 ? __float_as_uint(qb[col]) : 0u;
-                qf[ks][2] = row_a < P.Sq1 ? __float_as_uint(qa[col + 4]) : 0u;
-                qf[ks][3] = row_b < P.Sq1 ? __float_as_uint(qb[col + 4]) : 0u;
+                const bool ca = row_a < P.Sq1 && col < D, cb = row_b < P.Sq1 && col < D;
+                qf[ks][0] = ca ? __float_as_uint(qa[col]) : 0u;
+                qf[ks][1] = cb ? __float_as_uint(qb[col]) : 0u;
+                qf[ks][2] = ca ? __float_as_uint(qa[col + 4]) : 0u;
+                qf[ks][3] = cb ? __float_as_uint(qb[col + 4]) : 0u;
             }
             stage(kb_ptr, c, sl);
             const uint32_t *ck = reinterpret_cast<const uint32_t *>(sBuf + st_off);
@@ -746,6 +750,7 @@ window_f32_wide_passes_kernel(const float *__restrict__ q, const float *__restri
             }
 #pragma unroll
             for (int d = 0; d < KS; ++d) {
+                if (sl * 64 + d * 8 >= D) continue;
                 if (row_a < P.Sq1) {
                     float2 val = make_float2(part[d][0], part[d][1]);
                     float2 *dst = reinterpret_cast<float2 *>(oa + sl * 64 + d * 8);
@@ -833,14 +838,14 @@ static int64_t warp_span(const Problem &p) {
     return std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16;
 }
 
-// fp32 window patterns (any taps, any dilation that divides the lengths) with head width 16, 32, 48, 64, 96, 128, 192,
-// ... 512;
+// fp32 window patterns (any taps, any dilation that divides the lengths) with a head width that is a multiple of 16
+// up to 512;
 // whole tensors, 16-byte aligned.
 // MAT_F32_KERNEL=tiled keeps them on the FMA-pipe kernels (a measurement aid).
 bool mma_window_f32_supports(const Problem &p) {
     if (p.pat.kind != MAT_WINDOW || p.dtype != MAT_F32) return false;
-    const bool wide_head = p.D > 64 && p.D <= 512 && p.D % 64 == 0;
     const bool narrow_head = p.D == 16 || p.D == 32 || p.D == 48 || p.D == 64 || p.D == 96;   // (96: 768 columns in 8 heads)
+    const bool wide_head = !narrow_head && p.D > 64 && p.D <= 512 && p.D % 16 == 0;   // 64 columns at a time
     if (!narrow_head && !wide_head) return false;
     if (wide_head && p.pat.dilation < 1) return false;
     if (p.k_prev || p.k_next || p.q_ts || p.k_ts || p.v_ts || p.o_ts) return false;
@@ -855,7 +860,7 @@ bool mma_window_f32_supports(const Problem &p) {
 }
 
 int launch_mma_window_f32(const Problem &p) {
-    if (p.D > 64 && p.D % 64 == 0) {   // one pass of 10 or 18 tiles per warp; wider windows, up to dense: passes of 10
+    if (p.D > 64 && p.D != 96) {   // one pass of 10 or 18 tiles per warp; wider windows, up to dense: passes of 10
         if (warp_span(p) > 144) return launch_wide<10, true, true>(p);
         // 18 tiles on a head of 512 columns stayed at 1.2e-5 with cut halves and one chain per score: two passes of 10
         if (warp_span(p) > 80 && p.D > 256) return launch_wide<10, true, true>(p);
