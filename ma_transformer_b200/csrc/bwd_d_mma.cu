@@ -352,12 +352,11 @@ bwd_d_wide_kernel(const BwdDArgs a) {
         const T *pa = x + (int64_t)row_a * tok + slice * 64, *pb = x + (int64_t)row_b * tok + slice * 64;
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
-            const int c = ks * 16 + 2 * t;   // (D is a multiple of 16: a 16-column step is inside D or beyond it)
-            const bool ca = row_a < a.S && slice * 64 + c < D, cb = row_b < a.S && slice * 64 + c < D;
-            xf[ks][0] = ca ? *reinterpret_cast<const uint32_t *>(pa + c) : 0u;
-            xf[ks][1] = cb ? *reinterpret_cast<const uint32_t *>(pb + c) : 0u;
-            xf[ks][2] = ca ? *reinterpret_cast<const uint32_t *>(pa + c + 8) : 0u;
-            xf[ks][3] = cb ? *reinterpret_cast<const uint32_t *>(pb + c + 8) : 0u;
+            const int c = ks * 16 + 2 * t, col = slice * 64 + c;   // (D is a multiple of 8: each half of a 16-column step is inside D or beyond it)
+            xf[ks][0] = row_a < a.S && col < D ? *reinterpret_cast<const uint32_t *>(pa + c) : 0u;
+            xf[ks][1] = row_b < a.S && col < D ? *reinterpret_cast<const uint32_t *>(pb + c) : 0u;
+            xf[ks][2] = row_a < a.S && col + 8 < D ? *reinterpret_cast<const uint32_t *>(pa + c + 8) : 0u;
+            xf[ks][3] = row_b < a.S && col + 8 < D ? *reinterpret_cast<const uint32_t *>(pb + c + 8) : 0u;
         }
     };
     // pass c: s (and dp) = the warp's rows against its NS steps of 16 columns, summed over the slices
@@ -432,7 +431,7 @@ bwd_d_wide_kernel(const BwdDArgs a) {
                 T *dst = out + (int64_t)rows[i] * tok + slice * 64 + 2 * t;
 #pragma unroll
                 for (int n = 0; n < 2 * KS; ++n) {
-                    if (slice * 64 + n * 8 >= D) continue;
+                    if (slice * 64 + n * 8 + 2 * t >= D) continue;
                     float vx = acc[n][2 * i], vy = acc[n][2 * i + 1];
                     if (c > 0) {   // the first pass of these rows wrote here
                         const uint32_t old = *reinterpret_cast<const uint32_t *>(dst + n * 8);
@@ -607,8 +606,8 @@ int launch_any_d(const BwdDArgs &a, int64_t B, int64_t D, cudaStream_t stream) {
 // keeps the one-warp-per-row kernels.
 bool bwd_d_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil, int64_t left, int64_t right) {
     if (dtype != MAT_BF16 && dtype != MAT_F16) return false;
-    if (D % 16 || D < 16 || D == 64 || dil < 1 || S % dil != 0) return false;
-    if (D > 128) {
+    if (D % 8 || D < 8 || D == 64 || dil < 1 || S % dil != 0) return false;   // (rows stay 16-byte aligned)
+    if (D > 128 || D % 16) {
         const int64_t Sv1 = S / dil;
         if (D > 512 || std::min(left, Sv1) + std::min(right, Sv1) + 16 > 160) return false;
     }
@@ -638,7 +637,7 @@ int launch_bwd_d_mma(const void *q, const void *k, const void *v, const void *do
     const char *walk = std::getenv("MAT_BWD_D_WALK");
     const bool sliced128 = D == 128 && (walk ? std::strcmp(walk, "sliced") == 0 && a.left + a.right + 16 <= 144
                                              : a.left + a.right + 16 > 80 && a.left + a.right + 16 <= 144);
-    if (D > 128 || sliced128)
+    if (D > 128 || D % 16 || sliced128)
     {
         // (a walk of 81 to 144 columns - the reference's default window of 64 either side - in one pass of 9 steps)
         if (a.left + a.right + 16 > 80 && a.left + a.right + 16 <= 144)

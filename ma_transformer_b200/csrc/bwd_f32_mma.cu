@@ -379,21 +379,21 @@ bwd_f32_wide_kernel(const BwdFArgs a) {
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             const int c = ks * 8 + t;
-            const bool ca = row_a < a.S && slice * 64 + c < D, cb = row_b < a.S && slice * 64 + c < D;
-            xf[ks][0] = ca ? __float_as_uint(pa[c]) : 0u;
-            xf[ks][1] = cb ? __float_as_uint(pb[c]) : 0u;
-            xf[ks][2] = ca ? __float_as_uint(pa[c + 4]) : 0u;
-            xf[ks][3] = cb ? __float_as_uint(pb[c + 4]) : 0u;
+            const int col = slice * 64 + c;   // (D is a multiple of 4: each half of an 8-column step is inside D or beyond it)
+            xf[ks][0] = row_a < a.S && col < D ? __float_as_uint(pa[c]) : 0u;
+            xf[ks][1] = row_b < a.S && col < D ? __float_as_uint(pb[c]) : 0u;
+            xf[ks][2] = row_a < a.S && col + 4 < D ? __float_as_uint(pa[c + 4]) : 0u;
+            xf[ks][3] = row_b < a.S && col + 4 < D ? __float_as_uint(pb[c + 4]) : 0u;
         }
     };
     // one 8-column step of those fragments
     auto load_x8 = [&](uint32_t (&xf)[4], const float *x, int slice, int ks) {
         const float *pa = x + (int64_t)row_a * tok + slice * 64 + ks * 8 + t, *pb = x + (int64_t)row_b * tok + slice * 64 + ks * 8 + t;
-        const bool ca = row_a < a.S && slice * 64 + ks * 8 < D, cb = row_b < a.S && slice * 64 + ks * 8 < D;
-        xf[0] = ca ? __float_as_uint(pa[0]) : 0u;
-        xf[1] = cb ? __float_as_uint(pb[0]) : 0u;
-        xf[2] = ca ? __float_as_uint(pa[4]) : 0u;
-        xf[3] = cb ? __float_as_uint(pb[4]) : 0u;
+        const int col = slice * 64 + ks * 8 + t;
+        xf[0] = row_a < a.S && col < D ? __float_as_uint(pa[0]) : 0u;
+        xf[1] = row_b < a.S && col < D ? __float_as_uint(pb[0]) : 0u;
+        xf[2] = row_a < a.S && col + 4 < D ? __float_as_uint(pa[4]) : 0u;
+        xf[3] = row_b < a.S && col + 4 < D ? __float_as_uint(pb[4]) : 0u;
     };
     // pass c: s[nt] (and dp[nt]) = the warp's rows against its NT tiles of columns, summed over the slices
     auto scores = [&](int c, float (&s)[NT][4], float (&dp)[NT][4], int st_off) {
@@ -490,7 +490,7 @@ bwd_f32_wide_kernel(const BwdFArgs a) {
                 float *dst = out + (int64_t)rows[i] * tok + slice * 64 + 2 * t;
 #pragma unroll
                 for (int d = 0; d < KS; ++d) {
-                    if (slice * 64 + d * 8 >= D) continue;
+                    if (slice * 64 + d * 8 + 2 * t >= D) continue;
                     float2 val = make_float2(part[d][2 * i], part[d][2 * i + 1]);
                     if (c > 0) {   // an earlier pass of these rows wrote here
                         const float2 old = *reinterpret_cast<const float2 *>(dst + d * 8);
@@ -626,11 +626,11 @@ int launch_f(const BwdFArgs &a, int64_t B, cudaStream_t stream) {
 
 }  // namespace
 
-// fp32 window patterns with head width 16, 32, 48, 64 or a multiple of 64 up to 512, lengths a multiple of the dilation,
+// fp32 window patterns with a head width that is a multiple of 4 up to 512, lengths a multiple of the dilation,
 // 16-byte aligned tensors.
 // MAT_BWD_KERNEL=warp keeps the warp-level kernels.
 bool bwd_f32_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil) {
-    const bool wide_head = D > 64 && D <= 512 && D % 16 == 0;   // 64 columns at a time
+    const bool wide_head = D >= 4 && D <= 512 && D % 4 == 0;   // 64 columns at a time (rows stay 16-byte aligned)
     const bool narrow_head = D == 16 || D == 32 || D == 48 || D == 64;
     if (dtype != MAT_F32 || (!narrow_head && !wide_head) || dil < 1 || S % dil != 0) return false;
     const char *env = std::getenv("MAT_BWD_KERNEL");
@@ -654,7 +654,7 @@ int launch_bwd_f32_mma(const void *q, const void *k, const void *v, const void *
     a.D = (int32_t)D;
     // (a walk of 81 to 144 columns - the reference's default window of 64 either side - in one pass of 18 tiles)
     const bool one18 = a.left + a.right + 16 > 80 && a.left + a.right + 16 <= 144;
-    if (D > 64) return one18 ? launch_wide<18>(a, B, stream) : launch_wide<10>(a, B, stream);
+    if (D != 16 && D != 32 && D != 48 && D != 64) return one18 ? launch_wide<18>(a, B, stream) : launch_wide<10>(a, B, stream);
     const char *walk = std::getenv("MAT_BWD_F32_WALK");
     // (a 64-wide head whose walk is one pass takes that kernel too: its rows pass keeps S and dP instead of
     // recomputing them; MAT_BWD_F32_WALK=recompute or chunks keeps it on the kernels below)

@@ -386,7 +386,7 @@ window_d_wide_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
     T *ob = o + (((int64_t)b * P.Sq1 + row_b) * P.HH + hh) * D + 2 * t;
 
     if (key_hi < key_lo) {   // a tile whose rows see no key (the whole CTA alike): zeros
-        for (int c = 0; c < D; c += 8) {
+        for (int c = 0; c + 2 * t < D; c += 8) {
             if (row_a < P.Sq1) *reinterpret_cast<uint32_t *>(oa + c) = 0u;
             if (row_b < P.Sq1) *reinterpret_cast<uint32_t *>(ob + c) = 0u;
         }
@@ -415,12 +415,11 @@ window_d_wide_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
         uint32_t qf[KS][4];
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
-            const int c = sl * 64 + ks * 16 + 2 * t;   // (D is a multiple of 16: a 16-column step is inside D or beyond it)
-            const bool ca = row_a < P.Sq1 && c < D, cb = row_b < P.Sq1 && c < D;
-            qf[ks][0] = ca ? *reinterpret_cast<const uint32_t *>(qa + c) : 0u;
-            qf[ks][1] = cb ? *reinterpret_cast<const uint32_t *>(qb + c) : 0u;
-            qf[ks][2] = ca ? *reinterpret_cast<const uint32_t *>(qa + c + 8) : 0u;
-            qf[ks][3] = cb ? *reinterpret_cast<const uint32_t *>(qb + c + 8) : 0u;
+            const int c = sl * 64 + ks * 16 + 2 * t;   // (D is a multiple of 8: each half of a 16-column step is inside D or beyond it)
+            qf[ks][0] = row_a < P.Sq1 && c < D ? *reinterpret_cast<const uint32_t *>(qa + c) : 0u;
+            qf[ks][1] = row_b < P.Sq1 && c < D ? *reinterpret_cast<const uint32_t *>(qb + c) : 0u;
+            qf[ks][2] = row_a < P.Sq1 && c + 8 < D ? *reinterpret_cast<const uint32_t *>(qa + c + 8) : 0u;
+            qf[ks][3] = row_b < P.Sq1 && c + 8 < D ? *reinterpret_cast<const uint32_t *>(qb + c + 8) : 0u;
         }
         issue(sl + 1);   // the next K slice, or the first V slice
         cp_async_wait<1>();
@@ -502,7 +501,7 @@ window_d_wide_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *
         }
 #pragma unroll
         for (int n = 0; n < 2 * KS; ++n) {
-            if (sl * 64 + n * 8 >= D) continue;
+            if (sl * 64 + n * 8 + 2 * t >= D) continue;
             if (row_a < P.Sq1)
                 *reinterpret_cast<uint32_t *>(oa + sl * 64 + n * 8) = ptx::Mma<T>::pack(acc[n][0] * inv[0], acc[n][1] * inv[0]);
             if (row_b < P.Sq1)
@@ -570,8 +569,8 @@ int launch_d(const Problem &p) {
 bool mma_window_d_supports(const Problem &p) {
     if (p.pat.kind != MAT_WINDOW) return false;
     if (p.dtype != MAT_BF16 && p.dtype != MAT_F16) return false;
-    if (p.D % 16 || p.D < 16 || p.D == 64) return false;   // (64: the TMA / tcgen05 kernels)
-    if (p.D > 128) {   // wide heads: multiples of 64 up to 512, windows one pass of a warp covers (at most 128 taps between the sides)
+    if (p.D % 8 || p.D < 8 || p.D == 64) return false;   // (64: the TMA / tcgen05 kernels; rows stay 16-byte aligned)
+    if (p.D > 128 || p.D % 16) {   // wide heads: multiples of 64 up to 512, windows one pass of a warp covers (at most 128 taps between the sides)
         if (p.D > 512 || p.pat.dilation < 1) return false;
         const int64_t skv1 = p.Skv / p.pat.dilation;
         if (std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16 > 144) return false;
@@ -622,7 +621,7 @@ int launch_mma_window_d(const Problem &p) {
     const bool sliced128 = p.D == 128 && !(force && (std::strcmp(force, "whole") == 0 || std::strcmp(force, "chunks") == 0)) &&
                            std::min<int64_t>(p.pat.left, p.Skv / p.pat.dilation) +
                                std::min<int64_t>(p.pat.right, p.Skv / p.pat.dilation) + 16 <= 144;
-    if (p.D > 128 || sliced128) {
+    if (p.D > 128 || p.D % 16 || sliced128) {
         const int64_t skv1 = p.Skv / p.pat.dilation;
         const bool five = std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16 <= 80;
         if (p.dtype == MAT_BF16) return five ? launch_wide<__nv_bfloat16, 5>(p) : launch_wide<__nv_bfloat16, 9>(p);

@@ -433,7 +433,7 @@ window_f32_wide_kernel(const float *__restrict__ q, const float *__restrict__ k,
     float *ob = o + (((int64_t)b * P.Sq1 + row_b) * P.HH + hh) * D + 2 * t;
 
     if (key_hi < key_lo) {   // a tile whose rows see no key (the whole CTA alike): zeros
-        for (int c = 0; c < D; c += 8) {
+        for (int c = 0; c + 2 * t < D; c += 8) {
             if (row_a < P.Sq1) *reinterpret_cast<float2 *>(oa + c) = make_float2(0.f, 0.f);
             if (row_b < P.Sq1) *reinterpret_cast<float2 *>(ob + c) = make_float2(0.f, 0.f);
         }
@@ -462,12 +462,11 @@ window_f32_wide_kernel(const float *__restrict__ q, const float *__restrict__ k,
         uint32_t qf[KS][4];
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
-            const int c = sl * 64 + ks * 8 + t;   // (D is a multiple of 16: an 8-column step is inside D or beyond it)
-            const bool ca = row_a < P.Sq1 && c < D, cb = row_b < P.Sq1 && c < D;
-            qf[ks][0] = ca ? __float_as_uint(qa[c]) : 0u;
-            qf[ks][1] = cb ? __float_as_uint(qb[c]) : 0u;
-            qf[ks][2] = ca ? __float_as_uint(qa[c + 4]) : 0u;
-            qf[ks][3] = cb ? __float_as_uint(qb[c + 4]) : 0u;
+            const int c = sl * 64 + ks * 8 + t;   // (D is a multiple of 4: each half of an 8-column step is inside D or beyond it)
+            qf[ks][0] = row_a < P.Sq1 && c < D ? __float_as_uint(qa[c]) : 0u;
+            qf[ks][1] = row_b < P.Sq1 && c < D ? __float_as_uint(qb[c]) : 0u;
+            qf[ks][2] = row_a < P.Sq1 && c + 4 < D ? __float_as_uint(qa[c + 4]) : 0u;
+            qf[ks][3] = row_b < P.Sq1 && c + 4 < D ? __float_as_uint(qb[c + 4]) : 0u;
         }
         issue(sl + 1);   // the next K slice, or the first V slice
         cp_async_wait<1>();
@@ -566,7 +565,7 @@ window_f32_wide_kernel(const float *__restrict__ q, const float *__restrict__ k,
         }
 #pragma unroll
         for (int d = 0; d < KS; ++d) {
-            if (sl * 64 + d * 8 >= D) continue;
+            if (sl * 64 + d * 8 + 2 * t >= D) continue;
             if (row_a < P.Sq1)
                 *reinterpret_cast<float2 *>(oa + sl * 64 + d * 8) =
                     make_float2((part[0][d][0] + part[1][d][0]) * inv[0], (part[0][d][1] + part[1][d][1]) * inv[0]);
@@ -621,7 +620,7 @@ window_f32_wide_passes_kernel(const float *__restrict__ q, const float *__restri
     const int pos[2] = {row_a + P.off1, row_b + P.off1};
 
     if (n_pass == 0) {   // a tile whose rows see no key (the whole CTA alike): zeros
-        for (int c = 0; c < D; c += 8) {
+        for (int c = 0; c + 2 * t < D; c += 8) {
             if (row_a < P.Sq1) *reinterpret_cast<float2 *>(oa + c) = make_float2(0.f, 0.f);
             if (row_b < P.Sq1) *reinterpret_cast<float2 *>(ob + c) = make_float2(0.f, 0.f);
         }
@@ -650,11 +649,10 @@ window_f32_wide_passes_kernel(const float *__restrict__ q, const float *__restri
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
                 const int col = sl * 64 + ks * 8 + t;
-                const bool ca = row_a < P.Sq1 && col < D, cb = row_b < P.Sq1 && col < D;
-                qf[ks][0] = ca ? __float_as_uint(qa[col]) : 0u;
-                qf[ks][1] = cb ? __float_as_uint(qb[col]) : 0u;
-                qf[ks][2] = ca ? __float_as_uint(qa[col + 4]) : 0u;
-                qf[ks][3] = cb ? __float_as_uint(qb[col + 4]) : 0u;
+                qf[ks][0] = row_a < P.Sq1 && col < D ? __float_as_uint(qa[col]) : 0u;
+                qf[ks][1] = row_b < P.Sq1 && col < D ? __float_as_uint(qb[col]) : 0u;
+                qf[ks][2] = row_a < P.Sq1 && col + 4 < D ? __float_as_uint(qa[col + 4]) : 0u;
+                qf[ks][3] = row_b < P.Sq1 && col + 4 < D ? __float_as_uint(qb[col + 4]) : 0u;
             }
             stage(kb_ptr, c, sl);
             const uint32_t *ck = reinterpret_cast<const uint32_t *>(sBuf + st_off);
@@ -750,7 +748,7 @@ window_f32_wide_passes_kernel(const float *__restrict__ q, const float *__restri
             }
 #pragma unroll
             for (int d = 0; d < KS; ++d) {
-                if (sl * 64 + d * 8 >= D) continue;
+                if (sl * 64 + d * 8 + 2 * t >= D) continue;
                 if (row_a < P.Sq1) {
                     float2 val = make_float2(part[d][0], part[d][1]);
                     float2 *dst = reinterpret_cast<float2 *>(oa + sl * 64 + d * 8);
@@ -838,14 +836,14 @@ static int64_t warp_span(const Problem &p) {
     return std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16;
 }
 
-// fp32 window patterns (any taps, any dilation that divides the lengths) with a head width that is a multiple of 16
-// up to 512;
+// fp32 window patterns (any taps, any dilation that divides the lengths) with a head width that is a multiple of 4
+// up to 512 (16, 32, 48, 64 and 96 columns have instantiations of their own, the others go 64 columns at a time);
 // whole tensors, 16-byte aligned.
 // MAT_F32_KERNEL=tiled keeps them on the FMA-pipe kernels (a measurement aid).
 bool mma_window_f32_supports(const Problem &p) {
     if (p.pat.kind != MAT_WINDOW || p.dtype != MAT_F32) return false;
     const bool narrow_head = p.D == 16 || p.D == 32 || p.D == 48 || p.D == 64 || p.D == 96;   // (96: 768 columns in 8 heads)
-    const bool wide_head = !narrow_head && p.D > 64 && p.D <= 512 && p.D % 16 == 0;   // 64 columns at a time
+    const bool wide_head = !narrow_head && p.D >= 4 && p.D <= 512 && p.D % 4 == 0;   // 64 columns at a time (rows stay 16-byte aligned)
     if (!narrow_head && !wide_head) return false;
     if (wide_head && p.pat.dilation < 1) return false;
     if (p.k_prev || p.k_next || p.q_ts || p.k_ts || p.v_ts || p.o_ts) return false;
@@ -860,7 +858,7 @@ bool mma_window_f32_supports(const Problem &p) {
 }
 
 int launch_mma_window_f32(const Problem &p) {
-    if (p.D > 64 && p.D != 96) {   // one pass of 10 or 18 tiles per warp; wider windows, up to dense: passes of 10
+    if (p.D != 16 && p.D != 32 && p.D != 48 && p.D != 64 && p.D != 96) {   // 64 columns at a time: one pass of 10 or 18 tiles per warp; wider windows, up to dense: passes of 10
         if (warp_span(p) > 144) return launch_wide<10, true, true>(p);
         // 18 tiles on a head of 512 columns stayed at 1.2e-5 with cut halves and one chain per score: two passes of 10
         if (warp_span(p) > 80 && p.D > 256) return launch_wide<10, true, true>(p);
