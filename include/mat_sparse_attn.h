@@ -115,7 +115,9 @@ int mat_sparse_attn_fwd_strided(const void *q, const void *k, const void *v, voi
                                 int64_t q_token_stride, int64_t k_token_stride,
                                 int64_t v_token_stride, int64_t o_token_stride, void *stream);
 
-/* Scratch bytes mat_sparse_attn_fwd needs for this problem (0 for most). */
+/* Scratch bytes mat_sparse_attn_fwd needs for this problem (0 for most: the Longformer pattern needs its partial
+ * results, 16-bit heads of more than 128 columns or of a width that is not a multiple of 16 need an fp32 copy of the
+ * output's shape when the window has more than 128 taps between its sides). */
 size_t mat_sparse_attn_workspace_bytes(int64_t B, int64_t S_q, int64_t S_kv, int64_t H,
                                        int64_t D, int dtype, const mat_pattern_spec *spec);
 

@@ -243,7 +243,8 @@ size_t mat_sparse_attn_workspace_bytes(int64_t B, int64_t S_q, int64_t S_kv, int
     if (make_problem(p, dummy, dummy, dummy, dummy, B, S_q, S_kv, H, D, dtype, spec,
                      0.f, nullptr, 0, nullptr))
         return 0;
-    return mma_flash_supports(p) ? mma_flash_workspace_bytes(p) : 0;
+    if (mma_flash_supports(p)) return mma_flash_workspace_bytes(p);
+    return mma_window_d_scratch_bytes(p);
 }
 
 int mat_sparse_attn_fwd_window(const void *q, const void *k, const void *v, void *o, int64_t B,

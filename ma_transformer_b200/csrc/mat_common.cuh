@@ -69,6 +69,7 @@ int launch_tiled_f32(const Problem &p);
 int tiled_status_read_and_clear(int *out);
 bool mma_window_d_supports(const Problem &p);   // mma_window_d.cu: 16-bit windows, head widths 16..128 in steps of 16 other than 64
 int launch_mma_window_d(const Problem &p);
+size_t mma_window_d_scratch_bytes(const Problem &p);   // fp32 scratch of the sliced kernel for windows of several passes
 bool mma_flash_supports(const Problem &p);   // mma_flash.cu
 int launch_mma_flash(const Problem &p);
 size_t mma_flash_workspace_bytes(const Problem &p);

@@ -534,6 +534,208 @@ int launch_wide(const Problem &p) {
     return MAT_OK;
 }
 
+// Wide or odd heads with windows that take a warp more than one pass (up to dense).  Two sweeps over the passes, the
+// head dimension 64 columns at a time in both: sweep one accumulates each pass's scores over the K slices and keeps the
+// rows' running maximum and sum; sweep two forms the scores again, turns them into normalised weights (rounded to the
+// input type, as everywhere) and multiplies them with every V slice.  The output rows are sums over the passes, and
+// 16-bit values cannot carry fifty partial sums, so they are kept in fp32 in a scratch tensor of the output's shape
+// (the caller's workspace): a row's first pass writes it, later passes add to it, the last pass adds, rounds and writes
+// the output itself (a row belongs to one thread pair of one CTA: no atomics, and nothing else reads the scratch).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+window_d_wide_passes_kernel(const T *__restrict__ q, const T *__restrict__ k, const T *__restrict__ v, T *__restrict__ o,
+                            float *__restrict__ scratch, const WinDParams P) {
+    constexpr int NS = 5, LD = 64 + 8, KS = 4;
+    constexpr int kStage = 48 + 16 * NS;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    T *sBuf = reinterpret_cast<T *>(smem_raw);   // [kStage][LD]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int m4 = lane >> 3, r8 = lane & 7;
+    const int hh = blockIdx.x, b = blockIdx.z, q0 = blockIdx.y * kTQ;
+    const int D = P.D, n_slices = (D + 63) >> 6;
+    const int p_first = q0 + P.off1;
+    const int key_lo = max(0, p_first - P.left);
+    const int key_hi = min(P.Skv1 - 1, min(q0 + kTQ, P.Sq1) - 1 + P.off1 + P.right);
+    const int base_w = max(key_lo, p_first + 16 * warp - P.left);   // the warp's first key
+    const int st_off = (base_w - key_lo) * LD;
+    int n_pass = 0;
+    if (key_hi >= key_lo) {
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) {
+            const int keys_w = min(key_hi, p_first + 16 * w + 15 + P.right) - max(key_lo, p_first + 16 * w - P.left) + 1;
+            n_pass = max(n_pass, (keys_w + 16 * NS - 1) / (16 * NS));
+        }
+        n_pass = min(n_pass, (key_hi - key_lo) / (16 * NS) + 1);
+    }
+    const int64_t tok = (int64_t)P.HH * D;
+    const T *kb_ptr = k + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+    const T *vb_ptr = v + ((int64_t)b * P.Skv1 * P.HH + hh) * D;
+    const int row_a = q0 + warp * 16 + g, row_b = row_a + 8;
+    const int64_t off_a = (((int64_t)b * P.Sq1 + row_a) * P.HH + hh) * D, off_b = (((int64_t)b * P.Sq1 + row_b) * P.HH + hh) * D;
+    const T *qa = q + off_a, *qb = q + off_b;
+    const int pos[2] = {row_a + P.off1, row_b + P.off1};
+
+    if (n_pass == 0) {   // a tile whose rows see no key (the whole CTA alike): zeros
+        for (int c = 2 * t; c < D; c += 8) {
+            if (row_a < P.Sq1) *reinterpret_cast<uint32_t *>(o + off_a + c) = 0u;
+            if (row_b < P.Sq1) *reinterpret_cast<uint32_t *>(o + off_b + c) = 0u;
+        }
+        return;
+    }
+    // one 64-column slice of the kStage rows of pass c, of K or V; rows past the tile's last key and columns past D are zeros
+    auto stage = [&](const T *src, int c, int slice) {
+        const int first = key_lo + c * 16 * NS;
+        __syncthreads();   // whoever still read the buffer is done
+        for (int x = threadIdx.x; x < kStage * 8; x += kThreads) {
+            const int r = x >> 3, pc = x & 7;
+            const int j = first + r;
+            const bool in = j <= key_hi && slice * 64 + pc * 8 < D;
+            cp_async16(sBuf + r * LD + pc * 8, src + (int64_t)(in ? j : 0) * tok + slice * 64 + pc * 8, in ? 16 : 0);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+    };
+    // the masked scores of pass c
+    auto scores = [&](int c, float (&s)[2 * NS][4]) {
+#pragma unroll
+        for (int n = 0; n < 2 * NS; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+        for (int sl = 0; sl < n_slices; ++sl) {
+            uint32_t qf[KS][4];
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                const int col = sl * 64 + ks * 16 + 2 * t;
+                qf[ks][0] = row_a < P.Sq1 && col < D ? *reinterpret_cast<const uint32_t *>(qa + col) : 0u;
+                qf[ks][1] = row_b < P.Sq1 && col < D ? *reinterpret_cast<const uint32_t *>(qb + col) : 0u;
+                qf[ks][2] = row_a < P.Sq1 && col + 8 < D ? *reinterpret_cast<const uint32_t *>(qa + col + 8) : 0u;
+                qf[ks][3] = row_b < P.Sq1 && col + 8 < D ? *reinterpret_cast<const uint32_t *>(qb + col + 8) : 0u;
+            }
+            stage(kb_ptr, c, sl);
+            const uint32_t k_addr = ptx::smem_u32(sBuf + st_off);
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+                for (int n2 = 0; n2 < NS; ++n2) {
+                    uint32_t kf[4];
+                    ptx::ldmatrix_x4(kf, k_addr + (uint32_t)(((n2 * 16 + r8 + (m4 >> 1) * 8) * LD + ks * 16 + (m4 & 1) * 8) * 2));
+                    ptx::Mma<T>::run(s[2 * n2], qf[ks], kf[0], kf[1]);
+                    ptx::Mma<T>::run(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
+                }
+        }
+        const int kb = base_w + c * 16 * NS;
+#pragma unroll
+        for (int n = 0; n < 2 * NS; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = kb + n * 8 + 2 * t + (e & 1), p = pos[e >> 1];
+                const bool ok = j >= p - P.left && j <= p + P.right && j < P.Skv1;
+                s[n][e] = ok ? s[n][e] : -INFINITY;
+            }
+    };
+    float s[2 * NS][4];
+    // ---- sweep one: the rows' maximum and sum ----
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    for (int c = 0; c < n_pass; ++c) {
+        scores(c, s);
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 2 * NS; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+        float mus[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float m_new = fmaxf(m_run[i], mx[i]);
+            l_run[i] *= m_new == -INFINITY ? 1.f : ptx::ex2((m_run[i] - m_new) * P.sl2);
+            m_run[i] = m_new;
+            mus[i] = m_new == -INFINITY ? 0.f : m_new * P.sl2;
+        }
+#pragma unroll
+        for (int n = 0; n < 2 * NS; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) l_run[e >> 1] += ptx::ex2(fmaf(s[n][e], P.sl2, -mus[e >> 1]));
+    }
+    float inv[2], mus[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float l = l_run[i];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        inv[i] = l > 0.f ? 1.f / l : 0.f;
+        mus[i] = m_run[i] == -INFINITY ? 0.f : m_run[i] * P.sl2;
+    }
+    // ---- sweep two: normalised weights, rows (+)= W V, 64 columns at a time ----
+    for (int c = 0; c < n_pass; ++c) {
+        scores(c, s);
+        uint32_t pa[NS][4];   // the weights as A fragments of the 16-key steps
+#pragma unroll
+        for (int n = 0; n < 2 * NS; ++n) {
+            float w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) w[e] = ptx::ex2(fmaf(s[n][e], P.sl2, -mus[e >> 1])) * inv[e >> 1];
+            pa[n >> 1][(n & 1) * 2] = ptx::Mma<T>::pack(w[0], w[1]);
+            pa[n >> 1][(n & 1) * 2 + 1] = ptx::Mma<T>::pack(w[2], w[3]);
+        }
+        const bool last = c + 1 == n_pass;
+        for (int sl = 0; sl < n_slices; ++sl) {
+            stage(vb_ptr, c, sl);
+            const uint32_t v_addr = ptx::smem_u32(sBuf + st_off);
+            float acc[2 * KS][4];
+#pragma unroll
+            for (int n = 0; n < 2 * KS; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < NS; ++kk)
+#pragma unroll
+                for (int d2 = 0; d2 < KS; ++d2) {
+                    uint32_t vf[4];
+                    ptx::ldmatrix_x4_trans(vf, v_addr + (uint32_t)(((kk * 16 + r8 + (m4 & 1) * 8) * LD + d2 * 16 + (m4 >> 1) * 8) * 2));
+                    ptx::Mma<T>::run(acc[2 * d2], pa[kk], vf[0], vf[1]);
+                    ptx::Mma<T>::run(acc[2 * d2 + 1], pa[kk], vf[2], vf[3]);
+                }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                if ((i == 0 ? row_a : row_b) >= P.Sq1) continue;
+                const int64_t off = (i == 0 ? off_a : off_b) + sl * 64 + 2 * t;
+#pragma unroll
+                for (int n = 0; n < 2 * KS; ++n) {
+                    if (sl * 64 + n * 8 + 2 * t >= D) continue;
+                    float2 val = make_float2(acc[n][2 * i], acc[n][2 * i + 1]);
+                    float2 *sc = reinterpret_cast<float2 *>(scratch + off + n * 8);
+                    if (c > 0) { const float2 old = *sc; val.x += old.x; val.y += old.y; }
+                    if (last) *reinterpret_cast<uint32_t *>(o + off + n * 8) = ptx::Mma<T>::pack(val.x, val.y);
+                    else *sc = val;
+                }
+            }
+        }
+    }
+}
+
+template <typename T>
+int launch_wide_passes(const Problem &p) {
+    const int64_t dil = p.pat.dilation;
+    WinDParams wp;
+    wp.Sq1 = (int32_t)(p.Sq / dil);
+    wp.Skv1 = (int32_t)(p.Skv / dil);
+    wp.off1 = (int32_t)(p.pat.q_offset / dil);
+    wp.HH = (int32_t)(p.H * dil);
+    wp.left = (int32_t)std::min<int64_t>(p.pat.left, wp.Skv1);
+    wp.right = (int32_t)std::min<int64_t>(p.pat.right, wp.Skv1);
+    wp.sl2 = p.scale * 1.4426950408889634f;
+    wp.D = (int32_t)p.D;
+    auto kern = window_d_wide_passes_kernel<T>;
+    constexpr size_t smem = (size_t)(48 + 16 * 5) * 72 * sizeof(T);
+    if (int rc = ensure_dynamic_smem((const void *)kern, smem, "cudaFuncSetAttribute(window_d_wide_passes_kernel)")) return rc;
+    const dim3 grid((unsigned)wp.HH, (unsigned)((wp.Sq1 + kTQ - 1) / kTQ), (unsigned)p.B);
+    kern<<<grid, kThreads, smem, p.stream>>>((const T *)p.q, (const T *)p.k, (const T *)p.v, (T *)p.o, (float *)p.workspace, wp);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "window_d_wide_passes_kernel launch");
+    note_kernel("mma_window_d");
+    return MAT_OK;
+}
+
 // NS = 0: the 64-key chunks; otherwise the per-warp walk in passes of NS 16-key steps
 template <typename T, int D, int NS>
 int launch_d(const Problem &p) {
@@ -566,14 +768,25 @@ int launch_d(const Problem &p) {
 // or 128, whole
 // tensors (no neighbour shards), 16-byte aligned.  MAT_WINDOW_D_KERNEL=rowwarp keeps the one-warp-per-row
 // kernel (a measurement aid).
+// fp32 scratch (a copy of the output's shape) for heads that go 64 columns at a time when the window takes a warp
+// more than one pass; 0 otherwise
+size_t mma_window_d_scratch_bytes(const Problem &p) {
+    if (p.pat.kind != MAT_WINDOW || (p.dtype != MAT_BF16 && p.dtype != MAT_F16)) return 0;
+    if (p.D % 8 || p.D < 8 || p.D > 512 || p.D == 64 || !(p.D > 128 || p.D % 16) || p.pat.dilation < 1) return 0;
+    const int64_t skv1 = p.Skv / p.pat.dilation;
+    if (std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16 <= 144) return 0;
+    return (size_t)p.B * p.Sq * p.H * p.D * sizeof(float);
+}
+
 bool mma_window_d_supports(const Problem &p) {
     if (p.pat.kind != MAT_WINDOW) return false;
     if (p.dtype != MAT_BF16 && p.dtype != MAT_F16) return false;
     if (p.D % 8 || p.D < 8 || p.D == 64) return false;   // (64: the TMA / tcgen05 kernels; rows stay 16-byte aligned)
-    if (p.D > 128 || p.D % 16) {   // wide heads: multiples of 64 up to 512, windows one pass of a warp covers (at most 128 taps between the sides)
+    if (p.D > 128 || p.D % 16) {   // 64 columns at a time: windows one pass of a warp covers, or an fp32 scratch copy of the output
         if (p.D > 512 || p.pat.dilation < 1) return false;
-        const int64_t skv1 = p.Skv / p.pat.dilation;
-        if (std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16 > 144) return false;
+        if (mma_window_d_scratch_bytes(p) > 0 && (!p.workspace || p.workspace_bytes < mma_window_d_scratch_bytes(p) ||
+                                                  (uintptr_t)p.workspace % 16))
+            return false;
     }
     if (p.k_prev || p.k_next || p.q_ts || p.k_ts || p.v_ts || p.o_ts) return false;
     const uintptr_t al = (uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.o;
@@ -621,6 +834,8 @@ int launch_mma_window_d(const Problem &p) {
     const bool sliced128 = p.D == 128 && !(force && (std::strcmp(force, "whole") == 0 || std::strcmp(force, "chunks") == 0)) &&
                            std::min<int64_t>(p.pat.left, p.Skv / p.pat.dilation) +
                                std::min<int64_t>(p.pat.right, p.Skv / p.pat.dilation) + 16 <= 144;
+    if ((p.D > 128 || p.D % 16) && mma_window_d_scratch_bytes(p) > 0)
+        return p.dtype == MAT_BF16 ? launch_wide_passes<__nv_bfloat16>(p) : launch_wide_passes<__half>(p);
     if (p.D > 128 || p.D % 16 || sliced128) {
         const int64_t skv1 = p.Skv / p.pat.dilation;
         const bool five = std::min<int64_t>(p.pat.left, skv1) + std::min<int64_t>(p.pat.right, skv1) + 16 <= 80;

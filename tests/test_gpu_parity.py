@@ -145,7 +145,7 @@ def test_16bit_windows_with_head_width_32_and_128(monkeypatch, spec, D):
 def test_16bit_windows_with_wide_heads(spec, D):
     """16-bit windows of at most 128 taps between their sides with one wide head (the reference's layer passes
     D = model_dim, src/layers/sparse_attention.py:71-78): the head dimension goes through the warp-level tensor-core
-    kernel 64 columns at a time.  Wider windows on such heads stay on the one-warp-per-row kernel."""
+    kernel 64 columns at a time."""
     for dtype in (torch.bfloat16, torch.float16):
         for B, S, H, off in [(1, 1024, 1, 0), (2, 330, 2, 0), (1, 64, 1, 0), (1, 200, 2, 48), (1, 7, 1, 0)]:
             S = S - S % spec.dilation if S >= spec.dilation else spec.dilation
@@ -155,11 +155,13 @@ def test_16bit_windows_with_wide_heads(spec, D):
             got = run(sp, q, k, v)
             assert nat.last_kernel() == "mma_window_d"
             check_close(got, oracle_out(q, k, v, sp), dtype)
-    q, k, v = seeded_qkv(34, 1, 330, 1, D, torch.bfloat16)
-    wide = PatternSpec.causal_window(300)
-    got = run(wide, q, k, v)
-    assert nat.last_kernel() == "rowwarp"
-    check_close(got, oracle_out(q, k, v, wide), torch.bfloat16)
+    # wider windows, up to dense: several passes per warp, the partial rows in an fp32 scratch (the workspace)
+    for wide, S in ((PatternSpec.causal_window(300), 330), (PatternSpec.sliding_window(200), 1000), (PatternSpec.sliding_window(5000), 700)):
+        for dtype in (torch.bfloat16, torch.float16):
+            q, k, v = seeded_qkv(34, 2, S, 2, D, dtype)
+            got = run(wide, q, k, v)
+            assert nat.last_kernel() == "mma_window_d"
+            check_close(got, oracle_out(q, k, v, wide), dtype)
 
 
 @pytest.mark.parametrize("B,S,H,D", [(1, 1, 1, 1), (1, 7, 2, 5), (2, 33, 1, 13), (1, 100, 3, 40), (1, 65, 2, 96),
