@@ -323,6 +323,10 @@ size_t mat_sparse_attn_bwd_general_workspace_bytes(int64_t B, int64_t S, int64_t
     n = (n + 255) & ~(size_t)255;
     if (spec->kind == MAT_LONGFORMER && bwd_longformer_mma_supports(B, S, H, D, dtype, spec->n_global))
         n += bwd_longformer_mma_extra_bytes(B, H, spec->n_global);
+    // (16-bit heads that go 64 columns at a time, windows of many passes: fp32 copies of the three outputs' shape;
+    // a call that brings only the statistics' bytes runs those on the warp-level kernels instead)
+    if (spec->kind == MAT_WINDOW && spec->dilation >= 1)
+        n += bwd_d_mma_scratch_bytes(B, S, H, D, dtype, spec->dilation, std::min<int64_t>(spec->left, S), std::min<int64_t>(spec->right, S));
     return n;
 }
 
@@ -355,7 +359,11 @@ int mat_sparse_attn_bwd_general(const void *q, const void *k, const void *v, con
     }
     if (!q || !k || !v || !dout || !dq || !dk || !dv) return fail(MAT_ERR_INVALID, "tensor pointers must be non-NULL");
     if (B <= 0 || S <= 0 || H <= 0 || D <= 0) return fail(MAT_ERR_INVALID, "all tensor dimensions must be > 0");
-    const size_t need = mat_sparse_attn_bwd_general_workspace_bytes(B, S, H, D, dtype, spec);
+    const size_t full = mat_sparse_attn_bwd_general_workspace_bytes(B, S, H, D, dtype, spec);
+    const size_t scratch_bytes = spec->kind == MAT_WINDOW
+        ? bwd_d_mma_scratch_bytes(B, S, H, D, dtype, spec->dilation, std::min<int64_t>(spec->left, S), std::min<int64_t>(spec->right, S)) : 0;
+    const size_t need = full - scratch_bytes;   // the scratch is optional: without it those problems take the warp-level kernels
+    const bool have_scratch = scratch_bytes > 0 && workspace && workspace_bytes >= full;
     if (!workspace || workspace_bytes < need || ((uintptr_t)workspace % 256) != 0)
         return fail(MAT_ERR_WORKSPACE, "workspace of %zu bytes (256-byte aligned) required, got %zu", need,
                     workspace ? workspace_bytes : (size_t)0);
@@ -391,8 +399,9 @@ int mat_sparse_attn_bwd_general(const void *q, const void *k, const void *v, con
     if (spec->kind == MAT_BLOCK && al % 16 == 0 && bwd_block_mma_supports(B, S, H, D, dtype, spec->block))
         return launch_bwd_block_mma(q, k, v, dout, dq, dk, dv, stats, B, S, H, dtype, spec->block, spec->causal,
                                     spec->blk_rowptr, spec->blk_colidx, t_rowptr, t_colidx, a.scale, st);
-    if (spec->kind == MAT_WINDOW && al % 16 == 0 && bwd_d_mma_supports(B, S, H, D, dtype, a.dil, a.left, a.right))
-        return launch_bwd_d_mma(q, k, v, dout, dq, dk, dv, stats, B, S, H, D, dtype, a.left, a.right, a.dil, a.scale, st);
+    if (spec->kind == MAT_WINDOW && al % 16 == 0 && bwd_d_mma_supports(B, S, H, D, dtype, a.dil, a.left, a.right, have_scratch))
+        return launch_bwd_d_mma(q, k, v, dout, dq, dk, dv, stats, B, S, H, D, dtype, a.left, a.right, a.dil, a.scale,
+                                have_scratch ? (float *)((uint8_t *)workspace + (full - scratch_bytes)) : nullptr, st);
     if (spec->kind == MAT_WINDOW && al % 16 == 0 && bwd_f32_mma_supports(B, S, H, D, dtype, a.dil))
         return launch_bwd_f32_mma(q, k, v, dout, dq, dk, dv, stats, B, S, H, D, a.left, a.right, a.dil, a.scale, st);
     if (spec->kind == MAT_WINDOW && al % 16 == 0 && bwd_mma_supports(B, S, H, D, dtype, a.left, a.right, a.dil))

@@ -28,6 +28,7 @@ struct BwdDArgs {
     int32_t left, right;
     float scale;
     int32_t D;                 // head width (read by the kernel for wide heads only)
+    float *scr_dq, *scr_dk, *scr_dv;   // wide heads, walks of more than two passes: fp32 copies of the three outputs' shape, or null
 };
 
 __device__ __forceinline__ void cp_async16(void *dst, const void *src, int bytes) {
@@ -296,7 +297,8 @@ bwd_d_kernel(const BwdDArgs a) {
 // of their operands, staged one slice at a time; the weights (P^T or dS, rounded to the input type) are formed once,
 // and every 64-column slice of the output is their product with one more staged slice, written out - added to what
 // the first pass of the same rows wrote when the walk has a second one (a row of dQ, dK or dV belongs to one thread
-// pair of one CTA: no atomics).  Registers hold one pass's two score tiles and one slice's fragments whatever D is.
+// pair of one CTA: no atomics).  Walks of more passes keep the sums in fp32 copies of the outputs' shape (the
+// caller's workspace) until a row's last pass rounds them: 16-bit values cannot carry fifty partial sums.  Registers hold one pass's two score tiles and one slice's fragments whatever D is.
 // A one-pass walk (windows of at most 64 taps) keeps S and dP from the statistics sweep instead of recomputing them.
 template <typename T, int PASS, int NS>
 __global__ void __launch_bounds__(kThreads)
@@ -402,6 +404,8 @@ bwd_d_wide_kernel(const BwdDArgs a) {
         }
     };
     // out rows (+)= W (the pass's weights as A fragments) . Y, 64 columns of Y at a time
+    float *const out32 = (PASS == kRows ? a.scr_dq : PASS == kColsV ? a.scr_dv : a.scr_dk) == nullptr
+                             ? nullptr : (PASS == kRows ? a.scr_dq : PASS == kColsV ? a.scr_dv : a.scr_dk) + head;
     auto emit = [&](int c, const uint32_t (&wa)[NS][4], const T *y, T *out, int st_off) {
         const int first = col_lo + c * 16 * NS;
         for (int slice = 0; slice < n_slices; ++slice) {
@@ -433,7 +437,11 @@ bwd_d_wide_kernel(const BwdDArgs a) {
                 for (int n = 0; n < 2 * KS; ++n) {
                     if (slice * 64 + n * 8 + 2 * t >= D) continue;
                     float vx = acc[n][2 * i], vy = acc[n][2 * i + 1];
-                    if (c > 0) {   // the first pass of these rows wrote here
+                    if (out32) {   // many passes: the sums stay in fp32 until the row's last pass rounds them
+                        float2 *sc = reinterpret_cast<float2 *>(out32 + (int64_t)rows[i] * tok + slice * 64 + 2 * t + n * 8);
+                        if (c > 0) { const float2 old = *sc; vx += old.x; vy += old.y; }
+                        if (c + 1 < n_pass) { *sc = make_float2(vx, vy); continue; }
+                    } else if (c > 0) {   // the first pass of these rows wrote here
                         const uint32_t old = *reinterpret_cast<const uint32_t *>(dst + n * 8);
                         vx += M::lo(old);
                         vy += M::hi(old);
@@ -604,12 +612,21 @@ int launch_any_d(const BwdDArgs &a, int64_t B, int64_t D, cudaStream_t stream) {
 // 144 taps with a head width of 192, 256, ... 512 (two passes of a warp's walk at most: the second pass adds to 16-bit
 // values the first one wrote); lengths a multiple of the dilation, 16-byte aligned tensors.  MAT_BWD_KERNEL=warp
 // keeps the one-warp-per-row kernels.
-bool bwd_d_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil, int64_t left, int64_t right) {
+size_t bwd_d_mma_scratch_bytes(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil, int64_t left, int64_t right) {
+    if (dtype != MAT_BF16 && dtype != MAT_F16) return 0;
+    if (D % 8 || D < 8 || D > 512 || D == 64 || !(D > 128 || D % 16) || dil < 1 || S % dil != 0) return 0;
+    const int64_t Sv1 = S / dil;
+    if (std::min(left, Sv1) + std::min(right, Sv1) + 16 <= 160) return 0;
+    return 3 * (((size_t)B * S * H * D * sizeof(float) + 255) & ~(size_t)255);
+}
+
+bool bwd_d_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil, int64_t left, int64_t right,
+                        bool have_scratch) {
     if (dtype != MAT_BF16 && dtype != MAT_F16) return false;
     if (D % 8 || D < 8 || D == 64 || dil < 1 || S % dil != 0) return false;   // (rows stay 16-byte aligned)
     if (D > 128 || D % 16) {
         const int64_t Sv1 = S / dil;
-        if (D > 512 || std::min(left, Sv1) + std::min(right, Sv1) + 16 > 160) return false;
+        if (D > 512 || (std::min(left, Sv1) + std::min(right, Sv1) + 16 > 160 && !have_scratch)) return false;
     }
     const char *env = std::getenv("MAT_BWD_KERNEL");
     if (env && std::strcmp(env, "warp") == 0) return false;
@@ -619,8 +636,13 @@ bool bwd_d_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, i
 
 int launch_bwd_d_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk, void *dv,
                      float2 *stats, int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t left, int64_t right,
-                     int64_t dil, float scale, cudaStream_t stream) {
+                     int64_t dil, float scale, float *scratch, cudaStream_t stream) {
     BwdDArgs a;
+    a.scr_dq = a.scr_dk = a.scr_dv = nullptr;
+    if (scratch && bwd_d_mma_scratch_bytes(B, S, H, D, dtype, dil, left, right)) {
+        const size_t one = bwd_d_mma_scratch_bytes(B, S, H, D, dtype, dil, left, right) / 3 / sizeof(float);
+        a.scr_dq = scratch; a.scr_dk = scratch + one; a.scr_dv = scratch + 2 * one;
+    }
     a.q = q; a.k = k; a.v = v; a.go = dout;
     a.dq = dq; a.dk = dk; a.dv = dv;
     a.stats = stats;

@@ -115,10 +115,12 @@ bool bwd_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int
 int launch_bwd_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk, void *dv,
                    float2 *stats, int64_t B, int64_t S, int64_t H, int dtype, int64_t left, int64_t right,
                    int64_t dil, float scale, cudaStream_t stream);
-bool bwd_d_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil, int64_t left, int64_t right);   // bwd_d_mma.cu
+bool bwd_d_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil, int64_t left, int64_t right,
+                        bool have_scratch);   // bwd_d_mma.cu
+size_t bwd_d_mma_scratch_bytes(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil, int64_t left, int64_t right);
 int launch_bwd_d_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk, void *dv,
                      float2 *stats, int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t left, int64_t right,
-                     int64_t dil, float scale, cudaStream_t stream);
+                     int64_t dil, float scale, float *scratch, cudaStream_t stream);
 bool bwd_f32_mma_supports(int64_t B, int64_t S, int64_t H, int64_t D, int dtype, int64_t dil);   // bwd_f32_mma.cu
 int launch_bwd_f32_mma(const void *q, const void *k, const void *v, const void *dout, void *dq, void *dk, void *dv,
                        float2 *stats, int64_t B, int64_t S, int64_t H, int64_t D, int64_t left, int64_t right,

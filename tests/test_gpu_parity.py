@@ -756,8 +756,7 @@ def test_fp32_backward_on_tensor_cores(monkeypatch, walk, B, S, H, left, right, 
 def test_16bit_backward_for_wide_heads(monkeypatch, dtype, D, B, S, H, left, right, dil):
     """The 16-bit backward for one wide head (192 to 512 columns; the reference's layer passes D = model_dim) with a
     window of at most 144 taps: the tensor-core passes with the head dimension 64 columns at a time, against autograd
-    in fp64 through a dense masked softmax on the same rounded inputs and against the one-warp-per-row kernels.
-    Wider windows on such heads stay on the one-warp-per-row kernels."""
+    in fp64 through a dense masked softmax on the same rounded inputs and against the one-warp-per-row kernels."""
     spec = PatternSpec(left=left, right=right, dilation=dil)
     q, k, v = seeded_qkv(91, B, S, H, D, dtype)
     go = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(92)).to(dtype)
@@ -772,8 +771,16 @@ def test_16bit_backward_for_wide_heads(monkeypatch, dtype, D, B, S, H, left, rig
         err = float((a.cpu().double() - r.grad).abs().max())
         assert err <= tol * max(1.0, float(r.grad.abs().max())), f"{name} vs fp64 autograd: {err}"
     if S // dil >= 200:   # (a window clamps to the sequence, so a short sequence makes every window narrow)
-        ext.backward_pattern(*args, PatternSpec(left=100, right=100, dilation=dil))
-        assert nat.last_kernel() == "bwd_window"
+        # walks of more than two passes keep their sums in fp32 copies of the outputs' shape (the workspace)
+        for wl, wr in ((100, 100), (S, S)):
+            wide = PatternSpec(left=wl, right=wr, dilation=dil)
+            gw = ext.backward_pattern(*args, wide)
+            assert nat.last_kernel() == "bwd_d_mma" and nat.device_status() == 0
+            refw = [t.double().requires_grad_(True) for t in (q, k, v)]
+            masked_dense_attention(*refw, wl, wr, dil).backward(go.double())
+            for name, a, r in zip(("dQ", "dK", "dV"), gw, refw):
+                err = float((a.cpu().double() - r.grad).abs().max())
+                assert err <= tol * max(1.0, float(r.grad.abs().max())), f"wide window {name} vs fp64 autograd: {err}"
     monkeypatch.setenv("MAT_BWD_KERNEL", "warp")
     want = ext.backward_pattern(*args, spec)
     assert nat.last_kernel() == "bwd_window"
