@@ -163,8 +163,12 @@ int mat_sparse_attn_fwd_sharded(const void *q, const void *k, const void *v, voi
  * 16-bit inputs with D = 64 and S a multiple of the dilation run on tensor-core
  * kernels (probabilities rounded to the input type for the second products; the
  * band of a window with at most 128 taps between its two sides stays in shared
- * memory, wider windows and dense stream it); everything else, fp32 included, on
- * warp-level kernels with fp32 math throughout.
+ * memory, wider windows and dense stream it).  So do 16-bit inputs with any other
+ * D that is a multiple of 8 up to 512, and fp32 inputs with a D that is a multiple
+ * of 4 up to 512 (every product as three TF32 products of error-compensated
+ * halves: fp32 accuracy).  Everything else (other head widths, tensors off a
+ * 16-byte boundary, lengths the dilation does not divide) runs on warp-level
+ * kernels with fp32 math throughout.
  */
 int mat_sparse_attn_bwd(const void *q, const void *k, const void *v, const void *dout,
                         void *dq, void *dk, void *dv, int64_t B, int64_t S, int64_t H, int64_t D,
@@ -190,7 +194,10 @@ size_t mat_sparse_attn_bwd_workspace_bytes(int64_t B, int64_t S, int64_t H);
  * the whole sequence); other shapes on the warp-level kernels (fp32 math, any
  * D <= 512).  Deterministic.  workspace: mat_sparse_attn_bwd_general_workspace_bytes()
  * bytes (what mat_sparse_attn_bwd wants, plus the gathered rows of a Longformer
- * call), 256-byte aligned.
+ * call, plus fp32 copies of the three outputs for a 16-bit window of more than 144
+ * taps on a head of more than 128 columns or of a width off the multiples of 16;
+ * a window call that brings only mat_sparse_attn_bwd_workspace_bytes() is served
+ * too, that case then on the warp-level kernels), 256-byte aligned.
  */
 size_t mat_sparse_attn_bwd_general_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t D, int dtype,
                                                    const mat_pattern_spec *spec);
